@@ -1,0 +1,139 @@
+/*
+ * ktir_b200 — C ABI of the B200 execution backend for KTIR kernels.
+ *
+ * The reference interpreter is pure Python and has no foreign-function layer;
+ * every entry point below names the Python routine whose work it takes over
+ * (paths are relative to the reference project root).  All functions return 0
+ * on success or a negative KTB_E_* code; ktb_last_error() gives the message.
+ * Pointers named `dev*`/`arena` are device addresses, everything else is host
+ * memory that the call copies before returning.  One context per (process,
+ * device); a context is not thread-safe.
+ */
+#ifndef KTIR_B200_H
+#define KTIR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ktb_ctx ktb_ctx;
+
+enum { KTB_OK = 0, KTB_E_CUDA = -1, KTB_E_ARG = -2, KTB_E_UNSUPPORTED = -3, KTB_E_DEVICE_STATUS = -4 };
+
+/* element type codes */
+enum { KTB_F16 = 0, KTB_F32 = 1, KTB_I32 = 2, KTB_I64 = 3, KTB_I1 = 4 };
+
+/* Device status word read back by ktb_sync(): kernels never trap; they record
+ * what went wrong here and return (ktir_cpu/ops/memory_ops.py:378-382 raises
+ * IndexError for a negative indirect index; ktir_cpu/grid.py:615-621 reports
+ * deadlock). */
+typedef struct {
+    int32_t negative_index;   /* != 0: an indirect index was negative */
+    int32_t bad_index_value;  /* the offending value */
+    int32_t wait_timeout;     /* != 0: a bounded device-side wait ran out */
+    int32_t wait_site;        /* which wait gave up */
+    int32_t reserved[4];
+} ktb_status;
+
+/* ---- context, memory, transfers ------------------------------------------
+ * Replaces SpyreMemoryHierarchy/HBMSimulator set-up, argument upload and
+ * read-back in KTIRInterpreter.execute_function
+ * (ktir_cpu/interpreter.py:95-120,156-194; ktir_cpu/memory.py:311-398). */
+int ktb_init(int device, ktb_ctx** out);
+int ktb_destroy(ktb_ctx* ctx);
+const char* ktb_last_error(ktb_ctx* ctx);
+int ktb_alloc(ktb_ctx* ctx, size_t bytes, void** dev_ptr);
+int ktb_free(ktb_ctx* ctx, void* dev_ptr);
+int ktb_alloc_host(ktb_ctx* ctx, size_t bytes, void** host_ptr);   /* pinned */
+int ktb_free_host(ktb_ctx* ctx, void* host_ptr);
+int ktb_memset(ktb_ctx* ctx, void* dev_ptr, int byte_value, size_t bytes);
+int ktb_h2d(ktb_ctx* ctx, void* dev_dst, const void* host_src, size_t bytes);
+int ktb_d2h(ktb_ctx* ctx, void* host_dst, const void* dev_src, size_t bytes);
+int ktb_d2d(ktb_ctx* ctx, void* dev_dst, const void* dev_src, size_t bytes);
+int ktb_sync(ktb_ctx* ctx, ktb_status* status_out);
+/* Use an existing CUDA stream (e.g. torch's current stream) for all work. */
+int ktb_set_stream(ktb_ctx* ctx, uint64_t cuda_stream);
+/* CUDA-event timing on the context's stream; slot in [0, 64). */
+int ktb_event_record(ktb_ctx* ctx, int slot);
+int ktb_event_elapsed_ms(ktb_ctx* ctx, int slot_begin, int slot_end, float* ms_out);
+/* Write `bytes` (> L2 size) of scratch so the next kernel starts with a cold L2. */
+int ktb_flush_l2(ktb_ctx* ctx);
+/* Number of kernels this library has launched on the context so far. */
+int64_t ktb_launch_count(ktb_ctx* ctx);
+
+/* ---- elementwise register programs ---------------------------------------
+ * A short straight-line program over f32 registers; inputs are loaded into
+ * registers 0..n_in-1.  Replaces per-op NumPy dispatch of the arith/math
+ * dialects (ktir_cpu/dialects/_helpers.py:39-72, ktir_cpu/dialects/arith_ops.py:49-308,
+ * ktir_cpu/ops/math_ops.py:27-138).  Setting KTB_VM_ROUND16 on an op rounds its
+ * result to f16 (round-to-nearest-even), which is how NumPy evaluates f16 tiles. */
+enum {
+    KTB_VM_MOV = 0, KTB_VM_CONST, KTB_VM_ADD, KTB_VM_SUB, KTB_VM_MUL, KTB_VM_DIV,
+    KTB_VM_MAX, KTB_VM_MAXNUM, KTB_VM_MIN, KTB_VM_MINNUM, KTB_VM_NEG, KTB_VM_ABS,
+    KTB_VM_EXP, KTB_VM_LOG, KTB_VM_LOG2, KTB_VM_SQRT, KTB_VM_RSQRT, KTB_VM_TANH,
+    KTB_VM_SIN, KTB_VM_COS, KTB_VM_FMA, KTB_VM_NOPS,
+    KTB_VM_ROUND16 = 0x100
+};
+#define KTB_VM_MAX_OPS 12
+#define KTB_VM_MAX_IN 4
+#define KTB_VM_REGS 8
+
+typedef struct {
+    int32_t opcode;      /* KTB_VM_* | optional KTB_VM_ROUND16 */
+    int32_t dst, a, b, c;
+    float imm;
+} ktb_vm_op;
+
+typedef struct {
+    int32_t n_in;
+    int32_t n_ops;
+    int32_t result_reg;
+    int32_t reserved;
+    ktb_vm_op ops[KTB_VM_MAX_OPS];
+} ktb_vm_program;
+
+/* ---- fused load -> elementwise -> store over all grid cores ----------------
+ * One launch covers every (core, loop iteration) work item of a statement:
+ * ktdp.load of each operand tile (ktir_cpu/dialects/ktdp_ops.py:200-227,
+ * ktir_cpu/ops/memory_ops.py:723-800), the elementwise ops between, and the
+ * ktdp.store (ktdp_ops.py:230-260, memory_ops.py:802-865).  Tiles are rows x
+ * cols with unit column stride; item_offsets holds, per item, the element
+ * offset of each input and then of the output, relative to `arena`. */
+typedef struct {
+    void* arena;
+    const int64_t* dev_item_offsets;   /* [n_items][n_in + 1] */
+    int64_t n_items;
+    int32_t rows, cols;
+    int64_t row_stride[KTB_VM_MAX_IN + 1];   /* elements; inputs then output */
+    int32_t dtype[KTB_VM_MAX_IN + 1];        /* KTB_F16 / KTB_F32 */
+    int32_t vector_ok;   /* 1: cols, every item offset and row stride are multiples of 8 elements */
+    ktb_vm_program program;
+} ktb_ew_args;
+int ktb_launch_ew_stream(ktb_ctx* ctx, const ktb_ew_args* args);
+
+/* ---- fused row softmax --------------------------------------------------------
+ * load -> [extf] -> reduce(max) -> sub -> exp -> reduce(add) -> div -> [truncf]
+ * -> store, one row per CTA.  Replaces the op sequence a softmax kernel runs per
+ * row through linalg.reduce's pairwise fold (ktir_cpu/dialects/linalg_ops.py:86-246),
+ * math.exp (ktir_cpu/ops/_helpers.py:50-60) and the arith binops.  The reduction
+ * follows the same halving order (x[i] op x[i+h]) when cols is a power of two. */
+typedef struct {
+    void* arena;
+    const int64_t* dev_item_offsets;   /* [n_items][2]: input, output element offsets */
+    int64_t n_items;
+    int32_t rows_per_item, cols;
+    int64_t in_row_stride, out_row_stride;   /* elements */
+    int32_t in_dtype, out_dtype;             /* KTB_F16 / KTB_F32 */
+    int32_t f16_arith;      /* 1: every op rounds to f16 (tile dtype f16 throughout) */
+    int32_t max_is_maxnum;  /* 1: arith.maxnumf (NaN ignored), 0: maximumf */
+    float max_init, sum_init;   /* the `outs` initial values of the two reductions */
+} ktb_softmax_args;
+int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KTIR_B200_H */

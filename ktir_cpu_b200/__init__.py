@@ -1,0 +1,11 @@
+"""ktir_cpu_b200 — B200-native execution backend for KTIR kernels.
+
+Public surface mirrors ``ktir_cpu`` (ktir_cpu/__init__.py:23-27):
+``KTIRInterpreter`` with ``load`` / ``arg_names`` / ``tensor_input_output_sizes`` /
+``execute_function`` / ``get_latency_report``, plus ``KTIRParserBase`` as the parser seam.
+"""
+from .interpreter import KTIRInterpreter, Session
+from .parser import KTIRParser, KTIRParserBase
+from .trace import Unsupported
+
+__all__ = ["KTIRInterpreter", "KTIRParser", "KTIRParserBase", "Session", "Unsupported"]

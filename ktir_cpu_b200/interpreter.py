@@ -1,0 +1,216 @@
+"""``KTIRInterpreter`` — drop-in for the reference class of the same name
+(ktir_cpu/interpreter.py:40-194, 312-341), executing on a B200.
+
+``load`` / ``arg_names`` / ``tensor_input_output_sizes`` / ``execute_function``
+/ ``get_latency_report`` keep their signatures and error behaviour.  Instead of
+interpreting op by op, ``execute_function`` traces the function once for the
+whole grid, lowers it to a launch plan (cached per tensor layout and scalar
+arguments) and runs the plan through ``libktir_b200``.
+
+Memory layout: one device arena whose byte offset equals the KTIR byte address
+(first tensor at 0x10000, each rounded up to a 128-byte stick, as
+ktir_cpu/memory.py:330-352 allocates), so SSA pointer values — element indices
+— mean the same thing on the device as in the reference.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from . import runtime as R
+from .dtypes import bytes_per_elem, to_ktir_dtype
+from .ir import IRModule
+from .lower import Allocation, ArenaMap, Plan, lower
+from .parser import KTIRParser, KTIRParserBase
+from .trace import Tracer
+
+STICK = 128
+ARENA_BASE = 0x10000
+
+
+class Session:
+    """One function bound to one tensor layout: the arena in HBM plus its launch plan."""
+
+    def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
+                 scalars: Dict[str, Any]):
+        self.dev = dev
+        self.func = func
+        self.layout: Dict[str, Tuple[int, int, Tuple[int, ...], np.dtype]] = {}
+        nxt = ARENA_BASE
+        allocs = []
+        ptrs = {}
+        for name, shape, dt in tensors:
+            nbytes = int(np.prod(shape)) * dt.itemsize if len(shape) else dt.itemsize
+            kdt = to_ktir_dtype(dt)
+            self.layout[name] = (nxt, nbytes, tuple(shape), dt)
+            allocs.append(Allocation(name, nxt, nxt + nbytes, kdt))
+            ptrs[name] = nxt // bytes_per_elem(kdt)
+            nxt = (nxt + nbytes + STICK - 1) & ~(STICK - 1)
+        self.arena_bytes = nxt
+        self.arena = dev.alloc(self.arena_bytes + 256)
+        self.arena_map = ArenaMap(allocs)
+        try:
+            stores = Tracer(func, scalars, ptrs).run()
+            self.plan: Plan = lower(dev, stores, self.arena_map)
+        except Exception:
+            dev.free(self.arena)
+            self.arena = None
+            raise
+        self.written = set(self.plan.written)
+        self.no_upload = set(self.plan.fully_overwritten)
+        self.last_h2d_bytes = 0
+        self.last_d2h_bytes = 0
+
+    def upload(self, name: str, arr: np.ndarray):
+        off, nbytes, shape, dt = self.layout[name]
+        if nbytes:
+            return self.dev.h2d(self.arena + off, arr)
+        return arr
+
+    def run(self):
+        self.plan.launch(self.dev, self.arena)
+
+    def download(self, name: str, out: Optional[np.ndarray] = None, pool=None) -> np.ndarray:
+        off, nbytes, shape, dt = self.layout[name]
+        if out is None:
+            out = pool.empty(shape, dt) if pool is not None else np.empty(shape, dtype=dt)
+        if nbytes:
+            self.dev.d2h(out, self.arena + off)
+        return out
+
+    def device_ptr(self, name: str) -> int:
+        return self.arena + self.layout[name][0]
+
+    def close(self):
+        if self.arena is not None:
+            self.dev.sync()
+            self.plan.release(self.dev)
+            self.dev.free(self.arena)
+            self.arena = None
+
+
+def _scalar_key(v):
+    if isinstance(v, (np.floating, float)):
+        return ("f", type(v).__name__, float(v))
+    if isinstance(v, (bool, np.bool_)):
+        return ("b", bool(v))
+    if isinstance(v, (int, np.integer)):
+        return ("i", int(v))
+    return ("o", repr(v))
+
+
+class KTIRInterpreter:
+    """Executes KTIR functions on a B200 through ``libktir_b200`` (no CPU fallback)."""
+
+    def __init__(self, latency_config=None, trace_latency: bool = False,
+                 parser: Optional[KTIRParserBase] = None, device: int = 0, max_sessions: int = 8):
+        self.module: Optional[IRModule] = None
+        self._parser = parser
+        self._latency_config = latency_config
+        self._trace_latency = trace_latency
+        self._device_index = device
+        self._dev: Optional[R.Device] = None
+        self._sessions: Dict[Any, Session] = {}
+        self._max_sessions = max_sessions
+        self._latency_report = None
+        self._pool = None
+
+    # -- front end ------------------------------------------------------------
+    def load(self, ktir_source: str):
+        parser = self._parser if self._parser is not None else KTIRParser()
+        if "\n" in ktir_source or ktir_source.lstrip().startswith("module"):
+            self.module = parser.parse_module(ktir_source)
+        else:
+            with open(ktir_source) as f:
+                self.module = parser.parse_module(f.read())
+        self._drop_sessions()
+
+    def _require_module(self) -> IRModule:
+        if not self.module:
+            raise RuntimeError("No module loaded. Call load() first.")
+        return self.module
+
+    def arg_names(self, func_name: str) -> List[str]:
+        return self._require_module().get_function(func_name).arg_names
+
+    def tensor_input_output_sizes(self, func_name: str) -> Dict[str, Dict[str, Any]]:
+        return self._require_module().get_function(func_name).tensor_sizes
+
+    def get_latency_report(self):
+        return self._latency_report
+
+    # -- device -----------------------------------------------------------------
+    @property
+    def device(self) -> R.Device:
+        if self._dev is None:
+            self._dev = R.get_device(self._device_index)
+        return self._dev
+
+    def _drop_sessions(self):
+        for s in self._sessions.values():
+            s.close()
+        self._sessions = {}
+
+    def close(self):
+        self._drop_sessions()
+        if self._pool is not None:
+            self._pool.close()
+            self._pool = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def session(self, func_name: str, **kwargs) -> Session:
+        """The cached (function, tensor layout, scalar arguments) session for these arguments."""
+        func = self._require_module().get_function(func_name)
+        declared = func.arg_names
+        if kwargs and declared and not any(k in declared for k in kwargs):
+            if len(kwargs) == len(declared):
+                kwargs = dict(zip(declared, kwargs.values()))
+        tensors, scalars = [], {}
+        for k, v in kwargs.items():
+            if isinstance(v, np.ndarray):
+                to_ktir_dtype(v.dtype)           # ValueError for unsupported dtypes
+                tensors.append((k, tuple(v.shape), v.dtype))
+            else:
+                scalars[k] = v
+        key = (func_name, tuple((n, s, str(d)) for n, s, d in tensors),
+               tuple((k, _scalar_key(v)) for k, v in scalars.items()))
+        sess = self._sessions.get(key)
+        if sess is None:
+            if len(self._sessions) >= self._max_sessions:
+                old = next(iter(self._sessions))
+                self._sessions.pop(old).close()
+            sess = Session(self.device, func, tensors, scalars)
+            self._sessions[key] = sess
+        return sess, kwargs
+
+    def execute_function(self, func_name: str, **kwargs) -> Dict[str, np.ndarray]:
+        sess, kwargs = self.session(func_name, **kwargs)
+        if self._pool is None:
+            from .pinned import PinnedPool
+            self._pool = PinnedPool(self.device)
+        keep = []
+        h2d = d2h = 0
+        for k, v in kwargs.items():
+            # a tensor the kernel overwrites completely and never reads needs no upload
+            if isinstance(v, np.ndarray) and k not in sess.no_upload:
+                keep.append(sess.upload(k, v))
+                h2d += v.nbytes
+        sess.run()
+        outputs: Dict[str, np.ndarray] = {}
+        for k, v in kwargs.items():
+            if isinstance(v, np.ndarray):
+                if k in sess.written:
+                    outputs[k] = sess.download(k, pool=self._pool)
+                    d2h += v.nbytes
+                else:
+                    outputs[k] = np.array(v, copy=True)
+        sess.dev.sync()
+        sess.last_h2d_bytes, sess.last_d2h_bytes = h2d, d2h
+        del keep
+        return outputs

@@ -57,7 +57,8 @@ class IRFunction:
 
     @property
     def arg_names(self) -> List[str]:
-        return [n for n, _ in self.args]
+        """Argument names in declaration order, without the leading ``%``."""
+        return [n[1:] for n, _ in self.args]
 
 
 @dataclass

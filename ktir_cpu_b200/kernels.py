@@ -1,0 +1,249 @@
+"""KTIR source generators for the benchmark workloads.
+
+The reference ships its kernels as ``.mlir`` examples and notebook templates
+(examples/triton-ktir/*.mlir, notebooks/demo_gen_mlir.py:109-218); the sizes the
+benchmarks need do not exist as files there, so the text is produced here.
+Every generator returns a complete ``module { func.func ... }`` string that both
+this backend and the reference interpreter accept.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+
+def _box(shape: Sequence[int]) -> str:
+    dims = ", ".join(f"d{i}" for i in range(len(shape)))
+    cons = ", ".join(f"d{i} >= 0, -d{i} + {s - 1} >= 0" for i, s in enumerate(shape))
+    return f"affine_set<({dims}) : ({cons})>"
+
+
+def _ident(n: int) -> str:
+    dims = ", ".join(f"d{i}" for i in range(n))
+    return f"affine_map<({dims}) -> ({dims})>"
+
+
+def _xs(shape: Sequence[int], dtype: str) -> str:
+    return "x".join(str(s) for s in shape) + "x" + dtype
+
+
+def _rowmajor(shape: Sequence[int]):
+    st, acc = [], 1
+    for s in reversed(shape):
+        st.append(acc)
+        acc *= s
+    return list(reversed(st))
+
+
+def view(name: str, ptr: str, shape: Sequence[int], dtype: str, strides=None) -> str:
+    strides = strides or _rowmajor(shape)
+    return (f"    %{name} = ktdp.construct_memory_view %{ptr}, sizes: {list(shape)}, strides: {list(strides)} {{\n"
+            f"      coordinate_set = {_box(shape)}, memory_space = #ktdp.memory_space<global>\n"
+            f"    }} : memref<{_xs(shape, dtype)}>\n")
+
+
+def tile(name: str, vw: str, idx: Sequence[str], tshape: Sequence[int], vshape: Sequence[int],
+         dtype: str, indent: str = "    ") -> str:
+    return (f"{indent}%{name} = ktdp.construct_access_tile %{vw}[{', '.join(idx)}] {{\n"
+            f"{indent}  access_tile_set = {_box(tshape)},\n"
+            f"{indent}  access_tile_order = {_ident(len(tshape))}\n"
+            f"{indent}}} : memref<{_xs(vshape, dtype)}> -> !ktdp.access_tile<{_xs(tshape, 'index')}>\n")
+
+
+def vector_add(n: int = 4096, block: int = 128, cores: int = 32, dtype: str = "f16") -> str:
+    """out = x + y; core c adds blocks c, c + cores, ... of ``block`` elements.
+
+    With ``n == block * cores`` this is the single-block-per-core kernel of
+    examples/triton-ktir/vector_add_ktir.mlir (same name and arguments)."""
+    nblk = n // block
+    assert nblk * block == n and nblk % cores == 0
+    per_core = nblk // cores
+    t = f"tensor<{block}x{dtype}>"
+    at = f"!ktdp.access_tile<{block}xindex>"
+    body_indent = "    " if per_core == 1 else "      "
+    off = "%offset" if per_core == 1 else "%off"
+    body = (tile("x_tile", "x_view", [off], [block], [n], dtype, body_indent)
+            + tile("y_tile", "y_view", [off], [block], [n], dtype, body_indent)
+            + f"{body_indent}%x = ktdp.load %x_tile : {at} -> {t}\n"
+            + f"{body_indent}%y = ktdp.load %y_tile : {at} -> {t}\n"
+            + f"{body_indent}%output = arith.addf %x, %y : {t}\n"
+            + tile("output_tile", "output_view", [off], [block], [n], dtype, body_indent)
+            + f"{body_indent}ktdp.store %output, %output_tile : {t}, {at}\n")
+    if per_core == 1:
+        loop = body
+    else:
+        loop = (f"    %c0 = arith.constant 0 : index\n"
+                f"    %c1 = arith.constant 1 : index\n"
+                f"    %nblk = arith.constant {per_core} : index\n"
+                f"    scf.for %i = %c0 to %nblk step %c1 {{\n"
+                f"      %step = arith.muli %i, %BLOCK_SIZE : index\n"
+                f"      %off = arith.addi %offset, %step : index\n"
+                + body + "      scf.yield\n    }\n")
+    span = "%BLOCK_SIZE" if per_core == 1 else "%span"
+    pre = "" if per_core == 1 else (f"    %per_core = arith.constant {per_core} : index\n"
+                                    f"    %span = arith.muli %per_core, %BLOCK_SIZE : index\n")
+    return (f"module {{\n  func.func @add_kernel(%x_ptr: index, %y_ptr: index, %output_ptr: index, "
+            f"%BLOCK_SIZE: index) attributes {{grid = [{cores}, 1]}} {{\n"
+            f"    %core_id = ktdp.get_compute_tile_id : index\n" + pre
+            + f"    %offset = arith.muli %core_id, {span} : index\n"
+            + view("x_view", "x_ptr", [n], dtype) + view("y_view", "y_ptr", [n], dtype)
+            + view("output_view", "output_ptr", [n], dtype) + loop + "    return\n  }\n}\n")
+
+
+def softmax_rows(n_rows: int = 8192, n_cols: int = 4096, cores: int = 32, rows_per_iter: int = 8,
+                 f32_stats: bool = True) -> str:
+    """Row softmax; core c owns rows [c*R, (c+1)*R), R = n_rows/cores, ``rows_per_iter`` at a time.
+
+    f32_stats: load f16, extend to f32, max/exp/sum/div in f32, truncate to f16
+    (the configuration the benchmark is quoted on).  Otherwise all arithmetic
+    stays in f16 like examples/triton-ktir/softmax_fwd_ktir.mlir."""
+    R = n_rows // cores
+    r = rows_per_iter
+    assert R * cores == n_rows and R % r == 0
+    ct = "f32" if f32_stats else "f16"
+    t16, tc, tv = f"tensor<{r}x{n_cols}xf16>", f"tensor<{r}x{n_cols}x{ct}>", f"tensor<{r}x{ct}>"
+    at = f"!ktdp.access_tile<{r}x{n_cols}xindex>"
+    s = (f"module {{\n  func.func @softmax_kernel(%output_ptr: index, %input_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %rows = arith.constant {R} : index\n"
+         f"    %step = arith.constant {r} : index\n"
+         f"    %row0 = arith.muli %core_id, %rows : index\n"
+         f"    %row_end = arith.addi %row0, %rows : index\n")
+    s += view("input_view", "input_ptr", [n_rows, n_cols], "f16")
+    s += view("output_view", "output_ptr", [n_rows, n_cols], "f16")
+    s += "    scf.for %row = %row0 to %row_end step %step {\n"
+    s += tile("in_tile", "input_view", ["%row", "%c0"], [r, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += f"      %x16 = ktdp.load %in_tile : {at} -> {t16}\n"
+    if f32_stats:
+        s += f"      %x = arith.extf %x16 : {t16} to {tc}\n"
+        s += "      %ninf_bits = arith.constant 0xFF800000 : i32\n"
+        s += "      %ninf = arith.bitcast %ninf_bits : i32 to f32\n"
+        s += "      %zero = arith.constant 0.0 : f32\n"
+    else:
+        s += "      %ninf = arith.constant 0xFC00 : f16\n"
+        s += "      %zero = arith.constant 0.0 : f16\n"
+    xin = "%x" if f32_stats else "%x16"
+    s += (f"      %max_init = tensor.splat %ninf : {tv}\n"
+          f"      %row_max = linalg.reduce {{ arith.maximumf }} ins({xin} : {tc}) outs(%max_init : {tv}) dimensions = [1]\n"
+          f"      %bshape = tensor.empty() : {tc}\n"
+          f"      %max_b = linalg.broadcast ins(%row_max : {tv}) outs(%bshape : {tc}) dimensions = [1]\n"
+          f"      %shifted = arith.subf {xin}, %max_b : {tc}\n"
+          f"      %num = math.exp %shifted : {tc}\n"
+          f"      %sum_init = tensor.splat %zero : {tv}\n"
+          f"      %row_sum = linalg.reduce {{ arith.addf }} ins(%num : {tc}) outs(%sum_init : {tv}) dimensions = [1]\n"
+          f"      %sum_b = linalg.broadcast ins(%row_sum : {tv}) outs(%bshape : {tc}) dimensions = [1]\n"
+          f"      %y = arith.divf %num, %sum_b : {tc}\n")
+    if f32_stats:
+        s += f"      %y16 = arith.truncf %y : {tc} to {t16}\n"
+    yout = "%y16" if f32_stats else "%y"
+    s += tile("out_tile", "output_view", ["%row", "%c0"], [r, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += f"      ktdp.store {yout}, %out_tile : {t16}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n"
+    return s
+
+
+def _iat(name: str, vw: str, idx_view: str, base: str, rows: int, cols: int, n_table_rows: int,
+         n_idx: int, idx_dtype: str, indent: str) -> str:
+    return (f"{indent}%{name} = ktdp.construct_indirect_access_tile\n"
+            f"{indent}    intermediate_variables(%d0, %d1)\n"
+            f"{indent}    %{vw}[ind(%{idx_view}[{base} + %d0]), (%d1)] {{\n"
+            f"{indent}  variables_space_set = {_box([rows, cols])},\n"
+            f"{indent}  variables_space_order = {_ident(2)}\n"
+            f"{indent}}} : memref<{_xs([n_table_rows, cols], 'f16')}>, memref<{n_idx}x{idx_dtype}>"
+            f" -> !ktdp.access_tile<{rows}x{cols}xindex>\n")
+
+
+def gather_scale_scatter(n_table_rows: int = 65536, cols: int = 128, n_idx: int = 262144,
+                         tile_rows: int = 64, cores: int = 64, scale: float = 0.5,
+                         idx_dtype: str = "i32") -> str:
+    """out[idx] = out[idx] + scale * table[idx], ``tile_rows`` index entries per tile.
+
+    Per tile: gather table rows through the index vector, scale, load the
+    destination rows through the same indices, add, scatter back (duplicate
+    rows within a tile keep the last writer, tiles apply in order)."""
+    per_core = n_idx // cores
+    assert per_core * cores == n_idx and per_core % tile_rows == 0
+    t = f"tensor<{tile_rows}x{cols}xf16>"
+    at = f"!ktdp.access_tile<{tile_rows}x{cols}xindex>"
+    s = (f"module {{\n  func.func @gather_scale_scatter(%table_ptr: index, %idx_ptr: index, %out_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n"
+         f"    %tile_rows = arith.constant {tile_rows} : index\n"
+         f"    %begin = arith.muli %pid, %per_core : index\n"
+         f"    %end = arith.addi %begin, %per_core : index\n"
+         f"    %scale = arith.constant {float(scale)} : f16\n")
+    s += view("table", "table_ptr", [n_table_rows, cols], "f16")
+    s += view("out", "out_ptr", [n_table_rows, cols], "f16")
+    s += view("idx", "idx_ptr", [n_idx], idx_dtype)
+    s += "    scf.for %base = %begin to %end step %tile_rows {\n"
+    s += _iat("src", "table", "idx", "%base", tile_rows, cols, n_table_rows, n_idx, idx_dtype, "      ")
+    s += _iat("dst", "out", "idx", "%base", tile_rows, cols, n_table_rows, n_idx, idx_dtype, "      ")
+    s += (f"      %rows = ktdp.load %src : {at} -> {t}\n"
+          f"      %scale_t = tensor.splat %scale : {t}\n"
+          f"      %scaled = arith.mulf %rows, %scale_t : {t}\n"
+          f"      %old = ktdp.load %dst : {at} -> {t}\n"
+          f"      %new = arith.addf %old, %scaled : {t}\n"
+          f"      ktdp.store %new, %dst : {t}, {at}\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
+def tiled_matmul(M: int = 4096, N: int = 4096, K: int = 4096, bm: int = 64, bn: int = 64, bk: int = 64,
+                 cores: int = 32, f32_acc: bool = True) -> str:
+    """C = A @ B with bm x bn output tiles and K-step bk; core c owns tiles [c*T, (c+1)*T).
+
+    f32_acc: operands extended to f32, f32 accumulator carried through the K
+    loop, one truncation to f16 at the end.  Otherwise the f16 form of
+    examples/triton-ktir/matmul_fwd_ktir.mlir: f16 matmul per K-step added into
+    an f16 accumulator."""
+    tiles_n = N // bn
+    n_tiles = (M // bm) * tiles_n
+    per_core = n_tiles // cores
+    assert per_core * cores == n_tiles and K % bk == 0
+    ct = "f32" if f32_acc else "f16"
+    ta, tb = f"tensor<{bm}x{bk}xf16>", f"tensor<{bk}x{bn}xf16>"
+    tc16, tcc = f"tensor<{bm}x{bn}xf16>", f"tensor<{bm}x{bn}x{ct}>"
+    s = (f"module {{\n  func.func @matmul_kernel(%a_ptr: index, %b_ptr: index, %c_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n"
+         f"    %K = arith.constant {K} : index\n"
+         f"    %bm = arith.constant {bm} : index\n"
+         f"    %bn = arith.constant {bn} : index\n"
+         f"    %bk = arith.constant {bk} : index\n"
+         f"    %tiles_n = arith.constant {tiles_n} : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n"
+         f"    %t_begin = arith.muli %pid, %per_core : index\n"
+         f"    %t_end = arith.addi %t_begin, %per_core : index\n")
+    s += view("a_view", "a_ptr", [M, K], "f16") + view("b_view", "b_ptr", [K, N], "f16")
+    s += view("c_view", "c_ptr", [M, N], "f16")
+    s += (f"    scf.for %t = %t_begin to %t_end step %c1 {{\n"
+          f"      %tm = arith.divui %t, %tiles_n : index\n"
+          f"      %tn = arith.remui %t, %tiles_n : index\n"
+          f"      %off_m = arith.muli %tm, %bm : index\n"
+          f"      %off_n = arith.muli %tn, %bn : index\n"
+          f"      %acc0 = arith.constant dense<0.0> : {tcc}\n"
+          f"      %acc = scf.for %off_k = %c0 to %K step %bk iter_args(%acc_it = %acc0) -> ({tcc}) {{\n")
+    s += tile("a_tile", "a_view", ["%off_m", "%off_k"], [bm, bk], [M, K], "f16", "        ")
+    s += tile("b_tile", "b_view", ["%off_k", "%off_n"], [bk, bn], [K, N], "f16", "        ")
+    s += (f"        %a = ktdp.load %a_tile : !ktdp.access_tile<{bm}x{bk}xindex> -> {ta}\n"
+          f"        %b = ktdp.load %b_tile : !ktdp.access_tile<{bk}x{bn}xindex> -> {tb}\n")
+    if f32_acc:
+        s += (f"        %a32 = arith.extf %a : {ta} to tensor<{bm}x{bk}xf32>\n"
+              f"        %b32 = arith.extf %b : {tb} to tensor<{bk}x{bn}xf32>\n"
+              f"        %next = linalg.matmul ins(%a32, %b32 : tensor<{bm}x{bk}xf32>, tensor<{bk}x{bn}xf32>) "
+              f"outs(%acc_it : {tcc}) -> {tcc}\n")
+    else:
+        s += (f"        %init = tensor.empty() : {tc16}\n"
+              f"        %ab = linalg.matmul ins(%a, %b : {ta}, {tb}) outs(%init : {tc16}) -> {tc16}\n"
+              f"        %next = arith.addf %acc_it, %ab : {tc16}\n")
+    s += f"        scf.yield %next : {tcc}\n      }}\n"
+    if f32_acc:
+        s += f"      %c16 = arith.truncf %acc : {tcc} to {tc16}\n"
+    cval = "%c16" if f32_acc else "%acc"
+    s += tile("c_tile", "c_view", ["%off_m", "%off_n"], [bm, bn], [M, N], "f16", "      ")
+    s += (f"      ktdp.store {cval}, %c_tile : {tc16}, !ktdp.access_tile<{bm}x{bn}xindex>\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s

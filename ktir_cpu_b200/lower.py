@@ -1,0 +1,579 @@
+"""Lowering: traced stores -> device launches (a :class:`Plan`).
+
+Each ``ktdp.store`` of the trace is matched against the kernel idioms this
+backend has hand-written CUDA for; one launch then covers every grid core and
+every iteration of the enclosing parallel loops.  The reference executes the
+same work op by op and core by core (ktir_cpu/grid.py:595-613); running the
+cores concurrently is only equivalent when no core (or loop iteration) touches
+memory another one writes, which :func:`check_hazards` verifies on the exact
+byte runs before a plan is accepted.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from . import runtime as R
+from .dtypes import bytes_per_elem
+from .trace import Access, IndirectAccess, Node, Store, Unsupported, iv_full
+
+F_DT = ("f16", "f32")
+
+
+@dataclass
+class Allocation:
+    name: str
+    byte_lo: int
+    byte_hi: int
+    dtype: str
+
+
+class ArenaMap:
+    """Host mirror of the allocation list (ktir_cpu/memory.py:167-214, 311-352)."""
+
+    def __init__(self, allocs: List[Allocation]):
+        self.allocs = sorted(allocs, key=lambda a: a.byte_lo)
+
+    def find(self, byte_addr: int) -> Optional[Allocation]:
+        for a in self.allocs:
+            if a.byte_lo <= byte_addr < a.byte_hi:
+                return a
+        return None
+
+    def check_range(self, lo_elem: int, hi_elem: int, dtype: str, what: str) -> Allocation:
+        bpe = bytes_per_elem(dtype)
+        a = self.find(lo_elem * bpe)
+        if a is None:
+            raise ValueError(f"{what} unmapped address 0x{lo_elem * bpe:x}")
+        if hi_elem * bpe > a.byte_hi:
+            raise Unsupported(f"{what.strip()} runs past the end of allocation '{a.name}' "
+                              "(zero-padded / dropped accesses have no device path yet)")
+        return a
+
+
+@dataclass
+class Footprint:
+    """Byte runs touched by one statement: starts/ends per run plus the point each run belongs to."""
+    starts: np.ndarray
+    ends: np.ndarray
+    points: np.ndarray
+    cores: np.ndarray
+    write: bool
+    stmt: int
+
+
+class Statement:
+    kind = "?"
+    device_arrays: List[int]
+    launches = 1
+
+    def launch(self, dev: R.Device, arena_ptr: int):
+        raise NotImplementedError
+
+    def footprints(self) -> List[Footprint]:
+        return []
+
+    def bytes_moved(self) -> int:
+        return 0
+
+
+def _points(store: Store):
+    """Flat indices (and core ids) of the active iteration points of a store."""
+    n = int(np.prod(store.axes))
+    idx = np.arange(n, dtype=np.int64)
+    if store.active is not None:
+        idx = idx[store.active.reshape(-1)]
+    inner = n // store.axes[0] if store.axes[0] else 1
+    return idx, idx // max(inner, 1)
+
+
+def _access_offsets(acc: Access, store: Store, sel: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(iv_full(acc.off, store.axes).reshape(-1)[sel])
+
+
+@dataclass
+class TileGeom:
+    """A strided-box tile as ``lead`` row origins (element offsets) of rows x cols each."""
+    lead: np.ndarray          # [n_lead] element offsets relative to the tile origin
+    rows: int
+    cols: int
+    row_stride: int
+
+
+def tile_geom(acc: Access, expand_rows: bool) -> TileGeom:
+    if acc.coords is not None:
+        raise Unsupported("coordinate-set (non-rectangular) access tile in a fused statement")
+    shape, strides = list(acc.shape), list(acc.strides)
+    if not shape:
+        shape, strides = [1], [1]
+    if strides[-1] != 1 and shape[-1] != 1:
+        raise Unsupported("access tile whose innermost dimension is not unit-stride")
+    cols = shape[-1]
+    if len(shape) == 1:
+        return TileGeom(np.zeros(1, np.int64), 1, cols, cols)
+    if expand_rows or len(shape) > 2:
+        grids = np.indices(shape[:-1], dtype=np.int64).reshape(len(shape) - 1, -1)
+        lead = (np.asarray(strides[:-1], np.int64)[:, None] * grids).sum(0)
+        return TileGeom(lead, 1, cols, cols)
+    return TileGeom(np.zeros(1, np.int64), shape[0], cols, strides[0])
+
+
+# ---------------------------------------------------------------------------
+# Elementwise programs
+# ---------------------------------------------------------------------------
+_VM_BIN = {"arith.addf": "ADD", "arith.subf": "SUB", "arith.mulf": "MUL", "arith.divf": "DIV",
+           "arith.maximumf": "MAX", "arith.maxnumf": "MAXNUM", "arith.minimumf": "MIN",
+           "arith.minnumf": "MINNUM"}
+_VM_UN = {"arith.negf": "NEG", "math.absf": "ABS", "math.exp": "EXP", "math.log": "LOG",
+          "math.log2": "LOG2", "math.sqrt": "SQRT", "math.rsqrt": "RSQRT", "math.tanh": "TANH",
+          "math.sin": "SIN", "math.cos": "COS"}
+
+
+def strip_views(n: Node) -> Node:
+    """Skip reshapes (row-major element order is unchanged) and full-shape broadcasts of constants."""
+    while n.kind == "reshape":
+        n = n.args[0]
+    return n
+
+
+class ProgramBuilder:
+    """Compiles an elementwise DAG over same-shaped tiles into a register program."""
+
+    def __init__(self, leaf_kinds=("load",)):
+        self.inputs: List[Node] = []
+        self.ops: List[Tuple[int, int, int, int, int, float]] = []
+        self.reg_of: Dict[int, int] = {}
+        self.free: List[int] = []
+        self.next_reg = 0
+        self.leaf_kinds = leaf_kinds
+
+    def collect_inputs(self, n: Node, seen=None):
+        seen = seen if seen is not None else set()
+        n = strip_views(n)
+        if id(n) in seen:
+            return
+        seen.add(id(n))
+        if n.kind in self.leaf_kinds:
+            if n.dtype not in F_DT:
+                raise Unsupported(f"{n.dtype} tile in an elementwise statement")
+            if not any(n is x for x in self.inputs):
+                self.inputs.append(n)
+            return
+        for a in n.args:
+            self.collect_inputs(a, seen)
+
+    def alloc(self) -> int:
+        if self.free:
+            return self.free.pop()
+        r = self.next_reg
+        self.next_reg += 1
+        if r >= R.VM_REGS:
+            raise Unsupported("elementwise expression needs more than 8 live registers")
+        return r
+
+    def emit(self, code: str, dst: int, a=0, b=0, c=0, imm=0.0, r16=False):
+        if len(self.ops) >= R.VM_MAX_OPS:
+            raise Unsupported("elementwise expression longer than 12 ops")
+        self.ops.append((R.VM[code] | (R.VM_ROUND16 if r16 else 0), dst, a, b, c, float(imm)))
+
+    def build(self, root: Node, full_shape: Tuple[int, ...]) -> R.VmProgram:
+        self.collect_inputs(root)
+        if not self.inputs:
+            raise Unsupported("store of a tile that reads no memory")
+        if len(self.inputs) > R.VM_MAX_IN:
+            raise Unsupported(f"elementwise statement with more than {R.VM_MAX_IN} input tiles")
+        self.full_elems = int(np.prod(full_shape)) if full_shape else 1
+        for i, n in enumerate(self.inputs):
+            self.reg_of[id(n)] = i
+        self.next_reg = len(self.inputs)
+        res = self.visit(root)
+        p = R.VmProgram()
+        p.n_in, p.n_ops, p.result_reg = len(self.inputs), len(self.ops), res
+        for i, (code, dst, a, b, c, imm) in enumerate(self.ops):
+            p.ops[i] = R.VmOp(code, dst, a, b, c, imm)
+        return p
+
+    def visit(self, n: Node) -> int:
+        n = strip_views(n)
+        if id(n) in self.reg_of:
+            return self.reg_of[id(n)]
+        r16 = n.dtype == "f16"
+        if n.kind == "const":
+            if n.attrs.get("list") is not None:
+                raise Unsupported("dense list constant in an elementwise statement")
+            v = n.attrs["value"]
+            v = float(np.float16(v)) if n.dtype == "f16" else float(np.float32(v))
+            r = self.alloc()
+            self.emit("CONST", r, imm=v)
+        elif n.kind == "bcast" and strip_views(n.args[0]).kind == "const":
+            return self.visit(n.args[0])
+        elif n.kind == "cast":
+            src = self.visit(n.args[0])
+            if n.args[0].dtype not in F_DT or n.dtype not in F_DT:
+                raise Unsupported(f"cast {n.args[0].dtype}->{n.dtype} in an elementwise statement")
+            if n.dtype == "f32":
+                return src                      # f16 values are exact in f32 registers
+            r = self.alloc()
+            self.emit("MOV", r, src, r16=True)
+        elif n.kind == "ew":
+            op = n.attrs["op"]
+            for a in n.args:
+                sa = strip_views(a)
+                if sa.kind not in ("const",) and not (sa.kind == "bcast" and strip_views(sa.args[0]).kind == "const"):
+                    if int(np.prod(sa.shape)) != self.full_elems:
+                        raise Unsupported("broadcasting between tiles of different shape in an "
+                                          "elementwise statement")
+            if n.dtype not in F_DT:
+                raise Unsupported(f"{op} producing {n.dtype} in an elementwise statement")
+            regs = [self.visit(a) for a in n.args]
+            r = self.alloc()
+            if op in _VM_BIN:
+                self.emit(_VM_BIN[op], r, regs[0], regs[1], r16=r16)
+            elif op in _VM_UN:
+                self.emit(_VM_UN[op], r, regs[0], r16=r16)
+            elif op == "math.fma":
+                self.emit("FMA", r, regs[0], regs[1], regs[2], r16=r16)
+            else:
+                raise Unsupported(f"{op} in an elementwise statement")
+        else:
+            raise Unsupported(f"{n.kind} node in an elementwise statement")
+        self.reg_of[id(n)] = r
+        return r
+
+
+class EwStatement(Statement):
+    kind = "ew_stream"
+
+    def __init__(self, dev: R.Device, store: Store, arena: ArenaMap, stmt_id: int):
+        tgt: Access = store.target
+        pb = ProgramBuilder()
+        self.program = pb.build(store.value, tgt.shape)
+        operands: List[Access] = [n.attrs["access"] for n in pb.inputs] + [tgt]
+        n_elems = int(np.prod(tgt.shape)) if tgt.shape else 1
+        for acc in operands[:-1]:
+            if (int(np.prod(acc.shape)) if acc.shape else 1) != n_elems:
+                raise Unsupported("operand tile shape differs from the stored tile")
+        simple = all(len(a.shape) <= 2 for a in operands) and len({tuple(a.shape) for a in operands}) == 1
+        geoms = [tile_geom(a, not simple) for a in operands]
+        g_out = geoms[-1]
+        if any((g.cols, g.rows, len(g.lead)) != (g_out.cols, g_out.rows, len(g_out.lead)) for g in geoms):
+            raise Unsupported("operand tiles with different row structure in an elementwise statement")
+        sel, cores = _points(store)
+        self.n_points = len(sel)
+        n_lead = len(g_out.lead)
+        table = np.empty((len(sel) * n_lead, len(operands)), np.int64)
+        self.fps: List[Footprint] = []
+        for k, (acc, g) in enumerate(zip(operands, geoms)):
+            offs = _access_offsets(acc, store, sel)
+            full = (offs[:, None] + g.lead[None, :]).reshape(-1)
+            table[:, k] = full
+            if len(full):
+                span = (g.rows - 1) * g.row_stride + g.cols
+                arena.check_range(int(full.min()), int(full.max()) + span, acc.view.dtype,
+                                  "Read from" if k < len(operands) - 1 else "Scatter to")
+            bpe = bytes_per_elem(acc.view.dtype)
+            rstart = (full[:, None] + np.arange(g.rows, dtype=np.int64)[None, :] * g.row_stride).reshape(-1) * bpe
+            pts = np.repeat(sel, n_lead * g.rows)
+            self.fps.append(Footprint(rstart, rstart + g.cols * bpe, pts, np.repeat(cores, n_lead * g.rows),
+                                      k == len(operands) - 1, stmt_id))
+        self.table = table
+        self.args = R.EwArgs()
+        a = self.args
+        a.n_items = table.shape[0]
+        a.rows, a.cols = g_out.rows, g_out.cols
+        vec = (g_out.cols % 8 == 0) and bool((table % 8 == 0).all())
+        for k, (acc, g) in enumerate(zip(operands, geoms)):
+            a.row_stride[k] = g.row_stride
+            a.dtype[k] = R.DTYPE_CODE[acc.view.dtype]
+            vec = vec and (g.row_stride % 8 == 0 or g.rows == 1)
+        a.vector_ok = 1 if vec else 0
+        a.program = self.program
+        self.dev_table = dev.upload(table)
+        a.dev_item_offsets = self.dev_table
+        self.device_arrays = [self.dev_table]
+        self.elems = int(table.shape[0]) * g_out.rows * g_out.cols
+        self._bytes = sum(self.elems * bytes_per_elem(acc.view.dtype) for acc in operands)
+
+    def launch(self, dev, arena_ptr):
+        self.args.arena = arena_ptr
+        dev.check(dev.lib.ktb_launch_ew_stream(dev.h, C.byref(self.args)))
+
+    def footprints(self):
+        return self.fps
+
+    def bytes_moved(self):
+        return self._bytes
+
+
+# ---------------------------------------------------------------------------
+# Row softmax idiom
+# ---------------------------------------------------------------------------
+def _skip(n: Node) -> Node:
+    """Strip reshapes and single-element extracts."""
+    while True:
+        if n.kind == "reshape":
+            n = n.args[0]
+        elif n.kind == "extract" and int(np.prod(n.args[0].shape) if n.args[0].shape else 1) == 1:
+            n = n.args[0]
+        else:
+            return n
+
+
+def _row_broadcast(n: Node, tile_shape) -> Optional[Node]:
+    """If ``n`` spreads one value per row along the last dim of ``tile_shape``, return that value."""
+    n = strip_views(n)
+    if n.kind != "bcast" or tuple(n.shape) != tuple(tile_shape):
+        return None
+    src = _skip(n.args[0])
+    rows = int(np.prod(tile_shape[:-1])) if len(tile_shape) > 1 else 1
+    if (int(np.prod(src.shape)) if src.shape else 1) != rows:
+        return None
+    dims = list(n.attrs.get("dims", []))
+    nd = len(tile_shape)
+    if dims == [nd - 1] or (rows == 1 and sorted(dims) == list(range(nd))):
+        return src
+    return None
+
+
+def _row_reduce(n: Node, opnames) -> Optional[Tuple[Node, str, Optional[float]]]:
+    """Match ``combine(reduce(op, src, last dim), const init)`` -> (src, op, init)."""
+    n = _skip(n)
+    init = None
+    if n.kind == "ew" and n.attrs["op"] in opnames and len(n.args) == 2:
+        red, c = _skip(n.args[0]), strip_views(n.args[1])
+        while c.kind == "bcast":
+            c = strip_views(c.args[0])
+        if c.kind != "const" or c.attrs.get("list") is not None:
+            return None
+        init = float(c.attrs["value"])
+        n = red
+    if n.kind != "reduce" or n.attrs["op"] not in opnames:
+        return None
+    src = n.args[0]
+    dims = n.attrs["dims"]
+    if dims is None:
+        if len([s for s in src.shape if s != 1]) > 1:
+            return None
+    elif tuple(dims) != (len(src.shape) - 1,):
+        return None
+    return src, n.attrs["op"], init
+
+
+def match_softmax(value: Node):
+    """Recognise store(truncf?(exp(x - rowmax(x)) / rowsum(exp(x - rowmax(x)))))."""
+    root = strip_views(value)
+    out_cast = False
+    if root.kind == "cast" and root.dtype == "f16" and root.args[0].dtype == "f32":
+        out_cast = True
+        root = strip_views(root.args[0])
+    if root.kind != "ew" or root.attrs["op"] != "arith.divf":
+        return None
+    num, den = strip_views(root.args[0]), root.args[1]
+    shape = tuple(num.shape)
+    if not shape:
+        return None
+    dsrc = _row_broadcast(den, shape)
+    if dsrc is None:
+        return None
+    dr = _row_reduce(dsrc, ("arith.addf",))
+    if dr is None or strip_views(dr[0]) is not num:
+        return None
+    if num.kind != "ew" or num.attrs["op"] != "math.exp":
+        return None
+    sub = strip_views(num.args[0])
+    if sub.kind != "ew" or sub.attrs["op"] != "arith.subf":
+        return None
+    x = strip_views(sub.args[0])
+    msrc = _row_broadcast(sub.args[1], shape)
+    if msrc is None:
+        return None
+    mr = _row_reduce(msrc, ("arith.maximumf", "arith.maxnumf"))
+    if mr is None or strip_views(mr[0]) is not x:
+        return None
+    xl = x
+    if xl.kind == "cast" and xl.dtype == "f32":
+        xl = strip_views(xl.args[0])
+    if xl.kind != "load" or xl.dtype not in F_DT:
+        return None
+    arith = num.dtype
+    if arith == "f16" and (x.dtype != "f16" or out_cast):
+        return None
+    return dict(load=xl, arith=arith, maxop=mr[1],
+                max_init=mr[2] if mr[2] is not None else float("-inf"),
+                sum_init=dr[2] if dr[2] is not None else 0.0)
+
+
+class SoftmaxStatement(Statement):
+    kind = "row_softmax"
+
+    def __init__(self, dev: R.Device, store: Store, m: dict, arena: ArenaMap, stmt_id: int):
+        tgt: Access = store.target
+        src: Access = m["load"].attrs["access"]
+        gi, go = tile_geom(src, False), tile_geom(tgt, False)
+        if len(gi.lead) != 1 or len(go.lead) != 1:
+            gi, go = tile_geom(src, True), tile_geom(tgt, True)
+        if (gi.rows, gi.cols, len(gi.lead)) != (go.rows, go.cols, len(go.lead)):
+            raise Unsupported("softmax input and output tiles differ in shape")
+        cols = gi.cols
+        if cols < 8 or cols > 16384 or cols & (cols - 1):
+            raise Unsupported(f"fused softmax over rows of {cols} elements (power of two in [8, 16384] only)")
+        sel, cores = _points(store)
+        n_lead = len(gi.lead)
+        table = np.empty((len(sel) * n_lead, 2), np.int64)
+        self.fps = []
+        for k, (acc, g) in enumerate(((src, gi), (tgt, go))):
+            full = (_access_offsets(acc, store, sel)[:, None] + g.lead[None, :]).reshape(-1)
+            table[:, k] = full
+            if len(full):
+                arena.check_range(int(full.min()), int(full.max()) + (g.rows - 1) * g.row_stride + g.cols,
+                                  acc.view.dtype, "Read from" if k == 0 else "Scatter to")
+            bpe = bytes_per_elem(acc.view.dtype)
+            rstart = (full[:, None] + np.arange(g.rows, dtype=np.int64)[None, :] * g.row_stride).reshape(-1) * bpe
+            self.fps.append(Footprint(rstart, rstart + g.cols * bpe, np.repeat(sel, n_lead * g.rows),
+                                      np.repeat(cores, n_lead * g.rows), k == 1, stmt_id))
+        if (table % 8).any() or (gi.rows > 1 and (gi.row_stride % 8 or go.row_stride % 8)):
+            raise Unsupported("fused softmax needs 16-byte aligned rows")
+        self.args = a = R.SoftmaxArgs()
+        a.n_items = table.shape[0]
+        a.rows_per_item, a.cols = gi.rows, cols
+        a.in_row_stride, a.out_row_stride = max(gi.row_stride, 8), max(go.row_stride, 8)
+        a.in_dtype, a.out_dtype = R.DTYPE_CODE[src.view.dtype], R.DTYPE_CODE[tgt.view.dtype]
+        a.f16_arith = 1 if m["arith"] == "f16" else 0
+        a.max_is_maxnum = 1 if m["maxop"] == "arith.maxnumf" else 0
+        a.max_init, a.sum_init = m["max_init"], m["sum_init"]
+        self.dev_table = dev.upload(table)
+        a.dev_item_offsets = self.dev_table
+        self.device_arrays = [self.dev_table]
+        self.elems = int(table.shape[0]) * gi.rows * cols
+        self._bytes = self.elems * (bytes_per_elem(src.view.dtype) + bytes_per_elem(tgt.view.dtype))
+
+    def launch(self, dev, arena_ptr):
+        self.args.arena = arena_ptr
+        dev.check(dev.lib.ktb_launch_row_softmax(dev.h, C.byref(self.args)))
+
+    def footprints(self):
+        return self.fps
+
+    def bytes_moved(self):
+        return self._bytes
+
+
+# ---------------------------------------------------------------------------
+# Hazards and plans
+# ---------------------------------------------------------------------------
+def check_hazards(fps: List[Footprint]):
+    """Reject plans where concurrent cores / iterations would observe each other's writes.
+
+    All byte runs of all statements are sorted; a run that is written may only
+    coincide exactly with runs of the same (statement, point) — an in-place
+    update — or with runs of the same core in another statement (program order
+    on one core is kept by launch order).  Any other overlap involving a write
+    means the sequential core order of the reference matters."""
+    if not fps or not any(f.write for f in fps):
+        return
+    starts = np.concatenate([f.starts for f in fps])
+    ends = np.concatenate([f.ends for f in fps])
+    if not len(starts):
+        return
+    write = np.concatenate([np.full(len(f.starts), f.write) for f in fps])
+    stmt = np.concatenate([np.full(len(f.starts), f.stmt, np.int64) for f in fps])
+    point = np.concatenate([f.points for f in fps])
+    core = np.concatenate([f.cores for f in fps])
+    order = np.lexsort((ends, starts))
+    starts, ends, write, stmt, point, core = (x[order] for x in (starts, ends, write, stmt, point, core))
+    new = np.ones(len(starts), bool)
+    new[1:] = (starts[1:] != starts[:-1]) | (ends[1:] != ends[:-1])
+    gid = np.cumsum(new) - 1
+    ng = int(gid[-1]) + 1
+    g_write = np.zeros(ng, bool)
+    np.logical_or.at(g_write, gid, write)
+    # identical runs: with a writer in the group every member must be the same core, and members
+    # of one statement the same point
+    first = np.flatnonzero(new)
+    same_core = core == core[first][gid]
+    bad = g_write[gid] & ~same_core
+    key = stmt * (int(point.max()) + 1) + point
+    srt = np.lexsort((key, stmt, gid))
+    g2, s2, k2 = gid[srt], stmt[srt], key[srt]
+    clash = (g2[1:] == g2[:-1]) & (s2[1:] == s2[:-1]) & (k2[1:] != k2[:-1]) & g_write[g2[1:]]
+    if bad.any() or clash.any():
+        raise Unsupported("memory written by one core/iteration is accessed by another: "
+                          "sequential core order matters and has no device path yet")
+    # partial overlaps between distinct runs
+    us, ue = starts[first], ends[first]
+    k = np.searchsorted(us, ue, side="left")        # runs i+1 .. k-1 start inside run i
+    idx = np.arange(ng)
+    cw = np.concatenate([[0], np.cumsum(g_write)])
+    writes_after = cw[k] - cw[np.minimum(idx + 1, ng)]
+    if ((k > idx + 1) & (g_write | (writes_after > 0))).any():
+        raise Unsupported("overlapping tile stores/loads across cores or iterations: "
+                          "sequential core order matters and has no device path yet")
+
+
+class Plan:
+    """Everything needed to run one (function, scalars, tensor layout) on the device."""
+
+    def __init__(self):
+        self.statements: List[Statement] = []
+        self.written: set = set()
+        self.fully_overwritten: set = set()
+
+    def launch(self, dev: R.Device, arena_ptr: int):
+        for s in self.statements:
+            s.launch(dev, arena_ptr)
+
+    def release(self, dev: R.Device):
+        for s in self.statements:
+            for p in getattr(s, "device_arrays", []):
+                dev.free(p)
+        self.statements = []
+
+
+def lower(dev: R.Device, stores: List[Store], arena: ArenaMap) -> Plan:
+    plan = Plan()
+    for st in stores:
+        sid = len(plan.statements)
+        if isinstance(st.target, IndirectAccess):
+            from .lower_scatter import lower_indirect_store
+            plan.statements.append(lower_indirect_store(dev, st, arena, sid))
+            continue
+        stmt = None
+        m = match_softmax(st.value)
+        if m is not None:
+            stmt = SoftmaxStatement(dev, st, m, arena, sid)
+        if stmt is None:
+            from .lower_mm import try_lower_matmul
+            stmt = try_lower_matmul(dev, st, arena, sid)
+        if stmt is None:
+            stmt = EwStatement(dev, st, arena, sid)
+        plan.statements.append(stmt)
+    fps = [f for s in plan.statements for f in s.footprints()]
+    check_hazards(fps)
+    read_names, write_runs = set(), {}
+    for s in plan.statements:
+        for f in s.footprints():
+            if not len(f.starts):
+                continue
+            a = arena.find(int(f.starts[0]))
+            if a is None:
+                continue
+            if f.write:
+                plan.written.add(a.name)
+                write_runs.setdefault(a.name, []).append((f.starts, f.ends))
+            else:
+                read_names.add(a.name)
+        for name in getattr(s, "extra_written", []):
+            plan.written.add(name)
+            read_names.add(name)
+    # tensors whose every byte is stored and none is loaded: their old contents cannot matter
+    for a in arena.allocs:
+        if a.name in write_runs and a.name not in read_names:
+            st = np.concatenate([x for x, _ in write_runs[a.name]])
+            en = np.concatenate([y for _, y in write_runs[a.name]])
+            runs = np.unique(np.stack([st, en], 1), axis=0)
+            if int((runs[:, 1] - runs[:, 0]).sum()) == a.byte_hi - a.byte_lo and runs[:, 0].min() == a.byte_lo:
+                plan.fully_overwritten.add(a.name)
+    return plan

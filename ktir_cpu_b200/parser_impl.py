@@ -201,7 +201,7 @@ class ModuleParser:
         ops = self.block()
         self.eat("}")
         fn = IRFunction(name, args, grid, ops)
-        arg_names = set(fn.arg_names)
+        arg_names = {n for n, _ in fn.args}
         from .ir import walk
         for op in walk(ops):
             if op.name == "ktdp.construct_memory_view" and op.operands:

@@ -1,0 +1,239 @@
+"""ctypes binding of ``libktir_b200.so`` (declared in ``include/ktir_b200.h``).
+
+There is no CPU fallback: if the library is missing or no CUDA device answers,
+:func:`lib` / :class:`Device` raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libktir_b200.so")
+
+KTB_F16, KTB_F32, KTB_I32, KTB_I64, KTB_I1 = range(5)
+DTYPE_CODE = {"f16": KTB_F16, "f32": KTB_F32, "i32": KTB_I32, "i64": KTB_I64, "i1": KTB_I1, "index": KTB_I32}
+
+VM_MAX_OPS, VM_MAX_IN, VM_REGS = 12, 4, 8
+VM_OPS = ["MOV", "CONST", "ADD", "SUB", "MUL", "DIV", "MAX", "MAXNUM", "MIN", "MINNUM", "NEG", "ABS",
+          "EXP", "LOG", "LOG2", "SQRT", "RSQRT", "TANH", "SIN", "COS", "FMA"]
+VM = {n: i for i, n in enumerate(VM_OPS)}
+VM_ROUND16 = 0x100
+
+
+class Status(C.Structure):
+    _fields_ = [("negative_index", C.c_int32), ("bad_index_value", C.c_int32),
+                ("wait_timeout", C.c_int32), ("wait_site", C.c_int32), ("reserved", C.c_int32 * 4)]
+
+
+class VmOp(C.Structure):
+    _fields_ = [("opcode", C.c_int32), ("dst", C.c_int32), ("a", C.c_int32), ("b", C.c_int32),
+                ("c", C.c_int32), ("imm", C.c_float)]
+
+
+class VmProgram(C.Structure):
+    _fields_ = [("n_in", C.c_int32), ("n_ops", C.c_int32), ("result_reg", C.c_int32),
+                ("reserved", C.c_int32), ("ops", VmOp * VM_MAX_OPS)]
+
+
+class EwArgs(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("dev_item_offsets", C.c_void_p), ("n_items", C.c_int64),
+                ("rows", C.c_int32), ("cols", C.c_int32),
+                ("row_stride", C.c_int64 * (VM_MAX_IN + 1)), ("dtype", C.c_int32 * (VM_MAX_IN + 1)),
+                ("vector_ok", C.c_int32), ("program", VmProgram)]
+
+
+class SoftmaxArgs(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("dev_item_offsets", C.c_void_p), ("n_items", C.c_int64),
+                ("rows_per_item", C.c_int32), ("cols", C.c_int32),
+                ("in_row_stride", C.c_int64), ("out_row_stride", C.c_int64),
+                ("in_dtype", C.c_int32), ("out_dtype", C.c_int32),
+                ("f16_arith", C.c_int32), ("max_is_maxnum", C.c_int32),
+                ("max_init", C.c_float), ("sum_init", C.c_float)]
+
+
+_lib: Optional[C.CDLL] = None
+
+# name -> (restype, argtypes); every symbol include/ktir_b200.h declares
+SYMBOLS = {
+    "ktb_init": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "ktb_destroy": (C.c_int, [C.c_void_p]),
+    "ktb_last_error": (C.c_char_p, [C.c_void_p]),
+    "ktb_alloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "ktb_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ktb_alloc_host": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "ktb_free_host": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ktb_memset": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t]),
+    "ktb_h2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ktb_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ktb_d2d": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "ktb_sync": (C.c_int, [C.c_void_p, C.POINTER(Status)]),
+    "ktb_set_stream": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "ktb_event_record": (C.c_int, [C.c_void_p, C.c_int]),
+    "ktb_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "ktb_flush_l2": (C.c_int, [C.c_void_p]),
+    "ktb_launch_count": (C.c_int64, [C.c_void_p]),
+    "ktb_launch_ew_stream": (C.c_int, [C.c_void_p, C.POINTER(EwArgs)]),
+    "ktb_launch_row_softmax": (C.c_int, [C.c_void_p, C.POINTER(SoftmaxArgs)]),
+}
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m ktir_cpu_b200.build` "
+                "(this backend has no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(_lib, name)
+            fn.restype, fn.argtypes = res, args
+    return _lib
+
+
+class DeviceError(RuntimeError):
+    pass
+
+
+class DeviceIndexError(IndexError):
+    pass
+
+
+class Device:
+    """One context on one GPU: memory, transfers, launches, events."""
+
+    def __init__(self, device: int = 0):
+        self.lib = lib()
+        h = C.c_void_p()
+        rc = self.lib.ktb_init(device, C.byref(h))
+        if rc != 0 or not h:
+            raise DeviceError(f"ktb_init(device={device}) failed (code {rc}): no usable CUDA device; "
+                              "this backend has no CPU fallback")
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.ktb_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, rc: int):
+        if rc != 0:
+            msg = self.lib.ktb_last_error(self.h).decode(errors="replace")
+            if rc == -4 and "is negative" in msg:
+                raise DeviceIndexError(msg)
+            if rc == -3:
+                raise NotImplementedError(msg)
+            raise DeviceError(f"libktir_b200 error {rc}: {msg}")
+
+    # memory ---------------------------------------------------------------
+    def alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self.check(self.lib.ktb_alloc(self.h, nbytes, C.byref(p)))
+        return p.value
+
+    def free(self, ptr: int):
+        self.check(self.lib.ktb_free(self.h, C.c_void_p(ptr)))
+
+    def alloc_host(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self.check(self.lib.ktb_alloc_host(self.h, nbytes, C.byref(p)))
+        return p.value
+
+    def free_host(self, ptr: int):
+        self.check(self.lib.ktb_free_host(self.h, C.c_void_p(ptr)))
+
+    def memset(self, ptr: int, value: int, nbytes: int):
+        self.check(self.lib.ktb_memset(self.h, C.c_void_p(ptr), value, nbytes))
+
+    def h2d(self, dev_ptr: int, host: np.ndarray):
+        host = np.ascontiguousarray(host)
+        self.check(self.lib.ktb_h2d(self.h, C.c_void_p(dev_ptr), C.c_void_p(host.ctypes.data), host.nbytes))
+        return host          # keep alive until the next sync
+
+    def h2d_raw(self, dev_ptr: int, host_ptr: int, nbytes: int):
+        self.check(self.lib.ktb_h2d(self.h, C.c_void_p(dev_ptr), C.c_void_p(host_ptr), nbytes))
+
+    def d2h(self, host: np.ndarray, dev_ptr: int):
+        assert host.flags["C_CONTIGUOUS"]
+        self.check(self.lib.ktb_d2h(self.h, C.c_void_p(host.ctypes.data), C.c_void_p(dev_ptr), host.nbytes))
+
+    def d2h_raw(self, host_ptr: int, dev_ptr: int, nbytes: int):
+        self.check(self.lib.ktb_d2h(self.h, C.c_void_p(host_ptr), C.c_void_p(dev_ptr), nbytes))
+
+    def sync(self) -> Status:
+        st = Status()
+        self.check(self.lib.ktb_sync(self.h, C.byref(st)))
+        return st
+
+    def upload(self, arr: np.ndarray) -> int:
+        """Allocate device memory holding ``arr`` (synchronous)."""
+        arr = np.ascontiguousarray(arr)
+        p = self.alloc(max(arr.nbytes, 16))
+        if arr.nbytes:
+            self.h2d(p, arr)
+            self.sync()
+        return p
+
+    # timing ----------------------------------------------------------------
+    def record(self, slot: int):
+        self.check(self.lib.ktb_event_record(self.h, slot))
+
+    def elapsed_ms(self, a: int, b: int) -> float:
+        ms = C.c_float()
+        self.check(self.lib.ktb_event_elapsed_ms(self.h, a, b, C.byref(ms)))
+        return float(ms.value)
+
+    def flush_l2(self):
+        self.check(self.lib.ktb_flush_l2(self.h))
+
+    def launch_count(self) -> int:
+        return int(self.lib.ktb_launch_count(self.h))
+
+
+_devices = {}
+
+
+def get_device(index: int = 0) -> Device:
+    d = _devices.get(index)
+    if d is None or d.h is None:
+        d = _devices[index] = Device(index)
+    return d
+
+
+class PlanOnlyDevice:
+    """Stands in for :class:`Device` when only the launch plan is wanted (no GPU needed).
+
+    It can hold no data and launch nothing: planning code may call ``upload`` /
+    ``alloc`` / ``free``; anything that would run on the GPU raises."""
+
+    h = None
+    lib = None
+
+    def alloc(self, nbytes: int) -> int:
+        return 0
+
+    def free(self, ptr: int):
+        pass
+
+    def upload(self, arr) -> int:
+        return 0
+
+    def sync(self):
+        return Status()
+
+    def check(self, rc):
+        raise DeviceError("plan-only device cannot launch kernels")
+
+    def __getattr__(self, name):
+        raise DeviceError(f"plan-only device has no '{name}'")

@@ -1,0 +1,358 @@
+"""Trace rules for tensor / linalg / scf / ktdp ops (second half of the table)."""
+from __future__ import annotations
+
+from typing import Any, Dict, List
+
+import numpy as np
+
+from .affine import AffineMap, AffineSet
+from .dtypes import canon
+from .ir import Op
+from .trace import (MAX_UNROLL, Access, IndirectAccess, LoopInfo, Node, Store, Tracer, Unsupported,
+                    View, _Yield, is_iv, iv_align, iv_bin, iv_full, iv_uniform)
+from .trace_ops import (TABLE, _as_operand, cast, const_node, ew, is_fscalar, is_node, param_node, rule)
+
+
+# ---- tensor dialect --------------------------------------------------------------
+@rule("tensor.empty")
+def _empty(tr, op, scope):
+    ty = op.result_types[0]
+    n = const_node(0.0 if ty.dtype in ("f16", "f32") else 0, ty.shape, ty.dtype)
+    n.attrs["empty"] = True
+    return n
+
+
+@rule("tensor.splat")
+def _splat(tr, op, scope):
+    s = tr.get(scope, op.operands[0])
+    ty = op.result_types[0]
+    shape, dtype = tuple(ty.shape), canon(ty.dtype)
+    if is_node(s):
+        src = s if s.shape == () else Node("extract", (), s.dtype, (s,), {"index": (0,) * len(s.shape)})
+        if src.dtype in ("i32", "i64"):
+            src, dtype = cast(src, "i32"), "i32"
+        else:
+            src = cast(src, dtype)
+        return Node("bcast", shape, dtype, (src,), {"dims": list(range(len(shape)))})
+    if isinstance(s, np.ndarray):
+        return Node("bcast", shape, "i32", (cast(param_node(s), "i32"),), {"dims": list(range(len(shape)))})
+    if isinstance(s, (int, np.integer)) and not isinstance(s, (bool, np.bool_)):
+        return const_node(int(s), shape, "i32")
+    return const_node(float(np.asarray(s, dtype={"f16": np.float16, "f32": np.float32}.get(dtype, np.float32))),
+                      shape, dtype)
+
+
+@rule("tensor.extract")
+def _extract(tr, op, scope):
+    src = tr.get(scope, op.operands[0])
+    if not is_node(src):
+        return src
+    idx = []
+    for i in op.attrs.get("indices", []):
+        v = tr.get(scope, i) if isinstance(i, str) else i
+        u = iv_uniform(v)
+        if u is None:
+            raise Unsupported("tensor.extract with a per-core index")
+        idx.append(u)
+    if not idx:
+        idx = [0] * len(src.shape)
+    return Node("extract", (), src.dtype, (src,), {"index": tuple(idx)})
+
+
+@rule("tensor.collapse_shape", "tensor.expand_shape", "tensor.reshape")
+def _reshape(tr, op, scope):
+    src = tr.get(scope, op.operands[0])
+    if not is_node(src):
+        return src
+    return Node("reshape", tuple(op.result_types[0].shape), src.dtype, (src,), {})
+
+
+# ---- linalg ------------------------------------------------------------------------
+def _combiner_of(op: Op):
+    if "combiner" in op.attrs:
+        return op.attrs["combiner"]
+    if not op.regions:
+        return "arith.addf"
+    reg = op.regions[0]
+    body = [o for o in reg.ops if o.name != "linalg.yield"]
+    if len(body) == 1 and len(body[0].operands) == 2:
+        names = reg.arg_names or list(body[0].operands)
+        if set(body[0].operands) == set(names[:2]):
+            return body[0].name
+    return None
+
+
+_CANON_COMB = {"arith.maxf": "arith.maximumf", "arith.minf": "arith.minimumf"}
+
+
+@rule("linalg.reduce")
+def _reduce(tr, op, scope):
+    tile = tr.get(scope, op.operands[0])
+    outs_name = op.operands[1] if len(op.operands) > 1 else None
+    outs = tr.get(scope, outs_name) if outs_name else None
+    if not is_node(tile):
+        result = tile
+    else:
+        comb = _combiner_of(op)
+        if comb is None:
+            raise Unsupported("linalg.reduce with a multi-op combiner region")
+        comb = _CANON_COMB.get(comb, comb)
+        dims = op.attrs.get("dimensions")
+        if dims is None:
+            shape = ()
+        else:
+            shape = tuple(s for i, s in enumerate(tile.shape) if i not in dims)
+        result = Node("reduce", shape, tile.dtype, (tile,),
+                      {"op": comb, "dims": None if dims is None else tuple(sorted(dims))})
+        if is_node(outs):
+            result = ew(comb, [result, outs], dtype=tile.dtype)
+    if outs_name and result is not None:
+        scope[outs_name] = result
+    return result
+
+
+@rule("linalg.fill")
+def _fill(tr, op, scope):
+    s, out = tr.get(scope, op.operands[0]), tr.get(scope, op.operands[1])
+    if is_node(s) or isinstance(s, np.ndarray):
+        raise Unsupported("linalg.fill with a non-constant scalar")
+    return const_node(float(s), out.shape, out.dtype)
+
+
+@rule("linalg.broadcast")
+def _broadcast(tr, op, scope):
+    inp, out = tr.get(scope, op.operands[0]), tr.get(scope, op.operands[1])
+    dims = sorted(op.attrs.get("dimensions", []))
+    return Node("bcast", tuple(out.shape), inp.dtype, (inp,), {"dims": dims})
+
+
+@rule("linalg.transpose")
+def _transpose(tr, op, scope):
+    inp = tr.get(scope, op.operands[0])
+    perm = op.attrs.get("permutation")
+    if perm is None:
+        raise ValueError("linalg.transpose: missing permutation attribute")
+    return Node("transpose", tuple(inp.shape[i] for i in perm), inp.dtype, (inp,), {"perm": tuple(perm)})
+
+
+@rule("linalg.add", "linalg.max")
+def _named_bin(tr, op, scope):
+    a, b = tr.get(scope, op.operands[0]), tr.get(scope, op.operands[1])
+    if not is_node(a) or not is_node(b):
+        raise TypeError(f"{op.name}: ins must be Tiles")
+    return ew("arith.addf" if op.name == "linalg.add" else "arith.maximumf", [a, b], dtype=a.dtype)
+
+
+@rule("linalg.matmul", "linalg.batch_matmul")
+def _matmul(tr, op, scope):
+    a, b = tr.get(scope, op.operands[0]), tr.get(scope, op.operands[1])
+    acc = tr.get(scope, op.operands[2]) if len(op.operands) > 2 else None
+    shape = tuple(a.shape[:-1]) + (b.shape[-1],)
+    args = (a, b) + ((acc,) if is_node(acc) else ())
+    n = Node("matmul", shape, acc.dtype if is_node(acc) else a.dtype, args,
+             {"batched": op.name.endswith("batch_matmul"), "prod_dtype": a.dtype})
+    if is_node(acc):
+        scope[op.operands[2]] = n
+    return n
+
+
+@rule("linalg.index")
+def _index(tr, op, scope):
+    shape = scope["__linalg_shape__"]
+    d = op.attrs["dim"]
+    rs = [1] * len(shape)
+    rs[d] = shape[d]
+    return Node("iota", tuple(rs), "i64", (), {"dim": d})
+
+
+@rule("linalg.yield", "scf.yield", "tensor.yield")
+def _yield(tr, op, scope):
+    return _Yield([tr.get(scope, n) for n in op.operands])
+
+
+def _map_input(node: Node, m: AffineMap, iter_shape) -> Node:
+    """View an input through a projection indexing map (linalg_ops.py:398-419)."""
+    if not all(e[0] == "dim" for e in m.exprs):
+        raise Unsupported("linalg.generic with a non-projection indexing map")
+    plain = [e[1] for e in m.exprs]
+    if plain != sorted(plain):
+        perm = tuple(plain.index(d) for d in sorted(plain))
+        node = Node("transpose", tuple(node.shape[i] for i in perm), node.dtype, (node,), {"perm": perm})
+        plain = sorted(plain)
+    if len(plain) == len(iter_shape):
+        return node
+    missing = [d for d in range(len(iter_shape)) if d not in plain]
+    return Node("bcast", tuple(iter_shape), node.dtype, (node,), {"dims": missing})
+
+
+@rule("linalg.generic")
+def _generic(tr, op, scope):
+    n_ins = op.attrs["n_ins"]
+    maps = op.attrs.get("indexing_maps", [])
+    iters = op.attrs.get("iterator_types") or []
+    if any(t == "reduction" for t in iters):
+        raise Unsupported("linalg.generic with reduction iterators")
+    ins = [tr.get(scope, o) for o in op.operands[:n_ins]]
+    outs = tr.get(scope, op.operands[n_ins])
+    if not is_node(outs):
+        raise TypeError(f"linalg.generic: outs must be a Tile, got {type(outs)}")
+    reg = op.regions[0]
+    if not reg.arg_names:
+        raise ValueError("linalg.generic: cannot determine bb0 argument names")
+    inner = dict(scope)
+    inner["__linalg_shape__"] = tuple(outs.shape)
+    for i, (v, m) in enumerate(zip(ins, maps[:n_ins])):
+        inner[reg.arg_names[i]] = _map_input(v, m, outs.shape) if is_node(v) else v
+    if n_ins < len(reg.arg_names):
+        inner[reg.arg_names[n_ins]] = outs
+    r = tr.trace_ops(reg.ops, inner)
+    v = r.values[0] if isinstance(r, _Yield) else None
+    if is_node(v):
+        v = cast(v, outs.dtype)
+        if tuple(v.shape) != tuple(outs.shape):
+            v = Node("bcast", tuple(outs.shape), v.dtype, (v,), {"dims": [], "numpy": True})
+        return v
+    if isinstance(v, np.ndarray):
+        raise Unsupported("linalg.generic yielding a per-core scalar")
+    return const_node(v, outs.shape, outs.dtype)
+
+
+# ---- control flow -------------------------------------------------------------------
+def _loop_operand(tr, op, scope, k, key):
+    name = op.operands[k]
+    if name.startswith("__const_"):
+        return op.attrs["const_operands"][key]
+    return tr.get(scope, name)
+
+
+def _has_op(ops, names) -> bool:
+    from .ir import walk
+    return any(o.name in names for o in walk(ops))
+
+
+@rule("scf.for")
+def _for(tr: Tracer, op: Op, scope):
+    lb = _loop_operand(tr, op, scope, 0, "lb")
+    ub = _loop_operand(tr, op, scope, 1, "ub")
+    step = _loop_operand(tr, op, scope, 2, "step")
+    if not (is_iv(lb) and is_iv(ub) and is_iv(step)):
+        raise Unsupported("scf.for bounds must be integer values")
+    step = iv_bin(np.maximum, step, 1) if isinstance(step, np.ndarray) else max(int(step), 1)
+    span = iv_bin(lambda a, b: a - b, ub, lb)
+    trips = iv_bin(lambda s, st: np.maximum(-((-s) // st), 0), span, step)
+    trips_full = iv_full(trips, tuple(tr.axes))
+    if tr.active is not None:
+        trips_full = np.where(tr.active, trips_full, 0)
+    T = int(trips_full.max()) if trips_full.size else 0
+    reg = op.regions[0]
+    iv_name, iter_names = reg.arg_names[0], reg.arg_names[1:]
+    inits = [tr.get(scope, n) for n in op.operands[3:]]
+
+    if not iter_names:
+        if T == 0:
+            return None
+        depth = len(tr.axes)
+        k = np.arange(T, dtype=np.int64)
+        lb_f = iv_full(lb, tuple(tr.axes))[..., None]
+        st_f = iv_full(step, tuple(tr.axes))[..., None]
+        ivs = lb_f + k.reshape((1,) * depth + (T,)) * st_f
+        mask = k.reshape((1,) * depth + (T,)) < trips_full[..., None]
+        saved_axes, saved_active = list(tr.axes), tr.active
+        tr.axes.append(T)
+        tr.active = None if mask.all() else mask
+        tr._loop_counter += 1
+        tr.loop_path.append(tr._loop_counter)
+        inner = dict(scope)
+        inner[iv_name] = ivs
+        tr.trace_ops(reg.ops, inner)
+        tr.loop_path.pop()
+        tr.axes, tr.active = saved_axes, saved_active
+        return None
+
+    # loop-carried values
+    tmin = int(trips_full.min()) if trips_full.size else 0
+    live = trips_full if tr.active is None else trips_full[tr.active]
+    if live.size and int(live.min()) != T:
+        raise Unsupported("scf.for with iter_args and a trip count that differs between cores")
+    tile_carried = any(is_node(v) for v in inits)
+    if tile_carried and _has_op(reg.ops, ("linalg.matmul", "linalg.batch_matmul")) and T > 1:
+        return _symbolic_loop(tr, op, scope, lb, step, T, inits)
+    if T > MAX_UNROLL:
+        raise Unsupported(f"scf.for with iter_args and {T} iterations")
+    vals = list(inits)
+    for k in range(T):
+        inner = dict(scope)
+        inner[iv_name] = iv_bin(lambda a, b: a + b, lb, iv_bin(lambda s, kk: s * kk, step, k))
+        for n, v in zip(iter_names, vals):
+            inner[n] = v
+        r = tr.trace_ops(reg.ops, inner)
+        if isinstance(r, _Yield):
+            vals = list(r.values)
+    if not op.results:
+        return None
+    return vals[0] if len(vals) == 1 else tuple(vals)
+
+
+def _symbolic_loop(tr: Tracer, op: Op, scope, lb, step, T: int, inits):
+    """Trace the body once with the trip count as an extra (sequential) axis."""
+    reg = op.regions[0]
+    iv_name, iter_names = reg.arg_names[0], reg.arg_names[1:]
+    depth = len(tr.axes)
+    k = np.arange(T, dtype=np.int64)
+    ivs = (iv_full(lb, tuple(tr.axes))[..., None]
+           + k.reshape((1,) * depth + (T,)) * iv_full(step, tuple(tr.axes))[..., None])
+    saved_axes, n_stores = list(tr.axes), len(tr.stores)
+    tr.axes.append(T)
+    inner = dict(scope)
+    inner[iv_name] = ivs
+    placeholders = []
+    for i, (n, v) in enumerate(zip(iter_names, inits)):
+        if not is_node(v):
+            raise Unsupported("scf.for carrying both tiles and scalars around a matmul")
+        ph = Node("iter", v.shape, v.dtype, (), {"index": i})
+        placeholders.append(ph)
+        inner[n] = ph
+    r = tr.trace_ops(reg.ops, inner)
+    tr.axes = saved_axes
+    if len(tr.stores) != n_stores:
+        raise Unsupported("ktdp.store inside an scf.for that carries a matmul accumulator")
+    if not isinstance(r, _Yield):
+        raise ValueError("scf.for with iter_args must end in scf.yield")
+    info = LoopInfo(T, depth, list(inits), list(r.values))
+    for ph in placeholders:
+        ph.attrs["loop"] = info
+    results = [Node("loopres", v.shape, v.dtype, (), {"loop": info, "index": i})
+               for i, v in enumerate(inits)]
+    if not op.results:
+        return None
+    return results[0] if len(results) == 1 else tuple(results)
+
+
+@rule("scf.if")
+def _if(tr, op, scope):
+    cond = tr.get(scope, op.operands[0])
+    if is_node(cond):
+        raise Unsupported("scf.if on a tile condition")
+    if isinstance(cond, np.ndarray):
+        if op.results:
+            raise Unsupported("scf.if with results on a per-core condition")
+        full = iv_full(cond.astype(np.int64), tuple(tr.axes)).astype(bool)
+        saved = tr.active
+        for reg, m in zip(op.regions, (full, ~full)):
+            tr.active = m if saved is None else (saved & m)
+            if tr.active.any():
+                tr.trace_ops(reg.ops, dict(scope))
+        tr.active = saved
+        return None
+    reg = op.regions[0] if cond else (op.regions[1] if len(op.regions) > 1 else None)
+    if reg is None:
+        return None
+    r = tr.trace_ops(reg.ops, dict(scope))
+    if isinstance(r, _Yield) and r.values:
+        return r.values[0] if len(r.values) == 1 else tuple(r.values)
+    return None
+
+
+@rule("return", "func.return")
+def _return(tr, op, scope):
+    return None

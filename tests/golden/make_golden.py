@@ -1,0 +1,83 @@
+"""Regenerates ``tests/golden/*.npz`` by running the UNMODIFIED reference interpreter.
+
+Usage (only where the reference checkout is available):
+
+    python tests/golden/make_golden.py /path/to/reference
+
+Each fixture stores the KTIR source, the seeded inputs and the outputs the
+reference produced, plus the NumPy version and CPU features of the generating
+host (f16 transcendentals in NumPy are host-dependent by 1 ulp).  The tests
+never import the reference; they only read these files.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from ktir_cpu_b200 import kernels as K  # noqa: E402
+
+
+def cases():
+    """name -> (source, function, kwargs). Shared with the tests through the fixture files."""
+    out = {}
+    rng = np.random.default_rng(1)
+    x, y = rng.standard_normal(4096).astype(np.float16), rng.standard_normal(4096).astype(np.float16)
+    out["vector_add_4096"] = (K.vector_add(4096, 128, 32), "add_kernel",
+                              dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(4096, np.float16), BLOCK_SIZE=128))
+    x, y = rng.standard_normal(16384).astype(np.float16), rng.standard_normal(16384).astype(np.float16)
+    out["vector_add_loop"] = (K.vector_add(16384, 128, 32), "add_kernel",
+                              dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(16384, np.float16), BLOCK_SIZE=128))
+    rng = np.random.default_rng(2)
+    for f32 in (True, False):
+        x = (rng.standard_normal((64, 256)) * 2).astype(np.float16)
+        out[f"softmax_{'f32' if f32 else 'f16'}_64x256"] = (
+            K.softmax_rows(64, 256, 4, 4, f32), "softmax_kernel",
+            dict(output_ptr=np.zeros_like(x), input_ptr=x))
+    x = (rng.standard_normal((32, 4096)) * 2).astype(np.float16)
+    out["softmax_f32_32x4096"] = (K.softmax_rows(32, 4096, 4, 2, True), "softmax_kernel",
+                                  dict(output_ptr=np.zeros_like(x), input_ptr=x))
+    rng = np.random.default_rng(3)
+    table = rng.standard_normal((256, 128)).astype(np.float16)
+    idx = rng.integers(0, 256, 1024).astype(np.int32)
+    for t in range(1024 // 64):                     # ~10 % duplicates inside each 64-entry tile
+        pos = rng.choice(64, 12, replace=False)
+        idx[t * 64 + pos[:6]] = idx[t * 64 + pos[6:]]
+    out["gather_scale_scatter_256"] = (
+        K.gather_scale_scatter(256, 128, 1024, 64, 4), "gather_scale_scatter",
+        dict(table_ptr=table, idx_ptr=idx, out_ptr=np.zeros_like(table)))
+    idx0 = np.zeros(256, np.int32)                  # every entry hits row 0
+    out["gather_scale_scatter_allzero"] = (
+        K.gather_scale_scatter(16, 128, 256, 64, 2), "gather_scale_scatter",
+        dict(table_ptr=table[:16].copy(), idx_ptr=idx0, out_ptr=np.zeros((16, 128), np.float16)))
+    rng = np.random.default_rng(4)
+    for f32 in (True, False):
+        a = rng.uniform(-1, 1, (128, 128)).astype(np.float16)
+        b = rng.uniform(-1, 1, (128, 128)).astype(np.float16)
+        out[f"matmul_{'f32acc' if f32 else 'f16acc'}_128"] = (
+            K.tiled_matmul(128, 128, 128, 64, 64, 64, 2, f32), "matmul_kernel",
+            dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((128, 128), np.float16)))
+    return out
+
+
+def main(ref_root: str):
+    sys.path.insert(0, ref_root)
+    from ktir_cpu import KTIRInterpreter
+    meta = f"numpy {np.__version__}"
+    for name, (src, fn, kw) in cases().items():
+        interp = KTIRInterpreter()
+        interp.load(src)
+        res = interp.execute_function(fn, **kw)
+        payload = {"__source__": np.array(src), "__function__": np.array(fn), "__host__": np.array(meta)}
+        for k, v in kw.items():
+            payload["in__" + k] = np.asarray(v)
+        for k, v in res.items():
+            payload["out__" + k] = v
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **payload)
+        print("wrote", name)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,109 @@
+"""Host-side logic that needs no GPU: parser, whole-grid trace, launch plans, C-ABI exports."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, load_golden
+from ktir_cpu_b200 import kernels as K
+from ktir_cpu_b200 import runtime as R
+from ktir_cpu_b200.affine import parse_affine_map, parse_affine_set
+from ktir_cpu_b200.interpreter import KTIRInterpreter, Session
+from ktir_cpu_b200.parser import KTIRParser
+from ktir_cpu_b200.trace import Unsupported
+
+F16 = np.dtype(np.float16)
+
+
+def _plan(src, fn, tensors, scalars):
+    m = KTIRParser().parse_module(src)
+    return Session(R.PlanOnlyDevice(), m.get_function(fn), tensors, scalars)
+
+
+def test_affine_parse_and_box():
+    s = parse_affine_set("affine_set<(d0, d1) : (d0 >= 0, -d0 + 31 >= 0, d1 >= 0, -d1 + 127 >= 0)>")
+    assert s.box() == ((0, 0), (32, 128))
+    m = parse_affine_map("affine_map<(d0, d1) -> (d1, d0 * 2 + 1)>")
+    assert m.eval([3, 5]) == (5, 7)
+    assert not m.is_identity() and parse_affine_map("affine_map<(d0) -> (d0)>").is_identity()
+    tri = parse_affine_set("affine_set<(d0, d1) : (d0 >= 0, -d0 + 3 >= 0, d1 >= 0, d0 - d1 >= 0)>")
+    assert tri.box() is None
+    assert tri.enumerate((4, 4)) == [(i, j) for i in range(4) for j in range(4) if j <= i]
+
+
+def test_parser_function_metadata():
+    m = KTIRParser().parse_module(K.vector_add())
+    f = m.get_function("add_kernel")
+    assert f.grid == (32, 1, 1)
+    assert f.arg_names == ["x_ptr", "y_ptr", "output_ptr", "BLOCK_SIZE"]
+    assert f.tensor_sizes["x_ptr"] == {"shape": (4096,), "dtype": "f16"}
+    with pytest.raises(ValueError, match="not found in module"):
+        m.get_function("nope")
+
+
+def test_interpreter_api_errors():
+    it = KTIRInterpreter()
+    with pytest.raises(RuntimeError, match="No module loaded"):
+        it.arg_names("f")
+    with pytest.raises(RuntimeError, match="No module loaded"):
+        it.tensor_input_output_sizes("f")
+    it.load(K.vector_add())
+    assert it.arg_names("add_kernel")[0] == "x_ptr"
+    assert it.get_latency_report() is None
+
+
+def test_plan_vector_add():
+    t = [("x_ptr", (4096,), F16), ("y_ptr", (4096,), F16), ("output_ptr", (4096,), F16)]
+    s = _plan(K.vector_add(), "add_kernel", t, dict(BLOCK_SIZE=128))
+    (st,) = s.plan.statements
+    assert st.kind == "ew_stream" and st.args.n_items == 32 and st.args.cols == 128
+    assert st.program.n_ops == 1 and st.program.ops[0].opcode == (R.VM["ADD"] | R.VM_ROUND16)
+    # KTIR pointer values are element indices of byte addresses starting at 0x10000
+    assert st.table[0].tolist() == [0x10000 // 2, (0x10000 + 8192) // 2, (0x10000 + 16384) // 2]
+    assert st.table[1, 0] - st.table[0, 0] == 128
+    assert s.written == {"output_ptr"}
+
+
+def test_plan_softmax_flattens_loop_into_launch():
+    t = [("output_ptr", (8192, 4096), F16), ("input_ptr", (8192, 4096), F16)]
+    s = _plan(K.softmax_rows(8192, 4096, 32, 8, True), "softmax_kernel", t, {})
+    (st,) = s.plan.statements
+    assert st.kind == "row_softmax"
+    assert st.args.n_items == 32 * 32 and st.args.rows_per_item == 8 and st.args.cols == 4096
+    assert st.args.f16_arith == 0 and st.args.max_init == float("-inf")
+    assert st.bytes_moved() == 2 * 8192 * 4096 * 2
+
+
+def test_cross_core_overlap_is_rejected():
+    """Two cores storing to the same tile need the sequential core order of the reference."""
+    src = K.vector_add(4096, 128, 32).replace("%offset = arith.muli %core_id, %BLOCK_SIZE : index",
+                                              "%offset = arith.constant 0 : index")
+    t = [("x_ptr", (4096,), F16), ("y_ptr", (4096,), F16), ("output_ptr", (4096,), F16)]
+    with pytest.raises(Unsupported, match="sequential core order"):
+        _plan(src, "add_kernel", t, dict(BLOCK_SIZE=128))
+
+
+def test_unmapped_pointer_raises_value_error():
+    src = K.vector_add(4096, 128, 32)
+    t = [("x_ptr", (4096,), F16), ("y_ptr", (4096,), F16)]
+    with pytest.raises(ValueError, match="unmapped address"):
+        _plan(src, "add_kernel", t, dict(output_ptr=0, BLOCK_SIZE=128))
+
+
+def test_unknown_op_is_reported_at_execution():
+    src = K.vector_add().replace("arith.addf %x, %y", "arith.frobnicate %x, %y")
+    t = [("x_ptr", (4096,), F16), ("y_ptr", (4096,), F16), ("output_ptr", (4096,), F16)]
+    with pytest.raises(ValueError, match="Unknown operation: arith.frobnicate"):
+        _plan(src, "add_kernel", t, dict(BLOCK_SIZE=128))
+
+
+def test_library_exports_every_declared_symbol(build_lib):
+    header = open(os.path.join(ROOT, "include", "ktir_b200.h")).read()
+    declared = set(re.findall(r"\b(ktb_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(build_lib)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in include/ktir_b200.h but not exported"
+    assert declared == set(R.SYMBOLS), "ctypes binding and header disagree"
