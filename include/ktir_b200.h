@@ -133,6 +133,52 @@ typedef struct {
 } ktb_softmax_args;
 int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args);
 
+/* ---- row gather / ordered row scatter ---------------------------------------------
+ * A statement moves E = n_tiles * tile_rows rows ("entries") of `cols` elements per
+ * operand; entry (t, pos) of an operand lives at element offset
+ *     base[t] + IDX[idx_off[t] + pos * idx_stride] * idx_mult + pos * pos_stride   (indirect)
+ *     base[t] + pos * pos_stride                                                    (direct)
+ * Replaces MemoryOps.indirect_load / indirect_store and the per-point index
+ * resolution behind them (ktir_cpu/ops/memory_ops.py:330-386, 488-576, 867-964) plus
+ * the fancy-index gather/scatter of the memory simulator (ktir_cpu/memory.py:243-251,
+ * 281-291): reads outside [lo, hi) give 0, writes outside are dropped, a negative
+ * index sets ktb_status.negative_index. */
+#define KTB_ROWS_MAX_IN 3
+typedef struct {
+    int32_t indirect;             /* 1: the row address uses an index lookup */
+    int32_t dtype;                /* KTB_F16 / KTB_F32 */
+    int32_t idx_dtype;            /* KTB_I32 / KTB_I64 */
+    int32_t alias_dst;            /* inputs only: 1 = reads the destination row (read-modify-write) */
+    const int64_t* dev_base;      /* [n_tiles] element offset of the tile's direct part */
+    const int64_t* dev_idx_off;   /* [n_tiles] element offset (index units) of the tile's first index */
+    int64_t idx_stride;           /* index elements between consecutive tile rows (0: one index per tile) */
+    int64_t idx_mult;             /* data elements per unit of index value */
+    int64_t pos_stride;           /* data elements between consecutive tile rows (direct part) */
+    int64_t lo, hi;               /* allocation bounds in data elements */
+} ktb_row_operand;
+
+typedef struct {
+    void* arena;
+    int64_t n_tiles;
+    int32_t tile_rows, cols;
+    int32_t n_in;
+    int32_t vector_ok;            /* 1: cols and every row address are multiples of 4 elements */
+    ktb_row_operand in[KTB_ROWS_MAX_IN];
+    ktb_row_operand out;
+    ktb_vm_program program;
+    int32_t* dev_rowid_scratch;   /* scatter only: n_tiles * tile_rows int32 of scratch */
+    int64_t dst_row0;             /* scatter only: element offset of destination row id 0 */
+    int64_t dst_rows;             /* scatter only: number of destination rows */
+} ktb_rows_args;
+
+/* out (direct) = program(inputs); inputs may be gathered.  ktdp.load through an
+ * indirect access tile followed by elementwise ops and a direct ktdp.store. */
+int ktb_launch_rows_program(ktb_ctx* ctx, const ktb_rows_args* args);
+/* out (indirect) = program(inputs), tiles applied in order, last writer of a row
+ * within a tile wins — ktdp.store through an indirect access tile, including the
+ * load/modify/store-back form. */
+int ktb_launch_scatter_rows(ktb_ctx* ctx, const ktb_rows_args* args);
+
 #ifdef __cplusplus
 }
 #endif

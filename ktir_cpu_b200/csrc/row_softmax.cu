@@ -1,11 +1,19 @@
-// Fused row softmax: one pass over HBM (read the row once, write it once).
-// A row of `cols` elements is held in registers by T = min(256, cols/8) threads,
-// thread t owning 16-byte vectors j*T + t, so global accesses are unit-stride
-// and 128-bit.  Both reductions fold x[i] (op) x[i + h] for h = cols/2 ... 1 —
-// the halving order of the reference's linalg.reduce
-// (ktir_cpu/dialects/linalg_ops.py:86-133) — first across a thread's own
-// vectors, then across warps through shared memory, then by warp shuffle, then
-// across the 8 lanes of the remaining vector.
+// Fused row softmax: one pass over HBM (the row is read once and written once).
+//
+// A row of `cols` elements is held in registers by a group of T threads
+// (T = cols/64, between 1 and 256; 8 vectors of 8 elements per thread at most),
+// thread t owning the 16-byte vectors j*T + t, so global accesses are unit-stride
+// and 128-bit.  A CTA of 256 threads carries 256/T independent row groups; groups
+// wider than a warp synchronise on their own named barrier, narrower ones need no
+// barrier at all, so many rows are in flight per SM and the kernel stays HBM-bound.
+//
+// Both reductions fold x[i] (op) x[i + h] for h = cols/2 ... 1 — the halving order
+// of the reference's linalg.reduce (ktir_cpu/dialects/linalg_ops.py:86-133): first
+// across a thread's own vectors, then across the warps of the group (one shared
+// memory exchange, combined in the same pairing), then by warp shuffle, then
+// across the 8 elements of the remaining vector.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 template <bool MAXNUM>
@@ -14,102 +22,140 @@ static __device__ __forceinline__ float sm_max(float a, float b) {
     return fmaxf(a, b);
 }
 
-// OP 0: max, 1: add.  Returns the fold of the T*8*NV values in every thread of the row group.
+template <int OP, bool MAXNUM, bool R16>
+static __device__ __forceinline__ float sm_comb(float a, float b) {
+    if (OP == 0) return sm_max<MAXNUM>(a, b);
+    const float r = a + b;
+    return R16 ? ktb_round16(r) : r;
+}
+
+// Named barrier of one row group (ids 1..4 as literals so only those are reserved).
+static __device__ __forceinline__ void group_barrier(int id, int threads) {
+    switch (id) {
+        case 1: asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory"); break;
+        case 2: asm volatile("bar.sync 2, %0;" ::"r"(threads) : "memory"); break;
+        case 3: asm volatile("bar.sync 3, %0;" ::"r"(threads) : "memory"); break;
+        default: asm volatile("bar.sync 4, %0;" ::"r"(threads) : "memory"); break;
+    }
+}
+
+// Pairing of the cross-warp levels: value(base, stride, n) = value(base, 2*stride, n/2)
+// (op) value(base + stride, 2*stride, n/2), leaves are the per-warp partials.
+template <int OP, bool MAXNUM, bool R16>
+static __device__ __forceinline__ float warp_tree(const float* p, int n_warps, int lane_slot_stride) {
+    // p[w * lane_slot_stride] is the partial of warp w for this (lane, slot)
+    float o[8];
+#pragma unroll
+    for (int w = 0; w < 8; ++w) o[w] = w < n_warps ? p[w * lane_slot_stride] : 0.f;
+    if (n_warps == 8) {
+        const float a = sm_comb<OP, MAXNUM, R16>(sm_comb<OP, MAXNUM, R16>(o[0], o[4]), sm_comb<OP, MAXNUM, R16>(o[2], o[6]));
+        const float b = sm_comb<OP, MAXNUM, R16>(sm_comb<OP, MAXNUM, R16>(o[1], o[5]), sm_comb<OP, MAXNUM, R16>(o[3], o[7]));
+        return sm_comb<OP, MAXNUM, R16>(a, b);
+    }
+    if (n_warps == 4)
+        return sm_comb<OP, MAXNUM, R16>(sm_comb<OP, MAXNUM, R16>(o[0], o[2]), sm_comb<OP, MAXNUM, R16>(o[1], o[3]));
+    return sm_comb<OP, MAXNUM, R16>(o[0], o[1]);
+}
+
+// Fold of the T*8*NV values of a row; every thread of the group gets the result.
 template <int NV, int OP, bool MAXNUM, bool R16>
-static __device__ __forceinline__ float row_fold(float (&x)[NV][8], int T, int t, int group,
-                                                 float* xchg /* [groups][T][8] */, float* bcast /* [groups] */) {
-    auto comb = [](float a, float b) -> float {
-        float r = OP == 0 ? sm_max<MAXNUM>(a, b) : a + b;
-        return (R16 && OP == 1) ? ktb_round16(r) : r;
-    };
+static __device__ __forceinline__ float row_fold(const float (&x)[NV][8], int T, int t, int group,
+                                                 float* xchg /* [256][8] */, float* bcast /* [256/32] */) {
     float v[8];
+    if (NV == 1) {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) v[k] = x[0][k];
-    if (NV > 1) {
-        float w[NV][8];
+        for (int k = 0; k < 8; ++k) v[k] = x[0][k];
+    } else {
+        constexpr int H = NV / 2 > 0 ? NV / 2 : 1;
+        float w[H][8];
 #pragma unroll
-        for (int j = 0; j < NV; ++j)
+        for (int j = 0; j < H; ++j)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) w[j][k] = x[j][k];
+            for (int k = 0; k < 8; ++k) w[j][k] = sm_comb<OP, MAXNUM, R16>(x[j][k], x[j + H][k]);
 #pragma unroll
-        for (int m = NV / 2; m >= 1; m >>= 1)
+        for (int m = H / 2; m >= 1; m >>= 1)
 #pragma unroll
             for (int j = 0; j < m; ++j)
 #pragma unroll
-                for (int k = 0; k < 8; ++k) w[j][k] = comb(w[j][k], w[j + m][k]);
+                for (int k = 0; k < 8; ++k) w[j][k] = sm_comb<OP, MAXNUM, R16>(w[j][k], w[j + m][k]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = w[0][k];
     }
-    float* mine = xchg + ((size_t)group * T + t) * 8;
-    for (int d = T / 2; d >= 32; d >>= 1) {
+    if (T > 32) {
+        const int n_warps = T >> 5;
+        float* mine = xchg + (size_t)threadIdx.x * 8;
 #pragma unroll
         for (int k = 0; k < 8; ++k) mine[k] = v[k];
-        __syncthreads();
-        if (t < d) {
-            const float* other = mine + (size_t)d * 8;
+        group_barrier(1 + group, T);
+        if (t < 32) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = comb(v[k], other[k]);
+            for (int k = 0; k < 8; ++k) v[k] = warp_tree<OP, MAXNUM, R16>(mine + k, n_warps, 32 * 8);
         }
-        __syncthreads();
     }
     const int w = T < 32 ? T : 32;
-    for (int d = w / 2; d >= 1; d >>= 1) {
+    for (int d = w >> 1; d >= 1; d >>= 1) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            float o = __shfl_down_sync(0xffffffffu, v[k], d, w);
-            v[k] = comb(v[k], o);
+            const float o = __shfl_down_sync(0xffffffffu, v[k], d, w);
+            v[k] = sm_comb<OP, MAXNUM, R16>(v[k], o);
         }
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = comb(v[k], v[k + 4]);
-    v[0] = comb(v[0], v[2]);
-    v[1] = comb(v[1], v[3]);
-    v[0] = comb(v[0], v[1]);
-    if (t == 0) bcast[group] = v[0];
-    __syncthreads();
-    float r = bcast[group];
-    __syncthreads();
-    return r;
+    for (int k = 0; k < 4; ++k) v[k] = sm_comb<OP, MAXNUM, R16>(v[k], v[k + 4]);
+    v[0] = sm_comb<OP, MAXNUM, R16>(v[0], v[2]);
+    v[1] = sm_comb<OP, MAXNUM, R16>(v[1], v[3]);
+    v[0] = sm_comb<OP, MAXNUM, R16>(v[0], v[1]);
+    if (T > 32) {
+        if (t == 0) bcast[group] = v[0];
+        group_barrier(1 + group, T);
+        return bcast[group];
+    }
+    return __shfl_sync(0xffffffffu, v[0], 0, w);
 }
 
 template <int NV, bool MAXNUM, bool R16>
-__global__ void __launch_bounds__(256) ktb_row_softmax_kernel(const ktb_softmax_args a, int T, int64_t total_rows) {
-    extern __shared__ float smem[];
+__global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3) ktb_row_softmax_kernel(const ktb_softmax_args a, int T, int64_t total_rows) {
+    __shared__ float xchg[256 * 8];
+    __shared__ float bcast[8];
     const int groups = 256 / T;
-    float* xchg = smem;
-    float* bcast = smem + 256 * 8;
     const int group = threadIdx.x / T;
     const int t = threadIdx.x - group * T;
-    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    const __half* in16 = reinterpret_cast<const __half*>(a.arena);
+    const float* in32 = reinterpret_cast<const float*>(a.arena);
 
+    // the trip count is the same for every thread of the CTA (shuffles use full-warp masks);
+    // a group past the last row recomputes row 0 and skips the store
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
     for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
-        const int64_t row = it * groups + group;
-        const bool live = row < total_rows;
-        const int64_t item = live ? row / a.rows_per_item : 0;
-        const int64_t r = live ? row - item * a.rows_per_item : 0;
+        const bool live = it * groups + group < total_rows;
+        const int64_t row = live ? it * groups + group : 0;
+        const int64_t item = row / a.rows_per_item;
+        const int64_t r = row - item * a.rows_per_item;
         const int64_t in_off = a.dev_item_offsets[item * 2] + r * a.in_row_stride;
         const int64_t out_off = a.dev_item_offsets[item * 2 + 1] + r * a.out_row_stride;
 
         float x[NV][8];
+        if (a.in_dtype == KTB_F16) {
+            uint4 raw[NV];
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int64_t e = in_off + ((int64_t)j * T + t) * 8;
-            if (!live) {
+            for (int j = 0; j < NV; ++j)
+                raw[j] = __ldcs(reinterpret_cast<const uint4*>(in16 + in_off + ((int64_t)j * T + t) * 8));
 #pragma unroll
-                for (int k = 0; k < 8; ++k) x[j][k] = 0.f;
-            } else if (a.in_dtype == KTB_F16) {
-                uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(a.arena) + e);
-                const __half2* h = reinterpret_cast<const __half2*>(&raw);
+            for (int j = 0; j < NV; ++j) {
+                const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    float2 f = __half22float2(h[i]);
+                    const float2 f = __half22float2(h[i]);
                     x[j][2 * i] = f.x;
                     x[j][2 * i + 1] = f.y;
                 }
-            } else {
-                const float* p = reinterpret_cast<const float*>(a.arena) + e;
-                float4 lo = *reinterpret_cast<const float4*>(p);
-                float4 hi = *reinterpret_cast<const float4*>(p + 4);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const float* p = in32 + in_off + ((int64_t)j * T + t) * 8;
+                const float4 lo = __ldcs(reinterpret_cast<const float4*>(p));
+                const float4 hi = __ldcs(reinterpret_cast<const float4*>(p + 4));
                 x[j][0] = lo.x; x[j][1] = lo.y; x[j][2] = lo.z; x[j][3] = lo.w;
                 x[j][4] = hi.x; x[j][5] = hi.y; x[j][6] = hi.z; x[j][7] = hi.w;
             }
@@ -123,31 +169,30 @@ __global__ void __launch_bounds__(256) ktb_row_softmax_kernel(const ktb_softmax_
             for (int k = 0; k < 8; ++k) {
                 float d = x[j][k] - mx;
                 if (R16) d = ktb_round16(d);
-                float e = expf(d);
+                const float e = expf(d);
                 x[j][k] = R16 ? ktb_round16(e) : e;
             }
         float sum = row_fold<NV, 1, MAXNUM, R16>(x, T, t, group, xchg, bcast);
         sum = sum + a.sum_init;
         if (R16) sum = ktb_round16(sum);
 
-        if (live) {
+        if (!live) continue;
 #pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int64_t e = out_off + ((int64_t)j * T + t) * 8;
-                float y[8];
+        for (int j = 0; j < NV; ++j) {
+            const int64_t e = out_off + ((int64_t)j * T + t) * 8;
+            float y[8];
 #pragma unroll
-                for (int k = 0; k < 8; ++k) y[k] = x[j][k] / sum;
-                if (a.out_dtype == KTB_F16) {
-                    uint4 raw;
-                    __half2* h = reinterpret_cast<__half2*>(&raw);
+            for (int k = 0; k < 8; ++k) y[k] = x[j][k] / sum;
+            if (a.out_dtype == KTB_F16) {
+                uint4 raw;
+                __half2* h = reinterpret_cast<__half2*>(&raw);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + e) = raw;
-                } else {
-                    float* p = reinterpret_cast<float*>(a.arena) + e;
-                    *reinterpret_cast<float4*>(p) = make_float4(y[0], y[1], y[2], y[3]);
-                    *reinterpret_cast<float4*>(p + 4) = make_float4(y[4], y[5], y[6], y[7]);
-                }
+                for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+                __stcs(reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + e), raw);
+            } else {
+                float* p = reinterpret_cast<float*>(a.arena) + e;
+                __stcs(reinterpret_cast<float4*>(p), make_float4(y[0], y[1], y[2], y[3]));
+                __stcs(reinterpret_cast<float4*>(p + 4), make_float4(y[4], y[5], y[6], y[7]));
             }
         }
     }
@@ -159,10 +204,8 @@ static void launch_softmax(ktb_ctx* ctx, const ktb_softmax_args& a, int T, int64
     const int64_t n_iter = (total_rows + groups - 1) / groups;
     int64_t blocks = (int64_t)ctx->sm_count * 8;
     if (blocks > n_iter) blocks = n_iter;
-    const size_t smem = (256 * 8 + 256) * sizeof(float);
     const bool mn = a.max_is_maxnum != 0, r16 = a.f16_arith != 0;
-#define KTB_SM_LAUNCH(MN, R)                                                                       \
-    ktb_row_softmax_kernel<NV, MN, R><<<(unsigned)blocks, 256, smem, ctx->stream>>>(a, T, total_rows)
+#define KTB_SM_LAUNCH(MN, R) ktb_row_softmax_kernel<NV, MN, R><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows)
     if (mn && r16) KTB_SM_LAUNCH(true, true);
     else if (mn) KTB_SM_LAUNCH(true, false);
     else if (r16) KTB_SM_LAUNCH(false, true);
@@ -181,7 +224,14 @@ extern "C" int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args
     if ((a.in_row_stride % 8) || (a.out_row_stride % 8))
         return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_softmax", "row strides must be multiples of 8 elements");
     const int vecs = a.cols / 8;
-    const int T = vecs < 256 ? vecs : 256;
+    int per_thread = 8;               // vectors per thread (tunable for experiments)
+    if (const char* e = getenv("KTB_SOFTMAX_NV")) {
+        const int v = atoi(e);
+        if (v == 1 || v == 2 || v == 4 || v == 8) per_thread = v;
+    }
+    int T = vecs / per_thread;
+    if (T < 1) T = 1;
+    if (T > 256) T = 256;             // ... unless the row is wider than 16384 elements
     const int NV = vecs / T;
     const int64_t total_rows = a.n_items * (int64_t)a.rows_per_item;
     switch (NV) {

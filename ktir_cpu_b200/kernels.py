@@ -247,3 +247,57 @@ def tiled_matmul(M: int = 4096, N: int = 4096, K: int = 4096, bm: int = 64, bn: 
     s += (f"      ktdp.store {cval}, %c_tile : {tc16}, !ktdp.access_tile<{bm}x{bn}xindex>\n"
           f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
     return s
+
+
+def gather_rows(n_table_rows: int, cols: int, n_idx: int, tile_rows: int, cores: int,
+                idx_dtype: str = "i32") -> str:
+    """out[e, :] = table[idx[e], :] — indirect load, direct store."""
+    per_core = n_idx // cores
+    assert per_core * cores == n_idx and per_core % tile_rows == 0
+    t = f"tensor<{tile_rows}x{cols}xf16>"
+    at = f"!ktdp.access_tile<{tile_rows}x{cols}xindex>"
+    s = (f"module {{\n  func.func @gather_rows(%table_ptr: index, %idx_ptr: index, %out_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n"
+         f"    %tile_rows = arith.constant {tile_rows} : index\n"
+         f"    %begin = arith.muli %pid, %per_core : index\n"
+         f"    %end = arith.addi %begin, %per_core : index\n")
+    s += view("table", "table_ptr", [n_table_rows, cols], "f16")
+    s += view("out", "out_ptr", [n_idx, cols], "f16")
+    s += view("idx", "idx_ptr", [n_idx], idx_dtype)
+    s += "    scf.for %base = %begin to %end step %tile_rows {\n"
+    s += _iat("src", "table", "idx", "%base", tile_rows, cols, n_table_rows, n_idx, idx_dtype, "      ")
+    s += tile("dst", "out", ["%base", "%c0"], [tile_rows, cols], [n_idx, cols], "f16", "      ")
+    s += (f"      %rows = ktdp.load %src : {at} -> {t}\n"
+          f"      ktdp.store %rows, %dst : {t}, {at}\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
+def scatter_rows(n_out_rows: int, cols: int, n_idx: int, tile_rows: int, cores: int,
+                 idx_dtype: str = "i32") -> str:
+    """out[idx[e], :] = src[e, :] — direct load, indirect store (last writer of a row wins)."""
+    per_core = n_idx // cores
+    assert per_core * cores == n_idx and per_core % tile_rows == 0
+    t = f"tensor<{tile_rows}x{cols}xf16>"
+    at = f"!ktdp.access_tile<{tile_rows}x{cols}xindex>"
+    s = (f"module {{\n  func.func @scatter_rows(%src_ptr: index, %idx_ptr: index, %out_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n"
+         f"    %tile_rows = arith.constant {tile_rows} : index\n"
+         f"    %begin = arith.muli %pid, %per_core : index\n"
+         f"    %end = arith.addi %begin, %per_core : index\n")
+    s += view("src", "src_ptr", [n_idx, cols], "f16")
+    s += view("out", "out_ptr", [n_out_rows, cols], "f16")
+    s += view("idx", "idx_ptr", [n_idx], idx_dtype)
+    s += "    scf.for %base = %begin to %end step %tile_rows {\n"
+    s += tile("from", "src", ["%base", "%c0"], [tile_rows, cols], [n_idx, cols], "f16", "      ")
+    s += _iat("to", "out", "idx", "%base", tile_rows, cols, n_out_rows, n_idx, idx_dtype, "      ")
+    s += (f"      %rows = ktdp.load %from : {at} -> {t}\n"
+          f"      ktdp.store %rows, %to : {t}, {at}\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s

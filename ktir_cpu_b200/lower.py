@@ -548,6 +548,10 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap) -> Plan:
             from .lower_mm import try_lower_matmul
             stmt = try_lower_matmul(dev, st, arena, sid)
         if stmt is None:
+            from .lower_scatter import RowsStatement, has_indirect_load
+            if has_indirect_load(st.value):
+                stmt = RowsStatement(dev, st, arena, sid)
+        if stmt is None:
             stmt = EwStatement(dev, st, arena, sid)
         plan.statements.append(stmt)
     fps = [f for s in plan.statements for f in s.footprints()]

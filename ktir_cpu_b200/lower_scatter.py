@@ -1,8 +1,264 @@
-"""Lowering of indirect (gather / scatter) statements."""
+"""Lowering of statements that move whole rows through an index tensor.
+
+``ktdp.load`` / ``ktdp.store`` through an indirect access tile resolve, per
+point of the variable space, one coordinate per dimension of the parent view —
+either an affine expression of the point or a value read from an index view
+(ktir_cpu/ops/memory_ops.py:488-576).  The device kernels handle the common
+blocked form: a tile of R rows x C contiguous columns whose row address is
+``base + IDX[i0 + r * istride] * mult + r * rstride`` (MoE / paged-attention /
+embedding-style gathers and scatters).  Anything else raises ``Unsupported``.
+"""
 from __future__ import annotations
 
-from .trace import Unsupported
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any, List, Optional, Tuple
+
+import numpy as np
+
+from . import runtime as R
+from .dtypes import bytes_per_elem
+from .lower import ArenaMap, Footprint, ProgramBuilder, Statement, _points
+from .trace import Access, IndirectAccess, Node, Store, Unsupported, iv_bin, iv_full
+
+
+def _lin(expr, n_vars: int, ssa) -> Tuple[List[int], Any]:
+    """expr -> (integer coefficient per variable, constant part as an integer value)."""
+    k = expr[0]
+    if k == "const":
+        return [0] * n_vars, int(expr[1])
+    if k == "var":
+        c = [0] * n_vars
+        c[expr[1]] = 1
+        return c, 0
+    if k == "ssa":
+        return [0] * n_vars, ssa[expr[1]]
+    if k == "neg":
+        c, b = _lin(expr[1], n_vars, ssa)
+        return [-x for x in c], iv_bin(lambda a, _: -a, b, 0)
+    ca, ba = _lin(expr[1], n_vars, ssa)
+    cb, bb = _lin(expr[2], n_vars, ssa)
+    if k in ("add", "sub"):
+        s = 1 if k == "add" else -1
+        return [x + s * y for x, y in zip(ca, cb)], iv_bin(lambda a, b: a + s * b, ba, bb)
+    if k == "mul":
+        if not any(ca) and isinstance(ba, (int, np.integer)):
+            return [int(ba) * y for y in cb], iv_bin(lambda a, b: a * b, ba, bb)
+        if not any(cb) and isinstance(bb, (int, np.integer)):
+            return [int(bb) * x for x in ca], iv_bin(lambda a, b: a * b, ba, bb)
+        if not any(ca) and not any(cb):
+            return [0] * n_vars, iv_bin(lambda a, b: a * b, ba, bb)
+    raise Unsupported(f"non-affine subscript ({k}) in an indirect access tile")
+
+
+@dataclass
+class RowForm:
+    """Row-addressing of one operand over the tiles of a statement."""
+    indirect: bool
+    dtype: str
+    base: np.ndarray                 # [n_tiles] element offsets
+    pos_stride: int
+    idx_dtype: str = "i32"
+    idx_off: Optional[np.ndarray] = None
+    idx_stride: int = 0
+    idx_mult: int = 0
+    rows: int = 1
+    cols: int = 1
+
+    def same_rows(self, o: "RowForm") -> bool:
+        return (self.indirect and o.indirect and self.dtype == o.dtype and self.pos_stride == o.pos_stride
+                and self.idx_dtype == o.idx_dtype and self.idx_stride == o.idx_stride
+                and self.idx_mult == o.idx_mult and np.array_equal(self.base, o.base)
+                and np.array_equal(self.idx_off, o.idx_off))
+
+
+def _rc_dims(shape) -> Tuple[Optional[int], Optional[int]]:
+    big = [i for i, s in enumerate(shape) if s > 1]
+    if len(big) > 2:
+        raise Unsupported(f"indirect tile of shape {tuple(shape)} (more than two non-unit dims)")
+    if not big:
+        return None, None
+    if len(big) == 1:
+        return None, big[0]
+    return big[0], big[1]
+
+
+def row_form(acc, store: Store, sel: np.ndarray) -> RowForm:
+    axes = store.axes
+
+    def per_tile(v) -> np.ndarray:
+        return np.ascontiguousarray(iv_full(v, axes).reshape(-1)[sel]).astype(np.int64)
+
+    if isinstance(acc, Access):
+        if acc.coords is not None:
+            raise Unsupported("coordinate-set access tile next to an indirect one")
+        rd, cd = _rc_dims(acc.shape)
+        if cd is not None and acc.strides[cd] != 1:
+            raise Unsupported("row operand whose columns are not unit-stride")
+        return RowForm(False, acc.view.dtype, per_tile(acc.off), acc.strides[rd] if rd is not None else 0,
+                       rows=acc.shape[rd] if rd is not None else 1, cols=acc.shape[cd] if cd is not None else 1)
+
+    ia: IndirectAccess = acc
+    if ia.order is not None and not ia.order.is_identity():
+        raise Unsupported("indirect access tile with a permuted variables_space_order")
+    box = ia.aset.box()
+    if box is None:
+        raise Unsupported("indirect access tile over a non-rectangular variable space")
+    lo, hi = box
+    ext = [h - l for l, h in zip(lo, hi)]
+    nv = len(ext)
+    rd, cd = _rc_dims(ext)
+    base = ia.view.base
+    pos_stride, col_stride = 0, 0
+    form = RowForm(True, ia.view.dtype, None, 0, rows=ext[rd] if rd is not None else 1,
+                   cols=ext[cd] if cd is not None else 1)
+    n_ind = 0
+    for sub, stride in zip(ia.subs, ia.view.strides):
+        if sub["kind"] == "direct":
+            c, b = _lin(sub["expr"], nv, ia.ssa)
+            b = iv_bin(lambda x, y: x + y, b, sum(ci * l for ci, l in zip(c, lo)))
+            base = iv_bin(lambda x, y: x + y, base, iv_bin(lambda x, y: x * y, b, stride))
+            if rd is not None:
+                pos_stride += c[rd] * stride
+            if cd is not None:
+                col_stride += c[cd] * stride
+            if any(ci for i, ci in enumerate(c) if i not in (rd, cd) and ext[i] > 1):
+                raise Unsupported("indirect tile subscript over an unexpected variable")
+        else:
+            n_ind += 1
+            if n_ind > 1:
+                raise Unsupported("indirect access tile with more than one indirect dimension")
+            iv = ia.index_views[sub["view"]]
+            ioff, istride = iv.base, 0
+            for e, s in zip(sub["exprs"], iv.strides):
+                c, b = _lin(e, nv, ia.ssa)
+                b = iv_bin(lambda x, y: x + y, b, sum(ci * l for ci, l in zip(c, lo)))
+                ioff = iv_bin(lambda x, y: x + y, ioff, iv_bin(lambda x, y: x * y, b, s))
+                if cd is not None and c[cd]:
+                    raise Unsupported("index lookup that varies along the tile's columns")
+                if rd is not None:
+                    istride += c[rd] * s
+            form.idx_dtype, form.idx_off, form.idx_stride, form.idx_mult = iv.dtype, per_tile(ioff), istride, stride
+    if n_ind == 0:
+        raise Unsupported("indirect access tile without an indirect subscript")
+    if cd is not None and col_stride != 1:
+        raise Unsupported("indirect tile whose columns are not unit-stride")
+    form.base, form.pos_stride = per_tile(base), pos_stride
+    return form
+
+
+class RowsStatement(Statement):
+    """rows_program (direct destination) or ordered scatter_rows (indirect destination)."""
+
+    def __init__(self, dev: R.Device, store: Store, arena: ArenaMap, stmt_id: int):
+        self.ordered = isinstance(store.target, IndirectAccess)
+        self.kind = "scatter_rows" if self.ordered else "rows_program"
+        pb = ProgramBuilder(leaf_kinds=("load", "iload"))
+        self.program = pb.build(store.value, store.target.shape)
+        if len(pb.inputs) > R.ROWS_MAX_IN:
+            raise Unsupported(f"row statement with more than {R.ROWS_MAX_IN} input tiles")
+        sel, cores = _points(store)
+        n_tiles = len(sel)
+        accs = [n.attrs["access"] for n in pb.inputs] + [store.target]
+        forms = [row_form(a, store, sel) for a in accs]
+        out = forms[-1]
+        for f in forms[:-1]:
+            if (f.rows, f.cols) != (out.rows, out.cols):
+                raise Unsupported("row statement operands with different tile shapes")
+        self.args = a = R.RowsArgs()
+        a.n_tiles, a.tile_rows, a.cols, a.n_in = n_tiles, out.rows, out.cols, len(forms) - 1
+        a.program = self.program
+        self.device_arrays = []
+        self.fps: List[Footprint] = []
+        vec = out.cols % 4 == 0
+        dst_alloc = None
+        for k, (acc, f) in enumerate(zip(accs, forms)):
+            is_out = k == len(forms) - 1
+            op = a.out if is_out else a.inp[k]
+            view = acc.view
+            bpe = bytes_per_elem(view.dtype)
+            first = int(f.base.min()) if n_tiles else int(np.asarray(view.base).reshape(-1)[0])
+            alloc = arena.find(int(iv_full(view.base, store.axes).reshape(-1)[0]) * bpe)
+            if alloc is None:
+                raise ValueError(f"{'Scatter to' if is_out else 'Read from'} unmapped address "
+                                 f"0x{first * bpe:x}")
+            op.indirect, op.dtype = int(f.indirect), R.DTYPE_CODE[f.dtype]
+            op.pos_stride = f.pos_stride
+            op.lo, op.hi = alloc.byte_lo // bpe, alloc.byte_hi // bpe
+            p = dev.upload(f.base)
+            self.device_arrays.append(p)
+            op.dev_base = p
+            vec = vec and f.pos_stride % 4 == 0 and bool((f.base % 4 == 0).all())
+            if f.indirect:
+                ibpe = bytes_per_elem(f.idx_dtype)
+                if n_tiles:
+                    ia = arena.check_range(int(f.idx_off.min()),
+                                           int(f.idx_off.max()) + (f.rows - 1) * f.idx_stride + 1,
+                                           f.idx_dtype, "Read from")
+                    self.fps.append(Footprint(np.array([ia.byte_lo]), np.array([ia.byte_hi]),
+                                              np.array([-1]), np.array([-1]), False, stmt_id))
+                op.idx_dtype, op.idx_stride, op.idx_mult = R.DTYPE_CODE[f.idx_dtype], f.idx_stride, f.idx_mult
+                p = dev.upload(f.idx_off)
+                self.device_arrays.append(p)
+                op.dev_idx_off = p
+                vec = vec and f.idx_mult % 4 == 0
+            else:
+                if n_tiles:
+                    arena.check_range(int(f.base.min()), int(f.base.max()) + (f.rows - 1) * f.pos_stride + f.cols,
+                                      f.dtype, "Scatter to" if is_out else "Read from")
+            if is_out:
+                dst_alloc = alloc
+            elif self.ordered and f.same_rows(out):
+                op.alias_dst = 1
+            if not (not is_out and self.ordered and f.same_rows(out)):
+                whole = f.indirect or not n_tiles
+                if whole:
+                    self.fps.append(Footprint(np.array([alloc.byte_lo]), np.array([alloc.byte_hi]),
+                                              np.array([-1]), np.array([-1]), is_out, stmt_id))
+                else:
+                    rs = (f.base[:, None] + np.arange(f.rows, dtype=np.int64)[None, :] * f.pos_stride).reshape(-1) * bpe
+                    self.fps.append(Footprint(rs, rs + f.cols * bpe, np.repeat(sel, f.rows),
+                                              np.repeat(cores, f.rows), is_out, stmt_id))
+        a.vector_ok = int(vec)
+        if self.ordered:
+            if out.pos_stride != 0 or out.idx_mult < out.cols or (n_tiles and (out.base != out.base[0]).any()):
+                raise Unsupported("indirect store whose destination rows are not whole rows of one table")
+            for k, f in enumerate(forms[:-1]):
+                acc = accs[k]
+                al = arena.find(int(iv_full(acc.view.base, store.axes).reshape(-1)[0]) * bytes_per_elem(acc.view.dtype))
+                if al is dst_alloc and not a.inp[k].alias_dst:
+                    raise Unsupported("indirect store whose value reads other rows of its destination")
+            a.dst_row0 = int(out.base[0]) if n_tiles else 0
+            bpe = bytes_per_elem(out.dtype)
+            a.dst_rows = max(0, (dst_alloc.byte_hi // bpe - a.dst_row0 - out.cols) // out.idx_mult + 1)
+            self.scratch = dev.alloc(max(4 * n_tiles * out.rows, 16))
+            self.device_arrays.append(self.scratch)
+            a.dev_rowid_scratch = self.scratch
+            self.launches = 2
+        self.extra_written = [dst_alloc.name] if (self.ordered and dst_alloc is not None) else []
+        self.entries = n_tiles * out.rows
+        self._bytes = sum(self.entries * f.cols * bytes_per_elem(f.dtype) + (self.entries * bytes_per_elem(f.idx_dtype) if f.indirect and f.idx_stride else 0)
+                          for f in forms)
+
+    def launch(self, dev, arena_ptr):
+        self.args.arena = arena_ptr
+        fn = dev.lib.ktb_launch_scatter_rows if self.ordered else dev.lib.ktb_launch_rows_program
+        dev.check(fn(dev.h, C.byref(self.args)))
+
+    def footprints(self):
+        return self.fps
+
+    def bytes_moved(self):
+        return self._bytes
 
 
 def lower_indirect_store(dev, store, arena, stmt_id):
-    raise Unsupported("indirect ktdp.store")
+    return RowsStatement(dev, store, arena, stmt_id)
+
+
+def has_indirect_load(n: Node, seen=None) -> bool:
+    seen = seen if seen is not None else set()
+    if id(n) in seen:
+        return False
+    seen.add(id(n))
+    return n.kind == "iload" or any(has_indirect_load(a, seen) for a in n.args)

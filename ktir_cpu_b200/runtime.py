@@ -55,6 +55,23 @@ class SoftmaxArgs(C.Structure):
                 ("max_init", C.c_float), ("sum_init", C.c_float)]
 
 
+ROWS_MAX_IN = 3
+
+
+class RowOperand(C.Structure):
+    _fields_ = [("indirect", C.c_int32), ("dtype", C.c_int32), ("idx_dtype", C.c_int32),
+                ("alias_dst", C.c_int32), ("dev_base", C.c_void_p), ("dev_idx_off", C.c_void_p),
+                ("idx_stride", C.c_int64), ("idx_mult", C.c_int64), ("pos_stride", C.c_int64),
+                ("lo", C.c_int64), ("hi", C.c_int64)]
+
+
+class RowsArgs(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("n_tiles", C.c_int64), ("tile_rows", C.c_int32),
+                ("cols", C.c_int32), ("n_in", C.c_int32), ("vector_ok", C.c_int32),
+                ("inp", RowOperand * ROWS_MAX_IN), ("out", RowOperand), ("program", VmProgram),
+                ("dev_rowid_scratch", C.c_void_p), ("dst_row0", C.c_int64), ("dst_rows", C.c_int64)]
+
+
 _lib: Optional[C.CDLL] = None
 
 # name -> (restype, argtypes); every symbol include/ktir_b200.h declares
@@ -78,6 +95,8 @@ SYMBOLS = {
     "ktb_launch_count": (C.c_int64, [C.c_void_p]),
     "ktb_launch_ew_stream": (C.c_int, [C.c_void_p, C.POINTER(EwArgs)]),
     "ktb_launch_row_softmax": (C.c_int, [C.c_void_p, C.POINTER(SoftmaxArgs)]),
+    "ktb_launch_rows_program": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
+    "ktb_launch_scatter_rows": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
 }
 
 

@@ -28,7 +28,7 @@ def _exact(name):
     return name.startswith(("vector_add", "gather"))
 
 
-SUPPORTED = [n for n in golden_names() if n.startswith(("vector_add", "softmax"))]
+SUPPORTED = [n for n in golden_names() if n.startswith(("vector_add", "softmax", "gather"))]
 
 
 @pytest.mark.parametrize("name", SUPPORTED)
@@ -91,3 +91,86 @@ def test_softmax_full_size_properties(build_lib):
     e = np.exp(xf - xf.max(1, keepdims=True))
     np.testing.assert_allclose(y[rows].astype(np.float32), e / e.sum(1, keepdims=True), rtol=2e-3, atol=2e-6)
     assert (np.argmax(y, 1) == np.argmax(x, 1)).mean() > 0.99
+
+
+def _dup_indices(rng, n_rows, n_idx, tile_rows, dup):
+    idx = rng.integers(0, n_rows, n_idx)
+    for t in range(n_idx // tile_rows):
+        pos = rng.choice(tile_rows, 2 * dup, replace=False)
+        idx[t * tile_rows + pos[:dup]] = idx[t * tile_rows + pos[dup:]]
+    return idx
+
+
+@pytest.mark.parametrize("idx_dtype", ["i32", "i64"])
+def test_gather_rows_bit_exact(idx_dtype, build_lib):
+    rng = np.random.default_rng(7)
+    table = rng.standard_normal((512, 128)).astype(np.float16)
+    idx = rng.integers(0, 512, 4096).astype(np.int32 if idx_dtype == "i32" else np.int64)
+    got, want = _run_both(K.gather_rows(512, 128, 4096, 64, 8, idx_dtype), "gather_rows",
+                          dict(table_ptr=table, idx_ptr=idx, out_ptr=np.zeros((4096, 128), np.float16)))
+    np.testing.assert_array_equal(got["out_ptr"], want["out_ptr"])
+    np.testing.assert_array_equal(got["out_ptr"], table[idx])
+
+
+@pytest.mark.parametrize("cols,tile_rows", [(128, 64), (32, 16), (20, 8)])
+def test_scatter_rows_last_writer_wins(cols, tile_rows, build_lib):
+    rng = np.random.default_rng(8)
+    n_idx = tile_rows * 64
+    src = rng.standard_normal((n_idx, cols)).astype(np.float16)
+    idx = _dup_indices(rng, 96, n_idx, tile_rows, max(1, tile_rows // 8)).astype(np.int32)
+    got, want = _run_both(K.scatter_rows(96, cols, n_idx, tile_rows, 4), "scatter_rows",
+                          dict(src_ptr=src, idx_ptr=idx, out_ptr=np.full((96, cols), -1, np.float16)))
+    np.testing.assert_array_equal(got["out_ptr"], want["out_ptr"])
+
+
+@pytest.mark.parametrize("n_rows,n_idx", [(1024, 16384), (64, 8192), (1, 1024)])
+def test_gather_scale_scatter_ordered_rmw(n_rows, n_idx, build_lib):
+    """Heavy row reuse: the tile-sequential read-modify-write order must be reproduced bit for bit."""
+    rng = np.random.default_rng(9)
+    table = rng.standard_normal((n_rows, 128)).astype(np.float16)
+    idx = _dup_indices(rng, n_rows, n_idx, 64, 6).astype(np.int32)
+    kw = dict(table_ptr=table, idx_ptr=idx, out_ptr=rng.standard_normal((n_rows, 128)).astype(np.float16))
+    got, want = _run_both(K.gather_scale_scatter(n_rows, 128, n_idx, 64, 8), "gather_scale_scatter", kw)
+    np.testing.assert_array_equal(got["out_ptr"], want["out_ptr"])
+    # deterministic: a second run on the same inputs gives the same bits
+    got2, _ = _run_both(K.gather_scale_scatter(n_rows, 128, n_idx, 64, 8), "gather_scale_scatter", kw)
+    np.testing.assert_array_equal(got["out_ptr"], got2["out_ptr"])
+
+
+def test_negative_index_raises_index_error(build_lib):
+    src, fn, kwargs, _ = load_golden("gather_scale_scatter_256")
+    kwargs["idx_ptr"] = kwargs["idx_ptr"].copy()
+    kwargs["idx_ptr"][5] = -3
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    with pytest.raises(IndexError, match="negative"):
+        gpu.execute_function(fn, **kwargs)
+    # the context stays usable after the error
+    kwargs["idx_ptr"][5] = 3
+    gpu.execute_function(fn, **kwargs)
+    gpu.close()
+
+
+def test_gather_scale_scatter_full_size_properties(build_lib):
+    """BASELINE size (65536 x 128 table, 262144 indices): untouched rows stay zero and every
+    touched row equals h (+) h ... n times with h = 0.5 * table[row] (f16 rounding per add),
+    n = number of tiles containing the row."""
+    rng = np.random.default_rng(3)
+    table = rng.standard_normal((65536, 128)).astype(np.float16)
+    idx = _dup_indices(rng, 65536, 262144, 64, 6).astype(np.int32)
+    gpu = KTIRInterpreter()
+    gpu.load(K.gather_scale_scatter())
+    out = gpu.execute_function("gather_scale_scatter", table_ptr=table, idx_ptr=idx,
+                               out_ptr=np.zeros_like(table))["out_ptr"]
+    gpu.close()
+    tiles = idx.reshape(-1, 64)
+    counts = np.zeros(65536, np.int64)
+    for t in range(tiles.shape[0]):
+        counts[np.unique(tiles[t])] += 1
+    assert (out[counts == 0] == 0).all()
+    h = (table * np.float16(0.5)).astype(np.float16)
+    acc = np.zeros_like(table)
+    for n in range(1, int(counts.max()) + 1):
+        m = counts >= n
+        acc[m] = acc[m] + h[m]
+    np.testing.assert_array_equal(out, acc)
