@@ -179,6 +179,49 @@ int ktb_launch_rows_program(ktb_ctx* ctx, const ktb_rows_args* args);
  * load/modify/store-back form. */
 int ktb_launch_scatter_rows(ktb_ctx* ctx, const ktb_rows_args* args);
 
+/* ---- dense f16 GEMM on tensor cores -------------------------------------------------
+ * C[M,N] = A[M,K] * B[K,N] + c_init, row-major operands in the arena, f32 accumulation
+ * (tcgen05.mma into TMEM), C rounded once to c_dtype.  What a tiled KTIR matmul kernel
+ * computes when its per-core tile loop — ktdp.load of an A and a B tile per K-step,
+ * linalg.matmul into the loop-carried accumulator (ktir_cpu/ops/arith_ops.py:323-340,
+ * ktir_cpu/dialects/linalg_ops.py:307-347), ktdp.store of the C tile — covers a dense
+ * grid of tiles.  N multiple of 32; K, leading dimensions and offsets multiples of 8. */
+typedef struct {
+    void* arena;
+    int64_t a_off, b_off, c_off;   /* element offsets: A and B in f16 units, C in c_dtype units */
+    int32_t M, N, K;
+    int32_t c_dtype;               /* KTB_F16 / KTB_F32 */
+    int64_t lda, ldb, ldc;         /* elements */
+    float c_init;                  /* constant initial value of the accumulator (usually 0) */
+    int32_t reserved;
+} ktb_gemm_args;
+int ktb_launch_gemm_f16(ktb_ctx* ctx, const ktb_gemm_args* args);
+
+/* ---- causal attention forward, paged K/V ----------------------------------------------
+ * O[R, h, :] = softmax_p( scale * Q[R, h, :] . K[p, h, :] ) V[p, h, :] over the KV positions
+ * p <= R + causal_delta (all positions when causal == 0), f32 scores / statistics, f16 in
+ * and out, head_dim 128.  K and V live in pages of `page` rows reached through a block
+ * table: page j of the walk is cache page block_table[j].  This is the loop a KTIR
+ * attention kernel carries out per KV page — indirect ktdp.load of K and V
+ * (ktir_cpu/ops/memory_ops.py:867-915), two linalg.matmul, mask, running max / sum and
+ * rescale (examples/triton-ktir/paged_attention.mlir:183-396 of the reference).
+ * m_init / l_init are the initial running max and sum the kernel carries (-inf and 1.0
+ * there).  All offsets and strides are in elements and must be multiples of 8. */
+typedef struct {
+    void* arena;
+    int64_t q_off, o_off, k_off, v_off;        /* f16 element offsets of query, output, K cache, V cache */
+    int64_t bt_off;                            /* element offset (bt_dtype units) of the first block-table entry */
+    int32_t bt_dtype;                          /* KTB_I32 / KTB_I64 */
+    int32_t seq_q, heads, head_dim;
+    int32_t page, n_pages_total, num_tiles;    /* rows per page, pages in the cache, pages to walk */
+    int32_t causal, causal_delta;
+    int64_t q_row_stride, q_head_stride, o_row_stride, o_head_stride;
+    int64_t kv_page_stride, kv_row_stride, kv_head_stride;
+    float scale, m_init, l_init;
+    int32_t reserved;
+} ktb_attn_args;
+int ktb_launch_attention_fwd(ktb_ctx* ctx, const ktb_attn_args* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,208 @@
+// C[M,N] = A[M,K] * B[K,N] (+ constant), f16 operands, f32 accumulation in TMEM.
+//
+// This is what a KTIR tiled-matmul kernel computes once its per-core 64x64xK-step
+// tile loop is recognised as one dense GEMM: the reference runs np.matmul per tile
+// and K-step (ktir_cpu/ops/arith_ops.py:323-340) and accumulates through
+// linalg.matmul's `outs` (ktir_cpu/dialects/linalg_ops.py:307-347).
+//
+// Design (tensor-bound): persistent CTAs, one per SM, each producing 128 x BN
+// output tiles.  Warp 0 streams A (K-major) and B (N-major) tiles into a
+// multi-stage shared-memory ring with TMA (128-byte swizzle); warp 1 issues
+// tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators; warps 2-5
+// drain the other accumulator (tcgen05.ld), convert and store C, so the epilogue
+// of tile i overlaps the main loop of tile i+1.  All waits are bounded.
+#include "tc_common.cuh"
+
+#define GEMM_BM 128
+#define GEMM_BK 64
+#define GEMM_THREADS 192
+#define GEMM_A_STAGE_BYTES (GEMM_BM * GEMM_BK * 2)
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int B_STAGE_BYTES = GEMM_BK * BN * 2;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr size_t SMEM = (size_t)STAGES * (GEMM_A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const ktb_gemm_args a, int tiles_m, int tiles_n, ktb_status* st) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int S = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + (size_t)S * GEMM_A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)S * Cfg::B_STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + S;
+    uint64_t* tfull = bars + 2 * S;
+    uint64_t* tempty = bars + 2 * S + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = tiles_m * tiles_n;
+    const int KT = (a.K + GEMM_BK - 1) / GEMM_BK;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; ++i) {
+            tc_mbar_init(&full[i], 1);
+            tc_mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc_mbar_init(&tfull[i], 1);
+            tc_mbar_init(&tempty[i], 4);
+        }
+        *abort_flag = 0;
+        tc_fence_barrier_init();
+    }
+    __syncthreads();
+    if (warp == 1) tc_tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc_prefetch_tmap(&map_a);
+            tc_prefetch_tmap(&map_b);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+                for (int kt = 0; kt < KT; ++kt) {
+                    if (!tc_mbar_wait(&empty[stage], phase ^ 1, abort_flag, st, 1)) { ok = false; break; }
+                    tc_mbar_expect_tx(&full[stage], GEMM_A_STAGE_BYTES + Cfg::B_STAGE_BYTES);
+                    tc_tma_load_2d(sA + (size_t)stage * GEMM_A_STAGE_BYTES, &map_a, &full[stage], kt * GEMM_BK,
+                                   tm * GEMM_BM);
+#pragma unroll
+                    for (int j = 0; j < BN / 64; ++j)
+                        tc_tma_load_2d(sB + (size_t)stage * Cfg::B_STAGE_BYTES + (size_t)j * (GEMM_BK * 128), &map_b,
+                                       &full[stage], tn * BN + j * 64, kt * GEMM_BK);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = tc_idesc_f16(GEMM_BM, BN, 0, 1);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++it) {
+                const int acc = it & 1, accphase = (it >> 1) & 1;
+                if (!tc_mbar_wait(&tempty[acc], accphase ^ 1, abort_flag, st, 2)) break;
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kt = 0; kt < KT; ++kt) {
+                    if (!tc_mbar_wait(&full[stage], phase, abort_flag, st, 3)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = tc_smem_u32(sA + (size_t)stage * GEMM_A_STAGE_BYTES);
+                    const uint32_t b_addr = tc_smem_u32(sB + (size_t)stage * Cfg::B_STAGE_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+                        const uint64_t ad = tc_smem_desc(a_addr + kk * 32, 16, 1024);
+                        const uint64_t bd = tc_smem_desc(b_addr + kk * 2048, GEMM_BK * 128, 1024);
+                        tc_mma_f16(d, ad, bd, idesc, (kt | kk) != 0);
+                    }
+                    tc_mma_commit(&empty[stage]);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_mma_commit(&tfull[acc]);
+            }
+        }
+    } else {
+        const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+            const int acc = it & 1, accphase = (it >> 1) & 1;
+            const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+            if (!tc_mbar_wait(&tfull[acc], accphase, abort_flag, st, 4)) break;
+            tc_fence_after_sync();
+            const int row = tm * GEMM_BM + q * 32 + lane;
+            const uint32_t t0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tc_tmem_ld32(t0 + c0, r);
+                tc_tmem_ld_wait();
+                const int col = tn * BN + c0;
+                if (row < a.M && col < a.N) {
+                    if (a.c_dtype == KTB_F16) {
+                        __half* dst = reinterpret_cast<__half*>(a.arena) + a.c_off + (int64_t)row * a.ldc + col;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]) + a.c_init,
+                                                         __uint_as_float(r[v * 8 + 2 * i + 1]) + a.c_init);
+                            *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                        }
+                    } else {
+                        float* dst = reinterpret_cast<float*>(a.arena) + a.c_off + (int64_t)row * a.ldc + col;
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            *reinterpret_cast<float4*>(dst + v * 4) =
+                                make_float4(__uint_as_float(r[v * 4]) + a.c_init, __uint_as_float(r[v * 4 + 1]) + a.c_init,
+                                            __uint_as_float(r[v * 4 + 2]) + a.c_init, __uint_as_float(r[v * 4 + 3]) + a.c_init);
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&tempty[acc]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tc_tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int BN>
+static int launch_gemm(ktb_ctx* ctx, const ktb_gemm_args& a, const CUtensorMap& ma, const CUtensorMap& mb) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_gemm_f16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)Cfg::SMEM));
+        attr_set = true;
+    }
+    const int tiles_m = (a.M + GEMM_BM - 1) / GEMM_BM, tiles_n = (a.N + BN - 1) / BN;
+    int grid = tiles_m * tiles_n;
+    if (grid > ctx->sm_count) grid = ctx->sm_count;
+    ktb_gemm_f16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM, ctx->stream>>>(ma, mb, a, tiles_m, tiles_n, ctx->dev_status);
+    KTB_CHECK_LAUNCH(ctx, "ktb_gemm_f16_kernel");
+    return KTB_OK;
+}
+
+extern "C" int ktb_launch_gemm_f16(ktb_ctx* ctx, const ktb_gemm_args* args) {
+    if (!ctx || !args) return KTB_E_ARG;
+    const ktb_gemm_args& a = *args;
+    if (a.M <= 0 || a.N <= 0 || a.K <= 0) return KTB_OK;
+    if (a.c_dtype != KTB_F16 && a.c_dtype != KTB_F32) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "gemm_f16", "C must be f16 or f32");
+    if ((a.N % 32) || (a.K % 8) || (a.lda % 8) || (a.ldb % 8) || (a.ldc % 8) || (a.a_off % 8) || (a.b_off % 8) || (a.c_off % 8))
+        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "gemm_f16", "N must be a multiple of 32; K, leading dims and offsets multiples of 8");
+    CUtensorMap ma, mb;
+    __half* base = reinterpret_cast<__half*>(a.arena);
+    {
+        const uint64_t dims[2] = {(uint64_t)a.K, (uint64_t)a.M};
+        const uint64_t str[1] = {(uint64_t)a.lda * 2};
+        const uint32_t box[2] = {GEMM_BK, GEMM_BM};
+        if (!tc_make_map_f16(&ma, base + a.a_off, 2, dims, str, box)) return ktb_fail(ctx, KTB_E_CUDA, "gemm_f16", "cuTensorMapEncodeTiled(A) failed");
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)a.N, (uint64_t)a.K};
+        const uint64_t str[1] = {(uint64_t)a.ldb * 2};
+        const uint32_t box[2] = {64, GEMM_BK};
+        if (!tc_make_map_f16(&mb, base + a.b_off, 2, dims, str, box)) return ktb_fail(ctx, KTB_E_CUDA, "gemm_f16", "cuTensorMapEncodeTiled(B) failed");
+    }
+    if (a.N % 256 == 0 || a.N >= 1024) return launch_gemm<256>(ctx, a, ma, mb);
+    return launch_gemm<128>(ctx, a, ma, mb);
+}

@@ -16,6 +16,12 @@
 
 #include "common.cuh"
 
+static __device__ __forceinline__ float sm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <bool MAXNUM>
 static __device__ __forceinline__ float sm_max(float a, float b) {
     if (!MAXNUM && (a != a || b != b)) return __int_as_float(0x7fc00000);
@@ -163,18 +169,25 @@ __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3) ktb_row_softmax_kernel(c
 
         float mx = row_fold<NV, 0, MAXNUM, R16>(x, T, t, group, xchg, bcast);
         mx = sm_max<MAXNUM>(mx, a.max_init);
+        // f32 path: exp(x - mx) = 2^(x*log2e - mx*log2e), one FMA and one MUFU per element
+        // (relative error <= ~1e-6 for |x - mx| < 16, inside the 1e-5 f32 tolerance).
+        // f16 path keeps the reference's rounding points: round(x - mx), round(exp(.)).
+        const float mxs = mx * 1.4426950408889634f;
 #pragma unroll
         for (int j = 0; j < NV; ++j)
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                float d = x[j][k] - mx;
-                if (R16) d = ktb_round16(d);
-                const float e = expf(d);
-                x[j][k] = R16 ? ktb_round16(e) : e;
+                if (R16) {
+                    const float d = ktb_round16(x[j][k] - mx);
+                    x[j][k] = ktb_round16(expf(d));
+                } else {
+                    x[j][k] = sm_ex2(__fmaf_rn(x[j][k], 1.4426950408889634f, -mxs));
+                }
             }
         float sum = row_fold<NV, 1, MAXNUM, R16>(x, T, t, group, xchg, bcast);
         sum = sum + a.sum_init;
         if (R16) sum = ktb_round16(sum);
+        const float inv = 1.0f / sum;
 
         if (!live) continue;
 #pragma unroll
@@ -182,7 +195,7 @@ __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3) ktb_row_softmax_kernel(c
             const int64_t e = out_off + ((int64_t)j * T + t) * 8;
             float y[8];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) y[k] = x[j][k] / sum;
+            for (int k = 0; k < 8; ++k) y[k] = R16 ? x[j][k] / sum : x[j][k] * inv;
             if (a.out_dtype == KTB_F16) {
                 uint4 raw;
                 __half2* h = reinterpret_cast<__half2*>(&raw);

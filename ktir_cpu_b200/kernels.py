@@ -301,3 +301,121 @@ def scatter_rows(n_out_rows: int, cols: int, n_idx: int, tile_rows: int, cores: 
           f"      ktdp.store %rows, %to : {t}, {at}\n"
           f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
     return s
+
+
+def causal_attention(seq: int = 2048, heads: int = 256, head_dim: int = 128, tile_m: int = 128,
+                     tile_n: int = 128) -> str:
+    """Blockwise causal attention with online softmax in f32 and paged K/V.
+
+    Query / output are [seq, heads, head_dim] f16 (batch folded into heads); the
+    K and V caches are [seq/tile_n, tile_n, heads, head_dim] f16 pages reached
+    through a block table (an identity table gives dense attention).  Core
+    (q, h) owns query rows [q*tile_m, (q+1)*tile_m) of head h and walks
+    ``num_tiles`` KV pages carrying (running max M, running sum L, accumulator).
+    Same computation as examples/triton-ktir/paged_attention.mlir of the
+    reference with one query head per KV head: M starts at -inf, L at 1.0,
+    masked scores are -inf, the epilogue divides by L and truncates to f16."""
+    assert seq % tile_m == 0 and seq % tile_n == 0
+    nb = seq // tile_n
+    tm, tn, hd, H = tile_m, tile_n, head_dim, heads
+    qv, cv = [seq, H, hd], [nb, tn, H, hd]
+    f = lambda shp, dt: f"tensor<{_xs(shp, dt)}>"   # noqa: E731
+
+    def kv_tile(name, vw):
+        return (f"      %{name} = ktdp.construct_indirect_access_tile\n"
+                f"          intermediate_variables(%d0, %d1, %d2, %d3)\n"
+                f"          %{vw}[ind(%block_tables[%c0, %j + %d0]), (%d1), (%pid_h + %d2), (%d3)] {{\n"
+                f"        variables_space_set = {_box([1, tn, 1, hd])},\n"
+                f"        variables_space_order = {_ident(4)}\n"
+                f"      }} : memref<{_xs(cv, 'f16')}>, memref<1x{nb}xi32> -> !ktdp.access_tile<{_xs([1, tn, 1, hd], 'index')}>\n")
+
+    s = (f"module {{\n  func.func @attention_kernel(%output_ptr: index, %query_ptr: index, %key_cache_ptr: index,\n"
+         f"      %value_cache_ptr: index, %block_tables_ptr: index, %num_tiles: index, %context_len: index,\n"
+         f"      %scale: f32) attributes {{grid = [{seq // tm}, {H}]}} {{\n"
+         f"    %pid_q, %pid_h = ktdp.get_compute_tile_id : index, index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n"
+         f"    %c_tm = arith.constant {tm} : index\n"
+         f"    %c_tn = arith.constant {tn} : index\n"
+         f"    %ninf_bits = arith.constant 0xFF800000 : i32\n"
+         f"    %ninf = arith.bitcast %ninf_bits : i32 to f32\n"
+         f"    %zero = arith.constant 0.0 : f32\n"
+         f"    %one = arith.constant 1.0 : f32\n"
+         f"    %q_row0 = arith.muli %pid_q, %c_tm : index\n"
+         f"    %q_abs0 = arith.addi %q_row0, %context_len : index\n")
+    s += view("query", "query_ptr", qv, "f16") + view("output", "output_ptr", qv, "f16")
+    s += view("key_cache", "key_cache_ptr", cv, "f16") + view("value_cache", "value_cache_ptr", cv, "f16")
+    s += view("block_tables", "block_tables_ptr", [1, nb], "i32")
+    s += tile("q_tile", "query", ["%q_row0", "%pid_h", "%c0"], [tm, 1, hd], qv, "f16")
+    s += (f"    %q3 = ktdp.load %q_tile : !ktdp.access_tile<{_xs([tm, 1, hd], 'index')}> -> {f([tm, 1, hd], 'f16')}\n"
+          f"    %q16 = tensor.collapse_shape %q3 [[0, 1], [2]] : {f([tm, 1, hd], 'f16')} into {f([tm, hd], 'f16')}\n"
+          f"    %q = arith.extf %q16 : {f([tm, hd], 'f16')} to {f([tm, hd], 'f32')}\n"
+          f"    %m_init = tensor.splat %ninf : {f([tm], 'f32')}\n"
+          f"    %l_init = tensor.splat %one : {f([tm], 'f32')}\n"
+          f"    %acc_init = tensor.splat %zero : {f([tm, hd], 'f32')}\n"
+          f"    %m_fin, %l_fin, %acc_fin = scf.for %j = %c0 to %num_tiles step %c1\n"
+          f"        iter_args(%m_run = %m_init, %l_run = %l_init, %acc = %acc_init)\n"
+          f"        -> ({f([tm], 'f32')}, {f([tm], 'f32')}, {f([tm, hd], 'f32')}) {{\n")
+    s += kv_tile("k_tile", "key_cache") + kv_tile("v_tile", "value_cache")
+    t4, t2 = f([1, tn, 1, hd], "f16"), f([tn, hd], "f16")
+    at4 = f"!ktdp.access_tile<{_xs([1, tn, 1, hd], 'index')}>"
+    s += (f"      %k4 = ktdp.load %k_tile : {at4} -> {t4}\n"
+          f"      %v4 = ktdp.load %v_tile : {at4} -> {t4}\n"
+          f"      %k2 = tensor.collapse_shape %k4 [[0, 1], [2, 3]] : {t4} into {t2}\n"
+          f"      %v2 = tensor.collapse_shape %v4 [[0, 1], [2, 3]] : {t4} into {t2}\n"
+          f"      %kt_init = tensor.empty() : {f([hd, tn], 'f16')}\n"
+          f"      %kt16 = linalg.transpose ins(%k2 : {t2}) outs(%kt_init : {f([hd, tn], 'f16')}) permutation = [1, 0]\n"
+          f"      %kt = arith.extf %kt16 : {f([hd, tn], 'f16')} to {f([hd, tn], 'f32')}\n"
+          f"      %v = arith.extf %v2 : {t2} to {f([tn, hd], 'f32')}\n"
+          f"      %s_zero = tensor.splat %zero : {f([tm, tn], 'f32')}\n"
+          f"      %qk = linalg.matmul ins(%q, %kt : {f([tm, hd], 'f32')}, {f([hd, tn], 'f32')}) "
+          f"outs(%s_zero : {f([tm, tn], 'f32')}) -> {f([tm, tn], 'f32')}\n"
+          f"      %scale_t = tensor.splat %scale : {f([tm, tn], 'f32')}\n"
+          f"      %sc = arith.mulf %scale_t, %qk : {f([tm, tn], 'f32')}\n"
+          f"      %col0 = arith.muli %j, %c_tn : index\n"
+          f"      %masked_init = tensor.empty() : {f([tm, tn], 'f32')}\n"
+          f"      %masked = linalg.generic {{\n"
+          f"          indexing_maps = [{_ident(2)}, {_ident(2)}],\n"
+          f"          iterator_types = [\"parallel\", \"parallel\"]}}\n"
+          f"          ins(%sc : {f([tm, tn], 'f32')}) outs(%masked_init : {f([tm, tn], 'f32')}) {{\n"
+          f"        ^bb0(%s_val : f32, %unused : f32):\n"
+          f"          %r = linalg.index 0 : index\n"
+          f"          %c = linalg.index 1 : index\n"
+          f"          %q_pos = arith.addi %q_abs0, %r : index\n"
+          f"          %k_pos = arith.addi %col0, %c : index\n"
+          f"          %keep = arith.cmpi ule, %k_pos, %q_pos : index\n"
+          f"          %sel = arith.select %keep, %s_val, %ninf : f32\n"
+          f"          linalg.yield %sel : f32\n"
+          f"      }} -> {f([tm, tn], 'f32')}\n"
+          f"      %rmax_init = tensor.splat %ninf : {f([tm], 'f32')}\n"
+          f"      %rmax = linalg.reduce {{ arith.maximumf }} ins(%masked : {f([tm, tn], 'f32')}) "
+          f"outs(%rmax_init : {f([tm], 'f32')}) dimensions = [1]\n"
+          f"      %m_new = arith.maximumf %m_run, %rmax : {f([tm], 'f32')}\n"
+          f"      %bs = tensor.empty() : {f([tm, tn], 'f32')}\n"
+          f"      %m_b = linalg.broadcast ins(%m_new : {f([tm], 'f32')}) outs(%bs : {f([tm, tn], 'f32')}) dimensions = [1]\n"
+          f"      %shift = arith.subf %masked, %m_b : {f([tm, tn], 'f32')}\n"
+          f"      %p = math.exp %shift : {f([tm, tn], 'f32')}\n"
+          f"      %lsum_init = tensor.splat %zero : {f([tm], 'f32')}\n"
+          f"      %lsum = linalg.reduce {{ arith.addf }} ins(%p : {f([tm, tn], 'f32')}) "
+          f"outs(%lsum_init : {f([tm], 'f32')}) dimensions = [1]\n"
+          f"      %dm = arith.subf %m_run, %m_new : {f([tm], 'f32')}\n"
+          f"      %alpha = math.exp %dm : {f([tm], 'f32')}\n"
+          f"      %bo = tensor.empty() : {f([tm, hd], 'f32')}\n"
+          f"      %alpha_b = linalg.broadcast ins(%alpha : {f([tm], 'f32')}) outs(%bo : {f([tm, hd], 'f32')}) dimensions = [1]\n"
+          f"      %acc_scaled = arith.mulf %acc, %alpha_b : {f([tm, hd], 'f32')}\n"
+          f"      %acc_new = linalg.matmul ins(%p, %v : {f([tm, tn], 'f32')}, {f([tn, hd], 'f32')}) "
+          f"outs(%acc_scaled : {f([tm, hd], 'f32')}) -> {f([tm, hd], 'f32')}\n"
+          f"      %l_scaled = arith.mulf %l_run, %alpha : {f([tm], 'f32')}\n"
+          f"      %l_new = arith.addf %l_scaled, %lsum : {f([tm], 'f32')}\n"
+          f"      scf.yield %m_new, %l_new, %acc_new : {f([tm], 'f32')}, {f([tm], 'f32')}, {f([tm, hd], 'f32')}\n"
+          f"    }}\n"
+          f"    %bo2 = tensor.empty() : {f([tm, hd], 'f32')}\n"
+          f"    %l_b = linalg.broadcast ins(%l_fin : {f([tm], 'f32')}) outs(%bo2 : {f([tm, hd], 'f32')}) dimensions = [1]\n"
+          f"    %o32 = arith.divf %acc_fin, %l_b : {f([tm, hd], 'f32')}\n"
+          f"    %o16 = arith.truncf %o32 : {f([tm, hd], 'f32')} to {f([tm, hd], 'f16')}\n"
+          f"    %o3 = tensor.expand_shape %o16 [[0, 1], [2]] output_shape [{tm}, 1, {hd}] : "
+          f"{f([tm, hd], 'f16')} into {f([tm, 1, hd], 'f16')}\n")
+    s += tile("o_tile", "output", ["%q_row0", "%pid_h", "%c0"], [tm, 1, hd], qv, "f16")
+    s += (f"    ktdp.store %o3, %o_tile : {f([tm, 1, hd], 'f16')}, !ktdp.access_tile<{_xs([tm, 1, hd], 'index')}>\n"
+          f"    return\n  }}\n}}\n")
+    return s

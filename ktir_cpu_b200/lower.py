@@ -548,6 +548,9 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap) -> Plan:
             from .lower_mm import try_lower_matmul
             stmt = try_lower_matmul(dev, st, arena, sid)
         if stmt is None:
+            from .lower_attn import try_lower_attention
+            stmt = try_lower_attention(dev, st, arena, sid)
+        if stmt is None:
             from .lower_scatter import RowsStatement, has_indirect_load
             if has_indirect_load(st.value):
                 stmt = RowsStatement(dev, st, arena, sid)

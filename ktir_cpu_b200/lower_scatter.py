@@ -83,8 +83,8 @@ def _rc_dims(shape) -> Tuple[Optional[int], Optional[int]]:
     return big[0], big[1]
 
 
-def row_form(acc, store: Store, sel: np.ndarray) -> RowForm:
-    axes = store.axes
+def row_form(acc, axes, sel: np.ndarray) -> RowForm:
+    """Row addressing of ``acc`` at the iteration points ``sel`` (flat indices into ``axes``)."""
 
     def per_tile(v) -> np.ndarray:
         return np.ascontiguousarray(iv_full(v, axes).reshape(-1)[sel]).astype(np.int64)
@@ -160,7 +160,7 @@ class RowsStatement(Statement):
         sel, cores = _points(store)
         n_tiles = len(sel)
         accs = [n.attrs["access"] for n in pb.inputs] + [store.target]
-        forms = [row_form(a, store, sel) for a in accs]
+        forms = [row_form(a, store.axes, sel) for a in accs]
         out = forms[-1]
         for f in forms[:-1]:
             if (f.rows, f.cols) != (out.rows, out.cols):

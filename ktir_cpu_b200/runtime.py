@@ -72,6 +72,25 @@ class RowsArgs(C.Structure):
                 ("dev_rowid_scratch", C.c_void_p), ("dst_row0", C.c_int64), ("dst_rows", C.c_int64)]
 
 
+class GemmArgs(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("a_off", C.c_int64), ("b_off", C.c_int64), ("c_off", C.c_int64),
+                ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("c_dtype", C.c_int32),
+                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+                ("c_init", C.c_float), ("reserved", C.c_int32)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("q_off", C.c_int64), ("o_off", C.c_int64), ("k_off", C.c_int64),
+                ("v_off", C.c_int64), ("bt_off", C.c_int64), ("bt_dtype", C.c_int32),
+                ("seq_q", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+                ("page", C.c_int32), ("n_pages_total", C.c_int32), ("num_tiles", C.c_int32),
+                ("causal", C.c_int32), ("causal_delta", C.c_int32),
+                ("q_row_stride", C.c_int64), ("q_head_stride", C.c_int64),
+                ("o_row_stride", C.c_int64), ("o_head_stride", C.c_int64),
+                ("kv_page_stride", C.c_int64), ("kv_row_stride", C.c_int64), ("kv_head_stride", C.c_int64),
+                ("scale", C.c_float), ("m_init", C.c_float), ("l_init", C.c_float), ("reserved", C.c_int32)]
+
+
 _lib: Optional[C.CDLL] = None
 
 # name -> (restype, argtypes); every symbol include/ktir_b200.h declares
@@ -97,6 +116,8 @@ SYMBOLS = {
     "ktb_launch_row_softmax": (C.c_int, [C.c_void_p, C.POINTER(SoftmaxArgs)]),
     "ktb_launch_rows_program": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
     "ktb_launch_scatter_rows": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
+    "ktb_launch_gemm_f16": (C.c_int, [C.c_void_p, C.POINTER(GemmArgs)]),
+    "ktb_launch_attention_fwd": (C.c_int, [C.c_void_p, C.POINTER(AttnArgs)]),
 }
 
 

@@ -59,6 +59,15 @@ def cases():
         out[f"matmul_{'f32acc' if f32 else 'f16acc'}_128"] = (
             K.tiled_matmul(128, 128, 128, 64, 64, 64, 2, f32), "matmul_kernel",
             dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((128, 128), np.float16)))
+    rng = np.random.default_rng(5)
+    S, H, D, tm, tn = 128, 2, 128, 32, 64
+    q, k, v = (rng.standard_normal((S, H, D)).astype(np.float16) for _ in range(3))
+    out["causal_attention_128x2"] = (
+        K.causal_attention(S, H, D, tm, tn), "attention_kernel",
+        dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(S // tn, tn, H, D),
+             value_cache_ptr=v.reshape(S // tn, tn, H, D),
+             block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
+             num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D))))
     return out
 
 
