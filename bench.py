@@ -1,11 +1,15 @@
-"""Benchmark: KTIR execution throughput on the row-softmax workload (8192 x 4096 f16, f32 stats).
+"""Benchmark of the KTIR execution hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-One "step" is one pass of the hot path over the whole workload: the launch plan
-of ``softmax_kernel`` (32 KTIR cores x 256 rows each) on tensors resident in
-HBM.  Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU
-restatement of the reference interpreter (oracle/) on the host cores instead.
+Default workload (the one the headline metric is quoted on): row softmax over
+f16[8192, 4096] with f32 statistics, 32 KTIR cores x 256 contiguous rows.  One
+"step" is one pass of the hot path over the whole workload: the launch plan of
+the KTIR function on tensors resident in HBM.  Prints ONE JSON line (rank 0).
+``--impl reference`` times the CPU restatement of the reference interpreter
+(oracle/) on the host cores instead.  Other workloads (vector_add,
+gather_scatter, matmul, attention) report the same fields for the other
+benchmark configurations.
 """
 from __future__ import annotations
 
@@ -22,30 +26,246 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-N_ROWS, N_COLS, CORES, ROWS_PER_ITER = 8192, 4096, 32, 8
-ELEMS = N_ROWS * N_COLS
-ALGO_BYTES = 2 * ELEMS * 2          # read f16 once + write f16 once
-METRIC = "KTIR exec throughput (row softmax 8192x4096 f16, f32 stats)"
-UNIT = "elem/s"
+
+# ---------------------------------------------------------------------------
+# Workloads: KTIR source, seeded synthetic inputs, algorithmic work per step
+# ---------------------------------------------------------------------------
+class Workload:
+    name = ""
+    func = ""
+    unit = "elem/s"
+    bound = "hbm"
+    kernel = ""
+    dtype = "f32"
+    units_per_step = 0          # elements (or FLOP) one step processes
+    algo_per_step = 0           # algorithmic bytes (hbm) or FLOP (tensor) of the dominant kernel
+    describe = ""
+
+    def source(self): ...
+    def inputs(self, rank=0): ...
+    def check(self, kw, res): return None
+    def cpu_case(self, procs): ...     # (source, func, kwargs, units) of a bounded CPU sample
 
 
-def workload_config(n_gpus):
-    return {"workload": "row_softmax f16[8192,4096], grid 32 cores x 256 rows, 8 rows/iteration, f32 stats",
-            "elements_per_step_per_gpu": ELEMS, "sharding": f"replica per GPU x{n_gpus} (independent shards)",
-            "l2": "flushed (256 MiB memset) between timed steps; step timed by CUDA events on the launch stream"}
+def _rows_fix(rows, cores, r):
+    cores = max(1, min(cores, rows // r))
+    while rows % (cores * r):
+        cores -= 1
+    return cores
 
 
-def make_input(seed=2):
-    rng = np.random.default_rng(seed)
-    return (rng.standard_normal((N_ROWS, N_COLS), dtype=np.float32) * 2).astype(np.float16)
+class Softmax(Workload):
+    name, func, kernel = "softmax", "softmax_kernel", "ktb_row_softmax_kernel"
+    R, C, CORES, RPI = 8192, 4096, 32, 8
+    units_per_step = R * C
+    algo_per_step = 2 * R * C * 2
+    describe = "row_softmax f16[8192,4096], grid 32 cores x 256 rows, 8 rows/iteration, f32 stats"
+    metric = "KTIR exec throughput (row softmax 8192x4096 f16, f32 stats)"
+
+    def source(self):
+        from ktir_cpu_b200 import kernels as K
+        return K.softmax_rows(self.R, self.C, self.CORES, self.RPI, True)
+
+    def _x(self, rows, seed):
+        return (np.random.default_rng(seed).standard_normal((rows, self.C), dtype=np.float32) * 2).astype(np.float16)
+
+    def inputs(self, rank=0):
+        x = self._x(self.R, 2 + rank)
+        return dict(output_ptr=np.zeros_like(x), input_ptr=x)
+
+    def check(self, kw, res):
+        x, y = kw["input_ptr"], res["output_ptr"]
+        rows = np.arange(0, self.R, 257)
+        xf = np.asarray(x[rows], dtype=np.float32)
+        e = np.exp(xf - xf.max(1, keepdims=True))
+        return float(np.abs(y[rows].astype(np.float32) - e / e.sum(1, keepdims=True)).max())
+
+    def cpu_case(self, rows, seed=2):
+        from ktir_cpu_b200 import kernels as K
+        cores = _rows_fix(rows, self.CORES, self.RPI)
+        x = self._x(rows, seed)
+        return (K.softmax_rows(rows, self.C, cores, self.RPI, True), self.func,
+                dict(output_ptr=np.zeros_like(x), input_ptr=x), rows * self.C)
+
+    cpu_full, cpu_small = 8192, 1024
 
 
-def measured_peak_gbs():
+class VectorAdd(Workload):
+    name, func, kernel = "vector_add", "add_kernel", "ktb_ew_stream_kernel"
+    N, BLOCK, CORES = 1 << 26, 131072, 32
+    units_per_step = N
+    algo_per_step = 3 * N * 2
+    describe = "vector_add f16[2^26], 32 cores x 16 blocks of 131072 (scaled twin of the 4096-element example)"
+    metric = "KTIR exec throughput (vector_add 2^26 f16)"
+    dtype = "f16"
+
+    def source(self):
+        from ktir_cpu_b200 import kernels as K
+        return K.vector_add(self.N, self.BLOCK, self.CORES)
+
+    def inputs(self, rank=0):
+        rng = np.random.default_rng(1 + rank)
+        x = rng.standard_normal(self.N, dtype=np.float32).astype(np.float16)
+        y = rng.standard_normal(self.N, dtype=np.float32).astype(np.float16)
+        return dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(self.N, np.float16), BLOCK_SIZE=self.BLOCK)
+
+    def check(self, kw, res):
+        return float(np.abs((kw["x_ptr"][:65536] + kw["y_ptr"][:65536]).astype(np.float32)
+                            - res["output_ptr"][:65536].astype(np.float32)).max())
+
+    def cpu_case(self, n, seed=1):
+        from ktir_cpu_b200 import kernels as K
+        rng = np.random.default_rng(seed)
+        x = rng.standard_normal(n, dtype=np.float32).astype(np.float16)
+        y = rng.standard_normal(n, dtype=np.float32).astype(np.float16)
+        blk = min(self.BLOCK, n // 32)
+        return (K.vector_add(n, blk, 32), self.func,
+                dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(n, np.float16), BLOCK_SIZE=blk), n)
+
+    cpu_full, cpu_small = 1 << 26, 1 << 22
+
+
+class GatherScatter(Workload):
+    name, func, kernel = "gather_scatter", "gather_scale_scatter", "ktb_scatter_apply_kernel"
+    ROWS, COLS, NIDX, TILE, CORES = 65536, 128, 262144, 64, 64
+    units_per_step = NIDX * COLS
+    algo_per_step = NIDX * (4 + 3 * COLS * 2)
+    describe = ("gather + x0.5 + read-modify-write scatter: table f16[65536,128], 262144 int32 indices, "
+                "64-row tiles with 6 duplicates per tile, 64 cores")
+    metric = "KTIR exec throughput (indirect gather+scatter, gathered elements)"
+    dtype = "f16"
+
+    def _idx(self, rng, rows, n):
+        idx = rng.integers(0, rows, n)
+        for t in range(n // self.TILE):
+            pos = rng.choice(self.TILE, 12, replace=False)
+            idx[t * self.TILE + pos[:6]] = idx[t * self.TILE + pos[6:]]
+        return idx.astype(np.int32)
+
+    def source(self):
+        from ktir_cpu_b200 import kernels as K
+        return K.gather_scale_scatter(self.ROWS, self.COLS, self.NIDX, self.TILE, self.CORES)
+
+    def inputs(self, rank=0):
+        rng = np.random.default_rng(3 + rank)
+        table = rng.standard_normal((self.ROWS, self.COLS), dtype=np.float32).astype(np.float16)
+        return dict(table_ptr=table, idx_ptr=self._idx(rng, self.ROWS, self.NIDX), out_ptr=np.zeros_like(table))
+
+    def reset(self, sess, kw):
+        sess.upload("out_ptr", kw["out_ptr"])      # the kernel accumulates into out
+
+    def cpu_case(self, n, seed=3):
+        from ktir_cpu_b200 import kernels as K
+        rng = np.random.default_rng(seed)
+        rows = max(64, n // 4)
+        table = rng.standard_normal((rows, self.COLS), dtype=np.float32).astype(np.float16)
+        cores = max(1, min(self.CORES, n // self.TILE))
+        return (K.gather_scale_scatter(rows, self.COLS, n, self.TILE, cores), self.func,
+                dict(table_ptr=table, idx_ptr=self._idx(rng, rows, n), out_ptr=np.zeros_like(table)),
+                n * self.COLS)
+
+    cpu_full, cpu_small = 262144, 16384
+
+
+class Matmul(Workload):
+    name, func, kernel = "matmul", "matmul_kernel", "ktb_gemm_f16_kernel"
+    M = N = KK = 4096
+    unit, bound = "FLOP/s", "tensor"
+    units_per_step = 2 * M * N * KK
+    algo_per_step = units_per_step
+    describe = "tiled matmul f16 4096^3, 64x64 tiles, K-step 64, 32 cores x 128 tiles, f32 accumulate"
+    metric = "KTIR exec throughput (tiled matmul 4096^3 f16, f32 accumulate)"
+
+    def source(self):
+        from ktir_cpu_b200 import kernels as K
+        return K.tiled_matmul(self.M, self.N, self.KK, 64, 64, 64, 32, True)
+
+    def inputs(self, rank=0):
+        rng = np.random.default_rng(4 + rank)
+        a = rng.uniform(-1, 1, (self.M, self.KK)).astype(np.float16)
+        b = rng.uniform(-1, 1, (self.KK, self.N)).astype(np.float16)
+        return dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((self.M, self.N), np.float16))
+
+    def check(self, kw, res):
+        rows = np.arange(0, self.M, 409)
+        want = kw["a_ptr"][rows].astype(np.float32) @ kw["b_ptr"].astype(np.float32)
+        return float(np.abs(res["c_ptr"][rows].astype(np.float32) - want).max())
+
+    def cpu_case(self, n, seed=4):
+        from ktir_cpu_b200 import kernels as K
+        rng = np.random.default_rng(seed)
+        a = rng.uniform(-1, 1, (n, n)).astype(np.float16)
+        b = rng.uniform(-1, 1, (n, n)).astype(np.float16)
+        tiles = (n // 64) ** 2
+        cores = min(32, tiles)
+        return (K.tiled_matmul(n, n, n, 64, 64, 64, cores, True), self.func,
+                dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((n, n), np.float16)), 2 * n ** 3)
+
+    cpu_full, cpu_small = 1024, 512
+
+
+class Attention(Workload):
+    name, func, kernel = "attention", "attention_kernel", "ktb_attention_fwd_kernel"
+    S, H, D, TM, TN = 2048, 256, 128, 128, 128
+    unit, bound = "FLOP/s", "tensor"
+    units_per_step = 4 * H * D * (S * (S + 1) // 2)
+    algo_per_step = units_per_step
+    describe = ("causal attention f16 B8 H32 (batch folded into 256 heads) S2048 D128, paged K/V with identity "
+                "block table, tiles 128x128, f32 online softmax")
+    metric = "KTIR exec throughput (causal attention B8 H32 S2048 D128, causal FLOP)"
+
+    def source(self):
+        from ktir_cpu_b200 import kernels as K
+        return K.causal_attention(self.S, self.H, self.D, self.TM, self.TN)
+
+    def _kw(self, rng, S, H):
+        D, tn = self.D, self.TN
+        q, k, v = (rng.standard_normal((S, H, D), dtype=np.float32).astype(np.float16) for _ in range(3))
+        return dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(S // tn, tn, H, D),
+                    value_cache_ptr=v.reshape(S // tn, tn, H, D),
+                    block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
+                    num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D)))
+
+    def inputs(self, rank=0):
+        return self._kw(np.random.default_rng(5 + rank), self.S, self.H)
+
+    def check(self, kw, res):
+        h = 3
+        q = kw["query_ptr"][:, h].astype(np.float64)
+        k = kw["key_cache_ptr"][:, :, h].reshape(self.S, self.D).astype(np.float64)
+        v = kw["value_cache_ptr"][:, :, h].reshape(self.S, self.D).astype(np.float64)
+        sc = q @ k.T / np.sqrt(self.D)
+        sc = np.where(np.tril(np.ones((self.S, self.S), bool)), sc, -np.inf)
+        p = np.exp(sc - sc.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        return float(np.abs(res["output_ptr"][:, h].astype(np.float64) - p @ v).max())
+
+    def cpu_case(self, S, seed=5):
+        from ktir_cpu_b200 import kernels as K
+        H = 1
+        return (K.causal_attention(S, H, self.D, self.TM, self.TN), self.func,
+                self._kw(np.random.default_rng(seed), S, H), 4 * H * self.D * (S * (S + 1) // 2))
+
+    cpu_full, cpu_small = 1024, 512
+
+
+WORKLOADS = {w.name: w for w in (Softmax(), VectorAdd(), GatherScatter(), Matmul(), Attention())}
+
+
+def workload_config(w, n_gpus):
+    return {"workload": w.describe, "units_per_step_per_gpu": w.units_per_step,
+            "sharding": f"one independent replica of the workload per GPU (x{n_gpus}), no collective",
+            "l2": "flushed (256 MiB memset) between timed steps; each step timed by CUDA events on the launch stream"}
+
+
+def measured_peak(bound):
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
-        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        d = json.load(open(p))
+        return (float(d["hbm_gbs"]), "GB/s", "measured (MEASURED_PEAKS.json)") if bound == "hbm" else \
+            (float(d["bf16_tflops"]), "TFLOP/s", "measured burst (MEASURED_PEAKS.json)")
     except Exception:
-        return 6650.0, "fallback"
+        return (6650.0, "GB/s", "fallback") if bound == "hbm" else (1590.0, "TFLOP/s", "fallback")
 
 
 class ClockSampler:
@@ -60,9 +280,10 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
+            time.sleep(0.3)
         except Exception:
             self.proc = None
 
@@ -73,10 +294,16 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
-        sm = [float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
+
+        def num(s):
+            try:
+                return float(s)
+            except ValueError:
+                return None
+        sm = [num(r[1]) for r in self.rows if len(r) > 8 and num(r[1]) is not None]
+        mx = [num(r[2]) for r in self.rows if len(r) > 8 and num(r[2]) is not None]
         reasons = set()
         for r in self.rows:
             if len(r) > 8:
@@ -91,61 +318,63 @@ class ClockSampler:
 # CPU side: the oracle port of the reference interpreter
 # ---------------------------------------------------------------------------
 def _cpu_worker(args):
-    rows, seed = args
-    from ktir_cpu_b200 import kernels as K
+    name, size, seed = args
     from oracle.numpy_interp import OracleInterpreter
-    cores = max(1, min(CORES, rows // ROWS_PER_ITER))
-    while rows % (cores * ROWS_PER_ITER):
-        cores -= 1
-    x = (np.random.default_rng(seed).standard_normal((rows, N_COLS), dtype=np.float32) * 2).astype(np.float16)
+    src, fn, kw, units = WORKLOADS[name].cpu_case(size, seed)
     it = OracleInterpreter()
-    it.load(K.softmax_rows(rows, N_COLS, cores, ROWS_PER_ITER, True))
+    it.load(src)
     t0 = time.perf_counter()
-    it.execute_function("softmax_kernel", output_ptr=np.zeros_like(x), input_ptr=x)
-    return time.perf_counter() - t0
+    it.execute_function(fn, **kw)
+    return time.perf_counter() - t0, units
 
 
-def cpu_sample(procs: int, rows_per_proc: int):
-    """elements/s of the oracle on `procs` host processes, each on its own shard of rows."""
+def _cpu_import(_):
+    import oracle.numpy_interp  # noqa: F401
+    import ktir_cpu_b200.kernels  # noqa: F401
+    return 0
+
+
+def cpu_sample(w, procs, size):
+    """units/s of the oracle on `procs` host processes, each running its own instance."""
     import multiprocessing as mp
     if procs == 1:
-        dt = _cpu_worker((rows_per_proc, 2))
-    else:
-        with mp.get_context("spawn").Pool(procs) as pool:
-            t0 = time.perf_counter()
-            pool.map(_cpu_worker, [(rows_per_proc, 2 + i) for i in range(procs)])
-            dt = time.perf_counter() - t0
-    return procs * rows_per_proc * N_COLS / dt, dt
+        dt, units = _cpu_worker((w.name, size, 2))
+        return units / dt, dt
+    with mp.get_context("spawn").Pool(procs) as pool:
+        pool.map(_cpu_import, range(procs))       # interpreter start-up stays outside the timing
+        t0 = time.perf_counter()
+        out = pool.map(_cpu_worker, [(w.name, size, 2 + i) for i in range(procs)])
+        dt = time.perf_counter() - t0
+    return sum(u for _, u in out) / dt, dt
 
 
-def run_reference(args):
+def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     procs = max(1, min(os.cpu_count() or 1, 32))
-    rows_per_proc = max(ROWS_PER_ITER * 8, (N_ROWS // procs) // ROWS_PER_ITER * ROWS_PER_ITER)
-    times = []
+    size = w.cpu_small
+    res = []
     for i in range(args.warmup + args.steps):
-        v, dt = cpu_sample(procs, rows_per_proc)
+        v, dt = cpu_sample(w, procs, size)
         if i >= args.warmup:
-            times.append((v, dt))
-    value = float(np.mean([v for v, _ in times]))
-    sample = (f"{procs} processes x {rows_per_proc} rows x {N_COLS} cols per step "
+            res.append((v, dt))
+    value = float(np.mean([v for v, _ in res]))
+    sample = (f"{procs} processes, each the same KTIR kernel at size {size} "
               f"(oracle/numpy_interp.py, NumPy {np.__version__})")
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": float(np.mean([dt for _, dt in times])) * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args.gpus),
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": procs, "kind": "port", "sample": sample},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    line = {"impl": "reference", "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean([dt for _, dt in res])) * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
+            "data": "synthetic", "config": workload_config(w, args.gpus),
+            "cpu_baseline": {"value": value, "unit": w.unit, "cores": procs, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
 # ---------------------------------------------------------------------------
 # GPU side
 # ---------------------------------------------------------------------------
-def run_gpu(args):
+def run_gpu(args, w):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -156,29 +385,37 @@ def run_gpu(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    from ktir_cpu_b200 import kernels as K
     from ktir_cpu_b200.interpreter import KTIRInterpreter
     from ktir_cpu_b200.pinned import pinned_empty
 
     interp = KTIRInterpreter(device=local)
-    interp.load(K.softmax_rows(N_ROWS, N_COLS, CORES, ROWS_PER_ITER, True))
+    interp.load(w.source())
     dev = interp.device
-    x = pinned_empty(dev, (N_ROWS, N_COLS), np.float16)
-    x[...] = make_input(2 + rank)
-    out0 = pinned_empty(dev, (N_ROWS, N_COLS), np.float16)
-    out0[...] = 0
-    sess, _ = interp.session("softmax_kernel", output_ptr=out0, input_ptr=x)
-    sess.upload("input_ptr", x)
-    sess.upload("output_ptr", out0)
+    kw = {}
+    for k, v in w.inputs(rank).items():
+        if isinstance(v, np.ndarray):
+            p = pinned_empty(dev, v.shape, v.dtype)
+            p[...] = v
+            kw[k] = p
+        else:
+            kw[k] = v
+    sess, _ = interp.session(w.func, **kw)
+    for k, v in kw.items():
+        if isinstance(v, np.ndarray):
+            sess.upload(k, v)
     dev.sync()
 
     def barrier():
         if dist is not None:
             dist.barrier()
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         sess.run()
     dev.sync()
+    if hasattr(w, "reset"):
+        w.reset(sess, kw)
+        dev.sync()
 
     sampler = ClockSampler(local)
     sampler.start()
@@ -186,7 +423,7 @@ def run_gpu(args):
     dev.sync()
     l0 = dev.launch_count()
     per_step = []
-    for i in range(args.steps):
+    for _ in range(args.steps):
         dev.flush_l2()
         dev.record(0)
         sess.run()
@@ -199,23 +436,16 @@ def run_gpu(args):
     clocks = sampler.stop()
     total_ms = float(sum(per_step))
 
-    # end to end through the public API: host (pinned) buffers in, host arrays out, every step
+    # end to end through the public API: host (pinned) buffers in, fresh host arrays out, every step
     for _ in range(2):
-        interp.execute_function("softmax_kernel", output_ptr=out0, input_ptr=x)
+        interp.execute_function(w.func, **kw)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        res = interp.execute_function("softmax_kernel", output_ptr=out0, input_ptr=x)
+        res = interp.execute_function(w.func, **kw)
     e2e_s = time.perf_counter() - t0
-    h2d = int(sess.last_h2d_bytes)
-    d2h = int(sess.last_d2h_bytes)
-
-    # spot check of the timed result against a float32 softmax of the same rows
-    y = res["output_ptr"]
-    rows = np.arange(0, N_ROWS, 257)
-    xf = np.asarray(x[rows], dtype=np.float32)
-    e = np.exp(xf - xf.max(1, keepdims=True))
-    err = float(np.abs(y[rows].astype(np.float32) - e / e.sum(1, keepdims=True)).max())
+    h2d, d2h = int(sess.last_h2d_bytes), int(sess.last_d2h_bytes)
+    err = w.check(kw, res) if not hasattr(w, "reset") else None
 
     if dist is not None:
         import torch
@@ -224,30 +454,26 @@ def run_gpu(args):
         total_ms, e2e_s = float(t[0]), float(t[1])
     if rank == 0:
         ms_per_step = total_ms / args.steps
-        value = world * ELEMS / (ms_per_step * 1e-3)
-        peak, peak_src = measured_peak_gbs()
-        achieved = ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
+        value = world * w.units_per_step / (ms_per_step * 1e-3)
+        peak, punit, peak_src = measured_peak(w.bound)
+        achieved = w.algo_per_step / (ms_per_step * 1e-3) / (1e9 if w.bound == "hbm" else 1e12)
         traffic = None
         tp = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tp):
-            traffic = json.load(open(tp)).get("row_softmax_8192x4096_dram_bytes_per_launch")
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": workload_config(world),
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            traffic = json.load(open(tp)).get(w.name)
+        line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps,
+                "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": workload_config(w, world),
+                "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": punit,
                              "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
-                             "algorithmic_bytes_per_launch": ALGO_BYTES, "kernel": "ktb_row_softmax_kernel"},
-                "e2e": {"value": world * ELEMS * args.steps / e2e_s, "unit": UNIT,
-                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                        "ms_per_step": e2e_s / args.steps * 1e3},
-                "gpu_launches": int(launches), "clocks": clocks, "max_abs_err_vs_f32_softmax": err}
+                             "algorithmic_per_launch": w.algo_per_step, "kernel": w.kernel},
+                "e2e": {"value": world * w.units_per_step * args.steps / e2e_s, "unit": w.unit,
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / args.steps * 1e3},
+                "gpu_launches": int(launches), "clocks": clocks, "max_abs_err_spot_check": err}
         if world == 1 and not args.no_cpu:
-            procs = 1
-            rows = 1024
-            v, dt = cpu_sample(procs, rows)
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": procs, "kind": "port",
-                                    "sample": f"{rows} rows x {N_COLS} cols of the same kernel, "
+            v, dt = cpu_sample(w, 1, w.cpu_small)
+            line["cpu_baseline"] = {"value": v, "unit": w.unit, "cores": 1, "kind": "port",
+                                    "sample": f"same KTIR kernel at size {w.cpu_small} through "
                                               f"oracle/numpy_interp.py on 1 core, {dt:.2f} s"}
         print(json.dumps(line))
     interp.close()
@@ -261,12 +487,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
+    w = WORKLOADS[args.workload]
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, w)
     else:
-        run_gpu(args)
+        run_gpu(args, w)
 
 
 if __name__ == "__main__":
