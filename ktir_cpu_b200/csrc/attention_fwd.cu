@@ -192,18 +192,66 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         bool ok = true;
 
         auto fold_pv = [&](int jp, float alpha) {
-            const int s = jp & 1;
+            const uint32_t base = tmem_pv + (jp & 1) * 128 + lane_off;
+            uint32_t va[32], vb[32];
+            tc_tmem_ld32(base, va);
+            tc_tmem_ld_wait();
+            tc_tmem_ld32(base + 32, vb);
 #pragma unroll
-            for (int c0 = 0; c0 < AT_D; c0 += 32) {
-                uint32_t v[32];
-                tc_tmem_ld32(tmem_pv + s * 128 + lane_off + c0, v);
-                tc_tmem_ld_wait();
+            for (int i = 0; i < 32; ++i) o[i] = __fmaf_rn(o[i], alpha, __uint_as_float(va[i]));
+            tc_tmem_ld_wait();
+            tc_tmem_ld32(base + 64, va);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c0 + i] = o[c0 + i] * alpha + __uint_as_float(v[i]);
-            }
+            for (int i = 0; i < 32; ++i) o[32 + i] = __fmaf_rn(o[32 + i], alpha, __uint_as_float(vb[i]));
+            tc_tmem_ld_wait();
+            tc_tmem_ld32(base + 96, vb);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[64 + i] = __fmaf_rn(o[64 + i], alpha, __uint_as_float(va[i]));
+            tc_tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[96 + i] = __fmaf_rn(o[96 + i], alpha, __uint_as_float(vb[i]));
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&bars[B_PVEMPTY + s]);
+            if (lane == 0) tc_mbar_arrive(&bars[B_PVEMPTY + (jp & 1)]);
+        };
+
+        // running-max update of one 32-column chunk (raw scores; scaled afterwards)
+        auto chunk_max = [&](const uint32_t (&v)[32], long long c_abs, bool need_mask, float& mx) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float t = __uint_as_float(v[i]) * sl;
+                if (need_mask && c_abs + i > limit) t = -INFINITY;
+                mx = fmaxf(mx, t);
+            }
+        };
+        // probabilities of one 32-column chunk -> packed f16 in shared memory, partial row sum
+        auto chunk_prob = [&](const uint32_t (&v)[32], int c0, long long c_abs, bool need_mask, float m_new,
+                              float& lsum) {
+            uint32_t packed[16];
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float p0 = at_ex2(__fmaf_rn(__uint_as_float(v[i]), sl, -m_new));
+                float p1 = at_ex2(__fmaf_rn(__uint_as_float(v[i + 1]), sl, -m_new));
+                if (need_mask) {
+                    if (c_abs + i > limit) p0 = 0.f;
+                    if (c_abs + i + 1 > limit) p1 = 0.f;
+                }
+                s0 += p0;
+                s1 += p1;
+                const __half2 h = __floats2half2_rn(p0, p1);
+                packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            lsum += s0 + s1;
+            // 32 columns = four 16-byte chunks of this row inside block (c0 / 64)
+            uint8_t* blk = sP + (c0 >> 6) * (AT_BM * 128) + r * 128;
+            const int chunk0 = (c0 & 63) >> 3;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int phys = (chunk0 + c) ^ (r & 7);
+                *reinterpret_cast<uint4*>(blk + phys * 16) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            }
         };
 
         for (int j = 0; j < n; ++j) {
@@ -212,18 +260,23 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (!tc_mbar_wait(&bars[B_SFULL + s], ph, abort_flag, st, 31)) { ok = false; break; }
             tc_fence_after_sync();
             const long long col0 = (long long)j * BN;
-            // pass 1: row maximum of the scaled, masked scores
+            const bool need_mask = a.causal && (col0 + BN - 1 > limit);
+            const uint32_t sbase = tmem_s + s * 128 + lane_off;
+            // pass 1: row maximum of the scaled (masked) scores; TMEM loads run one chunk ahead
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tc_tmem_ld32(tmem_s + s * 128 + lane_off + c0, v);
-                tc_tmem_ld_wait();
+            {
+                uint32_t va[32], vb[32];
+                tc_tmem_ld32(sbase, va);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float t = __uint_as_float(v[i]) * sl;
-                    const bool keep = !a.causal || (col0 + c0 + i <= limit);
-                    mx = fmaxf(mx, keep ? t : -INFINITY);
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    tc_tmem_ld_wait();
+                    if (c0 + 32 < BN) tc_tmem_ld32(sbase + c0 + 32, vb);
+                    chunk_max(va, col0 + c0, need_mask, mx);
+                    if (c0 + 32 < BN) {
+                        tc_tmem_ld_wait();
+                        if (c0 + 64 < BN) tc_tmem_ld32(sbase + c0 + 64, va);
+                        chunk_max(vb, col0 + c0 + 32, need_mask, mx);
+                    }
                 }
             }
             const float m_new = fmaxf(m_run, mx);
@@ -236,30 +289,19 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             // pass 2: probabilities -> f16 -> shared memory (K-major, 128-byte swizzle), row sum in f32
             float lsum = 0.f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t v[32];
-                tc_tmem_ld32(tmem_s + s * 128 + lane_off + c0, v);
-                tc_tmem_ld_wait();
-                uint32_t packed[16];
+            {
+                uint32_t va[32], vb[32];
+                tc_tmem_ld32(sbase, va);
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const bool k0 = !a.causal || (col0 + c0 + i <= limit);
-                    const bool k1 = !a.causal || (col0 + c0 + i + 1 <= limit);
-                    const float p0 = k0 ? at_ex2(__uint_as_float(v[i]) * sl - m_new) : 0.f;
-                    const float p1 = k1 ? at_ex2(__uint_as_float(v[i + 1]) * sl - m_new) : 0.f;
-                    lsum += p0 + p1;
-                    const __half2 h = __floats2half2_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-                // 32 columns = four 16-byte chunks of this row inside block (c0 / 64)
-                uint8_t* blk = sP + (c0 >> 6) * (AT_BM * 128) + r * 128;
-                const int chunk0 = (c0 & 63) >> 3;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int phys = (chunk0 + c) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(blk + phys * 16) =
-                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    tc_tmem_ld_wait();
+                    if (c0 + 32 < BN) tc_tmem_ld32(sbase + c0 + 32, vb);
+                    chunk_prob(va, c0, col0 + c0, need_mask, m_new, lsum);
+                    if (c0 + 32 < BN) {
+                        tc_tmem_ld_wait();
+                        if (c0 + 64 < BN) tc_tmem_ld32(sbase + c0 + 64, va);
+                        chunk_prob(vb, c0 + 32, col0 + c0 + 32, need_mask, m_new, lsum);
+                    }
                 }
             }
             tc_fence_before_sync();          // S buffer fully read

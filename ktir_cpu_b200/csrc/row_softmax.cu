@@ -211,6 +211,107 @@ __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3) ktb_row_softmax_kernel(c
     }
 }
 
+// ---- fast path: f16 input, f32 statistics -------------------------------------------------------
+// max is exact in any order, so it is taken on the packed f16 data (one HMNMX2 per two elements);
+// exp is ex2.approx of an FMA-scaled argument and therefore not bit-comparable with NumPy anyway,
+// so the sum uses a plain per-thread accumulation + butterfly instead of the halving order.
+// About 6 instructions per element; the row is read once and written once.
+template <int NV, bool MAXNUM>
+__global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3)
+ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows) {
+    __shared__ float xmax[8], xsum[8];            // one slot per warp of the CTA
+    const int groups = 256 / T;
+    const int group = threadIdx.x / T;
+    const int t = threadIdx.x - group * T;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wpg = T >> 5;                        // warps per row group (0 when T < 32)
+    const __half* in16 = reinterpret_cast<const __half*>(a.arena);
+    const int w = T < 32 ? T : 32;
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
+        const bool live = it * groups + group < total_rows;
+        const int64_t row = live ? it * groups + group : 0;
+        const int64_t item = row / a.rows_per_item;
+        const int64_t r = row - item * a.rows_per_item;
+        const int64_t in_off = a.dev_item_offsets[item * 2] + r * a.in_row_stride;
+        const int64_t out_off = a.dev_item_offsets[item * 2 + 1] + r * a.out_row_stride;
+        const uint4* src = reinterpret_cast<const uint4*>(in16 + in_off) + t;
+
+        uint4 raw[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) raw[j] = __ldcs(src + (int64_t)j * T);
+
+        __half2 m2 = *reinterpret_cast<const __half2*>(&raw[0].x);
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) m2 = MAXNUM ? __hmax2(m2, h[i]) : __hmax2_nan(m2, h[i]);
+        }
+        for (int d = w >> 1; d >= 1; d >>= 1) {
+            uint32_t o = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&m2), d, w);
+            const __half2 oh = *reinterpret_cast<__half2*>(&o);
+            m2 = MAXNUM ? __hmax2(m2, oh) : __hmax2_nan(m2, oh);
+        }
+        float mx = sm_max<MAXNUM>(__low2float(m2), __high2float(m2));
+        if (wpg > 1) {
+            if (lane == 0) xmax[warp] = mx;
+            group_barrier(1 + group, T);
+            const int w0 = warp - (warp % wpg);
+            mx = xmax[w0];
+            for (int k = 1; k < wpg; ++k) mx = sm_max<MAXNUM>(mx, xmax[w0 + k]);
+        }
+        mx = sm_max<MAXNUM>(mx, a.max_init);
+        const float mxs = mx * 1.4426950408889634f;
+
+        float p[NV][8];
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                p[j][2 * i] = sm_ex2(__fmaf_rn(f.x, 1.4426950408889634f, -mxs));
+                p[j][2 * i + 1] = sm_ex2(__fmaf_rn(f.y, 1.4426950408889634f, -mxs));
+            }
+            s0 += p[j][0] + p[j][1];
+            s1 += p[j][2] + p[j][3];
+            s2 += p[j][4] + p[j][5];
+            s3 += p[j][6] + p[j][7];
+        }
+        float sum = (s0 + s1) + (s2 + s3);
+        for (int d = w >> 1; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, w);
+        if (wpg > 1) {
+            if (lane == 0) xsum[warp] = sum;
+            group_barrier(1 + group, T);
+            const int w0 = warp - (warp % wpg);
+            sum = xsum[w0];
+            for (int k = 1; k < wpg; ++k) sum += xsum[w0 + k];
+        }
+        const float inv = 1.0f / (sum + a.sum_init);
+        if (!live) continue;
+        if (a.out_dtype == KTB_F16) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + out_off) + t;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                uint4 o;
+                __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(p[j][2 * i] * inv, p[j][2 * i + 1] * inv);
+                __stcs(dst + (int64_t)j * T, o);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                float* q = reinterpret_cast<float*>(a.arena) + out_off + ((int64_t)j * T + t) * 8;
+                __stcs(reinterpret_cast<float4*>(q), make_float4(p[j][0] * inv, p[j][1] * inv, p[j][2] * inv, p[j][3] * inv));
+                __stcs(reinterpret_cast<float4*>(q + 4), make_float4(p[j][4] * inv, p[j][5] * inv, p[j][6] * inv, p[j][7] * inv));
+            }
+        }
+    }
+}
+
 template <int NV>
 static void launch_softmax(ktb_ctx* ctx, const ktb_softmax_args& a, int T, int64_t total_rows) {
     const int groups = 256 / T;
@@ -218,6 +319,11 @@ static void launch_softmax(ktb_ctx* ctx, const ktb_softmax_args& a, int T, int64
     int64_t blocks = (int64_t)ctx->sm_count * 8;
     if (blocks > n_iter) blocks = n_iter;
     const bool mn = a.max_is_maxnum != 0, r16 = a.f16_arith != 0;
+    if (a.in_dtype == KTB_F16 && !r16) {
+        if (mn) ktb_row_softmax_fast_kernel<NV, true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows);
+        else ktb_row_softmax_fast_kernel<NV, false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows);
+        return;
+    }
 #define KTB_SM_LAUNCH(MN, R) ktb_row_softmax_kernel<NV, MN, R><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows)
     if (mn && r16) KTB_SM_LAUNCH(true, true);
     else if (mn) KTB_SM_LAUNCH(true, false);

@@ -23,10 +23,6 @@
 // HBM-bound: per entry one index, one row per input, one row written.
 #include "vm.cuh"
 
-#define SC_THREADS 512
-#define SC_WARPS (SC_THREADS / 32)
-#define SC_LCAP 4096            // entries buffered per CTA before a batch is applied
-#define SC_MAX_OWN_ROWS 4096    // destination rows owned by one CTA (smem counters)
 
 static __device__ __forceinline__ int64_t sc_read_index(const void* arena, int idx_dtype, int64_t off) {
     return idx_dtype == KTB_I64 ? reinterpret_cast<const int64_t*>(arena)[off]
@@ -142,9 +138,56 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const ktb_rows_ar
     }
 }
 
+// ---- grouped entry processing: G entries per warp in flight at once -------------------------
+// Row addresses of all entries are resolved first (independent index loads), then all rows are
+// loaded, then programs run and rows are stored: the dependent index -> row chain of one entry
+// overlaps with the chains of the others.
+template <int V, int G>
+static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const int64_t (&ent)[G],
+                                                   const int64_t (&dst)[G], int n, int lane, ktb_status* st) {
+    int64_t in_addr[G][KTB_ROWS_MAX_IN];
+    bool ok[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        ok[g] = g < n && dst[g] >= 0;
+        if (g < n) {
+            const int64_t t = ent[g] / a.tile_rows;
+            const int pos = (int)(ent[g] - t * a.tile_rows);
+            for (int k = 0; k < a.n_in; ++k) {
+                in_addr[g][k] = a.in[k].alias_dst ? dst[g] : sc_row_addr(a.arena, a.in[k], t, pos, st);
+                ok[g] = ok[g] && in_addr[g][k] >= 0;
+            }
+        }
+    }
+    for (int col = lane * V; col < a.cols; col += 32 * V) {
+        float x[G][KTB_ROWS_MAX_IN][V];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+            if (ok[g])
+                for (int k = 0; k < a.n_in; ++k) sc_load_row<V>(a.arena, a.in[k], in_addr[g][k], col, a.cols, x[g][k]);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (!ok[g]) continue;
+            float regs[KTB_VM_REGS][V];
+            for (int k = 0; k < a.n_in; ++k)
+#pragma unroll
+                for (int v = 0; v < V; ++v) regs[k][v] = x[g][k][v];
+            float out[V];
+            ktb_vm_run<V>(a.program, regs, out);
+            sc_store_row<V>(a.arena, a.out, dst[g], col, a.cols, out);
+        }
+    }
+}
+
 // ---- indirect destination, step 1: row ids + last-writer-wins inside each tile -----------------
-__global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const ktb_rows_args a, ktb_status* st) {
+// Scratch layout: int32 row id per entry (-1 = dropped), then one owner byte per entry (255 = none).
+#define SC_NO_OWNER 255
+
+__global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const ktb_rows_args a, int rows_per_owner,
+                                                                  ktb_status* st) {
     extern __shared__ int64_t s_addr[];      // [tile_rows]
+    const int64_t E = a.n_tiles * a.tile_rows;
+    uint8_t* owner = reinterpret_cast<uint8_t*>(a.dev_rowid_scratch + E);
     for (int64_t t = blockIdx.x; t < a.n_tiles; t += gridDim.x) {
         for (int pos = threadIdx.x; pos < a.tile_rows; pos += blockDim.x) {
             int64_t addr = sc_row_addr(a.arena, a.out, t, pos, st);
@@ -161,27 +204,39 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const ktb_rows
             const int64_t mine = s_addr[pos];
             bool win = mine >= 0;
             for (int q = pos + 1; win && q < a.tile_rows; ++q) win = s_addr[q] != mine;
-            a.dev_rowid_scratch[t * a.tile_rows + pos] = win ? (int32_t)mine : -1;
+            const int64_t e = t * a.tile_rows + pos;
+            a.dev_rowid_scratch[e] = win ? (int32_t)mine : -1;
+            owner[e] = win ? (uint8_t)(mine / rows_per_owner) : (uint8_t)SC_NO_OWNER;
         }
         __syncthreads();
     }
 }
 
 // ---- step 2: owner-computes ordered apply ------------------------------------------------------
+#define SC_THREADS 1024
+#define SC_WARPS (SC_THREADS / 32)
+#define SC_STEP (SC_THREADS * 16)   // entries examined per scan step (16 owner bytes per thread)
+#define SC_LCAP SC_STEP             // entries buffered per CTA before a batch is applied
+#define SC_MAX_OWN_ROWS 4096        // destination rows owned by one CTA (shared-memory counters)
+#define SC_GROUP 4
+
 template <int V>
-__global__ void __launch_bounds__(SC_THREADS) ktb_scatter_apply_kernel(const ktb_rows_args a, int rows_per_owner,
-                                                                        ktb_status* st) {
-    __shared__ int32_t list_e[SC_LCAP];
-    __shared__ uint16_t list_r[SC_LCAP];
-    __shared__ uint16_t list_k[SC_LCAP];     // rank among entries of the same row in this batch
-    __shared__ uint16_t cnt[SC_MAX_OWN_ROWS];
+__global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const ktb_rows_args a, int rows_per_owner,
+                                                                           ktb_status* st) {
+    extern __shared__ uint8_t sc_smem[];
+    int32_t* list_e = reinterpret_cast<int32_t*>(sc_smem);                  // [SC_LCAP]
+    uint16_t* list_r = reinterpret_cast<uint16_t*>(list_e + SC_LCAP);       // [SC_LCAP]
+    uint16_t* list_k = list_r + SC_LCAP;                                    // [SC_LCAP] rank inside the batch
+    uint16_t* cnt = list_k + SC_LCAP;                                       // [SC_MAX_OWN_ROWS]
     __shared__ int32_t warp_tot[SC_WARPS];
     __shared__ int32_t s_len, s_maxrank;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int64_t E = a.n_tiles * a.tile_rows;
-    const int32_t own_lo = blockIdx.x * rows_per_owner;
-    const int32_t own_hi = own_lo + rows_per_owner;
+    const uint8_t* owner = reinterpret_cast<const uint8_t*>(a.dev_rowid_scratch + E);
+    const uint32_t me = blockIdx.x;
+    const uint32_t me4 = me * 0x01010101u;
+    const int32_t own_lo = (int32_t)me * rows_per_owner;
     for (int i = tid; i < rows_per_owner; i += SC_THREADS) cnt[i] = 0;
     if (tid == 0) { s_len = 0; s_maxrank = 0; }
     __syncthreads();
@@ -212,11 +267,18 @@ __global__ void __launch_bounds__(SC_THREADS) ktb_scatter_apply_kernel(const ktb
         __syncthreads();
         const int maxrank = s_maxrank;
         for (int round = 0; round <= maxrank; ++round) {
+            int64_t ent[SC_GROUP], dst[SC_GROUP];
+            int n = 0;
             for (int i = wid; i < len; i += SC_WARPS) {
                 if (list_k[i] != round) continue;
-                const int64_t row = (int64_t)own_lo + list_r[i];
-                sc_do_entry<V>(a, list_e[i], a.dst_row0 + row * a.out.idx_mult, lane, st);
+                ent[n] = list_e[i];
+                dst[n] = a.dst_row0 + ((int64_t)own_lo + list_r[i]) * a.out.idx_mult;
+                if (++n == SC_GROUP) {
+                    sc_do_group<V, SC_GROUP>(a, ent, dst, n, lane, st);
+                    n = 0;
+                }
             }
+            if (n) sc_do_group<V, SC_GROUP>(a, ent, dst, n, lane, st);
             __syncthreads();
         }
         for (int i = tid; i < len; i += SC_THREADS) cnt[list_r[i]] = 0;
@@ -224,45 +286,54 @@ __global__ void __launch_bounds__(SC_THREADS) ktb_scatter_apply_kernel(const ktb
         __syncthreads();
     };
 
-    for (int64_t base = 0; base < E; base += SC_THREADS * 4) {
-        // each thread looks at 4 consecutive entries; matches are appended in entry order
-        int32_t rid[4];
-        const int64_t e0 = base + (int64_t)tid * 4;
-        if (e0 + 4 <= E && (E % 4 == 0)) {
-            int4 v = *reinterpret_cast<const int4*>(a.dev_rowid_scratch + e0);
-            rid[0] = v.x; rid[1] = v.y; rid[2] = v.z; rid[3] = v.w;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) rid[j] = e0 + j < E ? a.dev_rowid_scratch[e0 + j] : -1;
-        }
+    const int64_t n_steps = (E + SC_STEP - 1) / SC_STEP;
+    auto load_bytes = [&](int64_t step) -> uint4 {
+        const int64_t e0 = step * SC_STEP + (int64_t)tid * 16;
+        if (e0 + 16 <= E && ((reinterpret_cast<uintptr_t>(owner) & 15) == 0))
+            return __ldg(reinterpret_cast<const uint4*>(owner + e0));
+        uint32_t w[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+        for (int j = 0; j < 16; ++j)
+            if (e0 + j < E) w[j >> 2] = (w[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((uint32_t)owner[e0 + j] << (8 * (j & 3)));
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    };
+    uint4 cur = n_steps > 0 ? load_bytes(0) : make_uint4(~0u, ~0u, ~0u, ~0u);
+    for (int64_t step = 0; step < n_steps; ++step) {
+        const uint4 nxt = step + 1 < n_steps ? load_bytes(step + 1) : make_uint4(~0u, ~0u, ~0u, ~0u);
+        const int64_t e0 = step * SC_STEP + (int64_t)tid * 16;
+        const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
+        uint32_t hit[4];
         int m = 0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) m += (rid[j] >= own_lo && rid[j] < own_hi) ? 1 : 0;
+        for (int j = 0; j < 4; ++j) {
+            hit[j] = __vcmpeq4(w[j], me4);          // 0xff in every byte that names this CTA
+            m += __popc(hit[j]) >> 3;
+        }
         int incl = m;
         for (int d = 1; d < 32; d <<= 1) {
-            int o = __shfl_up_sync(0xffffffffu, incl, d);
+            const int o = __shfl_up_sync(0xffffffffu, incl, d);
             if (lane >= d) incl += o;
         }
         if (lane == 31) warp_tot[wid] = incl;
         __syncthreads();
         int before = 0, total = 0;
-        for (int w = 0; w < SC_WARPS; ++w) {
-            const int x = warp_tot[w];
-            if (w < wid) before += x;
+        for (int wv = 0; wv < SC_WARPS; ++wv) {
+            const int x = warp_tot[wv];
+            if (wv < wid) before += x;
             total += x;
         }
         if (s_len + total > SC_LCAP) apply_batch();      // uniform: s_len and total are block-wide values
         int at = s_len + before + incl - m;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (rid[j] >= own_lo && rid[j] < own_hi) {
+        for (int j = 0; j < 16; ++j)
+            if (hit[j >> 2] & (0xffu << (8 * (j & 3)))) {
                 list_e[at] = (int32_t)(e0 + j);
-                list_r[at] = (uint16_t)(rid[j] - own_lo);
+                list_r[at] = (uint16_t)(a.dev_rowid_scratch[e0 + j] - own_lo);
                 ++at;
             }
         __syncthreads();
         if (tid == 0) s_len += total;
         __syncthreads();
+        cur = nxt;
     }
     if (s_len > 0) apply_batch();
 }
@@ -315,18 +386,27 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (a.out.idx_mult <= 0 || a.dst_rows <= 0) return ktb_fail(ctx, KTB_E_ARG, "scatter_rows", "bad destination row geometry");
     if (a.dst_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "too many destination rows");
     if (a.n_tiles == 0) return KTB_OK;
+    // destination rows are split over at most 254 owner CTAs of at most SC_MAX_OWN_ROWS rows each
+    int64_t rpo = (a.dst_rows + ctx->sm_count - 1) / ctx->sm_count;
+    if (rpo < 1) rpo = 1;
+    if (rpo > SC_MAX_OWN_ROWS) rpo = SC_MAX_OWN_ROWS;
+    const int64_t owners = (a.dst_rows + rpo - 1) / rpo;
+    if (owners >= SC_NO_OWNER)
+        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "destination has more than 254 x 4096 rows");
     int64_t prep_blocks = a.n_tiles < (int64_t)ctx->sm_count * 16 ? a.n_tiles : (int64_t)ctx->sm_count * 16;
     const size_t smem = (size_t)a.tile_rows * sizeof(int64_t);
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
-    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, ctx->dev_status);
+    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
-    int64_t owners = (int64_t)ctx->sm_count * 2;
-    int64_t rpo = (a.dst_rows + owners - 1) / owners;
-    if (rpo > SC_MAX_OWN_ROWS) rpo = SC_MAX_OWN_ROWS;
-    if (rpo < 1) rpo = 1;
-    owners = (a.dst_rows + rpo - 1) / rpo;
-    if (a.vector_ok) ktb_scatter_apply_kernel<4><<<(unsigned)owners, SC_THREADS, 0, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
-    else ktb_scatter_apply_kernel<1><<<(unsigned)owners, SC_THREADS, 0, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
+    const size_t asmem = (size_t)SC_LCAP * 8 + (size_t)SC_MAX_OWN_ROWS * 2;
+    static bool attr_set = false;
+    if (!attr_set) {
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem));
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem));
+        attr_set = true;
+    }
+    if (a.vector_ok) ktb_scatter_apply_kernel<4><<<(unsigned)owners, SC_THREADS, asmem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
+    else ktb_scatter_apply_kernel<1><<<(unsigned)owners, SC_THREADS, asmem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_apply_kernel");
     return KTB_OK;
 }

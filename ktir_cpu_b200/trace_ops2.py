@@ -275,7 +275,7 @@ def _for(tr: Tracer, op: Op, scope):
     if live.size and int(live.min()) != T:
         raise Unsupported("scf.for with iter_args and a trip count that differs between cores")
     tile_carried = any(is_node(v) for v in inits)
-    if tile_carried and _has_op(reg.ops, ("linalg.matmul", "linalg.batch_matmul")) and T > 1:
+    if tile_carried and _has_op(reg.ops, ("linalg.matmul", "linalg.batch_matmul")) and T >= 1:
         return _symbolic_loop(tr, op, scope, lb, step, T, inits)
     if T > MAX_UNROLL:
         raise Unsupported(f"scf.for with iter_args and {T} iterations")
