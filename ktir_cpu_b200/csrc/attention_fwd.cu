@@ -10,10 +10,11 @@
 // Roles: warp 0 streams Q once and K/V pages into 2-stage shared-memory rings by
 // TMA (page id read from the block table); warp 1 issues tcgen05.mma — S = Q K^T
 // into one of two TMEM score buffers, then P V into one of two TMEM product
-// buffers; warps 2-5 are the softmax: thread r owns query row r, reads its row of
-// S from TMEM, applies scale and mask, keeps the running max / sum, writes
-// P (f16) to shared memory in the 128-byte-swizzled K-major layout, and folds the
-// previous page's P V product into its f32 output row held in registers.  S of
+// buffers; warps 2-9 are the softmax: two threads share a query row (each owns half
+// of the page's columns and half of the output columns), read their part of S from
+// TMEM, apply scale and mask, agree on the running max through shared memory, write
+// P (f16) to shared memory in the 128-byte-swizzled K-major layout, and fold the
+// previous page's P V product into their f32 output half-row held in registers.  S of
 // page j+1 is computed while page j is in the softmax.  All waits are bounded.
 //
 // Numerics: scores, max, sum and the output accumulator are f32 as in the
@@ -23,7 +24,7 @@
 
 #define AT_BM 128
 #define AT_D 128
-#define AT_THREADS 192
+#define AT_THREADS 320
 #define AT_Q_BYTES (AT_BM * AT_D * 2)
 
 static __device__ __forceinline__ void at_tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x,
@@ -60,11 +61,14 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xm = reinterpret_cast<float*>(tmem_slot + 4);      // [2 parities][2 halves][128 rows] partial maxima
+    float* xl = xm + 2 * 2 * AT_BM;                           // [2 halves][128 rows] partial sums
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // heavy (late) query blocks first: they see the most KV pages
-    const int head = blockIdx.x % a.heads;
-    const int qb = q_blocks - 1 - blockIdx.x / a.heads;
+    // query blocks of one head run back to back (its K/V pages stay in L2); within a head the
+    // late blocks, which see the most KV pages, go first
+    const int head = blockIdx.x / q_blocks;
+    const int qb = q_blocks - 1 - blockIdx.x % q_blocks;
     const int q0 = qb * AT_BM;
     // pages this query block can see: kv position p is visible to row R iff p <= R + delta
     int n = a.num_tiles;
@@ -82,11 +86,11 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_mbar_init(&bars[B_VFULL + i], 1);
             tc_mbar_init(&bars[B_VEMPTY + i], 1);
             tc_mbar_init(&bars[B_SFULL + i], 1);
-            tc_mbar_init(&bars[B_SEMPTY + i], 4);
+            tc_mbar_init(&bars[B_SEMPTY + i], 8);
             tc_mbar_init(&bars[B_PVFULL + i], 1);
-            tc_mbar_init(&bars[B_PVEMPTY + i], 4);
+            tc_mbar_init(&bars[B_PVEMPTY + i], 8);
         }
-        tc_mbar_init(&bars[B_PFULL], 4);
+        tc_mbar_init(&bars[B_PFULL], 8);
         *abort_flag = 0;
         tc_fence_barrier_init();
     }
@@ -177,22 +181,26 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
         }
     } else {
-        const int q = warp & 3;
-        const int r = q * 32 + lane;               // row inside the query block == TMEM lane
+        constexpr int BH = BN / 2;                   // score columns per thread
+        constexpr int CW = BH >= 32 ? 32 : 16;       // columns per TMEM load
+        constexpr int OH = AT_D / 2;                 // output columns per thread
+        const int q = warp & 3;                      // TMEM lane quadrant this warp may read
+        const int half = (warp - 2) >> 2;            // which half of the columns this thread owns
+        const int r = q * 32 + lane;                 // row inside the query block == TMEM lane
         const int R = q0 + r;
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
         const float sl = a.scale * 1.4426950408889634f;
         float m_run = a.m_init * 1.4426950408889634f;          // running max, log2 domain
-        float l_run = a.l_init;
+        float l_run = half == 0 ? a.l_init : 0.f;              // this thread's share of the running sum
         float alpha_prev = 1.f;
-        float o[AT_D];
+        float o[OH];
 #pragma unroll
-        for (int i = 0; i < AT_D; ++i) o[i] = 0.f;
+        for (int i = 0; i < OH; ++i) o[i] = 0.f;
         const long long limit = (long long)R + a.causal_delta;  // last visible kv position
         bool ok = true;
 
         auto fold_pv = [&](int jp, float alpha) {
-            const uint32_t base = tmem_pv + (jp & 1) * 128 + lane_off;
+            const uint32_t base = tmem_pv + (jp & 1) * 128 + lane_off + half * OH;
             uint32_t va[32], vb[32];
             tc_tmem_ld32(base, va);
             tc_tmem_ld_wait();
@@ -200,37 +208,27 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __fmaf_rn(o[i], alpha, __uint_as_float(va[i]));
             tc_tmem_ld_wait();
-            tc_tmem_ld32(base + 64, va);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[32 + i] = __fmaf_rn(o[32 + i], alpha, __uint_as_float(vb[i]));
-            tc_tmem_ld_wait();
-            tc_tmem_ld32(base + 96, vb);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[64 + i] = __fmaf_rn(o[64 + i], alpha, __uint_as_float(va[i]));
-            tc_tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[96 + i] = __fmaf_rn(o[96 + i], alpha, __uint_as_float(vb[i]));
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&bars[B_PVEMPTY + (jp & 1)]);
         };
-
-        // running-max update of one 32-column chunk (raw scores; scaled afterwards)
-        auto chunk_max = [&](const uint32_t (&v)[32], long long c_abs, bool need_mask, float& mx) {
+        auto chunk_max = [&](const uint32_t (&v)[CW], long long c_abs, bool need_mask, float& mx) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < CW; ++i) {
                 float t = __uint_as_float(v[i]) * sl;
                 if (need_mask && c_abs + i > limit) t = -INFINITY;
                 mx = fmaxf(mx, t);
             }
         };
-        // probabilities of one 32-column chunk -> packed f16 in shared memory, partial row sum
-        auto chunk_prob = [&](const uint32_t (&v)[32], int c0, long long c_abs, bool need_mask, float m_new,
+        // probabilities of one chunk -> packed f16 in shared memory, partial row sum
+        auto chunk_prob = [&](const uint32_t (&v)[CW], int c0, long long c_abs, bool need_mask, float m_new,
                               float& lsum) {
-            uint32_t packed[16];
+            uint32_t packed[CW / 2];
             float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
+            for (int i = 0; i < CW; i += 2) {
                 float p0 = at_ex2(__fmaf_rn(__uint_as_float(v[i]), sl, -m_new));
                 float p1 = at_ex2(__fmaf_rn(__uint_as_float(v[i + 1]), sl, -m_new));
                 if (need_mask) {
@@ -243,11 +241,11 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             }
             lsum += s0 + s1;
-            // 32 columns = four 16-byte chunks of this row inside block (c0 / 64)
+            // CW columns = CW/8 16-byte chunks of this row inside block (c0 / 64)
             uint8_t* blk = sP + (c0 >> 6) * (AT_BM * 128) + r * 128;
             const int chunk0 = (c0 & 63) >> 3;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < CW / 8; ++c) {
                 const int phys = (chunk0 + c) ^ (r & 7);
                 *reinterpret_cast<uint4*>(blk + phys * 16) =
                     make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
@@ -257,61 +255,69 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int j = 0; j < n; ++j) {
             const int s = j & 1;
             const uint32_t ph = (j >> 1) & 1;
-            if (!tc_mbar_wait(&bars[B_SFULL + s], ph, abort_flag, st, 31)) { ok = false; break; }
+            // after a failed wait the thread keeps iterating (without touching TMEM) so that the
+            // named barriers below are still reached by all 256 softmax threads
+            if (ok && !tc_mbar_wait(&bars[B_SFULL + s], ph, abort_flag, st, 31)) ok = false;
             tc_fence_after_sync();
-            const long long col0 = (long long)j * BN;
-            const bool need_mask = a.causal && (col0 + BN - 1 > limit);
-            const uint32_t sbase = tmem_s + s * 128 + lane_off;
-            // pass 1: row maximum of the scaled (masked) scores; TMEM loads run one chunk ahead
+            const int cb = half * BH;                               // first column of this thread
+            const long long col0 = (long long)j * BN + cb;
+            const bool need_mask = a.causal && ((long long)j * BN + BN - 1 > limit);
+            const uint32_t sbase = tmem_s + s * 128 + lane_off + cb;
+            // pass 1: maximum of the scaled (masked) scores of this thread's columns
             float mx = -INFINITY;
-            {
-                uint32_t va[32], vb[32];
-                tc_tmem_ld32(sbase, va);
+            if (ok) {
+                uint32_t va[CW], vb[CW];
+                tc_tmem_ld<CW>(sbase, va);
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 64) {
+                for (int c0 = 0; c0 < BH; c0 += 2 * CW) {
                     tc_tmem_ld_wait();
-                    if (c0 + 32 < BN) tc_tmem_ld32(sbase + c0 + 32, vb);
+                    if (c0 + CW < BH) tc_tmem_ld<CW>(sbase + c0 + CW, vb);
                     chunk_max(va, col0 + c0, need_mask, mx);
-                    if (c0 + 32 < BN) {
+                    if (c0 + CW < BH) {
                         tc_tmem_ld_wait();
-                        if (c0 + 64 < BN) tc_tmem_ld32(sbase + c0 + 64, va);
-                        chunk_max(vb, col0 + c0 + 32, need_mask, mx);
+                        if (c0 + 2 * CW < BH) tc_tmem_ld<CW>(sbase + c0 + 2 * CW, va);
+                        chunk_max(vb, col0 + c0 + CW, need_mask, mx);
                     }
                 }
             }
+            // the two threads of a row agree on the page maximum
+            float* slot = xm + (j & 1) * (2 * AT_BM);
+            slot[half * AT_BM + r] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(mx, slot[(half ^ 1) * AT_BM + r]);
             const float m_new = fmaxf(m_run, mx);
             const float alpha = at_ex2(m_run - m_new);
-            if (j > 0) {
+            if (j > 0 && ok) {
                 // the previous P V product is complete: P may be overwritten, the product folded in
                 const int sp = (j - 1) & 1;
-                if (!tc_mbar_wait(&bars[B_PVFULL + sp], ((j - 1) >> 1) & 1, abort_flag, st, 32)) { ok = false; break; }
+                if (!tc_mbar_wait(&bars[B_PVFULL + sp], ((j - 1) >> 1) & 1, abort_flag, st, 32)) ok = false;
                 tc_fence_after_sync();
             }
             // pass 2: probabilities -> f16 -> shared memory (K-major, 128-byte swizzle), row sum in f32
             float lsum = 0.f;
-            {
-                uint32_t va[32], vb[32];
-                tc_tmem_ld32(sbase, va);
+            if (ok) {
+                uint32_t va[CW], vb[CW];
+                tc_tmem_ld<CW>(sbase, va);
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 64) {
+                for (int c0 = 0; c0 < BH; c0 += 2 * CW) {
                     tc_tmem_ld_wait();
-                    if (c0 + 32 < BN) tc_tmem_ld32(sbase + c0 + 32, vb);
-                    chunk_prob(va, c0, col0 + c0, need_mask, m_new, lsum);
-                    if (c0 + 32 < BN) {
+                    if (c0 + CW < BH) tc_tmem_ld<CW>(sbase + c0 + CW, vb);
+                    chunk_prob(va, cb + c0, col0 + c0, need_mask, m_new, lsum);
+                    if (c0 + CW < BH) {
                         tc_tmem_ld_wait();
-                        if (c0 + 64 < BN) tc_tmem_ld32(sbase + c0 + 64, va);
-                        chunk_prob(vb, c0 + 32, col0 + c0 + 32, need_mask, m_new, lsum);
+                        if (c0 + 2 * CW < BH) tc_tmem_ld<CW>(sbase + c0 + 2 * CW, va);
+                        chunk_prob(vb, cb + c0 + CW, col0 + c0 + CW, need_mask, m_new, lsum);
                     }
                 }
             }
             tc_fence_before_sync();          // S buffer fully read
             tc_fence_proxy_async();          // P stores visible to the tensor-core (async) proxy
             __syncwarp();
-            if (lane == 0) {
+            if (lane == 0 && ok) {
                 tc_mbar_arrive(&bars[B_SEMPTY + s]);
                 tc_mbar_arrive(&bars[B_PFULL]);
             }
-            if (j > 0) fold_pv(j - 1, alpha_prev);
+            if (j > 0 && ok) fold_pv(j - 1, alpha_prev);
             l_run = l_run * alpha + lsum;
             m_run = m_new;
             alpha_prev = alpha;
@@ -325,12 +331,16 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 ok = false;
             }
         }
-        if (ok && R < a.seq_q) {
-            const float inv = 1.0f / l_run;
+        // total row sum = the two partial sums (same rescaling history on both threads)
+        xl[half * AT_BM + r] = l_run;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        const float l_tot = xl[r] + xl[AT_BM + r];
+        if (ok && *abort_flag == 0 && R < a.seq_q) {
+            const float inv = 1.0f / l_tot;
             __half* dst = reinterpret_cast<__half*>(a.arena) + a.o_off + (int64_t)R * a.o_row_stride +
-                          (int64_t)head * a.o_head_stride;
+                          (int64_t)head * a.o_head_stride + half * OH;
 #pragma unroll
-            for (int c = 0; c < AT_D; c += 8) {
+            for (int c = 0; c < OH; c += 8) {
                 uint4 w;
                 __half2* h = reinterpret_cast<__half2*>(&w);
 #pragma unroll
@@ -347,7 +357,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 template <int BN>
 static int launch_attn(ktb_ctx* ctx, const ktb_attn_args& a, const CUtensorMap& mq, const CUtensorMap& mk,
                        const CUtensorMap& mv) {
-    constexpr size_t SMEM = AT_Q_BYTES + 4 * (size_t)(BN * AT_D * 2) + (size_t)(BN < 64 ? 64 : BN) * AT_BM * 2 + 1024 + 512;
+    constexpr size_t SMEM = AT_Q_BYTES + 4 * (size_t)(BN * AT_D * 2) + (size_t)(BN < 64 ? 64 : BN) * AT_BM * 2 + 1024 + 512 + 6 * AT_BM * 4;
     static bool attr_set = false;
     if (!attr_set) {
         KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));

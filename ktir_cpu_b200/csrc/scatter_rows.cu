@@ -97,63 +97,25 @@ static __device__ __forceinline__ void sc_store_row(void* arena, const ktb_row_o
     }
 }
 
-// One warp moves one entry: gathers every input row, runs the program, writes the output row.
-template <int V>
-static __device__ __forceinline__ void sc_do_entry(const ktb_rows_args& a, int64_t e, int64_t dst_addr, int lane,
-                                                   ktb_status* st) {
-    const int64_t t = e / a.tile_rows;
-    const int pos = (int)(e - t * a.tile_rows);
-    int64_t in_addr[KTB_ROWS_MAX_IN];
-    bool ok = dst_addr >= 0;
-    for (int k = 0; k < a.n_in; ++k) {
-        in_addr[k] = a.in[k].alias_dst ? dst_addr : sc_row_addr(a.arena, a.in[k], t, pos, st);
-        ok = ok && in_addr[k] >= 0;
-    }
-    if (!ok) return;
-    for (int col = lane * V; col < a.cols; col += 32 * V) {
-        float regs[KTB_VM_REGS][V];
-        for (int k = 0; k < a.n_in; ++k) {
-            float x[V];
-            sc_load_row<V>(a.arena, a.in[k], in_addr[k], col, a.cols, x);
-#pragma unroll
-            for (int v = 0; v < V; ++v) regs[k][v] = x[v];
-        }
-        float out[V];
-        ktb_vm_run<V>(a.program, regs, out);
-        sc_store_row<V>(a.arena, a.out, dst_addr, col, a.cols, out);
-    }
-}
-
-// ---- direct destination: every entry is independent ------------------------------------------
-template <int V>
-__global__ void __launch_bounds__(256) ktb_rows_program_kernel(const ktb_rows_args a, ktb_status* st) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int64_t E = a.n_tiles * a.tile_rows;
-    for (int64_t e = warp; e < E; e += n_warps) {
-        const int64_t t = e / a.tile_rows;
-        const int pos = (int)(e - t * a.tile_rows);
-        sc_do_entry<V>(a, e, sc_row_addr(a.arena, a.out, t, pos, st), lane, st);
-    }
-}
-
-// ---- grouped entry processing: G entries per warp in flight at once -------------------------
-// Row addresses of all entries are resolved first (independent index loads), then all rows are
-// loaded, then programs run and rows are stored: the dependent index -> row chain of one entry
-// overlaps with the chains of the others.
+// G entries per warp in flight at once.  Row addresses of all entries are resolved first
+// (independent index loads), then all rows are loaded, then programs run and rows are stored, so
+// the dependent index -> row chain of one entry overlaps with the chains of the others.
+// Everything is statically indexed (registers only).
 template <int V, int G>
-static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const int64_t (&ent)[G],
+static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const int32_t (&ent)[G],
                                                    const int64_t (&dst)[G], int n, int lane, ktb_status* st) {
     int64_t in_addr[G][KTB_ROWS_MAX_IN];
     bool ok[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         ok[g] = g < n && dst[g] >= 0;
-        if (g < n) {
-            const int64_t t = ent[g] / a.tile_rows;
-            const int pos = (int)(ent[g] - t * a.tile_rows);
-            for (int k = 0; k < a.n_in; ++k) {
+        const uint32_t e = g < n ? (uint32_t)ent[g] : 0u;
+        const uint32_t t = e / (uint32_t)a.tile_rows;
+        const int pos = (int)(e - t * (uint32_t)a.tile_rows);
+#pragma unroll
+        for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+            in_addr[g][k] = 0;
+            if (g < n && k < a.n_in) {
                 in_addr[g][k] = a.in[k].alias_dst ? dst[g] : sc_row_addr(a.arena, a.in[k], t, pos, st);
                 ok[g] = ok[g] && in_addr[g][k] >= 0;
             }
@@ -163,19 +125,47 @@ static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const
         float x[G][KTB_ROWS_MAX_IN][V];
 #pragma unroll
         for (int g = 0; g < G; ++g)
-            if (ok[g])
-                for (int k = 0; k < a.n_in; ++k) sc_load_row<V>(a.arena, a.in[k], in_addr[g][k], col, a.cols, x[g][k]);
+#pragma unroll
+            for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) x[g][k][v] = 0.f;
+                if (ok[g] && k < a.n_in) sc_load_row<V>(a.arena, a.in[k], in_addr[g][k], col, a.cols, x[g][k]);
+            }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             if (!ok[g]) continue;
-            float regs[KTB_VM_REGS][V];
-            for (int k = 0; k < a.n_in; ++k)
-#pragma unroll
-                for (int v = 0; v < V; ++v) regs[k][v] = x[g][k][v];
             float out[V];
-            ktb_vm_run<V>(a.program, regs, out);
+            ktb_vm_run_sel<V, KTB_ROWS_MAX_IN>(a.program, x[g], out);
             sc_store_row<V>(a.arena, a.out, dst[g], col, a.cols, out);
         }
+    }
+}
+
+// ---- direct destination: every entry is independent ------------------------------------------
+template <int V>
+__global__ void __launch_bounds__(256) ktb_rows_program_kernel(const ktb_rows_args a, ktb_status* st) {
+    constexpr int G = 4;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t E = a.n_tiles * a.tile_rows;
+    for (int64_t e0 = warp * G; e0 < E; e0 += n_warps * G) {
+        int32_t ent[G];
+        int64_t dst[G];
+        int n = 0;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            ent[g] = 0;
+            dst[g] = -1;
+            if (e0 + g < E) {
+                const uint32_t e = (uint32_t)(e0 + g);
+                const uint32_t t = e / (uint32_t)a.tile_rows;
+                ent[g] = (int32_t)e;
+                dst[g] = sc_row_addr(a.arena, a.out, t, (int)(e - t * (uint32_t)a.tile_rows), st);
+                n = g + 1;
+            }
+        }
+        sc_do_group<V, G>(a, ent, dst, n, lane, st);
     }
 }
 
@@ -213,75 +203,70 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const ktb_rows
 }
 
 // ---- step 2: owner-computes ordered apply ------------------------------------------------------
-#define SC_THREADS 1024
+// Destination rows are partitioned over CTAs; inside a CTA a row belongs to warp (row % 32).  A
+// CTA scans the owner bytes of all entries in order and appends its own entries to a list
+// (ordered compaction).  Each warp then walks the list in order and applies the entries of its
+// rows: updates of one row are applied by one warp in tile order, different rows never interact,
+// so no barrier and no atomic is needed while applying.
+#define SC_THREADS 512
 #define SC_WARPS (SC_THREADS / 32)
 #define SC_STEP (SC_THREADS * 16)   // entries examined per scan step (16 owner bytes per thread)
-#define SC_LCAP SC_STEP             // entries buffered per CTA before a batch is applied
-#define SC_MAX_OWN_ROWS 4096        // destination rows owned by one CTA (shared-memory counters)
+#define SC_LCAP SC_STEP             // entries buffered per CTA before the batch is applied
 #define SC_GROUP 4
 
 template <int V>
 __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const ktb_rows_args a, int rows_per_owner,
                                                                            ktb_status* st) {
     extern __shared__ uint8_t sc_smem[];
-    int32_t* list_e = reinterpret_cast<int32_t*>(sc_smem);                  // [SC_LCAP]
-    uint16_t* list_r = reinterpret_cast<uint16_t*>(list_e + SC_LCAP);       // [SC_LCAP]
-    uint16_t* list_k = list_r + SC_LCAP;                                    // [SC_LCAP] rank inside the batch
-    uint16_t* cnt = list_k + SC_LCAP;                                       // [SC_MAX_OWN_ROWS]
+    int32_t* list_e = reinterpret_cast<int32_t*>(sc_smem);                  // [SC_LCAP] entry ids
+    int32_t* list_r = list_e + SC_LCAP;                                     // [SC_LCAP] destination row ids
     __shared__ int32_t warp_tot[SC_WARPS];
-    __shared__ int32_t s_len, s_maxrank;
+    __shared__ int32_t s_len;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int64_t E = a.n_tiles * a.tile_rows;
     const uint8_t* owner = reinterpret_cast<const uint8_t*>(a.dev_rowid_scratch + E);
-    const uint32_t me = blockIdx.x;
-    const uint32_t me4 = me * 0x01010101u;
-    const int32_t own_lo = (int32_t)me * rows_per_owner;
-    for (int i = tid; i < rows_per_owner; i += SC_THREADS) cnt[i] = 0;
-    if (tid == 0) { s_len = 0; s_maxrank = 0; }
+    const uint32_t me4 = (uint32_t)blockIdx.x * 0x01010101u;
+    if (tid == 0) s_len = 0;
     __syncthreads();
 
     auto apply_batch = [&]() {
         const int len = s_len;
-        // ranks in list order (warp 0): entries of one row get 0, 1, 2, ... in tile order
-        if (wid == 0) {
-            int mr = 0;
-            for (int i0 = 0; i0 < len; i0 += 32) {
-                const int i = i0 + lane;
-                const bool act = i < len;
-                const unsigned amask = __ballot_sync(0xffffffffu, act);
-                if (act) {
-                    const int r = list_r[i];
-                    const unsigned m = __match_any_sync(amask, r);
-                    const int k = cnt[r] + __popc(m & ((1u << lane) - 1));
-                    list_k[i] = (uint16_t)k;
-                    mr = max(mr, k);
-                    __syncwarp(amask);
-                    if ((m >> lane) == 1u) cnt[r] = (uint16_t)(cnt[r] + __popc(m));
+        for (int i0 = 0; i0 < len; i0 += 32) {
+            const int i = i0 + lane;
+            const int32_t r = i < len ? list_r[i] : -1;
+            const int32_t e = i < len ? list_e[i] : 0;
+            unsigned mask = __ballot_sync(0xffffffffu, r >= 0 && (r & (SC_WARPS - 1)) == wid);
+            while (mask) {
+                int32_t ent[SC_GROUP];
+                int64_t dst[SC_GROUP];
+                int32_t rows[SC_GROUP];
+                int n = 0;
+#pragma unroll
+                for (int g = 0; g < SC_GROUP; ++g) {
+                    ent[g] = 0;
+                    dst[g] = -1;
+                    rows[g] = -1;
+                    if (mask && n == g) {
+                        const int src = __ffs(mask) - 1;
+                        const int32_t rr = __shfl_sync(0xffffffffu, r, src);
+                        const int32_t ee = __shfl_sync(0xffffffffu, e, src);
+                        bool clash = false;     // a second update of a row must wait for the first
+#pragma unroll
+                        for (int h = 0; h < SC_GROUP; ++h) clash = clash || (h < g && rows[h] == rr);
+                        if (!clash) {
+                            rows[g] = rr;
+                            ent[g] = ee;
+                            dst[g] = a.dst_row0 + (int64_t)rr * a.out.idx_mult;
+                            mask &= mask - 1;
+                            n = g + 1;
+                        }
+                    }
                 }
-                __syncwarp();
+                sc_do_group<V, SC_GROUP>(a, ent, dst, n, lane, st);
             }
-            for (int d = 16; d; d >>= 1) mr = max(mr, __shfl_xor_sync(0xffffffffu, mr, d));
-            if (lane == 0) s_maxrank = mr;
         }
         __syncthreads();
-        const int maxrank = s_maxrank;
-        for (int round = 0; round <= maxrank; ++round) {
-            int64_t ent[SC_GROUP], dst[SC_GROUP];
-            int n = 0;
-            for (int i = wid; i < len; i += SC_WARPS) {
-                if (list_k[i] != round) continue;
-                ent[n] = list_e[i];
-                dst[n] = a.dst_row0 + ((int64_t)own_lo + list_r[i]) * a.out.idx_mult;
-                if (++n == SC_GROUP) {
-                    sc_do_group<V, SC_GROUP>(a, ent, dst, n, lane, st);
-                    n = 0;
-                }
-            }
-            if (n) sc_do_group<V, SC_GROUP>(a, ent, dst, n, lane, st);
-            __syncthreads();
-        }
-        for (int i = tid; i < len; i += SC_THREADS) cnt[list_r[i]] = 0;
         if (tid == 0) s_len = 0;
         __syncthreads();
     };
@@ -327,7 +312,7 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
         for (int j = 0; j < 16; ++j)
             if (hit[j >> 2] & (0xffu << (8 * (j & 3)))) {
                 list_e[at] = (int32_t)(e0 + j);
-                list_r[at] = (uint16_t)(a.dev_rowid_scratch[e0 + j] - own_lo);
+                list_r[at] = a.dev_rowid_scratch[e0 + j];
                 ++at;
             }
         __syncthreads();
@@ -341,12 +326,14 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
 static int check_rows_args(ktb_ctx* ctx, const ktb_rows_args& a, const char* who) {
     const ktb_vm_program& p = a.program;
     if (a.n_in < 1 || a.n_in > KTB_ROWS_MAX_IN || p.n_in != a.n_in || p.n_ops < 0 || p.n_ops > KTB_VM_MAX_OPS ||
-        p.result_reg < 0 || p.result_reg >= KTB_VM_REGS)
+        p.result_reg < 0 || p.result_reg >= p.n_in + p.n_ops + (p.n_ops == 0 ? 1 : 0))
         return ktb_fail(ctx, KTB_E_ARG, who, "bad program header");
+    if (p.n_ops > KTB_VM_SEL_OPS) return ktb_fail(ctx, KTB_E_UNSUPPORTED, who, "row programs are limited to 8 ops");
     for (int i = 0; i < p.n_ops; ++i) {
         const ktb_vm_op& o = p.ops[i];
-        if ((o.opcode & 0xff) >= KTB_VM_NOPS || o.dst < 0 || o.dst >= KTB_VM_REGS || o.a < 0 || o.a >= KTB_VM_REGS ||
-            o.b < 0 || o.b >= KTB_VM_REGS || o.c < 0 || o.c >= KTB_VM_REGS)
+        // single-assignment form: op i defines register n_in + i and reads earlier ones
+        if ((o.opcode & 0xff) >= KTB_VM_NOPS || o.dst != p.n_in + i || o.a < 0 || o.a >= o.dst || o.b < 0 ||
+            o.b >= o.dst || o.c < 0 || o.c >= o.dst)
             return ktb_fail(ctx, KTB_E_ARG, who, "bad program op");
     }
     for (int k = 0; k <= a.n_in; ++k) {
@@ -386,19 +373,17 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (a.out.idx_mult <= 0 || a.dst_rows <= 0) return ktb_fail(ctx, KTB_E_ARG, "scatter_rows", "bad destination row geometry");
     if (a.dst_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "too many destination rows");
     if (a.n_tiles == 0) return KTB_OK;
-    // destination rows are split over at most 254 owner CTAs of at most SC_MAX_OWN_ROWS rows each
-    int64_t rpo = (a.dst_rows + ctx->sm_count - 1) / ctx->sm_count;
+    // destination rows are split evenly over one owner CTA per SM (at most 254 owners)
+    int64_t n_own = ctx->sm_count < 254 ? ctx->sm_count : 254;
+    int64_t rpo = (a.dst_rows + n_own - 1) / n_own;
     if (rpo < 1) rpo = 1;
-    if (rpo > SC_MAX_OWN_ROWS) rpo = SC_MAX_OWN_ROWS;
     const int64_t owners = (a.dst_rows + rpo - 1) / rpo;
-    if (owners >= SC_NO_OWNER)
-        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "destination has more than 254 x 4096 rows");
     int64_t prep_blocks = a.n_tiles < (int64_t)ctx->sm_count * 16 ? a.n_tiles : (int64_t)ctx->sm_count * 16;
     const size_t smem = (size_t)a.tile_rows * sizeof(int64_t);
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
     ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
-    const size_t asmem = (size_t)SC_LCAP * 8 + (size_t)SC_MAX_OWN_ROWS * 2;
+    const size_t asmem = (size_t)SC_LCAP * 8;
     static bool attr_set = false;
     if (!attr_set) {
         KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem));

@@ -109,3 +109,56 @@ static __device__ __forceinline__ void ktb_store_vec(void* base, int64_t elem_of
         }
     }
 }
+
+// Register-only evaluation for programs in single-assignment form (op i writes register
+// n_in + i, which is how the host emits them).  Operands are fetched with predicated moves over
+// the registers defined so far, so nothing is indexed dynamically and nothing lives in local
+// memory.  Used where a warp runs the program on 4-element slices (row gather / scatter).
+#define KTB_VM_SEL_OPS 8
+template <int V, int NIN>
+static __device__ __forceinline__ void ktb_vm_run_sel(const ktb_vm_program& prog, const float (&in)[NIN][V],
+                                                      float (&out)[V]) {
+    float r[NIN + KTB_VM_SEL_OPS][V];
+#pragma unroll
+    for (int k = 0; k < NIN; ++k)
+#pragma unroll
+        for (int v = 0; v < V; ++v) r[k][v] = in[k][v];
+    const int n_in = prog.n_in;
+#pragma unroll
+    for (int i = 0; i < KTB_VM_SEL_OPS; ++i) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) r[NIN + i][v] = 0.f;
+        if (i < prog.n_ops) {
+            const ktb_vm_op op = prog.ops[i];
+            const int ia = op.a < n_in ? op.a : op.a - n_in + NIN;
+            const int ib = op.b < n_in ? op.b : op.b - n_in + NIN;
+            const int ic = op.c < n_in ? op.c : op.c - n_in + NIN;
+            float av[V], bv[V], cv[V];
+#pragma unroll
+            for (int v = 0; v < V; ++v) av[v] = bv[v] = cv[v] = 0.f;
+#pragma unroll
+            for (int s = 0; s < NIN + i; ++s) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    av[v] = s == ia ? r[s][v] : av[v];
+                    bv[v] = s == ib ? r[s][v] : bv[v];
+                    cv[v] = s == ic ? r[s][v] : cv[v];
+                }
+            }
+            const int code = op.opcode & 0xff;
+            const bool r16 = (op.opcode & KTB_VM_ROUND16) != 0;
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                const float x = ktb_vm_apply(code, av[v], bv[v], cv[v], op.imm);
+                r[NIN + i][v] = r16 ? ktb_round16(x) : x;
+            }
+        }
+    }
+    const int ir = prog.result_reg < n_in ? prog.result_reg : prog.result_reg - n_in + NIN;
+#pragma unroll
+    for (int v = 0; v < V; ++v) out[v] = 0.f;
+#pragma unroll
+    for (int s = 0; s < NIN + KTB_VM_SEL_OPS; ++s)
+#pragma unroll
+        for (int v = 0; v < V; ++v) out[v] = s == ir ? r[s][v] : out[v];
+}
