@@ -98,12 +98,18 @@ static __device__ __forceinline__ void sc_store_row(void* arena, const ktb_row_o
 }
 
 // G entries per warp in flight at once.  Row addresses of all entries are resolved first
-// (independent index loads), then all rows are loaded, then programs run and rows are stored, so
-// the dependent index -> row chain of one entry overlaps with the chains of the others.
-// Everything is statically indexed (registers only).
-template <int V, int G>
+// (independent index loads), then all rows are loaded, then the program runs per entry and the
+// rows are stored, so the dependent index -> row chain of one entry overlaps with the chains of
+// the others.  `vm` is this thread's slot of the shared-memory register file.
+// PROG selects how the row program is evaluated: the general register program, a plain copy of
+// input 0, or out = round16(in[acc] + round16(in[1 - acc] * c)) with acc = 0 / 1 (the f16
+// scaled-accumulate of a read-modify-write scatter), the latter two without any decoding.
+enum { SC_PROG_VM = 0, SC_PROG_COPY = 1, SC_PROG_AXPY0 = 2, SC_PROG_AXPY1 = 3 };
+
+template <int V, int G, int PROG>
 static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const int32_t (&ent)[G],
-                                                   const int64_t (&dst)[G], int n, int lane, ktb_status* st) {
+                                                   const int64_t (&dst)[G], int n, int lane, ktb_status* st,
+                                                   float4* vm, int vm_stride) {
     int64_t in_addr[G][KTB_ROWS_MAX_IN];
     bool ok[G];
 #pragma unroll
@@ -135,16 +141,34 @@ static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const
         for (int g = 0; g < G; ++g) {
             if (!ok[g]) continue;
             float out[V];
-            ktb_vm_run_sel<V, KTB_ROWS_MAX_IN>(a.program, x[g], out);
+            if (PROG == SC_PROG_COPY) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) out[v] = x[g][0][v];
+            } else if (PROG == SC_PROG_AXPY0 || PROG == SC_PROG_AXPY1) {
+                constexpr int ACC = PROG == SC_PROG_AXPY0 ? 0 : 1;
+                const float c = a.program.ops[0].imm;
+#pragma unroll
+                for (int v = 0; v < V; ++v) out[v] = ktb_round16(x[g][ACC][v] + ktb_round16(x[g][1 - ACC][v] * c));
+            } else {
+#pragma unroll
+                for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+                    vm[k * vm_stride] = make_float4(x[g][k][0], V > 1 ? x[g][k][1 % V] : 0.f,
+                                                    V > 1 ? x[g][k][2 % V] : 0.f, V > 1 ? x[g][k][3 % V] : 0.f);
+                const float4 res = ktb_vm_run_smem4(a.program, vm, vm_stride);
+                const float rv[4] = {res.x, res.y, res.z, res.w};
+#pragma unroll
+                for (int v = 0; v < V; ++v) out[v] = rv[v];
+            }
             sc_store_row<V>(a.arena, a.out, dst[g], col, a.cols, out);
         }
     }
 }
 
 // ---- direct destination: every entry is independent ------------------------------------------
-template <int V>
-__global__ void __launch_bounds__(256) ktb_rows_program_kernel(const ktb_rows_args a, ktb_status* st) {
+template <int V, int PROG>
+__global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_constant__ ktb_rows_args a, ktb_status* st) {
     constexpr int G = 4;
+    extern __shared__ float4 rp_vm[];                 // [KTB_VM_REGS][blockDim.x] register file
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -165,7 +189,7 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const ktb_rows_ar
                 n = g + 1;
             }
         }
-        sc_do_group<V, G>(a, ent, dst, n, lane, st);
+        sc_do_group<V, G, PROG>(a, ent, dst, n, lane, st, rp_vm + threadIdx.x, blockDim.x);
     }
 }
 
@@ -173,7 +197,7 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const ktb_rows_ar
 // Scratch layout: int32 row id per entry (-1 = dropped), then one owner byte per entry (255 = none).
 #define SC_NO_OWNER 255
 
-__global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const ktb_rows_args a, int rows_per_owner,
+__global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_constant__ ktb_rows_args a, int rows_per_owner,
                                                                   ktb_status* st) {
     extern __shared__ int64_t s_addr[];      // [tile_rows]
     const int64_t E = a.n_tiles * a.tile_rows;
@@ -214,12 +238,13 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const ktb_rows
 #define SC_LCAP SC_STEP             // entries buffered per CTA before the batch is applied
 #define SC_GROUP 4
 
-template <int V>
-__global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const ktb_rows_args a, int rows_per_owner,
+template <int V, int PROG>
+__global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a, int rows_per_owner,
                                                                            ktb_status* st) {
     extern __shared__ uint8_t sc_smem[];
     int32_t* list_e = reinterpret_cast<int32_t*>(sc_smem);                  // [SC_LCAP] entry ids
     int32_t* list_r = list_e + SC_LCAP;                                     // [SC_LCAP] destination row ids
+    float4* vm = reinterpret_cast<float4*>(list_r + SC_LCAP) + threadIdx.x;  // [KTB_VM_REGS][SC_THREADS]
     __shared__ int32_t warp_tot[SC_WARPS];
     __shared__ int32_t s_len;
 
@@ -263,7 +288,7 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
                         }
                     }
                 }
-                sc_do_group<V, SC_GROUP>(a, ent, dst, n, lane, st);
+                sc_do_group<V, SC_GROUP, PROG>(a, ent, dst, n, lane, st, vm, SC_THREADS);
             }
         }
         __syncthreads();
@@ -323,17 +348,34 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
     if (s_len > 0) apply_batch();
 }
 
+// Recognise the two row programs that have a decoded fast path.
+static int sc_classify(const ktb_rows_args& a) {
+    const ktb_vm_program& p = a.program;
+    if (p.n_ops == 0 && p.result_reg == 0) return SC_PROG_COPY;
+    if (a.n_in == 2 && p.n_ops == 3 && (p.ops[0].opcode & 0xff) == KTB_VM_CONST &&
+        p.ops[1].opcode == (KTB_VM_MUL | KTB_VM_ROUND16) && p.ops[2].opcode == (KTB_VM_ADD | KTB_VM_ROUND16) &&
+        p.result_reg == p.ops[2].dst) {
+        const int creg = p.ops[0].dst, mreg = p.ops[1].dst;
+        int scaled = -1;
+        if (p.ops[1].a == creg && p.ops[1].b < 2) scaled = p.ops[1].b;
+        if (p.ops[1].b == creg && p.ops[1].a < 2) scaled = p.ops[1].a;
+        int acc = -1;
+        if (p.ops[2].a == mreg && p.ops[2].b < 2) acc = p.ops[2].b;
+        if (p.ops[2].b == mreg && p.ops[2].a < 2) acc = p.ops[2].a;
+        if (scaled >= 0 && acc >= 0 && scaled != acc) return acc == 0 ? SC_PROG_AXPY0 : SC_PROG_AXPY1;
+    }
+    return SC_PROG_VM;
+}
+
 static int check_rows_args(ktb_ctx* ctx, const ktb_rows_args& a, const char* who) {
     const ktb_vm_program& p = a.program;
     if (a.n_in < 1 || a.n_in > KTB_ROWS_MAX_IN || p.n_in != a.n_in || p.n_ops < 0 || p.n_ops > KTB_VM_MAX_OPS ||
-        p.result_reg < 0 || p.result_reg >= p.n_in + p.n_ops + (p.n_ops == 0 ? 1 : 0))
+        p.result_reg < 0 || p.result_reg >= KTB_VM_REGS)
         return ktb_fail(ctx, KTB_E_ARG, who, "bad program header");
-    if (p.n_ops > KTB_VM_SEL_OPS) return ktb_fail(ctx, KTB_E_UNSUPPORTED, who, "row programs are limited to 8 ops");
     for (int i = 0; i < p.n_ops; ++i) {
         const ktb_vm_op& o = p.ops[i];
-        // single-assignment form: op i defines register n_in + i and reads earlier ones
-        if ((o.opcode & 0xff) >= KTB_VM_NOPS || o.dst != p.n_in + i || o.a < 0 || o.a >= o.dst || o.b < 0 ||
-            o.b >= o.dst || o.c < 0 || o.c >= o.dst)
+        if ((o.opcode & 0xff) >= KTB_VM_NOPS || o.dst < 0 || o.dst >= KTB_VM_REGS || o.a < 0 || o.a >= KTB_VM_REGS ||
+            o.b < 0 || o.b >= KTB_VM_REGS || o.c < 0 || o.c >= KTB_VM_REGS)
             return ktb_fail(ctx, KTB_E_ARG, who, "bad program op");
     }
     for (int k = 0; k <= a.n_in; ++k) {
@@ -357,8 +399,18 @@ extern "C" int ktb_launch_rows_program(ktb_ctx* ctx, const ktb_rows_args* args) 
     int64_t blocks = (E + 7) / 8;
     const int64_t cap = (int64_t)ctx->sm_count * 16;
     if (blocks > cap) blocks = cap;
-    if (a.vector_ok) ktb_rows_program_kernel<4><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, ctx->dev_status);
-    else ktb_rows_program_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, ctx->dev_status);
+    const size_t vsmem = (size_t)KTB_VM_REGS * 256 * sizeof(float4);
+#define KTB_RP(V, P) ktb_rows_program_kernel<V, P><<<(unsigned)blocks, 256, vsmem, ctx->stream>>>(a, ctx->dev_status)
+    switch (sc_classify(a) * 2 + (a.vector_ok ? 1 : 0)) {
+        case SC_PROG_COPY * 2 + 1: KTB_RP(4, SC_PROG_COPY); break;
+        case SC_PROG_COPY * 2: KTB_RP(1, SC_PROG_COPY); break;
+        case SC_PROG_AXPY0 * 2 + 1: KTB_RP(4, SC_PROG_AXPY0); break;
+        case SC_PROG_AXPY1 * 2 + 1: KTB_RP(4, SC_PROG_AXPY1); break;
+        default:
+            if (a.vector_ok) KTB_RP(4, SC_PROG_VM);
+            else KTB_RP(1, SC_PROG_VM);
+    }
+#undef KTB_RP
     KTB_CHECK_LAUNCH(ctx, "ktb_rows_program_kernel");
     return KTB_OK;
 }
@@ -383,15 +435,23 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
     ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
-    const size_t asmem = (size_t)SC_LCAP * 8;
-    static bool attr_set = false;
-    if (!attr_set) {
-        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem));
-        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)asmem));
-        attr_set = true;
+    const size_t asmem = (size_t)SC_LCAP * 8 + (size_t)KTB_VM_REGS * SC_THREADS * sizeof(float4);
+#define KTB_SA(V, P)                                                                                              \
+    do {                                                                                                          \
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<V, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)asmem));                                                          \
+        ktb_scatter_apply_kernel<V, P><<<(unsigned)owners, SC_THREADS, asmem, ctx->stream>>>(a, (int)rpo, ctx->dev_status); \
+    } while (0)
+    switch (sc_classify(a) * 2 + (a.vector_ok ? 1 : 0)) {
+        case SC_PROG_COPY * 2 + 1: KTB_SA(4, SC_PROG_COPY); break;
+        case SC_PROG_COPY * 2: KTB_SA(1, SC_PROG_COPY); break;
+        case SC_PROG_AXPY0 * 2 + 1: KTB_SA(4, SC_PROG_AXPY0); break;
+        case SC_PROG_AXPY1 * 2 + 1: KTB_SA(4, SC_PROG_AXPY1); break;
+        default:
+            if (a.vector_ok) KTB_SA(4, SC_PROG_VM);
+            else KTB_SA(1, SC_PROG_VM);
     }
-    if (a.vector_ok) ktb_scatter_apply_kernel<4><<<(unsigned)owners, SC_THREADS, asmem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
-    else ktb_scatter_apply_kernel<1><<<(unsigned)owners, SC_THREADS, asmem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
+#undef KTB_SA
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_apply_kernel");
     return KTB_OK;
 }

@@ -110,55 +110,44 @@ static __device__ __forceinline__ void ktb_store_vec(void* base, int64_t elem_of
     }
 }
 
-// Register-only evaluation for programs in single-assignment form (op i writes register
-// n_in + i, which is how the host emits them).  Operands are fetched with predicated moves over
-// the registers defined so far, so nothing is indexed dynamically and nothing lives in local
-// memory.  Used where a warp runs the program on 4-element slices (row gather / scatter).
-#define KTB_VM_SEL_OPS 8
-template <int V, int NIN>
-static __device__ __forceinline__ void ktb_vm_run_sel(const ktb_vm_program& prog, const float (&in)[NIN][V],
-                                                      float (&out)[V]) {
-    float r[NIN + KTB_VM_SEL_OPS][V];
-#pragma unroll
-    for (int k = 0; k < NIN; ++k)
-#pragma unroll
-        for (int v = 0; v < V; ++v) r[k][v] = in[k][v];
-    const int n_in = prog.n_in;
-#pragma unroll
-    for (int i = 0; i < KTB_VM_SEL_OPS; ++i) {
-#pragma unroll
-        for (int v = 0; v < V; ++v) r[NIN + i][v] = 0.f;
-        if (i < prog.n_ops) {
-            const ktb_vm_op op = prog.ops[i];
-            const int ia = op.a < n_in ? op.a : op.a - n_in + NIN;
-            const int ib = op.b < n_in ? op.b : op.b - n_in + NIN;
-            const int ic = op.c < n_in ? op.c : op.c - n_in + NIN;
-            float av[V], bv[V], cv[V];
-#pragma unroll
-            for (int v = 0; v < V; ++v) av[v] = bv[v] = cv[v] = 0.f;
-#pragma unroll
-            for (int s = 0; s < NIN + i; ++s) {
-#pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    av[v] = s == ia ? r[s][v] : av[v];
-                    bv[v] = s == ib ? r[s][v] : bv[v];
-                    cv[v] = s == ic ? r[s][v] : cv[v];
-                }
-            }
-            const int code = op.opcode & 0xff;
-            const bool r16 = (op.opcode & KTB_VM_ROUND16) != 0;
-#pragma unroll
-            for (int v = 0; v < V; ++v) {
-                const float x = ktb_vm_apply(code, av[v], bv[v], cv[v], op.imm);
-                r[NIN + i][v] = r16 ? ktb_round16(x) : x;
-            }
+// Compact evaluator for the row gather / scatter kernels: the register file lives in shared
+// memory (register k of a thread is regs[k * stride], one float4 per thread, conflict-free), so
+// operands can be indexed dynamically without local memory, and the routine is a single
+// out-of-line copy, which keeps the kernels small enough for the instruction cache.  The opcode
+// is decoded once per op, not once per element.
+#define KTB_VM4(EXPR)                                                                      \
+    {                                                                                      \
+        float a, b, c;                                                                     \
+        a = A.x; b = B.x; c = Cc.x; R.x = (EXPR);                                          \
+        a = A.y; b = B.y; c = Cc.y; R.y = (EXPR);                                          \
+        a = A.z; b = B.z; c = Cc.z; R.z = (EXPR);                                          \
+        a = A.w; b = B.w; c = Cc.w; R.w = (EXPR);                                          \
+        (void)a; (void)b; (void)c;                                                         \
+    }                                                                                      \
+    break;
+
+static __device__ __noinline__ float4 ktb_vm_run_smem4(const ktb_vm_program& prog, float4* regs, int stride) {
+    for (int i = 0; i < prog.n_ops; ++i) {
+        const ktb_vm_op op = prog.ops[i];
+        const float4 A = regs[op.a * stride], B = regs[op.b * stride], Cc = regs[op.c * stride];
+        const float imm = op.imm;
+        float4 R = A;
+        switch (op.opcode & 0xff) {
+            case KTB_VM_MOV: break;
+            case KTB_VM_CONST: R = make_float4(imm, imm, imm, imm); break;
+            case KTB_VM_ADD: KTB_VM4(a + b)
+            case KTB_VM_SUB: KTB_VM4(a - b)
+            case KTB_VM_MUL: KTB_VM4(a * b)
+            case KTB_VM_DIV: KTB_VM4(a / b)
+            case KTB_VM_MAXNUM: KTB_VM4(fmaxf(a, b))
+            case KTB_VM_MINNUM: KTB_VM4(fminf(a, b))
+            case KTB_VM_NEG: KTB_VM4(-a)
+            case KTB_VM_ABS: KTB_VM4(fabsf(a))
+            default: KTB_VM4(ktb_vm_apply(op.opcode & 0xff, a, b, c, imm))
         }
+        if (op.opcode & KTB_VM_ROUND16)
+            R = make_float4(ktb_round16(R.x), ktb_round16(R.y), ktb_round16(R.z), ktb_round16(R.w));
+        regs[op.dst * stride] = R;
     }
-    const int ir = prog.result_reg < n_in ? prog.result_reg : prog.result_reg - n_in + NIN;
-#pragma unroll
-    for (int v = 0; v < V; ++v) out[v] = 0.f;
-#pragma unroll
-    for (int s = 0; s < NIN + KTB_VM_SEL_OPS; ++s)
-#pragma unroll
-        for (int v = 0; v < V; ++v) out[v] = s == ir ? r[s][v] : out[v];
+    return regs[prog.result_reg * stride];
 }
