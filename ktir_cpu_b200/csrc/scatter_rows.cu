@@ -97,36 +97,38 @@ static __device__ __forceinline__ void sc_store_row(void* arena, const ktb_row_o
     }
 }
 
-// G entries per warp in flight at once.  Row addresses of all entries are resolved first
-// (independent index loads), then all rows are loaded, then the program runs per entry and the
-// rows are stored, so the dependent index -> row chain of one entry overlaps with the chains of
-// the others.  `vm` is this thread's slot of the shared-memory register file.
+// A warp handles up to 32 entries at a time.  The scalar work of an entry — decoding (tile, row),
+// reading its index, forming the row addresses — is done by ONE lane per entry, all lanes in
+// parallel (sc_resolve); the rows themselves are then moved by the whole warp, G entries in
+// flight at once (sc_move_group), with the addresses broadcast by shuffle.  This keeps the
+// per-entry instruction count low and overlaps the dependent index -> row chains of many entries.
 // PROG selects how the row program is evaluated: the general register program, a plain copy of
 // input 0, or out = round16(in[acc] + round16(in[1 - acc] * c)) with acc = 0 / 1 (the f16
 // scaled-accumulate of a read-modify-write scatter), the latter two without any decoding.
 enum { SC_PROG_VM = 0, SC_PROG_COPY = 1, SC_PROG_AXPY0 = 2, SC_PROG_AXPY1 = 3 };
 
-template <int V, int G, int PROG>
-static __device__ __forceinline__ void sc_do_group(const ktb_rows_args& a, const int32_t (&ent)[G],
-                                                   const int64_t (&dst)[G], int n, int lane, ktb_status* st,
-                                                   float4* vm, int vm_stride) {
-    int64_t in_addr[G][KTB_ROWS_MAX_IN];
-    bool ok[G];
+static __device__ __forceinline__ int64_t sc_shfl64(int64_t v, int src) {
+    const int lo = __shfl_sync(0xffffffffu, (int)(v & 0xffffffffll), src);
+    const int hi = __shfl_sync(0xffffffffu, (int)(v >> 32), src);
+    return ((int64_t)hi << 32) | (uint32_t)lo;
+}
+
+// Row addresses of the non-aliasing inputs of entry e (this lane's entry); -1 marks a bad index.
+static __device__ __forceinline__ void sc_resolve(const ktb_rows_args& a, uint32_t e, ktb_status* st,
+                                                  int64_t (&addr)[KTB_ROWS_MAX_IN]) {
+    const uint32_t t = e / (uint32_t)a.tile_rows;
+    const int pos = (int)(e - t * (uint32_t)a.tile_rows);
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-        ok[g] = g < n && dst[g] >= 0;
-        const uint32_t e = g < n ? (uint32_t)ent[g] : 0u;
-        const uint32_t t = e / (uint32_t)a.tile_rows;
-        const int pos = (int)(e - t * (uint32_t)a.tile_rows);
-#pragma unroll
-        for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
-            in_addr[g][k] = 0;
-            if (g < n && k < a.n_in) {
-                in_addr[g][k] = a.in[k].alias_dst ? dst[g] : sc_row_addr(a.arena, a.in[k], t, pos, st);
-                ok[g] = ok[g] && in_addr[g][k] >= 0;
-            }
-        }
+    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+        addr[k] = 0;
+        if (k < a.n_in && !a.in[k].alias_dst) addr[k] = sc_row_addr(a.arena, a.in[k], t, pos, st);
     }
+}
+
+template <int V, int G, int PROG>
+static __device__ __forceinline__ void sc_move_group(const ktb_rows_args& a, const int64_t (&in_addr)[G][KTB_ROWS_MAX_IN],
+                                                     const int64_t (&dst)[G], const bool (&ok)[G], int lane,
+                                                     float4* vm, int vm_stride) {
     for (int col = lane * V; col < a.cols; col += 32 * V) {
         float x[G][KTB_ROWS_MAX_IN][V];
 #pragma unroll
@@ -173,23 +175,33 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_cons
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int64_t E = a.n_tiles * a.tile_rows;
-    for (int64_t e0 = warp * G; e0 < E; e0 += n_warps * G) {
-        int32_t ent[G];
-        int64_t dst[G];
-        int n = 0;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            ent[g] = 0;
-            dst[g] = -1;
-            if (e0 + g < E) {
-                const uint32_t e = (uint32_t)(e0 + g);
-                const uint32_t t = e / (uint32_t)a.tile_rows;
-                ent[g] = (int32_t)e;
-                dst[g] = sc_row_addr(a.arena, a.out, t, (int)(e - t * (uint32_t)a.tile_rows), st);
-                n = g + 1;
-            }
+    for (int64_t e0 = warp * 32; e0 < E; e0 += n_warps * 32) {
+        const bool have = e0 + lane < E;
+        const uint32_t e = (uint32_t)(have ? e0 + lane : 0);
+        int64_t my_in[KTB_ROWS_MAX_IN];
+        int64_t my_dst = -1;
+        sc_resolve(a, e, st, my_in);
+        if (have) {
+            const uint32_t t = e / (uint32_t)a.tile_rows;
+            my_dst = sc_row_addr(a.arena, a.out, t, (int)(e - t * (uint32_t)a.tile_rows), st);
         }
-        sc_do_group<V, G, PROG>(a, ent, dst, n, lane, st, rp_vm + threadIdx.x, blockDim.x);
+        const int cnt = (int)((E - e0) < 32 ? (E - e0) : 32);
+        for (int b0 = 0; b0 < cnt; b0 += G) {
+            int64_t in_addr[G][KTB_ROWS_MAX_IN], dst[G];
+            bool ok[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const int src = (b0 + g) & 31;
+                dst[g] = sc_shfl64(my_dst, src);
+                ok[g] = b0 + g < cnt && dst[g] >= 0;
+#pragma unroll
+                for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+                    in_addr[g][k] = sc_shfl64(my_in[k], src);
+                    if (k < a.n_in) ok[g] = ok[g] && in_addr[g][k] >= 0;
+                }
+            }
+            sc_move_group<V, G, PROG>(a, in_addr, dst, ok, lane, rp_vm + threadIdx.x, blockDim.x);
+        }
     }
 }
 
@@ -261,34 +273,48 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
             const int i = i0 + lane;
             const int32_t r = i < len ? list_r[i] : -1;
             const int32_t e = i < len ? list_e[i] : 0;
-            unsigned mask = __ballot_sync(0xffffffffu, r >= 0 && (r & (SC_WARPS - 1)) == wid);
+            const bool mine = r >= 0 && (r & (SC_WARPS - 1)) == wid;
+            unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mask == 0) continue;
+            int64_t my_in[KTB_ROWS_MAX_IN];
+            sc_resolve(a, mine ? (uint32_t)e : 0u, st, my_in);
+            const int64_t my_dst = a.dst_row0 + (int64_t)(r < 0 ? 0 : r) * a.out.idx_mult;
             while (mask) {
-                int32_t ent[SC_GROUP];
-                int64_t dst[SC_GROUP];
+                int64_t in_addr[SC_GROUP][KTB_ROWS_MAX_IN], dst[SC_GROUP];
                 int32_t rows[SC_GROUP];
+                bool ok[SC_GROUP];
                 int n = 0;
 #pragma unroll
                 for (int g = 0; g < SC_GROUP; ++g) {
-                    ent[g] = 0;
-                    dst[g] = -1;
                     rows[g] = -1;
+                    dst[g] = -1;
+                    ok[g] = false;
+#pragma unroll
+                    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) in_addr[g][k] = 0;
                     if (mask && n == g) {
                         const int src = __ffs(mask) - 1;
                         const int32_t rr = __shfl_sync(0xffffffffu, r, src);
-                        const int32_t ee = __shfl_sync(0xffffffffu, e, src);
                         bool clash = false;     // a second update of a row must wait for the first
 #pragma unroll
                         for (int h = 0; h < SC_GROUP; ++h) clash = clash || (h < g && rows[h] == rr);
                         if (!clash) {
                             rows[g] = rr;
-                            ent[g] = ee;
-                            dst[g] = a.dst_row0 + (int64_t)rr * a.out.idx_mult;
+                            dst[g] = sc_shfl64(my_dst, src);
+                            ok[g] = true;
+#pragma unroll
+                            for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+                                const int64_t v = sc_shfl64(my_in[k], src);
+                                if (k < a.n_in) {
+                                    in_addr[g][k] = a.in[k].alias_dst ? dst[g] : v;
+                                    ok[g] = ok[g] && in_addr[g][k] >= 0;
+                                }
+                            }
                             mask &= mask - 1;
                             n = g + 1;
                         }
                     }
                 }
-                sc_do_group<V, SC_GROUP, PROG>(a, ent, dst, n, lane, st, vm, SC_THREADS);
+                sc_move_group<V, SC_GROUP, PROG>(a, in_addr, dst, ok, lane, vm, SC_THREADS);
             }
         }
         __syncthreads();
