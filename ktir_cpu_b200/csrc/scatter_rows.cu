@@ -249,6 +249,7 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_c
 #define SC_STEP (SC_THREADS * 16)   // entries examined per scan step (16 owner bytes per thread)
 #define SC_LCAP SC_STEP             // entries buffered per CTA before the batch is applied
 #define SC_GROUP 4
+#define SC_PRIV 512                // entries in a warp's private list
 
 template <int V, int PROG>
 __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a, int rows_per_owner,
@@ -256,7 +257,9 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
     extern __shared__ uint8_t sc_smem[];
     int32_t* list_e = reinterpret_cast<int32_t*>(sc_smem);                  // [SC_LCAP] entry ids
     int32_t* list_r = list_e + SC_LCAP;                                     // [SC_LCAP] destination row ids
-    float4* vm = reinterpret_cast<float4*>(list_r + SC_LCAP) + threadIdx.x;  // [KTB_VM_REGS][SC_THREADS]
+    int32_t* my_e = list_r + SC_LCAP + (threadIdx.x >> 5) * (2 * SC_PRIV);   // this warp's private list
+    int32_t* my_r = my_e + SC_PRIV;
+    float4* vm = reinterpret_cast<float4*>(list_r + SC_LCAP + SC_WARPS * 2 * SC_PRIV) + threadIdx.x;  // [KTB_VM_REGS][SC_THREADS]
     __shared__ int32_t warp_tot[SC_WARPS];
     __shared__ int32_t s_len;
 
@@ -267,19 +270,19 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
     if (tid == 0) s_len = 0;
     __syncthreads();
 
-    auto apply_batch = [&]() {
-        const int len = s_len;
-        for (int i0 = 0; i0 < len; i0 += 32) {
-            const int i = i0 + lane;
-            const int32_t r = i < len ? list_r[i] : -1;
-            const int32_t e = i < len ? list_e[i] : 0;
-            const bool mine = r >= 0 && (r & (SC_WARPS - 1)) == wid;
-            unsigned mask = __ballot_sync(0xffffffffu, mine);
-            if (mask == 0) continue;
+    // One warp applies a dense run of its own entries: lane l resolves entry l, then the rows move
+    // SC_GROUP at a time in list order (an update of a row waits for the previous one of that row).
+    auto apply_private = [&](int cnt) {
+        for (int j0 = 0; j0 < cnt; j0 += 32) {
+            const bool have = j0 + lane < cnt;
+            const int32_t e = have ? my_e[j0 + lane] : 0;
+            const int32_t r = have ? my_r[j0 + lane] : -1;
             int64_t my_in[KTB_ROWS_MAX_IN];
-            sc_resolve(a, mine ? (uint32_t)e : 0u, st, my_in);
+            sc_resolve(a, (uint32_t)e, st, my_in);
             const int64_t my_dst = a.dst_row0 + (int64_t)(r < 0 ? 0 : r) * a.out.idx_mult;
-            while (mask) {
+            const int m = cnt - j0 < 32 ? cnt - j0 : 32;
+            int next = 0;
+            while (next < m) {
                 int64_t in_addr[SC_GROUP][KTB_ROWS_MAX_IN], dst[SC_GROUP];
                 int32_t rows[SC_GROUP];
                 bool ok[SC_GROUP];
@@ -291,10 +294,10 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
                     ok[g] = false;
 #pragma unroll
                     for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) in_addr[g][k] = 0;
-                    if (mask && n == g) {
-                        const int src = __ffs(mask) - 1;
+                    if (next < m && n == g) {
+                        const int src = next;
                         const int32_t rr = __shfl_sync(0xffffffffu, r, src);
-                        bool clash = false;     // a second update of a row must wait for the first
+                        bool clash = false;
 #pragma unroll
                         for (int h = 0; h < SC_GROUP; ++h) clash = clash || (h < g && rows[h] == rr);
                         if (!clash) {
@@ -309,7 +312,7 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
                                     ok[g] = ok[g] && in_addr[g][k] >= 0;
                                 }
                             }
-                            mask &= mask - 1;
+                            ++next;
                             n = g + 1;
                         }
                     }
@@ -317,6 +320,33 @@ __global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const 
                 sc_move_group<V, SC_GROUP, PROG>(a, in_addr, dst, ok, lane, vm, SC_THREADS);
             }
         }
+    };
+
+    // Entries of the CTA list are dealt to warps by destination row (row % SC_WARPS); each warp
+    // packs its entries, in list order, into a private list and applies them in dense runs.
+    auto apply_batch = [&]() {
+        const int len = s_len;
+        int cnt = 0;
+        for (int i0 = 0; i0 < len; i0 += 32) {
+            const int i = i0 + lane;
+            const int32_t r = i < len ? list_r[i] : -1;
+            const int32_t e = i < len ? list_e[i] : 0;
+            const bool mine = r >= 0 && (r & (SC_WARPS - 1)) == wid;
+            const unsigned mask = __ballot_sync(0xffffffffu, mine);
+            if (mine) {
+                const int at = cnt + __popc(mask & ((1u << lane) - 1));
+                my_e[at] = e;
+                my_r[at] = r;
+            }
+            cnt += __popc(mask);
+            __syncwarp();
+            if (cnt > SC_PRIV - 32) {
+                apply_private(cnt);
+                cnt = 0;
+                __syncwarp();
+            }
+        }
+        if (cnt) apply_private(cnt);
         __syncthreads();
         if (tid == 0) s_len = 0;
         __syncthreads();
@@ -461,7 +491,7 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
     ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
-    const size_t asmem = (size_t)SC_LCAP * 8 + (size_t)KTB_VM_REGS * SC_THREADS * sizeof(float4);
+    const size_t asmem = (size_t)SC_LCAP * 8 + (size_t)SC_WARPS * SC_PRIV * 8 + (size_t)KTB_VM_REGS * SC_THREADS * sizeof(float4);
 #define KTB_SA(V, P)                                                                                              \
     do {                                                                                                          \
         KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<V, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
