@@ -166,7 +166,7 @@ typedef struct {
     ktb_row_operand in[KTB_ROWS_MAX_IN];
     ktb_row_operand out;
     ktb_vm_program program;
-    int32_t* dev_rowid_scratch;   /* scatter only: 8 bytes of scratch per entry (n_tiles * tile_rows entries) */
+    int32_t* dev_rowid_scratch;   /* scatter only: scratch of 8 * (entries + dst_rows) + 16 bytes, entries = n_tiles * tile_rows */
     int64_t dst_row0;             /* scatter only: element offset of destination row id 0 */
     int64_t dst_rows;             /* scatter only: number of destination rows */
 } ktb_rows_args;

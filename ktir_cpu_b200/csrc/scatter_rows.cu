@@ -11,16 +11,12 @@
 //
 // Ordering.  The reference applies tiles one after another; inside a tile all
 // loads happen before the store and duplicate destination rows keep the LAST
-// writer (ktir_cpu/memory.py:281-291).  The scatter kernels reproduce exactly
-// that without atomics:
-//   1. ktb_scatter_prepare: per tile, resolve destination row ids and drop every
-//      entry that a later entry of the same tile overwrites.
-//   2. ktb_scatter_apply: destination rows are partitioned over CTAs (owner
-//      computes).  Each CTA scans the row-id list in order, keeps the entries it
-//      owns (ordered compaction), ranks entries of the same row by tile order,
-//      and applies rank 0, 1, 2, ... in rounds: inside a round all rows are
-//      distinct, so warps run in parallel; rounds are separated by a barrier.
-// HBM-bound: per entry one index, one row per input, one row written.
+// writer (ktir_cpu/memory.py:281-291).  The scatter path reproduces exactly that
+// without sorting the whole index list and without floating-point atomics: the
+// entries are bucketed by destination row (count, prefix sum, fill) and one warp
+// per row replays that row's updates in tile order with the row in registers.
+// HBM-bound: per entry one index and one row per gathered input; each touched
+// destination row is read and written once.
 #include "vm.cuh"
 
 
@@ -205,15 +201,19 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_cons
     }
 }
 
-// ---- indirect destination, step 1: row ids + last-writer-wins inside each tile -----------------
-// Scratch layout: int32 row id per entry (-1 = dropped), then one owner byte per entry (255 = none).
-#define SC_NO_OWNER 255
-
-__global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_constant__ ktb_rows_args a, int rows_per_owner,
-                                                                  ktb_status* st) {
+// ---- indirect destination -------------------------------------------------------------------------
+// Scratch layout (int32 words): rowid[E] | sorted_e[E] | count[R] | offsets[R + 1], with E entries
+// and R destination rows.
+//   1. prepare: per tile, destination row id of every entry; an entry that a later entry of the
+//      same tile overwrites is dropped (last writer wins); survivors are counted per row.
+//   2. scan:    exclusive prefix sum of the counts -> segment offsets per destination row.
+//   3. fill:    every surviving entry is placed into the segment of its row.
+//   4. apply:   one warp per destination row sorts its (short) segment by entry id — which is
+//      tile order — and applies the updates one after another with the row held in registers:
+//      the row is read once and written once however many tiles touch it.
+__global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_constant__ ktb_rows_args a,
+                                                                  int32_t* count, ktb_status* st) {
     extern __shared__ int64_t s_addr[];      // [tile_rows]
-    const int64_t E = a.n_tiles * a.tile_rows;
-    uint8_t* owner = reinterpret_cast<uint8_t*>(a.dev_rowid_scratch + E);
     for (int64_t t = blockIdx.x; t < a.n_tiles; t += gridDim.x) {
         for (int pos = threadIdx.x; pos < a.tile_rows; pos += blockDim.x) {
             int64_t addr = sc_row_addr(a.arena, a.out, t, pos, st);
@@ -230,178 +230,189 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_c
             const int64_t mine = s_addr[pos];
             bool win = mine >= 0;
             for (int q = pos + 1; win && q < a.tile_rows; ++q) win = s_addr[q] != mine;
-            const int64_t e = t * a.tile_rows + pos;
-            a.dev_rowid_scratch[e] = win ? (int32_t)mine : -1;
-            owner[e] = win ? (uint8_t)(mine / rows_per_owner) : (uint8_t)SC_NO_OWNER;
+            a.dev_rowid_scratch[t * a.tile_rows + pos] = win ? (int32_t)mine : -1;
+            if (win) atomicAdd(&count[mine], 1);
         }
         __syncthreads();
     }
 }
 
-// ---- step 2: owner-computes ordered apply ------------------------------------------------------
-// Destination rows are partitioned over CTAs; inside a CTA a row belongs to warp (row % 32).  A
-// CTA scans the owner bytes of all entries in order and appends its own entries to a list
-// (ordered compaction).  Each warp then walks the list in order and applies the entries of its
-// rows: updates of one row are applied by one warp in tile order, different rows never interact,
-// so no barrier and no atomic is needed while applying.
-#define SC_THREADS 512
-#define SC_WARPS (SC_THREADS / 32)
-#define SC_STEP (SC_THREADS * 16)   // entries examined per scan step (16 owner bytes per thread)
-#define SC_LCAP SC_STEP             // entries buffered per CTA before the batch is applied
-#define SC_GROUP 4
-#define SC_PRIV 512                // entries in a warp's private list
+// offsets[r] = sum of count[0..r), offsets[R] = total; count[] becomes the fill cursor (= offsets).
+__global__ void __launch_bounds__(1024) ktb_scatter_scan_kernel(int32_t* count, int32_t* offsets, int64_t R) {
+    __shared__ int32_t part[1024];
+    const int tid = threadIdx.x;
+    const int64_t per = (R + 1023) / 1024;
+    const int64_t lo = tid * per, hi = lo + per < R ? lo + per : R;
+    int32_t sum = 0;
+    for (int64_t i = lo; i < hi; ++i) sum += count[i];
+    part[tid] = sum;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {
+        const int32_t v = tid >= d ? part[tid - d] : 0;
+        __syncthreads();
+        part[tid] += v;
+        __syncthreads();
+    }
+    int32_t run = part[tid] - sum;
+    for (int64_t i = lo; i < hi; ++i) {
+        const int32_t c = count[i];
+        offsets[i] = run;
+        count[i] = run;
+        run += c;
+    }
+    if (tid == 1023) offsets[R] = part[1023];
+}
+
+__global__ void __launch_bounds__(256) ktb_scatter_fill_kernel(const int32_t* rowid, int32_t* cursor, int32_t* sorted_e,
+                                                               int64_t E) {
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
+        const int32_t r = rowid[e];
+        if (r >= 0) sorted_e[atomicAdd(&cursor[r], 1)] = (int32_t)e;
+    }
+}
 
 template <int V, int PROG>
-__global__ void __launch_bounds__(SC_THREADS, 1) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a, int rows_per_owner,
-                                                                           ktb_status* st) {
-    extern __shared__ uint8_t sc_smem[];
-    int32_t* list_e = reinterpret_cast<int32_t*>(sc_smem);                  // [SC_LCAP] entry ids
-    int32_t* list_r = list_e + SC_LCAP;                                     // [SC_LCAP] destination row ids
-    int32_t* my_e = list_r + SC_LCAP + (threadIdx.x >> 5) * (2 * SC_PRIV);   // this warp's private list
-    int32_t* my_r = my_e + SC_PRIV;
-    float4* vm = reinterpret_cast<float4*>(list_r + SC_LCAP + SC_WARPS * 2 * SC_PRIV) + threadIdx.x;  // [KTB_VM_REGS][SC_THREADS]
-    __shared__ int32_t warp_tot[SC_WARPS];
-    __shared__ int32_t s_len;
+static __device__ __forceinline__ void sc_apply_one(const ktb_rows_args& a, const float (&x)[KTB_ROWS_MAX_IN][V],
+                                                    float (&cur)[V], float4* vm, int vm_stride) {
+    // inputs that alias the destination read the running value of the row
+    float in[KTB_ROWS_MAX_IN][V];
+#pragma unroll
+    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+#pragma unroll
+        for (int v = 0; v < V; ++v) in[k][v] = (k < a.n_in && a.in[k].alias_dst) ? cur[v] : x[k][v];
+    if (PROG == SC_PROG_COPY) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) cur[v] = in[0][v];
+    } else if (PROG == SC_PROG_AXPY0 || PROG == SC_PROG_AXPY1) {
+        constexpr int ACC = PROG == SC_PROG_AXPY0 ? 0 : 1;
+        const float c = a.program.ops[0].imm;
+#pragma unroll
+        for (int v = 0; v < V; ++v) cur[v] = ktb_round16(in[ACC][v] + ktb_round16(in[1 - ACC][v] * c));
+    } else {
+#pragma unroll
+        for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+            vm[k * vm_stride] = make_float4(in[k][0], V > 1 ? in[k][1 % V] : 0.f, V > 1 ? in[k][2 % V] : 0.f,
+                                            V > 1 ? in[k][3 % V] : 0.f);
+        const float4 res = ktb_vm_run_smem4(a.program, vm, vm_stride);
+        const float rv[4] = {res.x, res.y, res.z, res.w};
+#pragma unroll
+        for (int v = 0; v < V; ++v) cur[v] = rv[v];
+    }
+    // what is stored is rounded to the destination type, so the next update must see that value
+    if (a.out.dtype == KTB_F16) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) cur[v] = ktb_round16(cur[v]);
+    }
+}
 
-    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int64_t E = a.n_tiles * a.tile_rows;
-    const uint8_t* owner = reinterpret_cast<const uint8_t*>(a.dev_rowid_scratch + E);
-    const uint32_t me4 = (uint32_t)blockIdx.x * 0x01010101u;
-    if (tid == 0) s_len = 0;
-    __syncthreads();
+template <int V, int PROG>
+__global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a,
+                                                                const int32_t* sorted_e, const int32_t* offsets,
+                                                                ktb_status* st) {
+    constexpr int G = 4;
+    extern __shared__ float4 sa_vm[];                 // [KTB_VM_REGS][blockDim.x] register file
+    float4* vm = sa_vm + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    bool rmw = false;
+#pragma unroll
+    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) rmw = rmw || (k < a.n_in && a.in[k].alias_dst);
 
-    // One warp applies a dense run of its own entries: lane l resolves entry l, then the rows move
-    // SC_GROUP at a time in list order (an update of a row waits for the previous one of that row).
-    auto apply_private = [&](int cnt) {
-        for (int j0 = 0; j0 < cnt; j0 += 32) {
-            const bool have = j0 + lane < cnt;
-            const int32_t e = have ? my_e[j0 + lane] : 0;
-            const int32_t r = have ? my_r[j0 + lane] : -1;
+    for (int64_t row = warp; row < a.dst_rows; row += n_warps) {
+        const int32_t lo = offsets[row], hi = offsets[row + 1];
+        const int cnt = hi - lo;
+        if (cnt == 0) continue;
+        const int64_t dst = a.dst_row0 + row * a.out.idx_mult;
+        if (cnt <= 32) {
+            const int32_t e = lane < cnt ? sorted_e[lo + lane] : 0x7fffffff;
+            int rank = 0;
+            for (int j = 0; j < cnt; ++j) rank += __shfl_sync(0xffffffffu, e, j) < e ? 1 : 0;
             int64_t my_in[KTB_ROWS_MAX_IN];
-            sc_resolve(a, (uint32_t)e, st, my_in);
-            const int64_t my_dst = a.dst_row0 + (int64_t)(r < 0 ? 0 : r) * a.out.idx_mult;
-            const int m = cnt - j0 < 32 ? cnt - j0 : 32;
-            int next = 0;
-            while (next < m) {
-                int64_t in_addr[SC_GROUP][KTB_ROWS_MAX_IN], dst[SC_GROUP];
-                int32_t rows[SC_GROUP];
-                bool ok[SC_GROUP];
-                int n = 0;
+            sc_resolve(a, lane < cnt ? (uint32_t)e : 0u, st, my_in);
+            const int first = rmw ? 0 : cnt - 1;      // a plain overwrite only keeps the last writer
+            for (int c0 = 0; c0 < a.cols; c0 += 32 * V) {     // uniform trip count: the body shuffles
+                const int col = c0 + lane * V;
+                const bool act = col < a.cols;
+                float cur[V];
 #pragma unroll
-                for (int g = 0; g < SC_GROUP; ++g) {
-                    rows[g] = -1;
-                    dst[g] = -1;
-                    ok[g] = false;
+                for (int v = 0; v < V; ++v) cur[v] = 0.f;
+                if (rmw && act) sc_load_row<V>(a.arena, a.out, dst, col, a.cols, cur);
+                for (int k0 = first; k0 < cnt; k0 += G) {
+                    int64_t in_addr[G][KTB_ROWS_MAX_IN];
+                    bool ok[G];
 #pragma unroll
-                    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) in_addr[g][k] = 0;
-                    if (next < m && n == g) {
-                        const int src = next;
-                        const int32_t rr = __shfl_sync(0xffffffffu, r, src);
-                        bool clash = false;
+                    for (int g = 0; g < G; ++g) {
+                        const unsigned m = __ballot_sync(0xffffffffu, lane < cnt && rank == k0 + g);
+                        const int src = m ? __ffs(m) - 1 : 0;
+                        ok[g] = m != 0;
 #pragma unroll
-                        for (int h = 0; h < SC_GROUP; ++h) clash = clash || (h < g && rows[h] == rr);
-                        if (!clash) {
-                            rows[g] = rr;
-                            dst[g] = sc_shfl64(my_dst, src);
-                            ok[g] = true;
-#pragma unroll
-                            for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
-                                const int64_t v = sc_shfl64(my_in[k], src);
-                                if (k < a.n_in) {
-                                    in_addr[g][k] = a.in[k].alias_dst ? dst[g] : v;
-                                    ok[g] = ok[g] && in_addr[g][k] >= 0;
-                                }
-                            }
-                            ++next;
-                            n = g + 1;
+                        for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+                            in_addr[g][k] = sc_shfl64(my_in[k], src);
+                            if (k < a.n_in && !a.in[k].alias_dst) ok[g] = ok[g] && in_addr[g][k] >= 0;
                         }
                     }
+                    float x[G][KTB_ROWS_MAX_IN][V];
+#pragma unroll
+                    for (int g = 0; g < G; ++g)
+#pragma unroll
+                        for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+#pragma unroll
+                            for (int v = 0; v < V; ++v) x[g][k][v] = 0.f;
+                            if (act && ok[g] && k < a.n_in && !a.in[k].alias_dst)
+                                sc_load_row<V>(a.arena, a.in[k], in_addr[g][k], col, a.cols, x[g][k]);
+                        }
+#pragma unroll
+                    for (int g = 0; g < G; ++g)
+                        if (ok[g]) sc_apply_one<V, PROG>(a, x[g], cur, vm, blockDim.x);
                 }
-                sc_move_group<V, SC_GROUP, PROG>(a, in_addr, dst, ok, lane, vm, SC_THREADS);
+                if (act) sc_store_row<V>(a.arena, a.out, dst, col, a.cols, cur);
             }
-        }
-    };
-
-    // Entries of the CTA list are dealt to warps by destination row (row % SC_WARPS); each warp
-    // packs its entries, in list order, into a private list and applies them in dense runs.
-    auto apply_batch = [&]() {
-        const int len = s_len;
-        int cnt = 0;
-        for (int i0 = 0; i0 < len; i0 += 32) {
-            const int i = i0 + lane;
-            const int32_t r = i < len ? list_r[i] : -1;
-            const int32_t e = i < len ? list_e[i] : 0;
-            const bool mine = r >= 0 && (r & (SC_WARPS - 1)) == wid;
-            const unsigned mask = __ballot_sync(0xffffffffu, mine);
-            if (mine) {
-                const int at = cnt + __popc(mask & ((1u << lane) - 1));
-                my_e[at] = e;
-                my_r[at] = r;
-            }
-            cnt += __popc(mask);
-            __syncwarp();
-            if (cnt > SC_PRIV - 32) {
-                apply_private(cnt);
-                cnt = 0;
-                __syncwarp();
-            }
-        }
-        if (cnt) apply_private(cnt);
-        __syncthreads();
-        if (tid == 0) s_len = 0;
-        __syncthreads();
-    };
-
-    const int64_t n_steps = (E + SC_STEP - 1) / SC_STEP;
-    auto load_bytes = [&](int64_t step) -> uint4 {
-        const int64_t e0 = step * SC_STEP + (int64_t)tid * 16;
-        if (e0 + 16 <= E && ((reinterpret_cast<uintptr_t>(owner) & 15) == 0))
-            return __ldg(reinterpret_cast<const uint4*>(owner + e0));
-        uint32_t w[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-        for (int j = 0; j < 16; ++j)
-            if (e0 + j < E) w[j >> 2] = (w[j >> 2] & ~(0xffu << (8 * (j & 3)))) | ((uint32_t)owner[e0 + j] << (8 * (j & 3)));
-        return make_uint4(w[0], w[1], w[2], w[3]);
-    };
-    uint4 cur = n_steps > 0 ? load_bytes(0) : make_uint4(~0u, ~0u, ~0u, ~0u);
-    for (int64_t step = 0; step < n_steps; ++step) {
-        const uint4 nxt = step + 1 < n_steps ? load_bytes(step + 1) : make_uint4(~0u, ~0u, ~0u, ~0u);
-        const int64_t e0 = step * SC_STEP + (int64_t)tid * 16;
-        const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
-        uint32_t hit[4];
-        int m = 0;
+        } else {
+            // long chain (one row hit by more than 32 tiles): select the entries in ascending order
+            for (int c0 = 0; c0 < a.cols; c0 += 32 * V) {     // uniform trip count: the body shuffles
+                const int col = c0 + lane * V;
+                const bool act = col < a.cols;
+                float cur[V];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            hit[j] = __vcmpeq4(w[j], me4);          // 0xff in every byte that names this CTA
-            m += __popc(hit[j]) >> 3;
-        }
-        int incl = m;
-        for (int d = 1; d < 32; d <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, incl, d);
-            if (lane >= d) incl += o;
-        }
-        if (lane == 31) warp_tot[wid] = incl;
-        __syncthreads();
-        int before = 0, total = 0;
-        for (int wv = 0; wv < SC_WARPS; ++wv) {
-            const int x = warp_tot[wv];
-            if (wv < wid) before += x;
-            total += x;
-        }
-        if (s_len + total > SC_LCAP) apply_batch();      // uniform: s_len and total are block-wide values
-        int at = s_len + before + incl - m;
+                for (int v = 0; v < V; ++v) cur[v] = 0.f;
+                if (rmw && act) sc_load_row<V>(a.arena, a.out, dst, col, a.cols, cur);
+                int32_t prev = -1;
+                for (int step = 0; step < cnt; ++step) {
+                    int32_t best = 0x7fffffff;
+                    if (rmw) {
+                        for (int i = lo + lane; i < hi; i += 32) {
+                            const int32_t v = sorted_e[i];
+                            if (v > prev && v < best) best = v;
+                        }
+                        for (int d = 16; d; d >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, d));
+                    } else {
+                        best = -1;
+                        for (int i = lo + lane; i < hi; i += 32) best = max(best, sorted_e[i]);
+                        for (int d = 16; d; d >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, d));
+                        step = cnt;            // only the last writer matters
+                    }
+                    prev = best;
+                    int64_t in_addr[KTB_ROWS_MAX_IN];
+                    sc_resolve(a, (uint32_t)best, st, in_addr);
+                    bool ok = true;
+                    float x[KTB_ROWS_MAX_IN][V];
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-            if (hit[j >> 2] & (0xffu << (8 * (j & 3)))) {
-                list_e[at] = (int32_t)(e0 + j);
-                list_r[at] = a.dev_rowid_scratch[e0 + j];
-                ++at;
+                    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
+#pragma unroll
+                        for (int v = 0; v < V; ++v) x[k][v] = 0.f;
+                        if (k < a.n_in && !a.in[k].alias_dst) ok = ok && in_addr[k] >= 0;
+                    }
+#pragma unroll
+                    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+                        if (act && ok && k < a.n_in && !a.in[k].alias_dst)
+                            sc_load_row<V>(a.arena, a.in[k], in_addr[k], col, a.cols, x[k]);
+                    if (ok) sc_apply_one<V, PROG>(a, x, cur, vm, blockDim.x);
+                }
+                if (act) sc_store_row<V>(a.arena, a.out, dst, col, a.cols, cur);
             }
-        __syncthreads();
-        if (tid == 0) s_len += total;
-        __syncthreads();
-        cur = nxt;
+        }
     }
-    if (s_len > 0) apply_batch();
 }
 
 // Recognise the two row programs that have a decoded fast path.
@@ -481,23 +492,26 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (a.out.idx_mult <= 0 || a.dst_rows <= 0) return ktb_fail(ctx, KTB_E_ARG, "scatter_rows", "bad destination row geometry");
     if (a.dst_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "too many destination rows");
     if (a.n_tiles == 0) return KTB_OK;
-    // destination rows are split evenly over one owner CTA per SM (at most 254 owners)
-    int64_t n_own = ctx->sm_count < 254 ? ctx->sm_count : 254;
-    int64_t rpo = (a.dst_rows + n_own - 1) / n_own;
-    if (rpo < 1) rpo = 1;
-    const int64_t owners = (a.dst_rows + rpo - 1) / rpo;
+    const int64_t E = a.n_tiles * a.tile_rows, R = a.dst_rows;
+    int32_t* sorted_e = scratch + E;
+    int32_t* count = scratch + 2 * E;
+    int32_t* offsets = count + R;
+    KTB_CUDA(ctx, cudaMemsetAsync(count, 0, (size_t)R * sizeof(int32_t), ctx->stream));
     int64_t prep_blocks = a.n_tiles < (int64_t)ctx->sm_count * 16 ? a.n_tiles : (int64_t)ctx->sm_count * 16;
     const size_t smem = (size_t)a.tile_rows * sizeof(int64_t);
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
-    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, (int)rpo, ctx->dev_status);
+    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, count, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
-    const size_t asmem = (size_t)SC_LCAP * 8 + (size_t)SC_WARPS * SC_PRIV * 8 + (size_t)KTB_VM_REGS * SC_THREADS * sizeof(float4);
-#define KTB_SA(V, P)                                                                                              \
-    do {                                                                                                          \
-        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_scatter_apply_kernel<V, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           (int)asmem));                                                          \
-        ktb_scatter_apply_kernel<V, P><<<(unsigned)owners, SC_THREADS, asmem, ctx->stream>>>(a, (int)rpo, ctx->dev_status); \
-    } while (0)
+    ktb_scatter_scan_kernel<<<1, 1024, 0, ctx->stream>>>(count, offsets, R);
+    KTB_CHECK_LAUNCH(ctx, "ktb_scatter_scan_kernel");
+    int64_t fill_blocks = (E + 255) / 256;
+    if (fill_blocks > (int64_t)ctx->sm_count * 32) fill_blocks = (int64_t)ctx->sm_count * 32;
+    ktb_scatter_fill_kernel<<<(unsigned)fill_blocks, 256, 0, ctx->stream>>>(scratch, count, sorted_e, E);
+    KTB_CHECK_LAUNCH(ctx, "ktb_scatter_fill_kernel");
+    int64_t blocks = (R + 7) / 8;
+    if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
+    const size_t asmem = (size_t)KTB_VM_REGS * 256 * sizeof(float4);
+#define KTB_SA(V, P) ktb_scatter_apply_kernel<V, P><<<(unsigned)blocks, 256, asmem, ctx->stream>>>(a, sorted_e, offsets, ctx->dev_status)
     switch (sc_classify(a) * 2 + (a.vector_ok ? 1 : 0)) {
         case SC_PROG_COPY * 2 + 1: KTB_SA(4, SC_PROG_COPY); break;
         case SC_PROG_COPY * 2: KTB_SA(1, SC_PROG_COPY); break;

@@ -231,7 +231,8 @@ class RowsStatement(Statement):
             a.dst_row0 = int(out.base[0]) if n_tiles else 0
             bpe = bytes_per_elem(out.dtype)
             a.dst_rows = max(0, (dst_alloc.byte_hi // bpe - a.dst_row0 - out.cols) // out.idx_mult + 1)
-            self.scratch = dev.alloc(max(8 * n_tiles * out.rows, 64))
+            # rowid[E] | sorted_e[E] | count[R] | offsets[R + 1] (int32 each)
+            self.scratch = dev.alloc(8 * n_tiles * out.rows + 8 * int(a.dst_rows) + 64)
             self.device_arrays.append(self.scratch)
             a.dev_rowid_scratch = self.scratch
             self.launches = 2
