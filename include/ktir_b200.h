@@ -166,7 +166,7 @@ typedef struct {
     ktb_row_operand in[KTB_ROWS_MAX_IN];
     ktb_row_operand out;
     ktb_vm_program program;
-    int32_t* dev_rowid_scratch;   /* scatter only: scratch of 8 * (entries + dst_rows) + 16 bytes, entries = n_tiles * tile_rows */
+    int32_t* dev_rowid_scratch;   /* scatter only: ktb_scatter_scratch_bytes(n_tiles * tile_rows, dst_rows) bytes, 16-byte aligned */
     int64_t dst_row0;             /* scatter only: element offset of destination row id 0 */
     int64_t dst_rows;             /* scatter only: number of destination rows */
 } ktb_rows_args;
@@ -178,6 +178,8 @@ int ktb_launch_rows_program(ktb_ctx* ctx, const ktb_rows_args* args);
  * within a tile wins — ktdp.store through an indirect access tile, including the
  * load/modify/store-back form. */
 int ktb_launch_scatter_rows(ktb_ctx* ctx, const ktb_rows_args* args);
+/* Bytes of device scratch ktb_launch_scatter_rows needs for this many entries and destination rows. */
+size_t ktb_scatter_scratch_bytes(int64_t entries, int64_t dst_rows);
 
 /* ---- dense f16 GEMM on tensor cores -------------------------------------------------
  * C[M,N] = A[M,K] * B[K,N] + c_init, row-major operands in the arena, f32 accumulation

@@ -202,17 +202,53 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_cons
 }
 
 // ---- indirect destination -------------------------------------------------------------------------
-// Scratch layout (int32 words): rowid[E] | sorted_e[E] | count[R] | offsets[R + 1], with E entries
-// and R destination rows.
-//   1. prepare: per tile, destination row id of every entry; an entry that a later entry of the
-//      same tile overwrites is dropped (last writer wins); survivors are counted per row.
-//   2. scan:    exclusive prefix sum of the counts -> segment offsets per destination row.
-//   3. fill:    every surviving entry is placed into the segment of its row.
-//   4. apply:   one warp per destination row sorts its (short) segment by entry id — which is
-//      tile order — and applies the updates one after another with the row held in registers:
-//      the row is read once and written once however many tiles touch it.
+// Entries are bucketed by destination row, then one warp per row replays that row's updates.
+//   prepare: per tile, the destination row id of every entry; an entry that a later entry of the
+//            same tile overwrites is dropped (last writer wins).  A surviving entry takes the next
+//            slot of its row's bucket (atomic counter) and records its id and the resolved row
+//            addresses of its gathered inputs; entries beyond the bucket capacity go to an
+//            overflow list.
+//   apply:   one warp per destination row orders its bucket by entry id — which is tile order —
+//            and applies the updates one after another with the row held in registers: the row is
+//            read once and written once however many tiles touch it.
+// Scratch layout: int32 count[R + 1] (count[R] = overflow length) | int32 bucket_e[R * C] |
+// int64 bucket_addr[KTB_ROWS_MAX_IN][R * C] | int32 overflow[2 * E] (row, entry pairs).
+struct sc_scratch {
+    int32_t* count;
+    int32_t* bucket_e;
+    int64_t* bucket_addr;     // [k][R * C]
+    int32_t* overflow;
+    int32_t cap;              // C
+    int64_t slots;            // R * C
+};
+
+static inline int sc_bucket_cap(int64_t E, int64_t R) {
+    int64_t want = 2 * ((E + R - 1) / (R > 0 ? R : 1)) + 4;
+    int c = 4;
+    while (c < want && c < 32) c <<= 1;
+    return c;
+}
+
+static inline size_t sc_scratch_bytes(int64_t E, int64_t R) {
+    const int64_t slots = R * sc_bucket_cap(E, R);
+    return (size_t)(4 * (R + 2) + 4 * slots + 8 + 8 * (int64_t)KTB_ROWS_MAX_IN * slots + 8 * E + 64);
+}
+
+static inline sc_scratch sc_carve(void* base, int64_t E, int64_t R) {
+    sc_scratch s;
+    s.cap = sc_bucket_cap(E, R);
+    s.slots = R * s.cap;
+    s.count = reinterpret_cast<int32_t*>(base);
+    s.bucket_e = s.count + (R + 2);
+    uintptr_t p = reinterpret_cast<uintptr_t>(s.bucket_e + s.slots);
+    p = (p + 7) & ~(uintptr_t)7;
+    s.bucket_addr = reinterpret_cast<int64_t*>(p);
+    s.overflow = reinterpret_cast<int32_t*>(s.bucket_addr + (int64_t)KTB_ROWS_MAX_IN * s.slots);
+    return s;
+}
+
 __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_constant__ ktb_rows_args a,
-                                                                  int32_t* count, ktb_status* st) {
+                                                                  const sc_scratch sc, ktb_status* st) {
     extern __shared__ int64_t s_addr[];      // [tile_rows]
     for (int64_t t = blockIdx.x; t < a.n_tiles; t += gridDim.x) {
         for (int pos = threadIdx.x; pos < a.tile_rows; pos += blockDim.x) {
@@ -230,44 +266,23 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_c
             const int64_t mine = s_addr[pos];
             bool win = mine >= 0;
             for (int q = pos + 1; win && q < a.tile_rows; ++q) win = s_addr[q] != mine;
-            a.dev_rowid_scratch[t * a.tile_rows + pos] = win ? (int32_t)mine : -1;
-            if (win) atomicAdd(&count[mine], 1);
+            if (!win) continue;
+            const int32_t e = (int32_t)(t * a.tile_rows + pos);
+            const int slot = atomicAdd(&sc.count[mine], 1);
+            if (slot < sc.cap) {
+                const int64_t at = mine * sc.cap + slot;
+                sc.bucket_e[at] = e;
+#pragma unroll
+                for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+                    if (k < a.n_in && !a.in[k].alias_dst)
+                        sc.bucket_addr[(int64_t)k * sc.slots + at] = sc_row_addr(a.arena, a.in[k], t, pos, st);
+            } else {
+                const int o = atomicAdd(&sc.count[a.dst_rows], 1);
+                sc.overflow[2 * o] = (int32_t)mine;
+                sc.overflow[2 * o + 1] = e;
+            }
         }
         __syncthreads();
-    }
-}
-
-// offsets[r] = sum of count[0..r), offsets[R] = total; count[] becomes the fill cursor (= offsets).
-__global__ void __launch_bounds__(1024) ktb_scatter_scan_kernel(int32_t* count, int32_t* offsets, int64_t R) {
-    __shared__ int32_t part[1024];
-    const int tid = threadIdx.x;
-    const int64_t per = (R + 1023) / 1024;
-    const int64_t lo = tid * per, hi = lo + per < R ? lo + per : R;
-    int32_t sum = 0;
-    for (int64_t i = lo; i < hi; ++i) sum += count[i];
-    part[tid] = sum;
-    __syncthreads();
-    for (int d = 1; d < 1024; d <<= 1) {
-        const int32_t v = tid >= d ? part[tid - d] : 0;
-        __syncthreads();
-        part[tid] += v;
-        __syncthreads();
-    }
-    int32_t run = part[tid] - sum;
-    for (int64_t i = lo; i < hi; ++i) {
-        const int32_t c = count[i];
-        offsets[i] = run;
-        count[i] = run;
-        run += c;
-    }
-    if (tid == 1023) offsets[R] = part[1023];
-}
-
-__global__ void __launch_bounds__(256) ktb_scatter_fill_kernel(const int32_t* rowid, int32_t* cursor, int32_t* sorted_e,
-                                                               int64_t E) {
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < E; e += (int64_t)gridDim.x * blockDim.x) {
-        const int32_t r = rowid[e];
-        if (r >= 0) sorted_e[atomicAdd(&cursor[r], 1)] = (int32_t)e;
     }
 }
 
@@ -307,8 +322,7 @@ static __device__ __forceinline__ void sc_apply_one(const ktb_rows_args& a, cons
 
 template <int V, int PROG>
 __global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a,
-                                                                const int32_t* sorted_e, const int32_t* offsets,
-                                                                ktb_status* st) {
+                                                                const sc_scratch sc, ktb_status* st) {
     constexpr int G = 4;
     extern __shared__ float4 sa_vm[];                 // [KTB_VM_REGS][blockDim.x] register file
     float4* vm = sa_vm + threadIdx.x;
@@ -320,16 +334,18 @@ __global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_con
     for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) rmw = rmw || (k < a.n_in && a.in[k].alias_dst);
 
     for (int64_t row = warp; row < a.dst_rows; row += n_warps) {
-        const int32_t lo = offsets[row], hi = offsets[row + 1];
-        const int cnt = hi - lo;
+        const int cnt = sc.count[row];
         if (cnt == 0) continue;
         const int64_t dst = a.dst_row0 + row * a.out.idx_mult;
-        if (cnt <= 32) {
-            const int32_t e = lane < cnt ? sorted_e[lo + lane] : 0x7fffffff;
+        if (cnt <= sc.cap) {
+            const int64_t at = row * sc.cap + lane;
+            const int32_t e = lane < cnt ? sc.bucket_e[at] : 0x7fffffff;
+            int64_t my_in[KTB_ROWS_MAX_IN];
+#pragma unroll
+            for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+                my_in[k] = (lane < cnt && k < a.n_in && !a.in[k].alias_dst) ? sc.bucket_addr[(int64_t)k * sc.slots + at] : 0;
             int rank = 0;
             for (int j = 0; j < cnt; ++j) rank += __shfl_sync(0xffffffffu, e, j) < e ? 1 : 0;
-            int64_t my_in[KTB_ROWS_MAX_IN];
-            sc_resolve(a, lane < cnt ? (uint32_t)e : 0u, st, my_in);
             const int first = rmw ? 0 : cnt - 1;      // a plain overwrite only keeps the last writer
             for (int c0 = 0; c0 < a.cols; c0 += 32 * V) {     // uniform trip count: the body shuffles
                 const int col = c0 + lane * V;
@@ -348,8 +364,11 @@ __global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_con
                         ok[g] = m != 0;
 #pragma unroll
                         for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) {
-                            in_addr[g][k] = sc_shfl64(my_in[k], src);
-                            if (k < a.n_in && !a.in[k].alias_dst) ok[g] = ok[g] && in_addr[g][k] >= 0;
+                            in_addr[g][k] = 0;
+                            if (k < a.n_in && !a.in[k].alias_dst) {
+                                in_addr[g][k] = sc_shfl64(my_in[k], src);
+                                ok[g] = ok[g] && in_addr[g][k] >= 0;
+                            }
                         }
                     }
                     float x[G][KTB_ROWS_MAX_IN][V];
@@ -369,8 +388,10 @@ __global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_con
                 if (act) sc_store_row<V>(a.arena, a.out, dst, col, a.cols, cur);
             }
         } else {
-            // long chain (one row hit by more than 32 tiles): select the entries in ascending order
-            for (int c0 = 0; c0 < a.cols; c0 += 32 * V) {     // uniform trip count: the body shuffles
+            // long chain (more tiles hit this row than a bucket holds): the entries are in the bucket
+            // and in the overflow list; they are selected one by one in ascending entry id
+            const int n_ovf = sc.count[a.dst_rows];
+            for (int c0 = 0; c0 < a.cols; c0 += 32 * V) {
                 const int col = c0 + lane * V;
                 const bool act = col < a.cols;
                 float cur[V];
@@ -379,19 +400,20 @@ __global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_con
                 if (rmw && act) sc_load_row<V>(a.arena, a.out, dst, col, a.cols, cur);
                 int32_t prev = -1;
                 for (int step = 0; step < cnt; ++step) {
-                    int32_t best = 0x7fffffff;
-                    if (rmw) {
-                        for (int i = lo + lane; i < hi; i += 32) {
-                            const int32_t v = sorted_e[i];
-                            if (v > prev && v < best) best = v;
-                        }
-                        for (int d = 16; d; d >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, d));
-                    } else {
-                        best = -1;
-                        for (int i = lo + lane; i < hi; i += 32) best = max(best, sorted_e[i]);
-                        for (int d = 16; d; d >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, d));
-                        step = cnt;            // only the last writer matters
+                    int32_t best = rmw ? 0x7fffffff : -1;
+                    for (int i = lane; i < sc.cap + n_ovf; i += 32) {
+                        int32_t v = -1;
+                        if (i < sc.cap) v = sc.bucket_e[row * sc.cap + i];
+                        else if (sc.overflow[2 * (i - sc.cap)] == (int32_t)row) v = sc.overflow[2 * (i - sc.cap) + 1];
+                        if (v < 0) continue;
+                        if (rmw) { if (v > prev && v < best) best = v; }
+                        else best = max(best, v);
                     }
+                    for (int d = 16; d; d >>= 1) {
+                        const int32_t o = __shfl_xor_sync(0xffffffffu, best, d);
+                        best = rmw ? min(best, o) : max(best, o);
+                    }
+                    if (!rmw) step = cnt;              // only the last writer matters
                     prev = best;
                     int64_t in_addr[KTB_ROWS_MAX_IN];
                     sc_resolve(a, (uint32_t)best, st, in_addr);
@@ -493,25 +515,17 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (a.dst_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "too many destination rows");
     if (a.n_tiles == 0) return KTB_OK;
     const int64_t E = a.n_tiles * a.tile_rows, R = a.dst_rows;
-    int32_t* sorted_e = scratch + E;
-    int32_t* count = scratch + 2 * E;
-    int32_t* offsets = count + R;
-    KTB_CUDA(ctx, cudaMemsetAsync(count, 0, (size_t)R * sizeof(int32_t), ctx->stream));
+    const sc_scratch sc = sc_carve(scratch, E, R);
+    KTB_CUDA(ctx, cudaMemsetAsync(sc.count, 0, (size_t)(R + 1) * sizeof(int32_t), ctx->stream));
     int64_t prep_blocks = a.n_tiles < (int64_t)ctx->sm_count * 16 ? a.n_tiles : (int64_t)ctx->sm_count * 16;
     const size_t smem = (size_t)a.tile_rows * sizeof(int64_t);
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
-    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, count, ctx->dev_status);
+    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, sc, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
-    ktb_scatter_scan_kernel<<<1, 1024, 0, ctx->stream>>>(count, offsets, R);
-    KTB_CHECK_LAUNCH(ctx, "ktb_scatter_scan_kernel");
-    int64_t fill_blocks = (E + 255) / 256;
-    if (fill_blocks > (int64_t)ctx->sm_count * 32) fill_blocks = (int64_t)ctx->sm_count * 32;
-    ktb_scatter_fill_kernel<<<(unsigned)fill_blocks, 256, 0, ctx->stream>>>(scratch, count, sorted_e, E);
-    KTB_CHECK_LAUNCH(ctx, "ktb_scatter_fill_kernel");
     int64_t blocks = (R + 7) / 8;
     if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
     const size_t asmem = (size_t)KTB_VM_REGS * 256 * sizeof(float4);
-#define KTB_SA(V, P) ktb_scatter_apply_kernel<V, P><<<(unsigned)blocks, 256, asmem, ctx->stream>>>(a, sorted_e, offsets, ctx->dev_status)
+#define KTB_SA(V, P) ktb_scatter_apply_kernel<V, P><<<(unsigned)blocks, 256, asmem, ctx->stream>>>(a, sc, ctx->dev_status)
     switch (sc_classify(a) * 2 + (a.vector_ok ? 1 : 0)) {
         case SC_PROG_COPY * 2 + 1: KTB_SA(4, SC_PROG_COPY); break;
         case SC_PROG_COPY * 2: KTB_SA(1, SC_PROG_COPY); break;
@@ -524,6 +538,10 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
 #undef KTB_SA
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_apply_kernel");
     return KTB_OK;
+}
+
+extern "C" size_t ktb_scatter_scratch_bytes(int64_t entries, int64_t dst_rows) {
+    return sc_scratch_bytes(entries, dst_rows);
 }
 
 extern "C" int ktb_launch_scatter_rows(ktb_ctx* ctx, const ktb_rows_args* args) {

@@ -231,8 +231,10 @@ class RowsStatement(Statement):
             a.dst_row0 = int(out.base[0]) if n_tiles else 0
             bpe = bytes_per_elem(out.dtype)
             a.dst_rows = max(0, (dst_alloc.byte_hi // bpe - a.dst_row0 - out.cols) // out.idx_mult + 1)
-            # rowid[E] | sorted_e[E] | count[R] | offsets[R + 1] (int32 each)
-            self.scratch = dev.alloc(8 * n_tiles * out.rows + 8 * int(a.dst_rows) + 64)
+            nbytes = 1 << 20
+            if getattr(dev, "lib", None) is not None:
+                nbytes = int(dev.lib.ktb_scatter_scratch_bytes(n_tiles * out.rows, int(a.dst_rows)))
+            self.scratch = dev.alloc(nbytes)
             self.device_arrays.append(self.scratch)
             a.dev_rowid_scratch = self.scratch
             self.launches = 2
