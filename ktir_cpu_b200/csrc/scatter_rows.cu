@@ -321,9 +321,9 @@ static __device__ __forceinline__ void sc_apply_one(const ktb_rows_args& a, cons
 }
 
 template <int V, int PROG>
-__global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a,
-                                                                const sc_scratch sc, ktb_status* st) {
-    constexpr int G = 4;
+__global__ void __launch_bounds__(256, 4) ktb_scatter_apply_kernel(const __grid_constant__ ktb_rows_args a,
+                                                                   const sc_scratch sc, ktb_status* st) {
+    constexpr int G = 2;
     extern __shared__ float4 sa_vm[];                 // [KTB_VM_REGS][blockDim.x] register file
     float4* vm = sa_vm + threadIdx.x;
     const int lane = threadIdx.x & 31;
@@ -333,17 +333,34 @@ __global__ void __launch_bounds__(256) ktb_scatter_apply_kernel(const __grid_con
 #pragma unroll
     for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) rmw = rmw || (k < a.n_in && a.in[k].alias_dst);
 
+    // the count and the bucket of the NEXT row are fetched while the current row is applied, so only
+    // the gathered rows themselves remain on the dependent-load path
+    const int bl = lane < sc.cap ? lane : 0;
+    int cnt_n = warp < a.dst_rows ? sc.count[warp] : 0;
+    int32_t e_n = warp < a.dst_rows ? sc.bucket_e[warp * sc.cap + bl] : 0;
+    int64_t in_n[KTB_ROWS_MAX_IN];
+#pragma unroll
+    for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+        in_n[k] = (warp < a.dst_rows && k < a.n_in && !a.in[k].alias_dst) ? sc.bucket_addr[(int64_t)k * sc.slots + warp * sc.cap + bl] : 0;
+
     for (int64_t row = warp; row < a.dst_rows; row += n_warps) {
-        const int cnt = sc.count[row];
+        const int cnt = cnt_n;
+        const int32_t e_cur = e_n;
+        int64_t my_in[KTB_ROWS_MAX_IN];
+#pragma unroll
+        for (int k = 0; k < KTB_ROWS_MAX_IN; ++k) my_in[k] = in_n[k];
+        const int64_t nrow = row + n_warps;
+        if (nrow < a.dst_rows) {
+            cnt_n = sc.count[nrow];
+            e_n = sc.bucket_e[nrow * sc.cap + bl];
+#pragma unroll
+            for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
+                if (k < a.n_in && !a.in[k].alias_dst) in_n[k] = sc.bucket_addr[(int64_t)k * sc.slots + nrow * sc.cap + bl];
+        }
         if (cnt == 0) continue;
         const int64_t dst = a.dst_row0 + row * a.out.idx_mult;
         if (cnt <= sc.cap) {
-            const int64_t at = row * sc.cap + lane;
-            const int32_t e = lane < cnt ? sc.bucket_e[at] : 0x7fffffff;
-            int64_t my_in[KTB_ROWS_MAX_IN];
-#pragma unroll
-            for (int k = 0; k < KTB_ROWS_MAX_IN; ++k)
-                my_in[k] = (lane < cnt && k < a.n_in && !a.in[k].alias_dst) ? sc.bucket_addr[(int64_t)k * sc.slots + at] : 0;
+            const int32_t e = lane < cnt ? e_cur : 0x7fffffff;
             int rank = 0;
             for (int j = 0; j < cnt; ++j) rank += __shfl_sync(0xffffffffu, e, j) < e ? 1 : 0;
             const int first = rmw ? 0 : cnt - 1;      // a plain overwrite only keeps the last writer
@@ -517,10 +534,12 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     const int64_t E = a.n_tiles * a.tile_rows, R = a.dst_rows;
     const sc_scratch sc = sc_carve(scratch, E, R);
     KTB_CUDA(ctx, cudaMemsetAsync(sc.count, 0, (size_t)(R + 1) * sizeof(int32_t), ctx->stream));
-    int64_t prep_blocks = a.n_tiles < (int64_t)ctx->sm_count * 16 ? a.n_tiles : (int64_t)ctx->sm_count * 16;
+    int64_t prep_blocks = a.n_tiles < (1 << 20) ? a.n_tiles : (1 << 20);
     const size_t smem = (size_t)a.tile_rows * sizeof(int64_t);
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
-    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, 128, smem, ctx->stream>>>(a, sc, ctx->dev_status);
+    int prep_threads = (a.tile_rows + 31) / 32 * 32;
+    if (prep_threads > 128) prep_threads = 128;
+    ktb_scatter_prepare_kernel<<<(unsigned)prep_blocks, prep_threads, smem, ctx->stream>>>(a, sc, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_scatter_prepare_kernel");
     int64_t blocks = (R + 7) / 8;
     if (blocks > (int64_t)ctx->sm_count * 32) blocks = (int64_t)ctx->sm_count * 32;
