@@ -180,6 +180,15 @@ int ktb_launch_rows_program(ktb_ctx* ctx, const ktb_rows_args* args);
 int ktb_launch_scatter_rows(ktb_ctx* ctx, const ktb_rows_args* args);
 /* Bytes of device scratch ktb_launch_scatter_rows needs for this many entries and destination rows. */
 size_t ktb_scatter_scratch_bytes(int64_t entries, int64_t dst_rows);
+/* ktb_launch_scatter_rows for callers that may not allocate: `dev_rowid_scratch` is ignored and
+ * the scratch is a fixed KTB_SCATTER_STATIC_BYTES array inside the library, so the call makes no
+ * device or host allocation.  A statement whose ktb_scatter_scratch_bytes() exceeds the array
+ * is rejected with KTB_E_UNSUPPORTED.  The first call on a device looks the array's address up
+ * and should come before any stream capture; all calls on a device share the array, so they
+ * must not overlap in time.  No counterpart in the reference, whose allocator is a Python dict
+ * (ktir_cpu/memory.py:311-345). */
+#define KTB_SCATTER_STATIC_BYTES (8u << 20)
+int ktb_launch_scatter_rows_static(ktb_ctx* ctx, const ktb_rows_args* args);
 
 /* ---- dense f16 GEMM on tensor cores -------------------------------------------------
  * C[M,N] = A[M,K] * B[K,N] + c_init, row-major operands in the arena, f32 accumulation

@@ -567,3 +567,48 @@ extern "C" int ktb_launch_scatter_rows(ktb_ctx* ctx, const ktb_rows_args* args) 
     if (!ctx || !args) return KTB_E_ARG;
     return ktb_scatter_rows_impl(ctx, *args, args->dev_rowid_scratch);
 }
+
+// ---- scatter without a caller-provided scratch buffer ---------------------------------------
+// The same launches as ktb_launch_scatter_rows, with the bucket scratch taken from a fixed array
+// in device global memory that is part of the loaded library image.  The entry point performs no
+// device or host allocation of any kind, so it can be used by callers that must not allocate:
+// code running while an allocator lock is held, a steady-state serving loop whose memory budget
+// was fixed at start-up, or a host thread that may not synchronise with the device (cudaFree and
+// some cudaMalloc calls do).
+//
+// The array's name in host code is only a handle of the symbol; the device address is looked up
+// with cudaGetSymbolAddress once per device, on the first call for that device, with that device
+// made current.  That first call should therefore come before any stream capture is started.
+// All calls on a device share the one array: nothing in it needs to survive between calls (the
+// per-row counters, the only part that must start at zero, are cleared on the stream at the start
+// of every call), but two calls in flight at the same time on different streams would race on it.
+static __device__ __align__(256) unsigned char ktb_scatter_static_scratch[KTB_SCATTER_STATIC_BYTES];
+
+#define KTB_STATIC_MAX_DEVICES 64
+static int32_t* sc_static_ptr[KTB_STATIC_MAX_DEVICES];   // device address of the array, per device
+
+extern "C" int ktb_launch_scatter_rows_static(ktb_ctx* ctx, const ktb_rows_args* args) {
+    if (!ctx || !args) return KTB_E_ARG;
+    const ktb_rows_args& a = *args;
+    if (a.n_tiles < 0 || a.tile_rows <= 0 || a.dst_rows <= 0)
+        return ktb_fail(ctx, KTB_E_ARG, "scatter_rows_static", "bad tile or destination row geometry");
+    if (a.n_tiles >= (1ll << 31) / a.tile_rows || a.dst_rows >= (1ll << 31))
+        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows_static", "too many entries or destination rows");
+    const size_t need = sc_scratch_bytes(a.n_tiles * a.tile_rows, a.dst_rows);
+    if (need > (size_t)KTB_SCATTER_STATIC_BYTES) {
+        char msg[160];
+        snprintf(msg, sizeof(msg), "needs %zu bytes of scratch, the built-in array holds %zu; use ktb_launch_scatter_rows",
+                 need, (size_t)KTB_SCATTER_STATIC_BYTES);
+        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows_static", msg);
+    }
+    if (ctx->device < 0 || ctx->device >= KTB_STATIC_MAX_DEVICES)
+        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows_static", "device ordinal out of range");
+    KTB_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!sc_static_ptr[ctx->device]) {
+        void* p = nullptr;
+        KTB_CUDA(ctx, cudaGetSymbolAddress(&p, ktb_scatter_static_scratch));
+        if (!p) return ktb_fail(ctx, KTB_E_CUDA, "scatter_rows_static", "symbol lookup returned a null address");
+        sc_static_ptr[ctx->device] = reinterpret_cast<int32_t*>(p);
+    }
+    return ktb_scatter_rows_impl(ctx, a, sc_static_ptr[ctx->device]);
+}

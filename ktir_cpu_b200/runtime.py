@@ -117,6 +117,7 @@ SYMBOLS = {
     "ktb_launch_rows_program": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
     "ktb_launch_scatter_rows": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
     "ktb_scatter_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "ktb_launch_scatter_rows_static": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
     "ktb_launch_gemm_f16": (C.c_int, [C.c_void_p, C.POINTER(GemmArgs)]),
     "ktb_launch_attention_fwd": (C.c_int, [C.c_void_p, C.POINTER(AttnArgs)]),
 }
