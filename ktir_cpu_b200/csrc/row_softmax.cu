@@ -216,8 +216,21 @@ __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3) ktb_row_softmax_kernel(c
 // exp is ex2.approx of an FMA-scaled argument and therefore not bit-comparable with NumPy anyway,
 // so the sum uses a plain per-thread accumulation + butterfly instead of the halving order.
 // About 6 instructions per element; the row is read once and written once.
-template <int NV, bool MAXNUM>
-__global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3)
+static __device__ __forceinline__ void sm_row_exp(const uint4& raw, float mxs, float (&p)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        p[2 * i] = sm_ex2(__fmaf_rn(f.x, 1.4426950408889634f, -mxs));
+        p[2 * i + 1] = sm_ex2(__fmaf_rn(f.y, 1.4426950408889634f, -mxs));
+    }
+}
+
+// RECOMP: the row stays in registers as packed f16 (NV x 4 registers) and exp is evaluated twice,
+// once for the sum and once for the output (same instruction sequence, so the same bits), instead
+// of holding NV x 8 f32 values; half the registers, twice the resident rows per SM.
+template <int NV, bool MAXNUM, bool RECOMP, bool PREF>
+__global__ void __launch_bounds__(256, RECOMP ? (NV >= 16 ? 2 : NV >= 8 ? (PREF ? 2 : 4) : (PREF ? 4 : 6)) : (NV >= 8 ? 2 : 3))
 ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows) {
     __shared__ float xmax[8], xsum[8];            // one slot per warp of the CTA
     const int groups = 256 / T;
@@ -228,6 +241,15 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
     const __half* in16 = reinterpret_cast<const __half*>(a.arena);
     const int w = T < 32 ? T : 32;
     const int64_t n_iter = (total_rows + groups - 1) / groups;
+    uint4 nxt[PREF ? NV : 1];
+    if (PREF && blockIdx.x < n_iter) {
+        const int64_t row = blockIdx.x * (int64_t)groups + group < total_rows ? blockIdx.x * (int64_t)groups + group : 0;
+        const int64_t item = row / a.rows_per_item;
+        const uint4* src = reinterpret_cast<const uint4*>(in16 + a.dev_item_offsets[item * 2] +
+                                                          (row - item * a.rows_per_item) * a.in_row_stride) + t;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) nxt[PREF ? j : 0] = __ldcs(src + (int64_t)j * T);
+    }
     for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
         const bool live = it * groups + group < total_rows;
         const int64_t row = live ? it * groups + group : 0;
@@ -238,8 +260,23 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
         const uint4* src = reinterpret_cast<const uint4*>(in16 + in_off) + t;
 
         uint4 raw[NV];
+        if (PREF) {
+            // this row was requested one iteration ago; request the next one before any arithmetic
 #pragma unroll
-        for (int j = 0; j < NV; ++j) raw[j] = __ldcs(src + (int64_t)j * T);
+            for (int j = 0; j < NV; ++j) raw[j] = nxt[PREF ? j : 0];
+            const int64_t nit = it + gridDim.x;
+            if (nit < n_iter) {
+                const int64_t nrow = nit * groups + group < total_rows ? nit * groups + group : 0;
+                const int64_t nitem = nrow / a.rows_per_item;
+                const uint4* nsrc = reinterpret_cast<const uint4*>(in16 + a.dev_item_offsets[nitem * 2] +
+                                                                   (nrow - nitem * a.rows_per_item) * a.in_row_stride) + t;
+#pragma unroll
+                for (int j = 0; j < NV; ++j) nxt[PREF ? j : 0] = __ldcs(nsrc + (int64_t)j * T);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV; ++j) raw[j] = __ldcs(src + (int64_t)j * T);
+        }
 
         __half2 m2 = *reinterpret_cast<const __half2*>(&raw[0].x);
 #pragma unroll
@@ -264,7 +301,7 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
         mx = sm_max<MAXNUM>(mx, a.max_init);
         const float mxs = mx * 1.4426950408889634f;
 
-        float p[NV][8];
+        float p[RECOMP ? 1 : NV][8];
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
@@ -272,13 +309,14 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 f = __half22float2(h[i]);
-                p[j][2 * i] = sm_ex2(__fmaf_rn(f.x, 1.4426950408889634f, -mxs));
-                p[j][2 * i + 1] = sm_ex2(__fmaf_rn(f.y, 1.4426950408889634f, -mxs));
+                p[RECOMP ? 0 : j][2 * i] = sm_ex2(__fmaf_rn(f.x, 1.4426950408889634f, -mxs));
+                p[RECOMP ? 0 : j][2 * i + 1] = sm_ex2(__fmaf_rn(f.y, 1.4426950408889634f, -mxs));
             }
-            s0 += p[j][0] + p[j][1];
-            s1 += p[j][2] + p[j][3];
-            s2 += p[j][4] + p[j][5];
-            s3 += p[j][6] + p[j][7];
+            const float(&q)[8] = p[RECOMP ? 0 : j];
+            s0 += q[0] + q[1];
+            s1 += q[2] + q[3];
+            s2 += q[4] + q[5];
+            s3 += q[6] + q[7];
         }
         float sum = (s0 + s1) + (s2 + s3);
         for (int d = w >> 1; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, w);
@@ -291,22 +329,33 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
         }
         const float inv = 1.0f / (sum + a.sum_init);
         if (!live) continue;
+        if (RECOMP) {
+            // opaque to the optimiser: otherwise the converted values of the first evaluation are
+            // kept alive for the second one, which is the register footprint this variant avoids
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+                asm volatile("" : "+r"(raw[j].x), "+r"(raw[j].y), "+r"(raw[j].z), "+r"(raw[j].w));
+        }
         if (a.out_dtype == KTB_F16) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + out_off) + t;
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
+                if (RECOMP) sm_row_exp(raw[j], mxs, p[0]);
+                const float(&pj)[8] = p[RECOMP ? 0 : j];
                 uint4 o;
                 __half2* h = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(p[j][2 * i] * inv, p[j][2 * i + 1] * inv);
+                for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(pj[2 * i] * inv, pj[2 * i + 1] * inv);
                 __stcs(dst + (int64_t)j * T, o);
             }
         } else {
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
+                if (RECOMP) sm_row_exp(raw[j], mxs, p[0]);
+                const float(&pj)[8] = p[RECOMP ? 0 : j];
                 float* q = reinterpret_cast<float*>(a.arena) + out_off + ((int64_t)j * T + t) * 8;
-                __stcs(reinterpret_cast<float4*>(q), make_float4(p[j][0] * inv, p[j][1] * inv, p[j][2] * inv, p[j][3] * inv));
-                __stcs(reinterpret_cast<float4*>(q + 4), make_float4(p[j][4] * inv, p[j][5] * inv, p[j][6] * inv, p[j][7] * inv));
+                __stcs(reinterpret_cast<float4*>(q), make_float4(pj[0] * inv, pj[1] * inv, pj[2] * inv, pj[3] * inv));
+                __stcs(reinterpret_cast<float4*>(q + 4), make_float4(pj[4] * inv, pj[5] * inv, pj[6] * inv, pj[7] * inv));
             }
         }
     }
@@ -320,16 +369,27 @@ static void launch_softmax(ktb_ctx* ctx, const ktb_softmax_args& a, int T, int64
     if (blocks > n_iter) blocks = n_iter;
     const bool mn = a.max_is_maxnum != 0, r16 = a.f16_arith != 0;
     if (a.in_dtype == KTB_F16 && !r16) {
-        if (mn) ktb_row_softmax_fast_kernel<NV, true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows);
-        else ktb_row_softmax_fast_kernel<NV, false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows);
+        int mode = 1;                  // 0: exp kept in registers, 1: exp evaluated twice, 2: + next-row prefetch
+        if (const char* e = getenv("KTB_SOFTMAX_RECOMP")) mode = atoi(e);
+        if (NV >= 16 && mode == 0) mode = 1;
+        int per_sm = mode == 2 ? (NV >= 8 ? 2 : 4) : 8;
+        if (const char* e = getenv("KTB_SOFTMAX_CTAS")) per_sm = atoi(e) > 0 ? atoi(e) : per_sm;
+        if (mode) blocks = n_iter < (int64_t)ctx->sm_count * per_sm ? n_iter : (int64_t)ctx->sm_count * per_sm;
+#define KTB_SMF(MN, RC, PF) ktb_row_softmax_fast_kernel<NV, MN, RC, PF><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows)
+        if (mode == 2 && NV <= 8) { if constexpr (NV <= 8) { if (mn) KTB_SMF(true, true, true); else KTB_SMF(false, true, true); } }
+        else if (mode) { if (mn) KTB_SMF(true, true, false); else KTB_SMF(false, true, false); }
+        else if constexpr (NV <= 8) { if (mn) KTB_SMF(true, false, false); else KTB_SMF(false, false, false); }
+#undef KTB_SMF
         return;
     }
+    if constexpr (NV <= 8) {
 #define KTB_SM_LAUNCH(MN, R) ktb_row_softmax_kernel<NV, MN, R><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows)
-    if (mn && r16) KTB_SM_LAUNCH(true, true);
-    else if (mn) KTB_SM_LAUNCH(true, false);
-    else if (r16) KTB_SM_LAUNCH(false, true);
-    else KTB_SM_LAUNCH(false, false);
+        if (mn && r16) KTB_SM_LAUNCH(true, true);
+        else if (mn) KTB_SM_LAUNCH(true, false);
+        else if (r16) KTB_SM_LAUNCH(false, true);
+        else KTB_SM_LAUNCH(false, false);
 #undef KTB_SM_LAUNCH
+    }
 }
 
 extern "C" int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args) {
@@ -346,7 +406,7 @@ extern "C" int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args
     int per_thread = 8;               // vectors per thread (tunable for experiments)
     if (const char* e = getenv("KTB_SOFTMAX_NV")) {
         const int v = atoi(e);
-        if (v == 1 || v == 2 || v == 4 || v == 8) per_thread = v;
+        if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) per_thread = v;
     }
     int T = vecs / per_thread;
     if (T < 1) T = 1;
@@ -358,6 +418,9 @@ extern "C" int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args
         case 2: launch_softmax<2>(ctx, a, T, total_rows); break;
         case 4: launch_softmax<4>(ctx, a, T, total_rows); break;
         case 8: launch_softmax<8>(ctx, a, T, total_rows); break;
+        case 16:
+            if (a.in_dtype == KTB_F16 && !a.f16_arith) { launch_softmax<16>(ctx, a, T, total_rows); break; }
+            return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_softmax", "unsupported row width");
         default: return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_softmax", "unsupported row width");
     }
     KTB_CHECK_LAUNCH(ctx, "ktb_row_softmax_kernel");
