@@ -283,9 +283,16 @@ class ClockSampler:
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
-            time.sleep(0.3)
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 5.0:      # first sample = the sampler is live
+                time.sleep(0.02)
+            self.first = len(self.rows)
         except Exception:
             self.proc = None
+
+    def under_load(self):
+        """Samples taken since start() returned."""
+        return len(self.rows) - getattr(self, "first", 0)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -294,8 +301,8 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.1)
         self.proc.terminate()
+        self.rows = self.rows[getattr(self, "first", 0):]
 
         def num(s):
             try:
@@ -432,6 +439,12 @@ def run_gpu(args, w):
         per_step.append(dev.elapsed_ms(0, 1))
     launches = dev.launch_count() - l0
     dev.sync()
+    # a timed region shorter than the sampling period: keep the same load running (untimed) until
+    # the sampler has seen it a few times
+    t_extra = time.time()
+    while sampler.proc is not None and sampler.under_load() < 4 and time.time() - t_extra < 3.0:
+        sess.run()
+        dev.sync()
     barrier()
     clocks = sampler.stop()
     total_ms = float(sum(per_step))
@@ -460,7 +473,9 @@ def run_gpu(args, w):
         traffic = None
         tp = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tp):
-            traffic = json.load(open(tp)).get(w.name)
+            t = json.load(open(tp)).get(w.name)
+            if t:        # DRAM bytes of one launch of the dominant kernel, from the ncu capture summarised in profiles/
+                traffic = t["dram_read_bytes"] + t["dram_write_bytes"]
         line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps,
                 "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": workload_config(w, world),
