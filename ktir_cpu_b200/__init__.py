@@ -2,10 +2,13 @@
 
 Public surface mirrors ``ktir_cpu`` (ktir_cpu/__init__.py:23-27):
 ``KTIRInterpreter`` with ``load`` / ``arg_names`` / ``tensor_input_output_sizes`` /
-``execute_function`` / ``get_latency_report``, plus ``KTIRParserBase`` as the parser seam.
+``execute_function`` / ``get_latency_report``, the latency model's ``HardwareConfig`` /
+``ExecutionModel`` / ``LatencyReport``, plus ``KTIRParserBase`` as the parser seam.
 """
 from .interpreter import KTIRInterpreter, Session
+from .latency import ExecutionModel, HardwareConfig, LatencyReport
 from .parser import KTIRParser, KTIRParserBase
 from .trace import Unsupported
 
-__all__ = ["KTIRInterpreter", "KTIRParser", "KTIRParserBase", "Session", "Unsupported"]
+__all__ = ["KTIRInterpreter", "ExecutionModel", "HardwareConfig", "LatencyReport", "KTIRParser", "KTIRParserBase",
+           "Session", "Unsupported"]

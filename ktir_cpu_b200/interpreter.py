@@ -29,13 +29,58 @@ STICK = 128
 ARENA_BASE = 0x10000
 
 
+def arena_layout(tensors):
+    """name -> (byte offset, nbytes, shape, dtype) and name -> element pointer, in argument order.
+
+    The first tensor sits at 0x10000 and each one starts on a 128-byte stick, like
+    HBMSimulator.allocate (ktir_cpu/memory.py:330-352).
+    """
+    layout, ptrs = {}, {}
+    nxt = ARENA_BASE
+    for name, shape, dt in tensors:
+        dt = np.dtype(dt)
+        nbytes = int(np.prod(shape)) * dt.itemsize if len(shape) else dt.itemsize
+        layout[name] = (nxt, nbytes, tuple(shape), dt)
+        ptrs[name] = nxt // bytes_per_elem(to_ktir_dtype(dt))
+        nxt = (nxt + nbytes + STICK - 1) & ~(STICK - 1)
+    return layout, ptrs
+
+
+def layout_of(sess) -> Dict[str, Tuple[int, int, Tuple[int, ...], np.dtype]]:
+    return sess.layout
+
+
+class HostTensors:
+    """Read access to the caller's arrays by KTIR element index (for data-dependent accounting)."""
+
+    def __init__(self, layout, kwargs):
+        self.spans = [(off, off + nbytes, np.ascontiguousarray(kwargs[name]).reshape(-1))
+                      for name, (off, nbytes, _, _) in layout.items() if isinstance(kwargs.get(name), np.ndarray)]
+
+    def read(self, dtype: str, elems: np.ndarray) -> np.ndarray:
+        bpe = bytes_per_elem(dtype)
+        elems = np.asarray(elems, np.int64)
+        if elems.size == 0:
+            return np.zeros(0, np.int64)
+        first = int(elems.min()) * bpe
+        for lo, hi, flat in self.spans:
+            if lo <= first < hi:
+                rel = elems - lo // bpe
+                ok = (rel >= 0) & (rel < flat.size)
+                out = np.zeros(elems.shape, np.int64)
+                out[ok] = flat[rel[ok]]
+                return out
+        raise ValueError(f"Read from unmapped address 0x{first:x}")
+
+
 class Session:
     """One function bound to one tensor layout: the arena in HBM plus its launch plan."""
 
     def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
-                 scalars: Dict[str, Any]):
+                 scalars: Dict[str, Any], latency: bool = False):
         self.dev = dev
         self.func = func
+        self.latency_records = None
         self.layout: Dict[str, Tuple[int, int, Tuple[int, ...], np.dtype]] = {}
         nxt = ARENA_BASE
         allocs = []
@@ -51,7 +96,14 @@ class Session:
         self.arena = dev.alloc(self.arena_bytes + 256)
         self.arena_map = ArenaMap(allocs)
         try:
-            stores = Tracer(func, scalars, ptrs).run()
+            tracer = Tracer(func, scalars, ptrs)
+            if latency:
+                from .trace_latency import LatencyRecorder
+                tracer.latency = LatencyRecorder(tracer.ncores)
+            stores = tracer.run()
+            if latency:
+                self.latency_records = tracer.latency.records
+            self.n_cores = tracer.ncores
             self.plan: Plan = lower(dev, stores, self.arena_map)
         except Exception:
             dev.free(self.arena)
@@ -114,6 +166,10 @@ class KTIRInterpreter:
         self._sessions: Dict[Any, Session] = {}
         self._max_sessions = max_sessions
         self._latency_report = None
+        self._latency_tracker = None
+        if latency_config is not None:
+            from .latency import LatencyTracker
+            self._latency_tracker = LatencyTracker(latency_config, trace=trace_latency)
         self._pool = None
 
     # -- front end ------------------------------------------------------------
@@ -138,7 +194,11 @@ class KTIRInterpreter:
         return self._require_module().get_function(func_name).tensor_sizes
 
     def get_latency_report(self):
-        return self._latency_report
+        """Report of the most recent call, or None without a ``latency_config``
+        (ktir_cpu/interpreter.py:337-341)."""
+        if self._latency_tracker is None:
+            return None
+        return self._latency_tracker.report()
 
     # -- device -----------------------------------------------------------------
     @property
@@ -185,7 +245,7 @@ class KTIRInterpreter:
             if len(self._sessions) >= self._max_sessions:
                 old = next(iter(self._sessions))
                 self._sessions.pop(old).close()
-            sess = Session(self.device, func, tensors, scalars)
+            sess = Session(self.device, func, tensors, scalars, latency=self._latency_config is not None)
             self._sessions[key] = sess
         return sess, kwargs
 
@@ -216,4 +276,34 @@ class KTIRInterpreter:
         sess.dev.sync()
         sess.last_h2d_bytes, sess.last_d2h_bytes = h2d, d2h
         del keep
+        if self._latency_tracker is not None:
+            self._charge_latency(sess.latency_records, sess.n_cores, layout_of(sess), kwargs)
         return outputs
+
+    def _charge_latency(self, records, n_cores, layout, kwargs):
+        """Per-call latency accounting (reset + charge, interpreter.py:118-120 of the reference)."""
+        self._latency_tracker.reset()
+        self._latency_tracker.set_cores_active(n_cores)
+        self._latency_tracker.feed(records, HostTensors(layout, kwargs))
+
+    def estimate_latency(self, func_name: str, **kwargs):
+        """The latency report of a call without running it: host-only, needs no device.
+
+        Uses the same trace as ``execute_function``; index tensors are read from ``kwargs``
+        for the data-dependent stick counts of indirect tiles.
+        """
+        if self._latency_tracker is None:
+            return None
+        func = self._require_module().get_function(func_name)
+        declared = func.arg_names
+        if kwargs and declared and not any(k in declared for k in kwargs) and len(kwargs) == len(declared):
+            kwargs = dict(zip(declared, kwargs.values()))
+        tensors = [(k, tuple(v.shape), v.dtype) for k, v in kwargs.items() if isinstance(v, np.ndarray)]
+        scalars = {k: v for k, v in kwargs.items() if not isinstance(v, np.ndarray)}
+        layout, ptrs = arena_layout(tensors)
+        from .trace_latency import LatencyRecorder
+        tracer = Tracer(func, scalars, ptrs)
+        tracer.latency = LatencyRecorder(tracer.ncores)
+        tracer.run()
+        self._charge_latency(tracer.latency.records, tracer.ncores, layout, kwargs)
+        return self._latency_tracker.report()

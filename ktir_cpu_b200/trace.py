@@ -148,6 +148,7 @@ class Tracer:
         self.stores: List[Store] = []
         self.loop_path: List[int] = []
         self._loop_counter = 0
+        self.latency = None            # a trace_latency.LatencyRecorder when the latency model is on
         self.scope: Dict[str, Any] = {}
         for n, _ in func.args:
             key = n[1:]
@@ -191,9 +192,13 @@ class Tracer:
             if op.name.startswith("ktdp."):
                 raise Unsupported(f"{op.name} (cross-core / distributed ops have no device path yet)")
             raise ValueError(f"Unknown operation: {op.name}")
+        lat = self.latency
+        pre = lat.before_op(self, op, scope) if lat is not None else None
         r = fn(self, op, scope)
         if isinstance(r, _Yield):
             return r
+        if pre is not None:
+            lat.after_op(self, op, scope, r, pre)
         self.bind(op, scope, r)
         return r
 

@@ -2,7 +2,7 @@
 
 Usage (only where the reference checkout is available):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [--latency-only]
 
 Each fixture stores the KTIR source, the seeded inputs and the outputs the
 reference produced, plus the NumPy version and CPU features of the generating
@@ -88,5 +88,31 @@ def main(ref_root: str):
         print("wrote", name)
 
 
+def latency_main(ref_root: str):
+    """``latency.json``: the reference's latency report for every case above (default hardware)."""
+    import json
+    sys.path.insert(0, ref_root)
+    from ktir_cpu import HardwareConfig, KTIRInterpreter
+    out = {}
+    for name, (src, fn, kw) in cases().items():
+        interp = KTIRInterpreter(latency_config=HardwareConfig())
+        interp.load(src)
+        interp.execute_function(fn, **kw)
+        rep = interp.get_latency_report()
+        out[name] = {
+            "summary": rep.summary_dict(),
+            "roofline": rep.roofline(),
+            "flops": {str(c): dict(v.flops_by_category) for c, v in rep.counters.items()},
+            "bytes": {str(c): dict(v.bytes_by_category) for c, v in rep.counters.items()},
+        }
+        print("latency", name, rep.kernel_cycles, rep.bottleneck)
+    with open(os.path.join(HERE, "latency.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    root = args[0] if args else "/root/reference"
+    if "--latency-only" not in sys.argv:
+        main(root)
+    latency_main(root)

@@ -272,3 +272,17 @@ def test_causal_attention_long_sequence_properties(build_lib):
     np.testing.assert_allclose(o[0].astype(np.float32), v[0].astype(np.float32), rtol=2e-3, atol=2e-3)
     assert (o.astype(np.float32).max(0) <= v.astype(np.float32).max(0) + 1e-2).all()
     np.testing.assert_allclose(o.astype(np.float64), _attention_f64(q, k, v, D), rtol=1e-2, atol=2e-3)
+
+
+def test_latency_report_through_execute_function(build_lib):
+    """With a latency_config the device run also feeds the latency model (same report as the host-only estimate)."""
+    from ktir_cpu_b200 import HardwareConfig
+    src, fn, kwargs, outs = load_golden("gather_scale_scatter_256")
+    gpu = KTIRInterpreter(latency_config=HardwareConfig())
+    gpu.load(src)
+    res = gpu.execute_function(fn, **kwargs)
+    np.testing.assert_array_equal(res["out_ptr"], outs["out_ptr"])
+    rep = gpu.get_latency_report()
+    est = gpu.estimate_latency(fn, **kwargs)
+    assert rep.kernel_cycles == est.kernel_cycles == 6304.0 and rep.bottleneck == "memory"
+    gpu.close()
