@@ -496,6 +496,85 @@ def run_gpu(args, w):
         dist.destroy_process_group()
 
 
+def run_sharded(args, w):
+    """Strong scaling: ONE instance of the workload split over the ranks (core ranges, or
+    destination-row ownership for the ordered scatter), each step = this rank's launches + the
+    exchange of the written slabs over NCCL, so every rank ends with the full result."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from ktir_cpu_b200.interpreter import KTIRInterpreter
+    from ktir_cpu_b200.sharded import ShardedRun
+    interp = KTIRInterpreter(device=local)
+    interp.load(w.source())
+    kw = w.inputs(0)                                   # the same instance on every rank
+    run = ShardedRun(interp, w.func, rank, world, dist, **kw)
+    dev = interp.device
+    arrays = {k: v for k, v in kw.items() if isinstance(v, np.ndarray)}
+    run.upload(**arrays)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        if hasattr(w, "reset"):
+            run.upload(**arrays)
+        run.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total_ms = 0.0
+    l0 = dev.launch_count()
+    for _ in range(args.steps):
+        if hasattr(w, "reset"):
+            run.upload(**arrays)
+        dev.flush_l2()
+        torch.cuda.synchronize()
+        barrier()
+        ev0.record()
+        run.step()
+        ev1.record()
+        torch.cuda.synchronize()
+        total_ms += ev0.elapsed_time(ev1)
+    launches = dev.launch_count() - l0
+    for _ in range(200 if sampler.proc is not None else 0):   # same load, untimed, until the sampler has seen it
+        run.step()
+        torch.cuda.synchronize()
+        if world == 1 and sampler.under_load() >= 4:
+            break
+    barrier()
+    clocks = sampler.stop()
+    res = {k: run.download(k) for k in arrays}
+    err = w.check(kw, res) if not hasattr(w, "reset") else None
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t[0])
+    if rank == 0:
+        ms = total_ms / args.steps
+        slabs = sum(hi - lo for lo, hi in run.my_ranges)
+        cfg = workload_config(w, 1)
+        cfg["sharding"] = (f"one instance split over {world} GPUs "
+                           f"({'destination-row ownership' if w.name == 'gather_scatter' else 'core ranges'}); "
+                           f"inputs replicated; per step each rank broadcasts its {slabs} B of results (NCCL)")
+        print(json.dumps({"metric": w.metric + " [one instance, sharded]", "value": w.units_per_step / (ms * 1e-3),
+                          "unit": w.unit, "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms,
+                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w.dtype,
+                          "data": "synthetic", "config": cfg, "gpu_launches": int(launches), "clocks": clocks,
+                          "max_abs_err_spot_check": err}))
+    run.close()
+    interp.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -504,10 +583,14 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--shard", action="store_true",
+                    help="split ONE instance of the workload over the ranks (strong scaling) instead of one replica per rank")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
+    elif args.shard:
+        run_sharded(args, w)
     else:
         run_gpu(args, w)
 

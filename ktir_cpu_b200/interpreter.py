@@ -77,10 +77,15 @@ class Session:
     """One function bound to one tensor layout: the arena in HBM plus its launch plan."""
 
     def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
-                 scalars: Dict[str, Any], latency: bool = False):
+                 scalars: Dict[str, Any], latency: bool = False, shard: Optional[Tuple[int, int]] = None,
+                 arena_ptr: Optional[int] = None):
+        """``shard = (rank, world)`` plans only this rank's part of the kernel (see ``sharded.py``);
+        ``arena_ptr`` places the arena in caller-owned device memory of at least ``arena_size(tensors)`` bytes."""
         self.dev = dev
         self.func = func
         self.latency_records = None
+        self.shard = shard
+        self.own_arena = arena_ptr is None
         self.layout: Dict[str, Tuple[int, int, Tuple[int, ...], np.dtype]] = {}
         nxt = ARENA_BASE
         allocs = []
@@ -93,7 +98,7 @@ class Session:
             ptrs[name] = nxt // bytes_per_elem(kdt)
             nxt = (nxt + nbytes + STICK - 1) & ~(STICK - 1)
         self.arena_bytes = nxt
-        self.arena = dev.alloc(self.arena_bytes + 256)
+        self.arena = dev.alloc(self.arena_bytes + 256) if arena_ptr is None else arena_ptr
         self.arena_map = ArenaMap(allocs)
         try:
             tracer = Tracer(func, scalars, ptrs)
@@ -104,9 +109,17 @@ class Session:
             if latency:
                 self.latency_records = tracer.latency.records
             self.n_cores = tracer.ncores
-            self.plan: Plan = lower(dev, stores, self.arena_map)
+            row_shard = None
+            if shard is not None and shard[1] > 1:
+                from .sharded import core_slice, needs_row_ownership
+                if needs_row_ownership(stores):
+                    row_shard = shard          # every core runs; each rank applies the rows it owns
+                else:
+                    stores = Tracer(func, scalars, ptrs, core_range=core_slice(tracer.ncores, *shard)).run()
+            self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard)
         except Exception:
-            dev.free(self.arena)
+            if self.own_arena:
+                dev.free(self.arena)
             self.arena = None
             raise
         self.written = set(self.plan.written)
@@ -134,11 +147,16 @@ class Session:
     def device_ptr(self, name: str) -> int:
         return self.arena + self.layout[name][0]
 
+    def written_ranges(self) -> List[Tuple[int, int]]:
+        """Merged arena byte ranges this session's launches write (this rank's slabs when sharded)."""
+        return self.plan.written_ranges()
+
     def close(self):
         if self.arena is not None:
             self.dev.sync()
             self.plan.release(self.dev)
-            self.dev.free(self.arena)
+            if self.own_arena:
+                self.dev.free(self.arena)
             self.arena = None
 
 

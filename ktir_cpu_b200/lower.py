@@ -525,6 +525,28 @@ class Plan:
         for s in self.statements:
             s.launch(dev, arena_ptr)
 
+    def written_ranges(self) -> List[Tuple[int, int]]:
+        """Arena byte ranges the launches write, merged and sorted."""
+        runs = []
+        for s in self.statements:
+            own = getattr(s, "owned_range", None)
+            if own is not None:
+                runs.append(np.array([own], np.int64))
+                continue
+            for f in s.footprints():
+                if f.write and len(f.starts):
+                    runs.append(np.stack([f.starts, f.ends], 1).astype(np.int64))
+        if not runs:
+            return []
+        r = np.concatenate(runs)
+        r = r[np.argsort(r[:, 0], kind="stable")]
+        hi = np.maximum.accumulate(r[:, 1])
+        new = np.ones(len(r), bool)
+        new[1:] = r[1:, 0] > hi[:-1]
+        first = np.flatnonzero(new)
+        last = np.concatenate([first[1:] - 1, [len(r) - 1]])
+        return [(int(r[a, 0]), int(hi[b])) for a, b in zip(first, last)]
+
     def release(self, dev: R.Device):
         for s in self.statements:
             for p in getattr(s, "device_arrays", []):
@@ -532,13 +554,14 @@ class Plan:
         self.statements = []
 
 
-def lower(dev: R.Device, stores: List[Store], arena: ArenaMap) -> Plan:
+def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None) -> Plan:
+    """``row_shard = (rank, world)``: ordered scatters apply only the destination rows this rank owns."""
     plan = Plan()
     for st in stores:
         sid = len(plan.statements)
         if isinstance(st.target, IndirectAccess):
             from .lower_scatter import lower_indirect_store
-            plan.statements.append(lower_indirect_store(dev, st, arena, sid))
+            plan.statements.append(lower_indirect_store(dev, st, arena, sid, row_shard))
             continue
         stmt = None
         m = match_softmax(st.value)

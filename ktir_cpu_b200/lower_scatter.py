@@ -150,7 +150,8 @@ def row_form(acc, axes, sel: np.ndarray) -> RowForm:
 class RowsStatement(Statement):
     """rows_program (direct destination) or ordered scatter_rows (indirect destination)."""
 
-    def __init__(self, dev: R.Device, store: Store, arena: ArenaMap, stmt_id: int):
+    def __init__(self, dev: R.Device, store: Store, arena: ArenaMap, stmt_id: int, row_shard=None):
+        self.owned_range = None
         self.ordered = isinstance(store.target, IndirectAccess)
         self.kind = "scatter_rows" if self.ordered else "rows_program"
         pb = ProgramBuilder(leaf_kinds=("load", "iload"))
@@ -231,6 +232,15 @@ class RowsStatement(Statement):
             a.dst_row0 = int(out.base[0]) if n_tiles else 0
             bpe = bytes_per_elem(out.dtype)
             a.dst_rows = max(0, (dst_alloc.byte_hi // bpe - a.dst_row0 - out.cols) // out.idx_mult + 1)
+            if row_shard is not None:
+                # destination rows are split over the ranks; a rank applies, in the global
+                # (tile, position) order, only the updates that land in its rows
+                rank, world = row_shard
+                total = int(a.dst_rows)
+                lo, hi = rank * total // world, (rank + 1) * total // world
+                a.dst_row0 += lo * out.idx_mult
+                a.dst_rows = hi - lo
+                self.owned_range = (int(a.dst_row0) * bpe, int(a.dst_row0 + (hi - lo) * out.idx_mult) * bpe)
             nbytes = 1 << 20
             if getattr(dev, "lib", None) is not None:
                 nbytes = int(dev.lib.ktb_scatter_scratch_bytes(n_tiles * out.rows, int(a.dst_rows)))
@@ -244,6 +254,8 @@ class RowsStatement(Statement):
                           for f in forms)
 
     def launch(self, dev, arena_ptr):
+        if self.ordered and self.args.dst_rows <= 0:
+            return                     # this rank owns no destination rows
         self.args.arena = arena_ptr
         fn = dev.lib.ktb_launch_scatter_rows if self.ordered else dev.lib.ktb_launch_rows_program
         dev.check(fn(dev.h, C.byref(self.args)))
@@ -255,8 +267,8 @@ class RowsStatement(Statement):
         return self._bytes
 
 
-def lower_indirect_store(dev, store, arena, stmt_id):
-    return RowsStatement(dev, store, arena, stmt_id)
+def lower_indirect_store(dev, store, arena, stmt_id, row_shard=None):
+    return RowsStatement(dev, store, arena, stmt_id, row_shard)
 
 
 def has_indirect_load(n: Node, seen=None) -> bool:

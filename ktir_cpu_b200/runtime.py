@@ -227,6 +227,14 @@ class Device:
             self.sync()
         return p
 
+    def set_stream(self, cuda_stream: int):
+        """Queue this context's work on an existing CUDA stream (e.g. torch's current stream)."""
+        self.check(self.lib.ktb_set_stream(self.h, C.c_uint64(cuda_stream)))
+
+    @property
+    def index(self) -> int:
+        return self.device
+
     # timing ----------------------------------------------------------------
     def record(self, slot: int):
         self.check(self.lib.ktb_event_record(self.h, slot))

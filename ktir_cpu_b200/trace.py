@@ -137,11 +137,20 @@ class LoopInfo:
 
 
 class Tracer:
-    def __init__(self, func: IRFunction, scalar_args: Dict[str, Any], ptr_args: Dict[str, int]):
+    def __init__(self, func: IRFunction, scalar_args: Dict[str, Any], ptr_args: Dict[str, int],
+                 core_range: Optional[Tuple[int, int]] = None):
+        """``core_range = (lo, hi)`` traces only the grid cores with linear id in [lo, hi) — the
+        slice of a kernel one GPU runs when its cores are split over several GPUs."""
         self.func = func
         nx, ny, nz = func.grid
-        self.ncores = nx * ny * nz
-        cid = np.arange(self.ncores, dtype=np.int64)
+        total = nx * ny * nz
+        lo, hi = core_range if core_range is not None else (0, total)
+        if not (0 <= lo <= hi <= total):
+            raise ValueError(f"core range [{lo}, {hi}) outside the grid of {total} cores")
+        self.total_cores = total
+        self.core_base = lo
+        self.ncores = hi - lo
+        cid = np.arange(lo, hi, dtype=np.int64)
         self.core_xyz = (cid % nx, (cid % (nx * ny)) // nx, cid // (nx * ny))
         self.axes: List[int] = [self.ncores]
         self.active: Optional[np.ndarray] = None

@@ -286,3 +286,59 @@ def test_latency_report_through_execute_function(build_lib):
     est = gpu.estimate_latency(fn, **kwargs)
     assert rep.kernel_cycles == est.kernel_cycles == 6304.0 and rep.bottleneck == "memory"
     gpu.close()
+
+
+def _sharded_on_one_gpu(src, fn, kw, world, out_name):
+    """Runs every rank's shard one after another on this GPU and merges the slabs on the host."""
+    from ktir_cpu_b200.interpreter import Session
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    func = gpu.module.get_function(fn)
+    tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items() if isinstance(v, np.ndarray)]
+    scalars = {k: v for k, v in kw.items() if not isinstance(v, np.ndarray)}
+    merged = kw[out_name].copy().reshape(-1).view(np.uint8)
+    covered = 0
+    for rank in range(world):
+        sess = Session(gpu.device, func, tensors, scalars, shard=(rank, world))
+        for k, v in kw.items():
+            if isinstance(v, np.ndarray):
+                sess.upload(k, v)
+        sess.run()
+        part = sess.download(out_name)
+        gpu.device.sync()
+        off = sess.layout[out_name][0]
+        for lo, hi in sess.written_ranges():
+            merged[lo - off:hi - off] = part.reshape(-1).view(np.uint8)[lo - off:hi - off]
+            covered += hi - lo
+        sess.close()
+    gpu.close()
+    return merged.view(kw[out_name].dtype).reshape(kw[out_name].shape), covered
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_ranks_reproduce_the_full_result(world, build_lib):
+    rng = np.random.default_rng(21)
+    x = (rng.standard_normal((96, 512)) * 2).astype(np.float16)
+    src = K.softmax_rows(96, 512, 6, 4, True)
+    kw = dict(output_ptr=np.zeros_like(x), input_ptr=x)
+    full, _ = _run_both(src, "softmax_kernel", kw)
+    got, covered = _sharded_on_one_gpu(src, "softmax_kernel", kw, world, "output_ptr")
+    np.testing.assert_array_equal(got, full["output_ptr"])
+    assert covered == x.nbytes
+    # ordered read-modify-write scatter: split by destination rows, still bit-exact
+    table = rng.standard_normal((257, 128)).astype(np.float16)
+    idx = _dup_indices(rng, 257, 4096, 64, 6).astype(np.int32)
+    kw = dict(table_ptr=table, idx_ptr=idx, out_ptr=rng.standard_normal((257, 128)).astype(np.float16))
+    src = K.gather_scale_scatter(257, 128, 4096, 64, 8)
+    full, want = _run_both(src, "gather_scale_scatter", kw)
+    got, _ = _sharded_on_one_gpu(src, "gather_scale_scatter", kw, world, "out_ptr")
+    np.testing.assert_array_equal(got, want["out_ptr"])
+    # tensor-core GEMM: ranks own disjoint tiles of C
+    a = rng.uniform(-1, 1, (256, 256)).astype(np.float16)
+    b = rng.uniform(-1, 1, (256, 256)).astype(np.float16)
+    kw = dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((256, 256), np.float16))
+    src = K.tiled_matmul(256, 256, 256, 64, 64, 64, 4, True)
+    full, _ = _run_both(src, "matmul_kernel", kw)
+    got, covered = _sharded_on_one_gpu(src, "matmul_kernel", kw, world, "c_ptr")
+    np.testing.assert_array_equal(got, full["c_ptr"])
+    assert covered == a.nbytes

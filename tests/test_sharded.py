@@ -1,0 +1,116 @@
+"""Multi-GPU host logic on CPU: core slices, per-rank plans (plan-only device), slab exchange over gloo."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ktir_cpu_b200 import kernels as K
+from ktir_cpu_b200.interpreter import Session
+from ktir_cpu_b200.parser import KTIRParser
+from ktir_cpu_b200.runtime import PlanOnlyDevice
+from ktir_cpu_b200.sharded import broadcast_slabs, check_disjoint, core_slice, exchange
+
+
+def _plan(src, fn, tensors, rank, world, scalars=None):
+    func = KTIRParser().parse_module(src).get_function(fn)
+    return Session(PlanOnlyDevice(), func, tensors, scalars or {}, shard=(rank, world), arena_ptr=0)
+
+
+def test_core_slices_cover_the_grid():
+    for n in (1, 7, 32, 64):
+        for world in (1, 2, 3, 8):
+            sl = [core_slice(n, r, world) for r in range(world)]
+            assert sl[0][0] == 0 and sl[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(sl, sl[1:]))
+            assert max(h - l for l, h in sl) - min(h - l for l, h in sl) <= 1
+    with pytest.raises(ValueError):
+        core_slice(8, 2, 2)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_softmax_slabs_are_contiguous_row_ranges(world):
+    rows, cols = 256, 512
+    t = [("output_ptr", (rows, cols), np.dtype(np.float16)), ("input_ptr", (rows, cols), np.dtype(np.float16))]
+    full = _plan(K.softmax_rows(rows, cols, 8, 4, True), "softmax_kernel", t, 0, 1).written_ranges()
+    assert len(full) == 1 and full[0][1] - full[0][0] == rows * cols * 2
+    per_rank = [_plan(K.softmax_rows(rows, cols, 8, 4, True), "softmax_kernel", t, r, world).written_ranges()
+                for r in range(world)]
+    check_disjoint(per_rank)
+    assert all(len(r) == 1 for r in per_rank)
+    assert per_rank[0][0][0] == full[0][0] and per_rank[-1][0][1] == full[0][1]
+    assert all(a[0][1] == b[0][0] for a, b in zip(per_rank, per_rank[1:]))
+
+
+def test_matmul_slabs_partition_c():
+    t = [(n, (256, 256), np.dtype(np.float16)) for n in ("a_ptr", "b_ptr", "c_ptr")]
+    src = K.tiled_matmul(256, 256, 256, 64, 64, 64, 4, True)
+    per_rank = [_plan(src, "matmul_kernel", t, r, 2).written_ranges() for r in range(2)]
+    check_disjoint(per_rank)
+    assert sum(h - l for rs in per_rank for l, h in rs) == 256 * 256 * 2
+
+
+def test_ordered_scatter_is_split_by_destination_rows():
+    n_rows, n_idx = 1024, 4096
+    t = [("table_ptr", (n_rows, 128), np.dtype(np.float16)), ("idx_ptr", (n_idx,), np.dtype(np.int32)),
+         ("out_ptr", (n_rows, 128), np.dtype(np.float16))]
+    src = K.gather_scale_scatter(n_rows, 128, n_idx, 64, 8)
+    sessions = [_plan(src, "gather_scale_scatter", t, r, 4) for r in range(4)]
+    per_rank = [s.written_ranges() for s in sessions]
+    check_disjoint(per_rank)
+    assert [h - l for rs in per_rank for l, h in rs] == [n_rows // 4 * 128 * 2] * 4
+    # every rank still walks every tile (order between cores matters), but owns a quarter of the rows
+    for s in sessions:
+        (stmt,) = s.plan.statements
+        assert stmt.args.n_tiles == n_idx // 64 and stmt.args.dst_rows == n_rows // 4
+
+
+def test_overlapping_slabs_are_rejected():
+    with pytest.raises(ValueError, match="both write"):
+        check_disjoint([[(0, 128)], [(64, 256)]])
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows, cols = 64, 256
+        t = [("output_ptr", (rows, cols), np.dtype(np.float16)), ("input_ptr", (rows, cols), np.dtype(np.float16))]
+        sess = _plan(K.softmax_rows(rows, cols, 4, 4, True), "softmax_kernel", t, rank, world)
+        arena = torch.zeros(sess.arena_bytes, dtype=torch.uint8)
+        mine = sess.written_ranges()
+        for lo, hi in mine:                      # stand-in for this rank's launches: mark its slab
+            arena[lo:hi] = rank + 1
+        all_ranges = exchange(arena, mine, dist)
+        off, nbytes, _, _ = sess.layout["output_ptr"]
+        got = arena[off:off + nbytes].numpy().copy()
+        want = np.concatenate([np.full(hi - lo, r + 1, np.uint8) for r, rs in enumerate(all_ranges) for lo, hi in rs])
+        ok = bool((got == want).all()) and int(arena[:off].sum()) == 0
+        # a second step reuses the slab lists (no object collective)
+        arena[off:off + nbytes] = 0
+        for lo, hi in mine:
+            arena[lo:hi] = 10 + rank
+        broadcast_slabs(arena, all_ranges, dist)
+        ok = ok and sorted(set(arena[off:off + nbytes].tolist())) == [10 + r for r in range(world)]
+        out[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_slab_exchange_over_gloo_world2():
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert dict(out) == {0: True, 1: True}
