@@ -575,17 +575,116 @@ def run_sharded(args, w):
         dist.destroy_process_group()
 
 
+def candidate_sweep(n=512, B=1, H=4, D=128):
+    """The 512-variant attention sweep: variant i has tile_m = (32,64,128)[i%3],
+    tile_n = (32,64,128)[(i//3)%3], S = (512,1024,2048)[(i//9)%3], inputs seeded 1000+i.
+    B and H are not fixed by the configuration; B=1, H=4 keeps the CPU interpreter able to finish a sample."""
+    from ktir_cpu_b200 import kernels as K
+    from ktir_cpu_b200.batch import Candidate
+    out, flops = [], 0
+    for i in range(n):
+        tm, tn, S = (32, 64, 128)[i % 3], (32, 64, 128)[(i // 3) % 3], (512, 1024, 2048)[(i // 9) % 3]
+        rng = np.random.default_rng(1000 + i)
+        q, k, v = (rng.standard_normal((S, B * H, D), dtype=np.float32).astype(np.float16) for _ in range(3))
+        kw = dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(S // tn, tn, B * H, D),
+                  value_cache_ptr=v.reshape(S // tn, tn, B * H, D),
+                  block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
+                  num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D)))
+        out.append(Candidate(K.causal_attention(S, B * H, D, tm, tn), "attention_kernel", kw, tag=(tm, tn, S)))
+        flops += 4 * B * H * D * (S * (S + 1) // 2)
+    return out, flops
+
+
+def run_candidates(args):
+    """kernels/s over the candidate sweep, host arrays in and out for every candidate (there is
+    no device-resident variant of this metric: a candidate arrives as text + host tensors)."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from ktir_cpu_b200.batch import BatchRunner
+    n = 512
+    cands, flops = candidate_sweep(n)
+    runner = BatchRunner(local)
+    checks = {}
+
+    def score(i, c, out):
+        if i % 64 == rank:                     # spot-check one head of a few variants against f64 math
+            S, h = c.tag[2], 1
+            q = c.kwargs["query_ptr"][:, h].astype(np.float64)
+            k = c.kwargs["key_cache_ptr"][:, :, h].reshape(S, -1).astype(np.float64)
+            v = c.kwargs["value_cache_ptr"][:, :, h].reshape(S, -1).astype(np.float64)
+            sc = np.where(np.tril(np.ones((S, S), bool)), q @ k.T / np.sqrt(q.shape[1]), -np.inf)
+            p = np.exp(sc - sc.max(-1, keepdims=True))
+            checks[i] = float(np.abs(out["output_ptr"][:, h].astype(np.float64) - (p / p.sum(-1, keepdims=True)) @ v).max())
+        return True
+    warm = runner.run(cands[:27 * world], rank, world, score=None, keep_outputs=False)   # every distinct kernel planned once
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    t0 = time.perf_counter()
+    steps = max(1, args.steps // 10)
+    launches = 0
+    for _ in range(steps):
+        res = runner.run(cands, rank, world, score=score, keep_outputs=False)
+        launches += res.launches
+    dt = time.perf_counter() - t0
+    clocks = sampler.stop()
+    errs = len(res.errors) + len(warm.errors)
+    if dist is not None:
+        import torch
+        t = torch.tensor([dt, float(errs)], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt, errs = float(t[0]), int(t[1])
+    if rank == 0:
+        h2d = sum(v.nbytes for c in cands for v in c.kwargs.values() if isinstance(v, np.ndarray)) // n
+        line = {"metric": "candidate kernels evaluated per second (512-variant causal attention sweep)",
+                "value": n * steps / dt, "unit": "kernels/s", "n_gpus": world, "steps": steps, "warmup": 1,
+                "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "512 variants: tile_m,tile_n in {32,64,128}, S in {512,1024,2048}, B=1, H=4, D=128; "
+                                       "variant i on rank i % world; 27 distinct kernels parsed and planned once",
+                           "flops_per_sweep": flops},
+                "e2e": {"value": n * steps / dt, "unit": "kernels/s", "h2d_bytes_per_step": h2d * n,
+                        "d2h_bytes_per_step": h2d * n},
+                "tflops": flops * steps / dt / 1e12, "gpu_launches": int(launches), "clocks": clocks,
+                "failed_candidates": errs, "max_abs_err_spot_check": max(checks.values()) if checks else None}
+        if world == 1 and not args.no_cpu:
+            sys.path.insert(0, ROOT)
+            from oracle.numpy_interp import OracleInterpreter
+            t1 = time.perf_counter()
+            c = cands[0]                          # smallest variant: tile 32x32, S = 512
+            o = OracleInterpreter()
+            o.load(c.source)
+            o.execute_function(c.function, **c.kwargs)
+            d1 = time.perf_counter() - t1
+            line["cpu_baseline"] = {"value": 1.0 / d1, "unit": "kernels/s", "cores": 1, "kind": "port",
+                                    "sample": f"variant 0 (tile 32x32, S=512, the cheapest) through oracle/numpy_interp.py on 1 core, {d1:.1f} s"}
+        print(json.dumps(line))
+    runner.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS) + ["candidates"])
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--shard", action="store_true",
                     help="split ONE instance of the workload over the ranks (strong scaling) instead of one replica per rank")
     args = ap.parse_args()
+    if args.workload == "candidates":
+        return run_candidates(args)
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)

@@ -201,11 +201,14 @@ class AttentionStatement(Statement):
         orow0, ohead = decode(O, o_off)
         if (row0 != orow0).any() or (head != ohead).any() or (row0 % tm).any():
             raise Unsupported("attention output tiles do not mirror the query tiles")
+        # the statement may cover a sub-range of the heads (a core slice of a sharded kernel)
+        hmin = int(head.min())
+        head = head - hmin
         heads = int(head.max()) + 1
         rmin = int(row0.min())
         nblk = int((row0.max() - rmin) // tm) + 1
         key = ((row0 - rmin) // tm) * heads + head
-        if head.min() != 0 or P != nblk * heads or len(np.unique(key)) != P:
+        if P != nblk * heads or len(np.unique(key)) != P:
             raise Unsupported("attention query tiles do not cover [rows x heads] exactly once")
         seq_q = nblk * tm
 
@@ -231,7 +234,7 @@ class AttentionStatement(Statement):
         kbase, vbase = (int(np.asarray(x.base).reshape(-1)[0]) for x in (kview, vview))
         for f, base in ((kf, kbase), (vf, vbase)):
             hh, rem = np.divmod(f.base.reshape(P, T) - base, kview.strides[2])
-            if rem.any() or (hh != head[:, None]).any():
+            if rem.any() or (hh != head[:, None] + hmin).any():
                 raise Unsupported("K/V head does not follow the query head")
 
         delta = 0
@@ -259,9 +262,9 @@ class AttentionStatement(Statement):
         n_pages = int(kview.shape[0])
 
         self.args = a = R.AttnArgs()
-        a.q_off = int(np.asarray(Q.view.base).reshape(-1)[0]) + rmin * Q.strides[0]
-        a.o_off = int(np.asarray(O.view.base).reshape(-1)[0]) + rmin * O.strides[0]
-        a.k_off, a.v_off = kbase, vbase
+        a.q_off = int(np.asarray(Q.view.base).reshape(-1)[0]) + rmin * Q.strides[0] + hmin * Q.strides[1]
+        a.o_off = int(np.asarray(O.view.base).reshape(-1)[0]) + rmin * O.strides[0] + hmin * O.strides[1]
+        a.k_off, a.v_off = kbase + hmin * kview.strides[2], vbase + hmin * kview.strides[2]
         a.bt_off, a.bt_dtype = int(idx[0, 0]), R.DTYPE_CODE[kf.idx_dtype]
         a.seq_q, a.heads, a.head_dim = seq_q, heads, hd
         a.page, a.n_pages_total, a.num_tiles = tn, n_pages, T

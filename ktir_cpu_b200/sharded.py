@@ -58,11 +58,48 @@ def exchange(arena, my_ranges: Sequence[Tuple[int, int]], dist, group=None) -> L
 
 
 def broadcast_slabs(arena, all_ranges, dist, group=None):
-    """The data step of ``exchange`` alone (slab lists already known, e.g. from an earlier step)."""
+    """The data step of ``exchange`` alone (slab lists already known, e.g. from an earlier step).
+
+    One equal-sized slab per rank, laid out back to back in rank order (the usual case: contiguous
+    row ranges of one output) is a single in-place all-gather under NCCL; anything else is one
+    broadcast per slab."""
+    world = len(all_ranges)
+    if world > 1 and dist.get_backend(group) == "nccl" and all(len(r) == 1 for r in all_ranges):
+        los = [r[0][0] for r in all_ranges]
+        n = all_ranges[0][0][1] - los[0]
+        if n > 0 and all(r[0][1] - r[0][0] == n for r in all_ranges) and \
+                all(b == a + n for a, b in zip(los, los[1:])):
+            me = dist.get_rank(group)
+            dist.all_gather_into_tensor(arena[los[0]:los[0] + world * n], arena[los[me]:los[me] + n], group=group)
+            return
+    me = dist.get_rank(group)
     for src, ranges in enumerate(all_ranges):
+        reg = _regular(ranges)
+        if reg is not None:
+            # many equal fragments at a constant stride (e.g. a head range of a [seq, heads, dim]
+            # output): pack, one broadcast, unpack
+            lo, length, stride, count = reg
+            view = arena.as_strided((count, length), (stride, 1), lo)
+            buf = view.contiguous() if src == me else arena.new_empty((count, length))
+            dist.broadcast(buf, src=src, group=group)
+            if src != me:
+                view.copy_(buf)
+            continue
         for lo, hi in ranges:
             if hi > lo:
                 dist.broadcast(arena[lo:hi], src=src, group=group)
+
+
+def _regular(ranges):
+    """(lo, length, stride, count) if ``ranges`` are > 4 equal-length runs at a constant stride."""
+    if len(ranges) <= 4:
+        return None
+    lo0, hi0 = ranges[0]
+    length, stride = hi0 - lo0, ranges[1][0] - lo0
+    for i, (lo, hi) in enumerate(ranges):
+        if hi - lo != length or lo != lo0 + i * stride:
+            return None
+    return lo0, length, stride, len(ranges)
 
 
 class ShardedRun:

@@ -342,3 +342,16 @@ def test_sharded_ranks_reproduce_the_full_result(world, build_lib):
     got, covered = _sharded_on_one_gpu(src, "matmul_kernel", kw, world, "c_ptr")
     np.testing.assert_array_equal(got, full["c_ptr"])
     assert covered == a.nbytes
+    if world == 2:
+        # attention: a core slice that is a whole number of heads becomes a head range
+        S, H, D, tm, tn = 256, 4, 128, 64, 64
+        q, k, v = (rng.standard_normal((S, H, D)).astype(np.float16) for _ in range(3))
+        kw = dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(S // tn, tn, H, D),
+                  value_cache_ptr=v.reshape(S // tn, tn, H, D),
+                  block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
+                  num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D)))
+        src = K.causal_attention(S, H, D, tm, tn)
+        full, _ = _run_both(src, "attention_kernel", kw)
+        got, covered = _sharded_on_one_gpu(src, "attention_kernel", kw, world, "output_ptr")
+        np.testing.assert_array_equal(got, full["output_ptr"])
+        assert covered == q.nbytes

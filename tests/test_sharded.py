@@ -68,6 +68,13 @@ def test_ordered_scatter_is_split_by_destination_rows():
         assert stmt.args.n_tiles == n_idx // 64 and stmt.args.dst_rows == n_rows // 4
 
 
+def test_regular_fragments_are_recognised():
+    from ktir_cpu_b200.sharded import _regular
+    assert _regular([(100 + 64 * i, 132 + 64 * i) for i in range(10)]) == (100, 32, 64, 10)
+    assert _regular([(0, 32), (64, 96)]) is None
+    assert _regular([(64 * i, 64 * i + (32 if i != 3 else 16)) for i in range(8)]) is None
+
+
 def test_overlapping_slabs_are_rejected():
     with pytest.raises(ValueError, match="both write"):
         check_disjoint([[(0, 128)], [(64, 256)]])
@@ -103,6 +110,12 @@ def _worker(rank, world, port, out):
             arena[lo:hi] = 10 + rank
         broadcast_slabs(arena, all_ranges, dist)
         ok = ok and sorted(set(arena[off:off + nbytes].tolist())) == [10 + r for r in range(world)]
+        # strided fragments (a column block per rank of a [16, 64]-byte matrix)
+        m = torch.zeros(16 * 64, dtype=torch.uint8)
+        frag = [[(r * 32 + 64 * i, r * 32 + 32 + 64 * i) for i in range(16)] for r in range(world)]
+        m.view(16, 64)[:, rank * 32:(rank + 1) * 32] = 50 + rank
+        broadcast_slabs(m, frag, dist)
+        ok = ok and all(bool((m.view(16, 64)[:, r * 32:(r + 1) * 32] == 50 + r).all()) for r in range(world))
         out[rank] = ok
     finally:
         dist.destroy_process_group()
