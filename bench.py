@@ -614,7 +614,7 @@ def run_candidates(args):
     checks = {}
 
     def score(i, c, out):
-        if i % 64 == rank:                     # spot-check one head of a few variants against f64 math
+        if i % 9 == rank % 9:                  # spot-check one head of a few variants against f64 math (warm-up pass only)
             S, h = c.tag[2], 1
             q = c.kwargs["query_ptr"][:, h].astype(np.float64)
             k = c.kwargs["key_cache_ptr"][:, :, h].reshape(S, -1).astype(np.float64)
@@ -623,7 +623,7 @@ def run_candidates(args):
             p = np.exp(sc - sc.max(-1, keepdims=True))
             checks[i] = float(np.abs(out["output_ptr"][:, h].astype(np.float64) - (p / p.sum(-1, keepdims=True)) @ v).max())
         return True
-    warm = runner.run(cands[:27 * world], rank, world, score=None, keep_outputs=False)   # every distinct kernel planned once
+    warm = runner.run(cands[:27 * world], rank, world, score=score, keep_outputs=False)  # every distinct kernel planned once
     if dist is not None:
         dist.barrier()
     sampler = ClockSampler(local)
@@ -632,7 +632,7 @@ def run_candidates(args):
     steps = max(1, args.steps // 10)
     launches = 0
     for _ in range(steps):
-        res = runner.run(cands, rank, world, score=score, keep_outputs=False)
+        res = runner.run(cands, rank, world, score=None, keep_outputs=True)
         launches += res.launches
     dt = time.perf_counter() - t0
     clocks = sampler.stop()

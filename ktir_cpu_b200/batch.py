@@ -69,7 +69,7 @@ class BatchRunner:
                 it = self._interp(c.source)
                 dev = it.device
                 l0 = dev.launch_count()
-                out = it.execute_function(c.function, **c.kwargs)
+                out = self._execute(it, c)
                 res.launches += dev.launch_count() - l0
                 if score is not None:
                     out = score(i, c, out)
@@ -79,6 +79,21 @@ class BatchRunner:
                 res.errors[i] = f"{type(e).__name__}: {e}"
         res.parses = self.parses
         return res
+
+    @staticmethod
+    def _execute(it: KTIRInterpreter, c: Candidate) -> Dict[str, np.ndarray]:
+        """Upload, launch, and read back only the tensors the kernel writes (a scorer has the
+        inputs already; ``execute_function`` would copy every tensor back)."""
+        sess, kwargs = it.session(c.function, **c.kwargs)
+        for k, v in kwargs.items():
+            if isinstance(v, np.ndarray) and k not in sess.no_upload:
+                sess.upload(k, v)
+        sess.run()
+        out = {k: sess.download(k) for k in kwargs if k in sess.written}
+        st = sess.dev.sync()
+        if st.negative_index:
+            raise IndexError(f"indirect index {st.bad_index_value} is negative")
+        return out
 
     def close(self):
         for it in self._interps.values():
