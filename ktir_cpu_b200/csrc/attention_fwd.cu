@@ -7,17 +7,19 @@
 // (examples/triton-ktir/paged_attention.mlir:183-396, ktir_cpu/ops/memory_ops.py:867-915,
 // ktir_cpu/dialects/linalg_ops.py:136-347).
 //
-// Roles: warp 0 streams both Q tiles once and the K/V pages (page id from the block table)
-// through a 3-slot shared-memory ring by TMA; warp 1 issues tcgen05.mma — S_i = Q_i K^T into the
-// score buffer of tile i, P_i V accumulated into the output buffer of tile i, both in TMEM;
-// warps 2-5 are the softmax of tile 0, warps 6-9 of tile 1, one thread per query row: read the
-// row of S from TMEM, mask, running max, P = exp2(..) as f16 into swizzled shared memory, row
-// sum in f32.  While one tile is in its softmax the tensor core works for the other tile.
+// Roles (five warpgroups of 4 warps): warp 0 streams both Q tiles once and the K/V pages (page
+// id from the block table) through a shared-memory ring by TMA; warp 1 issues tcgen05.mma —
+// S_i = Q_i K^T into the score buffer of tile i, P_i V accumulated into the output buffer of
+// tile i, both in TMEM; warps 4-11 are the softmax of tile 0, warps 12-19 of tile 1, two threads
+// per query row (each owns half of the page's columns): read the scores from TMEM, mask,
+// running max, P = exp2(..) rounded to f16 and written back to TMEM over the scores it came
+// from, row sum in f32.  P V takes its A operand straight from TMEM, so shared memory carries
+// only Q, K and V; while one tile is in its softmax the tensor core works for the other tile.
 //
 // The output accumulator never leaves TMEM until the end.  The reference rescales it by
 // exp(m_old - m_new) after every page (paged_attention.mlir:330-372); here the exponent
 // reference m_ref of a row is only moved when the row maximum has grown by more than 2^8 since
-// it was set (then O and l are rescaled once, by the row's own thread, through tcgen05.ld/st).
+// it was set (then O and l are rescaled once, by the row's own threads, through tcgen05.ld/st).
 // P = exp2(s - m_ref) may therefore exceed 1 by at most 2^8, well inside f16 range; the
 // normalised result sum(P V) / sum(P) is the same number, only the rounding of P to f16 sees a
 // different exponent.  Scores, max, sum and accumulator are f32 as in the reference; P is
@@ -26,9 +28,9 @@
 
 #define AT_BM 128
 #define AT_D 128
-#define AT_THREADS 320
+#define AT_THREADS 640
 #define AT_Q_BYTES (AT_BM * AT_D * 2)
-#define AT_STAGES 3
+#define AT_MAX_STAGES 8
 #define AT_RESCALE_GAP 8.0f
 
 static __device__ __forceinline__ void at_tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x,
@@ -104,8 +106,8 @@ static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], in
     }
 }
 
-enum { B_QFULL = 0, B_KVFULL = 1, B_KVEMPTY = B_KVFULL + AT_STAGES, B_SFULL = B_KVEMPTY + AT_STAGES,
-       B_PFULL = B_SFULL + 2, B_ODONE = B_PFULL + 2, B_COUNT = B_ODONE + 2 };
+enum { B_QFULL = 0, B_KVFULL = 1, B_KVEMPTY = B_KVFULL + AT_MAX_STAGES, B_SFULL = B_KVEMPTY + AT_MAX_STAGES,
+       B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2, B_XCHG = B_PVDONE + 2, B_COUNT = B_XCHG + 2 };
 
 template <int BN>
 __global__ void __launch_bounds__(AT_THREADS, 1)
@@ -113,14 +115,14 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          const __grid_constant__ CUtensorMap map_v, const ktb_attn_args a, int q_pairs,
                          ktb_status* st) {
     constexpr int KV_BYTES = BN * AT_D * 2;            // one K or V page in shared memory
+    constexpr int AT_STAGES = BN == 128 ? 4 : 8;       // ring slots: 128 KB (64 KB for 32-row pages)
     constexpr int KV_BLK = BN * 128;                   // bytes of one [BN x 64] block
-    constexpr int P_BYTES = (BN < 64 ? 64 : BN) * AT_BM * 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;                                // 2 tiles x 2 blocks [128 x 64]
-    uint8_t* sP = sQ + 2 * AT_Q_BYTES;                 // 2 tiles x [128 x BN] as blocks of [128 x 64]
-    uint8_t* sKV = sP + 2 * P_BYTES;                   // ring of K / V pages
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + AT_STAGES * KV_BYTES);
+    uint8_t* sKV = sQ + 2 * AT_Q_BYTES;                // ring of K / V pages
+    float* xbuf = reinterpret_cast<float*>(sKV + AT_STAGES * KV_BYTES);   // [2 tiles][2 parities][2 halves][128 rows]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xbuf + 2 * 2 * 2 * AT_BM);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -151,8 +153,9 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         for (int i = 0; i < 2; ++i) {
             tc_mbar_init(&bars[B_SFULL + i], 1);
-            tc_mbar_init(&bars[B_PFULL + i], 4);
-            tc_mbar_init(&bars[B_ODONE + i], 1);
+            tc_mbar_init(&bars[B_PFULL + i], 8);
+            tc_mbar_init(&bars[B_PVDONE + i], 1);
+            tc_mbar_init(&bars[B_XCHG + i], 8);
         }
         *abort_flag = 0;
         tc_fence_barrier_init();
@@ -166,6 +169,11 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t tmem_s = tmem_base;            // S_0, S_1: 2 x 128 columns
     const uint32_t tmem_o = tmem_base + 256;      // O_0, O_1: 2 x 128 columns
 
+    // register budget: the copy/MMA warpgroup needs few registers, the softmax warpgroups hold a
+    // half a row of scores each; the MMA issue loop must not spill, it paces the whole CTA
+    // (each setmaxnreg sits at the head of the region it governs, with no join in between)
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     if (warp == 0) {
         if (lane == 0 && nmax > 0) {
             tc_prefetch_tmap(&map_q);
@@ -179,10 +187,12 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const int32_t* bt32 = reinterpret_cast<const int32_t*>(a.arena) + a.bt_off;
             const int64_t* bt64 = reinterpret_cast<const int64_t*>(a.arena) + a.bt_off;
-            // load t = 2 j is K of page j, t = 2 j + 1 is V of page j; slot t % 3
+            // load t = 2 j is K of page j, t = 2 j + 1 is V of page j; slot t % AT_STAGES
             for (int t = 0; t < 2 * nmax; ++t) {
-                const int j = t >> 1, slot = t % AT_STAGES;
+                const int slot = t % AT_STAGES;
                 const uint32_t ph = (t / AT_STAGES) & 1;
+                const bool is_v = t & 1;
+                const int j = t >> 1;
                 long long page = a.bt_dtype == KTB_I64 ? bt64[j] : (long long)bt32[j];
                 if (page < 0) {
                     if (atomicExch(&st->negative_index, 1) == 0) st->bad_index_value = (int32_t)page;
@@ -190,7 +200,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
                 if (!tc_mbar_wait(&bars[B_KVEMPTY + slot], ph ^ 1, abort_flag, st, 11)) break;
                 tc_mbar_expect_tx(&bars[B_KVFULL + slot], KV_BYTES);
-                const CUtensorMap* map = (t & 1) ? &map_v : &map_k;
+                const CUtensorMap* map = is_v ? &map_v : &map_k;
                 at_tma_load_4d(sKV + slot * KV_BYTES, map, &bars[B_KVFULL + slot], 0, head, 0, (int)page);
                 at_tma_load_4d(sKV + slot * KV_BYTES + KV_BLK, map, &bars[B_KVFULL + slot], 64, head, 0, (int)page);
             }
@@ -203,188 +213,223 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 return tc_mbar_wait(&bars[B_KVFULL + t % AT_STAGES], (t / AT_STAGES) & 1, abort_flag, st, 22);
             };
             auto kv_release = [&](int t) { tc_mma_commit(&bars[B_KVEMPTY + t % AT_STAGES]); };
+            auto t_k = [&](int m) { return 2 * m; };          // load index of K_m
+            auto t_v = [&](int m) { return 2 * m + 1; };      // load index of V_m
             auto issue_s = [&](int i, int j) {
                 const uint32_t q_addr = tc_smem_u32(sQ + i * AT_Q_BYTES);
-                const uint32_t k_addr = tc_smem_u32(sKV + ((2 * j) % AT_STAGES) * KV_BYTES);
+                const uint32_t k_addr = tc_smem_u32(sKV + (t_k(j) % AT_STAGES) * KV_BYTES);
+                // the start-address field is the low 14 bits of the descriptor (in 16-byte units), so
+                // stepping along K is an add of a constant.  The loop is unrolled: this one thread has
+                // to hand the tensor core an instruction every 64 cycles while sharing its scheduler
+                // with four softmax warps, so every instruction between two MMAs counts.
+                const uint64_t ad0 = tc_smem_desc(q_addr, 16, 1024), bd0 = tc_smem_desc(k_addr, 16, 1024);
 #pragma unroll
                 for (int kk = 0; kk < AT_D / 16; ++kk) {
-                    const uint64_t ad = tc_smem_desc(q_addr + (kk >> 2) * (AT_BM * 128) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = tc_smem_desc(k_addr + (kk >> 2) * KV_BLK + (kk & 3) * 32, 16, 1024);
-                    tc_mma_f16(tmem_s + i * 128, ad, bd, idesc_s, kk != 0);
+                    const uint32_t ao = ((kk >> 2) * (AT_BM * 128) + (kk & 3) * 32) >> 4;
+                    const uint32_t bo = ((kk >> 2) * KV_BLK + (kk & 3) * 32) >> 4;
+                    tc_mma_f16(tmem_s + i * 128, ad0 + ao, bd0 + bo, idesc_s, kk != 0);
                 }
                 tc_mma_commit(&bars[B_SFULL + i]);
             };
             auto issue_pv = [&](int i, int j) {
-                const uint32_t p_addr = tc_smem_u32(sP + i * P_BYTES);
-                const uint32_t v_addr = tc_smem_u32(sKV + ((2 * j + 1) % AT_STAGES) * KV_BYTES);
+                // A = P_i from TMEM: row r in lane r, 16 f16 of a K step packed in 8 columns
+                const uint32_t v_addr = tc_smem_u32(sKV + (t_v(j) % AT_STAGES) * KV_BYTES);
+                const uint64_t bd0 = tc_smem_desc(v_addr, KV_BLK, 1024);
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint64_t ad = tc_smem_desc(p_addr + (kk >> 2) * (AT_BM * 128) + (kk & 3) * 32, 16, 1024);
-                    const uint64_t bd = tc_smem_desc(v_addr + kk * 2048, KV_BLK, 1024);
-                    tc_mma_f16(tmem_o + i * 128, ad, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < BN / 16; ++kk)
+                    tc_mma_f16_ts(tmem_o + i * 128, tmem_s + i * 128 + kk * 8, bd0 + (uint32_t)(kk * 2048 >> 4), idesc_pv,
+                                  (j > 0 || kk > 0) ? 1u : 0u);
             };
-            bool ok = tc_mbar_wait(&bars[B_QFULL], 0, abort_flag, st, 21) && kv_wait(0);
-            if (ok) {
-                tc_fence_after_sync();
-                for (int i = 0; i < 2; ++i)
-                    if (n_of[i] > 0) issue_s(i, 0);
-                kv_release(0);
-            }
-            // The commit that publishes S_i(j+1) also covers P_i V(j), issued just before it: when
-            // the softmax of tile i sees its next scores, its P buffer and O accumulator are idle.
-            for (int j = 0; ok && j < nmax; ++j) {
-                if (!kv_wait(2 * j + 1)) { ok = false; break; }
-                bool k_ready = false;
-                for (int i = 0; i < 2 && ok; ++i) {
-                    if (j < n_of[i]) {
-                        if (!tc_mbar_wait(&bars[B_PFULL + i], j & 1, abort_flag, st, 25)) { ok = false; break; }
-                        tc_fence_after_sync();
-                        issue_pv(i, j);
-                        if (j == n_of[i] - 1) tc_mma_commit(&bars[B_ODONE + i]);
-                    }
-                    if (j + 1 < n_of[i]) {
-                        if (!k_ready) {
-                            if (!kv_wait(2 * j + 2)) { ok = false; break; }
-                            tc_fence_after_sync();
-                            k_ready = true;
-                        }
-                        issue_s(i, j + 1);
+            // Event-driven issue: whichever tile has its next step ready goes first, so the two
+            // softmax warpgroups stay out of phase and the tensor core always has the other tile's
+            // work.  Per tile and page j:  P V(j) needs P(j) in TMEM and V_j in shared memory;  S(j+1)
+            // overwrites the columns P(j) lives in, so it is issued after P V(j) (the tensor core runs
+            // one thread's MMAs in issue order) and needs K_{j+1}.  A K (V) slot is released once every
+            // tile that uses the page has had its S (P V) issued.
+            bool ok = tc_mbar_wait(&bars[B_QFULL], 0, abort_flag, st, 21);
+            if (ok) tc_fence_after_sync();
+            int ns0 = 0, ns1 = 0, np0 = 0, np1 = 0;        // next page to issue: S / P V of tile 0 / 1
+            int rel_k = 0, rel_v = 0;
+            const long long t_start = clock64();
+            uint32_t idle = 0;
+            // one tile's turn; its counters are plain registers (no indexed arrays in this loop)
+            auto turn = [&](const int i, int& js, int& jp) -> bool {
+                bool did = false;
+                if (jp < n_of[i] && jp < js && tc_mbar_test(&bars[B_PFULL + i], jp & 1) &&
+                    tc_mbar_test(&bars[B_KVFULL + t_v(jp) % AT_STAGES], (t_v(jp) / AT_STAGES) & 1)) {
+                    tc_fence_after_sync();
+                    issue_pv(i, jp);
+                    if (jp == n_of[i] - 1) tc_mma_commit(&bars[B_PVDONE + i]);
+                    ++jp;
+                    did = true;
+                }
+                if (js < n_of[i] && js == jp &&
+                    tc_mbar_test(&bars[B_KVFULL + t_k(js) % AT_STAGES], (t_k(js) / AT_STAGES) & 1)) {
+                    tc_fence_after_sync();
+                    issue_s(i, js);
+                    ++js;
+                    did = true;
+                }
+                return did;
+            };
+            const int n0 = n_of[0], n1 = n_of[1];
+            while (ok && rel_v < nmax) {
+                bool progressed = turn(0, ns0, np0);
+                progressed |= turn(1, ns1, np1);
+                while (rel_k < nmax && (rel_k >= n0 || ns0 > rel_k) && (rel_k >= n1 || ns1 > rel_k)) {
+                    kv_release(t_k(rel_k));
+                    ++rel_k;
+                }
+                while (rel_v < nmax && (rel_v >= n0 || np0 > rel_v) && (rel_v >= n1 || np1 > rel_v)) {
+                    kv_release(t_v(rel_v));
+                    ++rel_v;
+                }
+                if (progressed) {
+                    idle = 0;
+                } else if ((++idle & 1023u) == 0) {
+                    if (*abort_flag) ok = false;
+                    else if (clock64() - t_start > 4000000000ll) {     // bounded: a couple of seconds at most
+                        *abort_flag = 1;
+                        if (atomicExch(&st->wait_timeout, 1) == 0) st->wait_site = 23;
+                        ok = false;
                     }
                 }
-                if (!ok) break;
-                kv_release(2 * j + 1);
-                if (j + 1 < nmax) kv_release(2 * j + 2);
             }
         }
+    }
     } else {
-        constexpr int CW = BN >= 32 ? 32 : 16;       // columns per TMEM load
-        const int tile = (warp - 2) >> 2;            // which query tile this warpgroup owns
+        // (the softmax warpgroups keep the launch allocation of 96 registers)
+        // Two threads share a query row: `half` 0 owns the first BN/2 score columns and the first 64
+        // output columns, `half` 1 the rest.  Their row maxima (and, at the end, row sums) are swapped
+        // through shared memory.
+        constexpr int HB = BN / 2;                   // score columns per thread
+        constexpr int CW = HB < 32 ? HB : 32;        // columns per TMEM load
+        constexpr int NCH = HB / CW;
+        constexpr int OH = AT_D / 2;                 // output columns per thread
+        const int tile = (warp - 4) >> 3;            // which query tile this pair of warpgroups owns
+        const int half = ((warp - 4) >> 2) & 1;
         const int n = n_of[tile];
         const int q = warp & 3;                      // TMEM lane quadrant this warp may access
         const int r = q * 32 + lane;                 // row inside the tile == TMEM lane
         const int R = q0 + tile * AT_BM + r;
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-        const uint32_t s_addr = tmem_s + tile * 128 + lane_off;
-        const uint32_t o_addr = tmem_o + tile * 128 + lane_off;
-        uint8_t* p_row = sP + tile * P_BYTES + r * 128;
+        const uint32_t s_addr = tmem_s + tile * 128 + lane_off + half * HB;
+        // P (f16, two per 32-bit column) goes over the first BN/2 columns of the score buffer
+        const uint32_t p_addr = tmem_s + tile * 128 + lane_off + half * (HB / 2);
+        const uint32_t o_addr = tmem_o + tile * 128 + lane_off + half * OH;
+        float* xrow = xbuf + tile * (2 * 2 * AT_BM) + r;        // + parity * 256 + half * 128
         const float sl = a.scale * 1.4426950408889634f;
         float m_ref = a.m_init * 1.4426950408889634f;           // exponent reference, log2 domain
         float m_run = m_ref;                                    // true running maximum
-        float l_run = a.l_init;
+        float l_run = half == 0 ? a.l_init : 0.f;               // this thread's share of the running sum
         const long long limit = (long long)R + a.causal_delta;  // last visible kv position
         const long long tile_limit = (long long)q0 + tile * AT_BM + a.causal_delta;
         bool ok = true;
+        uint32_t xphase = 0;
+
+        // swap one f32 with the partner thread of the row (slot parity alternates, so a value is
+        // not overwritten before the partner has read it)
+        auto swap_with_partner = [&](float mine, float& theirs) -> bool {
+            float* slot = xrow + (xphase & 1) * (2 * AT_BM);
+            slot[half * AT_BM] = mine;
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive(&bars[B_XCHG + tile]);        // release: orders the stores above
+            const bool w = tc_mbar_wait(&bars[B_XCHG + tile], xphase & 1, abort_flag, st, 34);
+            ++xphase;
+            if (!__all_sync(0xffffffffu, w)) return false;
+            theirs = slot[(half ^ 1) * AT_BM];
+            return true;
+        };
 
         for (int j = 0; j < n && ok; ++j) {
-            // the whole warp leaves together: the TMEM accesses below are warp-collective
+            // the whole warp leaves together: the TMEM accesses below are warp-collective.
+            // S(j) is issued after P V(j-1), so its arrival also means O and the P columns are idle.
             if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_SFULL + tile], j & 1, abort_flag, st, 31))) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            // columns of this page the row may see (all of them except on the diagonal pages)
-            const long long vis_ll = limit - (long long)j * BN + 1;
-            const int vis = vis_ll > BN ? BN : (vis_ll < 0 ? 0 : (int)vis_ll);
-            const bool need_mask = a.causal && ((long long)j * BN + BN - 1 > tile_limit);   // same for the whole tile
-            // pass 1: row maximum of the raw scores (the scale is positive, so it commutes with max)
-            float mx = -INFINITY;
-            {
-                uint32_t va[CW], vb[CW];
-                tc_tmem_ld<CW>(s_addr, va);
+            // this thread's part of the score row moves to registers in one go
+            uint32_t v[NCH][CW];
 #pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 2 * CW) {
-                    tc_tmem_ld_wait();
-                    if (c0 + CW < BN) tc_tmem_ld<CW>(s_addr + c0 + CW, vb);
-                    mx = need_mask ? at_chunk_max<CW, true>(va, vis - c0, mx) : at_chunk_max<CW, false>(va, 0, mx);
-                    if (c0 + CW < BN) {
-                        tc_tmem_ld_wait();
-                        if (c0 + 2 * CW < BN) tc_tmem_ld<CW>(s_addr + c0 + 2 * CW, va);
-                        mx = need_mask ? at_chunk_max<CW, true>(vb, vis - c0 - CW, mx)
-                                       : at_chunk_max<CW, false>(vb, 0, mx);
-                    }
-                }
-            }
-            m_run = fmaxf(m_run, mx * sl);
+            for (int c = 0; c < NCH; ++c) tc_tmem_ld<CW>(s_addr + c * CW, v[c]);
+            tc_tmem_ld_wait();
+
+            // columns of this thread's range the row may see (all of them except on the diagonal pages)
+            const long long vis_ll = limit - ((long long)j * BN + half * HB) + 1;
+            const int vis = vis_ll > HB ? HB : (vis_ll < 0 ? 0 : (int)vis_ll);
+            const bool need_mask = a.causal && ((long long)j * BN + BN - 1 > tile_limit);   // same for the whole tile
+            // row maximum of the raw scores (the scale is positive, so it commutes with max)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+                mx = need_mask ? at_chunk_max<CW, true>(v[c], vis - c * CW, mx) : at_chunk_max<CW, false>(v[c], 0, mx);
+            float mx_other;
+            // after the swap both threads of the row have their scores in registers: P may go over them
+            if (!swap_with_partner(mx, mx_other)) { ok = false; break; }
+            m_run = fmaxf(m_run, fmaxf(mx, mx_other) * sl);
             // move the exponent reference only when the maximum has outgrown it by 2^8
+            // (m_run and m_ref are the same on both threads of a row, so they move together)
             const bool move = m_run > m_ref + AT_RESCALE_GAP;
             if (__any_sync(0xffffffffu, move)) {
                 const float alpha = move ? at_ex2(m_ref - m_run) : 1.0f;
                 if (move) m_ref = m_run;
                 l_run *= alpha;
                 if (j > 0) {
-                    // P_i V(j-1) has completed (its commit published these scores): O is idle
-#pragma unroll
-                    for (int c0 = 0; c0 < AT_D; c0 += 32) {
-                        uint32_t o[32];
-                        tc_tmem_ld32(o_addr + c0, o);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < OH; c0 += 16) {
+                        uint32_t o[16];
+                        tc_tmem_ld16(o_addr + c0, o);
                         tc_tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tc_tmem_st32(o_addr + c0, o);
+                        for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tc_tmem_st16(o_addr + c0, o);
                     }
-                    tc_tmem_st_wait();
                 }
             }
-            // pass 2: P = exp2(s * sl - m_ref) -> f16 -> shared memory (K-major, 128-byte swizzle)
+            // P = exp2(s * sl - m_ref) -> f16 pairs -> TMEM
             uint64_t acc2 = at_pack2(0.f, 0.f);
-            {
-                uint32_t va[CW], vb[CW];
-                auto emit = [&](const uint32_t (&v)[CW], int c0) {
-                    uint32_t packed[CW / 2];
-                    if (need_mask) at_chunk_prob<CW, true>(v, vis - c0, sl, m_ref, acc2, packed);
-                    else at_chunk_prob<CW, false>(v, 0, sl, m_ref, acc2, packed);
-                    uint8_t* blk = p_row + (c0 >> 6) * (AT_BM * 128);
-                    const int chunk0 = (c0 & 63) >> 3;
 #pragma unroll
-                    for (int c = 0; c < CW / 8; ++c) {
-                        const int phys = (chunk0 + c) ^ (r & 7);
-                        *reinterpret_cast<uint4*>(blk + phys * 16) =
-                            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-                    }
-                };
-                tc_tmem_ld<CW>(s_addr, va);
-#pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 2 * CW) {
-                    tc_tmem_ld_wait();
-                    if (c0 + CW < BN) tc_tmem_ld<CW>(s_addr + c0 + CW, vb);
-                    emit(va, c0);
-                    if (c0 + CW < BN) {
-                        tc_tmem_ld_wait();
-                        if (c0 + 2 * CW < BN) tc_tmem_ld<CW>(s_addr + c0 + 2 * CW, va);
-                        emit(vb, c0 + CW);
-                    }
-                }
+            for (int c = 0; c < NCH; ++c) {
+                uint32_t packed[CW / 2];
+                if (need_mask) at_chunk_prob<CW, true>(v[c], vis - c * CW, sl, m_ref, acc2, packed);
+                else at_chunk_prob<CW, false>(v[c], 0, sl, m_ref, acc2, packed);
+                tc_tmem_st<CW / 2>(p_addr + c * (CW / 2), packed);
             }
             float s0, s1;
             at_unpack2(acc2, s0, s1);
             l_run += s0 + s1;
-            tc_fence_before_sync();          // S and O accesses of this thread are complete
-            tc_fence_proxy_async();          // P stores visible to the tensor-core (async) proxy
+            tc_tmem_st_wait();
+            tc_fence_before_sync();          // P (and O) stores of this thread are complete
             __syncwarp();
             if (lane == 0) tc_mbar_arrive(&bars[B_PFULL + tile]);
         }
-        if (ok && n > 0 && __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_ODONE + tile], 0, abort_flag, st, 33))) {
+        if (ok && n > 0 &&
+            __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PVDONE + tile], 0, abort_flag, st, 33))) {
             tc_fence_after_sync();
-            const float inv = 1.0f / l_run;
-            const bool store = *abort_flag == 0 && R < a.seq_q;
-            __half* dst = reinterpret_cast<__half*>(a.arena) + a.o_off + (int64_t)R * a.o_row_stride +
-                          (int64_t)head * a.o_head_stride;
+            // total row sum = the two partial sums (same rescaling history on both threads)
+            float l_other = 0.f;
+            if (swap_with_partner(l_run, l_other)) {
+                const float inv = 1.0f / (l_run + l_other);
+                const bool store = *abort_flag == 0 && R < a.seq_q;
+                __half* dst = reinterpret_cast<__half*>(a.arena) + a.o_off + (int64_t)R * a.o_row_stride +
+                              (int64_t)head * a.o_head_stride + half * OH;
 #pragma unroll
-            for (int c0 = 0; c0 < AT_D; c0 += 32) {
-                uint32_t o[32];
-                tc_tmem_ld32(o_addr + c0, o);
-                tc_tmem_ld_wait();
-                if (store) {
+                for (int c0 = 0; c0 < OH; c0 += 32) {
+                    uint32_t o[32];
+                    tc_tmem_ld32(o_addr + c0, o);
+                    tc_tmem_ld_wait();
+                    if (store) {
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        uint4 w;
-                        __half2* h = reinterpret_cast<__half2*>(&w);
+                        for (int c = 0; c < 32; c += 8) {
+                            uint4 w;
+                            __half2* h = reinterpret_cast<__half2*>(&w);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            h[i] = __floats2half2_rn(__uint_as_float(o[c + 2 * i]) * inv,
-                                                     __uint_as_float(o[c + 2 * i + 1]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c0 + c) = w;
+                            for (int i = 0; i < 4; ++i)
+                                h[i] = __floats2half2_rn(__uint_as_float(o[c + 2 * i]) * inv,
+                                                         __uint_as_float(o[c + 2 * i + 1]) * inv);
+                            *reinterpret_cast<uint4*>(dst + c0 + c) = w;
+                        }
                     }
                 }
             }
@@ -398,7 +443,8 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 template <int BN>
 static int launch_attn(ktb_ctx* ctx, const ktb_attn_args& a, const CUtensorMap& mq, const CUtensorMap& mk,
                        const CUtensorMap& mv) {
-    constexpr size_t SMEM = 2 * AT_Q_BYTES + AT_STAGES * (size_t)(BN * AT_D * 2) + 2 * (size_t)(BN < 64 ? 64 : BN) * AT_BM * 2 + 1024 + 256;
+    constexpr int AT_STAGES = BN == 128 ? 4 : 8;
+    constexpr size_t SMEM = 2 * AT_Q_BYTES + AT_STAGES * (size_t)(BN * AT_D * 2) + 2 * 2 * 2 * AT_BM * 4 + 1024 + 512;
     static bool attr_set = false;
     if (!attr_set) {
         KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));

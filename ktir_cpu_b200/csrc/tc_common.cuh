@@ -44,6 +44,19 @@ static __device__ __forceinline__ uint32_t tc_mbar_try_wait(uint64_t* bar, uint3
     return ok;
 }
 
+// Non-blocking test of a phase (for a thread that serves several barriers).
+static __device__ __forceinline__ uint32_t tc_mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(tc_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
+}
+
 // Bounded wait (about one second of SM clocks).  Returns false (and records `site`) if the
 // phase never completed or the CTA aborted.
 static __device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -153,6 +166,17 @@ static __device__ __forceinline__ void tc_tmem_ld16(uint32_t taddr, uint32_t (&r
         : "memory");
 }
 
+// one column: thread i of the warp gets / sets the word of row (lane base + i)
+static __device__ __forceinline__ uint32_t tc_tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return r;
+}
+
+static __device__ __forceinline__ void tc_tmem_st1(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+
 template <int N>
 static __device__ __forceinline__ void tc_tmem_ld(uint32_t taddr, uint32_t (&r)[N]);
 template <>
@@ -175,6 +199,31 @@ static __device__ __forceinline__ void tc_tmem_st32(uint32_t taddr, const uint32
           "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+
+static __device__ __forceinline__ void tc_tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+static __device__ __forceinline__ void tc_tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+        : "memory");
+}
+
+template <int N>
+static __device__ __forceinline__ void tc_tmem_st(uint32_t taddr, const uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tc_tmem_st<32>(uint32_t taddr, const uint32_t (&r)[32]) { tc_tmem_st32(taddr, r); }
+template <>
+__device__ __forceinline__ void tc_tmem_st<16>(uint32_t taddr, const uint32_t (&r)[16]) { tc_tmem_st16(taddr, r); }
+template <>
+__device__ __forceinline__ void tc_tmem_st<8>(uint32_t taddr, const uint32_t (&r)[8]) { tc_tmem_st8(taddr, r); }
 
 static __device__ __forceinline__ void tc_tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
