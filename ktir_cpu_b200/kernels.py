@@ -419,3 +419,137 @@ def causal_attention(seq: int = 2048, heads: int = 256, head_dim: int = 128, til
     s += (f"    ktdp.store %o3, %o_tile : {f([tm, 1, hd], 'f16')}, !ktdp.access_tile<{_xs([tm, 1, hd], 'index')}>\n"
           f"    return\n  }}\n}}\n")
     return s
+
+
+def layernorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, eps: float = 1e-5) -> str:
+    """y = (x - mean) / sqrt(var + eps) * w + b per row, f32 statistics, one row per iteration.
+
+    The op mix of examples/triton-ktir/layernorm_fwd_ktir.mlir (sum reduction, broadcast, rsqrt,
+    per-column weight and bias) at a size of one's choosing; also writes the row means."""
+    R = n_rows // cores
+    assert R * cores == n_rows
+    t16, t32, tv = f"tensor<1x{n_cols}xf16>", f"tensor<1x{n_cols}xf32>", "tensor<1xf32>"
+    at, atv = f"!ktdp.access_tile<1x{n_cols}xindex>", "!ktdp.access_tile<1xindex>"
+    s = (f"module {{\n  func.func @layernorm_kernel(%x_ptr: index, %w_ptr: index, %b_ptr: index, %y_ptr: index, "
+         f"%mean_ptr: index) attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n    %c1 = arith.constant 1 : index\n"
+         f"    %rows = arith.constant {R} : index\n"
+         f"    %row0 = arith.muli %core_id, %rows : index\n"
+         f"    %row_end = arith.addi %row0, %rows : index\n"
+         f"    %zero = arith.constant 0.0 : f32\n"
+         f"    %inv_n = arith.constant {1.0 / n_cols} : f32\n"
+         f"    %eps = arith.constant {eps} : f32\n")
+    s += view("x_view", "x_ptr", [n_rows, n_cols], "f16") + view("y_view", "y_ptr", [n_rows, n_cols], "f16")
+    s += view("w_view", "w_ptr", [1, n_cols], "f16") + view("b_view", "b_ptr", [1, n_cols], "f16")
+    s += view("mean_view", "mean_ptr", [n_rows], "f32")
+    s += tile("w_tile", "w_view", ["%c0", "%c0"], [1, n_cols], [1, n_cols], "f16")
+    s += tile("b_tile", "b_view", ["%c0", "%c0"], [1, n_cols], [1, n_cols], "f16")
+    s += (f"    %w16 = ktdp.load %w_tile : {at} -> {t16}\n    %b16 = ktdp.load %b_tile : {at} -> {t16}\n"
+          f"    %w = arith.extf %w16 : {t16} to {t32}\n    %b = arith.extf %b16 : {t16} to {t32}\n"
+          f"    scf.for %row = %row0 to %row_end step %c1 {{\n")
+    s += tile("x_tile", "x_view", ["%row", "%c0"], [1, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += (f"      %x16 = ktdp.load %x_tile : {at} -> {t16}\n"
+          f"      %x = arith.extf %x16 : {t16} to {t32}\n"
+          f"      %acc0 = tensor.splat %zero : {tv}\n"
+          f"      %sum = linalg.reduce {{ arith.addf }} ins(%x : {t32}) outs(%acc0 : {tv}) dimensions = [1]\n"
+          f"      %inv_n_t = tensor.splat %inv_n : {tv}\n"
+          f"      %mean = arith.mulf %sum, %inv_n_t : {tv}\n"
+          f"      %bshape = tensor.empty() : {t32}\n"
+          f"      %mean_b = linalg.broadcast ins(%mean : {tv}) outs(%bshape : {t32}) dimensions = [1]\n"
+          f"      %xc = arith.subf %x, %mean_b : {t32}\n"
+          f"      %sq = arith.mulf %xc, %xc : {t32}\n"
+          f"      %acc1 = tensor.splat %zero : {tv}\n"
+          f"      %ssq = linalg.reduce {{ arith.addf }} ins(%sq : {t32}) outs(%acc1 : {tv}) dimensions = [1]\n"
+          f"      %var = arith.mulf %ssq, %inv_n_t : {tv}\n"
+          f"      %eps_t = tensor.splat %eps : {tv}\n"
+          f"      %var_eps = arith.addf %var, %eps_t : {tv}\n"
+          f"      %rstd = math.rsqrt %var_eps : {tv}\n"
+          f"      %rstd_b = linalg.broadcast ins(%rstd : {tv}) outs(%bshape : {t32}) dimensions = [1]\n"
+          f"      %xn = arith.mulf %xc, %rstd_b : {t32}\n"
+          f"      %xw = arith.mulf %xn, %w : {t32}\n"
+          f"      %y = arith.addf %xw, %b : {t32}\n"
+          f"      %y16 = arith.truncf %y : {t32} to {t16}\n")
+    s += tile("y_tile", "y_view", ["%row", "%c0"], [1, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += tile("m_tile", "mean_view", ["%row"], [1], [n_rows], "f32", "      ")
+    s += (f"      ktdp.store %y16, %y_tile : {t16}, {at}\n"
+          f"      ktdp.store %mean, %m_tile : {tv}, {atv}\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
+def naive_attention(seq: int = 64, head_dim: int = 32, cores: int = 2) -> str:
+    """softmax(Q K^T * scale) V with whole-tile matmuls, a transpose and f32 softmax — the shape of
+    examples/triton-ktir/sdpa_2d.mlir: each core handles a block of query rows against all of K and V."""
+    R = seq // cores
+    assert R * cores == seq
+    tq, tk = f"tensor<{R}x{head_dim}xf16>", f"tensor<{seq}x{head_dim}xf16>"
+    tq32, tk32, tkt = f"tensor<{R}x{head_dim}xf32>", f"tensor<{seq}x{head_dim}xf32>", f"tensor<{head_dim}x{seq}xf32>"
+    ts, tv = f"tensor<{R}x{seq}xf32>", f"tensor<{R}xf32>"
+    atq, atk = f"!ktdp.access_tile<{R}x{head_dim}xindex>", f"!ktdp.access_tile<{seq}x{head_dim}xindex>"
+    s = (f"module {{\n  func.func @naive_attention(%q_ptr: index, %k_ptr: index, %v_ptr: index, %o_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %rows = arith.constant {R} : index\n"
+         f"    %row0 = arith.muli %core_id, %rows : index\n"
+         f"    %scale = arith.constant {head_dim ** -0.5} : f32\n"
+         f"    %zero = arith.constant 0.0 : f32\n"
+         f"    %ninf_bits = arith.constant 0xFF800000 : i32\n"
+         f"    %ninf = arith.bitcast %ninf_bits : i32 to f32\n")
+    for nm in ("q", "k", "v", "o"):
+        s += view(f"{nm}_view", f"{nm}_ptr", [seq, head_dim], "f16")
+    s += tile("q_tile", "q_view", ["%row0", "%c0"], [R, head_dim], [seq, head_dim], "f16")
+    s += tile("k_tile", "k_view", ["%c0", "%c0"], [seq, head_dim], [seq, head_dim], "f16")
+    s += tile("v_tile", "v_view", ["%c0", "%c0"], [seq, head_dim], [seq, head_dim], "f16")
+    s += tile("o_tile", "o_view", ["%row0", "%c0"], [R, head_dim], [seq, head_dim], "f16")
+    s += (f"    %q16 = ktdp.load %q_tile : {atq} -> {tq}\n"
+          f"    %k16 = ktdp.load %k_tile : {atk} -> {tk}\n"
+          f"    %v16 = ktdp.load %v_tile : {atk} -> {tk}\n"
+          f"    %q = arith.extf %q16 : {tq} to {tq32}\n"
+          f"    %k = arith.extf %k16 : {tk} to {tk32}\n"
+          f"    %v = arith.extf %v16 : {tk} to {tk32}\n"
+          f"    %kt_init = tensor.empty() : {tkt}\n"
+          f"    %kt = linalg.transpose ins(%k : {tk32}) outs(%kt_init : {tkt}) permutation = [1, 0]\n"
+          f"    %s_init = tensor.splat %zero : {ts}\n"
+          f"    %s = linalg.matmul ins(%q, %kt : {tq32}, {tkt}) outs(%s_init : {ts}) -> {ts}\n"
+          f"    %scale_t = tensor.splat %scale : {ts}\n"
+          f"    %ss = arith.mulf %s, %scale_t : {ts}\n"
+          f"    %m_init = tensor.splat %ninf : {tv}\n"
+          f"    %m = linalg.reduce {{ arith.maximumf }} ins(%ss : {ts}) outs(%m_init : {tv}) dimensions = [1]\n"
+          f"    %bshape = tensor.empty() : {ts}\n"
+          f"    %m_b = linalg.broadcast ins(%m : {tv}) outs(%bshape : {ts}) dimensions = [1]\n"
+          f"    %sh = arith.subf %ss, %m_b : {ts}\n"
+          f"    %p = math.exp %sh : {ts}\n"
+          f"    %l_init = tensor.splat %zero : {tv}\n"
+          f"    %l = linalg.reduce {{ arith.addf }} ins(%p : {ts}) outs(%l_init : {tv}) dimensions = [1]\n"
+          f"    %l_b = linalg.broadcast ins(%l : {tv}) outs(%bshape : {ts}) dimensions = [1]\n"
+          f"    %pn = arith.divf %p, %l_b : {ts}\n"
+          f"    %o_init = tensor.splat %zero : {tq32}\n"
+          f"    %o = linalg.matmul ins(%pn, %v : {ts}, {tk32}) outs(%o_init : {tq32}) -> {tq32}\n"
+          f"    %o16 = arith.truncf %o : {tq32} to {tq}\n"
+          f"    ktdp.store %o16, %o_tile : {tq}, {atq}\n"
+          f"    return\n  }}\n}}\n")
+    return s
+
+
+def gather_elements(n_rows: int = 32, n_cols: int = 16, n_src: int = 64) -> str:
+    """out[i, j] = src[idx[i, j], j] — an indirect access tile whose index varies along both tile
+    dimensions (the general form of examples/rfc/indirect-access-copy.mlir), one core."""
+    t = f"tensor<{n_rows}x{n_cols}xf16>"
+    at = f"!ktdp.access_tile<{n_rows}x{n_cols}xindex>"
+    s = (f"module {{\n  func.func @gather_elements(%src_ptr: index, %idx_ptr: index, %out_ptr: index) "
+         f"attributes {{grid = [1, 1]}} {{\n    %c0 = arith.constant 0 : index\n")
+    s += view("src", "src_ptr", [n_src, n_cols], "f16") + view("idx", "idx_ptr", [n_rows, n_cols], "i32")
+    s += view("out", "out_ptr", [n_rows, n_cols], "f16")
+    s += (f"    %g = ktdp.construct_indirect_access_tile\n"
+          f"        intermediate_variables(%d0, %d1)\n"
+          f"        %src[ind(%idx[%d0, %d1]), (%d1)] {{\n"
+          f"      variables_space_set = {_box([n_rows, n_cols])},\n"
+          f"      variables_space_order = {_ident(2)}\n"
+          f"    }} : memref<{_xs([n_src, n_cols], 'f16')}>, memref<{_xs([n_rows, n_cols], 'i32')}>"
+          f" -> {at}\n")
+    s += tile("o_tile", "out", ["%c0", "%c0"], [n_rows, n_cols], [n_rows, n_cols], "f16")
+    s += (f"    %vals = ktdp.load %g : {at} -> {t}\n"
+          f"    ktdp.store %vals, %o_tile : {t}, {at}\n    return\n  }}\n}}\n")
+    return s

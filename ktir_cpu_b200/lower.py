@@ -554,31 +554,41 @@ class Plan:
         self.statements = []
 
 
+def _fused_statement(dev, st: Store, arena: ArenaMap, sid: int, row_shard):
+    """The fused kernel that fits this store, trying the idioms in a fixed order."""
+    if isinstance(st.target, IndirectAccess):
+        from .lower_scatter import lower_indirect_store
+        return lower_indirect_store(dev, st, arena, sid, row_shard)
+    m = match_softmax(st.value)
+    if m is not None:
+        return SoftmaxStatement(dev, st, m, arena, sid)
+    from .lower_mm import try_lower_matmul
+    stmt = try_lower_matmul(dev, st, arena, sid)
+    if stmt is None:
+        from .lower_attn import try_lower_attention
+        stmt = try_lower_attention(dev, st, arena, sid)
+    if stmt is None:
+        from .lower_scatter import RowsStatement, has_indirect_load
+        if has_indirect_load(st.value):
+            stmt = RowsStatement(dev, st, arena, sid)
+    if stmt is None:
+        stmt = EwStatement(dev, st, arena, sid)
+    return stmt
+
+
 def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None) -> Plan:
     """``row_shard = (rank, world)``: ordered scatters apply only the destination rows this rank owns."""
     plan = Plan()
     for st in stores:
         sid = len(plan.statements)
-        if isinstance(st.target, IndirectAccess):
-            from .lower_scatter import lower_indirect_store
-            plan.statements.append(lower_indirect_store(dev, st, arena, sid, row_shard))
-            continue
-        stmt = None
-        m = match_softmax(st.value)
-        if m is not None:
-            stmt = SoftmaxStatement(dev, st, m, arena, sid)
-        if stmt is None:
-            from .lower_mm import try_lower_matmul
-            stmt = try_lower_matmul(dev, st, arena, sid)
-        if stmt is None:
-            from .lower_attn import try_lower_attention
-            stmt = try_lower_attention(dev, st, arena, sid)
-        if stmt is None:
-            from .lower_scatter import RowsStatement, has_indirect_load
-            if has_indirect_load(st.value):
-                stmt = RowsStatement(dev, st, arena, sid)
-        if stmt is None:
-            stmt = EwStatement(dev, st, arena, sid)
+        try:
+            stmt = _fused_statement(dev, st, arena, sid, row_shard)
+        except Unsupported:
+            # no fused kernel fits: run the tile program step by step
+            if row_shard is not None and isinstance(st.target, IndirectAccess):
+                raise
+            from .lower_generic import generic_statement
+            stmt = generic_statement(dev, st, arena, sid)
         plan.statements.append(stmt)
     fps = [f for s in plan.statements for f in s.footprints()]
     check_hazards(fps)

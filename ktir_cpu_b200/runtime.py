@@ -91,6 +91,23 @@ class AttnArgs(C.Structure):
                 ("scale", C.c_float), ("m_init", C.c_float), ("l_init", C.c_float), ("reserved", C.c_int32)]
 
 
+G_MAXDIM = 6
+G_KINDS = {k: i for i, k in enumerate(["load", "addr", "idxadd", "gather", "constv", "fill", "param", "iota", "map",
+                                       "ew", "redl", "matmul", "store", "scatter"])}
+
+
+class GenOpArgs(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("op", C.c_int32), ("dt_dst", C.c_int32), ("dt_a", C.c_int32),
+                ("dt_b", C.c_int32), ("dt_c", C.c_int32), ("flags", C.c_int32), ("ndim", C.c_int32),
+                ("points", C.c_int64), ("elems", C.c_int64), ("ea", C.c_int64), ("eb", C.c_int64), ("ec", C.c_int64),
+                ("dst", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("arena", C.c_void_p),
+                ("dev_base", C.c_void_p), ("dev_rel", C.c_void_p), ("dev_table", C.c_void_p),
+                ("lo", C.c_int64), ("hi", C.c_int64), ("shape", C.c_int64 * G_MAXDIM),
+                ("strides", C.c_int64 * G_MAXDIM), ("offset", C.c_int64), ("outer", C.c_int64), ("n", C.c_int64),
+                ("inner", C.c_int64), ("h", C.c_int64), ("batch", C.c_int64), ("M", C.c_int64), ("N", C.c_int64),
+                ("K", C.c_int64), ("fimm", C.c_double), ("iimm", C.c_int64)]
+
+
 _lib: Optional[C.CDLL] = None
 
 # name -> (restype, argtypes); every symbol include/ktir_b200.h declares
@@ -118,6 +135,7 @@ SYMBOLS = {
     "ktb_launch_scatter_rows": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
     "ktb_scatter_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
     "ktb_launch_scatter_rows_static": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
+    "ktb_launch_generic": (C.c_int, [C.c_void_p, C.POINTER(GenOpArgs)]),
     "ktb_launch_gemm_f16": (C.c_int, [C.c_void_p, C.POINTER(GemmArgs)]),
     "ktb_launch_attention_fwd": (C.c_int, [C.c_void_p, C.POINTER(AttnArgs)]),
 }

@@ -210,7 +210,11 @@ def indirect_sticks(acc: IndirectAccess, axes, sel: np.ndarray, host) -> np.ndar
     ``host.read(dtype, element_indices)`` returns the caller's values at those element indices.
     """
     from .lower_scatter import row_form
-    f = row_form(acc, axes, sel)
+    from .trace import Unsupported
+    try:
+        f = row_form(acc, axes, sel)
+    except Unsupported:
+        return _indirect_sticks_general(acc, axes, sel, host)
     n = len(sel)
     if n == 0:
         return np.zeros(0, np.int64)
@@ -227,3 +231,49 @@ def indirect_sticks(acc: IndirectAccess, axes, sel: np.ndarray, host) -> np.ndar
     ia = idx_elems * ib
     idx = _union_count(ia // STICK_BYTES, (ia + ib - 1) // STICK_BYTES)
     return (data + idx).astype(np.int64)
+
+
+def _unique_per_row(x: np.ndarray) -> np.ndarray:
+    """Number of distinct values in each row of a 2-D integer array."""
+    if x.shape[1] == 0:
+        return np.zeros(x.shape[0], np.int64)
+    y = np.sort(x, axis=1)
+    return 1 + (np.diff(y, axis=1) != 0).sum(1)
+
+
+def _indirect_sticks_general(ia: IndirectAccess, axes, sel: np.ndarray, host) -> np.ndarray:
+    """Stick counts of an indirect tile of any rectangular form: one address per element, host side."""
+    from .lower_scatter import _lin
+    from .trace import Unsupported
+    if ia.order is not None and not ia.order.is_identity():
+        raise Unsupported("indirect access tile with a permuted variables_space_order")
+    box = ia.aset.box()
+    if box is None:
+        raise Unsupported("indirect access tile over a non-rectangular variable space")
+    lo, hi = box
+    ext = [h - l for l, h in zip(lo, hi)]
+    nv = len(ext)
+    vars_e = np.indices(ext, dtype=np.int64).reshape(nv, -1) + np.asarray(lo, np.int64)[:, None]
+
+    def at(v):
+        return np.ascontiguousarray(iv_full(v, axes).reshape(-1)[sel]).astype(np.int64)
+
+    addr = at(ia.view.base)[:, None] + np.zeros((1, vars_e.shape[1]), np.int64)
+    idx_sticks = np.zeros(len(sel), np.int64)
+    for sub, stride in zip(ia.subs, ia.view.strides):
+        if sub["kind"] == "direct":
+            c, b = _lin(sub["expr"], nv, ia.ssa)
+            addr = addr + stride * ((np.asarray(c, np.int64)[:, None] * vars_e).sum(0)[None, :] + at(b)[:, None])
+        else:
+            iv = ia.index_views[sub["view"]]
+            iaddr = at(iv.base)[:, None] + np.zeros((1, vars_e.shape[1]), np.int64)
+            for e_, s_ in zip(sub["exprs"], iv.strides):
+                c, b = _lin(e_, nv, ia.ssa)
+                iaddr = iaddr + s_ * ((np.asarray(c, np.int64)[:, None] * vars_e).sum(0)[None, :] + at(b)[:, None])
+            vals = host.read(iv.dtype, iaddr.reshape(-1)).reshape(iaddr.shape).astype(np.int64)
+            if (vals < 0).any():
+                raise IndexError(f"indirect index {int(vals[vals < 0][0])} is negative")
+            addr = addr + vals * stride
+            idx_sticks += _unique_per_row(iaddr * bytes_per_elem(iv.dtype) // STICK_BYTES)
+    data = _unique_per_row(addr * bytes_per_elem(ia.view.dtype) // STICK_BYTES)
+    return (data + idx_sticks).astype(np.int64)

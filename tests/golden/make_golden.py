@@ -2,7 +2,7 @@
 
 Usage (only where the reference checkout is available):
 
-    python tests/golden/make_golden.py /path/to/reference [--latency-only]
+    python tests/golden/make_golden.py /path/to/reference [--latency-only] [--only=<case> ...]
 
 Each fixture stores the KTIR source, the seeded inputs and the outputs the
 reference produced, plus the NumPy version and CPU features of the generating
@@ -68,14 +68,30 @@ def cases():
              value_cache_ptr=v.reshape(S // tn, tn, H, D),
              block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
              num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D))))
+    rng = np.random.default_rng(6)
+    out["layernorm_16x64"] = (
+        K.layernorm_rows(16, 64, 4), "layernorm_kernel",
+        dict(x_ptr=rng.standard_normal((16, 64)).astype(np.float16), w_ptr=rng.standard_normal((1, 64)).astype(np.float16),
+             b_ptr=rng.standard_normal((1, 64)).astype(np.float16), y_ptr=np.zeros((16, 64), np.float16),
+             mean_ptr=np.zeros(16, np.float32)))
+    out["naive_attention_32x16"] = (
+        K.naive_attention(32, 16, 2), "naive_attention",
+        dict(q_ptr=rng.standard_normal((32, 16)).astype(np.float16), k_ptr=rng.standard_normal((32, 16)).astype(np.float16),
+             v_ptr=rng.standard_normal((32, 16)).astype(np.float16), o_ptr=np.zeros((32, 16), np.float16)))
+    out["gather_elements_8x16"] = (
+        K.gather_elements(8, 16, 32), "gather_elements",
+        dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),
+             idx_ptr=rng.integers(0, 32, (8, 16)).astype(np.int32), out_ptr=np.zeros((8, 16), np.float16)))
     return out
 
 
-def main(ref_root: str):
+def main(ref_root: str, only=None):
     sys.path.insert(0, ref_root)
     from ktir_cpu import KTIRInterpreter
     meta = f"numpy {np.__version__}"
     for name, (src, fn, kw) in cases().items():
+        if only and name not in only:
+            continue
         interp = KTIRInterpreter()
         interp.load(src)
         res = interp.execute_function(fn, **kw)
@@ -113,6 +129,7 @@ def latency_main(ref_root: str):
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     root = args[0] if args else "/root/reference"
+    only = [a[len("--only="):] for a in sys.argv[1:] if a.startswith("--only=")]
     if "--latency-only" not in sys.argv:
-        main(root)
+        main(root, only)
     latency_main(root)

@@ -355,3 +355,42 @@ def test_sharded_ranks_reproduce_the_full_result(world, build_lib):
         got, covered = _sharded_on_one_gpu(src, "attention_kernel", kw, world, "output_ptr")
         np.testing.assert_array_equal(got, full["output_ptr"])
         assert covered == q.nbytes
+
+
+def test_fallback_steps_match_the_oracle(build_lib):
+    """Kernels no fused kernel covers run step by step on the device (statement kind 'generic')."""
+    rng = np.random.default_rng(31)
+    cases = [
+        (K.layernorm_rows(64, 256, 4), "layernorm_kernel",
+         dict(x_ptr=rng.standard_normal((64, 256)).astype(np.float16), w_ptr=rng.standard_normal((1, 256)).astype(np.float16),
+              b_ptr=rng.standard_normal((1, 256)).astype(np.float16), y_ptr=np.zeros((64, 256), np.float16),
+              mean_ptr=np.zeros(64, np.float32)), 2e-3),
+        (K.naive_attention(64, 32, 2), "naive_attention",
+         dict(q_ptr=rng.standard_normal((64, 32)).astype(np.float16), k_ptr=rng.standard_normal((64, 32)).astype(np.float16),
+              v_ptr=rng.standard_normal((64, 32)).astype(np.float16), o_ptr=np.zeros((64, 32), np.float16)), 2e-3),
+        (K.gather_elements(32, 16, 64), "gather_elements",
+         dict(src_ptr=rng.standard_normal((64, 16)).astype(np.float16), idx_ptr=rng.integers(0, 64, (32, 16)).astype(np.int32),
+              out_ptr=np.zeros((32, 16), np.float16)), 0.0),
+    ]
+    for src, fn, kw, tol in cases:
+        gpu = KTIRInterpreter()
+        gpu.load(src)
+        sess, _ = gpu.session(fn, **kw)
+        assert any(s.kind == "generic" for s in sess.plan.statements)
+        gpu.close()
+        got, want = _run_both(src, fn, kw)
+        for k in want:
+            if tol == 0.0:
+                np.testing.assert_array_equal(got[k], want[k])
+            else:
+                np.testing.assert_allclose(got[k].astype(np.float32), want[k].astype(np.float32), rtol=tol, atol=tol)
+    # a negative index on the step-by-step path raises like the fused kernels do
+    src, fn, kw, _ = cases[2]
+    kw = dict(kw)
+    kw["idx_ptr"] = kw["idx_ptr"].copy()
+    kw["idx_ptr"][1, 1] = -5
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    with pytest.raises(IndexError, match="negative"):
+        gpu.execute_function(fn, **kw)
+    gpu.close()
