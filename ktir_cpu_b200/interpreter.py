@@ -14,7 +14,7 @@ ktir_cpu/memory.py:330-352 allocates), so SSA pointer values — element indices
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Sequence, Any, Dict, List, Optional, Tuple
 
 import numpy as np
 
@@ -78,9 +78,11 @@ class Session:
 
     def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
                  scalars: Dict[str, Any], latency: bool = False, shard: Optional[Tuple[int, int]] = None,
-                 arena_ptr: Optional[int] = None):
+                 arena_ptr: Optional[int] = None, seeded: Sequence[Tuple[int, int, str]] = ()):
         """``shard = (rank, world)`` plans only this rank's part of the kernel (see ``sharded.py``);
-        ``arena_ptr`` places the arena in caller-owned device memory of at least ``arena_size(tensors)`` bytes."""
+        ``arena_ptr`` places the arena in caller-owned device memory of at least ``arena_size(tensors)`` bytes;
+        ``seeded`` = (byte address, nbytes, dtype) of memory written through ``interp.memory.hbm`` at fixed
+        addresses, which becomes part of the arena next to the argument tensors."""
         self.dev = dev
         self.func = func
         self.latency_records = None
@@ -97,6 +99,9 @@ class Session:
             allocs.append(Allocation(name, nxt, nxt + nbytes, kdt))
             ptrs[name] = nxt // bytes_per_elem(kdt)
             nxt = (nxt + nbytes + STICK - 1) & ~(STICK - 1)
+        for addr, nbytes, kdt in seeded:
+            allocs.append(Allocation(f"hbm@0x{addr:x}", addr, addr + nbytes, kdt))
+            nxt = max(nxt, (addr + nbytes + STICK - 1) & ~(STICK - 1))
         self.arena_bytes = nxt
         self.arena = dev.alloc(self.arena_bytes + 256) if arena_ptr is None else arena_ptr
         self.arena_map = ArenaMap(allocs)
@@ -170,6 +175,43 @@ def _scalar_key(v):
     return ("o", repr(v))
 
 
+class _HBMFacade:
+    """``interp.memory.hbm`` of the reference, as far as its tests use it: ``write(stick, data)`` before a
+    run places data at byte address ``stick * 128`` (ktir_cpu/memory.py:354-398); ``read(stick, n, dtype)``
+    afterwards returns what the kernels left there.  The data lives in the arena during the run."""
+
+    def __init__(self):
+        self.regions: Dict[int, np.ndarray] = {}         # byte address -> flat array
+
+    def write(self, stick: int, data):
+        arr = np.ascontiguousarray(np.asarray(data)).reshape(-1)
+        to_ktir_dtype(arr.dtype)
+        self.regions[int(stick) * STICK] = arr.copy()
+
+    def read(self, stick: int, n_elements: int, dtype: str) -> np.ndarray:
+        from .dtypes import to_np_dtype
+        npdt = np.dtype(to_np_dtype(dtype))
+        addr = int(stick) * STICK
+        for base, arr in self.regions.items():
+            end = base + arr.nbytes
+            if base <= addr < end:
+                raw = arr.view(np.uint8)[addr - base:addr - base + n_elements * npdt.itemsize]
+                out = np.zeros(n_elements, npdt)                  # short reads are zero padded
+                out.view(np.uint8)[:raw.size] = raw
+                return out
+        raise ValueError(f"Read from unmapped address 0x{addr:x} (n_elements={n_elements})")
+
+
+class _MemoryFacade:
+    def __init__(self):
+        self.hbm = _HBMFacade()
+
+
+class _GridFacade:
+    def __init__(self, n_cores: int):
+        self.cores = list(range(n_cores))
+
+
 class KTIRInterpreter:
     """Executes KTIR functions on a B200 through ``libktir_b200`` (no CPU fallback)."""
 
@@ -189,6 +231,8 @@ class KTIRInterpreter:
             from .latency import LatencyTracker
             self._latency_tracker = LatencyTracker(latency_config, trace=trace_latency)
         self._pool = None
+        self.memory = _MemoryFacade()
+        self.grid_executor = _GridFacade(0)
 
     # -- front end ------------------------------------------------------------
     def load(self, ktir_source: str):
@@ -256,19 +300,32 @@ class KTIRInterpreter:
                 tensors.append((k, tuple(v.shape), v.dtype))
             else:
                 scalars[k] = v
+        seeded = tuple((addr, arr.nbytes, to_ktir_dtype(arr.dtype)) for addr, arr in
+                       sorted(self.memory.hbm.regions.items()))
         key = (func_name, tuple((n, s, str(d)) for n, s, d in tensors),
-               tuple((k, _scalar_key(v)) for k, v in scalars.items()))
+               tuple((k, _scalar_key(v)) for k, v in scalars.items()), seeded)
         sess = self._sessions.get(key)
         if sess is None:
             if len(self._sessions) >= self._max_sessions:
                 old = next(iter(self._sessions))
                 self._sessions.pop(old).close()
-            sess = Session(self.device, func, tensors, scalars, latency=self._latency_config is not None)
+            sess = Session(self.device, func, tensors, scalars, latency=self._latency_config is not None,
+                           seeded=seeded)
             self._sessions[key] = sess
         return sess, kwargs
 
+    def _prepare_execution(self, grid_shape):
+        """Fresh memory for a call (ktir_cpu/interpreter.py:95-120).  The reference's tests wrap this
+        method to place data at fixed addresses through ``self.memory.hbm.write`` before the run."""
+        self.memory = _MemoryFacade()
+        n = int(np.prod(grid_shape)) if len(grid_shape) else 1
+        self.grid_executor = _GridFacade(n)
+
     def execute_function(self, func_name: str, **kwargs) -> Dict[str, np.ndarray]:
+        self._prepare_execution(tuple(self._require_module().get_function(func_name).grid))
         sess, kwargs = self.session(func_name, **kwargs)
+        for addr, arr in self.memory.hbm.regions.items():
+            sess.dev.h2d(sess.arena + addr, arr)
         if self._pool is None:
             from .pinned import PinnedPool
             self._pool = PinnedPool(self.device)
@@ -291,6 +348,8 @@ class KTIRInterpreter:
                     d2h += v.nbytes
                 else:
                     outputs[k] = np.array(v, copy=True)
+        for addr, arr in self.memory.hbm.regions.items():
+            sess.dev.d2h(arr, sess.arena + addr)              # what the kernels left at the fixed addresses
         sess.dev.sync()
         sess.last_h2d_bytes, sess.last_d2h_bytes = h2d, d2h
         del keep

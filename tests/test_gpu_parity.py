@@ -394,3 +394,63 @@ def test_fallback_steps_match_the_oracle(build_lib):
     with pytest.raises(IndexError, match="negative"):
         gpu.execute_function(fn, **kw)
     gpu.close()
+
+
+FIXED_ADDRESS_KERNEL = """
+module {
+  func.func @scale_rows() attributes {grid = [2, 1]} {
+    %pid = ktdp.get_compute_tile_id : index
+    %c0 = arith.constant 0 : index
+    %c8 = arith.constant 8 : index
+    %row = arith.muli %pid, %c8 : index
+    %src_ptr = arith.constant 0 : index
+    %dst_ptr = arith.constant 1024 : index
+    %two = arith.constant 2.0 : f16
+    %src = ktdp.construct_memory_view %src_ptr, sizes: [16, 64], strides: [64, 1] {
+      coordinate_set = affine_set<(d0, d1) : (d0 >= 0, -d0 + 15 >= 0, d1 >= 0, -d1 + 63 >= 0)>,
+      memory_space = #ktdp.memory_space<global>
+    } : memref<16x64xf16>
+    %dst = ktdp.construct_memory_view %dst_ptr, sizes: [16, 64], strides: [64, 1] {
+      coordinate_set = affine_set<(d0, d1) : (d0 >= 0, -d0 + 15 >= 0, d1 >= 0, -d1 + 63 >= 0)>,
+      memory_space = #ktdp.memory_space<global>
+    } : memref<16x64xf16>
+    %s_tile = ktdp.construct_access_tile %src[%row, %c0] {
+      access_tile_set = affine_set<(d0, d1) : (d0 >= 0, -d0 + 7 >= 0, d1 >= 0, -d1 + 63 >= 0)>,
+      access_tile_order = affine_map<(d0, d1) -> (d0, d1)>
+    } : memref<16x64xf16> -> !ktdp.access_tile<8x64xindex>
+    %d_tile = ktdp.construct_access_tile %dst[%row, %c0] {
+      access_tile_set = affine_set<(d0, d1) : (d0 >= 0, -d0 + 7 >= 0, d1 >= 0, -d1 + 63 >= 0)>,
+      access_tile_order = affine_map<(d0, d1) -> (d0, d1)>
+    } : memref<16x64xf16> -> !ktdp.access_tile<8x64xindex>
+    %x = ktdp.load %s_tile : !ktdp.access_tile<8x64xindex> -> tensor<8x64xf16>
+    %t = tensor.splat %two : tensor<8x64xf16>
+    %y = arith.mulf %x, %t : tensor<8x64xf16>
+    ktdp.store %y, %d_tile : tensor<8x64xf16>, !ktdp.access_tile<8x64xindex>
+    return
+  }
+}
+"""
+
+
+def test_memory_seeded_at_fixed_addresses(build_lib):
+    """Kernels with hard-coded pointers: data placed through interp.memory.hbm.write before the run
+    (the way the reference's tests wrap _prepare_execution) and read back with hbm.read afterwards."""
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal((16, 64)).astype(np.float16)
+    gpu = KTIRInterpreter()
+    gpu.load(FIXED_ADDRESS_KERNEL)
+    orig = gpu._prepare_execution
+
+    def prepare_and_seed(grid_shape):
+        orig(grid_shape)
+        gpu.memory.hbm.write(0, x.reshape(-1))                    # element 0 of f16 = stick 0
+        gpu.memory.hbm.write(16, np.zeros(16 * 64, np.float16))   # element 1024 of f16 = byte 2048 = stick 16
+    gpu._prepare_execution = prepare_and_seed
+    gpu.execute_function("scale_rows")
+    got = gpu.memory.hbm.read(16, 16 * 64, "f16").reshape(16, 64)
+    np.testing.assert_array_equal(got, (x * np.float16(2)).astype(np.float16))
+    np.testing.assert_array_equal(gpu.memory.hbm.read(0, 16 * 64, "f16").reshape(16, 64), x)
+    assert len(gpu.grid_executor.cores) == 2
+    with pytest.raises(ValueError, match="unmapped"):
+        gpu.memory.hbm.read(4096, 4, "f16")
+    gpu.close()
