@@ -464,7 +464,7 @@ __global__ void __launch_bounds__(256, 4) ktb_scatter_apply_kernel(const __grid_
 // quarter of its instructions: no operand descriptors, no per-element guards, rows loaded four at a
 // time before the dependent adds.
 template <int ACC>
-__global__ void __launch_bounds__(256, 8) ktb_scatter_apply_axpy128_kernel(const __grid_constant__ ktb_rows_args a,
+__global__ void __launch_bounds__(256, 6) ktb_scatter_apply_axpy128_kernel(const __grid_constant__ ktb_rows_args a,
                                                                           const sc_scratch sc, ktb_status* st) {
     constexpr int K = 1 - ACC;                      // the gathered operand
     const int lane = threadIdx.x & 31;
@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(256, 8) ktb_scatter_apply_axpy128_kernel(const
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const __half* arena = reinterpret_cast<const __half*>(a.arena);
     __half* arena_w = reinterpret_cast<__half*>(a.arena);
-    const float c = a.program.ops[0].imm;
+    const __half2 c2 = __float2half2_rn(a.program.ops[0].imm);      // the scale is an f16 value (checked on the host)
     const int64_t in_lo = a.in[K].lo, in_hi = a.in[K].hi - 128;
     const int64_t* baddr = sc.bucket_addr + (int64_t)K * sc.slots;
     const int bl = lane < sc.cap ? lane : 0;
@@ -493,22 +493,20 @@ __global__ void __launch_bounds__(256, 8) ktb_scatter_apply_axpy128_kernel(const
         int rank = 0;
         for (int j = 0; j < cnt; ++j) rank += __shfl_sync(0xffffffffu, e, j) < e ? 1 : 0;
         __half* drow = arena_w + a.dst_row0 + row * a.out.idx_mult + lane * 4;
-        float cur[4];
-        {
-            const uint2 raw = *reinterpret_cast<const uint2*>(drow);
-            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-            cur[0] = lo.x; cur[1] = lo.y; cur[2] = hi.x; cur[3] = hi.y;
-        }
+        // f16 multiply and add with one rounding each are what NumPy's half ufuncs compute (f32
+        // arithmetic on f16 inputs rounds to the same f16 value: 24 >= 2 * 11 + 2 bits); the _rn
+        // forms are never contracted into a fused multiply-add
+        uint2 raw = *reinterpret_cast<const uint2*>(drow);
+        __half2 cur0 = *reinterpret_cast<const __half2*>(&raw.x), cur1 = *reinterpret_cast<const __half2*>(&raw.y);
         for (int j0 = 0; j0 < cnt; j0 += 4) {
             uint2 x[4];
             bool use[4];
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 x[g] = make_uint2(0u, 0u);
-                const unsigned m = __ballot_sync(0xffffffffu, lane < cnt && rank == j0 + g);
                 use[g] = false;
-                if (m) {                             // uniform: the ballot is the same on every lane
+                if (j0 + g < cnt) {                  // uniform
+                    const unsigned m = __ballot_sync(0xffffffffu, lane < cnt && rank == j0 + g);
                     const int64_t ad = sc_shfl64(my_ad, __ffs(m) - 1);
                     use[g] = ad >= 0;                // an unresolved (negative) index was reported by prepare
                     if (ad >= in_lo && ad <= in_hi) {
@@ -528,23 +526,21 @@ __global__ void __launch_bounds__(256, 8) ktb_scatter_apply_axpy128_kernel(const
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 if (!use[g]) continue;
-                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&x[g].x));
-                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&x[g].y));
-                const float v[4] = {lo.x, lo.y, hi.x, hi.y};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) cur[i] = ktb_round16(cur[i] + ktb_round16(v[i] * c));
+                cur0 = __hadd2_rn(cur0, __hmul2_rn(*reinterpret_cast<const __half2*>(&x[g].x), c2));
+                cur1 = __hadd2_rn(cur1, __hmul2_rn(*reinterpret_cast<const __half2*>(&x[g].y), c2));
             }
         }
-        uint2 o;
-        *reinterpret_cast<__half2*>(&o.x) = __floats2half2_rn(cur[0], cur[1]);
-        *reinterpret_cast<__half2*>(&o.y) = __floats2half2_rn(cur[2], cur[3]);
-        *reinterpret_cast<uint2*>(drow) = o;
+        raw.x = *reinterpret_cast<const uint32_t*>(&cur0);
+        raw.y = *reinterpret_cast<const uint32_t*>(&cur1);
+        *reinterpret_cast<uint2*>(drow) = raw;
     }
 }
 
 static bool sc_axpy128_ok(const ktb_rows_args& a, int acc) {
     if (a.n_in != 2 || !a.in[acc].alias_dst || a.in[1 - acc].alias_dst || !a.vector_ok || a.cols != 128) return false;
     if (a.in[0].dtype != KTB_F16 || a.in[1].dtype != KTB_F16 || a.out.dtype != KTB_F16) return false;
+    const float c = a.program.ops[0].imm;
+    if (!(__half2float(__float2half_rn(c)) == c)) return false;      // the scale must be exact in f16
     if (a.dst_rows <= 0 || a.dst_row0 < a.out.lo || a.dst_row0 + (a.dst_rows - 1) * a.out.idx_mult + 128 > a.out.hi) return false;
     return (a.dst_row0 % 4) == 0 && (a.out.idx_mult % 4) == 0;
 }
@@ -643,7 +639,7 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     int only_long = 0;
     if ((prog == SC_PROG_AXPY0 || prog == SC_PROG_AXPY1) && sc_axpy128_ok(a, prog == SC_PROG_AXPY0 ? 0 : 1)) {
         int64_t fb = (R + 7) / 8;
-        if (fb > (int64_t)ctx->sm_count * 64) fb = (int64_t)ctx->sm_count * 64;
+        if (fb > (int64_t)ctx->sm_count * 48) fb = (int64_t)ctx->sm_count * 48;
         if (prog == SC_PROG_AXPY0) ktb_scatter_apply_axpy128_kernel<0><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
         else ktb_scatter_apply_axpy128_kernel<1><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
         KTB_CHECK_LAUNCH(ctx, "ktb_scatter_apply_axpy128_kernel");
