@@ -87,7 +87,7 @@ class Softmax(Workload):
         return (K.softmax_rows(rows, self.C, cores, self.RPI, True), self.func,
                 dict(output_ptr=np.zeros_like(x), input_ptr=x), rows * self.C)
 
-    cpu_full, cpu_small = 8192, 1024
+    cpu_full, cpu_small = 8192, 8192
 
 
 class VectorAdd(Workload):
@@ -122,7 +122,7 @@ class VectorAdd(Workload):
         return (K.vector_add(n, blk, 32), self.func,
                 dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(n, np.float16), BLOCK_SIZE=blk), n)
 
-    cpu_full, cpu_small = 1 << 26, 1 << 22
+    cpu_full, cpu_small = 1 << 26, 1 << 26
 
 
 class GatherScatter(Workload):
@@ -164,7 +164,7 @@ class GatherScatter(Workload):
                 dict(table_ptr=table, idx_ptr=self._idx(rng, rows, n), out_ptr=np.zeros_like(table)),
                 n * self.COLS)
 
-    cpu_full, cpu_small = 262144, 16384
+    cpu_full, cpu_small = 262144, 131072
 
 
 class Matmul(Workload):
@@ -201,7 +201,7 @@ class Matmul(Workload):
         return (K.tiled_matmul(n, n, n, 64, 64, 64, cores, True), self.func,
                 dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((n, n), np.float16)), 2 * n ** 3)
 
-    cpu_full, cpu_small = 1024, 512
+    cpu_full, cpu_small = 2048, 2048
 
 
 class Attention(Workload):
@@ -246,7 +246,7 @@ class Attention(Workload):
         return (K.causal_attention(S, H, self.D, self.TM, self.TN), self.func,
                 self._kw(np.random.default_rng(seed), S, H), 4 * H * self.D * (S * (S + 1) // 2))
 
-    cpu_full, cpu_small = 1024, 512
+    cpu_full, cpu_small = 2048, 2048
 
 
 WORKLOADS = {w.name: w for w in (Softmax(), VectorAdd(), GatherScatter(), Matmul(), Attention())}
