@@ -639,7 +639,7 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     int only_long = 0;
     if ((prog == SC_PROG_AXPY0 || prog == SC_PROG_AXPY1) && sc_axpy128_ok(a, prog == SC_PROG_AXPY0 ? 0 : 1)) {
         int64_t fb = (R + 7) / 8;
-        if (fb > (int64_t)ctx->sm_count * 48) fb = (int64_t)ctx->sm_count * 48;
+        if (fb > (int64_t)ctx->sm_count * 6) fb = (int64_t)ctx->sm_count * 6;      // resident CTAs; rows are strided over them
         if (prog == SC_PROG_AXPY0) ktb_scatter_apply_axpy128_kernel<0><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
         else ktb_scatter_apply_axpy128_kernel<1><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
         KTB_CHECK_LAUNCH(ctx, "ktb_scatter_apply_axpy128_kernel");
