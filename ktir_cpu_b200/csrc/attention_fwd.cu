@@ -28,7 +28,6 @@
 
 #define AT_BM 128
 #define AT_D 128
-#define AT_THREADS 640
 #define AT_Q_BYTES (AT_BM * AT_D * 2)
 #define AT_MAX_STAGES 8
 #define AT_RESCALE_GAP 8.0f
@@ -109,8 +108,10 @@ static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], in
 enum { B_QFULL = 0, B_KVFULL = 1, B_KVEMPTY = B_KVFULL + AT_MAX_STAGES, B_SFULL = B_KVEMPTY + AT_MAX_STAGES,
        B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2, B_XCHG = B_PVDONE + 2, B_COUNT = B_XCHG + 2 };
 
-template <int BN>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// TPR = threads per query row in the softmax (1: a thread holds the whole score row of a page in
+// registers, 384 threads; 2: two threads share a row, 640 threads).
+template <int BN, int TPR>
+__global__ void __launch_bounds__(128 + 256 * TPR, 1)
 ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const ktb_attn_args a, int q_pairs,
                          ktb_status* st) {
@@ -153,7 +154,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         for (int i = 0; i < 2; ++i) {
             tc_mbar_init(&bars[B_SFULL + i], 1);
-            tc_mbar_init(&bars[B_PFULL + i], 8);
+            tc_mbar_init(&bars[B_PFULL + i], 4 * TPR);
             tc_mbar_init(&bars[B_PVDONE + i], 1);
             tc_mbar_init(&bars[B_XCHG + i], 8);
         }
@@ -173,7 +174,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // half a row of scores each; the MMA issue loop must not spill, it paces the whole CTA
     // (each setmaxnreg sits at the head of the region it governs, with no join in between)
     if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");          // (a decrease only for TPR = 1, see below)
     if (warp == 0) {
         if (lane == 0 && nmax > 0) {
             tc_prefetch_tmap(&map_q);
@@ -298,16 +299,18 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
     }
     } else {
-        // (the softmax warpgroups keep the launch allocation of 96 registers)
+        // TPR = 2: the softmax warpgroups keep the launch allocation of 96 registers.  TPR = 1: 384 threads
+        // start with 168 each; the copy/MMA warpgroup gave back 80, the two softmax warpgroups take 40 more
+        if (TPR == 1) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         // Two threads share a query row: `half` 0 owns the first BN/2 score columns and the first 64
         // output columns, `half` 1 the rest.  Their row maxima (and, at the end, row sums) are swapped
         // through shared memory.
-        constexpr int HB = BN / 2;                   // score columns per thread
+        constexpr int HB = BN / TPR;                 // score columns per thread
         constexpr int CW = HB < 32 ? HB : 32;        // columns per TMEM load
         constexpr int NCH = HB / CW;
-        constexpr int OH = AT_D / 2;                 // output columns per thread
-        const int tile = (warp - 4) >> 3;            // which query tile this pair of warpgroups owns
-        const int half = ((warp - 4) >> 2) & 1;
+        constexpr int OH = AT_D / TPR;               // output columns per thread
+        const int tile = (warp - 4) / (4 * TPR);     // which query tile this warpgroup (pair) owns
+        const int half = TPR == 2 ? ((warp - 4) >> 2) & 1 : 0;
         const int n = n_of[tile];
         const int q = warp & 3;                      // TMEM lane quadrant this warp may access
         const int r = q * 32 + lane;                 // row inside the tile == TMEM lane
@@ -364,9 +367,9 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
             for (int c = 0; c < NCH; ++c)
                 mx = need_mask ? at_chunk_max<CW, true>(v[c], vis - c * CW, mx) : at_chunk_max<CW, false>(v[c], 0, mx);
-            float mx_other;
+            float mx_other = mx;
             // after the swap both threads of the row have their scores in registers: P may go over them
-            if (!swap_with_partner(mx, mx_other)) { ok = false; break; }
+            if (TPR == 2 && !swap_with_partner(mx, mx_other)) { ok = false; break; }
             m_run = fmaxf(m_run, fmaxf(mx, mx_other) * sl);
             // move the exponent reference only when the maximum has outgrown it by 2^8
             // (m_run and m_ref are the same on both threads of a row, so they move together)
@@ -409,7 +412,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_fence_after_sync();
             // total row sum = the two partial sums (same rescaling history on both threads)
             float l_other = 0.f;
-            if (swap_with_partner(l_run, l_other)) {
+            if (TPR == 1 || swap_with_partner(l_run, l_other)) {
                 const float inv = 1.0f / (l_run + l_other);
                 const bool store = *abort_flag == 0 && R < a.seq_q;
                 __half* dst = reinterpret_cast<__half*>(a.arena) + a.o_off + (int64_t)R * a.o_row_stride +
@@ -440,18 +443,18 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 1) tc_tmem_dealloc(tmem_base, 512);
 }
 
-template <int BN>
+template <int BN, int TPR>
 static int launch_attn(ktb_ctx* ctx, const ktb_attn_args& a, const CUtensorMap& mq, const CUtensorMap& mk,
                        const CUtensorMap& mv) {
     constexpr int AT_STAGES = BN == 128 ? 4 : 8;
     constexpr size_t SMEM = 2 * AT_Q_BYTES + AT_STAGES * (size_t)(BN * AT_D * 2) + 2 * 2 * 2 * AT_BM * 4 + 1024 + 512;
     static bool attr_set = false;
     if (!attr_set) {
-        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN, TPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
         attr_set = true;
     }
     const int q_pairs = (a.seq_q + 2 * AT_BM - 1) / (2 * AT_BM);
-    ktb_attention_fwd_kernel<BN><<<q_pairs * a.heads, AT_THREADS, SMEM, ctx->stream>>>(mq, mk, mv, a, q_pairs, ctx->dev_status);
+    ktb_attention_fwd_kernel<BN, TPR><<<q_pairs * a.heads, 128 + 256 * TPR, SMEM, ctx->stream>>>(mq, mk, mv, a, q_pairs, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_attention_fwd_kernel");
     return KTB_OK;
 }
@@ -484,9 +487,11 @@ extern "C" int ktb_launch_attention_fwd(ktb_ctx* ctx, const ktb_attn_args* args)
         if (!tc_make_map_f16(which ? &mv : &mk, base + (which ? a.v_off : a.k_off), 4, dims, str, box))
             return ktb_fail(ctx, KTB_E_CUDA, "attention_fwd", "cuTensorMapEncodeTiled(K/V) failed");
     }
+    int tpr = 1;                        // softmax threads per query row (experiments: KTB_ATT_TPR=2)
+    if (const char* e = getenv("KTB_ATT_TPR")) tpr = atoi(e) == 2 ? 2 : 1;
     switch (a.page) {
-        case 32: return launch_attn<32>(ctx, a, mq, mk, mv);
-        case 64: return launch_attn<64>(ctx, a, mq, mk, mv);
-        default: return launch_attn<128>(ctx, a, mq, mk, mv);
+        case 32: return launch_attn<32, 2>(ctx, a, mq, mk, mv);
+        case 64: return tpr == 1 ? launch_attn<64, 1>(ctx, a, mq, mk, mv) : launch_attn<64, 2>(ctx, a, mq, mk, mv);
+        default: return tpr == 1 ? launch_attn<128, 1>(ctx, a, mq, mk, mv) : launch_attn<128, 2>(ctx, a, mq, mk, mv);
     }
 }
