@@ -231,7 +231,7 @@ static __device__ __forceinline__ void sm_row_exp(const uint4& raw, float mxs, f
 // of holding NV x 8 f32 values; half the registers, twice the resident rows per SM.
 template <int NV, bool MAXNUM, bool RECOMP, bool PREF>
 __global__ void __launch_bounds__(256, RECOMP ? (NV >= 16 ? 2 : NV >= 8 ? (PREF ? 2 : 4) : (PREF ? 4 : 6)) : (NV >= 8 ? 2 : 3))
-ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows) {
+ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows, int pack_ok) {
     __shared__ float xmax[8], xsum[8];            // one slot per warp of the CTA
     const int groups = 256 / T;
     const int group = threadIdx.x / T;
@@ -241,6 +241,9 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
     const __half* in16 = reinterpret_cast<const __half*>(a.arena);
     const int w = T < 32 ? T : 32;
     const int64_t n_iter = (total_rows + groups - 1) / groups;
+    // f16 output: exp is evaluated once and parked as f16 (one extra rounding, <= 2^-11 relative,
+    // inside the f16 tolerance of this op); f32 output keeps full precision by evaluating exp twice
+    const bool pack = RECOMP && !PREF && a.out_dtype == KTB_F16 && pack_ok;
     uint4 nxt[PREF ? NV : 1];
     if (PREF && blockIdx.x < n_iter) {
         const int64_t row = blockIdx.x * (int64_t)groups + group < total_rows ? blockIdx.x * (int64_t)groups + group : 0;
@@ -317,6 +320,14 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
             s1 += q[2] + q[3];
             s2 += q[4] + q[5];
             s3 += q[6] + q[7];
+            if (pack) {
+                // keep exp(x - max) * 2^15 as f16 in the registers the input occupied (0 < p <= 1, so the
+                // scaled value keeps 11 significant bits down to p = 2^-29): the output pass then needs
+                // neither the input nor a second exp
+                __half2* hw = reinterpret_cast<__half2*>(&raw[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) hw[i] = __floats2half2_rn(q[2 * i] * 32768.f, q[2 * i + 1] * 32768.f);
+            }
         }
         float sum = (s0 + s1) + (s2 + s3);
         for (int d = w >> 1; d >= 1; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d, w);
@@ -329,7 +340,7 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
         }
         const float inv = 1.0f / (sum + a.sum_init);
         if (!live) continue;
-        if (RECOMP) {
+        if (RECOMP && !pack) {
             // opaque to the optimiser: otherwise the converted values of the first evaluation are
             // kept alive for the second one, which is the register footprint this variant avoids
 #pragma unroll
@@ -339,13 +350,23 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
         if (a.out_dtype == KTB_F16) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + out_off) + t;
 #pragma unroll
+            const float inv_s = inv * (1.0f / 32768.f);
             for (int j = 0; j < NV; ++j) {
-                if (RECOMP) sm_row_exp(raw[j], mxs, p[0]);
-                const float(&pj)[8] = p[RECOMP ? 0 : j];
                 uint4 o;
                 __half2* h = reinterpret_cast<__half2*>(&o);
+                if (pack) {
+                    const __half2* hp = reinterpret_cast<const __half2*>(&raw[j]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(pj[2 * i] * inv, pj[2 * i + 1] * inv);
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __half22float2(hp[i]);
+                        h[i] = __floats2half2_rn(f.x * inv_s, f.y * inv_s);
+                    }
+                } else {
+                    if (RECOMP) sm_row_exp(raw[j], mxs, p[0]);
+                    const float(&pj)[8] = p[RECOMP ? 0 : j];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(pj[2 * i] * inv, pj[2 * i + 1] * inv);
+                }
                 __stcs(dst + (int64_t)j * T, o);
             }
         } else {
@@ -375,7 +396,9 @@ static void launch_softmax(ktb_ctx* ctx, const ktb_softmax_args& a, int T, int64
         int per_sm = mode == 2 ? (NV >= 8 ? 2 : 4) : 8;
         if (const char* e = getenv("KTB_SOFTMAX_CTAS")) per_sm = atoi(e) > 0 ? atoi(e) : per_sm;
         if (mode) blocks = n_iter < (int64_t)ctx->sm_count * per_sm ? n_iter : (int64_t)ctx->sm_count * per_sm;
-#define KTB_SMF(MN, RC, PF) ktb_row_softmax_fast_kernel<NV, MN, RC, PF><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows)
+        int pack_ok = 1;
+        if (const char* e = getenv("KTB_SOFTMAX_PACK")) pack_ok = atoi(e) != 0;
+#define KTB_SMF(MN, RC, PF) ktb_row_softmax_fast_kernel<NV, MN, RC, PF><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows, pack_ok)
         if (mode == 2 && NV <= 8) { if constexpr (NV <= 8) { if (mn) KTB_SMF(true, true, true); else KTB_SMF(false, true, true); } }
         else if (mode) { if (mn) KTB_SMF(true, true, false); else KTB_SMF(false, true, false); }
         else if constexpr (NV <= 8) { if (mn) KTB_SMF(true, false, false); else KTB_SMF(false, false, false); }
