@@ -63,6 +63,14 @@ int ktb_event_elapsed_ms(ktb_ctx* ctx, int slot_begin, int slot_end, float* ms_o
 int ktb_flush_l2(ktb_ctx* ctx);
 /* Number of kernels this library has launched on the context so far. */
 int64_t ktb_launch_count(ktb_ctx* ctx);
+/* Record the launches issued between begin and end (they do not run) and replay them with one
+ * ktb_graph_launch — the per-op dispatch loop of the reference (ktir_cpu/interpreter.py:343-395)
+ * collapses into a single submission.  The recorded calls must not allocate; arguments and
+ * device pointers are frozen at capture time. */
+int ktb_graph_begin(ktb_ctx* ctx);
+int ktb_graph_end(ktb_ctx* ctx, void** graph_out);
+int ktb_graph_launch(ktb_ctx* ctx, void* graph);
+int ktb_graph_destroy(ktb_ctx* ctx, void* graph);
 
 /* ---- elementwise register programs ---------------------------------------
  * A short straight-line program over f32 registers; inputs are loaded into

@@ -20,6 +20,7 @@ struct ktb_ctx {
     ktb_status* dev_status;     // device copy of the status word
     void* flush_buf;            // lazily allocated L2 flush scratch
     int64_t launches;
+    int64_t capture_base;       // launch count when a graph capture began
     char err[512];
 };
 

@@ -166,4 +166,53 @@ int ktb_flush_l2(ktb_ctx* ctx) {
 
 int64_t ktb_launch_count(ktb_ctx* ctx) { return ctx ? ctx->launches : -1; }
 
+// ---- replaying a launch sequence as a CUDA graph -------------------------------------------
+struct ktb_graph {
+    cudaGraphExec_t exec;
+    int64_t launches;           // kernel launches the sequence contains
+};
+
+int ktb_graph_begin(ktb_ctx* ctx) {
+    if (!ctx) return KTB_E_ARG;
+    ctx->capture_base = ctx->launches;
+    KTB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    return KTB_OK;
+}
+
+int ktb_graph_end(ktb_ctx* ctx, void** graph_out) {
+    if (!ctx || !graph_out) return KTB_E_ARG;
+    *graph_out = nullptr;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    const int64_t n = ctx->launches - ctx->capture_base;
+    ctx->launches = ctx->capture_base;            // captured launches have not run
+    if (e != cudaSuccess || !g) {
+        cudaGetLastError();
+        return ktb_fail(ctx, KTB_E_CUDA, "cudaStreamEndCapture", cudaGetErrorString(e));
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return ktb_fail(ctx, KTB_E_CUDA, "cudaGraphInstantiate", cudaGetErrorString(e));
+    ktb_graph* out = new ktb_graph{exec, n};
+    *graph_out = out;
+    return KTB_OK;
+}
+
+int ktb_graph_launch(ktb_ctx* ctx, void* graph) {
+    if (!ctx || !graph) return KTB_E_ARG;
+    ktb_graph* g = static_cast<ktb_graph*>(graph);
+    KTB_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    ctx->launches += g->launches;
+    return KTB_OK;
+}
+
+int ktb_graph_destroy(ktb_ctx* ctx, void* graph) {
+    if (!graph) return KTB_OK;
+    ktb_graph* g = static_cast<ktb_graph*>(graph);
+    cudaGraphExecDestroy(g->exec);
+    delete g;
+    return KTB_OK;
+}
+
 }  // extern "C"

@@ -14,6 +14,8 @@ ktir_cpu/memory.py:330-352 allocates), so SSA pointer values — element indices
 """
 from __future__ import annotations
 
+import os
+
 from typing import Sequence, Any, Dict, List, Optional, Tuple
 
 import numpy as np
@@ -127,6 +129,9 @@ class Session:
                 dev.free(self.arena)
             self.arena = None
             raise
+        self._graph = None
+        self._runs = 0
+        self.use_graph = arena_ptr is None and os.environ.get("KTB_NO_GRAPH") is None
         self.written = set(self.plan.written)
         self.no_upload = set(self.plan.fully_overwritten)
         self.last_h2d_bytes = 0
@@ -139,6 +144,23 @@ class Session:
         return arr
 
     def run(self):
+        """Launch the plan.  A plan of several launches is recorded as a CUDA graph on its second run
+        and replayed from then on (arguments and the arena address are fixed for a session)."""
+        if self._graph is not None:
+            self.dev.graph_launch(self._graph)
+            return
+        self._runs += 1
+        n = sum(getattr(s, "launches", 1) for s in self.plan.statements)
+        if self._runs == 2 and n > 1 and self.use_graph and hasattr(self.dev, "graph_begin"):
+            self.dev.graph_begin()
+            try:
+                self.plan.launch(self.dev, self.arena)
+            finally:
+                self._graph = self.dev.graph_end()
+            if self._graph is not None:
+                self.dev.graph_launch(self._graph)
+                return
+            self.use_graph = False
         self.plan.launch(self.dev, self.arena)
 
     def download(self, name: str, out: Optional[np.ndarray] = None, pool=None) -> np.ndarray:
@@ -159,6 +181,9 @@ class Session:
     def close(self):
         if self.arena is not None:
             self.dev.sync()
+            if self._graph is not None:
+                self.dev.graph_destroy(self._graph)
+                self._graph = None
             self.plan.release(self.dev)
             if self.own_arena:
                 self.dev.free(self.arena)

@@ -129,6 +129,10 @@ SYMBOLS = {
     "ktb_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "ktb_flush_l2": (C.c_int, [C.c_void_p]),
     "ktb_launch_count": (C.c_int64, [C.c_void_p]),
+    "ktb_graph_begin": (C.c_int, [C.c_void_p]),
+    "ktb_graph_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "ktb_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ktb_graph_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ktb_launch_ew_stream": (C.c_int, [C.c_void_p, C.POINTER(EwArgs)]),
     "ktb_launch_row_softmax": (C.c_int, [C.c_void_p, C.POINTER(SoftmaxArgs)]),
     "ktb_launch_rows_program": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
@@ -267,6 +271,21 @@ class Device:
 
     def launch_count(self) -> int:
         return int(self.lib.ktb_launch_count(self.h))
+
+    # graphs -----------------------------------------------------------------
+    def graph_begin(self):
+        self.check(self.lib.ktb_graph_begin(self.h))
+
+    def graph_end(self) -> Optional[int]:
+        g = C.c_void_p()
+        rc = self.lib.ktb_graph_end(self.h, C.byref(g))
+        return g.value if rc == 0 else None
+
+    def graph_launch(self, g: int):
+        self.check(self.lib.ktb_graph_launch(self.h, C.c_void_p(g)))
+
+    def graph_destroy(self, g: int):
+        self.lib.ktb_graph_destroy(self.h, C.c_void_p(g))
 
 
 _devices = {}
