@@ -7,14 +7,17 @@
 // (examples/triton-ktir/paged_attention.mlir:183-396, ktir_cpu/ops/memory_ops.py:867-915,
 // ktir_cpu/dialects/linalg_ops.py:136-347).
 //
-// Roles (five warpgroups of 4 warps): warp 0 streams both Q tiles once and the K/V pages (page
-// id from the block table) through a shared-memory ring by TMA; warp 1 issues tcgen05.mma —
-// S_i = Q_i K^T into the score buffer of tile i, P_i V accumulated into the output buffer of
-// tile i, both in TMEM; warps 4-11 are the softmax of tile 0, warps 12-19 of tile 1, two threads
-// per query row (each owns half of the page's columns): read the scores from TMEM, mask,
-// running max, P = exp2(..) rounded to f16 and written back to TMEM over the scores it came
-// from, row sum in f32.  P V takes its A operand straight from TMEM, so shared memory carries
-// only Q, K and V; while one tile is in its softmax the tensor core works for the other tile.
+// Roles: warp 0 streams both Q tiles once and the K/V pages (page id from the block table)
+// through a shared-memory ring by TMA; warps 1 and 2 issue tcgen05.mma for tile 0 and tile 1 —
+// S_i = Q_i K^T into a score slot of tile i, P_i V accumulated into the output buffer of tile i,
+// both in TMEM; warps 4-7 are the softmax of tile 0, warps 8-11 of tile 1, one thread per query
+// row (two with TPR = 2): read the scores from TMEM, mask, running max, P = exp2(..) rounded to
+// f16 and written back to TMEM over the scores it came from, row sum in f32.  P V takes its A
+// operand straight from TMEM, so shared memory carries only Q, K and V.
+//
+// A page is walked in steps of 64 kv rows, and every tile has two score slots of 64 TMEM columns:
+// while the softmax works on step u the tensor core already holds the scores of step u+1, so in
+// the steady state the softmax never waits for a matmul and the tensor core never for a softmax.
 //
 // The output accumulator never leaves TMEM until the end.  The reference rescales it by
 // exp(m_old - m_new) after every page (paged_attention.mlir:330-372); here the exponent
@@ -71,33 +74,64 @@ static __device__ __forceinline__ uint64_t at_add2(uint64_t a, uint64_t b) {
     return r;
 }
 
-// Maximum of CW raw scores; with MASK, columns beyond `vis` (number of visible columns of this
-// chunk, may be <= 0 or >= CW) do not take part.
-template <int CW, bool MASK>
-static __device__ __forceinline__ float at_chunk_max(const uint32_t (&v)[CW], int vis, float mx) {
-    if (!MASK) {
+// 2^x for two values at once on the FMA pipe (the exp unit is the busiest unit of the softmax):
+// x = r + f with r = round(x), 2^f by a cubic on [-0.5, 0.5] (relative error 7.5e-5, a sixth of
+// an f16 ulp), 2^r by an add into the exponent field.  x is clamped to >= -125 so that the
+// exponent stays positive (such a term is zero in f16 either way).
+static __device__ __forceinline__ void at_ex2_poly2(float x0, float x1, float& p0, float& p1) {
+    const float magic = 12582912.f;                     // 1.5 * 2^23: the sum keeps round(x) in the low mantissa bits
+    const uint64_t x2 = at_pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+    const uint64_t t2 = at_add2(x2, at_pack2(magic, magic));
+    const uint64_t r2 = at_add2(t2, at_pack2(-magic, -magic));
+    const uint64_t f2 = at_fma2(r2, at_pack2(-1.f, -1.f), x2);
+    uint64_t q2 = at_fma2(at_pack2(0.05517164617776871f, 0.05517164617776871f), f2,
+                          at_pack2(0.2426111251115799f, 0.2426111251115799f));
+    q2 = at_fma2(q2, f2, at_pack2(0.6932609677314758f, 0.6932609677314758f));
+    q2 = at_fma2(q2, f2, at_pack2(0.9999280571937561f, 0.9999280571937561f));
+    float q0, q1, t0, t1;
+    at_unpack2(q2, q0, q1);
+    at_unpack2(t2, t0, t1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
+
+// Maximum of CW raw scores.
+template <int CW>
+static __device__ __forceinline__ float at_chunk_max(const uint32_t (&v)[CW], float mx) {
+    if (CW % 8 == 0) {                 // four independent chains: the latency of max is not hidden otherwise
+        float m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < CW; i += 2) mx = at_max3(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-    } else {
-#pragma unroll
-        for (int i = 0; i < CW; ++i) mx = fmaxf(mx, i < vis ? __uint_as_float(v[i]) : -INFINITY);
+        for (int i = 0; i < CW; i += 8) {
+            mx = at_max3(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            m1 = at_max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            m2 = at_max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+            m3 = at_max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+        }
+        return at_max3(mx, m1, fmaxf(m2, m3));
     }
+#pragma unroll
+    for (int i = 0; i < CW; i += 2) mx = at_max3(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
     return mx;
 }
 
 // P = exp2(s * sl - m) for CW scores -> CW/2 packed f16 pairs; the f32 values are added to acc2.
-template <int CW, bool MASK>
-static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], int vis, float sl, float m,
-                                                     uint64_t& acc2, uint32_t (&packed)[CW / 2]) {
+// POLY of every 4 pairs take the polynomial instead of the exp unit.  A score of -inf (a masked
+// column) gives 0 on either path (the polynomial clamps it to 2^-125, which is 0 in f16 and
+// vanishes in the sum).
+template <int CW, int POLY>
+static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], float sl, float m, uint64_t& acc2,
+                                                     uint32_t (&packed)[CW / 2]) {
     const uint64_t sl2 = at_pack2(sl, sl), nm2 = at_pack2(-m, -m);
 #pragma unroll
     for (int i = 0; i < CW; i += 2) {
         float x0, x1;
         at_unpack2(at_fma2(at_pack2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sl2, nm2), x0, x1);
-        float p0 = at_ex2(x0), p1 = at_ex2(x1);
-        if (MASK) {
-            if (i >= vis) p0 = 0.f;
-            if (i + 1 >= vis) p1 = 0.f;
+        float p0, p1;
+        if (((i >> 1) & 3) < POLY) {
+            at_ex2_poly2(x0, x1, p0, p1);
+        } else {
+            p0 = at_ex2(x0);
+            p1 = at_ex2(x1);
         }
         acc2 = at_add2(acc2, at_pack2(p0, p1));
         const __half2 h = __floats2half2_rn(p0, p1);
@@ -105,12 +139,16 @@ static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], in
     }
 }
 
+// S-full and P-full barriers exist per tile and score slot (index tile * 2 + slot)
+// cycles the softmax of tile 1 starts behind that of tile 0, so that the two do not need the exp
+// unit (and the tensor core) at the same moments
+__constant__ int at_stagger = 800;
 enum { B_QFULL = 0, B_KVFULL = 1, B_KVEMPTY = B_KVFULL + AT_MAX_STAGES, B_SFULL = B_KVEMPTY + AT_MAX_STAGES,
-       B_PFULL = B_SFULL + 2, B_PVDONE = B_PFULL + 2, B_XCHG = B_PVDONE + 2, B_COUNT = B_XCHG + 2 };
+       B_PFULL = B_SFULL + 4, B_PVDONE = B_PFULL + 4, B_OFINAL = B_PVDONE + 2, B_XCHG = B_OFINAL + 2, B_COUNT = B_XCHG + 2 };
 
 // TPR = threads per query row in the softmax (1: a thread holds the whole score row of a page in
 // registers, 384 threads; 2: two threads share a row, 640 threads).
-template <int BN, int TPR>
+template <int BN, int TPR, int POLY>
 __global__ void __launch_bounds__(128 + 256 * TPR, 1)
 ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const ktb_attn_args a, int q_pairs,
@@ -118,6 +156,8 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     constexpr int KV_BYTES = BN * AT_D * 2;            // one K or V page in shared memory
     constexpr int AT_STAGES = BN == 128 ? 4 : 8;       // ring slots: 128 KB (64 KB for 32-row pages)
     constexpr int KV_BLK = BN * 128;                   // bytes of one [BN x 64] block
+    constexpr int SB = BN > 64 ? 64 : BN;              // kv rows of one step (a page is NSUB steps)
+    constexpr int NSUB = BN / SB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;                                // 2 tiles x 2 blocks [128 x 64]
@@ -127,35 +167,39 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // (through a shuffle, so that the compiler knows the warp index is the same in all lanes)
+    const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
     // query-tile pairs of one head run back to back (its K/V pages stay in L2); within a head the
     // late pairs, which see the most KV pages, go first
     const int head = blockIdx.x / q_pairs;
     const int qp = q_pairs - 1 - blockIdx.x % q_pairs;
     const int q0 = qp * 2 * AT_BM;
-    // pages tile i can see: kv position p is visible to row R iff p <= R + delta
+    // steps (SB kv rows each) tile i can see: kv position p is visible to row R iff p <= R + delta
     int n_of[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        int n = a.num_tiles;
+        int n = a.num_tiles * NSUB;
         const long long last = (long long)q0 + i * AT_BM + AT_BM - 1 + a.causal_delta;
-        const long long vis = last < 0 ? 0 : last / BN + 1;
+        const long long vis = last < 0 ? 0 : last / SB + 1;
         if (a.causal && vis < n) n = (int)vis;
         if (q0 + i * AT_BM >= a.seq_q) n = 0;          // no second tile in the last pair of an odd count
         n_of[i] = n;
     }
-    const int nmax = n_of[0] > n_of[1] ? n_of[0] : n_of[1];
+    const int nmax = ((n_of[0] > n_of[1] ? n_of[0] : n_of[1]) + NSUB - 1) / NSUB;      // pages to stream
 
     if (threadIdx.x == 0) {
         tc_mbar_init(&bars[B_QFULL], 1);
         for (int i = 0; i < AT_STAGES; ++i) {
             tc_mbar_init(&bars[B_KVFULL + i], 1);
-            tc_mbar_init(&bars[B_KVEMPTY + i], 1);
+            tc_mbar_init(&bars[B_KVEMPTY + i], 2);      // both issuing threads
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             tc_mbar_init(&bars[B_SFULL + i], 1);
             tc_mbar_init(&bars[B_PFULL + i], 4 * TPR);
+        }
+        for (int i = 0; i < 2; ++i) {
             tc_mbar_init(&bars[B_PVDONE + i], 1);
+            tc_mbar_init(&bars[B_OFINAL + i], 1);
             tc_mbar_init(&bars[B_XCHG + i], 8);
         }
         *abort_flag = 0;
@@ -166,8 +210,8 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;            // S_0, S_1: 2 x 128 columns
+    const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+    const uint32_t tmem_s = tmem_base;            // per tile two score slots of 64 columns: 2 x 128 columns
     const uint32_t tmem_o = tmem_base + 256;      // O_0, O_1: 2 x 128 columns
 
     // register budget: the copy/MMA warpgroup needs few registers, the softmax warpgroups hold a
@@ -206,94 +250,92 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 at_tma_load_4d(sKV + slot * KV_BYTES + KV_BLK, map, &bars[B_KVFULL + slot], 64, head, 0, (int)page);
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0 && nmax > 0) {
-            const uint32_t idesc_s = tc_idesc_f16(AT_BM, BN, 0, 0);
+    } else if (warp == 1 || warp == 2) {
+        // One issuing thread per query tile (warps 1 and 2 sit on different schedulers): a single
+        // thread cannot prepare descriptors fast enough to keep the tensor core busy for both tiles.
+        // The scores of step u go to slot u & 1 of the tile, and P(u) is written over the front of
+        // the same slot; so S(u+2) is issued right after P V(u) (the tensor core runs one thread's
+        // MMAs in issue order), and the scores of step u+1 are already waiting when the softmax
+        // finishes step u.  P V(u) needs P(u) in TMEM and the V page in shared memory, S(u) the K
+        // page.  Both issuers release every slot of the ring (two arrivals per slot and round): a
+        // tile that sees fewer pages follows the remaining ones along without issuing anything.
+        // The whole warp runs this code converged; one elected lane executes the tcgen05 instructions.
+        if (nmax > 0) {
+            const uint32_t lead = tc_elect_one();
+            const int i = warp - 1;
+            const int n = n_of[i];
+            const uint32_t idesc_s = tc_idesc_f16(AT_BM, SB, 0, 0);
             const uint32_t idesc_pv = tc_idesc_f16(AT_BM, AT_D, 0, 1);
+            const uint32_t ts = tmem_s + i * 128, to = tmem_o + i * 128;
+            const uint64_t qd0 = tc_smem_desc(tc_smem_u32(sQ + i * AT_Q_BYTES), 16, 1024);
             auto kv_wait = [&](int t) {
-                return tc_mbar_wait(&bars[B_KVFULL + t % AT_STAGES], (t / AT_STAGES) & 1, abort_flag, st, 22);
+                return __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_KVFULL + t % AT_STAGES], (t / AT_STAGES) & 1, abort_flag, st, 22)) != 0;
             };
-            auto kv_release = [&](int t) { tc_mma_commit(&bars[B_KVEMPTY + t % AT_STAGES]); };
-            auto t_k = [&](int m) { return 2 * m; };          // load index of K_m
-            auto t_v = [&](int m) { return 2 * m + 1; };      // load index of V_m
-            auto issue_s = [&](int i, int j) {
-                const uint32_t q_addr = tc_smem_u32(sQ + i * AT_Q_BYTES);
-                const uint32_t k_addr = tc_smem_u32(sKV + (t_k(j) % AT_STAGES) * KV_BYTES);
+            auto kv_release = [&](int t) { tc_mma_commit_p(&bars[B_KVEMPTY + t % AT_STAGES], lead); };
+            const uint32_t kv_addr0 = tc_smem_u32(sKV);
+            // Operands of a step are computed ahead of the wait that gates it: this thread's own
+            // instructions, not the tensor core, are what a step of a tile costs.
+            // step u = rows [h * SB, h * SB + SB) of page m; 64 rows of a block are whole swizzle atoms.
+            auto s_desc = [&](int u) {           // K rows of step u (load 2 m is K of page m)
+                const int m = u / NSUB, h = u % NSUB;
+                return tc_smem_desc(kv_addr0 + ((2 * m) % AT_STAGES) * KV_BYTES + h * SB * 128, 16, 1024);
+            };
+            auto pv_desc = [&](int u) {          // V rows of step u (load 2 m + 1 is V of page m)
+                const int m = u / NSUB, h = u % NSUB;
+                return tc_smem_desc(kv_addr0 + ((2 * m + 1) % AT_STAGES) * KV_BYTES, KV_BLK, 1024) +
+                       (uint32_t)(h * (SB / 16) * 2048 >> 4);
+            };
+            auto issue_s = [&](int u, uint64_t bd0) {
                 // the start-address field is the low 14 bits of the descriptor (in 16-byte units), so
-                // stepping along K is an add of a constant.  The loop is unrolled: this one thread has
-                // to hand the tensor core an instruction every 64 cycles while sharing its scheduler
-                // with four softmax warps, so every instruction between two MMAs counts.
-                const uint64_t ad0 = tc_smem_desc(q_addr, 16, 1024), bd0 = tc_smem_desc(k_addr, 16, 1024);
+                // stepping along K is an add of a constant; the loop is unrolled
+                const uint32_t d = ts + (u & 1) * 64;
 #pragma unroll
                 for (int kk = 0; kk < AT_D / 16; ++kk) {
                     const uint32_t ao = ((kk >> 2) * (AT_BM * 128) + (kk & 3) * 32) >> 4;
                     const uint32_t bo = ((kk >> 2) * KV_BLK + (kk & 3) * 32) >> 4;
-                    tc_mma_f16(tmem_s + i * 128, ad0 + ao, bd0 + bo, idesc_s, kk != 0);
+                    tc_mma_f16_p(d, qd0 + ao, bd0 + bo, idesc_s, kk != 0, lead);
                 }
-                tc_mma_commit(&bars[B_SFULL + i]);
+                tc_mma_commit_p(&bars[B_SFULL + i * 2 + (u & 1)], lead);
+                if (u % NSUB == NSUB - 1 || u == n - 1) kv_release(2 * (u / NSUB));
             };
-            auto issue_pv = [&](int i, int j) {
-                // A = P_i from TMEM: row r in lane r, 16 f16 of a K step packed in 8 columns
-                const uint32_t v_addr = tc_smem_u32(sKV + (t_v(j) % AT_STAGES) * KV_BYTES);
-                const uint64_t bd0 = tc_smem_desc(v_addr, KV_BLK, 1024);
+            auto issue_pv = [&](int u, uint64_t bd0) {
+                // A = P from TMEM: row r in lane r, 16 f16 of a K step packed in 8 columns
+                const uint32_t pa = ts + (u & 1) * 64;
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)
-                    tc_mma_f16_ts(tmem_o + i * 128, tmem_s + i * 128 + kk * 8, bd0 + (uint32_t)(kk * 2048 >> 4), idesc_pv,
-                                  (j > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < SB / 16; ++kk)
+                    tc_mma_f16_ts_p(to, pa + kk * 8, bd0 + (uint32_t)(kk * 2048 >> 4), idesc_pv, (u > 0 || kk > 0) ? 1u : 0u, lead);
+                tc_mma_commit_p(&bars[B_PVDONE + i], lead);
+                if (u == n - 1) tc_mma_commit_p(&bars[B_OFINAL + i], lead);      // the accumulator is final
+                if (u % NSUB == NSUB - 1 || u == n - 1) kv_release(2 * (u / NSUB) + 1);
             };
-            // Event-driven issue: whichever tile has its next step ready goes first, so the two
-            // softmax warpgroups stay out of phase and the tensor core always has the other tile's
-            // work.  Per tile and page j:  P V(j) needs P(j) in TMEM and V_j in shared memory;  S(j+1)
-            // overwrites the columns P(j) lives in, so it is issued after P V(j) (the tensor core runs
-            // one thread's MMAs in issue order) and needs K_{j+1}.  A K (V) slot is released once every
-            // tile that uses the page has had its S (P V) issued.
-            bool ok = tc_mbar_wait(&bars[B_QFULL], 0, abort_flag, st, 21);
+            bool ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_QFULL], 0, abort_flag, st, 21)) != 0;
             if (ok) tc_fence_after_sync();
-            int ns0 = 0, ns1 = 0, np0 = 0, np1 = 0;        // next page to issue: S / P V of tile 0 / 1
-            int rel_k = 0, rel_v = 0;
-            const long long t_start = clock64();
-            uint32_t idle = 0;
-            // one tile's turn; its counters are plain registers (no indexed arrays in this loop)
-            auto turn = [&](const int i, int& js, int& jp) -> bool {
-                bool did = false;
-                if (jp < n_of[i] && jp < js && tc_mbar_test(&bars[B_PFULL + i], jp & 1) &&
-                    tc_mbar_test(&bars[B_KVFULL + t_v(jp) % AT_STAGES], (t_v(jp) / AT_STAGES) & 1)) {
+            for (int u = 0; u < 2 && u < n && ok; ++u) {
+                if (u % NSUB == 0) ok = kv_wait(2 * (u / NSUB));
+                if (ok) {
                     tc_fence_after_sync();
-                    issue_pv(i, jp);
-                    if (jp == n_of[i] - 1) tc_mma_commit(&bars[B_PVDONE + i]);
-                    ++jp;
-                    did = true;
+                    issue_s(u, s_desc(u));
                 }
-                if (js < n_of[i] && js == jp &&
-                    tc_mbar_test(&bars[B_KVFULL + t_k(js) % AT_STAGES], (t_k(js) / AT_STAGES) & 1)) {
+            }
+            for (int u = 0; u < n && ok; ++u) {
+                const uint64_t vd = pv_desc(u), kd = s_desc(u + 2);
+                ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PFULL + i * 2 + (u & 1)], (u >> 1) & 1, abort_flag, st, 23)) != 0;
+                if (ok && u % NSUB == 0) ok = kv_wait(2 * (u / NSUB) + 1);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_pv(u, vd);
+                if (u + 2 < n) {
+                    if ((u + 2) % NSUB == 0) ok = kv_wait(2 * ((u + 2) / NSUB));
+                    if (!ok) break;
                     tc_fence_after_sync();
-                    issue_s(i, js);
-                    ++js;
-                    did = true;
+                    issue_s(u + 2, kd);
                 }
-                return did;
-            };
-            const int n0 = n_of[0], n1 = n_of[1];
-            while (ok && rel_v < nmax) {
-                bool progressed = turn(0, ns0, np0);
-                progressed |= turn(1, ns1, np1);
-                while (rel_k < nmax && (rel_k >= n0 || ns0 > rel_k) && (rel_k >= n1 || ns1 > rel_k)) {
-                    kv_release(t_k(rel_k));
-                    ++rel_k;
-                }
-                while (rel_v < nmax && (rel_v >= n0 || np0 > rel_v) && (rel_v >= n1 || np1 > rel_v)) {
-                    kv_release(t_v(rel_v));
-                    ++rel_v;
-                }
-                if (progressed) {
-                    idle = 0;
-                } else if ((++idle & 1023u) == 0) {
-                    if (*abort_flag) ok = false;
-                    else if (clock64() - t_start > 4000000000ll) {     // bounded: a couple of seconds at most
-                        *abort_flag = 1;
-                        if (atomicExch(&st->wait_timeout, 1) == 0) st->wait_site = 23;
-                        ok = false;
-                    }
+            }
+            // pages only the other tile uses: keep the ring's arrival counts in step
+            for (int m = (n + NSUB - 1) / NSUB; m < nmax && ok; ++m) {
+                for (int t = 2 * m; t < 2 * m + 2 && ok; ++t) {
+                    ok = kv_wait(t);
+                    if (ok && lead) tc_mbar_arrive(&bars[B_KVEMPTY + t % AT_STAGES]);
                 }
             }
         }
@@ -305,7 +347,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // Two threads share a query row: `half` 0 owns the first BN/2 score columns and the first 64
         // output columns, `half` 1 the rest.  Their row maxima (and, at the end, row sums) are swapped
         // through shared memory.
-        constexpr int HB = BN / TPR;                 // score columns per thread
+        constexpr int HB = SB / TPR;                 // score columns per thread
         constexpr int CW = HB < 32 ? HB : 32;        // columns per TMEM load
         constexpr int NCH = HB / CW;
         constexpr int OH = AT_D / TPR;               // output columns per thread
@@ -317,7 +359,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int R = q0 + tile * AT_BM + r;
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
         const uint32_t s_addr = tmem_s + tile * 128 + lane_off + half * HB;
-        // P (f16, two per 32-bit column) goes over the first BN/2 columns of the score buffer
+        // P (f16, two per 32-bit column) goes over the first SB/2 columns of the score slot
         const uint32_t p_addr = tmem_s + tile * 128 + lane_off + half * (HB / 2);
         const uint32_t o_addr = tmem_o + tile * 128 + lane_off + half * OH;
         float* xrow = xbuf + tile * (2 * 2 * AT_BM) + r;        // + parity * 256 + half * 128
@@ -344,29 +386,41 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             return true;
         };
 
-        for (int j = 0; j < n && ok; ++j) {
+        for (int j = 0; j < n && ok; ++j) {            // j counts steps of SB kv rows
+            const uint32_t slot_off = (j & 1) * 64;
             // the whole warp leaves together: the TMEM accesses below are warp-collective.
-            // S(j) is issued after P V(j-1), so its arrival also means O and the P columns are idle.
-            if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_SFULL + tile], j & 1, abort_flag, st, 31))) {
+            // S(j) is issued after P V(j-2), which read the P columns of this slot.
+            if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_SFULL + tile * 2 + (j & 1)], (j >> 1) & 1, abort_flag, st, 31))) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
+            if (j == 0 && tile == 1 && at_stagger > 0) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < at_stagger) {}
+            }
             // this thread's part of the score row moves to registers in one go
             uint32_t v[NCH][CW];
 #pragma unroll
-            for (int c = 0; c < NCH; ++c) tc_tmem_ld<CW>(s_addr + c * CW, v[c]);
+            for (int c = 0; c < NCH; ++c) tc_tmem_ld<CW>(s_addr + slot_off + c * CW, v[c]);
             tc_tmem_ld_wait();
 
             // columns of this thread's range the row may see (all of them except on the diagonal pages)
-            const long long vis_ll = limit - ((long long)j * BN + half * HB) + 1;
+            const long long vis_ll = limit - ((long long)j * SB + half * HB) + 1;
             const int vis = vis_ll > HB ? HB : (vis_ll < 0 ? 0 : (int)vis_ll);
-            const bool need_mask = a.causal && ((long long)j * BN + BN - 1 > tile_limit);   // same for the whole tile
+            const bool need_mask = a.causal && ((long long)j * SB + SB - 1 > tile_limit);   // same for the whole tile
+            // hidden columns become -inf once (exp2 turns them into zeros), then every step takes the same path
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < NCH; ++c)
+#pragma unroll
+                    for (int i = 0; i < CW; ++i)
+                        if (c * CW + i >= vis) v[c][i] = 0xff800000u;
+            }
             // row maximum of the raw scores (the scale is positive, so it commutes with max)
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < NCH; ++c)
-                mx = need_mask ? at_chunk_max<CW, true>(v[c], vis - c * CW, mx) : at_chunk_max<CW, false>(v[c], 0, mx);
+            for (int c = 0; c < NCH; ++c) mx = at_chunk_max<CW>(v[c], mx);
             float mx_other = mx;
             // after the swap both threads of the row have their scores in registers: P may go over them
             if (TPR == 2 && !swap_with_partner(mx, mx_other)) { ok = false; break; }
@@ -379,6 +433,13 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (move) m_ref = m_run;
                 l_run *= alpha;
                 if (j > 0) {
+                    // the accumulator may only be touched once P V(j-1) has completed; P V(j-2) completed
+                    // before S(j), so the barrier is in phase j-1 or has just completed it
+                    if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PVDONE + tile], (j - 1) & 1, abort_flag, st, 32))) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
 #pragma unroll 1
                     for (int c0 = 0; c0 < OH; c0 += 16) {
                         uint32_t o[16];
@@ -390,14 +451,14 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                 }
             }
-            // P = exp2(s * sl - m_ref) -> f16 pairs -> TMEM
+            // P = exp2(s * sl - m_ref) -> f16 pairs -> TMEM (a row that has seen nothing yet keeps zeros, not NaN)
+            const float m_exp = m_ref == -INFINITY ? 0.f : m_ref;
             uint64_t acc2 = at_pack2(0.f, 0.f);
 #pragma unroll
             for (int c = 0; c < NCH; ++c) {
                 uint32_t packed[CW / 2];
-                if (need_mask) at_chunk_prob<CW, true>(v[c], vis - c * CW, sl, m_ref, acc2, packed);
-                else at_chunk_prob<CW, false>(v[c], 0, sl, m_ref, acc2, packed);
-                tc_tmem_st<CW / 2>(p_addr + c * (CW / 2), packed);
+                at_chunk_prob<CW, POLY>(v[c], sl, m_exp, acc2, packed);
+                tc_tmem_st<CW / 2>(p_addr + slot_off + c * (CW / 2), packed);
             }
             float s0, s1;
             at_unpack2(acc2, s0, s1);
@@ -405,10 +466,10 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_tmem_st_wait();
             tc_fence_before_sync();          // P (and O) stores of this thread are complete
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&bars[B_PFULL + tile]);
+            if (lane == 0) tc_mbar_arrive(&bars[B_PFULL + tile * 2 + (j & 1)]);
         }
         if (ok && n > 0 &&
-            __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PVDONE + tile], 0, abort_flag, st, 33))) {
+            __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_OFINAL + tile], 0, abort_flag, st, 33))) {
             tc_fence_after_sync();
             // total row sum = the two partial sums (same rescaling history on both threads)
             float l_other = 0.f;
@@ -443,18 +504,18 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 1) tc_tmem_dealloc(tmem_base, 512);
 }
 
-template <int BN, int TPR>
+template <int BN, int TPR, int POLY = 0>
 static int launch_attn(ktb_ctx* ctx, const ktb_attn_args& a, const CUtensorMap& mq, const CUtensorMap& mk,
                        const CUtensorMap& mv) {
     constexpr int AT_STAGES = BN == 128 ? 4 : 8;
     constexpr size_t SMEM = 2 * AT_Q_BYTES + AT_STAGES * (size_t)(BN * AT_D * 2) + 2 * 2 * 2 * AT_BM * 4 + 1024 + 512;
     static bool attr_set = false;
     if (!attr_set) {
-        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN, TPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN, TPR, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
         attr_set = true;
     }
     const int q_pairs = (a.seq_q + 2 * AT_BM - 1) / (2 * AT_BM);
-    ktb_attention_fwd_kernel<BN, TPR><<<q_pairs * a.heads, 128 + 256 * TPR, SMEM, ctx->stream>>>(mq, mk, mv, a, q_pairs, ctx->dev_status);
+    ktb_attention_fwd_kernel<BN, TPR, POLY><<<q_pairs * a.heads, 128 + 256 * TPR, SMEM, ctx->stream>>>(mq, mk, mv, a, q_pairs, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_attention_fwd_kernel");
     return KTB_OK;
 }
@@ -487,11 +548,25 @@ extern "C" int ktb_launch_attention_fwd(ktb_ctx* ctx, const ktb_attn_args* args)
         if (!tc_make_map_f16(which ? &mv : &mk, base + (which ? a.v_off : a.k_off), 4, dims, str, box))
             return ktb_fail(ctx, KTB_E_CUDA, "attention_fwd", "cuTensorMapEncodeTiled(K/V) failed");
     }
+    if (const char* e = getenv("KTB_ATT_STAGGER")) {
+        const int v = atoi(e);
+        cudaMemcpyToSymbol(at_stagger, &v, sizeof(int));
+    }
     int tpr = 1;                        // softmax threads per query row (experiments: KTB_ATT_TPR=2)
     if (const char* e = getenv("KTB_ATT_TPR")) tpr = atoi(e) == 2 ? 2 : 1;
     switch (a.page) {
         case 32: return launch_attn<32, 2>(ctx, a, mq, mk, mv);
-        case 64: return tpr == 1 ? launch_attn<64, 1>(ctx, a, mq, mk, mv) : launch_attn<64, 2>(ctx, a, mq, mk, mv);
-        default: return tpr == 1 ? launch_attn<128, 1>(ctx, a, mq, mk, mv) : launch_attn<128, 2>(ctx, a, mq, mk, mv);
+        case 64: return tpr == 1 ? launch_attn<64, 1, 1>(ctx, a, mq, mk, mv) : launch_attn<64, 2>(ctx, a, mq, mk, mv);
+        default: {
+            int poly = 1;                       // pairs of every 4 whose exp2 runs on the FMA pipe
+            if (const char* e = getenv("KTB_ATT_POLY")) poly = atoi(e);
+            if (tpr == 2) return launch_attn<128, 2>(ctx, a, mq, mk, mv);
+            switch (poly) {
+                case 1: return launch_attn<128, 1, 1>(ctx, a, mq, mk, mv);
+                case 2: return launch_attn<128, 1, 2>(ctx, a, mq, mk, mv);
+                case 3: return launch_attn<128, 1, 3>(ctx, a, mq, mk, mv);
+                default: return launch_attn<128, 1, 0>(ctx, a, mq, mk, mv);
+            }
+        }
     }
 }

@@ -61,6 +61,7 @@ static __device__ __forceinline__ uint32_t tc_mbar_test(uint64_t* bar, uint32_t 
 // phase never completed or the CTA aborted.
 static __device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                     ktb_status* st, int site) {
+    if (tc_mbar_try_wait(bar, parity)) return true;          // the common case costs no clock read
     const long long start = clock64();
     for (uint32_t i = 0;; ++i) {
         if (tc_mbar_try_wait(bar, parity)) return true;
@@ -133,6 +134,43 @@ static __device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t t
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Variants for a warp that runs the issuing code converged and lets one elected lane execute the
+// tcgen05 instruction (`go` != 0 on that lane only): with warp-uniform operands the compiler can
+// keep descriptors in uniform registers instead of moving them there per instruction.
+static __device__ __forceinline__ uint32_t tc_elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred;
+}
+static __device__ __forceinline__ void tc_mma_f16_p(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t accumulate, uint32_t go) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(go)
+        : "memory");
+}
+static __device__ __forceinline__ void tc_mma_f16_ts_p(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                                       uint32_t accumulate, uint32_t go) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(go)
+        : "memory");
+}
+static __device__ __forceinline__ void tc_mma_commit_p(uint64_t* bar, uint32_t go) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(tc_smem_u32(bar)), "r"(go)
         : "memory");
 }
 
