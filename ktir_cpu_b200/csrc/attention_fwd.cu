@@ -143,16 +143,26 @@ static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], fl
 // cycles the softmax of tile 1 starts behind that of tile 0, so that the two do not need the exp
 // unit (and the tensor core) at the same moments
 __constant__ int at_stagger = 800;
-enum { B_QFULL = 0, B_KVFULL = 1, B_KVEMPTY = B_KVFULL + AT_MAX_STAGES, B_SFULL = B_KVEMPTY + AT_MAX_STAGES,
+// barriers: Q full / free per tile; S-full and P-full per tile and score slot (index tile * 2 + slot)
+enum { B_QFULL = 0, B_QFREE = 2, B_KVFULL = 4, B_KVEMPTY = B_KVFULL + AT_MAX_STAGES, B_SFULL = B_KVEMPTY + AT_MAX_STAGES,
        B_PFULL = B_SFULL + 4, B_PVDONE = B_PFULL + 4, B_OFINAL = B_PVDONE + 2, B_XCHG = B_OFINAL + 2, B_COUNT = B_XCHG + 2 };
 
-// TPR = threads per query row in the softmax (1: a thread holds the whole score row of a page in
+// TPR = threads per query row in the softmax (1: a thread holds the whole score row of a step in
 // registers, 384 threads; 2: two threads share a row, 640 threads).
+//
+// The kernel is persistent: CTA b walks the work items b, b + gridDim.x, ...  An item is the pair of
+// query-tile pairs (q_pairs - 1 - r, r) of one head — a late pair, which sees many KV pages, and its
+// early complement, so that all items cost the same — and the two halves are processed one after
+// the other as "sub-items".  Every role (copy thread, the two issuing warps, the softmax warps)
+// derives the same sequence on its own; barrier phases simply keep counting across sub-items.  The
+// point of it: the Q tiles and first K/V pages of the next sub-item are fetched while the last steps
+// of the current one run, and its first scores are computed while the softmax warps normalise and
+// store the output, so a tile pair no longer pays a start-up and a drain of its own.
 template <int BN, int TPR, int POLY>
 __global__ void __launch_bounds__(128 + 256 * TPR, 1)
 ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const ktb_attn_args a, int q_pairs,
-                         ktb_status* st) {
+                         int n_items, ktb_status* st) {
     constexpr int KV_BYTES = BN * AT_D * 2;            // one K or V page in shared memory
     constexpr int AT_STAGES = BN == 128 ? 4 : 8;       // ring slots: 128 KB (64 KB for 32-row pages)
     constexpr int KV_BLK = BN * 128;                   // bytes of one [BN x 64] block
@@ -169,26 +179,38 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
     // (through a shuffle, so that the compiler knows the warp index is the same in all lanes)
     const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
-    // query-tile pairs of one head run back to back (its K/V pages stay in L2); within a head the
-    // late pairs, which see the most KV pages, go first
-    const int head = blockIdx.x / q_pairs;
-    const int qp = q_pairs - 1 - blockIdx.x % q_pairs;
-    const int q0 = qp * 2 * AT_BM;
-    // steps (SB kv rows each) tile i can see: kv position p is visible to row R iff p <= R + delta
-    int n_of[2];
+    const int half_pairs = (q_pairs + 1) / 2;          // items per head
+
+    // Sub-item s of this CTA: false when the CTA has run out of items.  n_of[i] = steps (SB kv rows each)
+    // tile i can see (kv position p is visible to row R iff p <= R + delta), 0 for a tile that does
+    // not exist; nmax = pages to stream.  An item whose two halves coincide has an empty second half.
+    auto sub_item = [&](int s, int& head, int& q0, int (&n_of)[2], int& nmax) -> bool {
+        const long long item64 = (long long)blockIdx.x + (long long)(s >> 1) * gridDim.x;
+        if (item64 >= n_items) return false;
+        const int item = (int)item64;
+        head = item / half_pairs;
+        const int r = item % half_pairs;
+        const int qp = (s & 1) ? r : q_pairs - 1 - r;
+        q0 = qp * 2 * AT_BM;
+        const bool empty = (s & 1) && r == q_pairs - 1 - r;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        int n = a.num_tiles * NSUB;
-        const long long last = (long long)q0 + i * AT_BM + AT_BM - 1 + a.causal_delta;
-        const long long vis = last < 0 ? 0 : last / SB + 1;
-        if (a.causal && vis < n) n = (int)vis;
-        if (q0 + i * AT_BM >= a.seq_q) n = 0;          // no second tile in the last pair of an odd count
-        n_of[i] = n;
-    }
-    const int nmax = ((n_of[0] > n_of[1] ? n_of[0] : n_of[1]) + NSUB - 1) / NSUB;      // pages to stream
+        for (int i = 0; i < 2; ++i) {
+            int n = a.num_tiles * NSUB;
+            const long long last = (long long)q0 + i * AT_BM + AT_BM - 1 + a.causal_delta;
+            const long long vis = last < 0 ? 0 : last / SB + 1;
+            if (a.causal && vis < n) n = (int)vis;
+            if (q0 + i * AT_BM >= a.seq_q) n = 0;      // no second tile in the last pair of an odd count
+            n_of[i] = empty ? 0 : n;
+        }
+        nmax = ((n_of[0] > n_of[1] ? n_of[0] : n_of[1]) + NSUB - 1) / NSUB;
+        return true;
+    };
 
     if (threadIdx.x == 0) {
-        tc_mbar_init(&bars[B_QFULL], 1);
+        for (int i = 0; i < 2; ++i) {
+            tc_mbar_init(&bars[B_QFULL + i], 1);
+            tc_mbar_init(&bars[B_QFREE + i], 1);
+        }
         for (int i = 0; i < AT_STAGES; ++i) {
             tc_mbar_init(&bars[B_KVFULL + i], 1);
             tc_mbar_init(&bars[B_KVEMPTY + i], 2);      // both issuing threads
@@ -215,128 +237,158 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const uint32_t tmem_o = tmem_base + 256;      // O_0, O_1: 2 x 128 columns
 
     // register budget: the copy/MMA warpgroup needs few registers, the softmax warpgroups hold a
-    // half a row of scores each; the MMA issue loop must not spill, it paces the whole CTA
+    // row of scores each; the MMA issue loop must not spill, it paces the whole CTA
     // (each setmaxnreg sits at the head of the region it governs, with no join in between)
     if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");          // (a decrease only for TPR = 1, see below)
     if (warp == 0) {
-        if (lane == 0 && nmax > 0) {
+        if (lane == 0) {
             tc_prefetch_tmap(&map_q);
             tc_prefetch_tmap(&map_k);
             tc_prefetch_tmap(&map_v);
-            const int q_tiles = n_of[1] > 0 ? 2 : 1;
-            tc_mbar_expect_tx(&bars[B_QFULL], q_tiles * AT_Q_BYTES);
-            for (int i = 0; i < q_tiles; ++i) {
-                tc_tma_load_3d(sQ + i * AT_Q_BYTES, &map_q, &bars[B_QFULL], 0, head, q0 + i * AT_BM);
-                tc_tma_load_3d(sQ + i * AT_Q_BYTES + AT_BM * 128, &map_q, &bars[B_QFULL], 64, head, q0 + i * AT_BM);
-            }
             const int32_t* bt32 = reinterpret_cast<const int32_t*>(a.arena) + a.bt_off;
             const int64_t* bt64 = reinterpret_cast<const int64_t*>(a.arena) + a.bt_off;
-            // load t = 2 j is K of page j, t = 2 j + 1 is V of page j; slot t % AT_STAGES
-            for (int t = 0; t < 2 * nmax; ++t) {
-                const int slot = t % AT_STAGES;
-                const uint32_t ph = (t / AT_STAGES) & 1;
-                const bool is_v = t & 1;
-                const int j = t >> 1;
-                long long page = a.bt_dtype == KTB_I64 ? bt64[j] : (long long)bt32[j];
-                if (page < 0) {
-                    if (atomicExch(&st->negative_index, 1) == 0) st->bad_index_value = (int32_t)page;
-                    page = 0;
+            int t = 0;                  // ring loads issued so far: K of a page, then its V; slot t % AT_STAGES
+            int q_loads[2] = {0, 0};    // Q tiles loaded so far, per tile
+            bool ok = true;
+            for (int s = 0; ok; ++s) {
+                int head, q0, n_of[2], nmax;
+                if (!sub_item(s, head, q0, n_of, nmax)) break;
+                for (int i = 0; i < 2 && ok; ++i) {
+                    if (n_of[i] == 0) continue;
+                    // the tile's Q buffer is free once the last score MMA of its previous sub-item has completed
+                    if (q_loads[i] > 0) ok = tc_mbar_wait(&bars[B_QFREE + i], (q_loads[i] - 1) & 1, abort_flag, st, 12);
+                    if (!ok) break;
+                    ++q_loads[i];
+                    tc_mbar_expect_tx(&bars[B_QFULL + i], AT_Q_BYTES);
+                    tc_tma_load_3d(sQ + i * AT_Q_BYTES, &map_q, &bars[B_QFULL + i], 0, head, q0 + i * AT_BM);
+                    tc_tma_load_3d(sQ + i * AT_Q_BYTES + AT_BM * 128, &map_q, &bars[B_QFULL + i], 64, head, q0 + i * AT_BM);
                 }
-                if (!tc_mbar_wait(&bars[B_KVEMPTY + slot], ph ^ 1, abort_flag, st, 11)) break;
-                tc_mbar_expect_tx(&bars[B_KVFULL + slot], KV_BYTES);
-                const CUtensorMap* map = is_v ? &map_v : &map_k;
-                at_tma_load_4d(sKV + slot * KV_BYTES, map, &bars[B_KVFULL + slot], 0, head, 0, (int)page);
-                at_tma_load_4d(sKV + slot * KV_BYTES + KV_BLK, map, &bars[B_KVFULL + slot], 64, head, 0, (int)page);
+                for (int l = 0; l < 2 * nmax && ok; ++l, ++t) {
+                    const int slot = t % AT_STAGES;
+                    const int j = l >> 1;
+                    long long page = a.bt_dtype == KTB_I64 ? bt64[j] : (long long)bt32[j];
+                    if (page < 0) {
+                        if (atomicExch(&st->negative_index, 1) == 0) st->bad_index_value = (int32_t)page;
+                        page = 0;
+                    }
+                    if (!tc_mbar_wait(&bars[B_KVEMPTY + slot], ((t / AT_STAGES) & 1) ^ 1, abort_flag, st, 11)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_mbar_expect_tx(&bars[B_KVFULL + slot], KV_BYTES);
+                    const CUtensorMap* map = (l & 1) ? &map_v : &map_k;
+                    at_tma_load_4d(sKV + slot * KV_BYTES, map, &bars[B_KVFULL + slot], 0, head, 0, (int)page);
+                    at_tma_load_4d(sKV + slot * KV_BYTES + KV_BLK, map, &bars[B_KVFULL + slot], 64, head, 0, (int)page);
+                }
             }
         }
     } else if (warp == 1 || warp == 2) {
-        // One issuing thread per query tile (warps 1 and 2 sit on different schedulers): a single
-        // thread cannot prepare descriptors fast enough to keep the tensor core busy for both tiles.
-        // The scores of step u go to slot u & 1 of the tile, and P(u) is written over the front of
-        // the same slot; so S(u+2) is issued right after P V(u) (the tensor core runs one thread's
-        // MMAs in issue order), and the scores of step u+1 are already waiting when the softmax
-        // finishes step u.  P V(u) needs P(u) in TMEM and the V page in shared memory, S(u) the K
-        // page.  Both issuers release every slot of the ring (two arrivals per slot and round): a
-        // tile that sees fewer pages follows the remaining ones along without issuing anything.
-        // The whole warp runs this code converged; one elected lane executes the tcgen05 instructions.
-        if (nmax > 0) {
+        // One issuing warp per query tile (warps 1 and 2 sit on different schedulers); the warp runs
+        // this code converged and one elected lane executes the tcgen05 instructions.
+        // Steps of a tile are numbered g = 0, 1, ... across sub-items.  The scores of step g go to slot
+        // g & 1 of the tile, and P(g) is written over the front of the same slot; so S(g+2) is issued
+        // right after P V(g) (the tensor core runs one thread's MMAs in issue order), and the scores
+        // of step g+1 are already waiting when the softmax finishes step g.  P V(g) needs P(g) in TMEM
+        // and the V page in shared memory, S(g) the K page and the tile's Q.  Both issuers release
+        // every slot of the ring (two arrivals per slot and round): a tile that sees fewer pages
+        // follows the remaining ones along without issuing anything.
+        {
             const uint32_t lead = tc_elect_one();
             const int i = warp - 1;
-            const int n = n_of[i];
             const uint32_t idesc_s = tc_idesc_f16(AT_BM, SB, 0, 0);
             const uint32_t idesc_pv = tc_idesc_f16(AT_BM, AT_D, 0, 1);
             const uint32_t ts = tmem_s + i * 128, to = tmem_o + i * 128;
             const uint64_t qd0 = tc_smem_desc(tc_smem_u32(sQ + i * AT_Q_BYTES), 16, 1024);
+            const uint32_t kv_addr0 = tc_smem_u32(sKV);
+            int t0 = 0;                 // ring loads before this sub-item (load t0 + 2 m is K of page m, t0 + 2 m + 1 its V)
+            int g0 = 0;                 // steps of this tile before this sub-item
+            int q_uses = 0;             // Q tiles consumed so far
+            int n = 0;
             auto kv_wait = [&](int t) {
                 return __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_KVFULL + t % AT_STAGES], (t / AT_STAGES) & 1, abort_flag, st, 22)) != 0;
             };
             auto kv_release = [&](int t) { tc_mma_commit_p(&bars[B_KVEMPTY + t % AT_STAGES], lead); };
-            const uint32_t kv_addr0 = tc_smem_u32(sKV);
-            // Operands of a step are computed ahead of the wait that gates it: this thread's own
-            // instructions, not the tensor core, are what a step of a tile costs.
+            // Operands of a step are computed ahead of the wait that gates it.
             // step u = rows [h * SB, h * SB + SB) of page m; 64 rows of a block are whole swizzle atoms.
-            auto s_desc = [&](int u) {           // K rows of step u (load 2 m is K of page m)
+            auto s_desc = [&](int u) {
                 const int m = u / NSUB, h = u % NSUB;
-                return tc_smem_desc(kv_addr0 + ((2 * m) % AT_STAGES) * KV_BYTES + h * SB * 128, 16, 1024);
+                return tc_smem_desc(kv_addr0 + ((t0 + 2 * m) % AT_STAGES) * KV_BYTES + h * SB * 128, 16, 1024);
             };
-            auto pv_desc = [&](int u) {          // V rows of step u (load 2 m + 1 is V of page m)
+            auto pv_desc = [&](int u) {
                 const int m = u / NSUB, h = u % NSUB;
-                return tc_smem_desc(kv_addr0 + ((2 * m + 1) % AT_STAGES) * KV_BYTES, KV_BLK, 1024) +
+                return tc_smem_desc(kv_addr0 + ((t0 + 2 * m + 1) % AT_STAGES) * KV_BYTES, KV_BLK, 1024) +
                        (uint32_t)(h * (SB / 16) * 2048 >> 4);
             };
             auto issue_s = [&](int u, uint64_t bd0) {
                 // the start-address field is the low 14 bits of the descriptor (in 16-byte units), so
                 // stepping along K is an add of a constant; the loop is unrolled
-                const uint32_t d = ts + (u & 1) * 64;
+                const int g = g0 + u;
+                const uint32_t d = ts + (g & 1) * 64;
 #pragma unroll
                 for (int kk = 0; kk < AT_D / 16; ++kk) {
                     const uint32_t ao = ((kk >> 2) * (AT_BM * 128) + (kk & 3) * 32) >> 4;
                     const uint32_t bo = ((kk >> 2) * KV_BLK + (kk & 3) * 32) >> 4;
                     tc_mma_f16_p(d, qd0 + ao, bd0 + bo, idesc_s, kk != 0, lead);
                 }
-                tc_mma_commit_p(&bars[B_SFULL + i * 2 + (u & 1)], lead);
-                if (u % NSUB == NSUB - 1 || u == n - 1) kv_release(2 * (u / NSUB));
+                tc_mma_commit_p(&bars[B_SFULL + i * 2 + (g & 1)], lead);
+                if (u == n - 1) tc_mma_commit_p(&bars[B_QFREE + i], lead);       // last use of this Q tile
+                if (u % NSUB == NSUB - 1 || u == n - 1) kv_release(t0 + 2 * (u / NSUB));
             };
             auto issue_pv = [&](int u, uint64_t bd0) {
                 // A = P from TMEM: row r in lane r, 16 f16 of a K step packed in 8 columns
-                const uint32_t pa = ts + (u & 1) * 64;
+                const int g = g0 + u;
+                const uint32_t pa = ts + (g & 1) * 64;
 #pragma unroll
                 for (int kk = 0; kk < SB / 16; ++kk)
                     tc_mma_f16_ts_p(to, pa + kk * 8, bd0 + (uint32_t)(kk * 2048 >> 4), idesc_pv, (u > 0 || kk > 0) ? 1u : 0u, lead);
                 tc_mma_commit_p(&bars[B_PVDONE + i], lead);
                 if (u == n - 1) tc_mma_commit_p(&bars[B_OFINAL + i], lead);      // the accumulator is final
-                if (u % NSUB == NSUB - 1 || u == n - 1) kv_release(2 * (u / NSUB) + 1);
+                if (u % NSUB == NSUB - 1 || u == n - 1) kv_release(t0 + 2 * (u / NSUB) + 1);
             };
-            bool ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_QFULL], 0, abort_flag, st, 21)) != 0;
-            if (ok) tc_fence_after_sync();
-            for (int u = 0; u < 2 && u < n && ok; ++u) {
-                if (u % NSUB == 0) ok = kv_wait(2 * (u / NSUB));
-                if (ok) {
-                    tc_fence_after_sync();
-                    issue_s(u, s_desc(u));
+            bool ok = true;
+            for (int s = 0; ok; ++s) {
+                int head, q0, n_of[2], nmax;
+                if (!sub_item(s, head, q0, n_of, nmax)) break;
+                n = n_of[i];
+                if (n > 0) {
+                    ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_QFULL + i], q_uses & 1, abort_flag, st, 21)) != 0;
+                    ++q_uses;
+                    if (ok) tc_fence_after_sync();
+                    // the first P V of a sub-item overwrites the accumulator; that the softmax warps have
+                    // read the previous result out is implied by their P(0) arriving (program order there)
+                    for (int u = 0; u < 2 && u < n && ok; ++u) {
+                        if (u % NSUB == 0) ok = kv_wait(t0 + 2 * (u / NSUB));
+                        if (ok) {
+                            tc_fence_after_sync();
+                            issue_s(u, s_desc(u));
+                        }
+                    }
+                    for (int u = 0; u < n && ok; ++u) {
+                        const int g = g0 + u;
+                        const uint64_t vd = pv_desc(u), kd = s_desc(u + 2);
+                        ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PFULL + i * 2 + (g & 1)], (g >> 1) & 1, abort_flag, st, 23)) != 0;
+                        if (ok && u % NSUB == 0) ok = kv_wait(t0 + 2 * (u / NSUB) + 1);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_pv(u, vd);
+                        if (u + 2 < n) {
+                            if ((u + 2) % NSUB == 0) ok = kv_wait(t0 + 2 * ((u + 2) / NSUB));
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                            issue_s(u + 2, kd);
+                        }
+                    }
                 }
-            }
-            for (int u = 0; u < n && ok; ++u) {
-                const uint64_t vd = pv_desc(u), kd = s_desc(u + 2);
-                ok = __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PFULL + i * 2 + (u & 1)], (u >> 1) & 1, abort_flag, st, 23)) != 0;
-                if (ok && u % NSUB == 0) ok = kv_wait(2 * (u / NSUB) + 1);
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_pv(u, vd);
-                if (u + 2 < n) {
-                    if ((u + 2) % NSUB == 0) ok = kv_wait(2 * ((u + 2) / NSUB));
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_s(u + 2, kd);
+                // pages only the other tile uses: keep the ring's arrival counts in step
+                for (int m = (n + NSUB - 1) / NSUB; m < nmax && ok; ++m) {
+                    for (int t = t0 + 2 * m; t < t0 + 2 * m + 2 && ok; ++t) {
+                        ok = kv_wait(t);
+                        if (ok && lead) tc_mbar_arrive(&bars[B_KVEMPTY + t % AT_STAGES]);
+                    }
                 }
-            }
-            // pages only the other tile uses: keep the ring's arrival counts in step
-            for (int m = (n + NSUB - 1) / NSUB; m < nmax && ok; ++m) {
-                for (int t = 2 * m; t < 2 * m + 2 && ok; ++t) {
-                    ok = kv_wait(t);
-                    if (ok && lead) tc_mbar_arrive(&bars[B_KVEMPTY + t % AT_STAGES]);
-                }
+                t0 += 2 * nmax;
+                g0 += n;
             }
         }
     }
@@ -353,10 +405,8 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         constexpr int OH = AT_D / TPR;               // output columns per thread
         const int tile = (warp - 4) / (4 * TPR);     // which query tile this warpgroup (pair) owns
         const int half = TPR == 2 ? ((warp - 4) >> 2) & 1 : 0;
-        const int n = n_of[tile];
         const int q = warp & 3;                      // TMEM lane quadrant this warp may access
         const int r = q * 32 + lane;                 // row inside the tile == TMEM lane
-        const int R = q0 + tile * AT_BM + r;
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
         const uint32_t s_addr = tmem_s + tile * 128 + lane_off + half * HB;
         // P (f16, two per 32-bit column) goes over the first SB/2 columns of the score slot
@@ -364,13 +414,10 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const uint32_t o_addr = tmem_o + tile * 128 + lane_off + half * OH;
         float* xrow = xbuf + tile * (2 * 2 * AT_BM) + r;        // + parity * 256 + half * 128
         const float sl = a.scale * 1.4426950408889634f;
-        float m_ref = a.m_init * 1.4426950408889634f;           // exponent reference, log2 domain
-        float m_run = m_ref;                                    // true running maximum
-        float l_run = half == 0 ? a.l_init : 0.f;               // this thread's share of the running sum
-        const long long limit = (long long)R + a.causal_delta;  // last visible kv position
-        const long long tile_limit = (long long)q0 + tile * AT_BM + a.causal_delta;
         bool ok = true;
         uint32_t xphase = 0;
+        int g0 = 0;                  // steps of this tile before the current sub-item
+        int finals = 0;              // sub-items of this tile finished so far
 
         // swap one f32 with the partner thread of the row (slot parity alternates, so a value is
         // not overwritten before the partner has read it)
@@ -386,16 +433,35 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             return true;
         };
 
+        for (int s = 0; ok; ++s) {
+        int head, q0, n_of[2], nmax;
+        if (!sub_item(s, head, q0, n_of, nmax)) break;
+        const int n = n_of[tile];
+        if (n == 0) continue;
+        const int R = q0 + tile * AT_BM + r;
+        float m_ref = a.m_init * 1.4426950408889634f;           // exponent reference, log2 domain
+        float m_run = m_ref;                                    // true running maximum
+        float l_run = half == 0 ? a.l_init : 0.f;               // this thread's share of the running sum
+        const long long limit = (long long)R + a.causal_delta;  // last visible kv position
+        const long long tile_limit = (long long)q0 + tile * AT_BM + a.causal_delta;
+        // first step with a hidden column for some row of the tile: (j + 1) * SB - 1 > tile_limit
+        // (kept as one int so that the common, unmasked step pays one compare for the mask)
+        int j_mask = 0x7fffffff;
+        if (a.causal) {
+            const long long jm = tile_limit + 1 >= 0 ? (tile_limit + 1) / SB : 0;
+            j_mask = jm > 0x7fffffff ? 0x7fffffff : (int)jm;
+        }
         for (int j = 0; j < n && ok; ++j) {            // j counts steps of SB kv rows
-            const uint32_t slot_off = (j & 1) * 64;
+            const int g = g0 + j;                      // step number of the tile across sub-items
+            const uint32_t slot_off = (g & 1) * 64;
             // the whole warp leaves together: the TMEM accesses below are warp-collective.
-            // S(j) is issued after P V(j-2), which read the P columns of this slot.
-            if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_SFULL + tile * 2 + (j & 1)], (j >> 1) & 1, abort_flag, st, 31))) {
+            // S(g) is issued after P V(g-2), which read the P columns of this slot.
+            if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_SFULL + tile * 2 + (g & 1)], (g >> 1) & 1, abort_flag, st, 31))) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            if (j == 0 && tile == 1 && at_stagger > 0) {
+            if (g == 0 && tile == 1 && at_stagger > 0) {
                 const long long t0 = clock64();
                 while (clock64() - t0 < at_stagger) {}
             }
@@ -406,11 +472,11 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_tmem_ld_wait();
 
             // columns of this thread's range the row may see (all of them except on the diagonal pages)
-            const long long vis_ll = limit - ((long long)j * SB + half * HB) + 1;
-            const int vis = vis_ll > HB ? HB : (vis_ll < 0 ? 0 : (int)vis_ll);
-            const bool need_mask = a.causal && ((long long)j * SB + SB - 1 > tile_limit);   // same for the whole tile
+            const bool need_mask = j >= j_mask;          // same for the whole tile
             // hidden columns become -inf once (exp2 turns them into zeros), then every step takes the same path
             if (need_mask) {
+                const long long vis_ll = limit - ((long long)j * SB + half * HB) + 1;
+                const int vis = vis_ll > HB ? HB : (vis_ll < 0 ? 0 : (int)vis_ll);
 #pragma unroll
                 for (int c = 0; c < NCH; ++c)
 #pragma unroll
@@ -433,9 +499,9 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (move) m_ref = m_run;
                 l_run *= alpha;
                 if (j > 0) {
-                    // the accumulator may only be touched once P V(j-1) has completed; P V(j-2) completed
-                    // before S(j), so the barrier is in phase j-1 or has just completed it
-                    if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PVDONE + tile], (j - 1) & 1, abort_flag, st, 32))) {
+                    // the accumulator may only be touched once P V(g-1) has completed; P V(g-2) completed
+                    // before S(g), so the barrier is in phase g-1 or has just completed it
+                    if (!__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_PVDONE + tile], (g - 1) & 1, abort_flag, st, 32))) {
                         ok = false;
                         break;
                     }
@@ -466,10 +532,12 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tc_tmem_st_wait();
             tc_fence_before_sync();          // P (and O) stores of this thread are complete
             __syncwarp();
-            if (lane == 0) tc_mbar_arrive(&bars[B_PFULL + tile * 2 + (j & 1)]);
+            if (lane == 0) tc_mbar_arrive(&bars[B_PFULL + tile * 2 + (g & 1)]);
         }
-        if (ok && n > 0 &&
-            __all_sync(0xffffffffu, tc_mbar_wait(&bars[B_OFINAL + tile], 0, abort_flag, st, 33))) {
+        g0 += n;
+        if (ok && !__all_sync(0xffffffffu, tc_mbar_wait(&bars[B_OFINAL + tile], finals & 1, abort_flag, st, 33))) ok = false;
+        ++finals;
+        if (ok) {
             tc_fence_after_sync();
             // total row sum = the two partial sums (same rescaling history on both threads)
             float l_other = 0.f;
@@ -498,6 +566,7 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 }
             }
         }
+        }   // sub-items
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -515,7 +584,11 @@ static int launch_attn(ktb_ctx* ctx, const ktb_attn_args& a, const CUtensorMap& 
         attr_set = true;
     }
     const int q_pairs = (a.seq_q + 2 * AT_BM - 1) / (2 * AT_BM);
-    ktb_attention_fwd_kernel<BN, TPR, POLY><<<q_pairs * a.heads, 128 + 256 * TPR, SMEM, ctx->stream>>>(mq, mk, mv, a, q_pairs, ctx->dev_status);
+    // an item = the tile pairs (q_pairs - 1 - r, r) of one head; one persistent CTA per SM walks them
+    const long long items = (long long)((q_pairs + 1) / 2) * a.heads;
+    if (items > 0x7fffffff) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "attention_fwd", "too many query tiles");
+    const int grid = items < ctx->sm_count ? (int)items : ctx->sm_count;
+    ktb_attention_fwd_kernel<BN, TPR, POLY><<<grid, 128 + 256 * TPR, SMEM, ctx->stream>>>(mq, mk, mv, a, q_pairs, (int)items, ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_attention_fwd_kernel");
     return KTB_OK;
 }

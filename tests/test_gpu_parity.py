@@ -151,6 +151,29 @@ def test_gather_scale_scatter_ordered_rmw(n_rows, n_idx, build_lib):
     np.testing.assert_array_equal(got["out_ptr"], got2["out_ptr"])
 
 
+def test_cached_plan_replayed_as_graph_follows_new_inputs(build_lib):
+    """From its second run on a multi-launch plan is replayed as one CUDA graph: every replay must see the
+    inputs of its own call (new table, indices and destination), bit for bit like the oracle."""
+    n_rows, n_idx = 512, 4096
+    src = K.gather_scale_scatter(n_rows, 128, n_idx, 64, 8)
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    ora = OracleInterpreter()
+    ora.load(src)
+    for seed in range(4):
+        rng = np.random.default_rng(100 + seed)
+        kw = dict(table_ptr=rng.standard_normal((n_rows, 128)).astype(np.float16),
+                  idx_ptr=_dup_indices(rng, n_rows, n_idx, 64, 6).astype(np.int32),
+                  out_ptr=rng.standard_normal((n_rows, 128)).astype(np.float16))
+        got = gpu.execute_function("gather_scale_scatter", **kw)
+        want = ora.execute_function("gather_scale_scatter", **kw)
+        np.testing.assert_array_equal(got["out_ptr"], want["out_ptr"])
+    sessions = list(gpu._sessions.values()) if hasattr(gpu, "_sessions") else []
+    if sessions:
+        assert any(s._graph is not None for s in sessions)      # the replay path was the one exercised
+    gpu.close()
+
+
 def test_negative_index_raises_index_error(build_lib):
     src, fn, kwargs, _ = load_golden("gather_scale_scatter_256")
     kwargs["idx_ptr"] = kwargs["idx_ptr"].copy()
@@ -271,6 +294,21 @@ def test_causal_attention_long_sequence_properties(build_lib):
     gpu.close()
     np.testing.assert_allclose(o[0].astype(np.float32), v[0].astype(np.float32), rtol=2e-3, atol=2e-3)
     assert (o.astype(np.float32).max(0) <= v.astype(np.float32).max(0) + 1e-2).all()
+    np.testing.assert_allclose(o.astype(np.float64), _attention_f64(q, k, v, D), rtol=1e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("S,H", [(512, 320), (768, 160), (640, 200)])
+def test_causal_attention_many_tiles_per_cta(S, H, build_lib):
+    """More work items than SMs, so a persistent CTA walks several tile pairs one after another
+    (barrier phases carry over); 768 has an odd number of tile pairs (an item with one half only),
+    640 an odd number of tiles (a pair whose second tile does not exist)."""
+    rng = np.random.default_rng(S + H)
+    D, tn = 128, 128
+    q, k, v, kw = _attention_inputs(rng, S, H, D, tn, shuffle_pages=True)
+    gpu = KTIRInterpreter()
+    gpu.load(K_.causal_attention(S, H, D, 128, tn))
+    o = gpu.execute_function("attention_kernel", **kw)["output_ptr"]
+    gpu.close()
     np.testing.assert_allclose(o.astype(np.float64), _attention_f64(q, k, v, D), rtol=1e-2, atol=2e-3)
 
 
