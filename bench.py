@@ -55,7 +55,7 @@ def _rows_fix(rows, cores, r):
 
 
 class Softmax(Workload):
-    name, func, kernel = "softmax", "softmax_kernel", "ktb_row_softmax_kernel"
+    name, func, kernel = "softmax", "softmax_kernel", "ktb_row_softmax_fast_kernel"
     R, C, CORES, RPI = 8192, 4096, 32, 8
     units_per_step = R * C
     algo_per_step = 2 * R * C * 2
