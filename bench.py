@@ -624,6 +624,7 @@ def run_candidates(args):
             checks[i] = float(np.abs(out["output_ptr"][:, h].astype(np.float64) - (p / p.sum(-1, keepdims=True)) @ v).max())
         return True
     warm = runner.run(cands[:27 * world], rank, world, score=score, keep_outputs=False)  # every distinct kernel planned once
+    res = runner.run(cands, rank, world, score=None, keep_outputs=True)   # one untimed sweep: the pinned result buffers exist
     if dist is not None:
         dist.barrier()
     sampler = ClockSampler(local)
@@ -632,6 +633,7 @@ def run_candidates(args):
     steps = max(1, args.steps // 10)
     launches = 0
     for _ in range(steps):
+        res = None                            # the consumer is done with the previous sweep's results: their buffers are reused
         res = runner.run(cands, rank, world, score=None, keep_outputs=True)
         launches += res.launches
     dt = time.perf_counter() - t0
@@ -645,7 +647,7 @@ def run_candidates(args):
     if rank == 0:
         h2d = sum(v.nbytes for c in cands for v in c.kwargs.values() if isinstance(v, np.ndarray)) // n
         line = {"metric": "candidate kernels evaluated per second (512-variant causal attention sweep)",
-                "value": n * steps / dt, "unit": "kernels/s", "n_gpus": world, "steps": steps, "warmup": 1,
+                "value": n * steps / dt, "unit": "kernels/s", "n_gpus": world, "steps": steps, "warmup": 2,
                 "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic",
                 "config": {"workload": "512 variants: tile_m,tile_n in {32,64,128}, S in {512,1024,2048}, B=1, H=4, D=128; "

@@ -43,6 +43,8 @@ class BatchRunner:
         self.latency_config = latency_config
         self._interps: Dict[str, KTIRInterpreter] = {}
         self.parses = 0
+        self._pool = None                     # pinned buffers behind the result arrays
+        self._staging: Dict[int, np.ndarray] = {}     # pinned staging buffers for uploads, one per argument slot
 
     def _interp(self, source: str) -> KTIRInterpreter:
         it = self._interps.get(source)
@@ -80,16 +82,34 @@ class BatchRunner:
         res.parses = self.parses
         return res
 
-    @staticmethod
-    def _execute(it: KTIRInterpreter, c: Candidate) -> Dict[str, np.ndarray]:
+    def _stage(self, dev, slot: int, arr: np.ndarray) -> np.ndarray:
+        """Copy ``arr`` into the pinned staging buffer of argument slot ``slot``: the DMA of one
+        tensor then overlaps the host copy of the next.  The buffers are reused by the next
+        candidate, which is safe because every candidate ends with a stream synchronisation."""
+        from .pinned import pinned_empty
+        buf = self._staging.get(slot)
+        if buf is None or buf.nbytes < arr.nbytes:
+            buf = pinned_empty(dev, (max(arr.nbytes, 1) * 5 // 4,), np.uint8)
+            self._staging[slot] = buf
+        view = buf[:arr.nbytes].view(arr.dtype).reshape(arr.shape)
+        np.copyto(view, arr)
+        return view
+
+    def _execute(self, it: KTIRInterpreter, c: Candidate) -> Dict[str, np.ndarray]:
         """Upload, launch, and read back only the tensors the kernel writes (a scorer has the
-        inputs already; ``execute_function`` would copy every tensor back)."""
+        inputs already; ``execute_function`` would copy every tensor back).  Host copies go through
+        page-locked memory on both sides, so the transfers run asynchronously at PCIe speed."""
         sess, kwargs = it.session(c.function, **c.kwargs)
+        if self._pool is None:
+            from .pinned import PinnedPool
+            self._pool = PinnedPool(sess.dev)
+        slot = 0
         for k, v in kwargs.items():
             if isinstance(v, np.ndarray) and k not in sess.no_upload:
-                sess.upload(k, v)
+                sess.upload(k, self._stage(sess.dev, slot, v) if v.nbytes >= 65536 else v)
+                slot += 1
         sess.run()
-        out = {k: sess.download(k) for k in kwargs if k in sess.written}
+        out = {k: sess.download(k, pool=self._pool) for k in kwargs if k in sess.written}
         st = sess.dev.sync()
         if st.negative_index:
             raise IndexError(f"indirect index {st.bad_index_value} is negative")
@@ -99,6 +119,10 @@ class BatchRunner:
         for it in self._interps.values():
             it.close()
         self._interps.clear()
+        self._staging.clear()
+        if self._pool is not None:
+            self._pool.close()
+            self._pool = None
 
 
 def evaluate_many(candidates: Sequence[Candidate], device: int = 0, rank: int = 0, world: int = 1,
