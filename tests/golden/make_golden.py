@@ -128,7 +128,9 @@ def latency_main(ref_root: str):
 
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    root = args[0] if args else "/root/reference"
+    root = args[0] if args else os.environ.get("KTIR_REFERENCE", "")
+    if not root:
+        sys.exit("usage: make_golden.py <path of a ktir_cpu checkout> [--only=<case>] [--latency-only]")
     only = [a[len("--only="):] for a in sys.argv[1:] if a.startswith("--only=")]
     if "--latency-only" not in sys.argv:
         main(root, only)
