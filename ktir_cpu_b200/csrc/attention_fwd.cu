@@ -1,13 +1,13 @@
 // Causal attention forward with online softmax and paged K/V, head_dim 128.
 //
-// One CTA owns two 128-row query tiles of one head and walks the KV pages that the causal
-// mask leaves visible.  It replaces the per-page op sequence of a KTIR attention kernel —
+// A persistent CTA (one per SM) works through pairs of 128-row query tiles of one head, one pair
+// at a time, and walks the KV pages that the causal mask leaves visible.  It replaces the per-page op sequence of a KTIR attention kernel —
 // indirect ktdp.load of a K and a V page through the block table, two linalg.matmul,
 // mask / max / exp / sum / rescale in f32 — which the reference dispatches op by op
 // (examples/triton-ktir/paged_attention.mlir:183-396, ktir_cpu/ops/memory_ops.py:867-915,
 // ktir_cpu/dialects/linalg_ops.py:136-347).
 //
-// Roles: warp 0 streams both Q tiles once and the K/V pages (page id from the block table)
+// Roles: warp 0 streams the Q tiles of a pair once and the K/V pages (page id from the block table)
 // through a shared-memory ring by TMA; warps 1 and 2 issue tcgen05.mma for tile 0 and tile 1 —
 // S_i = Q_i K^T into a score slot of tile i, P_i V accumulated into the output buffer of tile i,
 // both in TMEM; warps 4-7 are the softmax of tile 0, warps 8-11 of tile 1, one thread per query
