@@ -262,7 +262,9 @@ int ktb_launch_gemm_f16(ktb_ctx* ctx, const ktb_gemm_args* args);
  * (ktir_cpu/ops/memory_ops.py:867-915), two linalg.matmul, mask, running max / sum and
  * rescale (examples/triton-ktir/paged_attention.mlir:183-396 of the reference).
  * m_init / l_init are the initial running max and sum the kernel carries (-inf and 1.0
- * there).  All offsets and strides are in elements and must be multiples of 8. */
+ * there).  kv_group query heads share one K/V head (query head h reads K/V head
+ * h / kv_group, paged_attention.mlir:163-181; 0 or 1 = one K/V head per query head).
+ * All offsets and strides are in elements and must be multiples of 8. */
 typedef struct {
     void* arena;
     int64_t q_off, o_off, k_off, v_off;        /* f16 element offsets of query, output, K cache, V cache */
@@ -274,7 +276,7 @@ typedef struct {
     int64_t q_row_stride, q_head_stride, o_row_stride, o_head_stride;
     int64_t kv_page_stride, kv_row_stride, kv_head_stride;
     float scale, m_init, l_init;
-    int32_t reserved;
+    int32_t kv_group;                          /* query heads per K/V head */
 } ktb_attn_args;
 int ktb_launch_attention_fwd(ktb_ctx* ctx, const ktb_attn_args* args);
 

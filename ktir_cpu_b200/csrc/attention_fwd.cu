@@ -142,7 +142,7 @@ static __device__ __forceinline__ void at_chunk_prob(const uint32_t (&v)[CW], fl
 // S-full and P-full barriers exist per tile and score slot (index tile * 2 + slot)
 // cycles the softmax of tile 1 starts behind that of tile 0, so that the two do not need the exp
 // unit (and the tensor core) at the same moments
-__constant__ int at_stagger = 800;
+#define AT_STAGGER 800
 // barriers: Q full / free per tile; S-full and P-full per tile and score slot (index tile * 2 + slot)
 enum { B_QFULL = 0, B_QFREE = 2, B_KVFULL = 4, B_KVEMPTY = B_KVFULL + AT_MAX_STAGES, B_SFULL = B_KVEMPTY + AT_MAX_STAGES,
        B_PFULL = B_SFULL + 4, B_PVDONE = B_PFULL + 4, B_OFINAL = B_PVDONE + 2, B_XCHG = B_OFINAL + 2, B_COUNT = B_XCHG + 2 };
@@ -250,10 +250,12 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const int64_t* bt64 = reinterpret_cast<const int64_t*>(a.arena) + a.bt_off;
             int t = 0;                  // ring loads issued so far: K of a page, then its V; slot t % AT_STAGES
             int q_loads[2] = {0, 0};    // Q tiles loaded so far, per tile
+            const int kv_group = a.kv_group > 1 ? a.kv_group : 1;
             bool ok = true;
             for (int s = 0; ok; ++s) {
                 int head, q0, n_of[2], nmax;
                 if (!sub_item(s, head, q0, n_of, nmax)) break;
+                const int kv_head = head / kv_group;   // grouped-query attention: kv_group query heads per K/V head
                 for (int i = 0; i < 2 && ok; ++i) {
                     if (n_of[i] == 0) continue;
                     // the tile's Q buffer is free once the last score MMA of its previous sub-item has completed
@@ -278,8 +280,8 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     }
                     tc_mbar_expect_tx(&bars[B_KVFULL + slot], KV_BYTES);
                     const CUtensorMap* map = (l & 1) ? &map_v : &map_k;
-                    at_tma_load_4d(sKV + slot * KV_BYTES, map, &bars[B_KVFULL + slot], 0, head, 0, (int)page);
-                    at_tma_load_4d(sKV + slot * KV_BYTES + KV_BLK, map, &bars[B_KVFULL + slot], 64, head, 0, (int)page);
+                    at_tma_load_4d(sKV + slot * KV_BYTES, map, &bars[B_KVFULL + slot], 0, kv_head, 0, (int)page);
+                    at_tma_load_4d(sKV + slot * KV_BYTES + KV_BLK, map, &bars[B_KVFULL + slot], 64, kv_head, 0, (int)page);
                 }
             }
         }
@@ -461,9 +463,9 @@ ktb_attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 break;
             }
             tc_fence_after_sync();
-            if (g == 0 && tile == 1 && at_stagger > 0) {
+            if (g == 0 && tile == 1) {
                 const long long t0 = clock64();
-                while (clock64() - t0 < at_stagger) {}
+                while (clock64() - t0 < AT_STAGGER) {}
             }
             // this thread's part of the score row moves to registers in one go
             uint32_t v[NCH][CW];
@@ -578,10 +580,10 @@ static int launch_attn(ktb_ctx* ctx, const ktb_attn_args& a, const CUtensorMap& 
                        const CUtensorMap& mv) {
     constexpr int AT_STAGES = BN == 128 ? 4 : 8;
     constexpr size_t SMEM = 2 * AT_Q_BYTES + AT_STAGES * (size_t)(BN * AT_D * 2) + 2 * 2 * 2 * AT_BM * 4 + 1024 + 512;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[KTB_MAX_DEVICES] = {};     // the attribute is per device
+    if (!attr_set[ctx->device & (KTB_MAX_DEVICES - 1)]) {
         KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_attention_fwd_kernel<BN, TPR, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM));
-        attr_set = true;
+        attr_set[ctx->device & (KTB_MAX_DEVICES - 1)] = true;
     }
     const int q_pairs = (a.seq_q + 2 * AT_BM - 1) / (2 * AT_BM);
     // an item = the tile pairs (q_pairs - 1 - r, r) of one head; one persistent CTA per SM walks them
@@ -615,31 +617,16 @@ extern "C" int ktb_launch_attention_fwd(ktb_ctx* ctx, const ktb_attn_args* args)
             return ktb_fail(ctx, KTB_E_CUDA, "attention_fwd", "cuTensorMapEncodeTiled(Q) failed");
     }
     for (int which = 0; which < 2; ++which) {
-        const uint64_t dims[4] = {AT_D, (uint64_t)a.heads, (uint64_t)a.page, (uint64_t)a.n_pages_total};
+        const int kvg = a.kv_group > 1 ? a.kv_group : 1;
+        const uint64_t dims[4] = {AT_D, (uint64_t)((a.heads + kvg - 1) / kvg), (uint64_t)a.page, (uint64_t)a.n_pages_total};
         const uint64_t str[3] = {(uint64_t)a.kv_head_stride * 2, (uint64_t)a.kv_row_stride * 2, (uint64_t)a.kv_page_stride * 2};
         const uint32_t box[4] = {64, 1, (uint32_t)a.page, 1};
         if (!tc_make_map_f16(which ? &mv : &mk, base + (which ? a.v_off : a.k_off), 4, dims, str, box))
             return ktb_fail(ctx, KTB_E_CUDA, "attention_fwd", "cuTensorMapEncodeTiled(K/V) failed");
     }
-    if (const char* e = getenv("KTB_ATT_STAGGER")) {
-        const int v = atoi(e);
-        cudaMemcpyToSymbol(at_stagger, &v, sizeof(int));
-    }
-    int tpr = 1;                        // softmax threads per query row (experiments: KTB_ATT_TPR=2)
-    if (const char* e = getenv("KTB_ATT_TPR")) tpr = atoi(e) == 2 ? 2 : 1;
     switch (a.page) {
-        case 32: return launch_attn<32, 2>(ctx, a, mq, mk, mv);
-        case 64: return tpr == 1 ? launch_attn<64, 1, 1>(ctx, a, mq, mk, mv) : launch_attn<64, 2>(ctx, a, mq, mk, mv);
-        default: {
-            int poly = 1;                       // pairs of every 4 whose exp2 runs on the FMA pipe
-            if (const char* e = getenv("KTB_ATT_POLY")) poly = atoi(e);
-            if (tpr == 2) return launch_attn<128, 2>(ctx, a, mq, mk, mv);
-            switch (poly) {
-                case 1: return launch_attn<128, 1, 1>(ctx, a, mq, mk, mv);
-                case 2: return launch_attn<128, 1, 2>(ctx, a, mq, mk, mv);
-                case 3: return launch_attn<128, 1, 3>(ctx, a, mq, mk, mv);
-                default: return launch_attn<128, 1, 0>(ctx, a, mq, mk, mv);
-            }
-        }
+        case 32: return launch_attn<32, 2>(ctx, a, mq, mk, mv);      // two softmax threads per row: a step is only 32 columns
+        case 64: return launch_attn<64, 1, 1>(ctx, a, mq, mk, mv);
+        default: return launch_attn<128, 1, 1>(ctx, a, mq, mk, mv);
     }
 }

@@ -9,6 +9,7 @@
 #include "../../include/ktir_b200.h"
 
 #define KTB_NUM_EVENTS 64
+#define KTB_MAX_DEVICES 64            // power of two; per-device launch state is indexed by device & (this - 1)
 #define KTB_FLUSH_BYTES (256u << 20)   // > 126 MB L2
 
 struct ktb_ctx {

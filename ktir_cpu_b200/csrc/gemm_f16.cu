@@ -168,11 +168,11 @@ ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <int BN>
 static int launch_gemm(ktb_ctx* ctx, const ktb_gemm_args& a, const CUtensorMap& ma, const CUtensorMap& mb) {
     using Cfg = GemmCfg<BN>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[KTB_MAX_DEVICES] = {};     // the attribute is per device
+    if (!attr_set[ctx->device & (KTB_MAX_DEVICES - 1)]) {
         KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_gemm_f16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)Cfg::SMEM));
-        attr_set = true;
+        attr_set[ctx->device & (KTB_MAX_DEVICES - 1)] = true;
     }
     const int tiles_m = (a.M + GEMM_BM - 1) / GEMM_BM, tiles_n = (a.N + BN - 1) / BN;
     int grid = tiles_m * tiles_n;

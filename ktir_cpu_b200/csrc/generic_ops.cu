@@ -10,7 +10,7 @@ enum { G_MOV, G_ADD, G_SUB, G_MUL, G_DIV, G_REM, G_MAX, G_MAXNUM, G_MIN, G_MINNU
        G_LOG2, G_LOG1P, G_SQRT, G_RSQRT, G_TANH, G_SIN, G_COS, G_CEIL, G_FLOOR, G_FMA, G_POW, G_SELECT,
        G_CMP_EQ, G_CMP_NE, G_CMP_LT, G_CMP_LE, G_CMP_GT, G_CMP_GE, G_CMP_ORD, G_CMP_UNO, G_CMP_TRUE, G_CMP_FALSE,
        G_AND, G_OR, G_XOR, G_SHL, G_SHR, G_DIVT, G_REMT, G_DIVF, G_CDIV, G_BITCAST, G_CMP_UNE, G_CMP_UEQ,
-       G_CMP_ULT, G_CMP_ULE, G_CMP_UGT, G_CMP_UGE };
+       G_CMP_ULT, G_CMP_ULE, G_CMP_UGT, G_CMP_UGE, G_SIGN };
 
 static __device__ __forceinline__ bool g_is_float(int dt) { return dt == KTB_F16 || dt == KTB_F32; }
 static __host__ __device__ __forceinline__ int g_size(int dt) {
@@ -79,10 +79,11 @@ static __device__ __forceinline__ float g_fop(int op, float a, float b, float c)
         case G_MUL: return a * b;
         case G_DIV: return a / b;
         case G_REM: return fmodf(a, b);
-        case G_MAX: return (a != a || b != b) ? nan : fmaxf(a, b);
-        case G_MAXNUM: return fmaxf(a, b);
-        case G_MIN: return (a != a || b != b) ? nan : fminf(a, b);
-        case G_MINNUM: return fminf(a, b);
+        // NumPy's selection rules: the first operand wins a tie (max(-0, +0) = -0)
+        case G_MAX: return (a >= b || a != a) ? a : b;
+        case G_MAXNUM: return (a >= b || b != b) ? a : b;
+        case G_MIN: return (a <= b || a != a) ? a : b;
+        case G_MINNUM: return (a <= b || b != b) ? a : b;
         case G_NEG: return -a;
         case G_ABS: return fabsf(a);
         case G_EXP: return expf(a);
@@ -98,6 +99,7 @@ static __device__ __forceinline__ float g_fop(int op, float a, float b, float c)
         case G_FLOOR: return floorf(a);
         case G_FMA: return __fadd_rn(__fmul_rn(a, b), c);
         case G_POW: return powf(a, b);
+        case G_SIGN: return a > 0.f ? 1.f : a < 0.f ? -1.f : a == 0.f ? 0.f : a;   // np.sign: +0 for either zero, NaN stays
         default: return a;
     }
 }

@@ -226,12 +226,14 @@ static __device__ __forceinline__ void sm_row_exp(const uint4& raw, float mxs, f
     }
 }
 
-// RECOMP: the row stays in registers as packed f16 (NV x 4 registers) and exp is evaluated twice,
-// once for the sum and once for the output (same instruction sequence, so the same bits), instead
-// of holding NV x 8 f32 values; half the registers, twice the resident rows per SM.
-template <int NV, bool MAXNUM, bool RECOMP, bool PREF>
-__global__ void __launch_bounds__(256, RECOMP ? (NV >= 16 ? 2 : NV >= 8 ? (PREF ? 2 : 4) : (PREF ? 4 : 6)) : (NV >= 8 ? 2 : 3))
-ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows, int pack_ok) {
+// The row stays in registers as packed f16 (NV x 4 registers) instead of NV x 8 f32 values: half
+// the registers, twice the resident rows per SM.  f16 output: exp is evaluated once and parked as
+// f16 (x 2^15) in the registers the input occupied (one extra rounding, <= 2^-11 relative, inside
+// the f16 tolerance of this op); f32 output evaluates exp twice (same instruction sequence, so
+// the same bits) and loses nothing.
+template <int NV, bool MAXNUM>
+__global__ void __launch_bounds__(256, NV >= 16 ? 2 : NV >= 8 ? 4 : 6)
+ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows) {
     __shared__ float xmax[8], xsum[8];            // one slot per warp of the CTA
     const int groups = 256 / T;
     const int group = threadIdx.x / T;
@@ -241,18 +243,7 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows,
     const __half* in16 = reinterpret_cast<const __half*>(a.arena);
     const int w = T < 32 ? T : 32;
     const int64_t n_iter = (total_rows + groups - 1) / groups;
-    // f16 output: exp is evaluated once and parked as f16 (one extra rounding, <= 2^-11 relative,
-    // inside the f16 tolerance of this op); f32 output keeps full precision by evaluating exp twice
-    const bool pack = RECOMP && !PREF && a.out_dtype == KTB_F16 && pack_ok;
-    uint4 nxt[PREF ? NV : 1];
-    if (PREF && blockIdx.x < n_iter) {
-        const int64_t row = blockIdx.x * (int64_t)groups + group < total_rows ? blockIdx.x * (int64_t)groups + group : 0;
-        const int64_t item = row / a.rows_per_item;
-        const uint4* src = reinterpret_cast<const uint4*>(in16 + a.dev_item_offsets[item * 2] +
-                                                          (row - item * a.rows_per_item) * a.in_row_stride) + t;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) nxt[PREF ? j : 0] = __ldcs(src + (int64_t)j * T);
-    }
+    const bool pack = a.out_dtype == KTB_F16;
     for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
         const bool live = it * groups + group < total_rows;
         const int64_t row = live ? it * groups + group : 0;
@@ -263,23 +254,8 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows,
         const uint4* src = reinterpret_cast<const uint4*>(in16 + in_off) + t;
 
         uint4 raw[NV];
-        if (PREF) {
-            // this row was requested one iteration ago; request the next one before any arithmetic
 #pragma unroll
-            for (int j = 0; j < NV; ++j) raw[j] = nxt[PREF ? j : 0];
-            const int64_t nit = it + gridDim.x;
-            if (nit < n_iter) {
-                const int64_t nrow = nit * groups + group < total_rows ? nit * groups + group : 0;
-                const int64_t nitem = nrow / a.rows_per_item;
-                const uint4* nsrc = reinterpret_cast<const uint4*>(in16 + a.dev_item_offsets[nitem * 2] +
-                                                                   (nrow - nitem * a.rows_per_item) * a.in_row_stride) + t;
-#pragma unroll
-                for (int j = 0; j < NV; ++j) nxt[PREF ? j : 0] = __ldcs(nsrc + (int64_t)j * T);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < NV; ++j) raw[j] = __ldcs(src + (int64_t)j * T);
-        }
+        for (int j = 0; j < NV; ++j) raw[j] = __ldcs(src + (int64_t)j * T);
 
         __half2 m2 = *reinterpret_cast<const __half2*>(&raw[0].x);
 #pragma unroll
@@ -304,26 +280,17 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows,
         mx = sm_max<MAXNUM>(mx, a.max_init);
         const float mxs = mx * 1.4426950408889634f;
 
-        float p[RECOMP ? 1 : NV][8];
         float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __half22float2(h[i]);
-                p[RECOMP ? 0 : j][2 * i] = sm_ex2(__fmaf_rn(f.x, 1.4426950408889634f, -mxs));
-                p[RECOMP ? 0 : j][2 * i + 1] = sm_ex2(__fmaf_rn(f.y, 1.4426950408889634f, -mxs));
-            }
-            const float(&q)[8] = p[RECOMP ? 0 : j];
+            float q[8];
+            sm_row_exp(raw[j], mxs, q);
             s0 += q[0] + q[1];
             s1 += q[2] + q[3];
             s2 += q[4] + q[5];
             s3 += q[6] + q[7];
             if (pack) {
-                // keep exp(x - max) * 2^15 as f16 in the registers the input occupied (0 < p <= 1, so the
-                // scaled value keeps 11 significant bits down to p = 2^-29): the output pass then needs
-                // neither the input nor a second exp
+                // 0 < p <= 1, so p * 2^15 keeps 11 significant bits down to p = 2^-29
                 __half2* hw = reinterpret_cast<__half2*>(&raw[j]);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) hw[i] = __floats2half2_rn(q[2 * i] * 32768.f, q[2 * i + 1] * 32768.f);
@@ -340,40 +307,31 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows,
         }
         const float inv = 1.0f / (sum + a.sum_init);
         if (!live) continue;
-        if (RECOMP && !pack) {
-            // opaque to the optimiser: otherwise the converted values of the first evaluation are
-            // kept alive for the second one, which is the register footprint this variant avoids
-#pragma unroll
-            for (int j = 0; j < NV; ++j)
-                asm volatile("" : "+r"(raw[j].x), "+r"(raw[j].y), "+r"(raw[j].z), "+r"(raw[j].w));
-        }
-        if (a.out_dtype == KTB_F16) {
+        if (pack) {
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + out_off) + t;
-#pragma unroll
             const float inv_s = inv * (1.0f / 32768.f);
+#pragma unroll
             for (int j = 0; j < NV; ++j) {
                 uint4 o;
                 __half2* h = reinterpret_cast<__half2*>(&o);
-                if (pack) {
-                    const __half2* hp = reinterpret_cast<const __half2*>(&raw[j]);
+                const __half2* hp = reinterpret_cast<const __half2*>(&raw[j]);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __half22float2(hp[i]);
-                        h[i] = __floats2half2_rn(f.x * inv_s, f.y * inv_s);
-                    }
-                } else {
-                    if (RECOMP) sm_row_exp(raw[j], mxs, p[0]);
-                    const float(&pj)[8] = p[RECOMP ? 0 : j];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(pj[2 * i] * inv, pj[2 * i + 1] * inv);
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(hp[i]);
+                    h[i] = __floats2half2_rn(f.x * inv_s, f.y * inv_s);
                 }
                 __stcs(dst + (int64_t)j * T, o);
             }
         } else {
+            // opaque to the optimiser: otherwise the converted values of the first evaluation are
+            // kept alive for the second one, which is the register footprint this form avoids
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+                asm volatile("" : "+r"(raw[j].x), "+r"(raw[j].y), "+r"(raw[j].z), "+r"(raw[j].w));
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
-                if (RECOMP) sm_row_exp(raw[j], mxs, p[0]);
-                const float(&pj)[8] = p[RECOMP ? 0 : j];
+                float pj[8];
+                sm_row_exp(raw[j], mxs, pj);
                 float* q = reinterpret_cast<float*>(a.arena) + out_off + ((int64_t)j * T + t) * 8;
                 __stcs(reinterpret_cast<float4*>(q), make_float4(pj[0] * inv, pj[1] * inv, pj[2] * inv, pj[3] * inv));
                 __stcs(reinterpret_cast<float4*>(q + 4), make_float4(pj[4] * inv, pj[5] * inv, pj[6] * inv, pj[7] * inv));
@@ -390,19 +348,9 @@ static void launch_softmax(ktb_ctx* ctx, const ktb_softmax_args& a, int T, int64
     if (blocks > n_iter) blocks = n_iter;
     const bool mn = a.max_is_maxnum != 0, r16 = a.f16_arith != 0;
     if (a.in_dtype == KTB_F16 && !r16) {
-        int mode = 1;                  // 0: exp kept in registers, 1: exp evaluated twice, 2: + next-row prefetch
-        if (const char* e = getenv("KTB_SOFTMAX_RECOMP")) mode = atoi(e);
-        if (NV >= 16 && mode == 0) mode = 1;
-        int per_sm = mode == 2 ? (NV >= 8 ? 2 : 4) : 8;
-        if (const char* e = getenv("KTB_SOFTMAX_CTAS")) per_sm = atoi(e) > 0 ? atoi(e) : per_sm;
-        if (mode) blocks = n_iter < (int64_t)ctx->sm_count * per_sm ? n_iter : (int64_t)ctx->sm_count * per_sm;
-        int pack_ok = 1;
-        if (const char* e = getenv("KTB_SOFTMAX_PACK")) pack_ok = atoi(e) != 0;
-#define KTB_SMF(MN, RC, PF) ktb_row_softmax_fast_kernel<NV, MN, RC, PF><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows, pack_ok)
-        if (mode == 2 && NV <= 8) { if constexpr (NV <= 8) { if (mn) KTB_SMF(true, true, true); else KTB_SMF(false, true, true); } }
-        else if (mode) { if (mn) KTB_SMF(true, true, false); else KTB_SMF(false, true, false); }
-        else if constexpr (NV <= 8) { if (mn) KTB_SMF(true, false, false); else KTB_SMF(false, false, false); }
-#undef KTB_SMF
+        blocks = n_iter < (int64_t)ctx->sm_count * 8 ? n_iter : (int64_t)ctx->sm_count * 8;
+        if (mn) ktb_row_softmax_fast_kernel<NV, true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows);
+        else ktb_row_softmax_fast_kernel<NV, false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows);
         return;
     }
     if constexpr (NV <= 8) {
@@ -426,11 +374,7 @@ extern "C" int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args
     if ((a.in_row_stride % 8) || (a.out_row_stride % 8))
         return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_softmax", "row strides must be multiples of 8 elements");
     const int vecs = a.cols / 8;
-    int per_thread = 8;               // vectors per thread (tunable for experiments)
-    if (const char* e = getenv("KTB_SOFTMAX_NV")) {
-        const int v = atoi(e);
-        if (v == 1 || v == 2 || v == 4 || v == 8 || v == 16) per_thread = v;
-    }
+    const int per_thread = 8;         // 16-byte vectors per thread
     int T = vecs / per_thread;
     if (T < 1) T = 1;
     if (T > 256) T = 256;             // ... unless the row is wider than 16384 elements

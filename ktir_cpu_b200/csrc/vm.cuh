@@ -15,10 +15,12 @@ static __device__ __forceinline__ float ktb_vm_apply(int op, float a, float b, f
         case KTB_VM_SUB: return a - b;
         case KTB_VM_MUL: return a * b;
         case KTB_VM_DIV: return a / b;
-        case KTB_VM_MAX: return (a != a || b != b) ? __int_as_float(0x7fc00000) : fmaxf(a, b);
-        case KTB_VM_MAXNUM: return fmaxf(a, b);
-        case KTB_VM_MIN: return (a != a || b != b) ? __int_as_float(0x7fc00000) : fminf(a, b);
-        case KTB_VM_MINNUM: return fminf(a, b);
+        // NumPy's selection rules (np.maximum / np.fmax / np.minimum / np.fmin on half and float): the
+        // first operand wins a tie, so max(-0, +0) = -0 and max(+0, -0) = +0
+        case KTB_VM_MAX: return (a >= b || a != a) ? a : b;
+        case KTB_VM_MAXNUM: return (a >= b || b != b) ? a : b;
+        case KTB_VM_MIN: return (a <= b || a != a) ? a : b;
+        case KTB_VM_MINNUM: return (a <= b || b != b) ? a : b;
         case KTB_VM_NEG: return -a;
         case KTB_VM_ABS: return fabsf(a);
         case KTB_VM_EXP: return expf(a);
@@ -139,8 +141,8 @@ static __device__ __noinline__ float4 ktb_vm_run_smem4(const ktb_vm_program& pro
             case KTB_VM_SUB: KTB_VM4(a - b)
             case KTB_VM_MUL: KTB_VM4(a * b)
             case KTB_VM_DIV: KTB_VM4(a / b)
-            case KTB_VM_MAXNUM: KTB_VM4(fmaxf(a, b))
-            case KTB_VM_MINNUM: KTB_VM4(fminf(a, b))
+            case KTB_VM_MAXNUM: KTB_VM4((a >= b || b != b) ? a : b)
+            case KTB_VM_MINNUM: KTB_VM4((a <= b || b != b) ? a : b)
             case KTB_VM_NEG: KTB_VM4(-a)
             case KTB_VM_ABS: KTB_VM4(fabsf(a))
             default: KTB_VM4(ktb_vm_apply(op.opcode & 0xff, a, b, c, imm))

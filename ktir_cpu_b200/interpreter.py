@@ -80,7 +80,7 @@ class Session:
 
     def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
                  scalars: Dict[str, Any], latency: bool = False, shard: Optional[Tuple[int, int]] = None,
-                 arena_ptr: Optional[int] = None, seeded: Sequence[Tuple[int, int, str]] = ()):
+                 arena_ptr: Optional[int] = None, seeded: Sequence[Tuple[int, int, str]] = (), fused: bool = True):
         """``shard = (rank, world)`` plans only this rank's part of the kernel (see ``sharded.py``);
         ``arena_ptr`` places the arena in caller-owned device memory of at least ``arena_size(tensors)`` bytes;
         ``seeded`` = (byte address, nbytes, dtype) of memory written through ``interp.memory.hbm`` at fixed
@@ -123,7 +123,7 @@ class Session:
                     row_shard = shard          # every core runs; each rank applies the rows it owns
                 else:
                     stores = Tracer(func, scalars, ptrs, core_range=core_slice(tracer.ncores, *shard)).run()
-            self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard)
+            self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard, fused=fused)
         except Exception:
             if self.own_arena:
                 dev.free(self.arena)
@@ -241,12 +241,17 @@ class KTIRInterpreter:
     """Executes KTIR functions on a B200 through ``libktir_b200`` (no CPU fallback)."""
 
     def __init__(self, latency_config=None, trace_latency: bool = False,
-                 parser: Optional[KTIRParserBase] = None, device: int = 0, max_sessions: int = 8):
+                 parser: Optional[KTIRParserBase] = None, device: int = 0, max_sessions: int = 8,
+                 fused_kernels: bool = True):
+        """The first three arguments are the reference's (ktir_cpu/interpreter.py:46-79).  ``device`` is the
+        CUDA device index; ``fused_kernels=False`` runs every statement step by step on the device
+        instead of through the fused kernels (slow; a cross-check)."""
         self.module: Optional[IRModule] = None
         self._parser = parser
         self._latency_config = latency_config
         self._trace_latency = trace_latency
         self._device_index = device
+        self._fused = fused_kernels
         self._dev: Optional[R.Device] = None
         self._sessions: Dict[Any, Session] = {}
         self._max_sessions = max_sessions
@@ -335,7 +340,7 @@ class KTIRInterpreter:
                 old = next(iter(self._sessions))
                 self._sessions.pop(old).close()
             sess = Session(self.device, func, tensors, scalars, latency=self._latency_config is not None,
-                           seeded=seeded)
+                           seeded=seeded, fused=self._fused)
             self._sessions[key] = sess
         return sess, kwargs
 

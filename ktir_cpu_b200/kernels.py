@@ -89,6 +89,58 @@ def vector_add(n: int = 4096, block: int = 128, cores: int = 32, dtype: str = "f
             + view("output_view", "output_ptr", [n], dtype) + loop + "    return\n  }\n}\n")
 
 
+# name -> (op text with {x} {y} {t} placeholders, result is a tile of the input dtype)
+ELEMENTWISE_OPS = {
+    "add": "arith.addf {x}, {y} : {t}", "sub": "arith.subf {x}, {y} : {t}", "mul": "arith.mulf {x}, {y} : {t}",
+    "div": "arith.divf {x}, {y} : {t}", "maximum": "arith.maximumf {x}, {y} : {t}",
+    "maxnum": "arith.maxnumf {x}, {y} : {t}", "minimum": "arith.minimumf {x}, {y} : {t}",
+    "minnum": "arith.minnumf {x}, {y} : {t}", "neg": "arith.negf {x} : {t}", "abs": "math.absf {x} : {t}",
+    "sqrt": "math.sqrt {x} : {t}", "exp": "math.exp {x} : {t}", "log": "math.log {x} : {t}",
+    "tanh": "math.tanh {x} : {t}", "rsqrt": "math.rsqrt {x} : {t}", "sin": "math.sin {x} : {t}",
+    "cos": "math.cos {x} : {t}", "log2": "math.log2 {x} : {t}", "erf": "math.erf {x} : {t}",
+}
+
+
+def elementwise_suite(ops: Sequence[str], n: int = 4096, block: int = 128, cores: int = 4, dtype: str = "f16",
+                      select_pred: str = "") -> str:
+    """One kernel, one output tensor per entry of ``ops`` (names of ELEMENTWISE_OPS): out_<op> = op(x, y)
+    on blocks of ``block`` elements, core c taking blocks c, c + cores, ...  ``select_pred`` (an
+    ``arith.cmpf`` predicate such as "olt") adds out_select = select(cmpf pred x y, x, y), and
+    ``dtype`` "f16" also adds out_ext_add = truncf(extf x + extf y): the cast ops with an f32 op between."""
+    nblk = n // block
+    assert nblk * block == n and nblk % cores == 0
+    t, at = f"tensor<{block}x{dtype}>", f"!ktdp.access_tile<{block}xindex>"
+    names = [f"out_{o}" for o in ops] + (["out_select"] if select_pred else []) + (["out_ext_add"] if dtype == "f16" else [])
+    ind = "      "
+    body = (tile("x_tile", "x_view", ["%off"], [block], [n], dtype, ind) + tile("y_tile", "y_view", ["%off"], [block], [n], dtype, ind)
+            + f"{ind}%x = ktdp.load %x_tile : {at} -> {t}\n{ind}%y = ktdp.load %y_tile : {at} -> {t}\n")
+    for o in ops:
+        body += f"{ind}%r_{o} = " + ELEMENTWISE_OPS[o].format(x="%x", y="%y", t=t) + "\n"
+    if select_pred:
+        body += (f"{ind}%keep = arith.cmpf {select_pred}, %x, %y : {t}\n"
+                 f"{ind}%r_select = arith.select %keep, %x, %y : tensor<{block}xi1>, {t}\n")
+    if dtype == "f16":
+        t32 = f"tensor<{block}xf32>"
+        body += (f"{ind}%x32 = arith.extf %x : {t} to {t32}\n{ind}%y32 = arith.extf %y : {t} to {t32}\n"
+                 f"{ind}%s32 = arith.addf %x32, %y32 : {t32}\n{ind}%r_ext_add = arith.truncf %s32 : {t32} to {t}\n")
+    for nm in names:
+        body += tile(f"{nm}_tile", f"{nm}_view", ["%off"], [block], [n], dtype, ind)
+        body += f"{ind}ktdp.store %r_{nm[4:]}, %{nm}_tile : {t}, {at}\n"
+    s = (f"module {{\n  func.func @elementwise_kernel(%x_ptr: index, %y_ptr: index"
+         + "".join(f", %{nm}_ptr: index" for nm in names) + f") attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n    %c1 = arith.constant 1 : index\n"
+         f"    %blk = arith.constant {block} : index\n    %per_core = arith.constant {nblk // cores} : index\n"
+         f"    %ncores = arith.constant {cores} : index\n")
+    s += view("x_view", "x_ptr", [n], dtype) + view("y_view", "y_ptr", [n], dtype)
+    for nm in names:
+        s += view(f"{nm}_view", f"{nm}_ptr", [n], dtype)
+    s += (f"    scf.for %i = %c0 to %per_core step %c1 {{\n"
+          f"      %b0 = arith.muli %i, %ncores : index\n      %b = arith.addi %b0, %core_id : index\n"
+          f"      %off = arith.muli %b, %blk : index\n" + body + "      scf.yield\n    }\n    return\n  }\n}\n")
+    return s
+
+
 def softmax_rows(n_rows: int = 8192, n_cols: int = 4096, cores: int = 32, rows_per_iter: int = 8,
                  f32_stats: bool = True) -> str:
     """Row softmax; core c owns rows [c*R, (c+1)*R), R = n_rows/cores, ``rows_per_iter`` at a time.
@@ -417,6 +469,152 @@ def causal_attention(seq: int = 2048, heads: int = 256, head_dim: int = 128, til
           f"{f([tm, hd], 'f16')} into {f([tm, 1, hd], 'f16')}\n")
     s += tile("o_tile", "output", ["%q_row0", "%pid_h", "%c0"], [tm, 1, hd], qv, "f16")
     s += (f"    ktdp.store %o3, %o_tile : {f([tm, 1, hd], 'f16')}, !ktdp.access_tile<{_xs([tm, 1, hd], 'index')}>\n"
+          f"    return\n  }}\n}}\n")
+    return s
+
+
+def _generic(res: str, ins, out_shape, body_args, body, indent="      ") -> str:
+    """``linalg.generic`` over parallel dims: ``ins`` = [(ssa name, shape)], a row vector broadcasts
+    along the last dim of ``out_shape``; ``body`` = lines of the region ending in the yielded name."""
+    nd = len(out_shape)
+    dims = ", ".join(f"d{i}" for i in range(nd))
+    maps = [f"affine_map<({dims}) -> ({', '.join(f'd{i}' for i in range(len(shp)))})>" for _, shp in ins]
+    maps.append(_ident(nd))
+    f = lambda shp: f"tensor<{_xs(shp, 'f32')}>"   # noqa: E731
+    lines = [f"{indent}%{res}_out = tensor.empty() : {f(out_shape)}",
+             f"{indent}%{res} = linalg.generic {{",
+             f"{indent}    indexing_maps = [{', '.join(maps)}],",
+             f"{indent}    iterator_types = [{', '.join(['\"parallel\"'] * nd)}]}}",
+             f"{indent}    ins({', '.join('%' + n for n, _ in ins)} : {', '.join(f(shp) for _, shp in ins)})",
+             f"{indent}    outs(%{res}_out : {f(out_shape)}) {{",
+             f"{indent}  ^bb0({', '.join(f'%{a} : f32' for a in body_args)}, %{res}_o : f32):"]
+    lines += [f"{indent}    {ln}" for ln in body[:-1]]
+    lines += [f"{indent}    linalg.yield %{body[-1]} : f32", f"{indent}}} -> {f(out_shape)}"]
+    return "\n".join(lines) + "\n"
+
+
+def paged_attention(num_tokens: int = 2048, context_len: int = 2048, num_query_heads: int = 256,
+                    num_kv_heads: int = 256, head_dim: int = 128, block_size: int = 128, block_q: int = 128) -> str:
+    """Paged attention with online softmax, the kernel shape of the reference's own generator
+    (notebooks/demo_gen_mlir.py:724-1012; examples/triton-ktir/paged_attention.mlir:163-433): same
+    function name, arguments and op sequence, so either text drives the same device kernel.
+
+    Grid = [num_tokens / block_q, num_kv_heads].  A core owns ``block_q`` query positions of the
+    ``num_query_heads / num_kv_heads`` query heads that share its K/V head: its tile is
+    [block_q, group, head_dim], collapsed position-major to [block_q * group, head_dim].  Per KV page
+    (``block_size`` rows, reached through the block table): S = scale * Q K^T, masked to
+    kv position <= context_len + query position (row / group inside a ``linalg.generic``),
+    m = max(M, rowmax S), P = exp(S - m), alpha = exp(M - m), acc = acc * alpha + P V,
+    L = L * alpha + rowsum P with M = -inf, L = 1.0 to start; O = acc / L as f16.  With an identity
+    block table, ``context_len = 0`` and ``num_tiles = num_tokens / block_size`` this is dense causal
+    attention over [num_tokens, heads, head_dim] (a batch folds into the heads)."""
+    grp = num_query_heads // num_kv_heads
+    bq, bs, hd, nt = block_q, block_size, head_dim, num_tokens
+    bm = grp * bq
+    nb = (context_len + bs - 1) // bs
+    qv, cv = [nt, num_query_heads, hd], [nb, bs, num_kv_heads, hd]
+    f = lambda shp, dt="f32": f"tensor<{_xs(shp, dt)}>"   # noqa: E731
+    q3, at3 = [bq, grp, hd], f"!ktdp.access_tile<{_xs([bq, grp, hd], 'index')}>"
+
+    def kv_tile(name, vw):
+        return (f"      %{name} = ktdp.construct_indirect_access_tile\n"
+                f"          intermediate_variables(%d0, %d1, %d2, %d3)\n"
+                f"          %{vw}[ind(%block_tables[%c0, %bt_idx + %d0]), (%d1), (%pid1 + %d2), (%d3)] {{\n"
+                f"        variables_space_set = {_box([1, bs, 1, hd])},\n"
+                f"        variables_space_order = {_ident(4)}\n"
+                f"      }} : memref<{_xs(cv, 'f16')}>, memref<1x{nb}xi32> -> !ktdp.access_tile<{_xs([1, bs, 1, hd], 'index')}>\n")
+
+    s = (f"module {{\n  func.func @paged_attention_kernel(%output_ptr: index, %query_ptr: index, %key_cache_ptr: index,\n"
+         f"      %value_cache_ptr: index, %block_tables_ptr: index, %cur_batch_start_index: index,\n"
+         f"      %block_table_offset: index, %num_tiles: index, %context_len: index, %scale: f32)\n"
+         f"      attributes {{grid = [{nt // bq}, {num_kv_heads}]}} {{\n"
+         f"    %pid0, %pid1 = ktdp.get_compute_tile_id : index, index\n"
+         f"    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n"
+         f"    %c_bq = arith.constant {bq} : index\n"
+         f"    %c_grp = arith.constant {grp} : index\n"
+         f"    %c_bs = arith.constant {bs} : index\n"
+         f"    %q_rel0 = arith.muli %pid0, %c_bq : index\n"
+         f"    %q_row0 = arith.addi %cur_batch_start_index, %q_rel0 : index\n"
+         f"    %q_head0 = arith.muli %pid1, %c_grp : index\n"
+         f"    %ninf_bits = arith.constant 0xFF800000 : i32\n"
+         f"    %ninf = arith.bitcast %ninf_bits : i32 to f32\n"
+         f"    %zero = arith.constant 0.0 : f32\n"
+         f"    %one = arith.constant 1.0 : f32\n")
+    s += view("query", "query_ptr", qv, "f16") + view("output", "output_ptr", qv, "f16")
+    s += view("key_cache", "key_cache_ptr", cv, "f16") + view("value_cache", "value_cache_ptr", cv, "f16")
+    s += view("block_tables", "block_tables_ptr", [1, nb], "i32")
+    s += tile("q_tile", "query", ["%q_row0", "%q_head0", "%c0"], q3, qv, "f16")
+    s += (f"    %q3 = ktdp.load %q_tile : {at3} -> {f(q3, 'f16')}\n"
+          f"    %q16 = tensor.collapse_shape %q3 [[0, 1], [2]] : {f(q3, 'f16')} into {f([bm, hd], 'f16')}\n"
+          f"    %q = arith.extf %q16 : {f([bm, hd], 'f16')} to {f([bm, hd])}\n"
+          f"    %m_init = tensor.splat %ninf : {f([bm])}\n"
+          f"    %l_init = tensor.splat %one : {f([bm])}\n"
+          f"    %acc_init = tensor.splat %zero : {f([bm, hd])}\n"
+          f"    %m_fin, %l_fin, %acc_fin = scf.for %j = %c0 to %num_tiles step %c1\n"
+          f"        iter_args(%m_run = %m_init, %l_run = %l_init, %acc = %acc_init)\n"
+          f"        -> ({f([bm])}, {f([bm])}, {f([bm, hd])}) {{\n"
+          f"      %bt_idx = arith.addi %block_table_offset, %j : index\n")
+    s += kv_tile("k_tile", "key_cache") + kv_tile("v_tile", "value_cache")
+    t4, t2 = f([1, bs, 1, hd], "f16"), f([bs, hd], "f16")
+    at4 = f"!ktdp.access_tile<{_xs([1, bs, 1, hd], 'index')}>"
+    s += (f"      %k4 = ktdp.load %k_tile : {at4} -> {t4}\n"
+          f"      %v4 = ktdp.load %v_tile : {at4} -> {t4}\n"
+          f"      %k2 = tensor.collapse_shape %k4 [[0, 1], [2, 3]] : {t4} into {t2}\n"
+          f"      %v2 = tensor.collapse_shape %v4 [[0, 1], [2, 3]] : {t4} into {t2}\n"
+          f"      %kt_init = tensor.empty() : {f([hd, bs], 'f16')}\n"
+          f"      %kt16 = linalg.transpose ins(%k2 : {t2}) outs(%kt_init : {f([hd, bs], 'f16')}) permutation = [1, 0]\n"
+          f"      %kt = arith.extf %kt16 : {f([hd, bs], 'f16')} to {f([hd, bs])}\n"
+          f"      %v = arith.extf %v2 : {t2} to {f([bs, hd])}\n"
+          f"      %s_zero = tensor.splat %zero : {f([bm, bs])}\n"
+          f"      %qk = linalg.matmul ins(%q, %kt : {f([bm, hd])}, {f([hd, bs])}) "
+          f"outs(%s_zero : {f([bm, bs])}) -> {f([bm, bs])}\n"
+          f"      %scale_t = tensor.splat %scale : {f([bm, bs])}\n"
+          f"      %sc = arith.mulf %scale_t, %qk : {f([bm, bs])}\n")
+    s += _generic("masked", [("sc", [bm, bs])], [bm, bs], ["s_val"], [
+        "%r = linalg.index 0 : index",
+        "%c = linalg.index 1 : index",
+        "%q_in_tile = arith.divui %r, %c_grp : index",
+        "%q_rel = arith.addi %q_rel0, %q_in_tile : index",
+        "%q_pos = arith.addi %context_len, %q_rel : index",
+        "%col0 = arith.muli %j, %c_bs : index",
+        "%k_pos = arith.addi %col0, %c : index",
+        "%keep = arith.cmpi ule, %k_pos, %q_pos : index",
+        "%sel = arith.select %keep, %s_val, %ninf : f32",
+        "sel"])
+    s += (f"      %rmax_init = tensor.splat %ninf : {f([bm])}\n"
+          f"      %rmax = linalg.reduce ins(%masked : {f([bm, bs])}) outs(%rmax_init : {f([bm])}) dimensions = [1]\n"
+          f"          (%ra : f32, %rb : f32) {{\n"
+          f"        %rm = arith.maximumf %ra, %rb : f32\n"
+          f"        linalg.yield %rm : f32\n"
+          f"      }}\n")
+    s += _generic("m_new", [("m_run", [bm]), ("rmax", [bm])], [bm], ["mo", "mn"],
+                  ["%mm = arith.maximumf %mo, %mn : f32", "mm"])
+    s += _generic("p", [("masked", [bm, bs]), ("m_new", [bm])], [bm, bs], ["sv", "mv"],
+                  ["%sh = arith.subf %sv, %mv : f32", "%ex = math.exp %sh : f32", "ex"])
+    s += (f"      %lsum_init = tensor.splat %zero : {f([bm])}\n"
+          f"      %lsum = linalg.reduce ins(%p : {f([bm, bs])}) outs(%lsum_init : {f([bm])}) dimensions = [1]\n"
+          f"          (%sa : f32, %sb : f32) {{\n"
+          f"        %ss = arith.addf %sa, %sb : f32\n"
+          f"        linalg.yield %ss : f32\n"
+          f"      }}\n")
+    s += _generic("alpha", [("m_run", [bm]), ("m_new", [bm])], [bm], ["mo", "mn"],
+                  ["%dm = arith.subf %mo, %mn : f32", "%ea = math.exp %dm : f32", "ea"])
+    s += _generic("acc_scaled", [("acc", [bm, hd]), ("alpha", [bm])], [bm, hd], ["av", "al"],
+                  ["%sa2 = arith.mulf %av, %al : f32", "sa2"])
+    s += (f"      %acc_new = linalg.matmul ins(%p, %v : {f([bm, bs])}, {f([bs, hd])}) "
+          f"outs(%acc_scaled : {f([bm, hd])}) -> {f([bm, hd])}\n")
+    s += _generic("l_new", [("l_run", [bm]), ("alpha", [bm]), ("lsum", [bm])], [bm], ["lv", "al", "lj"],
+                  ["%la = arith.mulf %lv, %al : f32", "%ln = arith.addf %la, %lj : f32", "ln"])
+    s += (f"      scf.yield %m_new, %l_new, %acc_new : {f([bm])}, {f([bm])}, {f([bm, hd])}\n"
+          f"    }}\n")
+    s += _generic("o32", [("acc_fin", [bm, hd]), ("l_fin", [bm])], [bm, hd], ["av", "lv"],
+                  ["%dv = arith.divf %av, %lv : f32", "dv"], indent="    ")
+    s += (f"    %o16 = arith.truncf %o32 : {f([bm, hd])} to {f([bm, hd], 'f16')}\n"
+          f"    %o3 = tensor.expand_shape %o16 [[0, 1], [2]] output_shape [{bq}, {grp}, {hd}] : "
+          f"{f([bm, hd], 'f16')} into {f(q3, 'f16')}\n")
+    s += tile("o_tile", "output", ["%q_row0", "%q_head0", "%c0"], q3, qv, "f16")
+    s += (f"    ktdp.store %o3, %o_tile : {f(q3, 'f16')}, {at3}\n"
           f"    return\n  }}\n}}\n")
     return s
 

@@ -576,12 +576,16 @@ def _fused_statement(dev, st: Store, arena: ArenaMap, sid: int, row_shard):
     return stmt
 
 
-def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None) -> Plan:
-    """``row_shard = (rank, world)``: ordered scatters apply only the destination rows this rank owns."""
+def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, fused: bool = True) -> Plan:
+    """``row_shard = (rank, world)``: ordered scatters apply only the destination rows this rank owns.
+    ``fused=False`` skips the fused kernels and runs every direct store step by step (the op-by-op
+    form of the reference, ktir_cpu/interpreter.py:196-281) — a cross-check for the fused paths."""
     plan = Plan()
     for st in stores:
         sid = len(plan.statements)
         try:
+            if not fused and not isinstance(st.target, IndirectAccess):
+                raise Unsupported("fused kernels disabled")
             stmt = _fused_statement(dev, st, arena, sid, row_shard)
         except Unsupported:
             # no fused kernel fits: run the tile program step by step

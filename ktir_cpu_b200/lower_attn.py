@@ -40,28 +40,40 @@ def _ew(n: Node, op: str) -> Optional[Node]:
 
 
 def _int_affine(n: Node):
-    """Integer tile expression -> (row coefficient, column coefficient, per-point constant)."""
+    """Integer tile expression -> (row coefficient, column coefficient, per-point constant, row divisor):
+    value = (row // divisor) * row coefficient + col * column coefficient + constant.
+
+    The divisor comes from ``arith.divui %row, %c`` on the bare row index: a tile whose rows
+    interleave ``c`` query heads per position (notebooks/demo_gen_mlir.py:879-883 of the reference)."""
     n = strip_views(n)
     if n.kind == "cast":
         return _int_affine(n.args[0])
     if n.kind == "iota":
-        return (1, 0, 0) if n.attrs["dim"] == 0 else (0, 1, 0)
+        return (1, 0, 0, 1) if n.attrs["dim"] == 0 else (0, 1, 0, 1)
     if n.kind == "param":
-        return (0, 0, n.attrs["values"])
+        return (0, 0, n.attrs["values"], 1)
     if n.kind == "const":
-        return (0, 0, int(n.attrs["value"]))
+        return (0, 0, int(n.attrs["value"]), 1)
     if n.kind == "bcast":
         return _int_affine(n.args[0])
     if n.kind == "ew" and n.attrs["op"] in ("arith.addi", "arith.subi"):
         a, b = _int_affine(n.args[0]), _int_affine(n.args[1])
         s = 1 if n.attrs["op"] == "arith.addi" else -1
-        return (a[0] + s * b[0], a[1] + s * b[1], iv_bin(lambda x, y: x + s * y, a[2], b[2]))
+        if a[0] and b[0] and a[3] != b[3]:
+            raise Unsupported("attention mask mixes row indices with different divisors")
+        return (a[0] + s * b[0], a[1] + s * b[1], iv_bin(lambda x, y: x + s * y, a[2], b[2]),
+                a[3] if a[0] else b[3])
     if n.kind == "ew" and n.attrs["op"] == "arith.muli":
         a, b = _int_affine(n.args[0]), _int_affine(n.args[1])
         for x, y in ((a, b), (b, a)):
             if x[0] == 0 and x[1] == 0 and isinstance(x[2], (int, np.integer)):
                 k = int(x[2])
-                return (y[0] * k, y[1] * k, iv_bin(lambda u, v: u * v, y[2], k))
+                return (y[0] * k, y[1] * k, iv_bin(lambda u, v: u * v, y[2], k), y[3])
+    if n.kind == "ew" and n.attrs["op"] in ("arith.divui", "arith.divsi", "arith.floordivsi"):
+        a, b = _int_affine(n.args[0]), _int_affine(n.args[1])
+        if (b[0] == 0 and b[1] == 0 and isinstance(b[2], (int, np.integer)) and int(b[2]) > 0
+                and a[0] == 1 and a[1] == 0 and a[3] == 1 and isinstance(a[2], (int, np.integer)) and int(a[2]) == 0):
+            return (1, 0, 0, int(b[2]))
     raise Unsupported("attention mask is not an affine comparison of row and column indices")
 
 
@@ -176,10 +188,12 @@ class AttentionStatement(Statement):
         sel, _ = _points(store)
         P = len(sel)
         for acc in (Q, O):
-            if acc.coords is not None or len(acc.shape) != 3 or acc.shape[1] != 1 or acc.strides[2] != 1:
-                raise Unsupported("attention query/output tile must be [rows, 1, head_dim] of a [seq, heads, dim] view")
-        hd = Q.shape[2]
-        if hd != 128 or tuple(O.shape) != tuple(Q.shape) or Q.shape[0] != tm:
+            if acc.coords is not None or len(acc.shape) != 3 or acc.strides[2] != 1:
+                raise Unsupported("attention query/output tile must be [rows, heads, head_dim] of a [seq, heads, dim] view")
+        # a tile holds bq query positions x grp query heads that share one K/V head; its rows are
+        # position-major (tensor.collapse_shape [[0, 1], [2]]): tile row r = position r // grp, head r % grp
+        bq, grp, hd = Q.shape
+        if hd != 128 or tuple(O.shape) != tuple(Q.shape) or bq * grp != tm:
             raise Unsupported("attention kernel supports head_dim 128 with matching query/output tiles")
         if Q.view.dtype != "f16" or O.view.dtype != "f16" or Kc.view.dtype != "f16" or Vc.view.dtype != "f16":
             raise Unsupported("attention operands must be f16")
@@ -199,18 +213,19 @@ class AttentionStatement(Statement):
             raise Unsupported("per-core query/output base pointers")
         row0, head = decode(Q, q_off)
         orow0, ohead = decode(O, o_off)
-        if (row0 != orow0).any() or (head != ohead).any() or (row0 % tm).any():
+        if (row0 != orow0).any() or (head != ohead).any() or ((row0 - row0.min()) % bq).any() or (head % grp).any():
             raise Unsupported("attention output tiles do not mirror the query tiles")
         # the statement may cover a sub-range of the heads (a core slice of a sharded kernel)
         hmin = int(head.min())
-        head = head - hmin
-        heads = int(head.max()) + 1
+        hgrp = (head - hmin) // grp                  # K/V head of the tile, relative to the first one
+        ngrp = int(hgrp.max()) + 1
+        heads = ngrp * grp
         rmin = int(row0.min())
-        nblk = int((row0.max() - rmin) // tm) + 1
-        key = ((row0 - rmin) // tm) * heads + head
-        if P != nblk * heads or len(np.unique(key)) != P:
+        nblk = int((row0.max() - rmin) // bq) + 1
+        key = ((row0 - rmin) // bq) * ngrp + hgrp
+        if P != nblk * ngrp or len(np.unique(key)) != P:
             raise Unsupported("attention query tiles do not cover [rows x heads] exactly once")
-        seq_q = nblk * tm
+        seq_q = nblk * bq
 
         # K / V pages: one block-table entry per loop trip, rows and head_dim direct
         flat = np.arange(int(np.prod(ext)), dtype=np.int64).reshape(-1, T)[sel].reshape(-1)
@@ -234,7 +249,7 @@ class AttentionStatement(Statement):
         kbase, vbase = (int(np.asarray(x.base).reshape(-1)[0]) for x in (kview, vview))
         for f, base in ((kf, kbase), (vf, vbase)):
             hh, rem = np.divmod(f.base.reshape(P, T) - base, kview.strides[2])
-            if rem.any() or (hh != head[:, None] + hmin).any():
+            if rem.any() or (hh != (hgrp + hmin // grp)[:, None]).any():
                 raise Unsupported("K/V head does not follow the query head")
 
         delta = 0
@@ -242,10 +257,10 @@ class AttentionStatement(Statement):
             cond = m["cond"]
             if cond.kind != "ew" or cond.attrs.get("op") != "arith.cmpi" or cond.attrs.get("pred") not in ("ule", "sle"):
                 raise Unsupported("attention mask must be `kv position <= query position`")
-            kr, kc, kconst = _int_affine(cond.args[0])
-            qr, qc, qconst = _int_affine(cond.args[1])
-            if (kr, kc, qr, qc) != (0, 1, 1, 0):
-                raise Unsupported("attention mask must compare a column index with a row index")
+            kr, kc, kconst, _ = _int_affine(cond.args[0])
+            qr, qc, qconst, qdiv = _int_affine(cond.args[1])
+            if (kr, kc, qr, qc) != (0, 1, 1, 0) or qdiv != grp:
+                raise Unsupported("attention mask must compare a column index with the query position of a row")
             kfull = iv_full(kconst, ext).reshape(-1, T)[sel] - np.arange(T)[None, :] * tn
             qfull = iv_full(qconst, ext).reshape(-1, T)[sel] - row0[:, None]
             d = qfull - kfull
@@ -254,8 +269,10 @@ class AttentionStatement(Statement):
             delta = int(d.flat[0]) + rmin
             if delta < 0:
                 raise Unsupported("attention rows that see no KV position")
-        arena.check_range(int(q_off.min()), int(q_off.max()) + (tm - 1) * Q.strides[0] + hd, "f16", "Read from")
-        arena.check_range(int(o_off.min()), int(o_off.max()) + (tm - 1) * O.strides[0] + hd, "f16", "Scatter to")
+        arena.check_range(int(q_off.min()), int(q_off.max()) + (bq - 1) * Q.strides[0] + (grp - 1) * Q.strides[1] + hd,
+                          "f16", "Read from")
+        arena.check_range(int(o_off.min()), int(o_off.max()) + (bq - 1) * O.strides[0] + (grp - 1) * O.strides[1] + hd,
+                          "f16", "Scatter to")
         kalloc = arena.check_range(kbase, kbase + 1, "f16", "Read from")
         valloc = arena.check_range(vbase, vbase + 1, "f16", "Read from")
         bt_alloc = arena.check_range(int(idx.min()), int(idx.max()) + 1, kf.idx_dtype, "Read from")
@@ -264,7 +281,8 @@ class AttentionStatement(Statement):
         self.args = a = R.AttnArgs()
         a.q_off = int(np.asarray(Q.view.base).reshape(-1)[0]) + rmin * Q.strides[0] + hmin * Q.strides[1]
         a.o_off = int(np.asarray(O.view.base).reshape(-1)[0]) + rmin * O.strides[0] + hmin * O.strides[1]
-        a.k_off, a.v_off = kbase + hmin * kview.strides[2], vbase + hmin * kview.strides[2]
+        a.k_off, a.v_off = kbase + (hmin // grp) * kview.strides[2], vbase + (hmin // grp) * kview.strides[2]
+        a.kv_group = grp
         a.bt_off, a.bt_dtype = int(idx[0, 0]), R.DTYPE_CODE[kf.idx_dtype]
         a.seq_q, a.heads, a.head_dim = seq_q, heads, hd
         a.page, a.n_pages_total, a.num_tiles = tn, n_pages, T
@@ -276,7 +294,7 @@ class AttentionStatement(Statement):
         self.device_arrays = []
         vis = np.minimum(T * tn, np.arange(seq_q) + 1 + delta) if m["causal"] else np.full(seq_q, T * tn)
         self.flops = int(4 * heads * hd * vis.sum())
-        self._bytes = heads * hd * 2 * (2 * seq_q + 2 * min(T, n_pages) * tn)
+        self._bytes = hd * 2 * (2 * heads * seq_q + 2 * ngrp * min(T, n_pages) * tn)
         neg = np.array([-1])
         rows = (np.arange(seq_q, dtype=np.int64)[:, None] * 1)
         qs = ((a.q_off + rows * Q.strides[0] + np.arange(heads)[None, :] * Q.strides[1]) * 2).reshape(-1)

@@ -34,7 +34,7 @@ EW_OPS = ["mov", "add", "sub", "mul", "div", "rem", "max", "maxnum", "min", "min
           "log2", "log1p", "sqrt", "rsqrt", "tanh", "sin", "cos", "ceil", "floor", "fma", "pow", "select",
           "cmp_eq", "cmp_ne", "cmp_lt", "cmp_le", "cmp_gt", "cmp_ge", "cmp_ord", "cmp_uno", "cmp_true", "cmp_false",
           "and", "or", "xor", "shl", "shr", "divt", "remt", "divf", "cdiv", "bitcast", "cmp_une_", "cmp_ueq_",
-          "cmp_ult_", "cmp_ule_", "cmp_ugt_", "cmp_uge_"]
+          "cmp_ult_", "cmp_ule_", "cmp_ugt_", "cmp_uge_", "sign"]
 EW_CODE = {n: i for i, n in enumerate(EW_OPS)}
 
 _FLOAT_EW = {"arith.addf": "add", "arith.subf": "sub", "arith.mulf": "mul", "arith.divf": "div", "arith.remf": "rem",
@@ -42,7 +42,7 @@ _FLOAT_EW = {"arith.addf": "add", "arith.subf": "sub", "arith.mulf": "mul", "ari
              "arith.negf": "neg", "math.absf": "abs", "math.exp": "exp", "math.log": "log", "math.log2": "log2",
              "math.log1p": "log1p", "math.sqrt": "sqrt", "math.rsqrt": "rsqrt", "math.tanh": "tanh",
              "math.sin": "sin", "math.cos": "cos", "math.ceil": "ceil", "math.floor": "floor", "math.fma": "fma",
-             "math.powf": "pow", "arith.select": "select"}
+             "math.powf": "pow", "arith.select": "select", "math.sign": "sign"}
 _INT_EW = {"arith.addi": "add", "arith.subi": "sub", "arith.muli": "mul", "arith.divui": "divf",
            "arith.floordivsi": "divf", "arith.divsi": "divt", "arith.remui": "rem", "arith.remsi": "remt",
            "arith.andi": "and", "arith.ori": "or", "arith.xori": "xor", "arith.shli": "shl", "arith.shrsi": "shr",

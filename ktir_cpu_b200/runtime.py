@@ -88,7 +88,7 @@ class AttnArgs(C.Structure):
                 ("q_row_stride", C.c_int64), ("q_head_stride", C.c_int64),
                 ("o_row_stride", C.c_int64), ("o_head_stride", C.c_int64),
                 ("kv_page_stride", C.c_int64), ("kv_row_stride", C.c_int64), ("kv_head_stride", C.c_int64),
-                ("scale", C.c_float), ("m_init", C.c_float), ("l_init", C.c_float), ("reserved", C.c_int32)]
+                ("scale", C.c_float), ("m_init", C.c_float), ("l_init", C.c_float), ("kv_group", C.c_int32)]
 
 
 G_MAXDIM = 6

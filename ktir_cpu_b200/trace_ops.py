@@ -136,10 +136,33 @@ _MATH = {"math.exp": np.exp, "math.sqrt": np.sqrt, "math.rsqrt": lambda x: 1.0 /
          "math.erf": None}
 
 
+_ERF_C = (0.254829592, -0.284496736, 1.421413741, -1.453152027, 1.061405429)
+
+
+def _erf_tile(x: Node) -> Node:
+    """``math.erf`` of a tile as the reference evaluates it: the Abramowitz & Stegun 7.1.26 formula
+    written with NumPy ufuncs on the tile's own dtype (ktir_cpu/ops/math_ops.py:99-111), so every
+    step — and every constant — is rounded to that dtype.  Expanded into the same chain of
+    elementwise nodes: sign(x) * (1 - poly(t) * exp(-|x| * |x|)), t = 1 / (1 + 0.3275911 |x|)."""
+    c = lambda v: const_node(v, (), x.dtype)     # noqa: E731  (rounded to the tile dtype when lowered)
+    a = ew("math.absf", [x])
+    t = ew("arith.divf", [c(1.0), ew("arith.addf", [c(1.0), ew("arith.mulf", [c(0.3275911), a])])])
+    inner = ew("arith.mulf", [t, c(_ERF_C[4])])
+    for k in (3, 2, 1, 0):
+        inner = ew("arith.mulf", [t, ew("arith.addf", [c(_ERF_C[k]), inner])])
+    e = ew("math.exp", [ew("arith.mulf", [ew("arith.negf", [a]), a])])
+    return ew("arith.mulf", [ew("math.sign", [x]), ew("arith.subf", [c(1.0), ew("arith.mulf", [inner, e])])])
+
+
 @rule(*_MATH)
 def _math_unary(tr, op, scope):
     a = tr.get(scope, op.operands[0])
     if is_node(a):
+        if op.name == "math.erf":
+            return _erf_tile(a)
+        if op.name == "math.rsqrt":
+            # 1.0 / np.sqrt(x) on the tile dtype (ktir_cpu/ops/math_ops.py:38-41): two ops, two roundings
+            return ew("arith.divf", [const_node(1.0, (), a.dtype), ew("math.sqrt", [a])])
         return ew(op.name, [a])
     if _MATH[op.name] is None or isinstance(a, np.ndarray):
         raise Unsupported(f"{op.name} on a scalar")

@@ -150,14 +150,17 @@ def _ew(op, dst_dt, src, attrs):
         one = np.float32(1)
         fn = {"add": lambda: x[0] + x[1], "sub": lambda: x[0] - x[1], "mul": lambda: x[0] * x[1],
               "div": lambda: x[0] / x[1], "rem": lambda: np.fmod(x[0], x[1]),
-              "max": lambda: np.maximum(x[0], x[1]), "maxnum": lambda: np.fmax(x[0], x[1]),
-              "min": lambda: np.minimum(x[0], x[1]), "minnum": lambda: np.fmin(x[0], x[1]),
+              # the first operand wins a tie, as in NumPy's half loops (and the device kernels)
+              "max": lambda: np.where((x[0] >= x[1]) | np.isnan(x[0]), x[0], x[1]),
+              "maxnum": lambda: np.where((x[0] >= x[1]) | np.isnan(x[1]), x[0], x[1]),
+              "min": lambda: np.where((x[0] <= x[1]) | np.isnan(x[0]), x[0], x[1]),
+              "minnum": lambda: np.where((x[0] <= x[1]) | np.isnan(x[1]), x[0], x[1]),
               "neg": lambda: -x[0], "abs": lambda: np.abs(x[0]), "exp": lambda: np.exp(x[0]),
               "log": lambda: np.log(x[0]), "log2": lambda: np.log2(x[0]), "log1p": lambda: np.log1p(x[0]),
               "sqrt": lambda: np.sqrt(x[0]), "rsqrt": lambda: one / np.sqrt(x[0]), "tanh": lambda: np.tanh(x[0]),
               "sin": lambda: np.sin(x[0]), "cos": lambda: np.cos(x[0]), "ceil": lambda: np.ceil(x[0]),
               "floor": lambda: np.floor(x[0]), "fma": lambda: x[0] * x[1] + x[2],
-              "pow": lambda: np.power(x[0], x[1])}[op]
+              "pow": lambda: np.power(x[0], x[1]), "sign": lambda: np.sign(x[0])}[op]
         return fn().astype(np.float32).astype(NP_DT[dst_dt])
     a, b = x[0], (x[1] if len(x) > 1 else None)
     safe = None if b is None else np.where(b == 0, 1, b)

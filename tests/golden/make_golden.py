@@ -20,9 +20,45 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from ktir_cpu_b200 import kernels as K  # noqa: E402
 
 
-def cases():
-    """name -> (source, function, kwargs). Shared with the tests through the fixture files."""
+def _reference_generators(ref_root: str):
+    """``notebooks/demo_gen_mlir.py`` of the reference checkout, imported as a module."""
+    import importlib.util
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    spec = importlib.util.spec_from_file_location("demo_gen_mlir", os.path.join(ref_root, "notebooks", "demo_gen_mlir.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def paged_attention_inputs(seed, S, H, Hkv, D, tn, ctx):
+    """Seeded inputs of a ``paged_attention_kernel`` call: K/V pages stored in a permuted order and
+    found through the block table, ``ctx`` KV positions before the first query position."""
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((S, H, D)).astype(np.float16)
+    nt = (S + ctx) // tn
+    k, v = (rng.standard_normal((nt, tn, Hkv, D)).astype(np.float16) for _ in range(2))
+    table = rng.permutation(nt).astype(np.int32).reshape(1, -1)
+    return dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k, value_cache_ptr=v,
+                block_tables_ptr=table, cur_batch_start_index=0, block_table_offset=0, num_tiles=nt,
+                context_len=ctx, scale=np.float32(1.0 / np.sqrt(D)))
+
+
+def cases(ref_root=None):
+    """name -> (source, function, kwargs). Shared with the tests through the fixture files.
+
+    With ``ref_root`` the kernels the reference's own generator writes
+    (``gen_paged_attention_mlir``) are added; their text is stored in the fixture like any other."""
     out = {}
+    if ref_root:
+        gen = _reference_generators(ref_root)
+        # (S, query heads, K/V heads, tile_m, tile_n, context before the queries)
+        for S, H, Hkv, tm, tn, ctx in ((128, 2, 2, 32, 32, 0), (256, 2, 2, 64, 128, 0), (256, 1, 1, 128, 128, 0),
+                                       (64, 4, 2, 32, 32, 64), (128, 2, 1, 128, 64, 0)):
+            src = gen.gen_paged_attention_mlir(num_tokens=S, context_len=S + ctx, num_query_heads=H, num_kv_heads=Hkv,
+                                               head_dim=128, block_size=tn, block_q=tm // (H // Hkv))
+            out[f"paged_attention_ref_S{S}_H{H}kv{Hkv}_t{tm}x{tn}_ctx{ctx}"] = (
+                src, "paged_attention_kernel", paged_attention_inputs(7 + S + tm + tn, S, H, Hkv, 128, tn, ctx))
     rng = np.random.default_rng(1)
     x, y = rng.standard_normal(4096).astype(np.float16), rng.standard_normal(4096).astype(np.float16)
     out["vector_add_4096"] = (K.vector_add(4096, 128, 32), "add_kernel",
@@ -78,6 +114,18 @@ def cases():
         K.naive_attention(32, 16, 2), "naive_attention",
         dict(q_ptr=rng.standard_normal((32, 16)).astype(np.float16), k_ptr=rng.standard_normal((32, 16)).astype(np.float16),
              v_ptr=rng.standard_normal((32, 16)).astype(np.float16), o_ptr=np.zeros((32, 16), np.float16)))
+    # every exactly-rounded f16 elementwise op on random bit patterns (specials included): pins the
+    # rounding, NaN and signed-zero rules of the arith / math dialects
+    rng = np.random.default_rng(8)
+    ops = ["add", "sub", "mul", "div", "maximum", "maxnum", "minimum", "minnum", "neg", "abs", "sqrt", "erf"]
+    x = rng.integers(0, 65536, 4096).astype(np.uint16)
+    y = rng.integers(0, 65536, 4096).astype(np.uint16)
+    x[:8] = [0x0000, 0x8000, 0x7c00, 0xfc00, 0x7e00, 0x0001, 0x7bff, 0x3c00]
+    y[:8] = [0x8000, 0x0000, 0x7c00, 0x7c00, 0x3c00, 0x0001, 0x7bff, 0x7e00]
+    names = [f"out_{o}_ptr" for o in ops] + ["out_select_ptr", "out_ext_add_ptr"]
+    out["elementwise_f16_suite"] = (
+        K.elementwise_suite(ops, 4096, 128, 4, "f16", "olt"), "elementwise_kernel",
+        dict(x_ptr=x.view(np.float16), y_ptr=y.view(np.float16), **{n: np.zeros(4096, np.float16) for n in names}))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),
@@ -89,7 +137,7 @@ def main(ref_root: str, only=None):
     sys.path.insert(0, ref_root)
     from ktir_cpu import KTIRInterpreter
     meta = f"numpy {np.__version__}"
-    for name, (src, fn, kw) in cases().items():
+    for name, (src, fn, kw) in cases(ref_root).items():
         if only and name not in only:
             continue
         interp = KTIRInterpreter()
@@ -110,7 +158,7 @@ def latency_main(ref_root: str):
     sys.path.insert(0, ref_root)
     from ktir_cpu import HardwareConfig, KTIRInterpreter
     out = {}
-    for name, (src, fn, kw) in cases().items():
+    for name, (src, fn, kw) in cases().items():      # own kernels only: keeps latency.json small
         interp = KTIRInterpreter(latency_config=HardwareConfig())
         interp.load(src)
         interp.execute_function(fn, **kw)

@@ -38,7 +38,7 @@ def run_generic(src, fn, kw):
     return out, kinds
 
 
-EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128")
+EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elementwise_f16_suite")
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 
@@ -48,8 +48,9 @@ def test_generic_steps_reproduce_the_reference(name):
     src, fn, kw, want = load_golden(name)
     got, kinds = run_generic(src, fn, kw)
     for k, w in want.items():
-        if name in EXACT:
+        if name in EXACT and "erf" not in k:
             np.testing.assert_array_equal(got[k], w)
+            np.testing.assert_array_equal(np.signbit(got[k]) | np.isnan(w), np.signbit(w) | np.isnan(w))
         else:
             # transcendental f16/f32 ufuncs differ by <= 1 ulp between hosts; f32 matmul order differs
             np.testing.assert_allclose(got[k].astype(np.float32), w.astype(np.float32), rtol=2e-3, atol=2e-3)

@@ -42,13 +42,19 @@ def test_gpu_matches_reference_fixture(name, build_lib):
     assert set(got) == set(expected)
     for k in expected:
         assert got[k].dtype == expected[k].dtype and got[k].shape == expected[k].shape
-        if _exact(name):
+        if name.startswith("elementwise"):
+            from test_gpu_elementwise import assert_same_bits, ulp_distance_f16
+            if "erf" in k:          # a chain of f16 roundings around one exp, which is host-dependent by 1 ulp
+                assert ulp_distance_f16(got[k], expected[k]).max() <= 4
+            else:
+                assert_same_bits(got[k], expected[k], k)
+        elif _exact(name):
             np.testing.assert_array_equal(got[k], expected[k])
         elif name.startswith("matmul_f32acc"):
             # f32 accumulation on both sides, only the summation order differs: <= 1 f16 ulp
             np.testing.assert_allclose(got[k].astype(np.float32), expected[k].astype(np.float32),
                                        rtol=2e-3, atol=1e-2)
-        elif name.startswith("causal_attention"):
+        elif name.startswith(("causal_attention", "paged_attention")):
             # probabilities pass through f16 before the second matmul (<= 2^-11 relative)
             np.testing.assert_allclose(got[k].astype(np.float32), expected[k].astype(np.float32),
                                        rtol=1e-2, atol=2e-3)

@@ -6,7 +6,7 @@ import re
 import numpy as np
 import pytest
 
-from conftest import ROOT, load_golden
+from conftest import ROOT, golden_names, load_golden
 from ktir_cpu_b200 import kernels as K
 from ktir_cpu_b200 import runtime as R
 from ktir_cpu_b200.affine import parse_affine_map, parse_affine_set
@@ -107,3 +107,31 @@ def test_library_exports_every_declared_symbol(build_lib):
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} declared in include/ktir_b200.h but not exported"
     assert declared == set(R.SYMBOLS), "ctypes binding and header disagree"
+
+
+@pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith("paged_attention_ref")])
+def test_reference_generated_attention_text_plans_as_the_tensor_core_kernel(name):
+    """Kernel text written by the reference's own generator (stored in the fixture): one fused
+    attention launch, with the grouping, context offset and page walk read off the text."""
+    src, fn, kw, _ = load_golden(name)
+    tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items() if isinstance(v, np.ndarray)]
+    scalars = {k: v for k, v in kw.items() if not isinstance(v, np.ndarray)}
+    sess = _plan(src, fn, tensors, scalars)
+    assert [s.kind for s in sess.plan.statements] == ["attention_fwd"]
+    a = sess.plan.statements[0].args
+    S, H, _ = kw["query_ptr"].shape
+    Hkv = kw["key_cache_ptr"].shape[2]
+    assert (a.seq_q, a.heads, max(a.kv_group, 1)) == (S, H, H // Hkv)
+    assert a.causal == 1 and a.causal_delta == kw["context_len"] and a.num_tiles == kw["num_tiles"]
+    assert sess.plan.fully_overwritten == {"output_ptr"}
+
+
+def test_own_paged_attention_text_plans_like_the_reference_generator():
+    sess = _plan(K.paged_attention(256, 384, 8, 2, 128, 64, 16), "paged_attention_kernel",
+                 [("output_ptr", (256, 8, 128), F16), ("query_ptr", (256, 8, 128), F16),
+                  ("key_cache_ptr", (6, 64, 2, 128), F16), ("value_cache_ptr", (6, 64, 2, 128), F16),
+                  ("block_tables_ptr", (1, 6), np.dtype(np.int32))],
+                 dict(cur_batch_start_index=0, block_table_offset=0, num_tiles=6, context_len=128, scale=np.float32(0.1)))
+    a = sess.plan.statements[0].args
+    assert sess.plan.statements[0].kind == "attention_fwd"
+    assert (a.seq_q, a.heads, a.kv_group, a.causal_delta, a.page, a.num_tiles) == (256, 8, 4, 128, 64, 6)
