@@ -240,7 +240,7 @@ static __device__ __forceinline__ void g_ew_one(const ktb_gen_op& o, int op, int
         else g_sti(o.dst, o.dt_dst, di, g_ldi(pa, dta, ia));
         return;
     }
-    if ((op >= G_CMP_EQ && op <= G_CMP_FALSE) || op >= G_CMP_UNE) {
+    if ((op >= G_CMP_EQ && op <= G_CMP_FALSE) || (op >= G_CMP_UNE && op <= G_CMP_UGE)) {
         bool r;
         if (!(o.flags & 1) && (g_is_float(dta) || g_is_float(dtb))) {
             const float a = g_ldf(pa, dta, ia), b = g_ldf(pb, dtb, ib);

@@ -80,21 +80,34 @@ def test_f16_compare_select_bit_exact(pred, build_lib):
     assert_same_bits(got["out_select_ptr"], want["out_select_ptr"], pred)
 
 
+_F64 = {"exp": np.exp, "log": np.log, "log2": np.log2, "tanh": np.tanh, "sin": np.sin, "cos": np.cos}
+
+
 @pytest.mark.parametrize("fused", [True, False], ids=["register_program", "step_by_step"])
-def test_f16_transcendentals_within_one_ulp_on_every_bit_pattern(fused, build_lib):
-    """NumPy's half-precision transcendental loops are within 1 ulp of correct rounding and differ
-    between hosts; the device computes in f32 and rounds once."""
+def test_f16_transcendentals_on_every_bit_pattern(fused, build_lib):
+    """The device computes in f32 and rounds once, so it must sit within 1 f16 step of the correctly
+    rounded value.  NumPy's half-precision loops are host-dependent (2-3 steps off correct rounding
+    on AVX-512 hosts), so against the oracle the allowance is the oracle's own distance plus one.
+    erf is a chain of ~20 f16 roundings around one exp (cancelling near 0): absolute tolerance."""
     x = np.arange(65536, dtype=np.uint16).view(np.float16)
     n = x.size
     src = K.elementwise_suite(ULP_OPS, n, 2048, 32, "f16")
     names = [f"out_{o}_ptr" for o in ULP_OPS]
     kw = dict(x_ptr=x, y_ptr=x, out_ext_add_ptr=np.zeros(n, np.float16), **{k: np.zeros(n, np.float16) for k in names})
     got, want, _ = _run(src, kw, fused)
-    for k in names:
-        d = ulp_distance_f16(got[k], want[k])
-        # erf chains ~20 f16 roundings around one exp: a 1-ulp exp difference can grow
-        limit = 4 if "erf" in k else 1
-        assert d.max() <= limit, f"{k}: {int(d.max())} ulp at pattern {int(d.argmax()):#06x}"
+    for o in ULP_OPS:
+        g, w = got[f"out_{o}_ptr"], want[f"out_{o}_ptr"]
+        if o == "erf":
+            np.testing.assert_array_equal(np.isnan(g), np.isnan(w))
+            np.testing.assert_allclose(g.astype(np.float32), w.astype(np.float32), rtol=0, atol=2e-3)
+            continue
+        with np.errstate(all="ignore"):
+            correct = _F64[o](x.astype(np.float64)).astype(np.float16)
+        d_correct = ulp_distance_f16(g, correct)
+        assert d_correct.max() <= 1, f"{o}: {int(d_correct.max())} steps from correct rounding at {int(d_correct.argmax()):#06x}"
+        slack = ulp_distance_f16(w, correct) + 1
+        d = ulp_distance_f16(g, w)
+        assert (d <= slack).all(), f"{o}: {int((d - slack).max())} steps beyond the oracle's own error at {int((d - slack).argmax()):#06x}"
 
 
 @pytest.mark.parametrize("fused", [True, False], ids=["register_program", "step_by_step"])

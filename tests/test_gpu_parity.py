@@ -43,9 +43,10 @@ def test_gpu_matches_reference_fixture(name, build_lib):
     for k in expected:
         assert got[k].dtype == expected[k].dtype and got[k].shape == expected[k].shape
         if name.startswith("elementwise"):
-            from test_gpu_elementwise import assert_same_bits, ulp_distance_f16
-            if "erf" in k:          # a chain of f16 roundings around one exp, which is host-dependent by 1 ulp
-                assert ulp_distance_f16(got[k], expected[k]).max() <= 4
+            from test_gpu_elementwise import assert_same_bits
+            if "erf" in k:          # a chain of f16 roundings around one host-dependent exp, cancelling near 0
+                np.testing.assert_array_equal(np.isnan(got[k]), np.isnan(expected[k]))
+                np.testing.assert_allclose(got[k].astype(np.float32), expected[k].astype(np.float32), rtol=0, atol=2e-3)
             else:
                 assert_same_bits(got[k], expected[k], k)
         elif _exact(name):

@@ -135,3 +135,11 @@ def test_own_paged_attention_text_plans_like_the_reference_generator():
     a = sess.plan.statements[0].args
     assert sess.plan.statements[0].kind == "attention_fwd"
     assert (a.seq_q, a.heads, a.kv_group, a.causal_delta, a.page, a.num_tiles) == (256, 8, 4, 128, 64, 6)
+
+
+def test_generic_opcode_tables_agree_between_host_and_device():
+    """``lower_generic.EW_OPS`` is the order of the ``G_*`` enum in ``csrc/generic_ops.cu``."""
+    from ktir_cpu_b200.lower_generic import EW_OPS
+    text = open(os.path.join(ROOT, "ktir_cpu_b200", "csrc", "generic_ops.cu")).read()
+    names = re.search(r"enum \{ (G_MOV.*?) \};", text, re.S).group(1).replace("\n", " ").split(",")
+    assert [n.strip()[2:].lower() for n in names] == [o.rstrip("_") for o in EW_OPS]
