@@ -72,6 +72,49 @@ int ktb_graph_end(ktb_ctx* ctx, void** graph_out);
 int ktb_graph_launch(ktb_ctx* ctx, void* graph);
 int ktb_graph_destroy(ktb_ctx* ctx, void* graph);
 
+/* ---- pipelined transfers ---------------------------------------------------------------
+ * Two copy lanes (streams) beside the launch stream: lane 1 uploads, lane 2 reads back; 0 names
+ * the launch stream.  ktb_lane_fence(from, to) makes everything queued later on `to` wait for
+ * what is queued on `from` so far; ktb_lane_d2h queues a read-back of `height` rows of `width`
+ * bytes, `pitch` bytes apart on both sides, on lane 2 (host_dst page-locked).  ktb_sync also
+ * waits for both lanes.
+ *
+ * ktb_run_pipeline is KTIRInterpreter.execute_function's data movement
+ * (ktir_cpu/interpreter.py:156-194: a flatten() copy of every ndarray argument into simulated
+ * memory, the run, a read-back of every argument into a new array) as one overlapped pass.  Per
+ * tensor t the caller gives src[t], its own array, and pinned[t], a page-locked array of the same
+ * layout that it will hand back.  A chunk lists the regions it needs on the device (`up`), an
+ * optional launch and the regions to read back (`down`).  Host threads copy the `up` regions
+ * src -> pinned for all chunks, in order; the calling thread follows behind: when a chunk's
+ * copies have landed it queues their DMAs pinned -> arena on lane 1, fences, calls
+ * launch(ctx, launch_args) (any ktb_launch_* with its argument struct), fences and queues the
+ * `down` DMAs arena -> pinned on lane 2.  So one host copy yields the upload and the caller's
+ * fresh array, and upload, kernels and read-back of neighbouring chunks overlap.  A region with
+ * dev_off == KTB_NO_DEVICE is copied on the host only; src[t] == pinned[t] skips the host copy.
+ * Returns once everything is queued (ktb_sync waits for it).  ktb_set_copy_threads sizes the
+ * process-wide pool of copy threads (default: half the hardware threads, at most 8). */
+#define KTB_NO_DEVICE UINT64_MAX
+typedef struct {
+    int32_t tensor;            /* index into pinned[] / src[] */
+    int32_t reserved;
+    uint64_t dev_off;          /* byte offset in the arena, or KTB_NO_DEVICE */
+    uint64_t rel;              /* byte offset inside the tensor */
+    uint64_t width, height, pitch;   /* rows of `width` bytes, `pitch` apart (height 1: one run) */
+} ktb_region;
+typedef struct {
+    int (*launch)(ktb_ctx*, const void*);   /* may be NULL */
+    const void* launch_args;
+    int32_t n_up, n_down;
+    const ktb_region* up;
+    const ktb_region* down;
+} ktb_pipe_chunk;
+int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, int n_chunks, void* const* pinned,
+                     const void* const* src, int n_tensors);
+int ktb_lane_fence(ktb_ctx* ctx, int from, int to);
+int ktb_lane_d2h(ktb_ctx* ctx, void* host_dst, const void* dev_src, size_t width, size_t height, size_t pitch);
+int ktb_set_copy_threads(int n);
+int ktb_copy_threads(void);
+
 /* ---- elementwise register programs ---------------------------------------
  * A short straight-line program over f32 registers; inputs are loaded into
  * registers 0..n_in-1.  Replaces per-op NumPy dispatch of the arith/math

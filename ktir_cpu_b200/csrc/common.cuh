@@ -11,6 +11,7 @@
 #define KTB_NUM_EVENTS 64
 #define KTB_MAX_DEVICES 64            // power of two; per-device launch state is indexed by device & (this - 1)
 #define KTB_FLUSH_BYTES (256u << 20)   // > 126 MB L2
+#define KTB_NUM_FENCES 64             // rotating events that order the copy lanes against the launch stream
 
 struct ktb_ctx {
     int device;
@@ -22,8 +23,15 @@ struct ktb_ctx {
     void* flush_buf;            // lazily allocated L2 flush scratch
     int64_t launches;
     int64_t capture_base;       // launch count when a graph capture began
+    cudaStream_t lane[2];       // upload lane, read-back lane (created on first use)
+    cudaEvent_t fences[KTB_NUM_FENCES];
+    unsigned next_fence;
+    bool lanes_ok, lanes_used;
     char err[512];
 };
+
+void ktb_transfer_destroy(ktb_ctx* ctx);   // transfer.cu
+int ktb_transfer_sync(ktb_ctx* ctx);
 
 static inline int ktb_fail(ktb_ctx* ctx, int code, const char* what, const char* detail) {
     if (ctx) snprintf(ctx->err, sizeof(ctx->err), "%s: %s", what, detail ? detail : "");

@@ -45,6 +45,7 @@ int ktb_destroy(ktb_ctx* ctx) {
     if (!ctx) return KTB_E_ARG;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    ktb_transfer_destroy(ctx);
     for (int i = 0; i < KTB_NUM_EVENTS; ++i) cudaEventDestroy(ctx->events[i]);
     if (ctx->flush_buf) cudaFree(ctx->flush_buf);
     cudaFree(ctx->dev_status);
@@ -121,6 +122,7 @@ int ktb_sync(ktb_ctx* ctx, ktb_status* status_out) {
     ktb_status st;
     KTB_CUDA(ctx, cudaMemcpyAsync(&st, ctx->dev_status, sizeof(st), cudaMemcpyDeviceToHost, ctx->stream));
     KTB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (int rc = ktb_transfer_sync(ctx)) return rc;      // the copy lanes, when a pipelined call used them
     if (status_out) *status_out = st;
     if (st.negative_index || st.wait_timeout) {
         KTB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(st), ctx->stream));

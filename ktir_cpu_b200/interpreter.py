@@ -78,6 +78,8 @@ class HostTensors:
 class Session:
     """One function bound to one tensor layout: the arena in HBM plus its launch plan."""
 
+    PIPELINE_PIECE = 16 << 20        # bytes moved (both directions) per part of a pipelined call
+
     def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
                  scalars: Dict[str, Any], latency: bool = False, shard: Optional[Tuple[int, int]] = None,
                  arena_ptr: Optional[int] = None, seeded: Sequence[Tuple[int, int, str]] = (), fused: bool = True):
@@ -122,6 +124,9 @@ class Session:
                 if needs_row_ownership(stores):
                     row_shard = shard          # every core runs; each rank applies the rows it owns
                 else:
+                    # a core of another rank may read or overlap what a core of this rank writes: the
+                    # whole grid must pass the sequential-order check, not just this rank's slice
+                    lower(R.PlanOnlyDevice(), stores, self.arena_map, fused=fused)
                     stores = Tracer(func, scalars, ptrs, core_range=core_slice(tracer.ncores, *shard)).run()
             self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard, fused=fused)
         except Exception:
@@ -136,6 +141,27 @@ class Session:
         self.no_upload = set(self.plan.fully_overwritten)
         self.last_h2d_bytes = 0
         self.last_d2h_bytes = 0
+        self._transfer = None
+        self._pipeline = None
+
+    def transfer_plan(self):
+        """How a call moves its tensors (``pipeline.TransferPlan``): the plan's statement in
+        independent parts when it has one statement that can be split, else as a whole."""
+        if self._transfer is None:
+            from .pipeline import TransferPlan
+            chunks = None
+            if len(self.plan.statements) == 1:
+                chunks = self.plan.statements[0].split(self.PIPELINE_PIECE)
+            tensors = {k: (off, nbytes) for k, (off, nbytes, _, _) in self.layout.items()}
+            self._transfer = TransferPlan(tensors, self.written, self.no_upload, chunks, self.plan.written_ranges(),
+                                          partial=self.shard is not None and self.shard[1] > 1)
+        return self._transfer
+
+    def pipeline(self):
+        if self._pipeline is None:
+            from .pipeline import BoundPipeline
+            self._pipeline = BoundPipeline(self.dev, self.arena, self.transfer_plan())
+        return self._pipeline
 
     def upload(self, name: str, arr: np.ndarray):
         off, nbytes, shape, dt = self.layout[name]
@@ -316,7 +342,7 @@ class KTIRInterpreter:
         except Exception:
             pass
 
-    def session(self, func_name: str, **kwargs) -> Session:
+    def session(self, func_name: str, _shard: Optional[Tuple[int, int]] = None, **kwargs) -> Session:
         """The cached (function, tensor layout, scalar arguments) session for these arguments."""
         func = self._require_module().get_function(func_name)
         declared = func.arg_names
@@ -333,14 +359,14 @@ class KTIRInterpreter:
         seeded = tuple((addr, arr.nbytes, to_ktir_dtype(arr.dtype)) for addr, arr in
                        sorted(self.memory.hbm.regions.items()))
         key = (func_name, tuple((n, s, str(d)) for n, s, d in tensors),
-               tuple((k, _scalar_key(v)) for k, v in scalars.items()), seeded)
+               tuple((k, _scalar_key(v)) for k, v in scalars.items()), seeded, _shard)
         sess = self._sessions.get(key)
         if sess is None:
             if len(self._sessions) >= self._max_sessions:
                 old = next(iter(self._sessions))
                 self._sessions.pop(old).close()
             sess = Session(self.device, func, tensors, scalars, latency=self._latency_config is not None,
-                           seeded=seeded, fused=self._fused)
+                           seeded=seeded, fused=self._fused, shard=_shard)
             self._sessions[key] = sess
         return sess, kwargs
 
@@ -352,39 +378,84 @@ class KTIRInterpreter:
         self.grid_executor = _GridFacade(n)
 
     def execute_function(self, func_name: str, **kwargs) -> Dict[str, np.ndarray]:
+        """Run ``func_name`` on the device.  As in the reference (ktir_cpu/interpreter.py:122-194)
+        every ndarray argument comes back as a new array and the caller's arrays are not touched.
+
+        Calls that move at least 1 MiB run pipelined (``pipeline.py``): the caller's arrays are copied
+        once, by host threads, into page-locked result arrays that double as the DMA source; a plan
+        whose statement splits into independent parts uploads, computes and reads back part by part
+        on three streams."""
         self._prepare_execution(tuple(self._require_module().get_function(func_name).grid))
         sess, kwargs = self.session(func_name, **kwargs)
-        for addr, arr in self.memory.hbm.regions.items():
-            sess.dev.h2d(sess.arena + addr, arr)
         if self._pool is None:
             from .pinned import PinnedPool
             self._pool = PinnedPool(self.device)
+        arrays = {k: v for k, v in kwargs.items() if isinstance(v, np.ndarray)}
+        seeded = self.memory.hbm.regions
+        if not seeded and sum(v.nbytes for v in arrays.values()) >= (1 << 20):
+            outputs = self._execute_pipelined(sess, arrays)
+        else:
+            outputs = self._execute_simple(sess, arrays, seeded)
+        if self._latency_tracker is not None:
+            self._charge_latency(sess.latency_records, sess.n_cores, layout_of(sess), kwargs)
+        return outputs
+
+    def execute_shard(self, func_name: str, rank: int, world: int, **kwargs) -> Dict[str, np.ndarray]:
+        """This rank's share of one kernel split over ``world`` GPUs (one process per GPU, every rank
+        calls with the same arguments): the cores ``[rank*C/world, (rank+1)*C/world)`` of the grid,
+        or — for an ordered indirect store — all cores but only the destination rows this rank owns
+        (``sharded.py``).  Only what these cores read is uploaded and only what they wrote is read
+        back: the returned arrays are valid inside ``last_slabs`` (arena byte ranges; tensor ``k``
+        starts at ``last_layout[k][0]``) and unspecified elsewhere.  Nothing is exchanged between
+        ranks; the caller merges slabs where it needs the whole result."""
+        if self.memory.hbm.regions:
+            raise ValueError("execute_shard does not take memory seeded at fixed addresses")
+        self._prepare_execution(tuple(self._require_module().get_function(func_name).grid))
+        sess, kwargs = self.session(func_name, _shard=(rank, world), **kwargs)
+        if self._pool is None:
+            from .pinned import PinnedPool
+            self._pool = PinnedPool(self.device)
+        arrays = {k: v for k, v in kwargs.items() if isinstance(v, np.ndarray)}
+        outputs = self._execute_pipelined(sess, arrays)
+        self.last_slabs = sess.written_ranges()
+        self.last_layout = dict(sess.layout)
+        return outputs
+
+    def _execute_pipelined(self, sess: Session, arrays: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
+        pipe = sess.pipeline()
+        tp = pipe.tp
+        host = {k: np.ascontiguousarray(v) for k, v in arrays.items()}
+        outputs = {k: self._pool.empty(v.shape, v.dtype) for k, v in arrays.items()}
+        pipe.run(sess.dev, sess.arena, host, outputs, sess.run)
+        sess.dev.sync()
+        sess.last_h2d_bytes, sess.last_d2h_bytes = tp.h2d_bytes, tp.d2h_bytes
+        return outputs
+
+    def _execute_simple(self, sess: Session, arrays, seeded) -> Dict[str, np.ndarray]:
+        """Small calls, and calls with memory seeded at fixed addresses: upload, launch, read back
+        what the kernels wrote, one after the other on the launch stream."""
+        for addr, arr in seeded.items():
+            sess.dev.h2d(sess.arena + addr, arr)
         keep = []
         h2d = d2h = 0
-        for k, v in kwargs.items():
+        for k, v in arrays.items():
             # a tensor the kernel overwrites completely and never reads needs no upload
-            if isinstance(v, np.ndarray) and k not in sess.no_upload:
+            if k not in sess.no_upload:
                 keep.append(sess.upload(k, v))
                 h2d += v.nbytes
         sess.run()
         outputs: Dict[str, np.ndarray] = {}
-        for k, v in kwargs.items():
-            if isinstance(v, np.ndarray):
-                # every ndarray argument comes back as a new array (interpreter.py:182-194 of the
-                # reference reads all of them back); for large untouched inputs a DMA copy from
-                # the device into pinned memory is faster than a host memcpy into fresh pages
-                if k in sess.written or (v.nbytes >= (1 << 20) and k not in sess.no_upload):
-                    outputs[k] = sess.download(k, pool=self._pool)
-                    d2h += v.nbytes
-                else:
-                    outputs[k] = np.array(v, copy=True)
-        for addr, arr in self.memory.hbm.regions.items():
+        for k, v in arrays.items():
+            if k in sess.written:
+                outputs[k] = sess.download(k, pool=self._pool)
+                d2h += v.nbytes
+            else:
+                outputs[k] = np.array(v, copy=True)
+        for addr, arr in seeded.items():
             sess.dev.d2h(arr, sess.arena + addr)              # what the kernels left at the fixed addresses
         sess.dev.sync()
         sess.last_h2d_bytes, sess.last_d2h_bytes = h2d, d2h
         del keep
-        if self._latency_tracker is not None:
-            self._charge_latency(sess.latency_records, sess.n_cores, layout_of(sess), kwargs)
         return outputs
 
     def _charge_latency(self, records, n_cores, layout, kwargs):

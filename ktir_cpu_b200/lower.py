@@ -79,6 +79,40 @@ class Statement:
     def bytes_moved(self) -> int:
         return 0
 
+    def split(self, piece_bytes: int):
+        """Independent parts of this statement for pipelined execution (``pipeline.Chunk`` list:
+        a launch over part of the work plus the arena regions it reads and writes), or None."""
+        return None
+
+
+def _copy_args(args):
+    return type(args).from_buffer_copy(args)
+
+
+def _split_item_table(stmt, table: np.ndarray, geoms, bpes, launch_fn, piece_bytes: int):
+    """Split a statement whose work is rows of an item table ``[n_items][operands]`` (the last
+    operand is the output) into contiguous item ranges."""
+    from .pipeline import Chunk, chunk_count, tile_regions
+    n_items, n_op = table.shape
+    total = sum(n_items * g[0] * g[2] * b for g, b in zip(geoms, bpes))
+    n = chunk_count(total, n_items, piece_bytes)
+    if n <= 1:
+        return None
+    bounds = np.linspace(0, n_items, n + 1).astype(np.int64)
+    chunks = []
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if a == b:
+            continue
+        regs = []
+        for k in range(n_op):
+            rows, stride, cols = geoms[k]
+            r = tile_regions(table[a:b, k], rows, stride, cols, bpes[k])
+            if r is None:
+                return None
+            regs.append(r)
+        chunks.append(Chunk(launch_fn(int(a), int(b)), [x for r in regs[:-1] for x in r], list(regs[-1])))
+    return chunks
+
 
 def _points(store: Store):
     """Flat indices (and core ids) of the active iteration points of a store."""
@@ -301,6 +335,18 @@ class EwStatement(Statement):
         self.args.arena = arena_ptr
         dev.check(dev.lib.ktb_launch_ew_stream(dev.h, C.byref(self.args)))
 
+    def split(self, piece_bytes: int):
+        a, n_op = self.args, self.table.shape[1]
+        geoms = [(a.rows, int(a.row_stride[k]), a.cols) for k in range(n_op)]
+        bpes = [2 if a.dtype[k] == R.KTB_F16 else 4 for k in range(n_op)]
+
+        def part(lo, hi):
+            sub = _copy_args(a)
+            sub.dev_item_offsets = self.dev_table + lo * n_op * 8
+            sub.n_items = hi - lo
+            return ("ktb_launch_ew_stream", sub)
+        return _split_item_table(self, self.table, geoms, bpes, part, piece_bytes)
+
     def footprints(self):
         return self.fps
 
@@ -444,6 +490,7 @@ class SoftmaxStatement(Statement):
         a.f16_arith = 1 if m["arith"] == "f16" else 0
         a.max_is_maxnum = 1 if m["maxop"] == "arith.maxnumf" else 0
         a.max_init, a.sum_init = m["max_init"], m["sum_init"]
+        self.table = table
         self.dev_table = dev.upload(table)
         a.dev_item_offsets = self.dev_table
         self.device_arrays = [self.dev_table]
@@ -453,6 +500,18 @@ class SoftmaxStatement(Statement):
     def launch(self, dev, arena_ptr):
         self.args.arena = arena_ptr
         dev.check(dev.lib.ktb_launch_row_softmax(dev.h, C.byref(self.args)))
+
+    def split(self, piece_bytes: int):
+        a = self.args
+        geoms = [(a.rows_per_item, int(a.in_row_stride), a.cols), (a.rows_per_item, int(a.out_row_stride), a.cols)]
+        bpes = [2 if d == R.KTB_F16 else 4 for d in (a.in_dtype, a.out_dtype)]
+
+        def part(lo, hi):
+            sub = _copy_args(a)
+            sub.dev_item_offsets = self.dev_table + lo * 2 * 8
+            sub.n_items = hi - lo
+            return ("ktb_launch_row_softmax", sub)
+        return _split_item_table(self, self.table, geoms, bpes, part, piece_bytes)
 
     def footprints(self):
         return self.fps

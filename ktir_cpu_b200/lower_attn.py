@@ -309,6 +309,41 @@ class AttentionStatement(Statement):
         self.args.arena = arena_ptr
         dev.check(dev.lib.ktb_launch_attention_fwd(dev.h, C.byref(self.args)))
 
+    def split(self, piece_bytes: int):
+        """Groups of heads (whole K/V heads): a group reads its columns of Q, K and V — ``seq`` rows of
+        ``heads x head_dim`` elements each, one strided region per tensor — and the block table."""
+        from .lower import _copy_args
+        from .pipeline import Chunk, Region, chunk_count
+        a = self.args
+        grp = max(a.kv_group, 1)
+        hd = a.head_dim
+        kv_rows = a.n_pages_total * a.page
+        if (a.q_head_stride != hd or a.o_head_stride != hd or a.kv_head_stride != hd
+                or a.kv_page_stride != a.page * a.kv_row_stride):
+            return None
+        n = chunk_count(self._bytes, a.heads // grp, piece_bytes)
+        if n <= 1:
+            return None
+        bt_bpe = 4 if a.bt_dtype == R.KTB_I32 else 8
+        bt = Region(a.bt_off * bt_bpe, a.num_tiles * bt_bpe)
+        bounds = np.linspace(0, a.heads // grp, n + 1).astype(np.int64)
+        chunks = []
+        for g0, g1 in zip(bounds[:-1], bounds[1:]):
+            g0, g1 = int(g0), int(g1)
+            if g0 == g1:
+                continue
+            h0, nh = g0 * grp, (g1 - g0) * grp
+            sub = _copy_args(a)
+            sub.q_off, sub.o_off = a.q_off + h0 * hd, a.o_off + h0 * hd
+            sub.k_off, sub.v_off = a.k_off + g0 * hd, a.v_off + g0 * hd
+            sub.heads = nh
+            q = Region(sub.q_off * 2, nh * hd * 2, a.seq_q, a.q_row_stride * 2)
+            o = Region(sub.o_off * 2, nh * hd * 2, a.seq_q, a.o_row_stride * 2)
+            k = Region(sub.k_off * 2, (g1 - g0) * hd * 2, kv_rows, a.kv_row_stride * 2)
+            v = Region(sub.v_off * 2, (g1 - g0) * hd * 2, kv_rows, a.kv_row_stride * 2)
+            chunks.append(Chunk(("ktb_launch_attention_fwd", sub), [bt, q, k, v], [o]))
+        return chunks
+
     def footprints(self):
         return self.fps
 

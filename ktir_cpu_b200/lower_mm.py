@@ -148,6 +148,33 @@ class GemmStatement(Statement):
         self.args.arena = arena_ptr
         dev.check(dev.lib.ktb_launch_gemm_f16(dev.h, C.byref(self.args)))
 
+    def split(self, piece_bytes: int):
+        """Row blocks of C: block [m0, m1) needs the same rows of A and all of B."""
+        from .lower import _copy_args
+        from .pipeline import Chunk, Region, chunk_count
+        a = self.args
+        cb = 2 if a.c_dtype == R.KTB_F16 else 4
+        blocks = (a.M + 127) // 128                      # the kernel works in 128-row tiles
+        n = chunk_count(a.M * a.K * 2 + a.M * a.N * cb, blocks, piece_bytes)
+        if n <= 1:
+            return None
+
+        def rows(off, r0, r1, ld, width, bpe):
+            if ld == width:
+                return Region((off + r0 * ld) * bpe, (r1 - r0) * width * bpe)
+            return Region((off + r0 * ld) * bpe, width * bpe, r1 - r0, ld * bpe)
+        b_reg = rows(a.b_off, 0, a.K, a.ldb, a.N, 2)
+        bounds = np.linspace(0, blocks, n + 1).astype(np.int64) * 128
+        chunks = []
+        for m0, m1 in zip(bounds[:-1], bounds[1:]):
+            m0, m1 = int(m0), int(min(m1, a.M))
+            if m0 >= m1:
+                continue
+            sub = _copy_args(a)
+            sub.a_off, sub.c_off, sub.M = a.a_off + m0 * a.lda, a.c_off + m0 * a.ldc, m1 - m0
+            chunks.append(Chunk(("ktb_launch_gemm_f16", sub), [b_reg, rows(a.a_off, m0, m1, a.lda, a.K, 2)], [rows(a.c_off, m0, m1, a.ldc, a.N, cb)]))
+        return chunks
+
     def footprints(self):
         return self.fps
 

@@ -48,7 +48,12 @@ def _free(dev, ptr):
 
 
 class PinnedPool:
-    def __init__(self, dev, max_bytes: int = 2 << 30):
+    """Recycled page-locked buffers (sizes rounded up to a power of two).  At most ``max_bytes`` are
+    kept page-locked; past that ``empty`` hands out an ordinary NumPy array, which still works as a
+    result array but is copied to synchronously and more slowly — raise ``max_bytes`` for calls
+    whose live results exceed it."""
+
+    def __init__(self, dev, max_bytes: int = 8 << 30):
         self.dev = dev
         self.max_bytes = max_bytes
         self.total = 0

@@ -96,6 +96,19 @@ G_KINDS = {k: i for i, k in enumerate(["load", "addr", "idxadd", "gather", "cons
                                        "ew", "redl", "matmul", "store", "scatter"])}
 
 
+NO_DEVICE = (1 << 64) - 1
+
+
+class PipeRegion(C.Structure):
+    _fields_ = [("tensor", C.c_int32), ("reserved", C.c_int32), ("dev_off", C.c_uint64), ("rel", C.c_uint64),
+                ("width", C.c_uint64), ("height", C.c_uint64), ("pitch", C.c_uint64)]
+
+
+class PipeChunk(C.Structure):
+    _fields_ = [("launch", C.c_void_p), ("launch_args", C.c_void_p), ("n_up", C.c_int32), ("n_down", C.c_int32),
+                ("up", C.POINTER(PipeRegion)), ("down", C.POINTER(PipeRegion))]
+
+
 class GenOpArgs(C.Structure):
     _fields_ = [("kind", C.c_int32), ("op", C.c_int32), ("dt_dst", C.c_int32), ("dt_a", C.c_int32),
                 ("dt_b", C.c_int32), ("dt_c", C.c_int32), ("flags", C.c_int32), ("ndim", C.c_int32),
@@ -133,6 +146,11 @@ SYMBOLS = {
     "ktb_graph_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "ktb_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ktb_graph_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ktb_lane_fence": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "ktb_run_pipeline": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
+    "ktb_lane_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "ktb_set_copy_threads": (C.c_int, [C.c_int]),
+    "ktb_copy_threads": (C.c_int, []),
     "ktb_launch_ew_stream": (C.c_int, [C.c_void_p, C.POINTER(EwArgs)]),
     "ktb_launch_row_softmax": (C.c_int, [C.c_void_p, C.POINTER(SoftmaxArgs)]),
     "ktb_launch_rows_program": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
@@ -234,6 +252,17 @@ class Device:
 
     def d2h_raw(self, host_ptr: int, dev_ptr: int, nbytes: int):
         self.check(self.lib.ktb_d2h(self.h, C.c_void_p(host_ptr), C.c_void_p(dev_ptr), nbytes))
+
+    # pipelined transfers: lane 0 = launch stream, 1 = upload lane, 2 = read-back lane
+    def fence(self, src_lane: int, dst_lane: int):
+        self.check(self.lib.ktb_lane_fence(self.h, src_lane, dst_lane))
+
+    def run_pipeline(self, arena: int, chunks, n_chunks: int, pinned, src, n_tensors: int):
+        self.check(self.lib.ktb_run_pipeline(self.h, C.c_void_p(arena), chunks, n_chunks, pinned, src, n_tensors))
+
+    def lane_d2h(self, host_ptr: int, dev_ptr: int, width: int, height: int = 1, pitch: int = 0):
+        self.check(self.lib.ktb_lane_d2h(self.h, C.c_void_p(host_ptr), C.c_void_p(dev_ptr), width, height,
+                                         pitch or width))
 
     def sync(self) -> Status:
         st = Status()

@@ -127,3 +127,60 @@ def test_slab_exchange_over_gloo_world2():
     out = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert dict(out) == {0: True, 1: True}
+
+
+SHIFT = """module {
+  func.func @shift(%x_ptr: index) attributes {grid = [4, 1]} {
+    %c = ktdp.get_compute_tile_id : index
+    %c1 = arith.constant 1 : index
+    %c4 = arith.constant 4 : index
+    %blk = arith.constant 64 : index
+    %n1 = arith.addi %c, %c1 : index
+    %nb = arith.remui %n1, %c4 : index
+    %src = arith.muli %nb, %blk : index
+    %dst = arith.muli %c, %blk : index
+    %v = ktdp.construct_memory_view %x_ptr, sizes: [256], strides: [1] {
+      coordinate_set = affine_set<(d0) : (d0 >= 0, -d0 + 255 >= 0)>, memory_space = #ktdp.memory_space<global>
+    } : memref<256xf16>
+    %rt = ktdp.construct_access_tile %v[%src] {
+      access_tile_set = affine_set<(d0) : (d0 >= 0, -d0 + 63 >= 0)>, access_tile_order = affine_map<(d0) -> (d0)>
+    } : memref<256xf16> -> !ktdp.access_tile<64xindex>
+    %wt = ktdp.construct_access_tile %v[%dst] {
+      access_tile_set = affine_set<(d0) : (d0 >= 0, -d0 + 63 >= 0)>, access_tile_order = affine_map<(d0) -> (d0)>
+    } : memref<256xf16> -> !ktdp.access_tile<64xindex>
+    %t = ktdp.load %rt : !ktdp.access_tile<64xindex> -> tensor<64xf16>
+    ktdp.store %t, %wt : tensor<64xf16>, !ktdp.access_tile<64xindex>
+    return
+  }
+}
+"""
+
+
+def test_cross_rank_read_after_write_is_rejected_like_on_one_gpu():
+    """Core c reads the block core c+1 writes: the sequential core order matters.  Inside one rank's
+    slice nothing clashes (with one core per rank there is no second core at all), so the whole grid
+    has to be checked."""
+    from ktir_cpu_b200.trace import Unsupported
+    t = [("x_ptr", (256,), np.dtype(np.float16))]
+    with pytest.raises(Unsupported, match="sequential core order"):
+        _plan(SHIFT, "shift", t, 0, 1)
+    for rank in range(4):
+        with pytest.raises(Unsupported, match="sequential core order"):
+            _plan(SHIFT, "shift", t, rank, 4)
+
+
+def test_a_rank_moves_only_its_own_slabs():
+    rows, cols = 4096, 4096
+    t = [("output_ptr", (rows, cols), np.dtype(np.float16)), ("input_ptr", (rows, cols), np.dtype(np.float16))]
+    s = _plan(K.softmax_rows(rows, cols, 32, 8, True), "softmax_kernel", t, 1, 4)
+    tp = s.transfer_plan()
+    assert tp.partial and tp.host_only == []
+    assert tp.h2d_bytes == tp.d2h_bytes == rows * cols * 2 // 4
+    in_off = s.layout["input_ptr"][0]
+    lo = min(r.off for c in tp.chunks for r in c.uploads)
+    assert lo == in_off + rows * cols * 2 // 4          # rank 1 starts at its first row
+    sc = _plan(K.gather_scale_scatter(1024, 128, 16384, 64, 8), "gather_scale_scatter",
+               [("table_ptr", (1024, 128), np.dtype(np.float16)), ("idx_ptr", (16384,), np.dtype(np.int32)),
+                ("out_ptr", (1024, 128), np.dtype(np.float16))], 2, 4)
+    tps = sc.transfer_plan()
+    assert not tps.split and tps.d2h_bytes == 1024 * 128 * 2 // 4       # only the destination rows it owns come back
