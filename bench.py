@@ -1,15 +1,31 @@
 """Benchmark of the KTIR execution hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+                    [--no-extras] [--no-cpu]
 
-Default workload (the one the headline metric is quoted on): row softmax over
-f16[8192, 4096] with f32 statistics, 32 KTIR cores x 256 contiguous rows.  One
-"step" is one pass of the hot path over the whole workload: the launch plan of
-the KTIR function on tensors resident in HBM.  Prints ONE JSON line (rank 0).
-``--impl reference`` times the CPU restatement of the reference interpreter
-(oracle/) on the host cores instead.  Other workloads (vector_add,
-gather_scatter, matmul, attention) report the same fields for the other
-benchmark configurations.
+Headline workload (the one the metric is quoted on): row softmax over f16[8192, 4096] with f32
+statistics, 32 KTIR cores x 256 contiguous rows.  One "step" is one pass of the hot path over the
+whole workload.  Prints ONE JSON line (rank 0):
+
+* ``value``     elements/s with the tensors resident in HBM, each step timed by CUDA events on the
+                launch stream, L2 flushed between steps;
+* ``roofline``  algorithmic bytes (or FLOP) / mean launch time against the measured peak; for the
+                HBM-bound kernels also ``frac_sustained``: eight back-to-back launches over eight
+                distinct buffer sets (together far larger than L2), one event pair, no flush, so
+                the write-back of each launch's output is paid inside the window;
+* ``e2e``       the same metric through ``KTIRInterpreter.execute_function`` with host arrays in
+                and fresh host arrays out every step (page-locked caller arrays; ``pageable`` is the
+                same with ordinary NumPy arrays);
+* ``cpu_baseline``  the reference interpreter itself (``baseline/_ref``, else the oracle port) on
+                the host cores, on a bounded sample of the same workload;
+* ``extras``    the same report for the other configurations (vector add, gather + ordered scatter,
+                tiled matmul, causal attention, the 512-variant candidate sweep).
+
+With N > 1 (one process per GPU, launched by torchrun) ONE instance of N times the rows is split by
+core range: rank r runs cores [32 r, 32 r + 32), uploads only the rows they read and reads back
+only the rows they wrote; nothing is exchanged (``scaling: weak``).  ``extras.strong`` is the
+fixed 8192-row instance split the same way, ``extras.candidates`` the sweep with candidate i on
+rank i mod N.  ``--impl reference`` times the reference interpreter on the host cores instead.
 """
 from __future__ import annotations
 
@@ -25,26 +41,25 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 
 # ---------------------------------------------------------------------------
 # Workloads: KTIR source, seeded synthetic inputs, algorithmic work per step
 # ---------------------------------------------------------------------------
 class Workload:
-    name = ""
-    func = ""
+    name = func = kernel = describe = metric = ""
     unit = "elem/s"
     bound = "hbm"
-    kernel = ""
     dtype = "f32"
     units_per_step = 0          # elements (or FLOP) one step processes
     algo_per_step = 0           # algorithmic bytes (hbm) or FLOP (tensor) of the dominant kernel
-    describe = ""
+    cpu_ladder = ()             # (size, rough seconds on one core of the reference) for CPU samples
 
     def source(self): ...
     def inputs(self, rank=0): ...
     def check(self, kw, res): return None
-    def cpu_case(self, procs): ...     # (source, func, kwargs, units) of a bounded CPU sample
+    def cpu_case(self, size, seed): ...     # (source, func, kwargs, units) of a bounded CPU sample
 
 
 def _rows_fix(rows, cores, r):
@@ -56,11 +71,16 @@ def _rows_fix(rows, cores, r):
 
 class Softmax(Workload):
     name, func, kernel = "softmax", "softmax_kernel", "ktb_row_softmax_fast_kernel"
-    R, C, CORES, RPI = 8192, 4096, 32, 8
-    units_per_step = R * C
-    algo_per_step = 2 * R * C * 2
-    describe = "row_softmax f16[8192,4096], grid 32 cores x 256 rows, 8 rows/iteration, f32 stats"
+    C, RPI = 4096, 8
     metric = "KTIR exec throughput (row softmax 8192x4096 f16, f32 stats)"
+    cpu_ladder = ((512, 0.3), (2048, 1.4), (4096, 6.0), (8192, 24.0))
+
+    def __init__(self, scale=1):
+        self.R, self.CORES = 8192 * scale, 32 * scale
+        self.units_per_step = self.R * self.C
+        self.algo_per_step = 2 * self.R * self.C * 2
+        self.describe = (f"row_softmax f16[{self.R},4096], grid {self.CORES} cores x 256 rows, 8 rows/iteration, "
+                         "f32 stats")
 
     def source(self):
         from ktir_cpu_b200 import kernels as K
@@ -69,25 +89,29 @@ class Softmax(Workload):
     def _x(self, rows, seed):
         return (np.random.default_rng(seed).standard_normal((rows, self.C), dtype=np.float32) * 2).astype(np.float16)
 
-    def inputs(self, rank=0):
-        x = self._x(self.R, 2 + rank)
+    def inputs(self, rank=0, rows=None):
+        """``rows = (lo, hi)``: only these rows carry data (a rank's share of a split instance)."""
+        if rows is None:
+            x = self._x(self.R, 2 + rank)
+        else:
+            x = np.zeros((self.R, self.C), np.float16)
+            x[rows[0]:rows[1]] = self._x(rows[1] - rows[0], 2 + rank)
         return dict(output_ptr=np.zeros_like(x), input_ptr=x)
 
-    def check(self, kw, res):
+    def check(self, kw, res, rows=None):
         x, y = kw["input_ptr"], res["output_ptr"]
-        rows = np.arange(0, self.R, 257)
-        xf = np.asarray(x[rows], dtype=np.float32)
+        lo, hi = rows or (0, self.R)
+        pick = np.arange(lo, hi, 257)
+        xf = np.asarray(x[pick], dtype=np.float32)
         e = np.exp(xf - xf.max(1, keepdims=True))
-        return float(np.abs(y[rows].astype(np.float32) - e / e.sum(1, keepdims=True)).max())
+        return float(np.abs(y[pick].astype(np.float32) - e / e.sum(1, keepdims=True)).max())
 
     def cpu_case(self, rows, seed=2):
         from ktir_cpu_b200 import kernels as K
-        cores = _rows_fix(rows, self.CORES, self.RPI)
+        cores = _rows_fix(rows, 32, self.RPI)
         x = self._x(rows, seed)
         return (K.softmax_rows(rows, self.C, cores, self.RPI, True), self.func,
                 dict(output_ptr=np.zeros_like(x), input_ptr=x), rows * self.C)
-
-    cpu_full, cpu_small = 8192, 8192
 
 
 class VectorAdd(Workload):
@@ -98,6 +122,7 @@ class VectorAdd(Workload):
     describe = "vector_add f16[2^26], 32 cores x 16 blocks of 131072 (scaled twin of the 4096-element example)"
     metric = "KTIR exec throughput (vector_add 2^26 f16)"
     dtype = "f16"
+    cpu_ladder = ((1 << 22, 0.3), (1 << 24, 3.0), (1 << 26, 23.0))
 
     def source(self):
         from ktir_cpu_b200 import kernels as K
@@ -122,8 +147,6 @@ class VectorAdd(Workload):
         return (K.vector_add(n, blk, 32), self.func,
                 dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(n, np.float16), BLOCK_SIZE=blk), n)
 
-    cpu_full, cpu_small = 1 << 26, 1 << 26
-
 
 class GatherScatter(Workload):
     name, func, kernel = "gather_scatter", "gather_scale_scatter", "ktb_scatter_apply_axpy128_kernel"
@@ -134,6 +157,8 @@ class GatherScatter(Workload):
                 "64-row tiles with 6 duplicates per tile, 64 cores")
     metric = "KTIR exec throughput (indirect gather+scatter, gathered elements)"
     dtype = "f16"
+    accumulates = "out_ptr"       # the kernel adds into this tensor: re-uploaded before the timed region
+    cpu_ladder = ((2048, 2.6), (4096, 5.1), (8192, 10.7))
 
     def _idx(self, rng, rows, n):
         idx = rng.integers(0, rows, n)
@@ -151,8 +176,18 @@ class GatherScatter(Workload):
         table = rng.standard_normal((self.ROWS, self.COLS), dtype=np.float32).astype(np.float16)
         return dict(table_ptr=table, idx_ptr=self._idx(rng, self.ROWS, self.NIDX), out_ptr=np.zeros_like(table))
 
-    def reset(self, sess, kw):
-        sess.upload("out_ptr", kw["out_ptr"])      # the kernel accumulates into out
+    def check(self, kw, res):
+        idx = kw["idx_ptr"].reshape(-1, self.TILE)[:64]
+        rows = np.unique(idx)
+        counts = np.zeros(self.ROWS, np.int64)
+        for t in kw["idx_ptr"].reshape(-1, self.TILE):
+            counts[np.unique(t)] += 1
+        h = (kw["table_ptr"][rows] * np.float16(0.5)).astype(np.float16)
+        acc = np.zeros_like(h)
+        for n in range(1, int(counts[rows].max()) + 1):
+            m = counts[rows] >= n
+            acc[m] = acc[m] + h[m]
+        return float(np.abs(res["out_ptr"][rows].astype(np.float32) - acc.astype(np.float32)).max())
 
     def cpu_case(self, n, seed=3):
         from ktir_cpu_b200 import kernels as K
@@ -164,8 +199,6 @@ class GatherScatter(Workload):
                 dict(table_ptr=table, idx_ptr=self._idx(rng, rows, n), out_ptr=np.zeros_like(table)),
                 n * self.COLS)
 
-    cpu_full, cpu_small = 262144, 131072
-
 
 class Matmul(Workload):
     name, func, kernel = "matmul", "matmul_kernel", "ktb_gemm_f16_kernel"
@@ -175,6 +208,7 @@ class Matmul(Workload):
     algo_per_step = units_per_step
     describe = "tiled matmul f16 4096^3, 64x64 tiles, K-step 64, 32 cores x 128 tiles, f32 accumulate"
     metric = "KTIR exec throughput (tiled matmul 4096^3 f16, f32 accumulate)"
+    cpu_ladder = ((512, 0.2), (1024, 1.5), (2048, 12.0))
 
     def source(self):
         from ktir_cpu_b200 import kernels as K
@@ -196,76 +230,80 @@ class Matmul(Workload):
         rng = np.random.default_rng(seed)
         a = rng.uniform(-1, 1, (n, n)).astype(np.float16)
         b = rng.uniform(-1, 1, (n, n)).astype(np.float16)
-        tiles = (n // 64) ** 2
-        cores = min(32, tiles)
+        cores = min(32, (n // 64) ** 2)
         return (K.tiled_matmul(n, n, n, 64, 64, 64, cores, True), self.func,
                 dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((n, n), np.float16)), 2 * n ** 3)
 
-    cpu_full, cpu_small = 2048, 2048
+
+def attention_kwargs(rng, S, H, D, tn):
+    """Inputs of a ``paged_attention_kernel`` call that is dense causal attention: identity block
+    table, no context before the queries."""
+    q, k, v = (rng.standard_normal((S, H, D), dtype=np.float32).astype(np.float16) for _ in range(3))
+    nt = S // tn
+    return dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(nt, tn, H, D),
+                value_cache_ptr=v.reshape(nt, tn, H, D), block_tables_ptr=np.arange(nt, dtype=np.int32).reshape(1, -1),
+                cur_batch_start_index=0, block_table_offset=0, num_tiles=nt, context_len=0,
+                scale=np.float32(1.0 / np.sqrt(D)))
+
+
+def attention_check(kw, out, h):
+    S, D = kw["query_ptr"].shape[0], kw["query_ptr"].shape[2]
+    q = kw["query_ptr"][:, h].astype(np.float64)
+    k = kw["key_cache_ptr"][:, :, h].reshape(S, D).astype(np.float64)
+    v = kw["value_cache_ptr"][:, :, h].reshape(S, D).astype(np.float64)
+    sc = np.where(np.tril(np.ones((S, S), bool)), q @ k.T / np.sqrt(D), -np.inf)
+    p = np.exp(sc - sc.max(-1, keepdims=True))
+    return float(np.abs(out[:, h].astype(np.float64) - (p / p.sum(-1, keepdims=True)) @ v).max())
 
 
 class Attention(Workload):
-    name, func, kernel = "attention", "attention_kernel", "ktb_attention_fwd_kernel"
+    name, func, kernel = "attention", "paged_attention_kernel", "ktb_attention_fwd_kernel"
     S, H, D, TM, TN = 2048, 256, 128, 128, 128
     unit, bound = "FLOP/s", "tensor"
     units_per_step = 4 * H * D * (S * (S + 1) // 2)
     algo_per_step = units_per_step
-    describe = ("causal attention f16 B8 H32 (batch folded into 256 heads) S2048 D128, paged K/V with identity "
-                "block table, tiles 128x128, f32 online softmax")
+    describe = ("causal attention f16 B8 H32 (batch folded into 256 heads) S2048 D128: the paged-attention kernel "
+                "shape of the reference's generator, identity block table, tiles 128x128, f32 online softmax")
     metric = "KTIR exec throughput (causal attention B8 H32 S2048 D128, causal FLOP)"
+    cpu_ladder = ((256, 0.8), (512, 3.0), (1024, 12.0), (2048, 49.0))
 
     def source(self):
         from ktir_cpu_b200 import kernels as K
-        return K.causal_attention(self.S, self.H, self.D, self.TM, self.TN)
-
-    def _kw(self, rng, S, H):
-        D, tn = self.D, self.TN
-        q, k, v = (rng.standard_normal((S, H, D), dtype=np.float32).astype(np.float16) for _ in range(3))
-        return dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(S // tn, tn, H, D),
-                    value_cache_ptr=v.reshape(S // tn, tn, H, D),
-                    block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
-                    num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D)))
+        return K.paged_attention(self.S, self.S, self.H, self.H, self.D, self.TN, self.TM)
 
     def inputs(self, rank=0):
-        return self._kw(np.random.default_rng(5 + rank), self.S, self.H)
+        return attention_kwargs(np.random.default_rng(5 + rank), self.S, self.H, self.D, self.TN)
 
     def check(self, kw, res):
-        h = 3
-        q = kw["query_ptr"][:, h].astype(np.float64)
-        k = kw["key_cache_ptr"][:, :, h].reshape(self.S, self.D).astype(np.float64)
-        v = kw["value_cache_ptr"][:, :, h].reshape(self.S, self.D).astype(np.float64)
-        sc = q @ k.T / np.sqrt(self.D)
-        sc = np.where(np.tril(np.ones((self.S, self.S), bool)), sc, -np.inf)
-        p = np.exp(sc - sc.max(-1, keepdims=True))
-        p /= p.sum(-1, keepdims=True)
-        return float(np.abs(res["output_ptr"][:, h].astype(np.float64) - p @ v).max())
+        return attention_check(kw, res["output_ptr"], 3)
 
     def cpu_case(self, S, seed=5):
         from ktir_cpu_b200 import kernels as K
-        H = 1
-        return (K.causal_attention(S, H, self.D, self.TM, self.TN), self.func,
-                self._kw(np.random.default_rng(seed), S, H), 4 * H * self.D * (S * (S + 1) // 2))
-
-    cpu_full, cpu_small = 2048, 2048
+        return (K.paged_attention(S, S, 1, 1, self.D, self.TN, self.TM), self.func,
+                attention_kwargs(np.random.default_rng(seed), S, 1, self.D, self.TN),
+                4 * self.D * (S * (S + 1) // 2))
 
 
 WORKLOADS = {w.name: w for w in (Softmax(), VectorAdd(), GatherScatter(), Matmul(), Attention())}
 
 
-def workload_config(w, n_gpus):
-    return {"workload": w.describe, "units_per_step_per_gpu": w.units_per_step,
-            "sharding": f"one independent replica of the workload per GPU (x{n_gpus}), no collective",
-            "l2": "flushed (256 MiB memset) between timed steps; each step timed by CUDA events on the launch stream"}
-
-
 def measured_peak(bound):
-    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
-        d = json.load(open(p))
+        d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         return (float(d["hbm_gbs"]), "GB/s", "measured (MEASURED_PEAKS.json)") if bound == "hbm" else \
             (float(d["bf16_tflops"]), "TFLOP/s", "measured burst (MEASURED_PEAKS.json)")
     except Exception:
         return (6650.0, "GB/s", "fallback") if bound == "hbm" else (1590.0, "TFLOP/s", "fallback")
+
+
+def dram_traffic(name):
+    """DRAM read + write bytes of one launch of the dominant kernel, from the ncu capture summarised
+    under profiles/."""
+    try:
+        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(name)
+        return t["dram_read_bytes"] + t["dram_write_bytes"] if t else None
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -275,7 +313,7 @@ class ClockSampler:
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.rows, self.proc, self.idx = [], None, gpu_index
+        self.rows, self.proc, self.idx, self.first = [], None, gpu_index, 0
 
     def start(self):
         try:
@@ -291,8 +329,7 @@ class ClockSampler:
             self.proc = None
 
     def under_load(self):
-        """Samples taken since start() returned."""
-        return len(self.rows) - getattr(self, "first", 0)
+        return len(self.rows) - self.first
 
     def _read(self):
         for line in self.proc.stdout:
@@ -302,17 +339,17 @@ class ClockSampler:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
-        self.rows = self.rows[getattr(self, "first", 0):]
+        rows = self.rows[self.first:]
 
         def num(s):
             try:
                 return float(s)
             except ValueError:
                 return None
-        sm = [num(r[1]) for r in self.rows if len(r) > 8 and num(r[1]) is not None]
-        mx = [num(r[2]) for r in self.rows if len(r) > 8 and num(r[2]) is not None]
+        sm = [num(r[1]) for r in rows if len(r) > 8 and num(r[1]) is not None]
+        mx = [num(r[2]) for r in rows if len(r) > 8 and num(r[2]) is not None]
         reasons = set()
-        for r in self.rows:
+        for r in rows:
             if len(r) > 8:
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
                     if v.lower().startswith("active"):
@@ -322,13 +359,26 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------
-# CPU side: the oracle port of the reference interpreter
+# CPU side: the reference interpreter (baseline/_ref) or, without it, the oracle port
 # ---------------------------------------------------------------------------
+def reference_available():
+    return os.path.isdir(os.path.join(REF_DIR, "ktir_cpu"))
+
+
+def _cpu_interpreter():
+    if reference_available():
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        from ktir_cpu import KTIRInterpreter
+        return KTIRInterpreter()
+    from oracle.numpy_interp import OracleInterpreter
+    return OracleInterpreter()
+
+
 def _cpu_worker(args):
     name, size, seed = args
-    from oracle.numpy_interp import OracleInterpreter
     src, fn, kw, units = WORKLOADS[name].cpu_case(size, seed)
-    it = OracleInterpreter()
+    it = _cpu_interpreter()
     it.load(src)
     t0 = time.perf_counter()
     it.execute_function(fn, **kw)
@@ -336,44 +386,79 @@ def _cpu_worker(args):
 
 
 def _cpu_import(_):
-    import oracle.numpy_interp  # noqa: F401
+    _cpu_interpreter()
     import ktir_cpu_b200.kernels  # noqa: F401
     return 0
 
 
-def cpu_sample(w, procs, size):
-    """units/s of the oracle on `procs` host processes, each running its own instance."""
+def host_cores():
+    try:
+        return max(1, min(len(os.sched_getaffinity(0)), 32))
+    except AttributeError:
+        return max(1, min(os.cpu_count() or 1, 32))
+
+
+def ladder_size(w, per_step_s):
+    """Largest sample of ``w`` the reference finishes in about ``per_step_s`` on one core (the port is
+    roughly ten times faster, so it gets the largest)."""
+    if not reference_available():
+        return w.cpu_ladder[-1][0]
+    ok = [s for s, t in w.cpu_ladder if t <= per_step_s]
+    return ok[-1] if ok else w.cpu_ladder[0][0]
+
+
+def cpu_sample(w, procs, size, pool=None):
+    """units/s of the CPU interpreter on ``procs`` host processes, each running its own instance
+    of the kernel at ``size`` (seeds differ).  Returns (units/s, seconds)."""
     import multiprocessing as mp
-    if procs == 1:
-        dt, units = _cpu_worker((w.name, size, 2))
-        return units / dt, dt
-    with mp.get_context("spawn").Pool(procs) as pool:
+    own = pool is None
+    if own:
+        pool = mp.get_context("spawn").Pool(procs)
         pool.map(_cpu_import, range(procs))       # interpreter start-up stays outside the timing
+    try:
         t0 = time.perf_counter()
         out = pool.map(_cpu_worker, [(w.name, size, 2 + i) for i in range(procs)])
         dt = time.perf_counter() - t0
+    finally:
+        if own:
+            pool.close()
     return sum(u for _, u in out) / dt, dt
 
 
+def cpu_baseline(w, per_step_s=20.0):
+    procs = host_cores()
+    size = ladder_size(w, per_step_s)
+    v, dt = cpu_sample(w, procs, size)
+    kind = "reference" if reference_available() else "port"
+    what = "the reference interpreter (baseline/_ref)" if kind == "reference" else "oracle/numpy_interp.py"
+    return {"value": v, "unit": w.unit, "cores": procs, "kind": kind,
+            "sample": f"{procs} processes, each the same KTIR kernel at size {size} (full size "
+                      f"{w.cpu_ladder[-1][0]}) through {what}, NumPy {np.__version__}, {dt:.1f} s"}
+
+
 def run_reference(args, w):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    procs = max(1, min(os.cpu_count() or 1, 32))
-    size = w.cpu_small
+    import multiprocessing as mp
+    procs = host_cores()
+    size = ladder_size(w, 150.0 / max(1, args.steps + args.warmup))
+    kind = "reference" if reference_available() else "port"
     res = []
-    for i in range(args.warmup + args.steps):
-        v, dt = cpu_sample(w, procs, size)
-        if i >= args.warmup:
-            res.append((v, dt))
+    with mp.get_context("spawn").Pool(procs) as pool:
+        pool.map(_cpu_import, range(procs))
+        for i in range(args.warmup + args.steps):
+            v, dt = cpu_sample(w, procs, size, pool)
+            if i >= args.warmup:
+                res.append((v, dt))
     value = float(np.mean([v for v, _ in res]))
-    sample = (f"{procs} processes, each the same KTIR kernel at size {size} "
-              f"(oracle/numpy_interp.py, NumPy {np.__version__})")
+    what = "the unmodified reference package (baseline/_ref)" if kind == "reference" else "oracle/numpy_interp.py"
+    sample = (f"{procs} processes, each the same KTIR kernel at size {size} (full size {w.cpu_ladder[-1][0]}) "
+              f"through {what}, NumPy {np.__version__}")
     line = {"impl": "reference", "metric": w.metric, "value": value, "unit": w.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean([dt for _, dt in res])) * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.dtype,
-            "data": "synthetic", "config": workload_config(w, args.gpus),
-            "cpu_baseline": {"value": value, "unit": w.unit, "cores": procs, "kind": "port", "sample": sample},
+            "data": "synthetic", "config": {"workload": w.describe, "units_per_step_per_gpu": w.units_per_step},
+            "cpu_baseline": {"value": value, "unit": w.unit, "cores": procs, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": w.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -381,198 +466,206 @@ def run_reference(args, w):
 # ---------------------------------------------------------------------------
 # GPU side
 # ---------------------------------------------------------------------------
-def run_gpu(args, w):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+class Dist:
+    """torch.distributed when there is more than one rank, no-ops otherwise."""
 
-    from ktir_cpu_b200.interpreter import KTIRInterpreter
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.d = None
+        if self.world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(self.local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.d, self.torch = dist, torch
+
+    def barrier(self):
+        if self.d is not None:
+            self.d.barrier()
+
+    def max(self, *vals):
+        if self.d is None:
+            return [float(v) for v in vals]
+        t = self.torch.tensor(list(vals), device="cuda", dtype=self.torch.float64)
+        self.d.all_reduce(t, op=self.d.ReduceOp.MAX)
+        return [float(x) for x in t]
+
+    def close(self):
+        if self.d is not None:
+            self.d.destroy_process_group()
+
+
+def pin_near_gpu(local):
+    """Keep this process (and its copy threads) on the CPUs of the GPU's NUMA node, so that eight
+    ranks do not all stage through one node's memory.  Read-only look-ups; nothing is changed on
+    the GPU."""
+    try:
+        bus = subprocess.run(["nvidia-smi", "--query-gpu=pci.bus_id", "--format=csv,noheader", "-i", str(local)],
+                             capture_output=True, text=True, timeout=10).stdout.strip().lower()
+        if bus.startswith("00000000:"):
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return node
+    except Exception:
+        pass
+    return None
+
+
+def pinned_copy(dev, kw):
     from ktir_cpu_b200.pinned import pinned_empty
-
-    interp = KTIRInterpreter(device=local)
-    interp.load(w.source())
-    dev = interp.device
-    kw = {}
-    for k, v in w.inputs(rank).items():
+    out = {}
+    for k, v in kw.items():
         if isinstance(v, np.ndarray):
             p = pinned_empty(dev, v.shape, v.dtype)
             p[...] = v
-            kw[k] = p
+            out[k] = p
         else:
-            kw[k] = v
-    sess, _ = interp.session(w.func, **kw)
-    for k, v in kw.items():
-        if isinstance(v, np.ndarray):
-            sess.upload(k, v)
-    dev.sync()
+            out[k] = v
+    return out
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
 
-    warm = max(args.warmup, 3)
+def time_device(dev, run, steps, warm):
+    """Per-step milliseconds of ``run()``: CUDA events on the launch stream, L2 flushed before each."""
     for _ in range(warm):
-        sess.run()
+        run()
     dev.sync()
-    if hasattr(w, "reset"):
-        w.reset(sess, kw)
-        dev.sync()
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    barrier()
-    dev.sync()
-    l0 = dev.launch_count()
     per_step = []
-    for _ in range(args.steps):
+    l0 = dev.launch_count()
+    for _ in range(steps):
         dev.flush_l2()
         dev.record(0)
-        sess.run()
+        run()
         dev.record(1)
         dev.sync()
         per_step.append(dev.elapsed_ms(0, 1))
-    launches = dev.launch_count() - l0
-    dev.sync()
-    # a timed region shorter than the sampling period: keep the same load running (untimed) until
-    # the sampler has seen it a few times
-    t_extra = time.time()
-    while sampler.proc is not None and sampler.under_load() < 4 and time.time() - t_extra < 3.0:
-        sess.run()
+    return per_step, dev.launch_count() - l0
+
+
+def time_sustained(dev, sess, sets=8, reps=3):
+    """Milliseconds per launch when ``sets`` launches over distinct copies of the arena run back to
+    back inside one event pair (no flush): steady-state streaming, deferred write-back included."""
+    size = sess.arena_bytes + 256
+    arenas = [sess.arena] + [dev.alloc(size) for _ in range(sets - 1)]
+    try:
+        for a in arenas[1:]:
+            dev.check(dev.lib.ktb_d2d(dev.h, a, sess.arena, sess.arena_bytes))
         dev.sync()
-    barrier()
-    clocks = sampler.stop()
+        best = None
+        for _ in range(reps + 1):
+            dev.flush_l2()
+            dev.record(2)
+            for a in arenas:
+                sess.plan.launch(dev, a)
+            dev.record(3)
+            dev.sync()
+            ms = dev.elapsed_ms(2, 3) / sets
+            best = ms if best is None else min(best, ms)
+        return best
+    finally:
+        for a in arenas[1:]:
+            dev.free(a)
+
+
+def time_e2e(call, steps, warm=3):
+    """Seconds per call of ``call()`` (host arrays in, fresh host arrays out), results of the previous
+    call still alive while the next one runs, as in a caller's loop."""
+    res = None
+    for _ in range(warm):
+        res = call()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        res = call()
+    return (time.perf_counter() - t0) / steps, res
+
+
+def report(w, interp, kw_host, steps, warm, dist, clocks_for=None, shard=None, world_units=1, cpu=True,
+           sustained=True, check_rows=None):
+    """Device-timed throughput, roofline, end-to-end and CPU baseline of one workload."""
+    dev = interp.device
+    kw = pinned_copy(dev, kw_host)
+    sess, _ = interp.session(w.func, _shard=shard, **kw)
+    tp = sess.transfer_plan()
+    for k, v in kw.items():
+        if isinstance(v, np.ndarray) and k not in sess.no_upload:
+            sess.upload(k, v)
+    dev.sync()
+    sampler = None
+    if clocks_for is not None:
+        sampler = ClockSampler(clocks_for)
+        sampler.start()
+    for _ in range(warm):
+        sess.run()
+    if getattr(w, "accumulates", None):
+        sess.upload(w.accumulates, kw[w.accumulates])
+    dev.sync()
+    dist.barrier()
+    per_step, launches = time_device(dev, sess.run, steps, 0)
+    if sampler is not None:
+        # a timed region shorter than the sampling period: keep the same load running (untimed) until
+        # the sampler has seen it a few times
+        t_extra = time.time()
+        while sampler.proc is not None and sampler.under_load() < 4 and time.time() - t_extra < 3.0:
+            sess.run()
+            dev.sync()
+    dist.barrier()
+    clocks = sampler.stop() if sampler is not None else None
     total_ms = float(sum(per_step))
 
-    # end to end through the public API: host (pinned) buffers in, fresh host arrays out, every step
-    for _ in range(2):
-        interp.execute_function(w.func, **kw)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        res = interp.execute_function(w.func, **kw)
-    e2e_s = time.perf_counter() - t0
-    h2d, d2h = int(sess.last_h2d_bytes), int(sess.last_d2h_bytes)
-    err = w.check(kw, res) if not hasattr(w, "reset") else None
-
-    if dist is not None:
-        import torch
-        t = torch.tensor([total_ms, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_s = float(t[0]), float(t[1])
-    if rank == 0:
-        ms_per_step = total_ms / args.steps
-        value = world * w.units_per_step / (ms_per_step * 1e-3)
-        peak, punit, peak_src = measured_peak(w.bound)
-        achieved = w.algo_per_step / (ms_per_step * 1e-3) / (1e9 if w.bound == "hbm" else 1e12)
-        traffic = None
-        tp = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tp):
-            t = json.load(open(tp)).get(w.name)
-            if t:        # DRAM bytes of one launch of the dominant kernel, from the ncu capture summarised in profiles/
-                traffic = t["dram_read_bytes"] + t["dram_write_bytes"]
-        line = {"metric": w.metric, "value": value, "unit": w.unit, "n_gpus": world, "steps": args.steps,
-                "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": w.dtype, "data": "synthetic", "config": workload_config(w, world),
-                "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": punit,
-                             "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
-                             "algorithmic_per_launch": w.algo_per_step, "kernel": w.kernel},
-                "e2e": {"value": world * w.units_per_step * args.steps / e2e_s, "unit": w.unit,
-                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s / args.steps * 1e3},
-                "gpu_launches": int(launches), "clocks": clocks, "max_abs_err_spot_check": err}
-        if world == 1 and not args.no_cpu:
-            v, dt = cpu_sample(w, 1, w.cpu_small)
-            line["cpu_baseline"] = {"value": v, "unit": w.unit, "cores": 1, "kind": "port",
-                                    "sample": f"same KTIR kernel at size {w.cpu_small} through "
-                                              f"oracle/numpy_interp.py on 1 core, {dt:.2f} s"}
-        print(json.dumps(line))
-    interp.close()
-    if dist is not None:
-        dist.destroy_process_group()
-
-
-def run_sharded(args, w):
-    """Strong scaling: ONE instance of the workload split over the ranks (core ranges, or
-    destination-row ownership for the ordered scatter), each step = this rank's launches + the
-    exchange of the written slabs over NCCL, so every rank ends with the full result."""
-    import torch
-    import torch.distributed as dist
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    from ktir_cpu_b200.interpreter import KTIRInterpreter
-    from ktir_cpu_b200.sharded import ShardedRun
-    interp = KTIRInterpreter(device=local)
-    interp.load(w.source())
-    kw = w.inputs(0)                                   # the same instance on every rank
-    run = ShardedRun(interp, w.func, rank, world, dist, **kw)
-    dev = interp.device
-    arrays = {k: v for k, v in kw.items() if isinstance(v, np.ndarray)}
-    run.upload(**arrays)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
-        if hasattr(w, "reset"):
-            run.upload(**arrays)
-        run.step()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    sampler.start()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    total_ms = 0.0
-    l0 = dev.launch_count()
-    for _ in range(args.steps):
-        if hasattr(w, "reset"):
-            run.upload(**arrays)
-        dev.flush_l2()
-        torch.cuda.synchronize()
-        barrier()
-        ev0.record()
-        run.step()
-        ev1.record()
-        torch.cuda.synchronize()
-        total_ms += ev0.elapsed_time(ev1)
-    launches = dev.launch_count() - l0
-    for _ in range(200 if sampler.proc is not None else 0):   # same load, untimed, until the sampler has seen it
-        run.step()
-        torch.cuda.synchronize()
-        if world == 1 and sampler.under_load() >= 4:
-            break
-    barrier()
-    clocks = sampler.stop()
-    res = {k: run.download(k) for k in arrays}
-    err = w.check(kw, res) if not hasattr(w, "reset") else None
-    if world > 1:
-        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t[0])
-    if rank == 0:
-        ms = total_ms / args.steps
-        slabs = sum(hi - lo for lo, hi in run.my_ranges)
-        cfg = workload_config(w, 1)
-        cfg["sharding"] = (f"one instance split over {world} GPUs "
-                           f"({'destination-row ownership' if w.name == 'gather_scatter' else 'core ranges'}); "
-                           f"inputs replicated; per step each rank broadcasts its {slabs} B of results (NCCL)")
-        print(json.dumps({"metric": w.metric + " [one instance, sharded]", "value": w.units_per_step / (ms * 1e-3),
-                          "unit": w.unit, "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms,
-                          "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w.dtype,
-                          "data": "synthetic", "config": cfg, "gpu_launches": int(launches), "clocks": clocks,
-                          "max_abs_err_spot_check": err}))
-    run.close()
-    interp.close()
-    if world > 1:
-        dist.destroy_process_group()
+    if shard is None:
+        call_pinned = lambda: interp.execute_function(w.func, **kw)             # noqa: E731
+        call_pageable = lambda: interp.execute_function(w.func, **kw_host)      # noqa: E731
+    else:
+        call_pinned = lambda: interp.execute_shard(w.func, shard[0], shard[1], **kw)          # noqa: E731
+        call_pageable = lambda: interp.execute_shard(w.func, shard[0], shard[1], **kw_host)   # noqa: E731
+    e2e_steps = max(3, min(steps, 10))
+    dist.barrier()
+    e2e_s, res = time_e2e(call_pinned, e2e_steps)
+    if check_rows is not None:
+        err = w.check(kw, res, check_rows)
+    else:
+        err = w.check(kw, res) if shard is None else None      # a rank holds only its slabs
+    dist.barrier()
+    e2e_pg, _ = time_e2e(call_pageable, e2e_steps)
+    del res
+    total_ms, e2e_s, e2e_pg = dist.max(total_ms, e2e_s, e2e_pg)
+    ms = total_ms / steps
+    peak, punit, peak_src = measured_peak(w.bound)
+    scale = 1e9 if w.bound == "hbm" else 1e12
+    units = w.units_per_step * world_units
+    algo = w.algo_per_step // (shard[1] if shard else 1)        # one rank's launch covers its share of the instance
+    achieved = algo / (ms * 1e-3) / scale
+    out = {"metric": w.metric, "workload": w.describe, "value": units / (ms * 1e-3), "unit": w.unit, "ms_per_step": ms,
+           "roofline": {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": punit, "frac": achieved / peak,
+                        "traffic": dram_traffic(w.name), "peak_source": peak_src, "algorithmic_per_launch": algo,
+                        "kernel": w.kernel},
+           "e2e": {"value": units / e2e_s, "unit": w.unit, "h2d_bytes_per_step": int(tp.h2d_bytes),
+                   "d2h_bytes_per_step": int(tp.d2h_bytes), "ms_per_step": e2e_s * 1e3,
+                   "parts": len(tp.chunks), "pageable": {"value": units / e2e_pg, "ms_per_step": e2e_pg * 1e3}},
+           "gpu_launches": int(launches), "max_abs_err_spot_check": err}
+    if clocks is not None:
+        out["clocks"] = clocks
+    if sustained and w.bound == "hbm" and shard is None:
+        if getattr(w, "accumulates", None):
+            sess.upload(w.accumulates, kw[w.accumulates])
+        sms = time_sustained(dev, sess)
+        ach = algo / (sms * 1e-3) / scale
+        out["roofline"]["frac_sustained"] = ach / peak
+        out["roofline"]["sustained"] = {"achieved": ach, "ms_per_launch": sms,
+                                        "how": "8 back-to-back launches over 8 distinct arenas, one event pair, no L2 flush"}
+    if cpu and dist.rank == 0:
+        out["cpu_baseline"] = cpu_baseline(w)
+    return out
 
 
 def candidate_sweep(n=512, B=1, H=4, D=128):
@@ -584,94 +677,169 @@ def candidate_sweep(n=512, B=1, H=4, D=128):
     out, flops = [], 0
     for i in range(n):
         tm, tn, S = (32, 64, 128)[i % 3], (32, 64, 128)[(i // 3) % 3], (512, 1024, 2048)[(i // 9) % 3]
-        rng = np.random.default_rng(1000 + i)
-        q, k, v = (rng.standard_normal((S, B * H, D), dtype=np.float32).astype(np.float16) for _ in range(3))
-        kw = dict(output_ptr=np.zeros_like(q), query_ptr=q, key_cache_ptr=k.reshape(S // tn, tn, B * H, D),
-                  value_cache_ptr=v.reshape(S // tn, tn, B * H, D),
-                  block_tables_ptr=np.arange(S // tn, dtype=np.int32).reshape(1, -1),
-                  num_tiles=S // tn, context_len=0, scale=float(1.0 / np.sqrt(D)))
-        out.append(Candidate(K.causal_attention(S, B * H, D, tm, tn), "attention_kernel", kw, tag=(tm, tn, S)))
+        kw = attention_kwargs(np.random.default_rng(1000 + i), S, B * H, D, tn)
+        out.append(Candidate(K.paged_attention(S, S, B * H, B * H, D, tn, tm), "paged_attention_kernel", kw, tag=(tm, tn, S)))
         flops += 4 * B * H * D * (S * (S + 1) // 2)
     return out, flops
 
 
-def run_candidates(args):
-    """kernels/s over the candidate sweep, host arrays in and out for every candidate (there is
-    no device-resident variant of this metric: a candidate arrives as text + host tensors)."""
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+def _candidate_cpu_worker(i):
+    from ktir_cpu_b200 import kernels as K
+    tm, tn, S = (32, 64, 128)[i % 3], (32, 64, 128)[(i // 3) % 3], (512, 1024, 2048)[(i // 9) % 3]
+    kw = attention_kwargs(np.random.default_rng(1000 + i), S, 4, 128, tn)
+    it = _cpu_interpreter()
+    it.load(K.paged_attention(S, S, 4, 4, 128, tn, tm))
+    t0 = time.perf_counter()
+    it.execute_function("paged_attention_kernel", **kw)
+    return time.perf_counter() - t0
+
+
+def candidates_report(dist, sweeps=2, cpu=True):
+    """kernels/s over the candidate sweep, host arrays in and out for every candidate (there is no
+    device-resident variant of this metric: a candidate arrives as text + host tensors)."""
     from ktir_cpu_b200.batch import BatchRunner
     n = 512
     cands, flops = candidate_sweep(n)
-    runner = BatchRunner(local)
+    runner = BatchRunner(dist.local)
     checks = {}
 
     def score(i, c, out):
-        if i % 9 == rank % 9:                  # spot-check one head of a few variants against f64 math (warm-up pass only)
-            S, h = c.tag[2], 1
-            q = c.kwargs["query_ptr"][:, h].astype(np.float64)
-            k = c.kwargs["key_cache_ptr"][:, :, h].reshape(S, -1).astype(np.float64)
-            v = c.kwargs["value_cache_ptr"][:, :, h].reshape(S, -1).astype(np.float64)
-            sc = np.where(np.tril(np.ones((S, S), bool)), q @ k.T / np.sqrt(q.shape[1]), -np.inf)
-            p = np.exp(sc - sc.max(-1, keepdims=True))
-            checks[i] = float(np.abs(out["output_ptr"][:, h].astype(np.float64) - (p / p.sum(-1, keepdims=True)) @ v).max())
+        if i % 27 == (7 * dist.rank + i // 27) % 27:       # one head of a few variants of every kernel, against f64 math
+            checks[i] = attention_check(c.kwargs, out["output_ptr"], 1)
         return True
-    warm = runner.run(cands[:27 * world], rank, world, score=score, keep_outputs=False)  # every distinct kernel planned once
-    res = runner.run(cands, rank, world, score=None, keep_outputs=True)   # one untimed sweep: the pinned result buffers exist
-    if dist is not None:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    sampler.start()
+    warm = runner.run(cands[:54 * dist.world], dist.rank, dist.world, score=score, keep_outputs=False)
+    res = runner.run(cands, dist.rank, dist.world, keep_outputs=True)   # one untimed sweep: result buffers exist
+    dist.barrier()
     t0 = time.perf_counter()
-    steps = max(1, args.steps // 10)
     launches = 0
-    for _ in range(steps):
-        res = None                            # the consumer is done with the previous sweep's results: their buffers are reused
-        res = runner.run(cands, rank, world, score=None, keep_outputs=True)
+    for _ in range(sweeps):
+        res = None                            # the consumer is done with the previous sweep's results
+        res = runner.run(cands, dist.rank, dist.world, keep_outputs=True)
         launches += res.launches
     dt = time.perf_counter() - t0
-    clocks = sampler.stop()
     errs = len(res.errors) + len(warm.errors)
-    if dist is not None:
-        import torch
-        t = torch.tensor([dt, float(errs)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dt, errs = float(t[0]), int(t[1])
-    if rank == 0:
-        h2d = sum(v.nbytes for c in cands for v in c.kwargs.values() if isinstance(v, np.ndarray)) // n
-        line = {"metric": "candidate kernels evaluated per second (512-variant causal attention sweep)",
-                "value": n * steps / dt, "unit": "kernels/s", "n_gpus": world, "steps": steps, "warmup": 2,
-                "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "512 variants: tile_m,tile_n in {32,64,128}, S in {512,1024,2048}, B=1, H=4, D=128; "
-                                       "variant i on rank i % world; 27 distinct kernels parsed and planned once",
-                           "flops_per_sweep": flops},
-                "e2e": {"value": n * steps / dt, "unit": "kernels/s", "h2d_bytes_per_step": h2d * n,
-                        "d2h_bytes_per_step": h2d * n},
-                "tflops": flops * steps / dt / 1e12, "gpu_launches": int(launches), "clocks": clocks,
-                "failed_candidates": errs, "max_abs_err_spot_check": max(checks.values()) if checks else None}
-        if world == 1 and not args.no_cpu:
-            sys.path.insert(0, ROOT)
-            from oracle.numpy_interp import OracleInterpreter
-            t1 = time.perf_counter()
-            c = cands[0]                          # smallest variant: tile 32x32, S = 512
-            o = OracleInterpreter()
-            o.load(c.source)
-            o.execute_function(c.function, **c.kwargs)
-            d1 = time.perf_counter() - t1
-            line["cpu_baseline"] = {"value": 1.0 / d1, "unit": "kernels/s", "cores": 1, "kind": "port",
-                                    "sample": f"variant 0 (tile 32x32, S=512, the cheapest) through oracle/numpy_interp.py on 1 core, {d1:.1f} s"}
-        print(json.dumps(line))
+    dt, errs, worst = dist.max(dt, float(errs), max(checks.values()) if checks else 0.0)
+    h2d = sum(v.nbytes for c in cands for k, v in c.kwargs.items() if isinstance(v, np.ndarray) and k != "output_ptr")
+    d2h = sum(c.kwargs["output_ptr"].nbytes for c in cands)
+    out = {"metric": "candidate kernels evaluated per second (512-variant causal attention sweep)",
+           "value": n * sweeps / dt, "unit": "kernels/s", "ms_per_step": dt / sweeps * 1e3,
+           "workload": "512 variants: tile_m, tile_n in {32,64,128}, S in {512,1024,2048}, B=1, H=4, D=128; variant i on "
+                       "rank i % world; 27 distinct kernels parsed and planned once",
+           "roofline": {"bound": "tensor", "achieved": flops * sweeps / dt / 1e12, "unit": "TFLOP/s",
+                        "peak": measured_peak("tensor")[0], "frac": flops * sweeps / dt / 1e12 / measured_peak("tensor")[0],
+                        "traffic": None, "note": "whole sweep including host transfers; the sweep is transfer-bound"},
+           "e2e": {"value": n * sweeps / dt, "unit": "kernels/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+           "gpu_launches": int(launches), "failed_candidates": int(errs), "max_abs_err_spot_check": worst}
     runner.close()
-    if dist is not None:
-        dist.destroy_process_group()
+    if cpu and dist.rank == 0:
+        import multiprocessing as mp
+        procs = host_cores()
+        picks = list(range(9))                   # the nine S = 512 variants: the cheapest third of the sweep
+        with mp.get_context("spawn").Pool(min(procs, len(picks))) as pool:
+            pool.map(_cpu_import, range(min(procs, len(picks))))
+            t1 = time.perf_counter()
+            pool.map(_candidate_cpu_worker, picks)
+            d1 = time.perf_counter() - t1
+        kind = "reference" if reference_available() else "port"
+        out["cpu_baseline"] = {"value": len(picks) / d1, "unit": "kernels/s", "cores": min(procs, len(picks)), "kind": kind,
+                               "sample": f"variants 0-8 (S = 512, every tile pair; the cheapest third of the sweep) one per "
+                                         f"process, {d1:.1f} s"}
+    return out
+
+
+def run_gpu(args, w):
+    dist = Dist()
+    from ktir_cpu_b200.interpreter import KTIRInterpreter
+    numa = None
+    if dist.world > 1:
+        from ktir_cpu_b200 import runtime as R
+        R.lib().ktb_set_copy_threads(max(2, min(8, host_cores() // dist.world)))     # the ranks share the host cores
+        numa = pin_near_gpu(dist.local)
+    interp = KTIRInterpreter(device=dist.local)
+    warm = max(args.warmup, 3)
+    cpu = not args.no_cpu
+    if dist.world == 1:
+        interp.load(w.source())
+        head = report(w, interp, w.inputs(0), args.steps, warm, dist, clocks_for=dist.local, cpu=cpu)
+        sharding = "single GPU"
+        scaling = "weak"
+    else:
+        # ONE instance of world x the rows, split by core range: this rank's cores own rows [lo, hi)
+        big = Softmax(dist.world) if w.name == "softmax" else w
+        interp.load(big.source())
+        if w.name == "softmax":
+            rows = (8192 * dist.rank, 8192 * (dist.rank + 1))
+            kw = big.inputs(dist.rank, rows)
+            head = report(big, interp, kw, args.steps, warm, dist, clocks_for=dist.local, shard=(dist.rank, dist.world),
+                          cpu=False, sustained=False, check_rows=rows)
+            head["metric"] = w.metric
+            sharding = (f"one instance of {big.R} rows split over {dist.world} GPUs by core range (32 cores = 8192 rows per "
+                        "rank); a rank uploads the rows its cores read and reads back the rows they wrote; no collective")
+            scaling = "weak"
+        else:
+            kw = big.inputs(0)
+            head = report(big, interp, kw, args.steps, warm, dist, clocks_for=dist.local, shard=(dist.rank, dist.world),
+                          cpu=False, sustained=False)
+            sharding = f"one instance split over {dist.world} GPUs (core ranges / destination-row ownership); no collective"
+            scaling = "strong"
+    line = {"metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": dist.world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": w.dtype, "data": "synthetic",
+            "config": {"workload": head["workload"], "units_per_step_per_gpu": w.units_per_step, "sharding": sharding,
+                       "l2": "flushed (256 MiB written, 256 MiB read) between timed steps; each step timed by CUDA "
+                             "events on the launch stream", "numa_node": numa},
+            "roofline": head["roofline"], "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
+            "clocks": head.get("clocks"), "max_abs_err_spot_check": head["max_abs_err_spot_check"]}
+    if "cpu_baseline" in head:
+        line["cpu_baseline"] = head["cpu_baseline"]
+    interp.close()
+
+    if not args.no_extras:
+        extras = {}
+        if dist.world == 1 and w.name == "softmax":
+            for name in ("vector_add", "gather_scatter", "matmul", "attention"):
+                x = WORKLOADS[name]
+                it = KTIRInterpreter(device=dist.local)
+                it.load(x.source())
+                try:
+                    extras[name] = report(x, it, x.inputs(0), max(5, args.steps // 2), warm, dist, cpu=cpu)
+                except Exception as e:                       # noqa: BLE001 - an extra must not lose the headline
+                    extras[name] = {"error": f"{type(e).__name__}: {e}"}
+                it.close()
+        elif dist.world > 1 and w.name == "softmax":
+            x = WORKLOADS["softmax"]                         # the fixed-size instance, split the same way
+            it = KTIRInterpreter(device=dist.local)
+            it.load(x.source())
+            try:
+                s = report(x, it, x.inputs(0), args.steps, warm, dist, shard=(dist.rank, dist.world), cpu=False,
+                           sustained=False, check_rows=(256 * 32 * dist.rank // dist.world, 256 * 32 * (dist.rank + 1) // dist.world))
+                s["scaling"] = "strong"
+                extras["strong"] = s
+            except Exception as e:                           # noqa: BLE001
+                extras["strong"] = {"error": f"{type(e).__name__}: {e}"}
+            it.close()
+        if w.name == "softmax":
+            try:
+                extras["candidates"] = candidates_report(dist, cpu=cpu and dist.world == 1)
+            except Exception as e:                           # noqa: BLE001
+                extras["candidates"] = {"error": f"{type(e).__name__}: {e}"}
+        line["extras"] = extras
+    if dist.rank == 0:
+        print(json.dumps(line))
+    dist.close()
+
+
+def run_candidates(args):
+    dist = Dist()
+    out = candidates_report(dist, sweeps=max(1, args.steps // 10), cpu=not args.no_cpu)
+    if dist.rank == 0:
+        line = {"metric": out["metric"], "value": out["value"], "unit": out["unit"], "n_gpus": dist.world,
+                "steps": max(1, args.steps // 10), "warmup": 2, "ms_per_step": out["ms_per_step"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": out["workload"]}, **{k: out[k] for k in out if k not in ("metric", "value", "unit",
+                                                                                             "ms_per_step", "workload")}}
+        print(json.dumps(line))
+    dist.close()
 
 
 def main():
@@ -681,17 +849,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS) + ["candidates"])
-    ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--shard", action="store_true",
-                    help="split ONE instance of the workload over the ranks (strong scaling) instead of one replica per rank")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline samples")
+    ap.add_argument("--no-extras", action="store_true", help="only the headline workload")
     args = ap.parse_args()
     if args.workload == "candidates":
         return run_candidates(args)
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
-    elif args.shard:
-        run_sharded(args, w)
     else:
         run_gpu(args, w)
 

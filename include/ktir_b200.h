@@ -59,6 +59,14 @@ int ktb_set_stream(ktb_ctx* ctx, uint64_t cuda_stream);
 /* CUDA-event timing on the context's stream; slot in [0, 64). */
 int ktb_event_record(ktb_ctx* ctx, int slot);
 int ktb_event_elapsed_ms(ktb_ctx* ctx, int slot_begin, int slot_end, float* ms_out);
+/* Record an event slot on the launch stream (lane 0) or a copy lane (1, 2) and wait for one on the
+ * host: several calls can be in flight and each is retired on its own, without ktb_sync. */
+int ktb_event_record_on(ktb_ctx* ctx, int slot, int lane);
+int ktb_event_sync(ktb_ctx* ctx, int slot);
+/* Queue, on the launch stream, a copy of the device status word into page-locked host memory
+ * followed by its reset: what the kernels queued so far reported, attributable to one call
+ * (read it after an event recorded behind it has completed). */
+int ktb_status_snapshot(ktb_ctx* ctx, ktb_status* host_pinned);
 /* Write `bytes` (> L2 size) of scratch so the next kernel starts with a cold L2. */
 int ktb_flush_l2(ktb_ctx* ctx);
 /* Number of kernels this library has launched on the context so far. */

@@ -142,6 +142,26 @@ int ktb_event_record(ktb_ctx* ctx, int slot) {
     return KTB_OK;
 }
 
+int ktb_event_record_on(ktb_ctx* ctx, int slot, int lane) {
+    if (!ctx || slot < 0 || slot >= KTB_NUM_EVENTS || lane < 0 || lane > 2) return KTB_E_ARG;
+    if (lane > 0 && !ctx->lanes_ok) return ktb_fail(ctx, KTB_E_ARG, "ktb_event_record_on", "copy lanes not in use");
+    KTB_CUDA(ctx, cudaEventRecord(ctx->events[slot], lane == 0 ? ctx->stream : ctx->lane[lane - 1]));
+    return KTB_OK;
+}
+
+int ktb_event_sync(ktb_ctx* ctx, int slot) {
+    if (!ctx || slot < 0 || slot >= KTB_NUM_EVENTS) return KTB_E_ARG;
+    KTB_CUDA(ctx, cudaEventSynchronize(ctx->events[slot]));
+    return KTB_OK;
+}
+
+int ktb_status_snapshot(ktb_ctx* ctx, ktb_status* host_pinned) {
+    if (!ctx || !host_pinned) return KTB_E_ARG;
+    KTB_CUDA(ctx, cudaMemcpyAsync(host_pinned, ctx->dev_status, sizeof(ktb_status), cudaMemcpyDeviceToHost, ctx->stream));
+    KTB_CUDA(ctx, cudaMemsetAsync(ctx->dev_status, 0, sizeof(ktb_status), ctx->stream));
+    return KTB_OK;
+}
+
 int ktb_event_elapsed_ms(ktb_ctx* ctx, int a, int b, float* ms_out) {
     if (!ctx || !ms_out || a < 0 || b < 0 || a >= KTB_NUM_EVENTS || b >= KTB_NUM_EVENTS) return KTB_E_ARG;
     KTB_CUDA(ctx, cudaEventSynchronize(ctx->events[b]));

@@ -96,8 +96,6 @@ def _split_item_table(stmt, table: np.ndarray, geoms, bpes, launch_fn, piece_byt
     n_items, n_op = table.shape
     total = sum(n_items * g[0] * g[2] * b for g, b in zip(geoms, bpes))
     n = chunk_count(total, n_items, piece_bytes)
-    if n <= 1:
-        return None
     bounds = np.linspace(0, n_items, n + 1).astype(np.int64)
     chunks = []
     for a, b in zip(bounds[:-1], bounds[1:]):

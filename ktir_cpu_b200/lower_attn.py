@@ -322,8 +322,6 @@ class AttentionStatement(Statement):
                 or a.kv_page_stride != a.page * a.kv_row_stride):
             return None
         n = chunk_count(self._bytes, a.heads // grp, piece_bytes)
-        if n <= 1:
-            return None
         bt_bpe = 4 if a.bt_dtype == R.KTB_I32 else 8
         bt = Region(a.bt_off * bt_bpe, a.num_tiles * bt_bpe)
         bounds = np.linspace(0, a.heads // grp, n + 1).astype(np.int64)

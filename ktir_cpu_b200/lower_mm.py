@@ -156,8 +156,6 @@ class GemmStatement(Statement):
         cb = 2 if a.c_dtype == R.KTB_F16 else 4
         blocks = (a.M + 127) // 128                      # the kernel works in 128-row tiles
         n = chunk_count(a.M * a.K * 2 + a.M * a.N * cb, blocks, piece_bytes)
-        if n <= 1:
-            return None
 
         def rows(off, r0, r1, ld, width, bpe):
             if ld == width:

@@ -238,8 +238,10 @@ class BoundPipeline:
             ch.up, ch.down = regions(up), regions(down)
         self.ptr_t = C.c_void_p * len(self.names)
 
-    def run(self, dev, arena: int, host: Dict[str, np.ndarray], results: Dict[str, np.ndarray], whole_launch):
-        """Queue the whole call; the caller synchronises afterwards."""
+    def run(self, dev, arena: int, host: Dict[str, np.ndarray], results: Dict[str, np.ndarray], whole_launch,
+            after_launch=None):
+        """Queue the whole call; the caller synchronises afterwards.  ``after_launch`` (plans that run
+        as a whole only) is called between the launches and the read-back."""
         pinned = self.ptr_t(*[results[k].ctypes.data for k in self.names])
         src = self.ptr_t(*[host[k].ctypes.data for k in self.names])
         dev.run_pipeline(arena, self.chunks, self.n_chunks, pinned, src, len(self.names))
@@ -247,6 +249,8 @@ class BoundPipeline:
             # a plan that runs as a whole: its launches (or their graph replay) go out from here,
             # then every written tensor comes back
             whole_launch()
+            if after_launch is not None:
+                after_launch()
             writes = self.tp.chunks[0].writes
             if writes:
                 dev.fence(0, 2)

@@ -140,6 +140,9 @@ SYMBOLS = {
     "ktb_set_stream": (C.c_int, [C.c_void_p, C.c_uint64]),
     "ktb_event_record": (C.c_int, [C.c_void_p, C.c_int]),
     "ktb_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "ktb_event_record_on": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
+    "ktb_event_sync": (C.c_int, [C.c_void_p, C.c_int]),
+    "ktb_status_snapshot": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ktb_flush_l2": (C.c_int, [C.c_void_p]),
     "ktb_launch_count": (C.c_int64, [C.c_void_p]),
     "ktb_graph_begin": (C.c_int, [C.c_void_p]),
@@ -289,6 +292,15 @@ class Device:
     # timing ----------------------------------------------------------------
     def record(self, slot: int):
         self.check(self.lib.ktb_event_record(self.h, slot))
+
+    def record_on(self, slot: int, lane: int):
+        self.check(self.lib.ktb_event_record_on(self.h, slot, lane))
+
+    def event_sync(self, slot: int):
+        self.check(self.lib.ktb_event_sync(self.h, slot))
+
+    def status_snapshot(self, host_ptr: int):
+        self.check(self.lib.ktb_status_snapshot(self.h, C.c_void_p(host_ptr)))
 
     def elapsed_ms(self, a: int, b: int) -> float:
         ms = C.c_float()

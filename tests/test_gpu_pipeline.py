@@ -9,6 +9,13 @@ from ktir_cpu_b200.interpreter import KTIRInterpreter
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def small_parts(monkeypatch):
+    """4 MiB per part instead of the default, so that these sizes split into many parts."""
+    from ktir_cpu_b200.interpreter import Session
+    monkeypatch.setattr(Session, "PIPELINE_PIECE", 4 << 20)
+
+
 def _both(src, fn, kw):
     gpu = KTIRInterpreter()
     gpu.load(src)

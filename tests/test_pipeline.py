@@ -12,6 +12,12 @@ from ktir_cpu_b200.pipeline import Region, TransferPlan, merge_intervals, tile_r
 F16, I32 = np.dtype(np.float16), np.dtype(np.int32)
 
 
+@pytest.fixture(autouse=True)
+def small_parts(monkeypatch):
+    """4 MiB per part instead of the default, so that modest sizes split into several parts."""
+    monkeypatch.setattr(Session, "PIPELINE_PIECE", 4 << 20)
+
+
 def _session(src, fn, tensors, scalars=None):
     f = KTIRParser().parse_module(src).get_function(fn)
     return Session(R.PlanOnlyDevice(), f, tensors, scalars or {})
@@ -69,14 +75,14 @@ def test_softmax_splits_into_row_ranges():
     assert all(len(c.uploads) == 1 and len(c.writes) == 1 for c in tp.chunks)
 
 
-def test_vector_add_splits_and_small_plans_do_not():
+def test_vector_add_splits_and_small_plans_run_as_one_part():
     n = 1 << 22
     sess = _session(K.vector_add(n, 16384, 32), "add_kernel",
                     [("x_ptr", (n,), F16), ("y_ptr", (n,), F16), ("output_ptr", (n,), F16)], {"BLOCK_SIZE": 16384})
     _check(sess)
     small = _session(K.vector_add(4096, 128, 32), "add_kernel",
                      [("x_ptr", (4096,), F16), ("y_ptr", (4096,), F16), ("output_ptr", (4096,), F16)], {"BLOCK_SIZE": 128})
-    _check(small, expect_split=False)
+    assert len(_check(small).chunks) == 1          # one part, still only the regions the kernel touches
 
 
 def test_matmul_splits_into_row_blocks_with_b_first():
