@@ -118,6 +118,18 @@ typedef struct {
 } ktb_pipe_chunk;
 int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, int n_chunks, void* const* pinned,
                      const void* const* src, int n_tensors);
+/* ktb_run_pipeline handed to the context's submission thread: the call copies its arguments (not
+ * the tensors), returns at once with a sequence number, and the thread stages, queues and — when
+ * given — snapshots the status word into `snapshot` (page-locked) and records event `event_slot`
+ * behind the job's last device work.  Jobs are issued in submission order.  While jobs are
+ * pending the caller must not queue other work on the context; ktb_wait_submitted(seq) returns
+ * once job `seq` has been issued (its event can then be waited for) and reports the first
+ * error of the jobs up to it; ktb_sync waits for all of them.  This is how a batch of
+ * candidate kernels keeps the host preparing call i+1 while call i is being staged
+ * (notebooks/demo_helpers.py:32-46 runs them one after the other). */
+int ktb_submit_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, int n_chunks, void* const* pinned,
+                        const void* const* src, int n_tensors, ktb_status* snapshot, int event_slot, uint64_t* seq_out);
+int ktb_wait_submitted(ktb_ctx* ctx, uint64_t seq);
 int ktb_lane_fence(ktb_ctx* ctx, int from, int to);
 int ktb_lane_d2h(ktb_ctx* ctx, void* host_dst, const void* dev_src, size_t width, size_t height, size_t pitch);
 int ktb_set_copy_threads(int n);

@@ -42,10 +42,10 @@ class BatchResult:
 
 class _Flight:
     """One candidate between submission and retirement."""
-    __slots__ = ("index", "cand", "out", "slot")
+    __slots__ = ("index", "cand", "out", "slot", "seq", "keep")
 
-    def __init__(self, index, cand, out, slot):
-        self.index, self.cand, self.out, self.slot = index, cand, out, slot
+    def __init__(self, index, cand, out, slot, seq, keep):
+        self.index, self.cand, self.out, self.slot, self.seq, self.keep = index, cand, out, slot, seq, keep
 
 
 class BatchRunner:
@@ -87,20 +87,24 @@ class BatchRunner:
     def _release_session(self, sess):
         for a in self._arenas.pop(id(sess), [])[1:]:
             sess.dev.free(a)
-        self._plans.pop(id(sess), None)
+        for key in [k for k in self._plans if k[0] == id(sess)]:
+            del self._plans[key]
         self._sessions.pop(id(sess), None)
 
     # -- per-session resources ---------------------------------------------------------------
-    def _transfer(self, sess):
-        """Whole-tensor transfer plan of a candidate: what the plan reads goes up, what it writes
-        comes back; a scorer has the inputs already, so no copies of them are made."""
-        b = self._plans.get(id(sess))
+    def _transfer(self, sess, slot: int):
+        """Transfer plan of a candidate on the arena of flight slot ``slot``: what the plan reads goes
+        up, what it writes comes back; a scorer has the inputs already, so no copies of them are
+        made.  A plan of one statement that launches through the C ABI runs as one part that the
+        submission thread can issue on its own."""
+        b = self._plans.get((id(sess), slot))
         if b is None:
             from .pipeline import BoundPipeline, TransferPlan
             tensors = {k: (off, nbytes) for k, (off, nbytes, _, _) in sess.layout.items()}
-            tp = TransferPlan(tensors, sess.written, sess.no_upload, None, None, partial=True)
-            b = BoundPipeline(sess.dev, sess.arena, tp)
-            self._plans[id(sess)] = b
+            chunks = sess.plan.statements[0].split(1 << 62) if len(sess.plan.statements) == 1 else None
+            tp = TransferPlan(tensors, sess.written, sess.no_upload, chunks, None, partial=True)
+            b = BoundPipeline(sess.dev, self._arena(sess, slot), tp)
+            self._plans[(id(sess), slot)] = b
             self._sessions[id(sess)] = sess
         return b
 
@@ -131,7 +135,7 @@ class BatchRunner:
         while len(self._status) <= slot:
             from .pinned import pinned_empty
             self._status.append(pinned_empty(dev, (C.sizeof(R.Status),), np.uint8))
-        pipe = self._transfer(sess)
+        pipe = self._transfer(sess, slot)
         arena = self._arena(sess, slot)
         host, pinned, out = {}, {}, {}
         for k, v in kwargs.items():
@@ -148,16 +152,23 @@ class BatchRunner:
                 pinned[k] = v
             else:
                 pinned[k] = self._stage_buffer(dev, slot, k, v)
-        l0 = dev.launch_count()
-        pipe.run(dev, arena, host, pinned, lambda: sess.plan.launch(dev, arena),
-                 after_launch=lambda: dev.status_snapshot(self._status[slot].ctypes.data))
-        dev.record_on(self.EVENT0 + slot, 2 if sess.written else 0)
-        res.launches += dev.launch_count() - l0
-        return _Flight(index, c, out, slot)
+        status_ptr = self._status[slot].ctypes.data
+        if pipe.tp.split:
+            seq = pipe.submit(dev, arena, host, pinned, status_ptr, self.EVENT0 + slot)
+        else:
+            dev.wait_submitted(0)              # this plan's launches go out from here: nothing may be pending
+            seq = None
+            pipe.run(dev, arena, host, pinned, lambda: sess.plan.launch(dev, arena),
+                     after_launch=lambda: dev.status_snapshot(status_ptr))
+            dev.record_on(self.EVENT0 + slot, 2 if sess.written else 0)
+        return _Flight(index, c, out, slot, seq, (host, pinned))
 
     def _retire(self, f: _Flight, res: BatchResult, score, keep_outputs: bool):
         dev = R.get_device(self.device)
+        if f.seq is not None:
+            dev.wait_submitted(f.seq)
         dev.event_sync(self.EVENT0 + f.slot)
+        f.keep = None
         st = R.Status.from_buffer_copy(self._status[f.slot].tobytes())
         if st.negative_index:
             res.errors[f.index] = f"IndexError: indirect index {st.bad_index_value} is negative"
@@ -184,17 +195,22 @@ class BatchRunner:
         res = BatchResult()
         flights: List[_Flight] = []
         n = 0
+        l0 = None
         for i in range(rank, len(candidates), world):
             slot = n % self.depth
             if len(flights) == self.depth:                 # the flight that used this slot before
                 self._retire(flights.pop(0), res, score, keep_outputs)
             try:
+                if l0 is None and self._interps:
+                    l0 = R.get_device(self.device).launch_count()
                 flights.append(self._submit(i, candidates[i], slot, res))
                 n += 1
             except Exception as e:           # noqa: BLE001 - a bad candidate is a result, not a crash
                 res.errors[i] = f"{type(e).__name__}: {e}"
         for f in flights:
             self._retire(f, res, score, keep_outputs)
+        if n:
+            res.launches = R.get_device(self.device).launch_count() - (l0 or 0)
         res.parses = self.parses
         return res
 

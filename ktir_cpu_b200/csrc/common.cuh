@@ -13,6 +13,8 @@
 #define KTB_FLUSH_BYTES (256u << 20)   // > 126 MB L2
 #define KTB_NUM_FENCES 64             // rotating events that order the copy lanes against the launch stream
 
+struct ktb_submitter;          // transfer.cu: the thread that issues queued pipeline jobs
+
 struct ktb_ctx {
     int device;
     int sm_count;
@@ -27,11 +29,13 @@ struct ktb_ctx {
     cudaEvent_t fences[KTB_NUM_FENCES];
     unsigned next_fence;
     bool lanes_ok, lanes_used;
+    ktb_submitter* submitter;   // created by the first ktb_submit_pipeline
     char err[512];
 };
 
 void ktb_transfer_destroy(ktb_ctx* ctx);   // transfer.cu
 int ktb_transfer_sync(ktb_ctx* ctx);
+int ktb_transfer_drain(ktb_ctx* ctx, uint64_t seq);
 
 static inline int ktb_fail(ktb_ctx* ctx, int code, const char* what, const char* detail) {
     if (ctx) snprintf(ctx->err, sizeof(ctx->err), "%s: %s", what, detail ? detail : "");

@@ -119,6 +119,7 @@ int ktb_d2d(ktb_ctx* ctx, void* dev_dst, const void* dev_src, size_t bytes) {
 
 int ktb_sync(ktb_ctx* ctx, ktb_status* status_out) {
     if (!ctx) return KTB_E_ARG;
+    if (int rc = ktb_transfer_drain(ctx, 0)) return rc;   // jobs still queued for the submission thread
     ktb_status st;
     KTB_CUDA(ctx, cudaMemcpyAsync(&st, ctx->dev_status, sizeof(st), cudaMemcpyDeviceToHost, ctx->stream));
     KTB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

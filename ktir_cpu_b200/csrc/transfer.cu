@@ -126,7 +126,7 @@ CopyPool& pool() {
     return *p;
 }
 
-constexpr size_t PIECE = 1u << 20;          // host copy granule
+constexpr size_t PIECE_MAX = 1u << 20, PIECE_MIN = 128u << 10;   // host copy granule
 
 int lanes_ready(ktb_ctx* ctx) {
     if (ctx->lanes_ok) return KTB_OK;
@@ -162,9 +162,76 @@ struct Piece {          // part of one upload region: rows [r0, r0 + rows) x byt
     int chunk;
 };
 
+// A queued ktb_run_pipeline call with everything it points at copied, so that the caller may move on.
+struct Job {
+    void* arena;
+    std::vector<ktb_pipe_chunk> chunks;
+    std::vector<std::vector<ktb_region>> up, down;
+    std::vector<void*> pinned;
+    std::vector<const void*> src;
+    ktb_status* snapshot;
+    int event_slot, event_lane;
+    uint64_t seq;
+};
+
 }  // namespace
 
+extern "C" int ktb_run_pipeline(ktb_ctx*, void*, const ktb_pipe_chunk*, int, void* const*, const void* const*, int);
+extern "C" int ktb_status_snapshot(ktb_ctx*, ktb_status*);
+extern "C" int ktb_event_record_on(ktb_ctx*, int, int);
+
+// One thread per context that issues queued jobs in order, so that the host thread that prepared a
+// call can prepare the next one while this one is staged and queued on the device.
+struct ktb_submitter {
+    std::mutex mu;
+    std::condition_variable work, progress;
+    std::deque<Job> queue;
+    std::thread thread;
+    uint64_t next_seq = 1, done_seq = 0;
+    int first_error = KTB_OK;
+    uint64_t error_seq = 0;
+    bool quit = false;
+
+    void run(ktb_ctx* ctx) {
+        cudaSetDevice(ctx->device);
+        std::unique_lock<std::mutex> lk(mu);
+        for (;;) {
+            work.wait(lk, [this] { return quit || !queue.empty(); });
+            if (queue.empty()) return;
+            Job job = std::move(queue.front());
+            queue.pop_front();
+            lk.unlock();
+            for (size_t c = 0; c < job.chunks.size(); ++c) {
+                job.chunks[c].up = job.up[c].data();
+                job.chunks[c].down = job.down[c].data();
+            }
+            int rc = ktb_run_pipeline(ctx, job.arena, job.chunks.data(), (int)job.chunks.size(), job.pinned.data(),
+                                      job.src.data(), (int)job.pinned.size());
+            if (rc == KTB_OK && job.snapshot) rc = ktb_status_snapshot(ctx, job.snapshot);
+            if (rc == KTB_OK && job.event_slot >= 0) {
+                // behind the read-backs when there are any, else behind the launches
+                if (job.event_lane == 2) rc = fence(ctx, 0, 2);
+                if (rc == KTB_OK) rc = ktb_event_record_on(ctx, job.event_slot, job.event_lane);
+            }
+            lk.lock();
+            if (rc != KTB_OK && first_error == KTB_OK) first_error = rc, error_seq = job.seq;
+            done_seq = job.seq;
+            progress.notify_all();
+        }
+    }
+};
+
 void ktb_transfer_destroy(ktb_ctx* ctx) {
+    if (ctx->submitter) {
+        {
+            std::lock_guard<std::mutex> lk(ctx->submitter->mu);
+            ctx->submitter->quit = true;
+        }
+        ctx->submitter->work.notify_all();
+        ctx->submitter->thread.join();
+        delete ctx->submitter;
+        ctx->submitter = nullptr;
+    }
     if (!ctx->lanes_ok) return;
     for (int i = 0; i < 2; ++i) {
         cudaStreamSynchronize(ctx->lane[i]);
@@ -174,7 +241,23 @@ void ktb_transfer_destroy(ktb_ctx* ctx) {
     ctx->lanes_ok = false;
 }
 
+// Everything queued with ktb_submit_pipeline has been issued to the device (0 = all jobs so far).
+int ktb_transfer_drain(ktb_ctx* ctx, uint64_t seq) {
+    ktb_submitter* s = ctx->submitter;
+    if (!s) return KTB_OK;
+    std::unique_lock<std::mutex> lk(s->mu);
+    const uint64_t want = seq ? seq : s->next_seq - 1;
+    s->progress.wait(lk, [&] { return s->done_seq >= want; });
+    if (s->first_error != KTB_OK && s->error_seq <= want) {
+        const int rc = s->first_error;
+        s->first_error = KTB_OK;
+        return rc;
+    }
+    return KTB_OK;
+}
+
 int ktb_transfer_sync(ktb_ctx* ctx) {
+    if (int rc = ktb_transfer_drain(ctx, 0)) return rc;
     if (!ctx->lanes_ok || !ctx->lanes_used) return KTB_OK;
     for (int i = 0; i < 2; ++i) KTB_CUDA(ctx, cudaStreamSynchronize(ctx->lane[i]));
     ctx->lanes_used = false;
@@ -207,6 +290,44 @@ int ktb_lane_d2h(ktb_ctx* ctx, void* host_dst, const void* dev_src, size_t width
     return copy_region(ctx, host_dst, dev_src, r, cudaMemcpyDeviceToHost, ctx->lane[1]);
 }
 
+int ktb_submit_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, int n_chunks, void* const* pinned,
+                        const void* const* src, int n_tensors, ktb_status* snapshot, int event_slot, uint64_t* seq_out) {
+    if (!ctx || !chunks || n_chunks < 0 || !seq_out || event_slot >= KTB_NUM_EVENTS) return KTB_E_ARG;
+    if (int rc = lanes_ready(ctx)) return rc;
+    if (!ctx->submitter) {
+        ctx->submitter = new ktb_submitter();
+        ctx->submitter->thread = std::thread([ctx] { ctx->submitter->run(ctx); });
+    }
+    Job job;
+    job.arena = arena;
+    job.chunks.assign(chunks, chunks + n_chunks);
+    bool reads_back = false;
+    for (int c = 0; c < n_chunks; ++c) {
+        job.up.emplace_back(chunks[c].up, chunks[c].up + chunks[c].n_up);
+        job.down.emplace_back(chunks[c].down, chunks[c].down + chunks[c].n_down);
+        reads_back = reads_back || chunks[c].n_down > 0;
+    }
+    job.pinned.assign(pinned, pinned + n_tensors);
+    job.src.assign(src, src + n_tensors);
+    job.snapshot = snapshot;
+    job.event_slot = event_slot;
+    job.event_lane = reads_back ? 2 : 0;
+    ktb_submitter* s = ctx->submitter;
+    {
+        std::lock_guard<std::mutex> lk(s->mu);
+        job.seq = s->next_seq++;
+        *seq_out = job.seq;
+        s->queue.push_back(std::move(job));
+    }
+    s->work.notify_one();
+    return KTB_OK;
+}
+
+int ktb_wait_submitted(ktb_ctx* ctx, uint64_t seq) {
+    if (!ctx) return KTB_E_ARG;
+    return ktb_transfer_drain(ctx, seq);
+}
+
 int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, int n_chunks, void* const* pinned,
                      const void* const* src, int n_tensors) {
     if (!ctx || !chunks || n_chunks < 0 || (n_tensors > 0 && (!pinned || !src))) return KTB_E_ARG;
@@ -217,6 +338,12 @@ int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, in
 
     // every upload region cut into pieces, in chunk order; a region whose source already is its
     // page-locked array needs no host copy
+    // (small calls get small pieces, so that a few MB still spread over the copy threads)
+    size_t staged = 0;
+    for (int c = 0; c < n_chunks; ++c)
+        for (int k = 0; k < chunks[c].n_up; ++k) staged += chunks[c].up[k].width * chunks[c].up[k].height;
+    size_t PIECE = staged / (2 * (size_t)(pool().size() > 0 ? pool().size() : 1));
+    PIECE = PIECE < PIECE_MIN ? PIECE_MIN : PIECE > PIECE_MAX ? PIECE_MAX : (PIECE + 4095) & ~(size_t)4095;
     std::vector<Piece> pieces;
     std::vector<int> left(n_chunks, 0);
     for (int c = 0; c < n_chunks; ++c) {

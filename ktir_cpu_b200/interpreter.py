@@ -358,7 +358,7 @@ class KTIRInterpreter:
                 scalars[k] = v
         seeded = tuple((addr, arr.nbytes, to_ktir_dtype(arr.dtype)) for addr, arr in
                        sorted(self.memory.hbm.regions.items()))
-        key = (func_name, tuple((n, s, str(d)) for n, s, d in tensors),
+        key = (func_name, tuple(tensors),
                tuple((k, _scalar_key(v)) for k, v in scalars.items()), seeded, _shard)
         sess = self._sessions.get(key)
         if sess is None:

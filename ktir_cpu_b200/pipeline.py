@@ -238,6 +238,15 @@ class BoundPipeline:
             ch.up, ch.down = regions(up), regions(down)
         self.ptr_t = C.c_void_p * len(self.names)
 
+    def submit(self, dev, arena: int, host: Dict[str, np.ndarray], results: Dict[str, np.ndarray],
+               snapshot_ptr: int, event_slot: int) -> int:
+        """Hand the call (a plan whose parts launch through the C ABI) to the context's submission thread;
+        returns the job's sequence number.  The arrays must stay alive until the job's event has completed."""
+        assert self.tp.split
+        pinned = self.ptr_t(*[results[k].ctypes.data for k in self.names])
+        src = self.ptr_t(*[host[k].ctypes.data for k in self.names])
+        return dev.submit_pipeline(arena, self.chunks, self.n_chunks, pinned, src, len(self.names), snapshot_ptr, event_slot)
+
     def run(self, dev, arena: int, host: Dict[str, np.ndarray], results: Dict[str, np.ndarray], whole_launch,
             after_launch=None):
         """Queue the whole call; the caller synchronises afterwards.  ``after_launch`` (plans that run

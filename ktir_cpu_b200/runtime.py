@@ -149,6 +149,9 @@ SYMBOLS = {
     "ktb_graph_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "ktb_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
     "ktb_graph_destroy": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "ktb_submit_pipeline": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                      C.c_void_p, C.c_int, C.POINTER(C.c_uint64)]),
+    "ktb_wait_submitted": (C.c_int, [C.c_void_p, C.c_uint64]),
     "ktb_lane_fence": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "ktb_run_pipeline": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
     "ktb_lane_d2h": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t]),
@@ -262,6 +265,16 @@ class Device:
 
     def run_pipeline(self, arena: int, chunks, n_chunks: int, pinned, src, n_tensors: int):
         self.check(self.lib.ktb_run_pipeline(self.h, C.c_void_p(arena), chunks, n_chunks, pinned, src, n_tensors))
+
+    def submit_pipeline(self, arena: int, chunks, n_chunks: int, pinned, src, n_tensors: int, snapshot_ptr: int,
+                        event_slot: int) -> int:
+        seq = C.c_uint64()
+        self.check(self.lib.ktb_submit_pipeline(self.h, C.c_void_p(arena), chunks, n_chunks, pinned, src, n_tensors,
+                                                C.c_void_p(snapshot_ptr), event_slot, C.byref(seq)))
+        return seq.value
+
+    def wait_submitted(self, seq: int):
+        self.check(self.lib.ktb_wait_submitted(self.h, C.c_uint64(seq)))
 
     def lane_d2h(self, host_ptr: int, dev_ptr: int, width: int, height: int = 1, pitch: int = 0):
         self.check(self.lib.ktb_lane_d2h(self.h, C.c_void_p(host_ptr), C.c_void_p(dev_ptr), width, height,

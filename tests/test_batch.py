@@ -11,9 +11,14 @@ from ktir_cpu_b200 import runtime as R
 from ktir_cpu_b200.batch import BatchRunner, Candidate, evaluate_many
 
 
+_OK = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p)(lambda ctx, args: 0)
+
+
 class _AnyCall:
+    """Every entry point is a C-callable that returns success."""
+
     def __getattr__(self, name):
-        return lambda *a, **k: 0
+        return _OK
 
 
 class FakeDevice(R.PlanOnlyDevice):
@@ -49,6 +54,11 @@ class FakeDevice(R.PlanOnlyDevice):
     def run_pipeline(self, arena, chunks, n_chunks, pinned, src, n_tensors):
         self.pipeline_calls.append((arena, n_chunks, n_tensors))
 
+    def submit_pipeline(self, arena, chunks, n_chunks, pinned, src, n_tensors, snapshot_ptr, event_slot):
+        self.pipeline_calls.append((arena, n_chunks, n_tensors))
+        return len(self.pipeline_calls)
+
+    def wait_submitted(self, seq): pass
     def fence(self, a, b): pass
     def lane_d2h(self, *a): pass
     def record_on(self, slot, lane): pass
