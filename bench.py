@@ -668,6 +668,39 @@ def report(w, interp, kw_host, steps, warm, dist, clocks_for=None, shard=None, w
     return out
 
 
+def host_link_probe(dev, dist, mib=64, reps=8):
+    """GB/s this rank moves when every rank copies ``mib`` MiB up and ``mib`` MiB down at once between
+    page-locked memory and its GPU (plain DMA, no kernels, no host copies), and the sum over ranks:
+    what the host gives N GPUs together, the ceiling of any end-to-end number."""
+    from ktir_cpu_b200.pinned import pinned_empty
+    n = mib << 20
+    a, b = pinned_empty(dev, (n,), np.uint8), pinned_empty(dev, (n,), np.uint8)
+    a[:] = 1
+    from ktir_cpu_b200 import runtime as R
+    up = (R.PipeRegion * 1)(R.PipeRegion(0, 0, 0, 0, n, 1, n))
+    down = (R.PipeRegion * 1)(R.PipeRegion(1, 0, n, 0, n, 1, n))
+    import ctypes as C
+    chunk = (R.PipeChunk * 1)()
+    chunk[0].n_up, chunk[0].n_down, chunk[0].up, chunk[0].down = 1, 1, up, down
+    ptrs = (C.c_void_p * 2)(a.ctypes.data, b.ctypes.data)
+    arena = dev.alloc(2 * n)
+
+    def once():
+        dev.run_pipeline(arena, chunk, 1, ptrs, ptrs, 2)        # source already page-locked: DMA only, both lanes
+        dev.sync()
+    once()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        once()
+    dt = (time.perf_counter() - t0) / reps
+    (dt,) = dist.max(dt)
+    dev.free(arena)
+    per_rank = 2 * n / dt / 1e9
+    return {"per_rank_gbs": per_rank, "aggregate_gbs": per_rank * dist.world,
+            "what": f"{mib} MiB up + {mib} MiB down per rank at the same time, page-locked memory, max time over ranks"}
+
+
 def candidate_sweep(n=512, B=1, H=4, D=128):
     """The 512-variant attention sweep: variant i has tile_m = (32,64,128)[i%3],
     tile_n = (32,64,128)[(i//3)%3], S = (512,1024,2048)[(i//9)%3], inputs seeded 1000+i.
@@ -819,6 +852,11 @@ def run_gpu(args, w):
                 extras["strong"] = {"error": f"{type(e).__name__}: {e}"}
             it.close()
         if w.name == "softmax":
+            try:
+                from ktir_cpu_b200 import runtime as R
+                extras["host_link"] = host_link_probe(R.get_device(dist.local), dist)
+            except Exception as e:                           # noqa: BLE001
+                extras["host_link"] = {"error": f"{type(e).__name__}: {e}"}
             try:
                 extras["candidates"] = candidates_report(dist, cpu=cpu and dist.world == 1)
             except Exception as e:                           # noqa: BLE001

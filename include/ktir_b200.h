@@ -267,15 +267,19 @@ int ktb_launch_scatter_rows_static(ktb_ctx* ctx, const ktb_rows_args* args);
  * handlers the reference dispatches (ktir_cpu/dialects/arith_ops.py, math_ops via
  * ktir_cpu/ops/math_ops.py:27-138, linalg_ops.py:61-347, tensor_ops.py:47-359,
  * ktir_cpu/ops/memory_ops.py:723-964) with the same rounding points: float tiles compute in
- * f32 and round to the destination type per step, integer tiles wrap in their width. */
+ * f32 and round to the destination type per step, integer tiles wrap in their width.
+ * KTB_G_RING is ktdp.inter_tile_reduce (ktir_cpu/dialects/ktdp_ops.py:1160-1240 with
+ * RingReduceBackend, ktir_cpu/ops/comm_ops.py:229-345): per point the fold of its own partial with
+ * its group's other partials in ring arrival order; a group of at most 8 cores runs as one
+ * thread-block cluster that reads the partials out of its members' shared memory. */
 enum { KTB_G_LOAD = 0, KTB_G_ADDR, KTB_G_IDXADD, KTB_G_GATHER, KTB_G_CONSTV, KTB_G_FILL, KTB_G_PARAM,
-       KTB_G_IOTA, KTB_G_MAP, KTB_G_EW, KTB_G_REDL, KTB_G_MATMUL, KTB_G_STORE, KTB_G_SCATTER };
+       KTB_G_IOTA, KTB_G_MAP, KTB_G_EW, KTB_G_REDL, KTB_G_MATMUL, KTB_G_STORE, KTB_G_SCATTER, KTB_G_RING };
 #define KTB_G_MAXDIM 6
 typedef struct {
     int32_t kind;                 /* KTB_G_* */
     int32_t op;                   /* KTB_G_EW / KTB_G_REDL: opcode (order of lower_generic.EW_OPS) */
     int32_t dt_dst, dt_a, dt_b, dt_c;   /* KTB_F16 .. KTB_I1 */
-    int32_t flags;                /* bit 0: compare as integers */
+    int32_t flags;                /* bit 0: compare as integers; bit 1 (RING): combiner takes (received, accumulator) */
     int32_t ndim;                 /* KTB_G_MAP / KTB_G_IOTA: rank of `shape` */
     int64_t points, elems;        /* extent of dst (of the stored tile for STORE / SCATTER) */
     int64_t ea, eb, ec;           /* elems of the sources; 1 = one value per point, broadcast */
@@ -284,14 +288,16 @@ typedef struct {
     const void* b;
     const void* c;
     void* arena;
-    const int64_t* dev_base;      /* [points] element address of the tile origin (LOAD / ADDR / STORE) */
-    const int64_t* dev_rel;       /* [elems] element offset of each element from the origin */
-    const void* dev_table;        /* CONSTV: [elems] values of dt_dst; PARAM: [points] values of dt_dst */
+    const int64_t* dev_base;      /* [points] element address of the tile origin (LOAD / ADDR / STORE); RING: sources per point */
+    const int64_t* dev_rel;       /* [elems] element offset of each element from the origin; RING with a cluster: point of each CTA */
+    const void* dev_table;        /* CONSTV: [elems] values of dt_dst; PARAM: [points] values of dt_dst;
+                                     RING: int64 [points][n] sources in fold order (cluster ranks with h > 1, else points) */
     int64_t lo, hi;               /* allocation bounds in elements: reads outside give 0, writes are dropped */
     int64_t shape[KTB_G_MAXDIM];  /* MAP: dst shape; IOTA: tile shape */
     int64_t strides[KTB_G_MAXDIM];/* MAP: source element stride per dst dim */
     int64_t offset;               /* MAP: source element offset; IOTA: dimension */
-    int64_t outer, n, inner, h;   /* REDL: src viewed as [outer][n][inner], pairs (i, i + h), odd tail carried */
+    int64_t outer, n, inner, h;   /* REDL: src viewed as [outer][n][inner], pairs (i, i + h), odd tail carried;
+                                     RING: n = row length of dev_table, h = cores per cluster (<= 1: no cluster) */
     int64_t batch, M, N, K;       /* MATMUL */
     double fimm;                  /* FILL value for float destinations */
     int64_t iimm;                 /* FILL value for integer destinations; IDXADD: stride */

@@ -4,7 +4,11 @@
 // (ktir_cpu/dialects/_helpers.py:39-72: f16 tiles compute in f32 and round per op;
 // ktir_cpu/dialects/linalg_ops.py:86-133: pairwise halving reduction; ktir_cpu/memory.py:243-291:
 // reads outside an allocation give 0, writes outside are dropped, negative indices are errors).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 enum { G_MOV, G_ADD, G_SUB, G_MUL, G_DIV, G_REM, G_MAX, G_MAXNUM, G_MIN, G_MINNUM, G_NEG, G_ABS, G_EXP, G_LOG,
        G_LOG2, G_LOG1P, G_SQRT, G_RSQRT, G_TANH, G_SIN, G_COS, G_CEIL, G_FLOOR, G_FMA, G_POW, G_SELECT,
@@ -12,7 +16,7 @@ enum { G_MOV, G_ADD, G_SUB, G_MUL, G_DIV, G_REM, G_MAX, G_MAXNUM, G_MIN, G_MINNU
        G_AND, G_OR, G_XOR, G_SHL, G_SHR, G_DIVT, G_REMT, G_DIVF, G_CDIV, G_BITCAST, G_CMP_UNE, G_CMP_UEQ,
        G_CMP_ULT, G_CMP_ULE, G_CMP_UGT, G_CMP_UGE, G_SIGN };
 
-static __device__ __forceinline__ bool g_is_float(int dt) { return dt == KTB_F16 || dt == KTB_F32; }
+static __host__ __device__ __forceinline__ bool g_is_float(int dt) { return dt == KTB_F16 || dt == KTB_F32; }
 static __host__ __device__ __forceinline__ int g_size(int dt) {
     return dt == KTB_F16 ? 2 : dt == KTB_I64 ? 8 : dt == KTB_I1 ? 1 : 4;
 }
@@ -334,6 +338,75 @@ __global__ void g_scatter_kernel(const __grid_constant__ ktb_gen_op o, ktb_statu
     }
 }
 
+// ---- cross-core ring reduce ---------------------------------------------------------------
+// dst[p] = fold of a[p] with the partials of the other cores of p's group, in the order the
+// reference's ring delivers them to that core (ktir_cpu/ops/comm_ops.py:294-345): core c folds in
+// the partial that started on core (c - k) mod n in round k.  A forwarded tile is never modified,
+// so the value that arrives equals the source core's own partial, and every fold rounds to the
+// tile dtype like one more pass through the combiner region.
+//
+// CLUSTER: the cores of a group run as one thread-block cluster (one CTA per core, consecutive
+// CTAs; dev_rel gives the point of each CTA).  Every CTA puts its partial into its own shared
+// memory, the cluster synchronises, and the fold reads the peers' partials straight out of their
+// shared memory (distributed shared memory, plain loads, no multicast); the sources of a point are
+// then ranks inside the cluster.  Otherwise (groups of unequal size or more than 8 cores) the
+// partials are read from global memory and the sources are point indices.
+// Only hardware cluster barriers are used: there is no flag to spin on.
+#define G_RING_CHUNK 8192          // elements of a partial staged in shared memory at a time
+template <bool CLUSTER>
+__global__ void __launch_bounds__(256) g_ring_kernel(const __grid_constant__ ktb_gen_op o) {
+    extern __shared__ __align__(16) unsigned char g_ring_smem[];
+    const int64_t p = CLUSTER ? o.dev_rel[blockIdx.x] : (int64_t)blockIdx.x;
+    const int64_t cnt = o.dev_base[p];
+    const int64_t* src = reinterpret_cast<const int64_t*>(o.dev_table) + p * o.n;
+    const bool swapped = (o.flags & 2) != 0, r16 = o.dt_dst == KTB_F16;
+    const int size = g_size(o.dt_a);
+    for (int64_t e0 = 0; e0 < o.elems; e0 += G_RING_CHUNK) {
+        const int64_t len = o.elems - e0 < G_RING_CHUNK ? o.elems - e0 : G_RING_CHUNK;
+        if (CLUSTER) {
+            for (int64_t i = threadIdx.x; i < len; i += blockDim.x) g_copy(g_ring_smem, i, o.a, p * o.elems + e0 + i, size);
+            cg::this_cluster().sync();                 // every partial of the group is in place
+        }
+        for (int64_t i = threadIdx.x; i < len; i += blockDim.x) {
+            float acc = CLUSTER ? g_ldf(g_ring_smem, o.dt_a, i) : g_ldf(o.a, o.dt_a, p * o.elems + e0 + i);
+            for (int64_t j = 0; j < cnt; ++j) {
+                float v;
+                if (CLUSTER) v = g_ldf(cg::this_cluster().map_shared_rank(g_ring_smem, (unsigned)src[j]), o.dt_a, i);
+                else v = g_ldf(o.a, o.dt_a, src[j] * o.elems + e0 + i);
+                acc = swapped ? g_fop(o.op, v, acc, 0.f) : g_fop(o.op, acc, v, 0.f);
+                if (r16) acc = ktb_round16(acc);
+            }
+            g_stf(o.dst, o.dt_dst, p * o.elems + e0 + i, acc);
+        }
+        if (CLUSTER) cg::this_cluster().sync();        // peers are done reading before the next chunk (or exit)
+    }
+}
+
+static int launch_ring(ktb_ctx* ctx, const ktb_gen_op& o) {
+    if (!g_is_float(o.dt_a) || o.dt_a != o.dt_dst) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "generic", "ring reduce of a non-float tile");
+    if (o.points > 0x7fffffff) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "generic", "too many points");
+    const int cluster = (int)o.h;
+    if (cluster <= 1) {
+        g_ring_kernel<false><<<(unsigned)o.points, 256, 0, ctx->stream>>>(o);
+        return KTB_OK;
+    }
+    if (cluster > 8 || o.points % cluster) return ktb_fail(ctx, KTB_E_ARG, "generic", "bad cluster size");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)o.points);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (size_t)(o.elems < G_RING_CHUNK ? o.elems : G_RING_CHUNK) * g_size(o.dt_a);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    KTB_CUDA(ctx, cudaLaunchKernelEx(&cfg, g_ring_kernel<true>, o));
+    return KTB_OK;
+}
+
 extern "C" int ktb_launch_generic(ktb_ctx* ctx, const ktb_gen_op* op) {
     if (!ctx || !op) return KTB_E_ARG;
     const ktb_gen_op& o = *op;
@@ -360,6 +433,9 @@ extern "C" int ktb_launch_generic(ktb_ctx* ctx, const ktb_gen_op* op) {
         case KTB_G_MATMUL: G_RUN(g_matmul_kernel); break;
         case KTB_G_STORE: G_RUN(g_store_kernel); break;
         case KTB_G_SCATTER: g_scatter_kernel<<<1, 32, 0, ctx->stream>>>(o, ctx->dev_status); break;
+        case KTB_G_RING:
+            if (int rc = launch_ring(ctx, o)) return rc;
+            break;
         default: return ktb_fail(ctx, KTB_E_ARG, "generic", "unknown step kind");
     }
 #undef G_RUN

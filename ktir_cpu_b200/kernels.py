@@ -619,6 +619,63 @@ def paged_attention(num_tokens: int = 2048, context_len: int = 2048, num_query_h
     return s
 
 
+def ring_allreduce(n_cores: int = 4, group: int = 4, cols: int = 128, combine: str = "add", dtype: str = "f16",
+                   inner: int = 1, strided: bool = False, absent_core: int = -1) -> str:
+    """Cross-core all-reduce inside groups of ``group`` cores (the op pair of examples/ktir/ring_reduce.mlir
+    and examples/latency/ring_reduce_multi_group.mlir of the reference): core c loads row c of ``in``
+    ([n_cores * inner, cols]), the cores of a group combine their rows through
+    ``ktdp.inter_tile_produce`` / ``ktdp.inter_tile_reduce`` (``combine``: add, mul, max), and EVERY core
+    stores what it holds to row c of ``out`` — each core folds in ring arrival order, so rows of one
+    group may differ in the last bit.  ``inner`` > 1 repeats this for ``inner`` rows per core in a
+    loop; ``strided`` makes group g the cores {g, g + n_groups, ...} instead of a contiguous range.
+    ``absent_core`` >= 0 puts the whole exchange under a condition that this core does not take: its
+    ring neighbours then wait for ever, which the interpreter must report as a deadlock."""
+    assert n_cores % group == 0 and (absent_core < 0 or inner == 1)
+    ng = n_cores // group
+    t, at = f"tensor<1x{cols}x{dtype}>", f"!ktdp.access_tile<1x{cols}xindex>"
+    rows = n_cores * inner
+    if strided:
+        members = f"affine_set<(i)[g] : (i - g >= 0, (i - g) mod {ng} == 0, -i + {n_cores - 1} >= 0)>"
+    else:
+        members = f"affine_set<(i)[g] : (i - {group} * g >= 0, -i + {group} * g + {group - 1} >= 0)>"
+    groups = f"affine_set<(g) : (g >= 0, -g + {ng - 1} >= 0)>"
+    body_op = {"add": f"linalg.add ins(%lhs, %rhs : {t}, {t}) outs(%init : {t}) -> {t}",
+               "max": f"linalg.max ins(%lhs, %rhs : {t}, {t}) outs(%init : {t}) -> {t}",
+               "mul": f"arith.mulf %lhs, %rhs : {t}"}[combine]
+    ident = {"add": "0.0", "max": "-65504.0", "mul": "1.0"}[combine]
+    ind = "      " if inner > 1 else "    "
+    body = (tile("in_tile", "in_view", ["%row", "%c0"], [1, cols], [rows, cols], dtype, ind)
+            + f"{ind}%partial = ktdp.load %in_tile : {at} -> {t}\n"
+            + f"{ind}%fut = ktdp.inter_tile_produce\n{ind}    producer_tiles_per_group = #ring_members\n"
+              f"{ind}    : {t} -> !ktdp.tile_future<{t}, groups = {groups}>\n{ind}{{\n"
+              f"{ind}  ^bb0(%gid: index):\n{ind}    ktdp.yield_partial %partial : {t}\n{ind}}}\n"
+            + f"{ind}%id_init = tensor.empty() : {t}\n"
+              f"{ind}%ident = linalg.fill ins(%c_ident : {dtype}) outs(%id_init : {t}) -> {t}\n"
+            + f"{ind}%reduced = ktdp.inter_tile_reduce(%fut)\n{ind}    consumer_tiles_per_group = #ring_members,\n"
+              f"{ind}    identity(%ident : {t}) : !ktdp.tile_future<{t}, groups = {groups}> -> {t}\n{ind}{{\n"
+              f"{ind}  ^bb0(%lhs: {t}, %rhs: {t}):\n{ind}    %init = tensor.empty() : {t}\n"
+              f"{ind}    %comb = {body_op}\n{ind}    ktdp.yield_reduced %comb : {t}\n{ind}}}\n"
+            + tile("out_tile", "out_view", ["%row", "%c0"], [1, cols], [rows, cols], dtype, ind)
+            + f"{ind}ktdp.store %reduced, %out_tile : {t}, {at}\n")
+    s = (f"#ring_members = {members}\n\n"
+         f"module {{\n  func.func @ring_allreduce(%in_ptr: index, %out_ptr: index) attributes {{grid = [{n_cores}]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n    %c_inner = arith.constant {inner} : index\n"
+         f"    %c_ident = arith.constant {ident} : {dtype}\n"
+         f"    %row0 = arith.muli %pid, %c_inner : index\n")
+    s += view("in_view", "in_ptr", [rows, cols], dtype) + view("out_view", "out_ptr", [rows, cols], dtype)
+    if inner > 1:
+        s += (f"    scf.for %i = %c0 to %c_inner step %c1 {{\n      %row = arith.addi %row0, %i : index\n"
+              + body + "      scf.yield\n    }\n")
+    elif absent_core >= 0:
+        s += (f"    %row = arith.addi %row0, %c0 : index\n    %c_absent = arith.constant {absent_core} : index\n"
+              f"    %present = arith.cmpi ne, %pid, %c_absent : index\n    scf.if %present {{\n"
+              + body.replace("\n    ", "\n      ").replace("    %in_tile", "      %in_tile", 1) + "    }\n")
+    else:
+        s += "    %row = arith.addi %row0, %c0 : index\n" + body
+    return s + "    return\n  }\n}\n"
+
+
 def layernorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, eps: float = 1e-5) -> str:
     """y = (x - mean) / sqrt(var + eps) * w + b per row, f32 statistics, one row per iteration.
 

@@ -20,7 +20,7 @@ The cost rules themselves are the reference's (ktir_cpu/latency.py:311-393):
 * ``compute_float`` / ``compute_int``  one element per SIMD lane per cycle (scalar index
                 arithmetic is free);
 * ``compute_transcendental``  the same times ``transcendental_penalty``;
-* ``comm``      ring bytes / ring bytes per cycle (no device path produces these yet).
+* ``comm``      ring bytes / ring bytes per cycle.
 """
 from __future__ import annotations
 
@@ -264,6 +264,13 @@ class LatencyTracker:
                 each = fl / cfg.systolic_flops_per_cycle
                 for c in cores:
                     self.record_weighted(int(c), r.op_type, r.category, int(r.count[c]), each, fl)
+            elif r.kind == "comm":
+                # bytes each core sends over the ring (ktir_cpu/latency.py:380-390)
+                bw = cfg.ring_bytes_per_cycle
+                for c in cores:
+                    b = int(r.nbytes[c])
+                    self.record_weighted(int(c), r.op_type, "comm", int(r.count[c]), 0.0, 0.0, b,
+                                         cycles_total=(b / bw if bw > 0 else 0.0))
             elif r.kind in ("bytes", "indirect"):
                 nb = r.nbytes if r.kind == "bytes" else r.resolve(tensors or {})
                 for c in cores:

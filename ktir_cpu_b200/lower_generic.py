@@ -311,6 +311,8 @@ class GenBuilder:
             return self.eval_reduce(n, ks, loops)
         if k == "matmul":
             return self.eval_matmul(n, ks, loops)
+        if k == "ringred":
+            return self.eval_ring(n, ks, loops)
         if k == "iter":
             info = n.attrs["loop"]
             return self.loop_state[(id(info), ks)][n.attrs["index"]]
@@ -384,6 +386,46 @@ class GenBuilder:
             raise Unsupported("reduce result shape mismatch")
         out = self.prog.new(n.dtype, n.shape)
         return self.prog.emit("ew", out, (cur,), op="mov")
+
+    def eval_ring(self, n: Node, ks, loops) -> Buf:
+        """``ktdp.inter_tile_reduce``: per point the fold of its partial with those of the other cores
+        of its group, in ring arrival order (see ``trace_comm``).  Points are core-major, so the
+        partial of core ``s`` at the same loop indices is point ``s * inner + p % inner``."""
+        if n.dtype not in ("f16", "f32"):
+            raise Unsupported(f"inter_tile_reduce of a {n.dtype} tile")
+        axes = tuple(self.store.axes)
+        P_all = _prod(axes)
+        if self.prog.P != P_all:
+            raise Unsupported("inter_tile_reduce evaluated on part of the grid")
+        src = self._full(self.eval(n.args[0], ks, loops), n.args[0].shape)
+        code = _FLOAT_EW.get(n.attrs["op"])
+        if code is None:
+            raise Unsupported(f"inter_tile_reduce with combiner {n.attrs['op']}")
+        inner = P_all // axes[0]
+        srcs, counts, groups = n.attrs["sources"], n.attrs["counts"], n.attrs["groups"]
+        S = srcs.shape[1]
+        core = np.arange(P_all, dtype=np.int64) // inner
+        lane = np.arange(P_all, dtype=np.int64) % inner
+        pts = np.where(srcs[core] >= 0, srcs[core] * inner + lane[:, None], -1)
+        # one cluster per (group, loop point) when every group has the same size of at most 8 cores
+        members = {int(g): np.flatnonzero(groups == g) for g in np.unique(groups)}
+        sizes = {len(m) for m in members.values()}
+        cluster, order, ranks = 0, None, None
+        if len(sizes) == 1 and 1 < next(iter(sizes)) <= 8:
+            cluster = next(iter(sizes))
+            rank_of = np.zeros(axes[0], np.int64)
+            for m in members.values():
+                rank_of[m] = np.arange(len(m))
+            same_group = (srcs < 0) | (groups[np.clip(srcs, 0, None)] == groups[:, None])
+            if same_group.all():
+                order = np.concatenate([(m[None, :] * inner + np.arange(inner)[:, None]).reshape(-1)
+                                        for m in members.values()]).astype(np.int64)
+                ranks = np.where(srcs[core] >= 0, rank_of[np.clip(srcs[core], 0, None)], -1)
+            else:
+                cluster = 0
+        return self.prog.emit("ringred", self.prog.new(n.dtype, n.shape), (src,), op=code, swapped=bool(n.attrs["swapped"]),
+                              counts=counts[core].astype(np.int64), sources=(ranks if cluster else pts).astype(np.int64),
+                              cluster=cluster, order=order, S=S)
 
     def eval_matmul(self, n: Node, ks, loops) -> Buf:
         a_n, b_n = n.args[0], n.args[1]
@@ -469,8 +511,31 @@ def _runs(rel: np.ndarray):
     return rel[starts], (ends - starts).astype(np.int64)
 
 
+def _contains_kind(root: Node, kind: str) -> bool:
+    seen, stack = set(), [root]
+    while stack:
+        n = stack.pop()
+        if id(n) in seen:
+            continue
+        seen.add(id(n))
+        if n.kind == kind:
+            return True
+        stack.extend(a for a in n.args if isinstance(a, Node))
+        if n.kind == "loopres":
+            info = n.attrs["loop"]
+            stack.extend(x for x in list(info.inits) + list(info.yields) if isinstance(x, Node))
+    return False
+
+
 def build_generic(store: Store, arena, sel: np.ndarray):
     """(program, written allocation names, direct footprints as (base, rel, dtype, write), indirect allocs)."""
+    n_points = _prod(tuple(store.axes))
+    ring = _contains_kind(store.value, "ringred")
+    store_sel = sel
+    if ring and len(sel) != n_points:
+        # the cores that do not store still contribute their partials: evaluate everywhere and keep
+        # their stores out of the allocation (writes outside are dropped)
+        sel = np.arange(n_points, dtype=np.int64)
     gb = GenBuilder(store, arena, sel)
     val = gb.eval(store.value)
     tgt = store.target
@@ -488,10 +553,15 @@ def build_generic(store: Store, arena, sel: np.ndarray):
             val = P.emit("map", P.new(dt, (n_el,)), (val,), shape=(n_el,), strides=[0], offset=0)
         base = gb.at_points(tgt.off, (), ())
         rel = access_rel_offsets(tgt)
-        al = gb.alloc_of(base.min() if base.size else 0, dt, "Scatter to")
+        live = base if len(store_sel) == len(sel) else base[store_sel]
+        al = gb.alloc_of(live.min() if live.size else 0, dt, "Scatter to")
         bpe = bytes_per_elem(dt)
+        if len(store_sel) != len(sel):
+            keep = np.zeros(len(sel), bool)
+            keep[store_sel] = True
+            base = np.where(keep, base, -(1 << 50))
         P.emit("store", None, (val,), base=base, rel=rel, lo=al.byte_lo // bpe, hi=al.byte_hi // bpe, dtype=dt)
-        direct.append((base, rel, dt, True))
+        direct.append((live, rel, dt, True))
         written.append(al.name)
     else:
         addr, al, dt = gb.indirect_addresses(tgt, (), ())
@@ -597,6 +667,14 @@ def _make_statement_class():
                         g.outer, g.n, g.inner, g.h = int(a["outer"]), int(a["n"]), int(a["inner"]), int(a["h"])
                 elif op.kind == "matmul":
                     g.batch, g.M, g.N, g.K = int(a["batch"]), int(a["M"]), int(a["N"]), int(a["K"])
+                elif op.kind == "ringred":
+                    g.op = EW_CODE[a["op"]]
+                    g.flags = 2 if a["swapped"] else 0
+                    g.n, g.h = int(a["S"]), int(a["cluster"])
+                    g.dev_base = self._up(dev, np.ascontiguousarray(a["counts"], np.int64))
+                    g.dev_table = self._up(dev, np.ascontiguousarray(a["sources"], np.int64))
+                    if a["cluster"]:
+                        g.dev_rel = self._up(dev, np.ascontiguousarray(a["order"], np.int64))
                 self.steps.append(g)
             # footprints for the sequential-order check
             self.fps: List[Footprint] = []

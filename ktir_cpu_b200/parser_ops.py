@@ -440,7 +440,131 @@ def parse_if(p, name, results) -> Op:
     return Op(name, results, [cond], {}, _result_types(results, rtypes, []), regions)
 
 
+def _split_top(text: str) -> List[str]:
+    """Split on commas outside angle / round brackets ('->', '>=' and '<=' are not brackets)."""
+    out, depth, cur, i = [], 0, [], 0
+    while i < len(text):
+        c = text[i]
+        two = text[i:i + 2]
+        if two in ("->", ">=", "<="):
+            cur.append(two)
+            i += 2
+            continue
+        if c in "<(":
+            depth += 1
+        elif c in ">)":
+            depth -= 1
+        if c == "," and depth == 0:
+            out.append("".join(cur))
+            cur = []
+        else:
+            cur.append(c)
+        i += 1
+    if "".join(cur).strip():
+        out.append("".join(cur))
+    return out
+
+
+def _tile_future_type(p):
+    """``!ktdp.tile_future<T {, T} [, groups = <affine set>]>`` -> (partial types, groups set or None).
+    The prefix may be elided (``<T, groups = ...>``), as the MLIR printer writes it."""
+    t = p.peek()
+    if t.kind == "type" and t.text.startswith("!ktdp.tile_future"):
+        p.i += 1
+        inner = t.text[t.text.index("<") + 1:-1]
+    else:
+        # elided prefix: collect the source text between the balanced '<' ... '>'
+        p.eat("<")
+        depth, parts = 1, []
+        while depth:
+            tok = p.eat()
+            if tok.kind == "punct" and tok.text == "<":
+                depth += 1
+            elif tok.kind == "punct" and tok.text == ">":
+                depth -= 1
+                if depth == 0:
+                    break
+            parts.append(tok.text)
+        inner = " ".join(parts)
+    types, groups = [], None
+    for part in _split_top(inner):
+        part = part.strip()
+        if part.startswith("groups"):
+            g = part.split("=", 1)[1].strip()
+            groups = p.aliases[g] if g.startswith("#") else p.affine(g)
+        elif part:
+            for t in _split_top(part.strip("() ")):
+                if t.strip():
+                    types.append(P.parse_type(t.strip()))
+    return types, groups
+
+
+def parse_inter_tile_produce(p, name, results) -> Op:
+    """``ktdp.inter_tile_produce producer_tiles_per_group = <set> : T -> !ktdp.tile_future<T, groups = <set>>
+    { ^bb0(%gid: index): ... ktdp.yield_partial %t : T }`` (ktir_cpu/dialects/ktdp_ops.py:1040-1097)."""
+    attrs: Dict[str, Any] = {}
+    while p.peek().kind == "id" and p.at("=", 1):
+        key = p.eat().text
+        p.eat("=")
+        attrs[key] = p.attr_value()
+        p.accept(",")
+    if "producer_tiles_per_group" not in attrs:
+        raise ValueError("ktdp.inter_tile_produce: missing producer_tiles_per_group")
+    if p.accept(":"):
+        attrs["partial_types"] = p.type_list()
+    if p.peek().kind != "arrow":
+        raise ValueError("ktdp.inter_tile_produce/reduce: missing !ktdp.tile_future<...> type")
+    p.i += 1
+    types, groups = _tile_future_type(p)
+    if groups is None:
+        raise ValueError("ktdp.inter_tile_produce: missing groups inside !ktdp.tile_future<...> type")
+    attrs["groups"] = groups
+    attrs["future_types"] = types
+    attrs.setdefault("partial_types", types)
+    regions = [_bb_region(p)] if p.at("{") else []
+    return Op(name, results, [], attrs, [Type("scalar", "tile_future")], regions)
+
+
+def parse_inter_tile_reduce(p, name, results) -> Op:
+    """``ktdp.inter_tile_reduce(%fut) consumer_tiles_per_group = <set>, identity(%id : T)
+    [, producer_dependency_per_consumer = <set>] : !ktdp.tile_future<...> -> T_r
+    { ^bb0(%lhs: T, %rhs: T): ... ktdp.yield_reduced %t : T }`` (ktir_cpu/dialects/ktdp_ops.py:1242-1330)."""
+    p.eat("(")
+    fut = p.eat_kind("ssa").text
+    p.eat(")")
+    attrs: Dict[str, Any] = {}
+    identity = None
+    while p.peek().kind == "id":
+        key = p.eat().text
+        if key == "identity":
+            p.eat("(")
+            identity = p.eat_kind("ssa").text
+            if p.accept(":"):
+                p.eat_kind("type")
+            p.eat(")")
+        else:
+            p.eat("=")
+            attrs[key] = p.attr_value()
+        p.accept(",")
+    if "consumer_tiles_per_group" not in attrs:
+        raise ValueError("ktdp.inter_tile_reduce: missing consumer_tiles_per_group")
+    if identity is None:
+        raise ValueError("ktdp.inter_tile_reduce: missing identity(...) operand")
+    p.eat(":")
+    _tile_future_type(p)
+    rtypes: List[Type] = []
+    if p.peek().kind == "arrow":
+        p.i += 1
+        rtypes = p.type_list()
+    regions = [_bb_region(p)] if p.at("{") else []
+    return Op(name, results, [fut, identity], attrs, _result_types(results, rtypes, []), regions)
+
+
 HANDLERS = {
+    "ktdp.inter_tile_produce": parse_inter_tile_produce,
+    "ktdp.inter_tile_reduce": parse_inter_tile_reduce,
+    "ktdp.yield_partial": parse_terminator,
+    "ktdp.yield_reduced": parse_terminator,
     "arith.constant": parse_constant,
     "ktdp.construct_memory_view": parse_memory_view,
     "ktdp.construct_access_tile": parse_access_tile,

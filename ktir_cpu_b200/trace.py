@@ -194,7 +194,7 @@ class Tracer:
                 scope[n] = v
 
     def trace_op(self, op: Op, scope):
-        from . import trace_mem, trace_ops2  # noqa: F401  (fill the rule table)
+        from . import trace_comm, trace_mem, trace_ops2  # noqa: F401  (fill the rule table)
         from . import trace_ops as T
         fn = T.TABLE.get(op.name)
         if fn is None:

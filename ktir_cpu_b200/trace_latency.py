@@ -38,13 +38,17 @@ class LatencyRecorder:
         self.records: List[OpRecord] = [OpRecord("func.return", LC.ZERO, np.ones(ncores, np.int64), "zero")]
 
     # -- executions per core at the tracer's current position ---------------------------------
+    repeat = None        # [n_cores] runs of the region being traced per execution (a ring reduce's combiner)
+
     def counts(self, tr) -> np.ndarray:
         axes = tuple(tr.axes)
         if tr.active is None:
-            return np.full(self.ncores, int(np.prod(axes[1:], dtype=np.int64)), np.int64)
-        act = tr.active
-        extra = int(np.prod(axes[act.ndim:], dtype=np.int64))        # axes of a symbolic loop
-        return act.reshape(self.ncores, -1).sum(1).astype(np.int64) * extra
+            c = np.full(self.ncores, int(np.prod(axes[1:], dtype=np.int64)), np.int64)
+        else:
+            act = tr.active
+            extra = int(np.prod(axes[act.ndim:], dtype=np.int64))        # axes of a symbolic loop
+            c = act.reshape(self.ncores, -1).sum(1).astype(np.int64) * extra
+        return c if self.repeat is None else c * self.repeat
 
     def _active_full(self, tr) -> np.ndarray:
         axes = tuple(tr.axes)
@@ -83,7 +87,14 @@ class LatencyRecorder:
             self.records.append(OpRecord(name, cat, cnt, "matmul", mnk=(int(m), int(n), int(k))))
             return
         if cat == LC.COMM:
-            raise NotImplementedError(f"Unknown category {cat}")
+            # every core sends its tile n - 1 times around the ring, whatever its group
+            # (RingReduceBackend.run, ktir_cpu/ops/comm_ops.py:294-345)
+            if not _is_node(result):
+                return
+            from .dtypes import bytes_per_elem
+            per_exec = (tr.total_cores - 1) * int(np.prod(result.shape, dtype=np.int64)) * bytes_per_elem(result.dtype)
+            self.records.append(OpRecord(name, cat, cnt, "comm", nbytes=cnt * per_exec))
+            return
         self.records.append(OpRecord(name, cat, cnt, "elems", n_elems=self._num_elements(result, operands)))
 
     @staticmethod

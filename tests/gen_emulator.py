@@ -100,6 +100,24 @@ def run(prog, arena: np.ndarray):
                 for kk in range(a["K"]):
                     acc = acc + A[..., :, kk:kk + 1] * B[..., kk:kk + 1, :]
                 out = acc.astype(NP_DT[d.dtype]).reshape(P, -1)
+            elif k == "ringred":
+                x = src[0].reshape(P, -1)
+                out = x.copy()
+                srcs = a["sources"]
+                if a["cluster"]:
+                    # ranks inside the cluster of each point -> points, through the CTA order table
+                    order = a["order"]
+                    cl = a["cluster"]
+                    where = np.empty(P, np.int64)
+                    where[order] = np.arange(P)
+                    first = (where // cl) * cl
+                    srcs = np.where(srcs >= 0, order[np.clip(first[:, None] + srcs, 0, P - 1)], -1)
+                for j in range(srcs.shape[1]):
+                    live = j < a["counts"]
+                    recv = x[np.clip(srcs[:, j], 0, None)]
+                    pair = (recv, out) if a["swapped"] else (out, recv)
+                    folded = _ew(a["op"], d.dtype, list(pair), {})
+                    out = np.where(live[:, None], folded, out)
             elif k == "store":
                 addr = a["base"][:, None] + a["rel"][None, :]
                 ok = (addr >= a["lo"]) & (addr < a["hi"])

@@ -126,6 +126,14 @@ def cases(ref_root=None):
     out["elementwise_f16_suite"] = (
         K.elementwise_suite(ops, 4096, 128, 4, "f16", "olt"), "elementwise_kernel",
         dict(x_ptr=x.view(np.float16), y_ptr=y.view(np.float16), **{n: np.zeros(4096, np.float16) for n in names}))
+    # cross-core all-reduce: every core stores what it holds (each folds in its own ring order)
+    rng = np.random.default_rng(9)
+    for n, g, cols, comb, dt, inner, strided in ((4, 4, 128, "add", "f16", 1, False), (8, 2, 64, "max", "f32", 1, True),
+                                                 (6, 3, 32, "mul", "f16", 2, False), (16, 16, 128, "add", "f16", 1, False),
+                                                 (16, 4, 256, "add", "f16", 1, False)):
+        x = rng.uniform(0.5, 1.5, (n * inner, cols)).astype(np.float16 if dt == "f16" else np.float32)
+        out[f"ring_allreduce_{n}x{g}_{comb}_{dt}" + ("_loop" if inner > 1 else "") + ("_strided" if strided else "")] = (
+            K.ring_allreduce(n, g, cols, comb, dt, inner, strided), "ring_allreduce", dict(in_ptr=x, out_ptr=np.zeros_like(x)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

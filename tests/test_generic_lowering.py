@@ -38,7 +38,9 @@ def run_generic(src, fn, kw):
     return out, kinds
 
 
-EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elementwise_f16_suite")
+EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elementwise_f16_suite",
+         "ring_allreduce_4x4_add_f16", "ring_allreduce_8x2_max_f32_strided", "ring_allreduce_6x3_mul_f16_loop",
+         "ring_allreduce_16x16_add_f16", "ring_allreduce_16x4_add_f16")
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 
@@ -64,6 +66,33 @@ def test_step_kinds_cover_reduction_matmul_and_indirect_access():
     assert {"load", "redl", "ew", "store"} <= k1
     assert {"matmul", "map", "redl"} <= k2
     assert {"addr", "idxadd", "gather"} <= k3
+
+
+def test_ring_reduce_uses_clusters_for_small_equal_groups():
+    """Groups of at most 8 cores of equal size become thread-block clusters (sources are ranks inside
+    the cluster); a 16-core group reads its partials from global memory (sources are points)."""
+    src, fn, kw, _ = load_golden("ring_allreduce_16x4_add_f16")
+    func = KTIRParser().parse_module(src).get_function(fn)
+    tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items()]
+    sess = Session(PlanOnlyDevice(), func, tensors, {}, arena_ptr=0)
+    (ring,) = [op for s in sess.plan.statements for op in s.prog.ops if op.kind == "ringred"]
+    assert ring.attrs["cluster"] == 4 and ring.attrs["sources"].max() == 3 and sorted(ring.attrs["order"]) == list(range(16))
+    assert (ring.attrs["counts"] == 3).all()
+    src, fn, kw, _ = load_golden("ring_allreduce_16x16_add_f16")
+    func = KTIRParser().parse_module(src).get_function(fn)
+    sess = Session(PlanOnlyDevice(), func, [(k, tuple(v.shape), v.dtype) for k, v in kw.items()], {}, arena_ptr=0)
+    (ring,) = [op for s in sess.plan.statements for op in s.prog.ops if op.kind == "ringred"]
+    assert ring.attrs["cluster"] == 0 and (ring.attrs["counts"] == 15).all()
+    # core 5 hears from 4, 3, 2, ... in that order
+    assert list(ring.attrs["sources"][5][:6]) == [4, 3, 2, 1, 0, 15]
+
+
+def test_a_core_that_skips_the_exchange_is_a_deadlock():
+    from ktir_cpu_b200 import kernels as K
+    func = KTIRParser().parse_module(K.ring_allreduce(4, 4, 128, absent_core=2)).get_function("ring_allreduce")
+    t = [("in_ptr", (4, 128), np.dtype(np.float16)), ("out_ptr", (4, 128), np.dtype(np.float16))]
+    with pytest.raises(RuntimeError, match="Deadlock detected: core 3 waiting on recv from core 2"):
+        Session(PlanOnlyDevice(), func, t, {}, arena_ptr=0)
 
 
 def test_scratch_is_reused():

@@ -75,3 +75,14 @@ def test_negative_index_raises():
     interp.load(src)
     with pytest.raises(IndexError, match="negative"):
         interp.execute_function(fn, **kwargs)
+
+
+def test_deadlock_message_when_a_core_skips_the_exchange():
+    """The message of the reference's scheduler (ktir_cpu/grid.py:615-621), core by core."""
+    from ktir_cpu_b200 import kernels as K
+    interp = OracleInterpreter()
+    interp.load(K.ring_allreduce(4, 4, 128, absent_core=2))
+    x = np.ones((4, 128), np.float16)
+    with pytest.raises(RuntimeError, match="Deadlock detected: core 3 waiting on recv from core 2; core 0 waiting on recv "
+                                           "from core 3; core 1 waiting on recv from core 0"):
+        interp.execute_function("ring_allreduce", in_ptr=x, out_ptr=np.zeros_like(x))
