@@ -82,11 +82,14 @@ class Session:
 
     def __init__(self, dev: R.Device, func, tensors: List[Tuple[str, Tuple[int, ...], np.dtype]],
                  scalars: Dict[str, Any], latency: bool = False, shard: Optional[Tuple[int, int]] = None,
-                 arena_ptr: Optional[int] = None, seeded: Sequence[Tuple[int, int, str]] = (), fused: bool = True):
+                 arena_ptr: Optional[int] = None, seeded: Sequence[Tuple[int, int, str]] = (), fused: bool = True,
+                 lx_bytes: int = 2 << 20):
         """``shard = (rank, world)`` plans only this rank's part of the kernel (see ``sharded.py``);
         ``arena_ptr`` places the arena in caller-owned device memory of at least ``arena_size(tensors)`` bytes;
         ``seeded`` = (byte address, nbytes, dtype) of memory written through ``interp.memory.hbm`` at fixed
-        addresses, which becomes part of the arena next to the argument tensors."""
+        addresses, which becomes part of the arena next to the argument tensors.  ``lx_bytes`` is the
+        per-core scratchpad capacity the kernel is checked against while it is traced
+        (``MemoryError("LX scratchpad overflow on core ...")``, ktir_cpu/grid.py:292-301)."""
         self.dev = dev
         self.func = func
         self.latency_records = None
@@ -110,11 +113,14 @@ class Session:
         self.arena = dev.alloc(self.arena_bytes + 256) if arena_ptr is None else arena_ptr
         self.arena_map = ArenaMap(allocs)
         try:
+            from .lx import LXModel, use_counts
             tracer = Tracer(func, scalars, ptrs)
+            tracer.lx = LXModel(tracer.ncores, 0, lx_bytes, use_counts(func.ops))
             if latency:
                 from .trace_latency import LatencyRecorder
                 tracer.latency = LatencyRecorder(tracer.ncores)
             stores = tracer.run()
+            self.lx_peak_bytes = int(tracer.lx.peak.max()) if tracer.ncores else 0
             if latency:
                 self.latency_records = tracer.latency.records
             self.n_cores = tracer.ncores
@@ -365,8 +371,9 @@ class KTIRInterpreter:
             if len(self._sessions) >= self._max_sessions:
                 old = next(iter(self._sessions))
                 self._sessions.pop(old).close()
+            lx_mb = getattr(self._latency_config, "lx_size_mb", 2) if self._latency_config is not None else 2
             sess = Session(self.device, func, tensors, scalars, latency=self._latency_config is not None,
-                           seeded=seeded, fused=self._fused, shard=_shard)
+                           seeded=seeded, fused=self._fused, shard=_shard, lx_bytes=int(lx_mb * 1024 * 1024))
             self._sessions[key] = sess
         return sess, kwargs
 

@@ -158,6 +158,7 @@ class Tracer:
         self.loop_path: List[int] = []
         self._loop_counter = 0
         self.latency = None            # a trace_latency.LatencyRecorder when the latency model is on
+        self.lx = None                 # an lx.LXModel when scratchpad accounting is on
         self.scope: Dict[str, Any] = {}
         for n, _ in func.args:
             key = n[1:]
@@ -177,6 +178,28 @@ class Tracer:
         self.trace_ops(self.func.ops, self.scope)
         return self.stores
 
+    def cores_active(self) -> np.ndarray:
+        """Per core: does it execute the op being traced (at any loop point)?"""
+        if self.active is None:
+            return np.ones(self.ncores, bool)
+        return self.active.reshape(self.ncores, -1).any(axis=1)
+
+    def trace_region(self, ops: Sequence[Op], scope: Dict[str, Any], bind: Sequence[Tuple[str, Any]] = ()):
+        """Trace a nested region in its own scratchpad scope (CoreContext.push_scope / pop_scope,
+        ktir_cpu/grid.py:210-236); ``bind`` = (name, tile) pairs the region starts with."""
+        lx = self.lx
+        if lx is None:
+            return self.trace_ops(ops, scope)
+        lx.push()
+        try:
+            cores = self.cores_active()
+            for name, tile in bind:
+                if hasattr(tile, "shape") and hasattr(tile, "dtype") and not isinstance(tile, np.ndarray):
+                    lx.set_value(name, tile, cores)
+            return self.trace_ops(ops, scope)
+        finally:
+            lx.pop()
+
     def trace_ops(self, ops: Sequence[Op], scope: Dict[str, Any]):
         for op in ops:
             r = self.trace_op(op, scope)
@@ -187,11 +210,15 @@ class Tracer:
     def bind(self, op: Op, scope, value):
         if not op.results:
             return
-        if len(op.results) == 1:
-            scope[op.results[0]] = value
-        else:
-            for n, v in zip(op.results, value):
-                scope[n] = v
+        pairs = [(op.results[0], value)] if len(op.results) == 1 else list(zip(op.results, value))
+        for n, v in pairs:
+            scope[n] = v
+        if self.lx is not None:
+            cores = self.cores_active()
+            for n, v in pairs:
+                if isinstance(v, Node):
+                    # constants are compile-time literals: no scratchpad (registry no_lx_charge)
+                    self.lx.set_value(n, v, cores, charge=op.name != "arith.constant")
 
     def trace_op(self, op: Op, scope):
         from . import trace_comm, trace_mem, trace_ops2  # noqa: F401  (fill the rule table)
@@ -203,6 +230,12 @@ class Tracer:
             raise ValueError(f"Unknown operation: {op.name}")
         lat = self.latency
         pre = lat.before_op(self, op, scope) if lat is not None else None
+        if self.lx is not None:
+            # operands are fetched before the result exists; a last use frees its tile
+            # (scf.for only peeks at its iter_args inits: they are copied, not consumed)
+            for n in op.operands[:_FETCHED.get(op.name, len(op.operands))]:
+                if isinstance(n, str):
+                    self.lx.fetch(n)
         r = fn(self, op, scope)
         if isinstance(r, _Yield):
             return r
@@ -210,6 +243,12 @@ class Tracer:
             lat.after_op(self, op, scope, r, pre)
         self.bind(op, scope, r)
         return r
+
+
+# How many leading operands a handler of the reference actually reads (the rest — an ``outs`` that only
+# gives the shape, the inits an scf.for copies — is never fetched, hence never released by a last use):
+# ktir_cpu/dialects/linalg_ops.py:254-303,600-608, ktir_cpu/dialects/scf_ops.py:57-66.
+_FETCHED = {"linalg.transpose": 1, "linalg.add": 2, "linalg.max": 2, "scf.for": 3}
 
 
 class _Yield:

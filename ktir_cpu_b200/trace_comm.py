@@ -89,7 +89,7 @@ def _combiner(tr: Tracer, op, partial: Node, folds: np.ndarray):
     if tr.latency is not None:
         tr.latency.repeat = folds
     try:
-        y = tr.trace_ops(reg.ops, inner)
+        y = tr.trace_region(reg.ops, inner, [(reg.arg_names[0], lhs), (reg.arg_names[1], rhs)])
     finally:
         if tr.latency is not None:
             tr.latency.repeat = None

@@ -266,7 +266,14 @@ def _select(tr, op, scope):
         nt, nf = _as_operand(t, like, False), _as_operand(f, like, False)
         return ew("arith.select", [c, nt, nf], dtype=like.dtype)
     if isinstance(c, np.ndarray):
-        raise Unsupported("arith.select on a per-core condition")
+        # a condition that differs between cores / loop points picks between integer values
+        if is_node(t) or is_node(f):
+            raise Unsupported("arith.select of tiles on a per-core condition")
+        if not (is_iv(t) and is_iv(f)):
+            raise Unsupported("arith.select of float scalars on a per-core condition")
+        n = max(x.ndim for x in (c, t, f) if isinstance(x, np.ndarray))
+        grow = lambda x: x.reshape(x.shape + (1,) * (n - x.ndim)) if isinstance(x, np.ndarray) else x   # noqa: E731
+        return np.where(grow(c.astype(bool)), grow(t), grow(f)).astype(np.int64)
     return t if c else f
 
 

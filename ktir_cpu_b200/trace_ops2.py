@@ -104,11 +104,63 @@ def _reduce(tr, op, scope):
             shape = tuple(s for i, s in enumerate(tile.shape) if i not in dims)
         result = Node("reduce", shape, tile.dtype, (tile,),
                       {"op": comb, "dims": None if dims is None else tuple(sorted(dims))})
+        if tr.lx is not None:
+            _reduce_transients(tr, op, tile, dims, shape, outs)
         if is_node(outs):
             result = ew(comb, [result, outs], dtype=tile.dtype)
     if outs_name and result is not None:
         scope[outs_name] = result
+        if tr.lx is not None and is_node(result):
+            tr.lx.set_value(outs_name, result, tr.cores_active())      # the result is bound under the outs name too
     return result
+
+
+def _reduce_transients(tr, op, tile, dims, out_shape, outs):
+    """Replay the scratchpad traffic of the pairwise fold (ktir_cpu/dialects/linalg_ops.py:61-133,
+    160-246): every level binds its two halves and runs the combiner ops on them in a scope of its
+    own, and the folded value is combined once more with ``outs``.  The shorthand form
+    (``linalg.reduce { arith.addf }``) runs a synthesised one-op region whose names no use count
+    knows, so nothing in it is released early."""
+    lx = tr.lx
+    cores = tr.cores_active()
+    if op.regions and op.regions[0].ops:
+        reg = op.regions[0]
+        body = reg.ops
+        names = list(reg.arg_names) or list(body[0].operands)
+    else:
+        names = ["__reduce_in__", "__reduce_acc__"]
+        body = [Op(op.attrs.get("combiner") or "arith.addf", ["__reduce_combined__"], list(names)),
+                Op("linalg.yield", [], ["__reduce_combined__"])]
+
+    def run(shape, rhs_tile=None):
+        lx.push()
+        try:
+            lx.set_value(names[0], Node("held", tuple(shape), tile.dtype), cores)
+            if len(names) > 1:
+                lx.set_value(names[1], rhs_tile if rhs_tile is not None else Node("held", tuple(shape), tile.dtype), cores)
+            for o in body:
+                for n in o.operands:
+                    lx.fetch(n)
+                for r in o.results:
+                    lx.set_value(r, Node("held", tuple(shape), tile.dtype), cores)
+        finally:
+            lx.pop()
+    shape = list(tile.shape)
+    if dims is None:
+        shape, fold = [int(np.prod(shape, dtype=np.int64))], [0]
+    else:
+        fold = sorted(dims, reverse=True)
+    for d in fold:
+        n = shape[d]
+        while n > 1:
+            half = n // 2
+            lvl = list(shape)
+            lvl[d] = half
+            run(lvl)
+            n = half + (n % 2)
+        shape[d] = 1
+    if is_node(outs) and len(out_shape):
+        run(out_shape, outs)
 
 
 @rule("linalg.fill")
@@ -153,6 +205,8 @@ def _matmul(tr, op, scope):
              {"batched": op.name.endswith("batch_matmul"), "prod_dtype": a.dtype})
     if is_node(acc):
         scope[op.operands[2]] = n
+        if tr.lx is not None and not tr.lx.is_free(acc):
+            tr.lx.same_tile(n, acc)              # accumulated in place: the result is the outs tile
     return n
 
 
@@ -201,11 +255,15 @@ def _generic(tr, op, scope):
         raise ValueError("linalg.generic: cannot determine bb0 argument names")
     inner = dict(scope)
     inner["__linalg_shape__"] = tuple(outs.shape)
+    held = []          # every tile input is gathered into the iteration shape, outs is copied: new tiles in the body's scope
     for i, (v, m) in enumerate(zip(ins, maps[:n_ins])):
         inner[reg.arg_names[i]] = _map_input(v, m, outs.shape) if is_node(v) else v
+        if is_node(v):
+            held.append((reg.arg_names[i], Node("held", tuple(outs.shape), v.dtype)))
     if n_ins < len(reg.arg_names):
         inner[reg.arg_names[n_ins]] = outs
-    r = tr.trace_ops(reg.ops, inner)
+        held.append((reg.arg_names[n_ins], Node("held", tuple(outs.shape), outs.dtype)))
+    r = tr.trace_region(reg.ops, inner, held)
     v = r.values[0] if isinstance(r, _Yield) else None
     if is_node(v):
         v = cast(v, outs.dtype)
@@ -264,7 +322,7 @@ def _for(tr: Tracer, op: Op, scope):
         tr.loop_path.append(tr._loop_counter)
         inner = dict(scope)
         inner[iv_name] = ivs
-        tr.trace_ops(reg.ops, inner)
+        tr.trace_region(reg.ops, inner)
         tr.loop_path.pop()
         tr.axes, tr.active = saved_axes, saved_active
         return None
@@ -280,17 +338,31 @@ def _for(tr: Tracer, op: Op, scope):
     if T > MAX_UNROLL:
         raise Unsupported(f"scf.for with iter_args and {T} iterations")
     vals = list(inits)
+    _lx_bind_carried(tr, iter_names, [Node("held", v.shape, v.dtype) if is_node(v) else v for v in vals])
     for k in range(T):
         inner = dict(scope)
         inner[iv_name] = iv_bin(lambda a, b: a + b, lb, iv_bin(lambda s, kk: s * kk, step, k))
         for n, v in zip(iter_names, vals):
             inner[n] = v
-        r = tr.trace_ops(reg.ops, inner)
+        r = tr.trace_region(reg.ops, inner)
         if isinstance(r, _Yield):
             vals = list(r.values)
+            _lx_bind_carried(tr, iter_names, vals)
     if not op.results:
         return None
     return vals[0] if len(vals) == 1 else tuple(vals)
+
+
+def _lx_bind_carried(tr: Tracer, names, values):
+    """Loop-carried tiles live in the scope AROUND the loop: bound there before the first iteration
+    (private copies of the inits) and re-bound there after every iteration's body scope has been
+    left (ktir_cpu/ops/control_ops.py:56-98, 160-182) — so the body can never release them early."""
+    if tr.lx is None:
+        return
+    cores = tr.cores_active()
+    for n, v in zip(names, values):
+        if is_node(v):
+            tr.lx.set_value(n, v, cores)
 
 
 def _symbolic_loop(tr: Tracer, op: Op, scope, lb, step, T: int, inits):
@@ -312,7 +384,8 @@ def _symbolic_loop(tr: Tracer, op: Op, scope, lb, step, T: int, inits):
         ph = Node("iter", v.shape, v.dtype, (), {"index": i})
         placeholders.append(ph)
         inner[n] = ph
-    r = tr.trace_ops(reg.ops, inner)
+    _lx_bind_carried(tr, iter_names, placeholders)
+    r = tr.trace_region(reg.ops, inner)
     tr.axes = saved_axes
     if len(tr.stores) != n_stores:
         raise Unsupported("ktdp.store inside an scf.for that carries a matmul accumulator")
@@ -323,6 +396,11 @@ def _symbolic_loop(tr: Tracer, op: Op, scope, lb, step, T: int, inits):
         ph.attrs["loop"] = info
     results = [Node("loopres", v.shape, v.dtype, (), {"loop": info, "index": i})
                for i, v in enumerate(inits)]
+    _lx_bind_carried(tr, iter_names, list(r.values))
+    if tr.lx is not None:
+        for res, y in zip(results, r.values):
+            if is_node(y):
+                tr.lx.same_tile(res, y)          # the loop's results are the tiles of the last yield
     if not op.results:
         return None
     return results[0] if len(results) == 1 else tuple(results)
@@ -341,13 +419,13 @@ def _if(tr, op, scope):
         for reg, m in zip(op.regions, (full, ~full)):
             tr.active = m if saved is None else (saved & m)
             if tr.active.any():
-                tr.trace_ops(reg.ops, dict(scope))
+                tr.trace_region(reg.ops, dict(scope))
         tr.active = saved
         return None
     reg = op.regions[0] if cond else (op.regions[1] if len(op.regions) > 1 else None)
     if reg is None:
         return None
-    r = tr.trace_ops(reg.ops, dict(scope))
+    r = tr.trace_region(reg.ops, dict(scope))
     if isinstance(r, _Yield) and r.values:
         return r.values[0] if len(r.values) == 1 else tuple(r.values)
     return None

@@ -182,12 +182,63 @@ def latency_main(ref_root: str):
         json.dump(out, f, indent=1, sort_keys=True)
 
 
+def overflow_cases():
+    """name -> (source, function, kwargs, lx_size_mb): kernels whose tiles do not fit the scratchpad."""
+    x = np.zeros((32, 16384), np.float16)
+    v = np.zeros(1 << 21, np.float16)
+    return {
+        "softmax_32_rows_of_16384_at_once": (K.softmax_rows(32, 16384, 1, 32, True), "softmax_kernel",
+                                             dict(output_ptr=np.zeros_like(x), input_ptr=x), 2),
+        "vector_add_block_524288_in_1MB": (K.vector_add(1 << 21, 524288, 4), "add_kernel",
+                                           dict(x_ptr=v, y_ptr=v, output_ptr=np.zeros_like(v), BLOCK_SIZE=524288), 1),
+    }
+
+
+def lx_main(ref_root: str):
+    """``lx.json``: the highest scratchpad use of any core, per case, as the reference accounts it
+    (ktir_cpu/grid.py:253-361), and the messages of the cases that overflow."""
+    import json
+    sys.path.insert(0, ref_root)
+    from ktir_cpu import HardwareConfig, KTIRInterpreter
+    from ktir_cpu.grid import CoreContext
+    peak = {}
+    charge = CoreContext._charge_lx
+
+    def watch(self, value):
+        charge(self, value)
+        peak[self.core_id] = max(peak.get(self.core_id, 0), self.lx.used)
+    CoreContext._charge_lx = watch
+    out = {"peak_bytes": {}, "overflow": {}}
+    for name, (src, fn, kw) in cases(ref_root).items():
+        peak.clear()
+        interp = KTIRInterpreter()
+        interp.load(src)
+        interp.execute_function(fn, **kw)
+        out["peak_bytes"][name] = int(max(peak.values())) if peak else 0
+    for name, (src, fn, kw, mb) in overflow_cases().items():
+        interp = KTIRInterpreter(latency_config=HardwareConfig(lx_size_mb=mb))
+        interp.load(src)
+        try:
+            interp.execute_function(fn, **kw)
+            raise SystemExit(f"{name}: expected an LX overflow")
+        except MemoryError as e:
+            out["overflow"][name] = str(e)
+            print("overflow", name, e)
+    CoreContext._charge_lx = charge
+    with open(os.path.join(HERE, "lx.json"), "w") as f:
+        json.dump(out, f, indent=1, sort_keys=True)
+
+
 if __name__ == "__main__":
     args = [a for a in sys.argv[1:] if not a.startswith("--")]
     root = args[0] if args else os.environ.get("KTIR_REFERENCE", "")
     if not root:
         sys.exit("usage: make_golden.py <path of a ktir_cpu checkout> [--only=<case>] [--latency-only]")
     only = [a[len("--only="):] for a in sys.argv[1:] if a.startswith("--only=")]
+    if "--lx-only" in sys.argv:
+        lx_main(root)
+        sys.exit(0)
     if "--latency-only" not in sys.argv:
         main(root, only)
     latency_main(root)
+    lx_main(root)
