@@ -676,6 +676,21 @@ def ring_allreduce(n_cores: int = 4, group: int = 4, cols: int = 128, combine: s
     return s + "    return\n  }\n}\n"
 
 
+def shared_slot_store(n_cores: int = 4, slots: int = 2, cols: int = 64, dtype: str = "f16") -> str:
+    """Every core doubles its row of ``x`` ([n_cores, cols]) and stores it to row ``core % slots`` of
+    ``out`` ([slots, cols]): several cores write the same bytes, and the reference — which runs its
+    cores one after the other (ktir_cpu/grid.py:595-613) — keeps the value of the highest core id."""
+    t, at = f"tensor<1x{cols}x{dtype}>", f"!ktdp.access_tile<1x{cols}xindex>"
+    return (f"module {{\n  func.func @shared_slot(%x_ptr: index, %out_ptr: index) attributes {{grid = [{n_cores}, 1]}} {{\n"
+            f"    %c = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+            f"    %n_slots = arith.constant {slots} : index\n    %slot = arith.remui %c, %n_slots : index\n"
+            + view("x_view", "x_ptr", [n_cores, cols], dtype) + view("out_view", "out_ptr", [slots, cols], dtype)
+            + tile("x_tile", "x_view", ["%c", "%c0"], [1, cols], [n_cores, cols], dtype)
+            + tile("out_tile", "out_view", ["%slot", "%c0"], [1, cols], [slots, cols], dtype)
+            + f"    %x = ktdp.load %x_tile : {at} -> {t}\n    %twice = arith.addf %x, %x : {t}\n"
+              f"    ktdp.store %twice, %out_tile : {t}, {at}\n    return\n  }}\n}}\n")
+
+
 def layernorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, eps: float = 1e-5) -> str:
     """y = (x - mean) / sqrt(var + eps) * w + b per row, f32 statistics, one row per iteration.
 

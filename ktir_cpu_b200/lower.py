@@ -112,6 +112,22 @@ def _split_item_table(stmt, table: np.ndarray, geoms, bpes, launch_fn, piece_byt
     return chunks
 
 
+def _order_item_table(stmt, sel: np.ndarray, n_lead: int, rounds: Dict[int, int], dev):
+    """Reorder a statement's item table so that items of later rounds come later and remember the
+    round boundaries; the launches then go out round by round."""
+    per_item = np.array([rounds.get(int(p), 0) for p in np.repeat(sel, n_lead)], np.int64)
+    order = np.argsort(per_item, kind="stable")
+    stmt.table = np.ascontiguousarray(stmt.table[order])
+    dev.free(stmt.dev_table)
+    stmt.dev_table = dev.upload(stmt.table)
+    stmt.args.dev_item_offsets = stmt.dev_table
+    stmt.device_arrays = [stmt.dev_table]
+    srt = per_item[order]
+    cuts = np.flatnonzero(np.diff(srt)) + 1
+    stmt.rounds = list(zip(np.concatenate([[0], cuts]).tolist(), np.concatenate([cuts, [len(srt)]]).tolist()))
+    stmt.launches = len(stmt.rounds)
+
+
 def _points(store: Store):
     """Flat indices (and core ids) of the active iteration points of a store."""
     n = int(np.prod(store.axes))
@@ -312,6 +328,7 @@ class EwStatement(Statement):
             self.fps.append(Footprint(rstart, rstart + g.cols * bpe, pts, np.repeat(cores, n_lead * g.rows),
                                       k == len(operands) - 1, stmt_id))
         self.table = table
+        self._sel, self._n_lead, self._dev, self.rounds = sel, n_lead, dev, None
         self.args = R.EwArgs()
         a = self.args
         a.n_items = table.shape[0]
@@ -331,9 +348,22 @@ class EwStatement(Statement):
 
     def launch(self, dev, arena_ptr):
         self.args.arena = arena_ptr
+        if self.rounds:                       # several points store to the same bytes: in sequential order
+            n_op = self.table.shape[1]
+            for lo, hi in self.rounds:
+                sub = _copy_args(self.args)
+                sub.dev_item_offsets = self.dev_table + lo * n_op * 8
+                sub.n_items = hi - lo
+                dev.check(dev.lib.ktb_launch_ew_stream(dev.h, C.byref(sub)))
+            return
         dev.check(dev.lib.ktb_launch_ew_stream(dev.h, C.byref(self.args)))
 
+    def order_points(self, rounds: Dict[int, int]):
+        _order_item_table(self, self._sel, self._n_lead, rounds, self._dev)
+
     def split(self, piece_bytes: int):
+        if self.rounds:
+            return None
         a, n_op = self.args, self.table.shape[1]
         geoms = [(a.rows, int(a.row_stride[k]), a.cols) for k in range(n_op)]
         bpes = [2 if a.dtype[k] == R.KTB_F16 else 4 for k in range(n_op)]
@@ -489,6 +519,7 @@ class SoftmaxStatement(Statement):
         a.max_is_maxnum = 1 if m["maxop"] == "arith.maxnumf" else 0
         a.max_init, a.sum_init = m["max_init"], m["sum_init"]
         self.table = table
+        self._sel, self._n_lead, self._dev, self.rounds = sel, n_lead, dev, None
         self.dev_table = dev.upload(table)
         a.dev_item_offsets = self.dev_table
         self.device_arrays = [self.dev_table]
@@ -497,9 +528,21 @@ class SoftmaxStatement(Statement):
 
     def launch(self, dev, arena_ptr):
         self.args.arena = arena_ptr
+        if self.rounds:
+            for lo, hi in self.rounds:
+                sub = _copy_args(self.args)
+                sub.dev_item_offsets = self.dev_table + lo * 2 * 8
+                sub.n_items = hi - lo
+                dev.check(dev.lib.ktb_launch_row_softmax(dev.h, C.byref(sub)))
+            return
         dev.check(dev.lib.ktb_launch_row_softmax(dev.h, C.byref(self.args)))
 
+    def order_points(self, rounds: Dict[int, int]):
+        _order_item_table(self, self._sel, self._n_lead, rounds, self._dev)
+
     def split(self, piece_bytes: int):
+        if self.rounds:
+            return None
         a = self.args
         geoms = [(a.rows_per_item, int(a.in_row_stride), a.cols), (a.rows_per_item, int(a.out_row_stride), a.cols)]
         bpes = [2 if d == R.KTB_F16 else 4 for d in (a.in_dtype, a.out_dtype)]
@@ -528,13 +571,19 @@ def check_hazards(fps: List[Footprint]):
     coincide exactly with runs of the same (statement, point) — an in-place
     update — or with runs of the same core in another statement (program order
     on one core is kept by launch order).  Any other overlap involving a write
-    means the sequential core order of the reference matters."""
+    means the sequential core order of the reference matters.
+
+    One such case has a device path and is returned instead of raised: byte runs that several
+    points of ONE statement store to and nobody else touches (every core writing the same
+    result tile, say).  The reference leaves the value of the last point in core-major order
+    (ktir_cpu/grid.py:595-613); the caller orders the statement's launches accordingly.
+    Returns {statement: [arrays of point ids sharing a run]}."""
     if not fps or not any(f.write for f in fps):
-        return
+        return {}
     starts = np.concatenate([f.starts for f in fps])
     ends = np.concatenate([f.ends for f in fps])
     if not len(starts):
-        return
+        return {}
     write = np.concatenate([np.full(len(f.starts), f.write) for f in fps])
     stmt = np.concatenate([np.full(len(f.starts), f.stmt, np.int64) for f in fps])
     point = np.concatenate([f.points for f in fps])
@@ -556,9 +605,27 @@ def check_hazards(fps: List[Footprint]):
     srt = np.lexsort((key, stmt, gid))
     g2, s2, k2 = gid[srt], stmt[srt], key[srt]
     clash = (g2[1:] == g2[:-1]) & (s2[1:] == s2[:-1]) & (k2[1:] != k2[:-1]) & g_write[g2[1:]]
+    ordered: Dict[int, List[np.ndarray]] = {}
     if bad.any() or clash.any():
-        raise Unsupported("memory written by one core/iteration is accessed by another: "
-                          "sequential core order matters and has no device path yet")
+        # groups whose members are all writes of one statement by known points can be ordered
+        g_all_write = np.ones(ng, bool)
+        np.logical_and.at(g_all_write, gid, write)
+        g_stmt_lo = np.full(ng, np.iinfo(np.int64).max)
+        g_stmt_hi = np.full(ng, -1)
+        np.minimum.at(g_stmt_lo, gid, stmt)
+        np.maximum.at(g_stmt_hi, gid, stmt)
+        g_known = np.ones(ng, bool)
+        np.logical_and.at(g_known, gid, point >= 0)
+        fixable = g_all_write & (g_stmt_lo == g_stmt_hi) & g_known
+        trouble = np.zeros(ng, bool)
+        trouble[gid[bad]] = True
+        trouble[g2[1:][clash]] = True
+        if (trouble & ~fixable).any():
+            raise Unsupported("memory written by one core/iteration is accessed by another: "
+                              "sequential core order matters and has no device path yet")
+        for g in np.flatnonzero(trouble):
+            members = np.unique(point[gid == g])
+            ordered.setdefault(int(g_stmt_lo[g]), []).append(members)
     # partial overlaps between distinct runs
     us, ue = starts[first], ends[first]
     k = np.searchsorted(us, ue, side="left")        # runs i+1 .. k-1 start inside run i
@@ -568,6 +635,27 @@ def check_hazards(fps: List[Footprint]):
     if ((k > idx + 1) & (g_write | (writes_after > 0))).any():
         raise Unsupported("overlapping tile stores/loads across cores or iterations: "
                           "sequential core order matters and has no device path yet")
+    return ordered
+
+
+def launch_rounds(groups: List[np.ndarray]) -> Dict[int, int]:
+    """Round of every point that shares a stored run with another point: points are taken in
+    sequential (core-major) order and each goes one round after the latest earlier point it
+    collides with, so launching the rounds in order reproduces last-writer-wins."""
+    rounds: Dict[int, int] = {}
+    by_point: Dict[int, List[np.ndarray]] = {}
+    for g in groups:
+        for p in g:
+            by_point.setdefault(int(p), []).append(g)
+    for p in sorted(by_point):
+        r = 0
+        for g in by_point[p]:
+            for q in g:
+                q = int(q)
+                if q < p and q in rounds:
+                    r = max(r, rounds[q] + 1)
+        rounds[p] = r
+    return rounds
 
 
 class Plan:
@@ -652,7 +740,12 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
             stmt = generic_statement(dev, st, arena, sid)
         plan.statements.append(stmt)
     fps = [f for s in plan.statements for f in s.footprints()]
-    check_hazards(fps)
+    for sid, groups in check_hazards(fps).items():
+        stmt = plan.statements[sid]
+        if not hasattr(stmt, "order_points"):
+            raise Unsupported(f"several cores store to the same bytes in a {stmt.kind} statement: "
+                              "sequential core order matters and has no device path yet")
+        stmt.order_points(launch_rounds(groups))
     read_names, write_runs = set(), {}
     for s in plan.statements:
         for f in s.footprints():

@@ -609,6 +609,8 @@ def _make_statement_class():
             sel, cores = _points(store)
             self.prog, written, direct, ind_reads, ind_write = build_generic(store, arena, sel)
             self.extra_written = list(written) if ind_write is not None else []
+            self._dev = dev
+            self._store_points = sel if self.prog.P == len(sel) else np.arange(self.prog.P)
             self.launches = len(self.prog.ops)
             self.device_arrays: List[int] = []
             self.scratch = dev.alloc(self.prog.scratch_bytes)
@@ -695,6 +697,24 @@ def _make_statement_class():
                 self.fps.append(Footprint(np.array([ind_write.byte_lo]), np.array([ind_write.byte_hi]), neg, neg,
                                           True, stmt_id))
             self._bytes = sum(int((f.ends - f.starts).sum()) for f in self.fps)
+
+        def order_points(self, rounds):
+            """Several points store to the same bytes: the final store step is repeated once per round,
+            each time with only that round's points inside the allocation (the others fall outside
+            and are dropped), so the last point in sequential order wins."""
+            last = self.steps[-1]
+            op = self.prog.ops[-1]
+            if op.kind != "store":
+                raise Unsupported("several cores scatter to the same bytes through an indirect store")
+            base = np.ascontiguousarray(op.attrs["base"], np.int64)
+            pts = self._store_points
+            per_point = np.array([rounds.get(int(p), 0) for p in pts], np.int64)
+            self.steps = self.steps[:-1]
+            for r in range(int(per_point.max()) + 1):
+                g = R.GenOpArgs.from_buffer_copy(last)
+                g.dev_base = self._up(self._dev, np.where(per_point == r, base, -(1 << 50)))
+                self.steps.append(g)
+            self.launches = len(self.steps)
 
         def _up(self, dev, arr: np.ndarray) -> int:
             p = dev.upload(arr if arr.size else np.zeros(1, arr.dtype))

@@ -134,6 +134,10 @@ def cases(ref_root=None):
         x = rng.uniform(0.5, 1.5, (n * inner, cols)).astype(np.float16 if dt == "f16" else np.float32)
         out[f"ring_allreduce_{n}x{g}_{comb}_{dt}" + ("_loop" if inner > 1 else "") + ("_strided" if strided else "")] = (
             K.ring_allreduce(n, g, cols, comb, dt, inner, strided), "ring_allreduce", dict(in_ptr=x, out_ptr=np.zeros_like(x)))
+    # several cores store to the same rows: the last core in id order wins
+    x = rng.standard_normal((12, 64)).astype(np.float16)
+    out["shared_slot_store_12x5"] = (K.shared_slot_store(12, 5, 64), "shared_slot",
+                                     dict(x_ptr=x, out_ptr=np.zeros((5, 64), np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

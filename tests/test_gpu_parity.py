@@ -26,7 +26,7 @@ def _run_both(src, fn, kwargs):
 
 
 def _exact(name):
-    return name.startswith(("vector_add", "gather", "ring_allreduce"))
+    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot"))
 
 
 SUPPORTED = golden_names()
@@ -66,6 +66,22 @@ def test_gpu_matches_reference_fixture(name, build_lib):
                                        rtol=2e-2, atol=2e-1)
         else:
             np.testing.assert_allclose(got[k].astype(np.float32), expected[k].astype(np.float32), **TOL)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_colliding_stores_keep_the_last_core(fused, build_lib):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((40, 256)).astype(np.float16)
+    src = K.shared_slot_store(40, 7, 256)
+    gpu = KTIRInterpreter(fused_kernels=fused)
+    gpu.load(src)
+    got = gpu.execute_function("shared_slot", x_ptr=x, out_ptr=np.zeros((7, 256), np.float16))["out_ptr"]
+    gpu.close()
+    want = np.stack([(x[max(c for c in range(40) if c % 7 == s)] * np.float16(2)) for s in range(7)])
+    np.testing.assert_array_equal(got, want)
+    ora = OracleInterpreter()
+    ora.load(src)
+    np.testing.assert_array_equal(got, ora.execute_function("shared_slot", x_ptr=x, out_ptr=np.zeros((7, 256), np.float16))["out_ptr"])
 
 
 def test_vector_add_bit_exact_and_inputs_untouched(build_lib):

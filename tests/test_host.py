@@ -76,13 +76,18 @@ def test_plan_softmax_flattens_loop_into_launch():
     assert st.bytes_moved() == 2 * 8192 * 4096 * 2
 
 
-def test_cross_core_overlap_is_rejected():
-    """Two cores storing to the same tile need the sequential core order of the reference."""
+def test_cores_storing_to_the_same_tile_are_launched_in_core_order():
+    """The reference runs its cores one after the other, so the last core's store survives
+    (ktir_cpu/grid.py:595-613); the plan launches colliding stores in as many ordered rounds."""
     src = K.vector_add(4096, 128, 32).replace("%offset = arith.muli %core_id, %BLOCK_SIZE : index",
                                               "%offset = arith.constant 0 : index")
     t = [("x_ptr", (4096,), F16), ("y_ptr", (4096,), F16), ("output_ptr", (4096,), F16)]
-    with pytest.raises(Unsupported, match="sequential core order"):
-        _plan(src, "add_kernel", t, dict(BLOCK_SIZE=128))
+    (stmt,) = _plan(src, "add_kernel", t, dict(BLOCK_SIZE=128)).plan.statements
+    assert stmt.rounds == [(i, i + 1) for i in range(32)] and stmt.launches == 32
+    sess = _plan(K.shared_slot_store(12, 5, 64), "shared_slot", [("x_ptr", (12, 64), F16), ("out_ptr", (5, 64), F16)], {})
+    (stmt,) = sess.plan.statements
+    assert stmt.rounds == [(0, 5), (5, 10), (10, 12)]         # cores 0-4, 5-9, 10-11
+    assert sess.transfer_plan().split is False                  # ordered launches are not pipelined
 
 
 def test_unmapped_pointer_raises_value_error():
