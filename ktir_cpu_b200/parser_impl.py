@@ -247,7 +247,11 @@ class ModuleParser:
             return self._infix(results, line)
         name = self.eat().text
         from .parser_ops import HANDLERS, parse_simple, parse_opaque
-        fn = HANDLERS.get(name)
+        from .registry import plugin_parser
+        from .trace_ops import TABLE
+        fn = plugin_parser(name) or HANDLERS.get(name)
+        if fn is None and name in TABLE and not name.startswith(("ktdp.", "linalg.", "scf.", "func.")):
+            fn = parse_simple                  # a registered plug-in op in the generic form
         if fn is None:
             if name.startswith(("arith.", "math.", "tensor.")) or name in ("ktdp.load", "ktdp.store",
                                                                             "ktdp.get_compute_tile_id",

@@ -218,7 +218,8 @@ class Tracer:
             for n, v in pairs:
                 if isinstance(v, Node):
                     # constants are compile-time literals: no scratchpad (registry no_lx_charge)
-                    self.lx.set_value(n, v, cores, charge=op.name != "arith.constant")
+                    from .registry import NO_LX_CHARGE
+                    self.lx.set_value(n, v, cores, charge=op.name not in NO_LX_CHARGE)
 
     def trace_op(self, op: Op, scope):
         from . import trace_comm, trace_mem, trace_ops2  # noqa: F401  (fill the rule table)
