@@ -88,7 +88,9 @@ extern "C" int ktb_launch_ew_stream(ktb_ctx* ctx, const ktb_ew_args* args) {
 
     // Single-op programs over inputs (0,1) run the specialised kernel.
     int special = -1;
-    if (p.n_ops == 1 && p.ops[0].a == 0 && (p.n_in == 1 || p.ops[0].b == 1) && p.ops[0].dst == p.result_reg)
+    // (a binary op whose two operands are the SAME input tile, x + x, takes the general path)
+    if (p.n_ops == 1 && p.ops[0].a == 0 && p.ops[0].dst == p.result_reg &&
+        ((p.ops[0].opcode & 0xff) == KTB_VM_MOV || (p.n_in >= 2 && p.ops[0].b == 1)))
         special = p.ops[0].opcode & 0xff;
     if (p.n_ops == 0 && p.result_reg == 0) special = KTB_VM_MOV;
 

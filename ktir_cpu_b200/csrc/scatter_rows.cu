@@ -211,13 +211,15 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_cons
 //   apply:   one warp per destination row orders its bucket by entry id — which is tile order —
 //            and applies the updates one after another with the row held in registers: the row is
 //            read once and written once however many tiles touch it.
-// Scratch layout: int32 count[R + 1] (count[R] = overflow length) | int32 bucket_e[R * C] |
-// int64 bucket_addr[KTB_ROWS_MAX_IN][R * C] | int32 overflow[2 * E] (row, entry pairs).
+// Scratch layout: int32 count[R + 2] (count[R] = overflow length, count[R + 1] = used part of `sorted`) |
+// int32 bucket_e[R * C] | int64 bucket_addr[KTB_ROWS_MAX_IN][R * C] | int32 overflow[2 * E] (row, entry
+// pairs) | int32 sorted[E] (per long row a segment with its entry ids in ascending order).
 struct sc_scratch {
     int32_t* count;
     int32_t* bucket_e;
     int64_t* bucket_addr;     // [k][R * C]
     int32_t* overflow;
+    int32_t* sorted;
     int32_t cap;              // C
     int64_t slots;            // R * C
 };
@@ -231,7 +233,7 @@ static inline int sc_bucket_cap(int64_t E, int64_t R) {
 
 static inline size_t sc_scratch_bytes(int64_t E, int64_t R) {
     const int64_t slots = R * sc_bucket_cap(E, R);
-    return (size_t)(4 * (R + 2) + 4 * slots + 8 + 8 * (int64_t)KTB_ROWS_MAX_IN * slots + 8 * E + 64);
+    return (size_t)(4 * (R + 2) + 4 * slots + 8 + 8 * (int64_t)KTB_ROWS_MAX_IN * slots + 12 * E + 64);
 }
 
 static inline sc_scratch sc_carve(void* base, int64_t E, int64_t R) {
@@ -244,6 +246,7 @@ static inline sc_scratch sc_carve(void* base, int64_t E, int64_t R) {
     p = (p + 7) & ~(uintptr_t)7;
     s.bucket_addr = reinterpret_cast<int64_t*>(p);
     s.overflow = reinterpret_cast<int32_t*>(s.bucket_addr + (int64_t)KTB_ROWS_MAX_IN * s.slots);
+    s.sorted = s.overflow + 2 * E;
     return s;
 }
 
@@ -409,9 +412,60 @@ __global__ void __launch_bounds__(256, 4) ktb_scatter_apply_kernel(const __grid_
                 if (act) sc_store_row<V>(a.arena, a.out, dst, col, a.cols, cur);
             }
         } else {
-            // long chain (more tiles hit this row than a bucket holds): the entries are in the bucket
-            // and in the overflow list; they are selected one by one in ascending entry id
+            // long chain (more tiles hit this row than a bucket holds): its entries sit in the bucket and,
+            // mixed with those of other rows, in the overflow list.  They are collected ONCE into a
+            // segment of the `sorted` area, ordered there by entry id (= tile order), and then replayed
+            // for every column chunk — cost O(list scan + n log^2 n + n * chunks) instead of a full
+            // rescan of the lists for every single update.
             const int n_ovf = sc.count[a.dst_rows];
+            int n = 0;
+            int32_t* seg;
+            {
+                int seg0 = 0;
+                if (lane == 0) seg0 = atomicAdd(&sc.count[a.dst_rows + 1], rmw ? cnt : 1);
+                seg = sc.sorted + __shfl_sync(0xffffffffu, seg0, 0);
+            }
+            if (rmw) {
+                for (int i0 = 0; i0 < sc.cap + n_ovf; i0 += 32) {
+                    const int i = i0 + lane;
+                    int32_t v = -1;
+                    if (i < sc.cap) v = sc.bucket_e[row * sc.cap + i];
+                    else if (i < sc.cap + n_ovf && sc.overflow[2 * (i - sc.cap)] == (int32_t)row) v = sc.overflow[2 * (i - sc.cap) + 1];
+                    const unsigned m = __ballot_sync(0xffffffffu, v >= 0);
+                    const int at = n + __popc(m & ((1u << lane) - 1u));
+                    if (v >= 0 && at < cnt) seg[at] = v;
+                    n += __popc(m);
+                }
+                if (n > cnt) n = cnt;
+                __syncwarp();
+                // bitonic network in which every comparator moves the smaller key to the lower index:
+                // positions >= n behave like +infinity and never take part, so n need not be a power of two
+                for (int k = 2; (k >> 1) < n; k <<= 1) {
+                    for (int j = k >> 1; j > 0; j >>= 1) {
+                        for (int i = lane; i < n; i += 32) {
+                            const int p = (j == (k >> 1)) ? (i ^ (k - 1)) : (i ^ j);
+                            if (p > i && p < n) {
+                                const int32_t lo = seg[i], hi = seg[p];
+                                if (lo > hi) { seg[i] = hi; seg[p] = lo; }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+            } else {
+                // plain overwrite: only the last writer matters
+                int32_t best = -1;
+                for (int i = lane; i < sc.cap + n_ovf; i += 32) {
+                    int32_t v = -1;
+                    if (i < sc.cap) v = sc.bucket_e[row * sc.cap + i];
+                    else if (sc.overflow[2 * (i - sc.cap)] == (int32_t)row) v = sc.overflow[2 * (i - sc.cap) + 1];
+                    best = max(best, v);
+                }
+                for (int d = 16; d; d >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, d));
+                if (lane == 0) seg[0] = best;
+                n = best >= 0 ? 1 : 0;
+                __syncwarp();
+            }
             for (int c0 = 0; c0 < a.cols; c0 += 32 * V) {
                 const int col = c0 + lane * V;
                 const bool act = col < a.cols;
@@ -419,25 +473,9 @@ __global__ void __launch_bounds__(256, 4) ktb_scatter_apply_kernel(const __grid_
 #pragma unroll
                 for (int v = 0; v < V; ++v) cur[v] = 0.f;
                 if (rmw && act) sc_load_row<V>(a.arena, a.out, dst, col, a.cols, cur);
-                int32_t prev = -1;
-                for (int step = 0; step < cnt; ++step) {
-                    int32_t best = rmw ? 0x7fffffff : -1;
-                    for (int i = lane; i < sc.cap + n_ovf; i += 32) {
-                        int32_t v = -1;
-                        if (i < sc.cap) v = sc.bucket_e[row * sc.cap + i];
-                        else if (sc.overflow[2 * (i - sc.cap)] == (int32_t)row) v = sc.overflow[2 * (i - sc.cap) + 1];
-                        if (v < 0) continue;
-                        if (rmw) { if (v > prev && v < best) best = v; }
-                        else best = max(best, v);
-                    }
-                    for (int d = 16; d; d >>= 1) {
-                        const int32_t o = __shfl_xor_sync(0xffffffffu, best, d);
-                        best = rmw ? min(best, o) : max(best, o);
-                    }
-                    if (!rmw) step = cnt;              // only the last writer matters
-                    prev = best;
+                for (int step = 0; step < n; ++step) {
                     int64_t in_addr[KTB_ROWS_MAX_IN];
-                    sc_resolve(a, (uint32_t)best, st, in_addr);
+                    sc_resolve(a, (uint32_t)seg[step], st, in_addr);
                     bool ok = true;
                     float x[KTB_ROWS_MAX_IN][V];
 #pragma unroll
@@ -624,7 +662,7 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if (a.n_tiles == 0) return KTB_OK;
     const int64_t E = a.n_tiles * a.tile_rows, R = a.dst_rows;
     const sc_scratch sc = sc_carve(scratch, E, R);
-    KTB_CUDA(ctx, cudaMemsetAsync(sc.count, 0, (size_t)(R + 1) * sizeof(int32_t), ctx->stream));
+    KTB_CUDA(ctx, cudaMemsetAsync(sc.count, 0, (size_t)(R + 2) * sizeof(int32_t), ctx->stream));
     int64_t prep_blocks = a.n_tiles < (1 << 20) ? a.n_tiles : (1 << 20);
     const size_t smem = (size_t)a.tile_rows * sizeof(int64_t);
     if (smem > 48 * 1024) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "scatter_rows", "tile has too many rows");
