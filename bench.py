@@ -793,7 +793,8 @@ def run_gpu(args, w):
     cpu = not args.no_cpu
     if dist.world == 1:
         interp.load(w.source())
-        head = report(w, interp, w.inputs(0), args.steps, warm, dist, clocks_for=dist.local, cpu=cpu)
+        head = report(w, interp, w.inputs(0), args.steps, warm, dist, clocks_for=dist.local, cpu=cpu,
+                      sustained=not args.no_sustained)
         sharding = "single GPU"
         scaling = "weak"
     else:
@@ -889,6 +890,7 @@ def main():
     ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS) + ["candidates"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline samples")
     ap.add_argument("--no-extras", action="store_true", help="only the headline workload")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the eight-arena steady-state measurement")
     args = ap.parse_args()
     if args.workload == "candidates":
         return run_candidates(args)
