@@ -14,7 +14,6 @@ ktir_cpu/memory.py:330-352 allocates), so SSA pointer values — element indices
 """
 from __future__ import annotations
 
-import os
 
 from typing import Sequence, Any, Dict, List, Optional, Tuple
 
@@ -142,7 +141,7 @@ class Session:
             raise
         self._graph = None
         self._runs = 0
-        self.use_graph = arena_ptr is None and os.environ.get("KTB_NO_GRAPH") is None
+        self.use_graph = arena_ptr is None
         self.written = set(self.plan.written)
         self.no_upload = set(self.plan.fully_overwritten)
         self.last_h2d_bytes = 0
