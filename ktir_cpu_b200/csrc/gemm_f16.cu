@@ -11,6 +11,12 @@
 // tcgen05.mma (M=128, N=BN, K=16) into one of two TMEM accumulators; warps 2-5
 // drain the other accumulator (tcgen05.ld), convert and store C, so the epilogue
 // of tile i overlaps the main loop of tile i+1.  All waits are bounded.
+//
+// Tail: with T tiles on G SMs the last T mod G tiles would keep only some SMs busy for a whole
+// tile time (4096^3: 512 tiles on 148 SMs = 3 full rounds + 68 tiles: 4 tile times for 3.46 of
+// work).  When at most G / 2 tiles are left over, each is cut into its left and right half
+// (128 x BN/2) and the halves go to twice as many SMs: the tail takes about half a tile time, the
+// k order of every sum is unchanged (results do not depend on how the tiles were dealt out).
 #include "tc_common.cuh"
 
 #define GEMM_BM 128
@@ -26,10 +32,64 @@ struct GemmCfg {
     static constexpr size_t SMEM = (size_t)STAGES * (GEMM_A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
 };
 
+// 32 consecutive f32 accumulators of one row (+ the constant initial value) -> C.
+static __device__ __forceinline__ void gemm_store_chunk(const ktb_gemm_args& a, int row, int col, const uint32_t (&r)[32]) {
+    if (row >= a.M || col >= a.N) return;
+    if (a.c_dtype == KTB_F16) {
+        __half* dst = reinterpret_cast<__half*>(a.arena) + a.c_off + (int64_t)row * a.ldc + col;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            __half2* h = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]) + a.c_init,
+                                         __uint_as_float(r[v * 8 + 2 * i + 1]) + a.c_init);
+            *reinterpret_cast<uint4*>(dst + v * 8) = o;
+        }
+    } else {
+        float* dst = reinterpret_cast<float*>(a.arena) + a.c_off + (int64_t)row * a.ldc + col;
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+            *reinterpret_cast<float4*>(dst + v * 4) =
+                make_float4(__uint_as_float(r[v * 4]) + a.c_init, __uint_as_float(r[v * 4 + 1]) + a.c_init,
+                            __uint_as_float(r[v * 4 + 2]) + a.c_init, __uint_as_float(r[v * 4 + 3]) + a.c_init);
+    }
+}
+
+// The i-th piece of work of a CTA: rows [128 tm, +128), columns [n0, n0 + bn).
+struct GemmUnit {
+    int tm, n0, bn;
+};
+
+// `full_rounds` whole tiles per CTA (tile = cta + round * G), then the `tail_tiles` left-over tiles:
+// whole, one per CTA, or (halved) as two half-width units on CTAs 2 t and 2 t + 1.
+template <int BN>
+static __device__ __forceinline__ bool gemm_unit(int full_rounds, int tail_tiles, int halved, int tiles_n, int i,
+                                                 GemmUnit& u) {
+    const int cta = blockIdx.x, G = gridDim.x;
+    int tile, half = 0;
+    u.bn = BN;
+    if (i < full_rounds) {
+        tile = cta + i * G;
+    } else if (i == full_rounds && !halved && cta < tail_tiles) {
+        tile = full_rounds * G + cta;
+    } else if (i == full_rounds && halved && cta < 2 * tail_tiles) {
+        tile = full_rounds * G + (cta >> 1);
+        half = cta & 1;
+        u.bn = BN / 2;
+    } else {
+        return false;
+    }
+    u.tm = tile / tiles_n;
+    u.n0 = (tile - u.tm * tiles_n) * BN + half * (BN / 2);
+    return true;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const ktb_gemm_args a, int tiles_m, int tiles_n, ktb_status* st) {
+                    const ktb_gemm_args a, int tiles_n, int full_rounds, int tail_tiles, int halved, ktb_status* st) {
     using Cfg = GemmCfg<BN>;
     constexpr int S = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -45,7 +105,6 @@ ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tiles = tiles_m * tiles_n;
     const int KT = (a.K + GEMM_BK - 1) / GEMM_BK;
 
     if (threadIdx.x == 0) {
@@ -73,28 +132,30 @@ ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_prefetch_tmap(&map_b);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+            GemmUnit u;
+            for (int it = 0; ok && gemm_unit<BN>(full_rounds, tail_tiles, halved, tiles_n, it, u); ++it) {
+                const int nb = u.bn / 64;
                 for (int kt = 0; kt < KT; ++kt) {
                     if (!tc_mbar_wait(&empty[stage], phase ^ 1, abort_flag, st, 1)) { ok = false; break; }
-                    tc_mbar_expect_tx(&full[stage], GEMM_A_STAGE_BYTES + Cfg::B_STAGE_BYTES);
+                    tc_mbar_expect_tx(&full[stage], GEMM_A_STAGE_BYTES + GEMM_BK * u.bn * 2);
                     tc_tma_load_2d(sA + (size_t)stage * GEMM_A_STAGE_BYTES, &map_a, &full[stage], kt * GEMM_BK,
-                                   tm * GEMM_BM);
+                                   u.tm * GEMM_BM);
 #pragma unroll
                     for (int j = 0; j < BN / 64; ++j)
-                        tc_tma_load_2d(sB + (size_t)stage * Cfg::B_STAGE_BYTES + (size_t)j * (GEMM_BK * 128), &map_b,
-                                       &full[stage], tn * BN + j * 64, kt * GEMM_BK);
+                        if (j < nb)
+                            tc_tma_load_2d(sB + (size_t)stage * Cfg::B_STAGE_BYTES + (size_t)j * (GEMM_BK * 128), &map_b,
+                                           &full[stage], u.n0 + j * 64, kt * GEMM_BK);
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = tc_idesc_f16(GEMM_BM, BN, 0, 1);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            int it = 0;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++it) {
+            GemmUnit u;
+            for (int it = 0; ok && gemm_unit<BN>(full_rounds, tail_tiles, halved, tiles_n, it, u); ++it) {
+                const uint32_t idesc = tc_idesc_f16(GEMM_BM, u.bn, 0, 1);
                 const int acc = it & 1, accphase = (it >> 1) & 1;
                 if (!tc_mbar_wait(&tempty[acc], accphase ^ 1, abort_flag, st, 2)) break;
                 tc_fence_after_sync();
@@ -118,42 +179,19 @@ ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else {
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
-        int it = 0;
-        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+        GemmUnit u;
+        for (int it = 0; gemm_unit<BN>(full_rounds, tail_tiles, halved, tiles_n, it, u); ++it) {
             const int acc = it & 1, accphase = (it >> 1) & 1;
-            const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
             if (!tc_mbar_wait(&tfull[acc], accphase, abort_flag, st, 4)) break;
             tc_fence_after_sync();
-            const int row = tm * GEMM_BM + q * 32 + lane;
+            const int row = u.tm * GEMM_BM + q * 32 + lane;
             const uint32_t t0 = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < u.bn; c0 += 32) {
                 uint32_t r[32];
                 tc_tmem_ld32(t0 + c0, r);
                 tc_tmem_ld_wait();
-                const int col = tn * BN + c0;
-                if (row < a.M && col < a.N) {
-                    if (a.c_dtype == KTB_F16) {
-                        __half* dst = reinterpret_cast<__half*>(a.arena) + a.c_off + (int64_t)row * a.ldc + col;
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            __half2* h = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]) + a.c_init,
-                                                         __uint_as_float(r[v * 8 + 2 * i + 1]) + a.c_init);
-                            *reinterpret_cast<uint4*>(dst + v * 8) = o;
-                        }
-                    } else {
-                        float* dst = reinterpret_cast<float*>(a.arena) + a.c_off + (int64_t)row * a.ldc + col;
-#pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            *reinterpret_cast<float4*>(dst + v * 4) =
-                                make_float4(__uint_as_float(r[v * 4]) + a.c_init, __uint_as_float(r[v * 4 + 1]) + a.c_init,
-                                            __uint_as_float(r[v * 4 + 2]) + a.c_init, __uint_as_float(r[v * 4 + 3]) + a.c_init);
-                    }
-                }
+                gemm_store_chunk(a, row, u.n0 + c0, r);
             }
             tc_fence_before_sync();
             __syncwarp();
@@ -163,6 +201,161 @@ ktb_gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tc_tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---- the same GEMM on CTA pairs -------------------------------------------------------------------
+// Two CTAs of a cluster produce a 256 x 256 tile with one tcgen05.mma.cta_group::2 per K = 16: each
+// CTA stages its own 128 rows of A and HALF of the tile's B columns, so a k-step costs a CTA 32 KB of
+// shared-memory fill instead of 48 KB, seven stages fit instead of four, and the loads in flight
+// cover the L2 latency that bounded the single-CTA kernel.  Roles per CTA as above; only the
+// leader's warp 1 issues MMAs.  Barriers: full[] of the leader collects the bytes of both CTAs'
+// loads; empty[] and tfull[] exist in both CTAs and are signalled together by the leader's commit;
+// tempty[] of the leader collects the arrivals of both CTAs' epilogue warps.
+#define GEMM2_STAGES 7
+#define GEMM2_BN 256
+#define GEMM2_B_STAGE_BYTES (GEMM_BK * (GEMM2_BN / 2) * 2)
+#define GEMM2_SMEM ((size_t)GEMM2_STAGES * (GEMM_A_STAGE_BYTES + GEMM2_B_STAGE_BYTES) + 1024 + 256)
+
+// The i-th unit of a pair: rows [256 tm, +256), columns [n0, n0 + bn); same dealing as gemm_unit with
+// clusters in the place of CTAs.
+static __device__ __forceinline__ bool gemm_pair_unit(int full_rounds, int tail_tiles, int halved, int tiles_n, int i,
+                                                      GemmUnit& u) {
+    const int cl = blockIdx.x >> 1, G = gridDim.x >> 1;
+    int tile, half = 0;
+    u.bn = GEMM2_BN;
+    if (i < full_rounds) {
+        tile = cl + i * G;
+    } else if (i == full_rounds && !halved && cl < tail_tiles) {
+        tile = full_rounds * G + cl;
+    } else if (i == full_rounds && halved && cl < 2 * tail_tiles) {
+        tile = full_rounds * G + (cl >> 1);
+        half = cl & 1;
+        u.bn = GEMM2_BN / 2;
+    } else {
+        return false;
+    }
+    u.tm = tile / tiles_n;
+    u.n0 = (tile - u.tm * tiles_n) * GEMM2_BN + half * (GEMM2_BN / 2);
+    return true;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+ktb_gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const ktb_gemm_args a, int tiles_n, int full_rounds, int tail_tiles, int halved, ktb_status* st) {
+    constexpr int S = GEMM2_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + (size_t)S * GEMM_A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)S * GEMM2_B_STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + S;
+    uint64_t* tfull = bars + 2 * S;
+    uint64_t* tempty = bars + 2 * S + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KT = (a.K + GEMM_BK - 1) / GEMM_BK;
+    const uint32_t rank = tc_cluster_ctarank();
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < S; ++i) {
+            tc_mbar_init(&full[i], 1);
+            tc_mbar_init(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            tc_mbar_init(&tfull[i], 1);
+            tc_mbar_init(&tempty[i], 8);
+        }
+        *abort_flag = 0;
+        tc_fence_barrier_init();
+    }
+    __syncthreads();
+    if (warp == 1) tc_tmem_alloc_pair(tmem_slot, 2 * GEMM2_BN);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_cluster_sync();                     // both CTAs' barriers exist before either is signalled from outside
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tc_prefetch_tmap(&map_a);
+            tc_prefetch_tmap(&map_b);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            GemmUnit u;
+            for (int it = 0; ok && gemm_pair_unit(full_rounds, tail_tiles, halved, tiles_n, it, u); ++it) {
+                const int bcols = u.bn / 2;                       // B columns this CTA stages
+                for (int kt = 0; kt < KT; ++kt) {
+                    if (!tc_mbar_wait(&empty[stage], phase ^ 1, abort_flag, st, 11)) { ok = false; break; }
+                    if (rank == 0) tc_mbar_expect_tx(&full[stage], 2 * (GEMM_A_STAGE_BYTES + GEMM_BK * bcols * 2));
+                    const uint32_t bar = tc_mapa(tc_smem_u32(&full[stage]), 0);
+                    tc_tma_load_2d_pair(sA + (size_t)stage * GEMM_A_STAGE_BYTES, &map_a, bar, kt * GEMM_BK,
+                                        u.tm * 2 * GEMM_BM + (int)rank * GEMM_BM);
+#pragma unroll
+                    for (int j = 0; j < GEMM2_BN / 128; ++j)
+                        if (j * 64 < bcols)
+                            tc_tma_load_2d_pair(sB + (size_t)stage * GEMM2_B_STAGE_BYTES + (size_t)j * (GEMM_BK * 128), &map_b,
+                                                bar, u.n0 + (int)rank * bcols + j * 64, kt * GEMM_BK);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            GemmUnit u;
+            for (int it = 0; ok && gemm_pair_unit(full_rounds, tail_tiles, halved, tiles_n, it, u); ++it) {
+                const uint32_t idesc = tc_idesc_f16(2 * GEMM_BM, u.bn, 0, 1);
+                const int acc = it & 1, accphase = (it >> 1) & 1;
+                if (!tc_mbar_wait(&tempty[acc], accphase ^ 1, abort_flag, st, 12)) break;
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + acc * GEMM2_BN;
+                for (int kt = 0; kt < KT; ++kt) {
+                    if (!tc_mbar_wait(&full[stage], phase, abort_flag, st, 13)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = tc_smem_u32(sA + (size_t)stage * GEMM_A_STAGE_BYTES);
+                    const uint32_t b_addr = tc_smem_u32(sB + (size_t)stage * GEMM2_B_STAGE_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+                        const uint64_t ad = tc_smem_desc(a_addr + kk * 32, 16, 1024);
+                        const uint64_t bd = tc_smem_desc(b_addr + kk * 2048, GEMM_BK * 128, 1024);
+                        tc_mma_f16_pair(d, ad, bd, idesc, (kt | kk) != 0);
+                    }
+                    tc_mma_commit_pair(&empty[stage]);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_mma_commit_pair(&tfull[acc]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        GemmUnit u;
+        for (int it = 0; gemm_pair_unit(full_rounds, tail_tiles, halved, tiles_n, it, u); ++it) {
+            const int acc = it & 1, accphase = (it >> 1) & 1;
+            if (!tc_mbar_wait(&tfull[acc], accphase, abort_flag, st, 14)) break;
+            tc_fence_after_sync();
+            const int row = u.tm * 2 * GEMM_BM + (int)rank * GEMM_BM + q * 32 + lane;
+            const uint32_t t0 = tmem_base + acc * GEMM2_BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < u.bn; c0 += 32) {
+                uint32_t r[32];
+                tc_tmem_ld32(t0 + c0, r);
+                tc_tmem_ld_wait();
+                gemm_store_chunk(a, row, u.n0 + c0, r);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc_mbar_arrive_cluster(tc_mapa(tc_smem_u32(&tempty[acc]), 0));
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_cluster_sync();                     // the peer may still read this CTA's shared memory or signal its barriers
+    if (warp == 1) tc_tmem_dealloc_pair(tmem_base, 2 * GEMM2_BN);
 }
 
 template <int BN>
@@ -175,10 +368,31 @@ static int launch_gemm(ktb_ctx* ctx, const ktb_gemm_args& a, const CUtensorMap& 
         attr_set[ctx->device & (KTB_MAX_DEVICES - 1)] = true;
     }
     const int tiles_m = (a.M + GEMM_BM - 1) / GEMM_BM, tiles_n = (a.N + BN - 1) / BN;
-    int grid = tiles_m * tiles_n;
-    if (grid > ctx->sm_count) grid = ctx->sm_count;
-    ktb_gemm_f16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM, ctx->stream>>>(ma, mb, a, tiles_m, tiles_n, ctx->dev_status);
+    const int n_tiles = tiles_m * tiles_n, G = ctx->sm_count;
+    const int full_rounds = n_tiles / G, tail = n_tiles % G;
+    const int halved = tail > 0 && 2 * tail <= G;
+    const int grid = full_rounds ? G : (halved ? 2 * tail : tail);
+    ktb_gemm_f16_kernel<BN><<<grid, GEMM_THREADS, Cfg::SMEM, ctx->stream>>>(ma, mb, a, tiles_n, full_rounds, tail, halved,
+                                                                            ctx->dev_status);
     KTB_CHECK_LAUNCH(ctx, "ktb_gemm_f16_kernel");
+    return KTB_OK;
+}
+
+static int launch_gemm_pair(ktb_ctx* ctx, const ktb_gemm_args& a, const CUtensorMap& ma, const CUtensorMap& mb) {
+    static bool attr_set[KTB_MAX_DEVICES] = {};
+    if (!attr_set[ctx->device & (KTB_MAX_DEVICES - 1)]) {
+        KTB_CUDA(ctx, cudaFuncSetAttribute(ktb_gemm_f16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)GEMM2_SMEM));
+        attr_set[ctx->device & (KTB_MAX_DEVICES - 1)] = true;
+    }
+    const int tiles_m = (a.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM), tiles_n = (a.N + GEMM2_BN - 1) / GEMM2_BN;
+    const int n_tiles = tiles_m * tiles_n, G = ctx->sm_count / 2;
+    const int full_rounds = n_tiles / G, tail = n_tiles % G;
+    const int halved = tail > 0 && 2 * tail <= G;
+    const int clusters = full_rounds ? G : (halved ? 2 * tail : tail);
+    ktb_gemm_f16_pair_kernel<<<2 * clusters, GEMM_THREADS, GEMM2_SMEM, ctx->stream>>>(ma, mb, a, tiles_n, full_rounds, tail,
+                                                                                      halved, ctx->dev_status);
+    KTB_CHECK_LAUNCH(ctx, "ktb_gemm_f16_pair_kernel");
     return KTB_OK;
 }
 
@@ -203,6 +417,12 @@ extern "C" int ktb_launch_gemm_f16(ktb_ctx* ctx, const ktb_gemm_args* args) {
         const uint32_t box[2] = {64, GEMM_BK};
         if (!tc_make_map_f16(&mb, base + a.b_off, 2, dims, str, box)) return ktb_fail(ctx, KTB_E_CUDA, "gemm_f16", "cuTensorMapEncodeTiled(B) failed");
     }
-    if (a.N % 256 == 0 || a.N >= 1024) return launch_gemm<256>(ctx, a, ma, mb);
+    const int row_tiles = (a.M + GEMM_BM - 1) / GEMM_BM;
+    if (a.N % 256 == 0 || a.N >= 1024) {
+        // CTA pairs work on 256 rows: not for a single row tile, nor where an odd count would idle much of a pair
+        if (row_tiles >= 2 && (row_tiles % 2 == 0 || row_tiles >= 9) && ctx->sm_count >= 2)
+            return launch_gemm_pair(ctx, a, ma, mb);
+        return launch_gemm<256>(ctx, a, ma, mb);
+    }
     return launch_gemm<128>(ctx, a, ma, mb);
 }

@@ -180,6 +180,72 @@ static __device__ __forceinline__ void tc_mma_commit(uint64_t* bar) {
                  : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, ranks 0 (leader) and 1 ------------------------
+// One tcgen05.mma issued by the leader multiplies a 256-row A (128 rows from each CTA's shared memory)
+// with B whose columns are split between the two CTAs; each CTA accumulates its 128 rows in its own
+// TMEM.  TMA loads of either CTA report to a barrier of the leader; tcgen05.commit reports to the
+// barrier at the same shared-memory offset in both.  No load is multicast.
+static __device__ __forceinline__ uint32_t tc_cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Address, in the cluster's shared window, of the same variable in CTA `rank`.
+static __device__ __forceinline__ uint32_t tc_mapa(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+
+static __device__ __forceinline__ void tc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+static __device__ __forceinline__ void tc_mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+static __device__ __forceinline__ void tc_tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+static __device__ __forceinline__ void tc_tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// TMA tile load into this CTA's shared memory, completion bytes reported to `bar_cluster_addr`
+// (a barrier of the pair's leader).
+static __device__ __forceinline__ void tc_tma_load_2d_pair(void* smem_dst, const CUtensorMap* map,
+                                                           uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(tc_smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+static __device__ __forceinline__ void tc_mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The barrier at this shared-memory offset in both CTAs of the pair gets one arrival once every MMA
+// issued so far by this thread has completed.
+static __device__ __forceinline__ void tc_mma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(tc_smem_u32(bar)), "h"((uint16_t)3)
+        : "memory");
+}
+
 // 32 lanes x 32 consecutive columns of 32-bit values: thread i of the warp gets row (lane base + i).
 static __device__ __forceinline__ void tc_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(

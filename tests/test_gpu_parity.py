@@ -265,13 +265,21 @@ def test_gather_scale_scatter_full_size_properties(build_lib):
 
 
 @pytest.mark.parametrize("f32_acc", [True, False])
-@pytest.mark.parametrize("M,N,K,cores", [(256, 256, 256, 4), (128, 512, 192, 2), (384, 128, 64, 3)])
+@pytest.mark.parametrize("M,N,K,cores", [(256, 256, 256, 4), (128, 512, 192, 2), (384, 128, 64, 3),
+                                         # few tiles: the left-over tiles are cut into half-width units
+                                         (512, 1024, 1024, 8), (256, 384, 832, 6)])
 def test_tiled_matmul_matches_oracle(M, N, K, cores, f32_acc, build_lib):
     rng = np.random.default_rng(4)
     a = rng.uniform(-1, 1, (M, K)).astype(np.float16)
     b = rng.uniform(-1, 1, (K, N)).astype(np.float16)
-    got, want = _run_both(K_.tiled_matmul(M, N, K, 64, 64, 64, cores, f32_acc), "matmul_kernel",
-                          dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((M, N), np.float16)))
+    src = K_.tiled_matmul(M, N, K, 64, 64, 64, cores, f32_acc)
+    got, want = _run_both(src, "matmul_kernel", dict(a_ptr=a, b_ptr=b, c_ptr=np.zeros((M, N), np.float16)))
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    for _ in range(3):                     # every run gives the same bits
+        again = gpu.execute_function("matmul_kernel", a_ptr=a, b_ptr=b, c_ptr=np.zeros((M, N), np.float16))
+        np.testing.assert_array_equal(again["c_ptr"], got["c_ptr"])
+    gpu.close()
     tol = dict(rtol=2e-3, atol=1e-2) if f32_acc else dict(rtol=2e-2, atol=2e-1)
     np.testing.assert_allclose(got["c_ptr"].astype(np.float32), want["c_ptr"].astype(np.float32), **tol)
     exact = a.astype(np.float64) @ b.astype(np.float64)
