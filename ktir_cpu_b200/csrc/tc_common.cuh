@@ -91,6 +91,21 @@ static __device__ __forceinline__ void tc_tma_load_3d(void* smem_dst, const CUte
         : "memory");
 }
 
+// Tile store shared -> global (clipped at the tensor's edges), tracked by the issuing thread's bulk groups.
+static __device__ __forceinline__ void tc_tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(tc_smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+static __device__ __forceinline__ void tc_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// At most N of this thread's bulk groups may still be READING their shared-memory source.
+template <int N>
+static __device__ __forceinline__ void tc_bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// All of this thread's bulk groups have completed (their writes are done).
+static __device__ __forceinline__ void tc_bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 static __device__ __forceinline__ void tc_prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -371,9 +386,9 @@ static inline tc_encode_fn tc_get_encode() {
     return fn;
 }
 
-// f16 tensor of `rank` dims (dims[0] innermost), 128-byte swizzle, zero fill outside.
-static inline bool tc_make_map_f16(CUtensorMap* map, void* base, int rank, const uint64_t* dims,
-                                   const uint64_t* strides_bytes /* rank-1 */, const uint32_t* box) {
+// Tensor of `rank` dims (dims[0] innermost), 128-byte swizzle, zero fill outside.
+static inline bool tc_make_map(CUtensorMap* map, CUtensorMapDataType dtype, void* base, int rank, const uint64_t* dims,
+                               const uint64_t* strides_bytes /* rank-1 */, const uint32_t* box) {
     tc_encode_fn enc = tc_get_encode();
     if (!enc) return false;
     cuuint64_t gdim[5], gstr[4];
@@ -384,7 +399,12 @@ static inline bool tc_make_map_f16(CUtensorMap* map, void* base, int rank, const
         es[i] = 1;
     }
     for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, base, gdim, gstr, bx, es,
+    return enc(map, dtype, (cuuint32_t)rank, base, gdim, gstr, bx, es,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static inline bool tc_make_map_f16(CUtensorMap* map, void* base, int rank, const uint64_t* dims,
+                                   const uint64_t* strides_bytes /* rank-1 */, const uint32_t* box) {
+    return tc_make_map(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, base, rank, dims, strides_bytes, box);
 }
