@@ -201,7 +201,7 @@ class GatherScatter(Workload):
 
 
 class Matmul(Workload):
-    name, func, kernel = "matmul", "matmul_kernel", "ktb_gemm_f16_kernel"
+    name, func, kernel = "matmul", "matmul_kernel", "ktb_gemm_f16_pair_kernel"
     M = N = KK = 4096
     unit, bound = "FLOP/s", "tensor"
     units_per_step = 2 * M * N * KK
