@@ -271,15 +271,19 @@ int ktb_launch_scatter_rows_static(ktb_ctx* ctx, const ktb_rows_args* args);
  * KTB_G_RING is ktdp.inter_tile_reduce (ktir_cpu/dialects/ktdp_ops.py:1160-1240 with
  * RingReduceBackend, ktir_cpu/ops/comm_ops.py:229-345): per point the fold of its own partial with
  * its group's other partials in ring arrival order; a group of at most 8 cores runs as one
- * thread-block cluster that reads the partials out of its members' shared memory. */
+ * thread-block cluster that reads the partials out of its members' shared memory.
+ * KTB_G_TABLE fills dst from a [points][elems] host-computed table — the element addresses of a tile
+ * that several partitions of a distributed memory view back (MemoryOps.distributed_tile_access,
+ * ktir_cpu/ops/memory_ops.py:985-1098); KTB_G_GATHER / KTB_G_SCATTER then move the data. */
 enum { KTB_G_LOAD = 0, KTB_G_ADDR, KTB_G_IDXADD, KTB_G_GATHER, KTB_G_CONSTV, KTB_G_FILL, KTB_G_PARAM,
-       KTB_G_IOTA, KTB_G_MAP, KTB_G_EW, KTB_G_REDL, KTB_G_MATMUL, KTB_G_STORE, KTB_G_SCATTER, KTB_G_RING };
+       KTB_G_IOTA, KTB_G_MAP, KTB_G_EW, KTB_G_REDL, KTB_G_MATMUL, KTB_G_STORE, KTB_G_SCATTER, KTB_G_RING, KTB_G_TABLE };
 #define KTB_G_MAXDIM 6
 typedef struct {
     int32_t kind;                 /* KTB_G_* */
     int32_t op;                   /* KTB_G_EW / KTB_G_REDL: opcode (order of lower_generic.EW_OPS) */
     int32_t dt_dst, dt_a, dt_b, dt_c;   /* KTB_F16 .. KTB_I1 */
-    int32_t flags;                /* bit 0: compare as integers; bit 1 (RING): combiner takes (received, accumulator) */
+    int32_t flags;                /* bit 0: compare as integers; bit 1 (RING): combiner takes (received, accumulator);
+                                     bit 2 (SCATTER): the addresses are all different, elements may be written in any order */
     int32_t ndim;                 /* KTB_G_MAP / KTB_G_IOTA: rank of `shape` */
     int64_t points, elems;        /* extent of dst (of the stored tile for STORE / SCATTER) */
     int64_t ea, eb, ec;           /* elems of the sources; 1 = one value per point, broadcast */
@@ -290,7 +294,7 @@ typedef struct {
     void* arena;
     const int64_t* dev_base;      /* [points] element address of the tile origin (LOAD / ADDR / STORE); RING: sources per point */
     const int64_t* dev_rel;       /* [elems] element offset of each element from the origin; RING with a cluster: point of each CTA */
-    const void* dev_table;        /* CONSTV: [elems] values of dt_dst; PARAM: [points] values of dt_dst;
+    const void* dev_table;        /* CONSTV: [elems] values of dt_dst; PARAM: [points] values of dt_dst; TABLE: [points][elems];
                                      RING: int64 [points][n] sources in fold order (cluster ranks with h > 1, else points) */
     int64_t lo, hi;               /* allocation bounds in elements: reads outside give 0, writes are dropped */
     int64_t shape[KTB_G_MAXDIM];  /* MAP: dst shape; IOTA: tile shape */

@@ -232,6 +232,44 @@ class AffineSet:
             return None
         return tuple(lo), tuple(hi)
 
+    def box_with(self, syms: Sequence[int]) -> Optional[Tuple[Tuple[int, ...], Tuple[int, ...]]]:
+        """``box()`` with the set's symbols bound to ``syms`` (left to right); None when the set is
+        not a box.  Coefficients are read off numerically, which is exact for affine constraints."""
+        if not self.n_syms:
+            return self.box()
+        if len(syms) < self.n_syms:
+            raise ValueError(f"AffineSet needs {self.n_syms} symbol value(s), got {len(syms)}: {self.source!r}")
+        syms = [int(x) for x in syms[:self.n_syms]]
+        lo = [None] * self.n_dims
+        hi = [None] * self.n_dims
+        zero = [0] * self.n_dims
+        for e, kind in self.constraints:
+            c = eval_expr(e, zero, syms)
+            coeffs = []
+            for d in range(self.n_dims):
+                unit = list(zero)
+                unit[d] = 1
+                k = eval_expr(e, unit, syms) - c
+                unit[d] = 2
+                if eval_expr(e, unit, syms) - c != 2 * k:
+                    return None
+                coeffs.append(k)
+            nz = [i for i, x in enumerate(coeffs) if x]
+            if len(nz) != 1 or abs(coeffs[nz[0]]) != 1:
+                return None
+            d, sgn = nz[0], coeffs[nz[0]]
+            if kind == "eq":
+                v = -c * sgn
+                lo[d] = v if lo[d] is None else max(lo[d], v)
+                hi[d] = v + 1 if hi[d] is None else min(hi[d], v + 1)
+            elif sgn == 1:
+                lo[d] = -c if lo[d] is None else max(lo[d], -c)
+            else:
+                hi[d] = c + 1 if hi[d] is None else min(hi[d], c + 1)
+        if any(x is None for x in lo) or any(x is None for x in hi):
+            return None
+        return tuple(lo), tuple(hi)
+
     def enumerate(self, shape: Sequence[int], syms: Sequence[int] = ()) -> List[Tuple[int, ...]]:
         """Points of ``[0, shape)`` in the set, row-major (parser_ast.py:525-544)."""
         if len(shape) != self.n_dims:

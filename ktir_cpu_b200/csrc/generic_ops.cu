@@ -201,6 +201,8 @@ __global__ void g_fillers_kernel(const __grid_constant__ ktb_gen_op o, ktb_statu
             g_copy(o.dst, i, o.dev_table, e, size);
         } else if (o.kind == KTB_G_PARAM) {
             g_copy(o.dst, i, o.dev_table, p, size);
+        } else if (o.kind == KTB_G_TABLE) {
+            g_copy(o.dst, i, o.dev_table, i, size);
         } else if (o.kind == KTB_G_FILL) {
             if (g_is_float(o.dt_dst)) g_stf(o.dst, o.dt_dst, i, (float)o.fimm);
             else g_sti(o.dst, o.dt_dst, i, o.iimm);
@@ -338,6 +340,15 @@ __global__ void g_scatter_kernel(const __grid_constant__ ktb_gen_op o, ktb_statu
     }
 }
 
+// the same when the caller knows that no two elements share an address
+__global__ void g_scatter_any_order_kernel(const __grid_constant__ ktb_gen_op o, ktb_status* st) {
+    const int size = g_size(o.dt_a);
+    G_LOOP(i, o.points * o.elems) {
+        const int64_t addr = reinterpret_cast<const int64_t*>(o.b)[i];
+        if (addr >= o.lo && addr < o.hi) g_copy(o.arena, addr, o.a, o.ea == 1 ? i / o.elems : i, size);
+    }
+}
+
 // ---- cross-core ring reduce ---------------------------------------------------------------
 // dst[p] = fold of a[p] with the partials of the other cores of p's group, in the order the
 // reference's ring delivers them to that core (ktir_cpu/ops/comm_ops.py:294-345): core c folds in
@@ -426,13 +437,17 @@ extern "C" int ktb_launch_generic(ktb_ctx* ctx, const ktb_gen_op* op) {
         case KTB_G_CONSTV:
         case KTB_G_FILL:
         case KTB_G_PARAM:
+        case KTB_G_TABLE:
         case KTB_G_IOTA: G_RUN(g_fillers_kernel); break;
         case KTB_G_MAP: G_RUN(g_map_kernel); break;
         case KTB_G_EW: G_RUN(g_ew_kernel); break;
         case KTB_G_REDL: G_RUN(g_redl_kernel); break;
         case KTB_G_MATMUL: G_RUN(g_matmul_kernel); break;
         case KTB_G_STORE: G_RUN(g_store_kernel); break;
-        case KTB_G_SCATTER: g_scatter_kernel<<<1, 32, 0, ctx->stream>>>(o, ctx->dev_status); break;
+        case KTB_G_SCATTER:
+            if (o.flags & 4) G_RUN(g_scatter_any_order_kernel);
+            else g_scatter_kernel<<<1, 32, 0, ctx->stream>>>(o, ctx->dev_status);
+            break;
         case KTB_G_RING:
             if (int rc = launch_ring(ctx, o)) return rc;
             break;

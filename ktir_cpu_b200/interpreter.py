@@ -114,6 +114,7 @@ class Session:
         try:
             from .lx import LXModel, use_counts
             tracer = Tracer(func, scalars, ptrs)
+            tracer.arena = self.arena_map
             tracer.lx = LXModel(tracer.ncores, 0, lx_bytes, use_counts(func.ops))
             if latency:
                 from .trace_latency import LatencyRecorder
@@ -132,7 +133,9 @@ class Session:
                     # a core of another rank may read or overlap what a core of this rank writes: the
                     # whole grid must pass the sequential-order check, not just this rank's slice
                     lower(R.PlanOnlyDevice(), stores, self.arena_map, fused=fused)
-                    stores = Tracer(func, scalars, ptrs, core_range=core_slice(tracer.ncores, *shard)).run()
+                    part = Tracer(func, scalars, ptrs, core_range=core_slice(tracer.ncores, *shard))
+                    part.arena = self.arena_map
+                    stores = part.run()
             self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard, fused=fused)
         except Exception:
             if self.own_arena:

@@ -691,6 +691,117 @@ def shared_slot_store(n_cores: int = 4, slots: int = 2, cols: int = 64, dtype: s
               f"    ktdp.store %twice, %out_tile : {t}, {at}\n    return\n  }}\n}}\n")
 
 
+def _box_at(lo: Sequence[int], hi: Sequence[int]) -> str:
+    """affine_set of the box [lo, hi) (hi exclusive)."""
+    dims = ", ".join(f"d{i}" for i in range(len(lo)))
+    cons = ", ".join(f"d{i} - {l} >= 0, -d{i} + {h - 1} >= 0" for i, (l, h) in enumerate(zip(lo, hi)))
+    return f"affine_set<({dims}) : ({cons})>"
+
+
+def _part(name: str, ptr: str, lo, hi, strides, dtype: str) -> str:
+    shape = [h - l for l, h in zip(lo, hi)]
+    return (f"    %{name} = ktdp.construct_memory_view %{ptr}, sizes: {shape}, strides: {list(strides)} {{\n"
+            f"      coordinate_set = {_box_at(lo, hi)}, memory_space = #ktdp.memory_space<global>\n"
+            f"    }} : memref<{_xs(shape, dtype)}>\n")
+
+
+def _dist(name: str, parts, shapes, shape, dtype: str) -> str:
+    names = ", ".join(f"%{p_}" for p_ in parts)
+    types = ", ".join(f"memref<{_xs(s_, dtype)}>" for s_ in shapes)
+    return (f"    %{name} = ktdp.construct_distributed_memory_view\n"
+            f"        ({names} : {types})\n        : memref<{_xs(shape, dtype)}>\n")
+
+
+def sharded_scale(rows: int = 64, cols: int = 64, tile_rows: int = 8, cores: int = 4, shift: int = 0,
+                  dtype: str = "f16") -> str:
+    """out = a + a on a [rows, cols] tensor that lives in three pieces — rows [0, rows/2) row-major in
+    ``a0``, rows [rows/2, rows) x cols [0, cols/2) COLUMN-major in ``a1``, the remaining quarter
+    row-major in ``a2`` — read through one distributed memory view, and written through another one
+    that splits the columns between ``o0`` and ``o1``.  Core c handles ``rows / cores / tile_rows``
+    tiles of ``tile_rows`` full rows starting at row ``c * rows / cores + shift``: with a shift that is
+    not a multiple of the tile height a tile crosses the row boundary between the partitions, every
+    tile crosses the column boundaries, and the last tile hangs over the end of the tensor (what no
+    partition backs reads as zero and is not written)."""
+    h, w = rows // 2, cols // 2
+    per_core = rows // cores
+    n_iter = per_core // tile_rows
+    assert h * 2 == rows and w * 2 == cols and n_iter * tile_rows * cores == rows and 0 <= shift < tile_rows
+    t, at = f"tensor<{_xs([tile_rows, cols], dtype)}>", f"!ktdp.access_tile<{_xs([tile_rows, cols], 'index')}>"
+    s = (f"module {{\n  func.func @sharded_scale(%a0_ptr: index, %a1_ptr: index, %a2_ptr: index, %o0_ptr: index, "
+         f"%o1_ptr: index) attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n    %c1 = arith.constant 1 : index\n"
+         f"    %n_iter = arith.constant {n_iter} : index\n    %th = arith.constant {tile_rows} : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n    %shift = arith.constant {shift} : index\n"
+         f"    %row_lo = arith.muli %core, %per_core : index\n    %row0 = arith.addi %row_lo, %shift : index\n")
+    s += _part("a0", "a0_ptr", [0, 0], [h, cols], [cols, 1], dtype)
+    s += _part("a1", "a1_ptr", [h, 0], [rows, w], [1, h], dtype)
+    s += _part("a2", "a2_ptr", [h, w], [rows, cols], [w, 1], dtype)
+    s += _dist("a_all", ["a0", "a1", "a2"], [[h, cols], [h, w], [h, w]], [rows, cols], dtype)
+    s += _part("o0", "o0_ptr", [0, 0], [rows, w], [w, 1], dtype)
+    s += _part("o1", "o1_ptr", [0, w], [rows, cols], [w, 1], dtype)
+    s += _dist("o_all", ["o0", "o1"], [[rows, w], [rows, w]], [rows, cols], dtype)
+    s += (f"    scf.for %i = %c0 to %n_iter step %c1 {{\n"
+          f"      %step = arith.muli %i, %th : index\n      %r = arith.addi %row0, %step : index\n"
+          + tile("a_tile", "a_all", ["%r", "%c0"], [tile_rows, cols], [rows, cols], dtype, "      ")
+          + f"      %x = ktdp.load %a_tile : {at} -> {t}\n      %y = arith.addf %x, %x : {t}\n"
+          + tile("o_tile", "o_all", ["%r", "%c0"], [tile_rows, cols], [rows, cols], dtype, "      ")
+          + f"      ktdp.store %y, %o_tile : {t}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
+def sharded_center(cols: int = 256, cores: int = 4, rows: int = 8, dtype: str = "f16") -> str:
+    """Tensor-parallel row centering: y = x - sum_over_all_columns(x) / cols.  x and y are [rows, cols];
+    core c owns the column block c of both, declared as partition c of a distributed memory view
+    (all partitions inside the one tensor).  Per row: local sum over the core's columns, all-reduce of
+    the [1, 1] partial sums over the cores (ring), subtract.  Every access tile lies whole inside one
+    partition, so the loads and stores are ordinary strided tiles on the device; the shape of
+    examples/latency/rmsnorm_4core_2x2.mlir of the reference."""
+    w = cols // cores
+    assert w * cores == cols
+    t, at = f"tensor<1x{w}x{dtype}>", f"!ktdp.access_tile<1x{w}xindex>"
+    tv = f"tensor<1x1x{dtype}>"
+    groups = "affine_set<(g) : (g >= 0, -g >= 0)>"
+    s = (f"#all_cores = affine_set<(i)[g] : (i >= 0, -i + {cores - 1} >= 0)>\n\n"
+         f"module {{\n  func.func @sharded_center(%x_ptr: index, %y_ptr: index) attributes {{grid = [{cores}]}} {{\n"
+         f"    %core = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n    %rows = arith.constant {rows} : index\n"
+         f"    %w = arith.constant {w} : index\n    %col0 = arith.muli %core, %w : index\n"
+         f"    %zero = arith.constant 0.0 : {dtype}\n    %inv_n = arith.constant {1.0 / cols} : {dtype}\n")
+    for nm, ptr in (("x", "x_ptr"), ("y", "y_ptr")):
+        names = []
+        for c in range(cores):
+            s += (f"    %{nm}_off{c} = arith.constant {c * w} : index\n"
+                  f"    %{nm}_base{c} = arith.addi %{ptr}, %{nm}_off{c} : index\n")
+            s += _part(f"{nm}_p{c}", f"{nm}_base{c}", [0, c * w], [rows, (c + 1) * w], [cols, 1], dtype)
+            names.append(f"{nm}_p{c}")
+        s += _dist(f"{nm}_all", names, [[rows, w]] * cores, [rows, cols], dtype)
+    ind = "      "
+    s += f"    scf.for %row = %c0 to %rows step %c1 {{\n"
+    s += tile("x_tile", "x_all", ["%row", "%col0"], [1, w], [rows, cols], dtype, ind)
+    s += (f"{ind}%x = ktdp.load %x_tile : {at} -> {t}\n"
+          f"{ind}%acc0 = tensor.splat %zero : tensor<1x{dtype}>\n"
+          f"{ind}%sum = linalg.reduce {{ arith.addf }} ins(%x : {t}) outs(%acc0 : tensor<1x{dtype}>) dimensions = [1]\n"
+          f"{ind}%partial = tensor.expand_shape %sum [[0, 1]] output_shape [1, 1] : tensor<1x{dtype}> into {tv}\n"
+          f"{ind}%fut = ktdp.inter_tile_produce\n{ind}    producer_tiles_per_group = #all_cores\n"
+          f"{ind}    : {tv} -> !ktdp.tile_future<{tv}, groups = {groups}>\n{ind}{{\n"
+          f"{ind}  ^bb0(%gid: index):\n{ind}    ktdp.yield_partial %partial : {tv}\n{ind}}}\n"
+          f"{ind}%ident = tensor.splat %zero : {tv}\n"
+          f"{ind}%total = ktdp.inter_tile_reduce(%fut)\n{ind}    consumer_tiles_per_group = #all_cores,\n"
+          f"{ind}    identity(%ident : {tv}) : !ktdp.tile_future<{tv}, groups = {groups}> -> {tv}\n{ind}{{\n"
+          f"{ind}  ^bb0(%lhs: {tv}, %rhs: {tv}):\n{ind}    %comb = arith.addf %lhs, %rhs : {tv}\n"
+          f"{ind}    ktdp.yield_reduced %comb : {tv}\n{ind}}}\n"
+          f"{ind}%inv_n_t = tensor.splat %inv_n : {tv}\n"
+          f"{ind}%mean = arith.mulf %total, %inv_n_t : {tv}\n"
+          f"{ind}%bshape = tensor.empty() : {t}\n"
+          f"{ind}%mean_row = tensor.collapse_shape %mean [[0, 1]] : {tv} into tensor<1x{dtype}>\n"
+          f"{ind}%mean_b = linalg.broadcast ins(%mean_row : tensor<1x{dtype}>) outs(%bshape : {t}) dimensions = [1]\n"
+          f"{ind}%y = arith.subf %x, %mean_b : {t}\n")
+    s += tile("y_tile", "y_all", ["%row", "%col0"], [1, w], [rows, cols], dtype, ind)
+    s += f"{ind}ktdp.store %y, %y_tile : {t}, {at}\n{ind}scf.yield\n    }}\n    return\n  }}\n}}\n"
+    return s
+
+
 def layernorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, eps: float = 1e-5) -> str:
     """y = (x - mean) / sqrt(var + eps) * w + b per row, f32 statistics, one row per iteration.
 

@@ -24,7 +24,7 @@ from typing import Any, Dict, List, Optional, Tuple
 import numpy as np
 
 from .dtypes import bytes_per_elem, to_np_dtype
-from .trace import Access, IndirectAccess, LoopInfo, Node, Store, Unsupported, iv_full
+from .trace import Access, IndirectAccess, LoopInfo, Node, Store, TableAccess, Unsupported, iv_full
 
 NP_DT = {"f16": np.float16, "f32": np.float32, "i32": np.int32, "i64": np.int64, "i1": np.uint8, "index": np.int64}
 ITEM = {"f16": 2, "f32": 4, "i32": 4, "i64": 8, "i1": 1, "index": 8}
@@ -167,6 +167,7 @@ class GenBuilder:
         self.loop_runs: Dict[Any, List[Buf]] = {}
         self.depth_memo: Dict[int, int] = {}
         self.loads: List[Tuple[Access, Tuple[int, ...]]] = []       # direct loads, for the hazard check
+        self.tables: List[Tuple[np.ndarray, str, bool]] = []        # (addresses [points, elems], dtype, written)
         self.indirect_reads: List[Any] = []                          # allocations read through address buffers
         self.loop_state: Dict[Any, List[Buf]] = {}
 
@@ -179,11 +180,22 @@ class GenBuilder:
             out = out[:, k]
         return np.ascontiguousarray(out).astype(np.int64)
 
+    def table_at_points(self, addr: np.ndarray, ks: Tuple[int, ...], trips: Tuple[int, ...]) -> np.ndarray:
+        """Rows of an address table (iteration space + element axis) for the selected points."""
+        axes = tuple(self.store.axes) + trips
+        lead, E = addr.shape[:-1], addr.shape[-1]
+        v = addr.reshape(lead + (1,) * (len(axes) - len(lead)) + (E,))
+        full = np.broadcast_to(v, axes + (E,)).reshape((-1,) + trips + (E,))
+        out = full[self.sel]
+        for k in ks:
+            out = out[:, k]
+        return np.ascontiguousarray(out, np.int64)
+
     def depth(self, n: Node) -> int:
         d = self.depth_memo.get(id(n))
         if d is not None:
             return d
-        if n.kind in ("load", "iload"):
+        if n.kind in ("load", "iload", "tload"):
             d = max(0, len(n.attrs["axes"]) - self.A)
         elif n.kind == "param":
             v = n.attrs["values"]
@@ -249,6 +261,12 @@ class GenBuilder:
             bpe = bytes_per_elem(dt)
             self.loads.append((acc, ks, trips))
             return P.emit("load", P.new(dt, n.shape), (), base=base, rel=rel, lo=al.byte_lo // bpe, hi=al.byte_hi // bpe)
+        if k == "tload":
+            ta: TableAccess = n.attrs["access"]
+            table = self.table_at_points(ta.addr, ks, trips)
+            self.tables.append((table, ta.dtype, False))
+            addr = P.emit("table", P.new("i64", (table.shape[1],)), (), values=table)
+            return P.emit("gather", P.new(ta.dtype, n.shape), (addr,), lo=0, hi=ALL_MEMORY)
         if k == "iload":
             addr, al, dt = self.indirect_addresses(n.attrs["access"], ks, trips)
             bpe = bytes_per_elem(dt)
@@ -501,6 +519,39 @@ class GenBuilder:
         return addr, al, dt
 
 
+ALL_MEMORY = 1 << 60      # upper bound of a gather / scatter whose addresses the host has already checked
+
+
+def table_footprints(table: np.ndarray, dtype: str, write: bool, sel, cores, arena, stmt_id: int):
+    """Byte runs of a resolved access (one address per point and element, -1 = none), one Footprint
+    per allocation touched."""
+    from .lower import Footprint
+    bpe = bytes_per_elem(dtype)
+    P_, E = table.shape
+    flat = table.reshape(-1)
+    valid = flat >= 0
+    if not valid.any():
+        return []
+    idx = np.flatnonzero(valid)
+    a = flat[idx]
+    # a run continues while the address grows by one inside the same row
+    brk = np.ones(len(idx), bool)
+    brk[1:] = (np.diff(a) != 1) | (np.diff(idx) != 1) | (idx[1:] // E != idx[:-1] // E)
+    first = np.flatnonzero(brk)
+    length = np.diff(np.append(first, len(idx)))
+    starts = a[first] * bpe
+    ends = starts + length * bpe
+    rows = idx[first] // E
+    pts = sel[rows] if len(sel) == P_ else np.full(len(rows), -1)
+    crs = cores[rows] if len(cores) == P_ else np.full(len(rows), -1)
+    out = []
+    for al in arena.allocs:
+        m = (starts >= al.byte_lo) & (starts < al.byte_hi)
+        if m.any():
+            out.append(Footprint(starts[m], ends[m], pts[m], crs[m], write, stmt_id))
+    return out
+
+
 def _runs(rel: np.ndarray):
     """Split sorted-as-given element offsets into maximal unit-stride runs: (starts, lengths)."""
     if rel.size == 0:
@@ -561,8 +612,29 @@ def build_generic(store: Store, arena, sel: np.ndarray):
             keep[store_sel] = True
             base = np.where(keep, base, -(1 << 50))
         P.emit("store", None, (val,), base=base, rel=rel, lo=al.byte_lo // bpe, hi=al.byte_hi // bpe, dtype=dt)
-        direct.append((live, rel, dt, True))
+        direct.append((live, rel, dt, True, al))
         written.append(al.name)
+    elif isinstance(tgt, TableAccess):
+        dt = tgt.dtype
+        table = gb.table_at_points(tgt.addr, (), ())
+        if len(store_sel) != len(sel):
+            keep = np.zeros(len(sel), bool)
+            keep[store_sel] = True
+            table = np.where(keep[:, None], table, -1)
+        E = table.shape[1]
+        if val.dtype != dt:
+            val = P.emit("ew", P.new(dt, val.shape), (val,), op="mov")
+        if val.elems != E:
+            if val.elems != 1:
+                raise ValueError(f"ktdp.store: tile of {val.elems} elements into an access tile of {E}")
+            val = P.emit("map", P.new(dt, (E,)), (val,), shape=(E,), strides=[0], offset=0)
+        live = table[table >= 0]
+        addr = P.emit("table", P.new("i64", (E,)), (), values=table)
+        P.emit("scatter", None, (val, addr), lo=0, hi=ALL_MEMORY, dtype=dt,
+               any_order=bool(len(np.unique(live)) == len(live)))
+        gb.tables.append((table, dt, True))
+        bpe = bytes_per_elem(dt)
+        written.extend(a_.name for a_ in arena.allocs if ((live * bpe >= a_.byte_lo) & (live * bpe < a_.byte_hi)).any())
     else:
         addr, al, dt = gb.indirect_addresses(tgt, (), ())
         gb.indirect_reads.pop()                       # the parent allocation is written, not read
@@ -577,9 +649,11 @@ def build_generic(store: Store, arena, sel: np.ndarray):
         P.emit("scatter", None, (val, addr), lo=al.byte_lo // bpe, hi=al.byte_hi // bpe, dtype=dt)
         written.append(al.name)
     for acc, ks, trips in gb.loads:
-        direct.append((gb.at_points(acc.off, ks, trips), access_rel_offsets(acc), acc.view.dtype, False))
+        lbase = gb.at_points(acc.off, ks, trips)
+        direct.append((lbase, access_rel_offsets(acc), acc.view.dtype, False,
+                       gb.alloc_of(lbase.min() if lbase.size else 0, acc.view.dtype, "Read from")))
     P.place()
-    ind_write = None if isinstance(tgt, Access) else al
+    ind_write = None if isinstance(tgt, (Access, TableAccess)) else al
     if ind_write is not None and len(sel) > 1:
         # all points are read before any is written: a read-modify-write of the scattered tensor
         # across iteration points would lose the sequential order (the fused row scatter keeps it)
@@ -589,7 +663,7 @@ def build_generic(store: Store, arena, sel: np.ndarray):
         if ind_write.name in reads:
             raise Unsupported("indirect store into a tensor the same statement reads, in a form the "
                               "ordered row scatter does not cover")
-    return P, written, direct, gb.indirect_reads, ind_write
+    return P, written, direct, gb.indirect_reads, ind_write, gb.tables
 
 
 # ---------------------------------------------------------------------------
@@ -607,7 +681,7 @@ def _make_statement_class():
 
         def __init__(self, dev, store: Store, arena, stmt_id: int):
             sel, cores = _points(store)
-            self.prog, written, direct, ind_reads, ind_write = build_generic(store, arena, sel)
+            self.prog, written, direct, ind_reads, ind_write, tables = build_generic(store, arena, sel)
             self.extra_written = list(written) if ind_write is not None else []
             self._dev = dev
             self._store_points = sel if self.prog.P == len(sel) else np.arange(self.prog.P)
@@ -642,6 +716,10 @@ def _make_statement_class():
                     g.dev_table = self._up(dev, np.ascontiguousarray(a["table"]))
                 elif op.kind == "param":
                     g.dev_table = self._up(dev, np.ascontiguousarray(a["values"]))
+                elif op.kind == "table":
+                    g.dev_table = self._up(dev, np.ascontiguousarray(a["values"], np.int64))
+                elif op.kind == "scatter" and a.get("any_order"):
+                    g.flags = 4
                 elif op.kind == "fill":
                     v = a["value"]
                     g.fimm = float(v) if d.dtype in ("f16", "f32") else 0.0
@@ -681,7 +759,7 @@ def _make_statement_class():
             # footprints for the sequential-order check
             self.fps: List[Footprint] = []
             neg = np.array([-1])
-            for base, rel, dt, write in direct:
+            for base, rel, dt, write, al in direct:
                 bpe = bytes_per_elem(dt)
                 rs, rl = _runs(rel)
                 starts = (base[:, None] + rs[None, :]).reshape(-1) * bpe
@@ -690,7 +768,14 @@ def _make_statement_class():
                     pts, crs = np.repeat(sel, len(rs)), np.repeat(cores, len(rs))
                 else:
                     pts, crs = np.repeat(neg, len(starts)), np.repeat(neg, len(starts))
+                # what lies outside the allocation is read as zero / not written: it touches no memory
+                starts, ends = np.maximum(starts, al.byte_lo), np.minimum(ends, al.byte_hi)
+                real = ends > starts
+                if not real.all():
+                    starts, ends, pts, crs = starts[real], ends[real], pts[real], crs[real]
                 self.fps.append(Footprint(starts, ends, pts, crs, write, stmt_id))
+            for table, dt, write in tables:
+                self.fps.extend(table_footprints(table, dt, write, sel, cores, arena, stmt_id))
             for al in ind_reads:
                 self.fps.append(Footprint(np.array([al.byte_lo]), np.array([al.byte_hi]), neg, neg, False, stmt_id))
             if ind_write is not None:

@@ -172,6 +172,23 @@ def parse_memory_view(p, name, results) -> Op:
     return Op(name, results, operands, attrs, [ty])
 
 
+def parse_distributed_view(p, name, results) -> Op:
+    """``ktdp.construct_distributed_memory_view (%p0, %p1 : memref<..>, memref<..>) : memref<..>``"""
+    p.eat("(")
+    parts = []
+    while p.peek().kind == "ssa":
+        parts.append(p.eat_kind("ssa").text)
+        p.accept(",")
+    p.eat(":")
+    while p.peek().kind == "type":
+        p.i += 1
+        p.accept(",")
+    p.eat(")")
+    p.eat(":")
+    ty = P.parse_type(p.eat_kind("type").text)
+    return Op(name, results, parts, {"shape": tuple(ty.shape), "dtype": ty.dtype}, [ty])
+
+
 def parse_access_tile(p, name, results) -> Op:
     view = p.eat_kind("ssa").text
     idx = p.int_or_ssa_list()
@@ -567,6 +584,7 @@ HANDLERS = {
     "ktdp.yield_reduced": parse_terminator,
     "arith.constant": parse_constant,
     "ktdp.construct_memory_view": parse_memory_view,
+    "ktdp.construct_distributed_memory_view": parse_distributed_view,
     "ktdp.construct_access_tile": parse_access_tile,
     "ktdp.construct_indirect_access_tile": parse_indirect_access_tile,
     "linalg.reduce": parse_linalg_named,

@@ -94,6 +94,31 @@ class View:
     strides: Tuple[int, ...]
     dtype: str
     space: str = "global"
+    box: Optional[Tuple[Tuple[int, ...], Tuple[int, ...]]] = None   # coordinate_set as (lo, hi) in global coordinates
+    points: Optional[np.ndarray] = None                             # ... or, when it is not a box, its points [n, ndim]
+    cset: Optional[AffineSet] = None
+    syms: Tuple[int, ...] = ()
+
+
+@dataclass
+class DistView:
+    """``ktdp.construct_distributed_memory_view``: partitions that each cover part of one global
+    coordinate space (ktir_cpu/ir_types.py:266-378)."""
+    parts: List[View]
+    shape: Tuple[int, ...]
+    dtype: str
+
+
+@dataclass
+class TableAccess:
+    """An access tile resolved element by element: ``addr`` holds, for every point of the iteration
+    space (leading axes) and every element of the tile (last axis, row-major), the element address
+    it lives at, or -1 where no memory backs it (reads give 0, writes are dropped)."""
+    dtype: str
+    shape: Tuple[int, ...]
+    addr: np.ndarray
+    multi: bool = False            # some element is backed by more than one partition
+    part: Optional[np.ndarray] = None   # which partition backs each entry of ``addr`` (for the stick counts)
 
 
 @dataclass
@@ -159,6 +184,7 @@ class Tracer:
         self._loop_counter = 0
         self.latency = None            # a trace_latency.LatencyRecorder when the latency model is on
         self.lx = None                 # an lx.LXModel when scratchpad accounting is on
+        self.arena = None              # a lower.ArenaMap: accesses are clipped to the allocation they start in
         self.scope: Dict[str, Any] = {}
         for n, _ in func.args:
             key = n[1:]

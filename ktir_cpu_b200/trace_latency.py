@@ -24,7 +24,7 @@ import numpy as np
 
 from .dtypes import bytes_per_elem
 from .latency import STICK_BYTES, LatencyCategory as LC, OpRecord, get_latency_category
-from .trace import Access, IndirectAccess, Node, iv_full
+from .trace import Access, IndirectAccess, Node, TableAccess, iv_full
 
 
 def _is_node(v) -> bool:
@@ -162,6 +162,10 @@ class LatencyRecorder:
             sticks = direct_sticks(acc, axes)
             per_core = np.where(active, sticks, 0).reshape(self.ncores, -1).sum(1) * STICK_BYTES
             self.records.append(OpRecord(op.name, LC.MEMORY, cnt, "bytes", nbytes=per_core.astype(np.int64)))
+        elif isinstance(acc, TableAccess):
+            sticks = table_sticks(acc, axes)
+            per_core = np.where(active, sticks, 0).reshape(self.ncores, -1).sum(1) * STICK_BYTES
+            self.records.append(OpRecord(op.name, LC.MEMORY, cnt, "bytes", nbytes=per_core.astype(np.int64)))
         elif isinstance(acc, IndirectAccess):
             sel = np.nonzero(active.reshape(-1))[0]
             per_point = int(np.prod(axes[1:], dtype=np.int64))
@@ -203,6 +207,21 @@ def direct_sticks(acc: Access, axes) -> np.ndarray:
         n = int(np.unique((int(r) + rel) // STICK_BYTES).size)
         out[res == r] = n
     return out
+
+
+def table_sticks(acc: TableAccess, axes) -> np.ndarray:
+    """Sticks per iteration point of a tile resolved through a distributed view: the distinct sticks
+    of each partition's share, summed over the partitions (MemoryOps.distributed_load adds up the
+    counts of its per-partition loads, ktir_cpu/ops/memory_ops.py:1127-1195)."""
+    E = acc.addr.shape[-1]
+    addr = np.broadcast_to(acc.addr.reshape(acc.addr.shape[:-1] + (1,) * (len(axes) - acc.addr.ndim + 1) + (E,)),
+                           tuple(axes) + (E,)).reshape(-1, E)
+    part = np.broadcast_to(acc.part.reshape(acc.part.shape[:-1] + (1,) * (len(axes) - acc.part.ndim + 1) + (E,)),
+                           tuple(axes) + (E,)).reshape(-1, E).astype(np.int64)
+    valid = addr >= 0
+    key = np.where(valid, (part << 44) + addr * bytes_per_elem(acc.dtype) // STICK_BYTES, -1)
+    n = _unique_per_row(key) - (~valid).any(1)
+    return n.reshape(axes).astype(np.int64)
 
 
 def _union_count(first: np.ndarray, last: np.ndarray) -> np.ndarray:

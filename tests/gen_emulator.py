@@ -69,6 +69,8 @@ def run(prog, arena: np.ndarray):
                 out = np.full((P, 1), a["value"]).astype(NP_DT[d.dtype])
             elif k == "param":
                 out = a["values"].reshape(P, 1).astype(NP_DT[d.dtype])
+            elif k == "table":
+                out = np.asarray(a["values"]).reshape(P, d.elems).astype(NP_DT[d.dtype])
             elif k == "iota":
                 shape = a["shape"]
                 idx = np.indices(shape)[a["dim"]].reshape(-1)
@@ -129,6 +131,11 @@ def run(prog, arena: np.ndarray):
                 addr = src[1]
                 mem = view(a["dtype"])
                 v = np.broadcast_to(src[0], addr.shape)
+                if a.get("any_order"):                  # the lowering promises distinct addresses
+                    ok = (addr >= a["lo"]) & (addr < a["hi"])
+                    assert len(np.unique(addr[ok])) == int(ok.sum())
+                    mem[addr[ok]] = v[ok]
+                    continue
                 for p in range(P):                      # points in order, elements in order
                     for e in range(addr.shape[1]):
                         t = addr[p, e]

@@ -138,6 +138,24 @@ def cases(ref_root=None):
     x = rng.standard_normal((12, 64)).astype(np.float16)
     out["shared_slot_store_12x5"] = (K.shared_slot_store(12, 5, 64), "shared_slot",
                                      dict(x_ptr=x, out_ptr=np.zeros((5, 64), np.float16)))
+    # tensors shorter than the kernel's views: what a tile reads past the end of its allocation is zero,
+    # what it would write there is dropped (the arrays of 4000 elements end inside the last 128-wide block)
+    short = np.random.default_rng(11)
+    x, y = short.standard_normal(4000).astype(np.float16), short.standard_normal(4000).astype(np.float16)
+    out["vector_add_short_4000"] = (K.vector_add(4096, 128, 32), "add_kernel",
+                                    dict(x_ptr=x, y_ptr=y, output_ptr=np.zeros(4000, np.float16), BLOCK_SIZE=128))
+    # one tensor in three differently laid-out pieces behind a distributed memory view; tiles that cross the
+    # partition boundaries and hang over the end
+    dist = np.random.default_rng(12)
+    for shift in (0, 3):
+        a = dist.standard_normal((64, 64)).astype(np.float16)
+        out[f"sharded_scale_64x64_shift{shift}"] = (
+            K.sharded_scale(64, 64, 8, 4, shift), "sharded_scale",
+            dict(a0_ptr=np.ascontiguousarray(a[:32]), a1_ptr=np.ascontiguousarray(a[32:, :32].T),
+                 a2_ptr=np.ascontiguousarray(a[32:, 32:]), o0_ptr=np.full((64, 32), 7, np.float16),
+                 o1_ptr=np.full((64, 32), 7, np.float16)))
+    x = dist.standard_normal((8, 256)).astype(np.float16)
+    out["sharded_center_8x256"] = (K.sharded_center(256, 4, 8), "sharded_center", dict(x_ptr=x, y_ptr=np.zeros_like(x)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

@@ -27,7 +27,9 @@ def run_generic(src, fn, kw):
         allocs.append(Allocation(name, off, off + nb, to_ktir_dtype(dt)))
     amap = ArenaMap(allocs)
     kinds = set()
-    for st in Tracer(func, scalars, ptrs).run():
+    tracer = Tracer(func, scalars, ptrs)
+    tracer.arena = amap
+    for st in tracer.run():
         sel, _ = _points(st)
         prog = build_generic(st, amap, sel)[0]
         kinds.update(op.kind for op in prog.ops)
@@ -40,7 +42,8 @@ def run_generic(src, fn, kw):
 
 EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elementwise_f16_suite",
          "ring_allreduce_4x4_add_f16", "ring_allreduce_8x2_max_f32_strided", "ring_allreduce_6x3_mul_f16_loop",
-         "ring_allreduce_16x16_add_f16", "ring_allreduce_16x4_add_f16", "shared_slot_store_12x5")
+         "ring_allreduce_16x16_add_f16", "ring_allreduce_16x4_add_f16", "shared_slot_store_12x5",
+         "vector_add_short_4000", "sharded_scale_64x64_shift0", "sharded_scale_64x64_shift3", "sharded_center_8x256")
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 
@@ -66,6 +69,24 @@ def test_step_kinds_cover_reduction_matmul_and_indirect_access():
     assert {"load", "redl", "ew", "store"} <= k1
     assert {"matmul", "map", "redl"} <= k2
     assert {"addr", "idxadd", "gather"} <= k3
+
+
+def test_distributed_view_tiles_resolve_to_address_tables_or_plain_tiles():
+    """A tile that crosses partition boundaries becomes a per-element address table (holes where no
+    partition backs it); tiles that lie whole inside one partition stay ordinary strided tiles."""
+    _, k1 = run_generic(*load_golden("sharded_scale_64x64_shift3")[:3])
+    _, k2 = run_generic(*load_golden("sharded_center_8x256")[:3])
+    assert {"table", "gather", "scatter"} <= k1 and "load" not in k1
+    assert {"load", "store", "ringred"} <= k2 and "table" not in k2
+    src, fn, kw, _ = load_golden("sharded_scale_64x64_shift3")
+    func = KTIRParser().parse_module(src).get_function(fn)
+    sess = Session(PlanOnlyDevice(), func, [(k, tuple(v.shape), v.dtype) for k, v in kw.items()], {}, arena_ptr=0)
+    (stmt,) = sess.plan.statements
+    (sc,) = [op for op in stmt.prog.ops if op.kind == "scatter"]
+    assert sc.attrs["any_order"]                      # every element has its own address: no ordering needed
+    tables = [op.attrs["values"] for op in stmt.prog.ops if op.kind == "table"]
+    assert all((t_ == -1).any() for t_ in tables)     # the last tile of the last core hangs over the end
+    assert sess.plan.written == {"o0_ptr", "o1_ptr"}
 
 
 def test_ring_reduce_uses_clusters_for_small_equal_groups():
