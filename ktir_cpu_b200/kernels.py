@@ -328,6 +328,46 @@ def gather_rows(n_table_rows: int, cols: int, n_idx: int, tile_rows: int, cores:
     return s
 
 
+def paged_gather(n_seq: int = 4, seq_len: int = 64, page: int = 16, heads: int = 2, dim: int = 32,
+                 n_pages: int = 32, chunk: int = 32, dtype: str = "f16") -> str:
+    """A paged tensor copied into a dense one: ``out[b, t, h, :] = pages[table[b, t floordiv page], h,
+    t mod page, :]`` — the position split into page and slot inside the subscripts of one indirect
+    access tile, and the [heads, chunk, dim] tile stored through an access tile that walks the dense
+    [seq, heads, dim] layout in the permuted order (h, t, d) -> (t, h, d).  The shape of
+    examples/rfc/paged-tensor-copy.mlir of the reference; core b copies sequence b, ``chunk`` positions
+    per iteration."""
+    assert seq_len % page == 0 and seq_len % chunk == 0
+    npg = seq_len // page
+    tshape = [heads, chunk, dim]
+    t, at = f"tensor<{_xs(tshape, dtype)}>", f"!ktdp.access_tile<{_xs(tshape, 'index')}>"
+    s = (f"module {{\n  func.func @paged_gather(%pages_ptr: index, %table_ptr: index, %out_ptr: index) "
+         f"attributes {{grid = [{n_seq}]}} {{\n"
+         f"    %b = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %chunk = arith.constant {chunk} : index\n    %seq_len = arith.constant {seq_len} : index\n")
+    s += view("pages", "pages_ptr", [n_pages, heads, page, dim], dtype)
+    s += view("table", "table_ptr", [n_seq, npg], "i32")
+    s += view("out", "out_ptr", [n_seq, seq_len, heads, dim], dtype)
+    s += (f"    scf.for %t0 = %c0 to %seq_len step %chunk {{\n"
+          f"      %src = ktdp.construct_indirect_access_tile\n"
+          f"          intermediate_variables(%h, %t, %d)\n"
+          f"          %pages[ind(%table[%b, (%t0 + %t) floordiv {page}]), (%h), ((%t0 + %t) mod {page}), (%d)] {{\n"
+          f"        variables_space_set = {_box(tshape)},\n"
+          f"        variables_space_order = {_ident(3)}\n"
+          f"      }} : memref<{_xs([n_pages, heads, page, dim], dtype)}>, memref<{_xs([n_seq, npg], 'i32')}>"
+          f" -> {at}\n"
+          f"      %dst = ktdp.construct_access_tile %out[%b, %t0, %c0, %c0] {{\n"
+          f"        access_tile_set = affine_set<(d0, d1, d2, d3) : (d0 >= 0, -d0 >= 0, d1 >= 0, -d1 + {heads - 1} >= 0, "
+          f"d2 >= 0, -d2 + {chunk - 1} >= 0, d3 >= 0, -d3 + {dim - 1} >= 0)>,\n"
+          f"        access_tile_order = affine_map<(d0, d1, d2, d3) -> (d0, d2, d1, d3)>\n"
+          f"      }} : memref<{_xs([n_seq, seq_len, heads, dim], dtype)}> -> !ktdp.access_tile<{_xs([1] + tshape, 'index')}>\n"
+          f"      %x = ktdp.load %src : {at} -> {t}\n"
+          f"      %x4 = tensor.expand_shape %x [[0, 1], [2], [3]] output_shape [1, {heads}, {chunk}, {dim}] : {t} into "
+          f"tensor<{_xs([1] + tshape, dtype)}>\n"
+          f"      ktdp.store %x4, %dst : tensor<{_xs([1] + tshape, dtype)}>, !ktdp.access_tile<{_xs([1] + tshape, 'index')}>\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
 def scatter_rows(n_out_rows: int, cols: int, n_idx: int, tile_rows: int, cores: int,
                  idx_dtype: str = "i32") -> str:
     """out[idx[e], :] = src[e, :] — direct load, indirect store (last writer of a row wins)."""

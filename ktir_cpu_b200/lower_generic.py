@@ -469,6 +469,70 @@ class GenBuilder:
         return self.prog.emit("map", self.prog.new(b.dtype, shape), (b,), shape=tuple(shape),
                               strides=[0] * len(shape), offset=0)
 
+    def _indirect_affine(self, ia: IndirectAccess, ks, trips, vars_e, nv: int, E: int) -> Buf:
+        """Subscripts affine in the variables: address = per-point base + per-element offset (+ lookups)."""
+        from .lower_scatter import _lin
+        P = self.prog
+        base = self.at_points(ia.view.base, ks, trips)
+        rel = np.zeros(E, np.int64)
+        lookups = []
+        pending_reads = []
+        for sub, stride in zip(ia.subs, ia.view.strides):
+            if sub["kind"] == "direct":
+                c, b = _lin(sub["expr"], nv, ia.ssa)
+                rel += stride * (np.asarray(c, np.int64)[:, None] * vars_e).sum(0)
+                base = base + stride * self.at_points(b, ks, trips)
+            else:
+                iv = ia.index_views[sub["view"]]
+                ibase = self.at_points(iv.base, ks, trips)
+                irel = np.zeros(E, np.int64)
+                for e_, s_ in zip(sub["exprs"], iv.strides):
+                    c, b = _lin(e_, nv, ia.ssa)
+                    irel += s_ * (np.asarray(c, np.int64)[:, None] * vars_e).sum(0)
+                    ibase = ibase + s_ * self.at_points(b, ks, trips)
+                ial = self.alloc_of(ibase.min() if ibase.size else 0, iv.dtype, "Read from")
+                pending_reads.append(ial)
+                lookups.append((iv.dtype, ibase, irel, ial, int(stride)))
+        # nothing is emitted before every subscript has proved affine
+        self.indirect_reads.extend(pending_reads)
+        addr = P.emit("addr", P.new("i64", (E,)), (), base=base, rel=rel)
+        for idt, ibase, irel, ial, stride in lookups:
+            ibpe = bytes_per_elem(idt)
+            idx = P.emit("load", P.new(idt, (E,)), (), base=ibase, rel=irel, lo=ial.byte_lo // ibpe, hi=ial.byte_hi // ibpe)
+            addr = P.emit("idxadd", P.new("i64", (E,)), (addr, idx), stride=stride)
+        return addr
+
+    def _indirect_tabulated(self, ia: IndirectAccess, ks, trips, vars_e, E: int) -> Buf:
+        """Any quasi-affine subscripts (``floordiv`` / ``mod`` of the variables — a position split into
+        page and slot, ktir_cpu/ops/memory_ops.py:488-576): the host evaluates them for every point and
+        element and hands the device tables of addresses."""
+        from .lower_scatter import sub_values
+        P = self.prog
+
+        def at(name):
+            return self.at_points(ia.ssa[name], ks, trips)
+        n_pts = len(self.sel)
+        table = np.broadcast_to(self.at_points(ia.view.base, ks, trips)[:, None], (n_pts, E)).astype(np.int64)
+        lookups = []
+        for sub, stride in zip(ia.subs, ia.view.strides):
+            if sub["kind"] == "direct":
+                table = table + stride * sub_values(sub["expr"], vars_e, at)
+            else:
+                iv = ia.index_views[sub["view"]]
+                itab = np.broadcast_to(self.at_points(iv.base, ks, trips)[:, None], (n_pts, E)).astype(np.int64)
+                for e_, s_ in zip(sub["exprs"], iv.strides):
+                    itab = itab + s_ * sub_values(e_, vars_e, at)
+                ial = self.alloc_of(itab.min() if itab.size else 0, iv.dtype, "Read from")
+                self.indirect_reads.append(ial)
+                lookups.append((iv.dtype, np.ascontiguousarray(itab), ial, int(stride)))
+        addr = P.emit("table", P.new("i64", (E,)), (), values=np.ascontiguousarray(table))
+        for idt, itab, ial, stride in lookups:
+            ibpe = bytes_per_elem(idt)
+            iaddr = P.emit("table", P.new("i64", (E,)), (), values=itab)
+            idx = P.emit("gather", P.new(idt, (E,)), (iaddr,), lo=ial.byte_lo // ibpe, hi=ial.byte_hi // ibpe)
+            addr = P.emit("idxadd", P.new("i64", (E,)), (addr, idx), stride=stride)
+        return addr
+
     # -- indirect access tiles: one address per element, through integer steps -------------------
     def indirect_addresses(self, ia: IndirectAccess, ks, trips):
         """Element addresses ``[points, elems]`` (i64 buffer) of an indirect tile, its allocation, dtype.
@@ -489,31 +553,10 @@ class GenBuilder:
         vars_e = np.indices(ext, dtype=np.int64).reshape(nv, -1) + np.asarray(lo, np.int64)[:, None]
         P = self.prog
         dt = ia.view.dtype
-        base = self.at_points(ia.view.base, ks, trips)
-        rel = np.zeros(E, np.int64)
-        lookups = []
-        for sub, stride in zip(ia.subs, ia.view.strides):
-            if sub["kind"] == "direct":
-                c, b = _lin(sub["expr"], nv, ia.ssa)
-                rel += stride * (np.asarray(c, np.int64)[:, None] * vars_e).sum(0)
-                base = base + stride * self.at_points(b, ks, trips)
-            else:
-                iv = ia.index_views[sub["view"]]
-                ibase = self.at_points(iv.base, ks, trips)
-                irel = np.zeros(E, np.int64)
-                for e_, s_ in zip(sub["exprs"], iv.strides):
-                    c, b = _lin(e_, nv, ia.ssa)
-                    irel += s_ * (np.asarray(c, np.int64)[:, None] * vars_e).sum(0)
-                    ibase = ibase + s_ * self.at_points(b, ks, trips)
-                ial = self.alloc_of(ibase.min() if ibase.size else 0, iv.dtype, "Read from")
-                ibpe = bytes_per_elem(iv.dtype)
-                self.indirect_reads.append(ial)
-                idx = P.emit("load", P.new(iv.dtype, (E,)), (), base=ibase, rel=irel,
-                             lo=ial.byte_lo // ibpe, hi=ial.byte_hi // ibpe)
-                lookups.append((idx, int(stride)))
-        addr = P.emit("addr", P.new("i64", (E,)), (), base=base, rel=rel)
-        for idx, stride in lookups:
-            addr = P.emit("idxadd", P.new("i64", (E,)), (addr, idx), stride=stride)
+        try:
+            addr = self._indirect_affine(ia, ks, trips, vars_e, nv, E)
+        except Unsupported:
+            addr = self._indirect_tabulated(ia, ks, trips, vars_e, E)
         al = self.alloc_of(int(np.asarray(ia.view.base).reshape(-1)[0]) if np.asarray(ia.view.base).size else 0,
                            dt, "Read from")
         return addr, al, dt

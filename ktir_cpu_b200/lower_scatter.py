@@ -51,6 +51,34 @@ def _lin(expr, n_vars: int, ssa) -> Tuple[List[int], Any]:
     raise Unsupported(f"non-affine subscript ({k}) in an indirect access tile")
 
 
+def sub_values(expr, vars_e: np.ndarray, at):
+    """Value of a subscript expression at every point (rows) and every element of the variable space
+    (columns), for expressions ``_lin`` cannot split into a per-point and a per-element part
+    (``floordiv`` / ``mod`` of the variables, products of variables and SSA values).  ``vars_e`` is
+    ``[n_vars, elems]``; ``at(ssa name)`` gives that value per point."""
+    k = expr[0]
+    if k == "const":
+        return np.int64(expr[1])
+    if k == "var":
+        return vars_e[expr[1]][None, :]
+    if k == "ssa":
+        return at(expr[1])[:, None]
+    if k == "neg":
+        return -sub_values(expr[1], vars_e, at)
+    a, b = sub_values(expr[1], vars_e, at), sub_values(expr[2], vars_e, at)
+    if k == "add":
+        return a + b
+    if k == "sub":
+        return a - b
+    if k == "mul":
+        return a * b
+    if k == "floordiv":
+        return np.floor_divide(a, b)
+    if k == "mod":
+        return np.mod(a, b)
+    raise ValueError(f"bad subscript node {k}")
+
+
 @dataclass
 class RowForm:
     """Row-addressing of one operand over the tiles of a statement."""

@@ -273,7 +273,7 @@ def _unique_per_row(x: np.ndarray) -> np.ndarray:
 
 def _indirect_sticks_general(ia: IndirectAccess, axes, sel: np.ndarray, host) -> np.ndarray:
     """Stick counts of an indirect tile of any rectangular form: one address per element, host side."""
-    from .lower_scatter import _lin
+    from .lower_scatter import sub_values
     from .trace import Unsupported
     if ia.order is not None and not ia.order.is_identity():
         raise Unsupported("indirect access tile with a permuted variables_space_order")
@@ -288,18 +288,19 @@ def _indirect_sticks_general(ia: IndirectAccess, axes, sel: np.ndarray, host) ->
     def at(v):
         return np.ascontiguousarray(iv_full(v, axes).reshape(-1)[sel]).astype(np.int64)
 
+    def ssa_at(name):
+        return at(ia.ssa[name])
+
     addr = at(ia.view.base)[:, None] + np.zeros((1, vars_e.shape[1]), np.int64)
     idx_sticks = np.zeros(len(sel), np.int64)
     for sub, stride in zip(ia.subs, ia.view.strides):
         if sub["kind"] == "direct":
-            c, b = _lin(sub["expr"], nv, ia.ssa)
-            addr = addr + stride * ((np.asarray(c, np.int64)[:, None] * vars_e).sum(0)[None, :] + at(b)[:, None])
+            addr = addr + stride * sub_values(sub["expr"], vars_e, ssa_at)
         else:
             iv = ia.index_views[sub["view"]]
             iaddr = at(iv.base)[:, None] + np.zeros((1, vars_e.shape[1]), np.int64)
             for e_, s_ in zip(sub["exprs"], iv.strides):
-                c, b = _lin(e_, nv, ia.ssa)
-                iaddr = iaddr + s_ * ((np.asarray(c, np.int64)[:, None] * vars_e).sum(0)[None, :] + at(b)[:, None])
+                iaddr = iaddr + s_ * sub_values(e_, vars_e, ssa_at)
             vals = host.read(iv.dtype, iaddr.reshape(-1)).reshape(iaddr.shape).astype(np.int64)
             if (vals < 0).any():
                 raise IndexError(f"indirect index {int(vals[vals < 0][0])} is negative")

@@ -236,6 +236,14 @@ def _access_tile(tr, op, scope):
         lo, hi = box
         off = iv_bin(lambda a, b: a + b, off, sum(l * s for l, s in zip(lo, view.strides)))
         return Access(view, off, tuple(h - l for l, h in zip(lo, hi)), tuple(view.strides))
+    if box is not None:
+        # a box walked in another order: its points, row-major, through the order map — whole columns at once
+        lo, hi = box
+        cols = np.indices(tuple(h - l for l, h in zip(lo, hi)), dtype=np.int64).reshape(len(lo), -1)
+        cols = [c + l for c, l in zip(cols, lo)]
+        mapped = order.eval(cols)
+        coords_arr = np.stack([np.broadcast_to(np.asarray(m, np.int64), cols[0].shape) for m in mapped], 1)
+        return Access(view, off, shape, tuple(view.strides), np.ascontiguousarray(coords_arr))
     pts = aset.enumerate(shape)
     if order is not None:
         pts = [order.eval(pt) for pt in pts]

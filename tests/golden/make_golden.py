@@ -156,6 +156,13 @@ def cases(ref_root=None):
                  o1_ptr=np.full((64, 32), 7, np.float16)))
     x = dist.standard_normal((8, 256)).astype(np.float16)
     out["sharded_center_8x256"] = (K.sharded_center(256, 4, 8), "sharded_center", dict(x_ptr=x, y_ptr=np.zeros_like(x)))
+    # position split into page and slot by floordiv / mod inside the subscripts; permuted store order
+    pg = np.random.default_rng(13)
+    out["paged_gather_4x64"] = (
+        K.paged_gather(4, 64, 16, 2, 32, 32, 32), "paged_gather",
+        dict(pages_ptr=pg.standard_normal((32, 2, 16, 32)).astype(np.float16),
+             table_ptr=pg.permutation(32)[:16].reshape(4, 4).astype(np.int32),
+             out_ptr=np.zeros((4, 64, 2, 32), np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),
