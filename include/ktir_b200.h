@@ -274,9 +274,13 @@ int ktb_launch_scatter_rows_static(ktb_ctx* ctx, const ktb_rows_args* args);
  * thread-block cluster that reads the partials out of its members' shared memory.
  * KTB_G_TABLE fills dst from a [points][elems] host-computed table — the element addresses of a tile
  * that several partitions of a distributed memory view back (MemoryOps.distributed_tile_access,
- * ktir_cpu/ops/memory_ops.py:985-1098); KTB_G_GATHER / KTB_G_SCATTER then move the data. */
+ * ktir_cpu/ops/memory_ops.py:985-1098); KTB_G_GATHER / KTB_G_SCATTER then move the data.
+ * KTB_G_CONCAT joins two tiles along one axis (dst [outer][n + h][inner] = a [outer][n][inner] followed by
+ * b [outer][h][inner]): the carried odd slice of a pairwise reduction level
+ * (_tree_fold, ktir_cpu/dialects/linalg_ops.py:86-133). */
 enum { KTB_G_LOAD = 0, KTB_G_ADDR, KTB_G_IDXADD, KTB_G_GATHER, KTB_G_CONSTV, KTB_G_FILL, KTB_G_PARAM,
-       KTB_G_IOTA, KTB_G_MAP, KTB_G_EW, KTB_G_REDL, KTB_G_MATMUL, KTB_G_STORE, KTB_G_SCATTER, KTB_G_RING, KTB_G_TABLE };
+       KTB_G_IOTA, KTB_G_MAP, KTB_G_EW, KTB_G_REDL, KTB_G_MATMUL, KTB_G_STORE, KTB_G_SCATTER, KTB_G_RING, KTB_G_TABLE,
+       KTB_G_CONCAT };
 #define KTB_G_MAXDIM 6
 typedef struct {
     int32_t kind;                 /* KTB_G_* */

@@ -302,6 +302,21 @@ __global__ void g_redl_kernel(const __grid_constant__ ktb_gen_op o, ktb_status* 
     }
 }
 
+// dst[p][ou][k][in] = k < n ? a[p][ou][k][in] : b[p][ou][k - n][in]      (n = o.n rows of a, o.h rows of b)
+__global__ void g_concat_kernel(const __grid_constant__ ktb_gen_op o, ktb_status* st) {
+    const int size = g_size(o.dt_dst);
+    const int64_t rows = o.n + o.h;
+    G_LOOP(i, o.points * o.elems) {
+        const int64_t p = i / o.elems;
+        int64_t rem = i - p * o.elems;
+        const int64_t in = rem % o.inner;
+        rem /= o.inner;
+        const int64_t k = rem % rows, ou = rem / rows;
+        if (k < o.n) g_copy(o.dst, i, o.a, p * o.ea + (ou * o.n + k) * o.inner + in, size);
+        else g_copy(o.dst, i, o.b, p * o.eb + (ou * o.h + (k - o.n)) * o.inner + in, size);
+    }
+}
+
 // dst[p][b][m][n] = sum_k a[p][b][m][k] * b[p][b][k][n], f32 accumulation over k in order
 __global__ void g_matmul_kernel(const __grid_constant__ ktb_gen_op o, ktb_status* st) {
     G_LOOP(i, o.points * o.elems) {
@@ -443,6 +458,7 @@ extern "C" int ktb_launch_generic(ktb_ctx* ctx, const ktb_gen_op* op) {
         case KTB_G_EW: G_RUN(g_ew_kernel); break;
         case KTB_G_REDL: G_RUN(g_redl_kernel); break;
         case KTB_G_MATMUL: G_RUN(g_matmul_kernel); break;
+        case KTB_G_CONCAT: G_RUN(g_concat_kernel); break;
         case KTB_G_STORE: G_RUN(g_store_kernel); break;
         case KTB_G_SCATTER:
             if (o.flags & 4) G_RUN(g_scatter_any_order_kernel);

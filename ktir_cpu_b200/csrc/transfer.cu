@@ -16,6 +16,7 @@
 #include <vector>
 
 #include <emmintrin.h>
+#include <sched.h>
 
 #include "common.cuh"
 
@@ -120,7 +121,10 @@ CopyPool& pool() {
     static CopyPool* p = nullptr;          // leaked on purpose: no join during process teardown
     static std::once_flag once;
     std::call_once(once, [] {
+        // the CPUs this process may run on (a container or a pinned rank sees fewer than the machine has)
         unsigned hw = std::thread::hardware_concurrency();
+        cpu_set_t set;
+        if (sched_getaffinity(0, sizeof(set), &set) == 0 && CPU_COUNT(&set) > 0) hw = (unsigned)CPU_COUNT(&set);
         int n = hw >= 16 ? 8 : hw >= 4 ? (int)hw / 2 : 1;
         p = new CopyPool(n);
     });

@@ -842,6 +842,51 @@ def sharded_center(cols: int = 256, cores: int = 4, rows: int = 8, dtype: str = 
     return s
 
 
+def region_reduce_rows(n_rows: int = 16, n_cols: int = 37, cores: int = 4, dtype: str = "f16") -> str:
+    """Two row reductions whose combiners are regions of several ops: ``mx[r] = max over the row``
+    written as ``arith.cmpf ogt`` + ``arith.select`` (examples/ktir/reduce_multiop.mlir of the
+    reference), and ``sa[r]``, the fold of ``(in, out) -> |in - out| * 0.5 + in`` — neither symmetric nor
+    associative, so its value pins the order of the pairwise fold (left half with right half, odd slice
+    carried, the folded value as lhs of the final combine with the initial value).
+    ``n_cols`` may be odd at any level."""
+    R = n_rows // cores
+    assert R * cores == n_rows
+    t, at = f"tensor<1x{n_cols}x{dtype}>", f"!ktdp.access_tile<1x{n_cols}xindex>"
+    tv, atv = f"tensor<1x{dtype}>", "!ktdp.access_tile<1xindex>"
+    s = (f"module {{\n  func.func @region_reduce(%x_ptr: index, %mx_ptr: index, %sa_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n    %c1 = arith.constant 1 : index\n"
+         f"    %rows = arith.constant {R} : index\n    %row0 = arith.muli %core_id, %rows : index\n"
+         f"    %row_end = arith.addi %row0, %rows : index\n"
+         f"    %ninf = arith.constant 0xFC00 : {dtype}\n    %zero = arith.constant 0.0 : {dtype}\n"
+         f"    %half_c = arith.constant 0.5 : {dtype}\n")
+    s += view("x_view", "x_ptr", [n_rows, n_cols], dtype)
+    s += view("mx_view", "mx_ptr", [n_rows], dtype) + view("sa_view", "sa_ptr", [n_rows], dtype)
+    s += f"    scf.for %row = %row0 to %row_end step %c1 {{\n"
+    s += tile("x_tile", "x_view", ["%row", "%c0"], [1, n_cols], [n_rows, n_cols], dtype, "      ")
+    s += (f"      %x = ktdp.load %x_tile : {at} -> {t}\n"
+          f"      %mx_init = tensor.splat %ninf : {tv}\n"
+          f"      %mx = linalg.reduce ins(%x : {t}) outs(%mx_init : {tv}) dimensions = [1]\n"
+          f"        (%in: {dtype}, %out: {dtype}) {{\n"
+          f"          %gt = arith.cmpf ogt, %in, %out : {dtype}\n"
+          f"          %sel = arith.select %gt, %in, %out : {dtype}\n"
+          f"          linalg.yield %sel : {dtype}\n        }}\n"
+          f"      %sa_init = tensor.splat %zero : {tv}\n"
+          f"      %sa = linalg.reduce ins(%x : {t}) outs(%sa_init : {tv}) dimensions = [1]\n"
+          f"        (%in2: {dtype}, %out2: {dtype}) {{\n"
+          f"          %df = arith.subf %in2, %out2 : {dtype}\n"
+          f"          %ab = math.absf %df : {dtype}\n"
+          f"          %hf = arith.mulf %ab, %half_c : {dtype}\n"
+          f"          %sm = arith.addf %hf, %in2 : {dtype}\n"
+          f"          linalg.yield %sm : {dtype}\n        }}\n")
+    s += tile("mx_tile", "mx_view", ["%row"], [1], [n_rows], dtype, "      ")
+    s += tile("sa_tile", "sa_view", ["%row"], [1], [n_rows], dtype, "      ")
+    s += (f"      ktdp.store %mx, %mx_tile : {tv}, {atv}\n      ktdp.store %sa, %sa_tile : {tv}, {atv}\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
 def layernorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, eps: float = 1e-5) -> str:
     """y = (x - mean) / sqrt(var + eps) * w + b per row, f32 statistics, one row per iteration.
 

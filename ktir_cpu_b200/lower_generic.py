@@ -310,6 +310,17 @@ class GenBuilder:
             st = _row_major_strides(n.args[0].shape)
             return P.emit("map", P.new(src.dtype, n.shape), (src,), shape=tuple(n.shape),
                           strides=[st[p] for p in perm], offset=0)
+        if k == "slice":
+            src = self._full(self.eval(n.args[0], ks, loops), n.args[0].shape)
+            st = _row_major_strides(n.args[0].shape)
+            return P.emit("map", P.new(src.dtype, n.shape), (src,), shape=tuple(n.shape), strides=list(st),
+                          offset=int(n.attrs["lo"] * st[n.attrs["dim"]]))
+        if k == "concat":
+            a = self._full(self.eval(n.args[0], ks, loops), n.args[0].shape)
+            b = self._full(self.eval(n.args[1], ks, loops), n.args[1].shape)
+            d_ = n.attrs["dim"]
+            return P.emit("concat", P.new(n.dtype, n.shape), (a, b), outer=_prod(n.shape[:d_]), na=int(n.args[0].shape[d_]),
+                          nb=int(n.args[1].shape[d_]), inner=_prod(n.shape[d_ + 1:]))
         if k == "extract":
             src = self.eval(n.args[0], ks, loops)
             if src.elems == 1:
@@ -790,6 +801,8 @@ def _make_statement_class():
                         g.outer, g.n, g.inner, g.h = int(a["outer"]), int(a["n"]), int(a["inner"]), int(a["h"])
                 elif op.kind == "matmul":
                     g.batch, g.M, g.N, g.K = int(a["batch"]), int(a["M"]), int(a["N"]), int(a["K"])
+                elif op.kind == "concat":
+                    g.outer, g.n, g.h, g.inner = int(a["outer"]), int(a["na"]), int(a["nb"]), int(a["inner"])
                 elif op.kind == "ringred":
                     g.op = EW_CODE[a["op"]]
                     g.flags = 2 if a["swapped"] else 0

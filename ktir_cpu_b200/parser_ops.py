@@ -362,6 +362,10 @@ def parse_linalg_named(p, name, results) -> Op:
         p.eat("{")
         reg.ops = p.block()
         p.eat("}")
+        # in this form the reference reads the block arguments off the operands of the region's first
+        # op, not off the header (ktir_cpu/dialects/linalg_ops.py:30-58): lhs and rhs bind in THAT order
+        if reg.ops:
+            reg.arg_names = [o_ for o_ in reg.ops[0].operands if isinstance(o_, str)]
         regions.append(reg)
     elif p.at("{"):
         regions.append(_bb_region(p))

@@ -93,7 +93,7 @@ class AttnArgs(C.Structure):
 
 G_MAXDIM = 6
 G_KINDS = {k: i for i, k in enumerate(["load", "addr", "idxadd", "gather", "constv", "fill", "param", "iota", "map",
-                                       "ew", "redl", "matmul", "store", "scatter", "ringred", "table"])}
+                                       "ew", "redl", "matmul", "store", "scatter", "ringred", "table", "concat"])}
 
 
 NO_DEVICE = (1 << 64) - 1

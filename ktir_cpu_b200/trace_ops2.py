@@ -95,7 +95,7 @@ def _reduce(tr, op, scope):
     else:
         comb = _combiner_of(op)
         if comb is None:
-            raise Unsupported("linalg.reduce with a multi-op combiner region")
+            return _reduce_by_region(tr, op, scope, tile, outs_name, outs)
         comb = _CANON_COMB.get(comb, comb)
         dims = op.attrs.get("dimensions")
         if dims is None:
@@ -112,6 +112,71 @@ def _reduce(tr, op, scope):
         scope[outs_name] = result
         if tr.lx is not None and is_node(result):
             tr.lx.set_value(outs_name, result, tr.cores_active())      # the result is bound under the outs name too
+    return result
+
+
+def _slice(node: Node, dim: int, lo: int, hi: int) -> Node:
+    shape = list(node.shape)
+    shape[dim] = hi - lo
+    return Node("slice", tuple(shape), node.dtype, (node,), {"dim": dim, "lo": lo, "hi": hi})
+
+
+def _reduce_by_region(tr, op, scope, tile: Node, outs_name, outs):
+    """A combiner region of several ops (e.g. max written as cmpf + select): the pairwise fold of the
+    reference spelled out in the DAG (ktir_cpu/dialects/linalg_ops.py:86-133) — per level the two
+    halves of the reduced axis go through the region, an odd leftover slice is carried to the next
+    level — followed by the combine with ``outs``.  The region's ops are charged by the level-wise
+    latency and scratchpad replays that every reduce gets, so it is traced here without them."""
+    reg = op.regions[0]
+    names = list(reg.arg_names)
+    if len(names) < 2:
+        raise ValueError("linalg.reduce: combiner region needs two block arguments")
+
+    def combine(lhs, rhs):
+        inner = dict(scope)
+        inner[names[0]], inner[names[1]] = lhs, rhs
+        y = tr.trace_ops(reg.ops, inner)
+        if not isinstance(y, _Yield) or not y.values:
+            raise TypeError("linalg.reduce: combiner region did not yield a value")
+        v = y.values[0]
+        if not is_node(v):
+            raise Unsupported("linalg.reduce whose combiner region yields a non-tile value")
+        return v if tuple(v.shape) == tuple(lhs.shape) else Node("bcast", tuple(lhs.shape), v.dtype, (v,), {"numpy": True})
+
+    dims = op.attrs.get("dimensions")
+    saved = tr.latency, tr.lx
+    tr.latency = tr.lx = None
+    try:
+        acc = tile
+        if dims is None:
+            acc = Node("reshape", (int(np.prod(tile.shape, dtype=np.int64)),), tile.dtype, (tile,), {})
+            fold = [0]
+        else:
+            fold = sorted(dims, reverse=True)
+        for d in fold:
+            n = acc.shape[d]
+            while n > 1:
+                half = n // 2
+                combined = combine(_slice(acc, d, 0, half), _slice(acc, d, half, 2 * half))
+                if n % 2:
+                    tail = _slice(acc, d, 2 * half, n)
+                    shape = list(combined.shape)
+                    shape[d] = half + 1
+                    combined = Node("concat", tuple(shape), combined.dtype, (combined, tail), {"dim": d})
+                acc = combined
+                n = acc.shape[d]
+        out_shape = () if dims is None else tuple(s_ for i, s_ in enumerate(tile.shape) if i not in dims)
+        result = Node("reshape", out_shape, tile.dtype, (acc,), {})
+        if is_node(outs):
+            result = combine(result, outs)
+    finally:
+        tr.latency, tr.lx = saved
+    if tr.lx is not None:
+        _reduce_transients(tr, op, tile, dims, out_shape, outs)
+    if outs_name:
+        scope[outs_name] = result
+        if tr.lx is not None:
+            tr.lx.set_value(outs_name, result, tr.cores_active())
     return result
 
 

@@ -95,6 +95,10 @@ def run(prog, arena: np.ndarray):
                 if a["n"] % 2:
                     comb = np.concatenate([comb, x[:, :, 2 * h:].astype(comb.dtype)], axis=2)
                 out = comb.reshape(P, -1)
+            elif k == "concat":
+                x = np.broadcast_to(src[0], (P, a["outer"] * a["na"] * a["inner"])).reshape(P, a["outer"], a["na"], a["inner"])
+                y = np.broadcast_to(src[1], (P, a["outer"] * a["nb"] * a["inner"])).reshape(P, a["outer"], a["nb"], a["inner"])
+                out = np.concatenate([x, y], axis=2).reshape(P, -1)
             elif k == "matmul":
                 A = src[0].reshape(P, a["batch"], a["M"], a["K"]).astype(np.float32)
                 B = src[1].reshape(P, a["batch"], a["K"], a["N"]).astype(np.float32)

@@ -163,6 +163,11 @@ def cases(ref_root=None):
         dict(pages_ptr=pg.standard_normal((32, 2, 16, 32)).astype(np.float16),
              table_ptr=pg.permutation(32)[:16].reshape(4, 4).astype(np.int32),
              out_ptr=np.zeros((4, 64, 2, 32), np.float16)))
+    # reductions whose combiner is a region of several ops; 37 columns: an odd slice is carried at three levels
+    rr = np.random.default_rng(14)
+    x = rr.standard_normal((16, 37)).astype(np.float16)
+    out["region_reduce_16x37"] = (K.region_reduce_rows(16, 37, 4), "region_reduce",
+                                  dict(x_ptr=x, mx_ptr=np.zeros(16, np.float16), sa_ptr=np.zeros(16, np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),
