@@ -887,6 +887,38 @@ def region_reduce_rows(n_rows: int = 16, n_cols: int = 37, cores: int = 4, dtype
     return s
 
 
+def generic_contraction(M: int = 8, N: int = 16, K: int = 24, cores: int = 2, dtype: str = "f32") -> str:
+    """C = A @ B + C0 written as one ``linalg.generic`` with a reduction iterator (maps (m, n, k) ->
+    (m, k), (k, n), (m, n); body mulf + addf into the outs argument) — the contraction form of the
+    reference's ``linalg.generic`` tests (tests/test_dialects_exec.py:1218-1283).  Core c computes
+    ``M / cores`` rows; the products over k are folded pairwise, not summed in k order."""
+    R = M // cores
+    assert R * cores == M
+    ta, tb, tc = f"tensor<{R}x{K}x{dtype}>", f"tensor<{K}x{N}x{dtype}>", f"tensor<{R}x{N}x{dtype}>"
+    s = (f"module {{\n  func.func @generic_contraction(%a_ptr: index, %b_ptr: index, %c_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %rows = arith.constant {R} : index\n    %row0 = arith.muli %core_id, %rows : index\n")
+    s += view("a_view", "a_ptr", [M, K], dtype) + view("b_view", "b_ptr", [K, N], dtype) + view("c_view", "c_ptr", [M, N], dtype)
+    s += tile("a_tile", "a_view", ["%row0", "%c0"], [R, K], [M, K], dtype)
+    s += tile("b_tile", "b_view", ["%c0", "%c0"], [K, N], [K, N], dtype)
+    s += tile("c_tile", "c_view", ["%row0", "%c0"], [R, N], [M, N], dtype)
+    s += (f"    %a = ktdp.load %a_tile : !ktdp.access_tile<{R}x{K}xindex> -> {ta}\n"
+          f"    %b = ktdp.load %b_tile : !ktdp.access_tile<{K}x{N}xindex> -> {tb}\n"
+          f"    %c_init = ktdp.load %c_tile : !ktdp.access_tile<{R}x{N}xindex> -> {tc}\n"
+          f"    %c = linalg.generic {{\n"
+          f"        indexing_maps = [affine_map<(d0, d1, d2) -> (d0, d2)>, affine_map<(d0, d1, d2) -> (d2, d1)>, "
+          f"affine_map<(d0, d1, d2) -> (d0, d1)>],\n"
+          f"        iterator_types = [\"parallel\", \"parallel\", \"reduction\"]}}\n"
+          f"        ins(%a, %b : {ta}, {tb})\n        outs(%c_init : {tc}) {{\n"
+          f"      ^bb0(%aa : {dtype}, %bb : {dtype}, %cc : {dtype}):\n"
+          f"        %prod = arith.mulf %aa, %bb : {dtype}\n"
+          f"        %acc = arith.addf %prod, %cc : {dtype}\n"
+          f"        linalg.yield %acc : {dtype}\n    }} -> {tc}\n"
+          f"    ktdp.store %c, %c_tile : {tc}, !ktdp.access_tile<{R}x{N}xindex>\n    return\n  }}\n}}\n")
+    return s
+
+
 def layernorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, eps: float = 1e-5) -> str:
     """y = (x - mean) / sqrt(var + eps) * w + b per row, f32 statistics, one row per iteration.
 

@@ -309,10 +309,10 @@ def _generic(tr, op, scope):
     n_ins = op.attrs["n_ins"]
     maps = op.attrs.get("indexing_maps", [])
     iters = op.attrs.get("iterator_types") or []
-    if any(t == "reduction" for t in iters):
-        raise Unsupported("linalg.generic with reduction iterators")
     ins = [tr.get(scope, o) for o in op.operands[:n_ins]]
     outs = tr.get(scope, op.operands[n_ins])
+    if any(t == "reduction" for t in iters):
+        return _generic_reduction(tr, op, scope, ins, outs, maps, [i for i, t in enumerate(iters) if t == "reduction"])
     if not is_node(outs):
         raise TypeError(f"linalg.generic: outs must be a Tile, got {type(outs)}")
     reg = op.regions[0]
@@ -338,6 +338,74 @@ def _generic(tr, op, scope):
     if isinstance(v, np.ndarray):
         raise Unsupported("linalg.generic yielding a per-core scalar")
     return const_node(v, outs.shape, outs.dtype)
+
+
+_GENERIC_IDENTITY = {"arith.addf": 0.0, "arith.addi": 0, "arith.mulf": 1.0, "arith.muli": 1,
+                     "arith.maxf": float("-inf"), "arith.maximumf": float("-inf"),
+                     "arith.minf": float("inf"), "arith.minimumf": float("inf")}
+
+
+def _generic_reduction(tr, op, scope, ins, outs, maps, red):
+    """``linalg.generic`` with reduction iterators (ktir_cpu/dialects/linalg_ops.py:466-585): the body
+    runs once over the full iteration space with the ``outs`` argument bound to the combiner's identity,
+    its result is folded pairwise along the reduction dims (rightmost first) by the combiner — the op
+    that produces the yielded value from the ``outs`` argument — and the fold is combined with the real
+    ``outs``."""
+    n_ins = op.attrs["n_ins"]
+    if not is_node(outs):
+        raise TypeError(f"linalg.generic: outs must be a Tile, got {type(outs)}")
+    reg = op.regions[0]
+    if not reg.arg_names:
+        raise ValueError("linalg.generic: cannot determine bb0 argument names")
+    extent = [None] * maps[0].n_dims
+    shapes = [v.shape for v in ins if is_node(v)] + [outs.shape]
+    for m, shp in zip(maps, shapes):
+        for k, e in enumerate(m.exprs):
+            if e[0] == "dim" and extent[e[1]] is None:
+                extent[e[1]] = shp[k]
+    if any(e is None for e in extent):
+        raise ValueError(f"linalg.generic: cannot infer extent for dims {[i for i, e in enumerate(extent) if e is None]}")
+    iter_shape = tuple(int(e) for e in extent)
+    outs_arg = reg.arg_names[n_ins] if n_ins < len(reg.arg_names) else None
+    yop = next((o for o in reg.ops if o.name == "linalg.yield"), None)
+    comb = None
+    if yop is not None and yop.operands:
+        comb = next((o for o in reg.ops if o.results and o.results[0] == yop.operands[0] and outs_arg in o.operands), None)
+    if comb is None:
+        raise ValueError(f"linalg.generic: cannot identify combiner op for reduction (outs block-arg '{outs_arg}' "
+                         "not found in body ops)")
+    if comb.name not in _GENERIC_IDENTITY:
+        raise ValueError(f"linalg.generic: unsupported combiner '{comb.name}' for reduction; "
+                         f"supported: {list(_GENERIC_IDENTITY)}")
+    inner = dict(scope)
+    inner["__linalg_shape__"] = iter_shape
+    held = []
+    for i, (v, m) in enumerate(zip(ins, maps[:n_ins])):
+        inner[reg.arg_names[i]] = _map_input(v, m, iter_shape) if is_node(v) else v
+        if is_node(v):
+            held.append((reg.arg_names[i], Node("held", iter_shape, v.dtype)))
+    inner[outs_arg] = const_node(_GENERIC_IDENTITY[comb.name], iter_shape, outs.dtype)
+    held.append((outs_arg, Node("held", iter_shape, outs.dtype)))
+    r = tr.trace_region(reg.ops, inner, held)
+    v = r.values[0] if isinstance(r, _Yield) else None
+    if isinstance(v, np.ndarray):
+        raise Unsupported("linalg.generic yielding a per-core scalar")
+    if not is_node(v):
+        v = const_node(v, iter_shape, outs.dtype)
+    elif tuple(v.shape) != iter_shape:
+        v = Node("bcast", iter_shape, v.dtype, (v,), {"dims": [], "numpy": True})
+    name = _CANON_COMB.get(comb.name, comb.name)
+    out_shape = tuple(s_ for i, s_ in enumerate(iter_shape) if i not in red)
+    folded = Node("reduce", out_shape, v.dtype, (v,), {"op": name, "dims": tuple(sorted(red))})
+    fake = Op("linalg.reduce", [], [], {"combiner": comb.name, "dimensions": list(red)})
+    if tr.lx is not None:
+        _reduce_transients(tr, fake, v, list(red), out_shape, outs)
+    if tr.latency is not None:
+        tr.latency._reduce(tr, fake, [v, outs])
+    result = ew(name, [cast(folded, outs.dtype), outs], dtype=outs.dtype)
+    if tuple(result.shape) != tuple(outs.shape):
+        result = Node("reshape", tuple(outs.shape), result.dtype, (result,), {})
+    return result
 
 
 # ---- control flow -------------------------------------------------------------------

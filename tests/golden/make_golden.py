@@ -168,6 +168,12 @@ def cases(ref_root=None):
     x = rr.standard_normal((16, 37)).astype(np.float16)
     out["region_reduce_16x37"] = (K.region_reduce_rows(16, 37, 4), "region_reduce",
                                   dict(x_ptr=x, mx_ptr=np.zeros(16, np.float16), sa_ptr=np.zeros(16, np.float16)))
+    # linalg.generic with a reduction iterator: products folded pairwise over k (13: odd levels)
+    gc = np.random.default_rng(15)
+    out["generic_contraction_4x8x13"] = (
+        K.generic_contraction(4, 8, 13, 2, "f16"), "generic_contraction",
+        dict(a_ptr=gc.standard_normal((4, 13)).astype(np.float16), b_ptr=gc.standard_normal((13, 8)).astype(np.float16),
+             c_ptr=gc.standard_normal((4, 8)).astype(np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),
