@@ -301,6 +301,37 @@ def tiled_matmul(M: int = 4096, N: int = 4096, K: int = 4096, bm: int = 64, bn: 
     return s
 
 
+def gather_rows_transposed(n_table_rows: int = 32, cols: int = 16, n_idx: int = 64, tile_rows: int = 8,
+                           cores: int = 2, idx_dtype: str = "i32") -> str:
+    """out[:, e] = table[idx[e], :] — the indirect tile enumerates its (row, column) variable space in
+    the order ``variables_space_order = (d0, d1) -> (d1, d0)``, i.e. column by column, so the loaded
+    tile is the transpose [cols, tile_rows] of the gathered rows and goes to ``out`` [cols, n_idx] as is."""
+    per_core = n_idx // cores
+    assert per_core * cores == n_idx and per_core % tile_rows == 0
+    t = f"tensor<{cols}x{tile_rows}xf16>"
+    s = (f"module {{\n  func.func @gather_rows_transposed(%table_ptr: index, %idx_ptr: index, %out_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n    %tile_rows = arith.constant {tile_rows} : index\n"
+         f"    %begin = arith.muli %pid, %per_core : index\n    %end = arith.addi %begin, %per_core : index\n")
+    s += view("table", "table_ptr", [n_table_rows, cols], "f16")
+    s += view("out", "out_ptr", [cols, n_idx], "f16")
+    s += view("idx", "idx_ptr", [n_idx], idx_dtype)
+    s += "    scf.for %base = %begin to %end step %tile_rows {\n"
+    s += (f"      %src = ktdp.construct_indirect_access_tile\n"
+          f"          intermediate_variables(%d0, %d1)\n"
+          f"          %table[ind(%idx[%base + %d0]), (%d1)] {{\n"
+          f"        variables_space_set = {_box([tile_rows, cols])},\n"
+          f"        variables_space_order = affine_map<(d0, d1) -> (d1, d0)>\n"
+          f"      }} : memref<{_xs([n_table_rows, cols], 'f16')}>, memref<{n_idx}x{idx_dtype}>"
+          f" -> !ktdp.access_tile<{tile_rows}x{cols}xindex>\n")
+    s += tile("dst", "out", ["%c0", "%base"], [cols, tile_rows], [cols, n_idx], "f16", "      ")
+    s += (f"      %cols_first = ktdp.load %src : !ktdp.access_tile<{tile_rows}x{cols}xindex> -> {t}\n"
+          f"      ktdp.store %cols_first, %dst : {t}, !ktdp.access_tile<{cols}x{tile_rows}xindex>\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
 def gather_rows(n_table_rows: int, cols: int, n_idx: int, tile_rows: int, cores: int,
                 idx_dtype: str = "i32") -> str:
     """out[e, :] = table[idx[e], :] — indirect load, direct store."""

@@ -553,15 +553,8 @@ class GenBuilder:
         enumerated row-major over the (rectangular) variable space.
         """
         from .lower_scatter import _lin
-        if ia.order is not None and not ia.order.is_identity():
-            raise Unsupported("indirect access tile with a permuted variables_space_order")
-        box = ia.aset.box()
-        if box is None:
-            raise Unsupported("indirect access tile over a non-rectangular variable space")
-        lo, hi = box
-        ext = [h - l for l, h in zip(lo, hi)]
-        nv, E = len(ext), _prod(ext)
-        vars_e = np.indices(ext, dtype=np.int64).reshape(nv, -1) + np.asarray(lo, np.int64)[:, None]
+        vars_e = variable_space_points(ia)
+        nv, E = vars_e.shape
         P = self.prog
         dt = ia.view.dtype
         try:
@@ -571,6 +564,25 @@ class GenBuilder:
         al = self.alloc_of(int(np.asarray(ia.view.base).reshape(-1)[0]) if np.asarray(ia.view.base).size else 0,
                            dt, "Read from")
         return addr, al, dt
+
+
+def variable_space_points(ia: IndirectAccess) -> np.ndarray:
+    """The points of an indirect tile's variable space as ``[n_vars, elems]``, in the order its elements
+    are enumerated: row-major over the set, re-sorted by ``variables_space_order`` when that permutes
+    the variables (ktir_cpu/ops/memory_ops.py:488-520)."""
+    box = ia.aset.box()
+    if box is not None:
+        lo, hi = box
+        ext = [h - l for l, h in zip(lo, hi)]
+        pts = np.indices(ext, dtype=np.int64).reshape(len(ext), -1) + np.asarray(lo, np.int64)[:, None]
+    else:
+        lst = ia.aset.enumerate(ia.shape)
+        pts = np.asarray(lst, np.int64).reshape(len(lst), len(ia.shape)).T
+    if ia.order is not None and not ia.order.is_identity():
+        keys = ia.order.eval(list(pts))
+        keys = [np.broadcast_to(np.asarray(k_, np.int64), pts.shape[1:]) for k_ in keys]
+        pts = pts[:, np.lexsort(tuple(reversed(keys)))]
+    return np.ascontiguousarray(pts)
 
 
 ALL_MEMORY = 1 << 60      # upper bound of a gather / scatter whose addresses the host has already checked

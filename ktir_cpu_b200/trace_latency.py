@@ -275,15 +275,9 @@ def _indirect_sticks_general(ia: IndirectAccess, axes, sel: np.ndarray, host) ->
     """Stick counts of an indirect tile of any rectangular form: one address per element, host side."""
     from .lower_scatter import sub_values
     from .trace import Unsupported
-    if ia.order is not None and not ia.order.is_identity():
-        raise Unsupported("indirect access tile with a permuted variables_space_order")
-    box = ia.aset.box()
-    if box is None:
-        raise Unsupported("indirect access tile over a non-rectangular variable space")
-    lo, hi = box
-    ext = [h - l for l, h in zip(lo, hi)]
-    nv = len(ext)
-    vars_e = np.indices(ext, dtype=np.int64).reshape(nv, -1) + np.asarray(lo, np.int64)[:, None]
+    from .lower_generic import variable_space_points
+    vars_e = variable_space_points(ia)
+    nv = vars_e.shape[0]
 
     def at(v):
         return np.ascontiguousarray(iv_full(v, axes).reshape(-1)[sel]).astype(np.int64)

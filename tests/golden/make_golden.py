@@ -174,6 +174,12 @@ def cases(ref_root=None):
         K.generic_contraction(4, 8, 13, 2, "f16"), "generic_contraction",
         dict(a_ptr=gc.standard_normal((4, 13)).astype(np.float16), b_ptr=gc.standard_normal((13, 8)).astype(np.float16),
              c_ptr=gc.standard_normal((4, 8)).astype(np.float16)))
+    # indirect tile enumerated column by column (permuted variables_space_order)
+    gt = np.random.default_rng(16)
+    out["gather_rows_transposed_64x16"] = (
+        K.gather_rows_transposed(32, 16, 64, 8, 2), "gather_rows_transposed",
+        dict(table_ptr=gt.standard_normal((32, 16)).astype(np.float16), idx_ptr=gt.integers(0, 32, 64).astype(np.int32),
+             out_ptr=np.zeros((16, 64), np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

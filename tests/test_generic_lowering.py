@@ -44,7 +44,8 @@ EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elemen
          "ring_allreduce_4x4_add_f16", "ring_allreduce_8x2_max_f32_strided", "ring_allreduce_6x3_mul_f16_loop",
          "ring_allreduce_16x16_add_f16", "ring_allreduce_16x4_add_f16", "shared_slot_store_12x5",
          "vector_add_short_4000", "sharded_scale_64x64_shift0", "sharded_scale_64x64_shift3", "sharded_center_8x256",
-         "paged_gather_4x64", "region_reduce_16x37", "generic_contraction_4x8x13")
+         "paged_gather_4x64", "region_reduce_16x37", "generic_contraction_4x8x13",
+         "gather_rows_transposed_64x16")
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 
