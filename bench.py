@@ -780,6 +780,80 @@ def candidates_report(dist, sweeps=2, cpu=True):
     return out
 
 
+# The block gathers of the reference's indirect-load benchmark (benchmarks/configs/load_path_compare.toml):
+# label -> (source shape, rows selected per indirect dim).  Leading dims are looked up, the rest taken whole.
+GATHER_WORKLOADS = {
+    "moe-262K": ((128, 256, 128), (8,)), "moe-1M": ((128, 1024, 128), (8,)),
+    "paged-attn-256K": ((1024, 16, 128, 128), (16,)),
+    "sparse-attn-32K": ((1024, 512, 64), (4, 16)), "sparse-attn-128K": ((4096, 512, 256), (4, 16)),
+    "retro-attn-16K": ((1024, 128, 128), (32, 4)), "multi-head-4M": ((128, 64, 256, 256), (8, 8)),
+}
+
+
+def _bit_pattern(n, seed):
+    """n pseudo-random f16 bit patterns (finite values), generated in pieces: these sources reach 1 GiB."""
+    out = np.empty(n, np.uint16)
+    step = 1 << 24
+    for i in range(0, n, step):
+        j = min(n, i + step)
+        x = (np.arange(i, j, dtype=np.uint64) + seed) * np.uint64(0x9E3779B97F4A7C15)
+        out[i:j] = ((x >> np.uint64(40)) & np.uint64(0x7BFF)).astype(np.uint16)       # exponent < 31: no inf / NaN
+    return out.view(np.float16)
+
+
+def gathers_report(device, steps=10, cpu=True):
+    """The seven block gathers as KTIR kernels (one indirect tile load + store), device-timed with the
+    tensors resident: result bytes moved (read + written) per second against the HBM roofline, and — for
+    the sizes the reference finishes in seconds — the reference interpreter on the same kernel."""
+    from ktir_cpu_b200 import HardwareConfig, KTIRInterpreter, kernels as K
+    peak, _, src_peak = measured_peak("hbm")
+    rows = {}
+    for label, (shape, sel) in GATHER_WORKLOADS.items():
+        rshape = tuple(sel) + tuple(shape[len(sel):])
+        rng = np.random.default_rng(17)
+        kw = {"src_ptr": _bit_pattern(int(np.prod(shape)), 17).reshape(shape)}
+        for i, n_ in enumerate(sel):
+            kw[f"idx{i}_ptr"] = rng.choice(shape[i], n_, replace=False).astype(np.int32)
+        kw["out_ptr"] = np.zeros(rshape, np.float16)
+        it = KTIRInterpreter(device=device, latency_config=HardwareConfig(lx_size_mb=64))
+        it.load(K.blocked_gather(shape, sel))
+        try:
+            sess, _ = it.session("blocked_gather", **kw)
+            for k, v in kw.items():
+                sess.upload(k, v)
+            dev = it.device
+            dev.sync()
+            per_step, launches = time_device(dev, sess.run, steps, 3)
+            got = sess.download("out_ptr")
+            dev.sync()
+            want = kw["src_ptr"][np.ix_(*[kw[f"idx{i}_ptr"] for i in range(len(sel))])]
+            ok = bool(np.array_equal(got.view(np.uint16), want.view(np.uint16)))
+            ms = float(np.mean(per_step))
+            moved = 2 * want.nbytes + sum(kw[f"idx{i}_ptr"].nbytes for i in range(len(sel)))
+            rows[label] = {"source_shape": list(shape), "result_shape": list(rshape), "kernels": [s_.kind for s_ in sess.plan.statements],
+                           "t_indirect_load_us": ms * 1e3, "launches_per_step": launches // max(steps, 1),
+                           "roofline": {"bound": "hbm", "achieved": moved / ms / 1e6, "peak": peak, "unit": "GB/s",
+                                        "frac": moved / ms / 1e6 / peak, "peak_source": src_peak,
+                                        "algorithmic_per_launch": moved},
+                           "bit_exact": ok}
+            if cpu and want.nbytes <= (4 << 20) and int(np.prod(shape)) <= (1 << 26):
+                ref = _cpu_interpreter()
+                if reference_available():
+                    from ktir_cpu import HardwareConfig as RefConfig
+                    ref = type(ref)(latency_config=RefConfig(lx_size_mb=64))
+                ref.load(K.blocked_gather(shape, sel))
+                t0 = time.perf_counter()
+                r = ref.execute_function("blocked_gather", **kw)
+                rows[label]["reference_ms"] = (time.perf_counter() - t0) * 1e3
+                rows[label]["reference_equal"] = bool(np.array_equal(r["out_ptr"].view(np.uint16), want.view(np.uint16)))
+        except Exception as e:                               # noqa: BLE001
+            rows[label] = {"error": f"{type(e).__name__}: {e}"}
+        it.close()
+    return {"metric": "block gathers of the reference's indirect-load benchmark, tensors resident", "workloads": rows,
+            "reference_kind": "reference" if reference_available() else "port",
+            "note": "reference_ms is one execute_function call of the reference interpreter, host copies included"}
+
+
 def run_gpu(args, w):
     dist = Dist()
     from ktir_cpu_b200.interpreter import KTIRInterpreter
@@ -862,6 +936,11 @@ def run_gpu(args, w):
                 extras["candidates"] = candidates_report(dist, cpu=cpu and dist.world == 1)
             except Exception as e:                           # noqa: BLE001
                 extras["candidates"] = {"error": f"{type(e).__name__}: {e}"}
+            if dist.world == 1:
+                try:
+                    extras["indirect_gathers"] = gathers_report(dist.local, cpu=cpu)
+                except Exception as e:                       # noqa: BLE001
+                    extras["indirect_gathers"] = {"error": f"{type(e).__name__}: {e}"}
         line["extras"] = extras
     if dist.rank == 0:
         print(json.dumps(line))
@@ -887,13 +966,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS) + ["candidates"])
+    ap.add_argument("--workload", default="softmax", choices=sorted(WORKLOADS) + ["candidates", "gathers"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline samples")
     ap.add_argument("--no-extras", action="store_true", help="only the headline workload")
     ap.add_argument("--no-sustained", action="store_true", help="skip the eight-arena steady-state measurement")
     args = ap.parse_args()
     if args.workload == "candidates":
         return run_candidates(args)
+    if args.workload == "gathers":
+        print(json.dumps(gathers_report(0, max(3, args.steps // 2), cpu=not args.no_cpu)))
+        return
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)

@@ -164,15 +164,19 @@ static __device__ __forceinline__ void sc_move_group(const ktb_rows_args& a, con
 
 // ---- direct destination: every entry is independent ------------------------------------------
 template <int V, int PROG>
-__global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_constant__ ktb_rows_args a, ktb_status* st) {
+// A warp resolves the addresses of `per_warp` entries at once (one per lane) and then moves their rows
+// four at a time; with few entries per_warp is small, so that the rows spread over many warps
+// instead of queueing behind one another in a few.
+__global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_constant__ ktb_rows_args a, int per_warp,
+                                                               ktb_status* st) {
     constexpr int G = 4;
     extern __shared__ float4 rp_vm[];                 // [KTB_VM_REGS][blockDim.x] register file
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     const int64_t E = a.n_tiles * a.tile_rows;
-    for (int64_t e0 = warp * 32; e0 < E; e0 += n_warps * 32) {
-        const bool have = e0 + lane < E;
+    for (int64_t e0 = warp * per_warp; e0 < E; e0 += n_warps * per_warp) {
+        const bool have = lane < per_warp && e0 + lane < E;
         const uint32_t e = (uint32_t)(have ? e0 + lane : 0);
         int64_t my_in[KTB_ROWS_MAX_IN];
         int64_t my_dst = -1;
@@ -181,7 +185,7 @@ __global__ void __launch_bounds__(256) ktb_rows_program_kernel(const __grid_cons
             const uint32_t t = e / (uint32_t)a.tile_rows;
             my_dst = sc_row_addr(a.arena, a.out, t, (int)(e - t * (uint32_t)a.tile_rows), st);
         }
-        const int cnt = (int)((E - e0) < 32 ? (E - e0) : 32);
+        const int cnt = (int)((E - e0) < per_warp ? (E - e0) : per_warp);
         for (int b0 = 0; b0 < cnt; b0 += G) {
             int64_t in_addr[G][KTB_ROWS_MAX_IN], dst[G];
             bool ok[G];
@@ -631,11 +635,13 @@ extern "C" int ktb_launch_rows_program(ktb_ctx* ctx, const ktb_rows_args* args) 
     if (rc) return rc;
     if (a.n_tiles == 0) return KTB_OK;
     const int64_t E = a.n_tiles * a.tile_rows;
-    int64_t blocks = (E + 7) / 8;
-    const int64_t cap = (int64_t)ctx->sm_count * 16;
+    const int64_t cap = (int64_t)ctx->sm_count * 16;                 // CTAs of 8 warps
+    int per_warp = (int)((E + cap * 8 - 1) / (cap * 8));             // entries a warp takes when all warps are used
+    per_warp = per_warp >= 32 ? 32 : (per_warp + 3) / 4 * 4;
+    int64_t blocks = (E + (int64_t)per_warp * 8 - 1) / ((int64_t)per_warp * 8);
     if (blocks > cap) blocks = cap;
     const size_t vsmem = (size_t)KTB_VM_REGS * 256 * sizeof(float4);
-#define KTB_RP(V, P) ktb_rows_program_kernel<V, P><<<(unsigned)blocks, 256, vsmem, ctx->stream>>>(a, ctx->dev_status)
+#define KTB_RP(V, P) ktb_rows_program_kernel<V, P><<<(unsigned)blocks, 256, vsmem, ctx->stream>>>(a, per_warp, ctx->dev_status)
     switch (sc_classify(a) * 2 + (a.vector_ok ? 1 : 0)) {
         case SC_PROG_COPY * 2 + 1: KTB_RP(4, SC_PROG_COPY); break;
         case SC_PROG_COPY * 2: KTB_RP(1, SC_PROG_COPY); break;

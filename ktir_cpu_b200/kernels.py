@@ -301,6 +301,36 @@ def tiled_matmul(M: int = 4096, N: int = 4096, K: int = 4096, bm: int = 64, bn: 
     return s
 
 
+def blocked_gather(src_shape: Sequence[int], n_selected: Sequence[int], dtype: str = "f16") -> str:
+    """out[e0, .., m, n, ..] = src[idx0[e0], .., m, n, ..]: the leading ``len(n_selected)`` dims of
+    ``src`` are looked up through index vectors (``idx0``, ``idx1``, ...), the rest taken whole — the
+    block gathers of the reference's indirect-load benchmark (expert weights ``X[IDX[e], m, n]``, KV
+    pages ``cache[BT[p], h, t, d]``, page/token pairs ``X[P[p], T[t], h]``, expert/head pairs
+    ``X[E[e], H[h], m, n]``; benchmarks/bench_utils.py:40-170).  One core loads the whole result as one
+    indirect tile and stores it."""
+    n_ind = len(n_selected)
+    rshape = list(n_selected) + list(src_shape[n_ind:])
+    nd = len(src_shape)
+    names = [f"%v{i}" for i in range(nd)]
+    subs = [f"ind(%idx{i}[{names[i]}])" for i in range(n_ind)] + [f"({names[i]})" for i in range(n_ind, nd)]
+    args = ", ".join(["%src_ptr: index"] + [f"%idx{i}_ptr: index" for i in range(n_ind)] + ["%out_ptr: index"])
+    t, at = f"tensor<{_xs(rshape, dtype)}>", f"!ktdp.access_tile<{_xs(rshape, 'index')}>"
+    s = (f"module {{\n  func.func @blocked_gather({args}) attributes {{grid = [1]}} {{\n"
+         f"    %c0 = arith.constant 0 : index\n")
+    s += view("src", "src_ptr", list(src_shape), dtype) + view("out", "out_ptr", rshape, dtype)
+    for i in range(n_ind):
+        s += view(f"idx{i}", f"idx{i}_ptr", [n_selected[i]], "i32")
+    idx_types = ", ".join(f"memref<{n_selected[i]}xi32>" for i in range(n_ind))
+    s += (f"    %tile = ktdp.construct_indirect_access_tile\n"
+          f"        intermediate_variables({', '.join(names)})\n"
+          f"        %src[{', '.join(subs)}] {{\n"
+          f"      variables_space_set = {_box(rshape)},\n      variables_space_order = {_ident(nd)}\n"
+          f"    }} : memref<{_xs(src_shape, dtype)}>, {idx_types} -> {at}\n")
+    s += tile("dst", "out", ["%c0"] * nd, rshape, rshape, dtype)
+    s += f"    %x = ktdp.load %tile : {at} -> {t}\n    ktdp.store %x, %dst : {t}, {at}\n    return\n  }}\n}}\n"
+    return s
+
+
 def gather_rows_transposed(n_table_rows: int = 32, cols: int = 16, n_idx: int = 64, tile_rows: int = 8,
                            cores: int = 2, idx_dtype: str = "i32") -> str:
     """out[:, e] = table[idx[e], :] — the indirect tile enumerates its (row, column) variable space in

@@ -100,15 +100,28 @@ class RowForm:
                 and np.array_equal(self.idx_off, o.idx_off))
 
 
-def _rc_dims(shape) -> Tuple[Optional[int], Optional[int]]:
+def _rc_dims(shape, unit_stride=None) -> Tuple[Optional[int], List[int]]:
+    """(row dim, column dims) of a tile seen as rows of contiguous columns.  ``unit_stride[d]`` is the
+    element stride dim ``d`` walks with (None: unknown, e.g. it feeds an index lookup): trailing dims
+    whose strides chain up (1, n_last, n_last * n_prev, ...) are one run of columns, so a block
+    gather ``X[IDX[e], m, n]`` is rows of ``m * n`` contiguous elements."""
     big = [i for i, s in enumerate(shape) if s > 1]
-    if len(big) > 2:
-        raise Unsupported(f"indirect tile of shape {tuple(shape)} (more than two non-unit dims)")
     if not big:
-        return None, None
+        return None, []
+    cols = [big[-1]]
+    if unit_stride is not None:
+        expect = shape[big[-1]] * (unit_stride[big[-1]] or 0)
+        for d in reversed(big[:-1]):
+            if len(big) - len(cols) <= 1 or unit_stride[big[-1]] != 1 or unit_stride[d] != expect:
+                break
+            cols.insert(0, d)
+            expect *= shape[d]
+    rest = [d for d in big if d not in cols]
+    if len(rest) > 1:
+        raise Unsupported(f"indirect tile of shape {tuple(shape)} (more than two non-unit dims)")
     if len(big) == 1:
-        return None, big[0]
-    return big[0], big[1]
+        return None, cols
+    return (rest[0] if rest else None), cols
 
 
 def row_form(acc, axes, sel: np.ndarray) -> RowForm:
@@ -120,11 +133,12 @@ def row_form(acc, axes, sel: np.ndarray) -> RowForm:
     if isinstance(acc, Access):
         if acc.coords is not None:
             raise Unsupported("coordinate-set access tile next to an indirect one")
-        rd, cd = _rc_dims(acc.shape)
-        if cd is not None and acc.strides[cd] != 1:
+        rd, cds = _rc_dims(acc.shape, list(acc.strides))
+        if cds and acc.strides[cds[-1]] != 1:
             raise Unsupported("row operand whose columns are not unit-stride")
         return RowForm(False, acc.view.dtype, per_tile(acc.off), acc.strides[rd] if rd is not None else 0,
-                       rows=acc.shape[rd] if rd is not None else 1, cols=acc.shape[cd] if cd is not None else 1)
+                       rows=acc.shape[rd] if rd is not None else 1,
+                       cols=int(np.prod([acc.shape[d] for d in cds], dtype=np.int64)) if cds else 1)
 
     ia: IndirectAccess = acc
     if ia.order is not None and not ia.order.is_identity():
@@ -135,11 +149,27 @@ def row_form(acc, axes, sel: np.ndarray) -> RowForm:
     lo, hi = box
     ext = [h - l for l, h in zip(lo, hi)]
     nv = len(ext)
-    rd, cd = _rc_dims(ext)
+    # element stride each variable walks the parent view with through the direct subscripts; a variable
+    # that feeds an index lookup has none
+    walk: List[Optional[int]] = [0] * nv
+    for sub, stride in zip(ia.subs, ia.view.strides):
+        if sub["kind"] == "direct":
+            c, _ = _lin(sub["expr"], nv, ia.ssa)
+            for i, ci in enumerate(c):
+                if walk[i] is not None:
+                    walk[i] += ci * stride
+        else:
+            for e in sub["exprs"]:
+                c, _ = _lin(e, nv, ia.ssa)
+                for i, ci in enumerate(c):
+                    if ci:
+                        walk[i] = None
+    rd, cds = _rc_dims(ext, walk)
+    cd = cds[-1] if cds else None
     base = ia.view.base
     pos_stride, col_stride = 0, 0
     form = RowForm(True, ia.view.dtype, None, 0, rows=ext[rd] if rd is not None else 1,
-                   cols=ext[cd] if cd is not None else 1)
+                   cols=int(np.prod([ext[d] for d in cds], dtype=np.int64)) if cds else 1)
     n_ind = 0
     for sub, stride in zip(ia.subs, ia.view.strides):
         if sub["kind"] == "direct":
@@ -150,7 +180,7 @@ def row_form(acc, axes, sel: np.ndarray) -> RowForm:
                 pos_stride += c[rd] * stride
             if cd is not None:
                 col_stride += c[cd] * stride
-            if any(ci for i, ci in enumerate(c) if i not in (rd, cd) and ext[i] > 1):
+            if any(ci for i, ci in enumerate(c) if i != rd and i not in cds and ext[i] > 1):
                 raise Unsupported("indirect tile subscript over an unexpected variable")
         else:
             n_ind += 1
@@ -162,7 +192,7 @@ def row_form(acc, axes, sel: np.ndarray) -> RowForm:
                 c, b = _lin(e, nv, ia.ssa)
                 b = iv_bin(lambda x, y: x + y, b, sum(ci * l for ci, l in zip(c, lo)))
                 ioff = iv_bin(lambda x, y: x + y, ioff, iv_bin(lambda x, y: x * y, b, s))
-                if cd is not None and c[cd]:
+                if any(c[d] for d in cds):
                     raise Unsupported("index lookup that varies along the tile's columns")
                 if rd is not None:
                     istride += c[rd] * s
@@ -194,6 +224,21 @@ class RowsStatement(Statement):
         for f in forms[:-1]:
             if (f.rows, f.cols) != (out.rows, out.cols):
                 raise Unsupported("row statement operands with different tile shapes")
+        if not self.ordered and out.cols >= 512 and n_tiles * out.rows < 65536:
+            # few, very long rows (a block gather of whole expert matrices or KV pages): the kernel gives a
+            # warp 32 rows to move one after the other, so each row is cut into short column segments that
+            # become tiles of their own — same index look-ups, bases moved along by the segment
+            seg = next((c for c in range(256, 7, -8) if out.cols % c == 0), None)
+            if seg is not None:
+                nseg = out.cols // seg
+                shift = np.arange(nseg, dtype=np.int64) * seg
+                for f in forms:
+                    f.base = (f.base[:, None] + shift[None, :]).reshape(-1)
+                    if f.idx_off is not None:
+                        f.idx_off = np.repeat(f.idx_off, nseg)
+                    f.cols = seg
+                sel, cores = np.repeat(sel, nseg), np.repeat(cores, nseg)
+                n_tiles *= nseg
         self.args = a = R.RowsArgs()
         a.n_tiles, a.tile_rows, a.cols, a.n_in = n_tiles, out.rows, out.cols, len(forms) - 1
         a.program = self.program
