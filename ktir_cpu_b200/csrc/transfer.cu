@@ -7,7 +7,6 @@
 // obligations — the device gets the data, the caller gets a fresh array — are met by ONE host
 // copy: caller array -> page-locked result array, which is both the array handed back and the
 // source of the DMA.  Upload of chunk i+1, kernels of chunk i and read-back of chunk i-1 overlap.
-#include <algorithm>
 #include <condition_variable>
 #include <deque>
 #include <functional>
@@ -351,21 +350,6 @@ int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, in
     PIECE = PIECE < PIECE_MIN ? PIECE_MIN : PIECE > PIECE_MAX ? PIECE_MAX : (PIECE + 4095) & ~(size_t)4095;
     std::vector<Piece> pieces;
     std::vector<int> left(n_chunks, 0);
-    // A tensor that only goes up and whose caller array is itself page-locked is uploaded straight
-    // from the caller's memory: its copy into the result array (what the call returns for it) then
-    // runs beside the transfers instead of in front of them.  A tensor that also comes back keeps the
-    // order copy -> upload -> kernel -> read-back, since the read-back lands in the same result array.
-    std::vector<char> direct(n_tensors, 0);
-    for (int t = 0; t < n_tensors; ++t) {
-        if (!src[t] || src[t] == pinned[t]) continue;
-        cudaPointerAttributes at;
-        if (cudaPointerGetAttributes(&at, src[t]) == cudaSuccess && at.type == cudaMemoryTypeHost) direct[t] = 1;
-        else cudaGetLastError();
-    }
-    for (int c = 0; c < n_chunks; ++c)
-        for (int k = 0; k < chunks[c].n_down; ++k)
-            if (chunks[c].down[k].tensor >= 0 && chunks[c].down[k].tensor < n_tensors) direct[chunks[c].down[k].tensor] = 0;
-    constexpr int LOOSE = -1;                 // a piece no chunk waits for
     for (int c = 0; c < n_chunks; ++c) {
         for (int k = 0; k < chunks[c].n_up; ++k) {
             const ktb_region& r = chunks[c].up[k];
@@ -373,24 +357,20 @@ int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, in
             char* dst = static_cast<char*>(pinned[r.tensor]) + r.rel;
             const char* from = static_cast<const char*>(src[r.tensor]) + r.rel;
             if (dst == from || r.width == 0 || r.height == 0) continue;
-            const int owner = direct[r.tensor] ? LOOSE : c;
             if (r.height == 1 || r.pitch == r.width) {
                 const size_t total = r.width * r.height;
                 for (size_t off = 0; off < total; off += PIECE)
-                    pieces.push_back({dst + off, from + off, off + PIECE <= total ? PIECE : total - off, 1, 0, owner});
+                    pieces.push_back({dst + off, from + off, off + PIECE <= total ? PIECE : total - off, 1, 0, c});
             } else {
                 size_t band = PIECE / r.width;
                 if (band < 1) band = 1;
                 for (size_t r0 = 0; r0 < r.height; r0 += band)
                     pieces.push_back({dst + r0 * r.pitch, from + r0 * r.pitch, (size_t)r.width,
-                                      r0 + band <= r.height ? band : (size_t)r.height - r0, (size_t)r.pitch, owner});
+                                      r0 + band <= r.height ? band : (size_t)r.height - r0, (size_t)r.pitch, c});
             }
         }
     }
-    // the pieces somebody waits for go first
-    std::stable_partition(pieces.begin(), pieces.end(), [](const Piece& p) { return p.chunk >= 0; });
-    for (const Piece& p : pieces)
-        if (p.chunk >= 0) ++left[p.chunk];
+    for (const Piece& p : pieces) ++left[p.chunk];
 
     std::mutex mu;
     std::condition_variable cv;
@@ -401,7 +381,6 @@ int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, in
             if (p.rows == 1) stream_copy(p.dst, p.src, p.len);
             else
                 for (size_t r = 0; r < p.rows; ++r) stream_copy(p.dst + r * p.pitch, p.src + r * p.pitch, p.len);
-            if (p.chunk < 0) return;
             std::lock_guard<std::mutex> lk(mu);
             if (--left[p.chunk] == 0) cv.notify_all();
         });
@@ -416,8 +395,8 @@ int ktb_run_pipeline(ktb_ctx* ctx, void* arena, const ktb_pipe_chunk* chunks, in
         for (int k = 0; k < ch.n_up && rc == KTB_OK; ++k) {
             const ktb_region& r = ch.up[k];
             if (r.dev_off == KTB_NO_DEVICE) continue;         // the caller's copy only
-            const char* host = direct[r.tensor] ? static_cast<const char*>(src[r.tensor]) : static_cast<char*>(pinned[r.tensor]);
-            rc = copy_region(ctx, base + r.dev_off, host + r.rel, r, cudaMemcpyHostToDevice, ctx->lane[0]);
+            rc = copy_region(ctx, base + r.dev_off, static_cast<char*>(pinned[r.tensor]) + r.rel, r,
+                             cudaMemcpyHostToDevice, ctx->lane[0]);
         }
         if (rc == KTB_OK && ch.n_up > 0) rc = fence(ctx, 1, 0);
         if (rc == KTB_OK && ch.launch) rc = ch.launch(ctx, ch.launch_args);
