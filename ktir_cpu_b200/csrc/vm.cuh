@@ -60,7 +60,7 @@ static __device__ __forceinline__ void ktb_load_vec(const void* base, int64_t el
     if (dtype == KTB_F16) {
         const __half* p = reinterpret_cast<const __half*>(base) + elem_off;
         if (V == 8) {
-            uint4 raw = *reinterpret_cast<const uint4*>(p);
+            uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));      // touched once: do not keep it in L2
             const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -75,8 +75,8 @@ static __device__ __forceinline__ void ktb_load_vec(const void* base, int64_t el
     } else {
         const float* p = reinterpret_cast<const float*>(base) + elem_off;
         if (V == 8) {
-            float4 a = *reinterpret_cast<const float4*>(p);
-            float4 b = *reinterpret_cast<const float4*>(p + 4);
+            float4 a = __ldcs(reinterpret_cast<const float4*>(p));
+            float4 b = __ldcs(reinterpret_cast<const float4*>(p + 4));
             x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
             x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
         } else {
@@ -95,7 +95,7 @@ static __device__ __forceinline__ void ktb_store_vec(void* base, int64_t elem_of
             __half2* h = reinterpret_cast<__half2*>(&raw);
 #pragma unroll
             for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(x[2 * i], x[2 * i + 1]);
-            *reinterpret_cast<uint4*>(p) = raw;
+            __stcs(reinterpret_cast<uint4*>(p), raw);
         } else {
 #pragma unroll
             for (int i = 0; i < V; ++i) p[i] = __float2half_rn(x[i]);
@@ -103,8 +103,8 @@ static __device__ __forceinline__ void ktb_store_vec(void* base, int64_t elem_of
     } else {
         float* p = reinterpret_cast<float*>(base) + elem_off;
         if (V == 8) {
-            *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
-            *reinterpret_cast<float4*>(p + 4) = make_float4(x[4], x[5], x[6], x[7]);
+            __stcs(reinterpret_cast<float4*>(p), make_float4(x[0], x[1], x[2], x[3]));
+            __stcs(reinterpret_cast<float4*>(p + 4), make_float4(x[4], x[5], x[6], x[7]));
         } else {
 #pragma unroll
             for (int i = 0; i < V; ++i) p[i] = x[i];
