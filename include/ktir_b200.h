@@ -209,6 +209,8 @@ int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args);
  * operand; entry (t, pos) of an operand lives at element offset
  *     base[t] + IDX[idx_off[t] + pos * idx_stride] * idx_mult + pos * pos_stride   (indirect)
  *     base[t] + pos * pos_stride                                                    (direct)
+ * and an input with two index subscripts (X[P[p], T[t], :]) adds a second term
+ * IDX2[idx2_off[t] + pos * idx2_stride] * idx2_mult.
  * Replaces MemoryOps.indirect_load / indirect_store and the per-point index
  * resolution behind them (ktir_cpu/ops/memory_ops.py:330-386, 488-576, 867-964) plus
  * the fancy-index gather/scatter of the memory simulator (ktir_cpu/memory.py:243-251,
@@ -216,7 +218,7 @@ int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args);
  * index sets ktb_status.negative_index. */
 #define KTB_ROWS_MAX_IN 3
 typedef struct {
-    int32_t indirect;             /* 1: the row address uses an index lookup */
+    int32_t indirect;             /* number of index lookups in the row address: 0, 1, or (inputs only) 2 */
     int32_t dtype;                /* KTB_F16 / KTB_F32 */
     int32_t idx_dtype;            /* KTB_I32 / KTB_I64 */
     int32_t alias_dst;            /* inputs only: 1 = reads the destination row (read-modify-write) */
@@ -226,6 +228,11 @@ typedef struct {
     int64_t idx_mult;             /* data elements per unit of index value */
     int64_t pos_stride;           /* data elements between consecutive tile rows (direct part) */
     int64_t lo, hi;               /* allocation bounds in data elements */
+    const int64_t* dev_idx2_off;  /* second lookup (indirect == 2): as dev_idx_off / idx_stride / idx_mult */
+    int64_t idx2_stride;
+    int64_t idx2_mult;
+    int32_t idx2_dtype;           /* KTB_I32 / KTB_I64 */
+    int32_t reserved;
 } ktb_row_operand;
 
 typedef struct {

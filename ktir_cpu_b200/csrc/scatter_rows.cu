@@ -36,6 +36,14 @@ static __device__ __forceinline__ int64_t sc_row_addr(const void* arena, const k
             return -1;
         }
         a += iv * op.idx_mult;
+        if (op.indirect > 1) {
+            const int64_t jv = sc_read_index(arena, op.idx2_dtype, op.dev_idx2_off[t] + (int64_t)pos * op.idx2_stride);
+            if (jv < 0) {
+                if (atomicExch(&st->negative_index, 1) == 0) st->bad_index_value = (int32_t)jv;
+                return -1;
+            }
+            a += jv * op.idx2_mult;
+        }
     }
     return a;
 }
@@ -622,6 +630,10 @@ static int check_rows_args(ktb_ctx* ctx, const ktb_rows_args& a, const char* who
         if (op.dtype != KTB_F16 && op.dtype != KTB_F32) return ktb_fail(ctx, KTB_E_UNSUPPORTED, who, "row dtype must be f16 or f32");
         if (op.indirect && op.idx_dtype != KTB_I32 && op.idx_dtype != KTB_I64)
             return ktb_fail(ctx, KTB_E_UNSUPPORTED, who, "index dtype must be i32 or i64");
+        if (op.indirect < 0 || op.indirect > (k < a.n_in ? 2 : 1))
+            return ktb_fail(ctx, KTB_E_UNSUPPORTED, who, "an input takes at most two index lookups, the destination one");
+        if (op.indirect > 1 && (!op.dev_idx2_off || (op.idx2_dtype != KTB_I32 && op.idx2_dtype != KTB_I64)))
+            return ktb_fail(ctx, KTB_E_ARG, who, "second index lookup needs offsets and an i32 or i64 dtype");
     }
     if (a.tile_rows <= 0 || a.cols <= 0 || a.n_tiles < 0) return ktb_fail(ctx, KTB_E_ARG, who, "bad tile geometry");
     if (a.n_tiles * (int64_t)a.tile_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, who, "too many entries");

@@ -92,8 +92,14 @@ class RowForm:
     idx_mult: int = 0
     rows: int = 1
     cols: int = 1
+    idx2_dtype: str = "i32"          # second index lookup of a two-subscript gather (joint_forms only)
+    idx2_off: Optional[np.ndarray] = None
+    idx2_stride: int = 0
+    idx2_mult: int = 0
 
     def same_rows(self, o: "RowForm") -> bool:
+        if self.idx2_off is not None or o.idx2_off is not None:
+            return False
         return (self.indirect and o.indirect and self.dtype == o.dtype and self.pos_stride == o.pos_stride
                 and self.idx_dtype == o.idx_dtype and self.idx_stride == o.idx_stride
                 and self.idx_mult == o.idx_mult and np.array_equal(self.base, o.base)
@@ -205,6 +211,91 @@ def row_form(acc, axes, sel: np.ndarray) -> RowForm:
     return form
 
 
+def _walks(acc):
+    """An operand as (dims, base, direct walk, lookups): ``dims`` the extent of each tile dimension,
+    ``base`` the element offset of the tile's first element (an integer value over the iteration
+    axes), ``direct walk[d]`` the elements one step along dim ``d`` moves through the direct
+    subscripts, and per index lookup ``(index dtype, index offset of the first element, index
+    elements one step along each dim moves, data elements per unit of index value)``."""
+    if isinstance(acc, Access):
+        if acc.coords is not None:
+            raise Unsupported("coordinate-set access tile next to an indirect one")
+        return list(acc.shape), acc.off, [int(s) for s in acc.strides], []
+    ia: IndirectAccess = acc
+    if ia.order is not None and not ia.order.is_identity():
+        raise Unsupported("indirect access tile with a permuted variables_space_order")
+    box = ia.aset.box()
+    if box is None:
+        raise Unsupported("indirect access tile over a non-rectangular variable space")
+    lo, hi = box
+    nv = len(lo)
+    add = lambda x, y: iv_bin(lambda a, b: a + b, x, y)
+    mul = lambda x, y: iv_bin(lambda a, b: a * b, x, y)
+    base, walk, lookups = ia.view.base, [0] * nv, []
+    for sub, stride in zip(ia.subs, ia.view.strides):
+        if sub["kind"] == "direct":
+            c, b = _lin(sub["expr"], nv, ia.ssa)
+            base = add(base, mul(add(b, sum(ci * l for ci, l in zip(c, lo))), stride))
+            walk = [w + ci * stride for w, ci in zip(walk, c)]
+        else:
+            iv = ia.index_views[sub["view"]]
+            ioff, iwalk = iv.base, [0] * nv
+            for e, s_ in zip(sub["exprs"], iv.strides):
+                c, b = _lin(e, nv, ia.ssa)
+                ioff = add(ioff, mul(add(b, sum(ci * l for ci, l in zip(c, lo))), s_))
+                iwalk = [w + ci * s_ for w, ci in zip(iwalk, c)]
+            lookups.append((iv.dtype, ioff, iwalk, int(stride)))
+    return [h - l for l, h in zip(lo, hi)], base, walk, lookups
+
+
+def joint_forms(accs, axes, sel: np.ndarray) -> Tuple[List[RowForm], int]:
+    """Row addressing of all operands of a statement under ONE split of the tile's dimensions:
+    trailing dims every operand walks contiguously are the columns, the dim before them the rows,
+    and the dims before that unroll into tiles of their own (``n_outer`` per iteration point) — so
+    ``out[p, t, :] = X[P[p], T[t], :]`` is ``len(P)`` tiles of ``len(T)`` rows with one lookup fixed per
+    tile and one walking the rows.  An operand takes up to two index lookups."""
+    ops = [_walks(a) for a in accs]
+    bigs = [[i for i, n in enumerate(d) if n > 1] for d, _, _, _ in ops]
+    dims = [ops[0][0][i] for i in bigs[0]]
+    if not dims or any([d[i] for i in b] != dims for (d, _, _, _), b in zip(ops, bigs)):
+        raise Unsupported("row statement operands with different tile shapes")
+    n = len(dims)
+
+    def contiguous(j, run):        # dim j (position among the non-unit dims) continues a run of `run` elements
+        return all(w[b[j]] == run and not any(lw[b[j]] for _, _, lw, _ in lk)
+                   for (_, _, w, lk), b in zip(ops, bigs))
+
+    if not contiguous(n - 1, 1):
+        raise Unsupported("indirect tile whose columns are not unit-stride")
+    k, run = 1, dims[-1]
+    while n - k > 1 and contiguous(n - k - 1, run):
+        k, run = k + 1, run * dims[n - k - 1]
+    rd = n - k - 1 if n - k >= 1 else None
+    outer = list(range(rd)) if rd is not None else []
+    n_outer = int(np.prod([dims[j] for j in outer], dtype=np.int64)) if outer else 1
+    coords = (np.indices([dims[j] for j in outer]).reshape(len(outer), -1).astype(np.int64)
+              if outer else np.zeros((0, 1), np.int64))
+
+    def per_tile(v, steps) -> np.ndarray:
+        t = np.ascontiguousarray(iv_full(v, axes).reshape(-1)[sel]).astype(np.int64)
+        return (t[:, None] + (np.asarray(steps, np.int64) @ coords)[None, :]).reshape(-1)
+
+    forms = []
+    for (d, base, walk, lookups), b, acc in zip(ops, bigs, accs):
+        if len(lookups) > 2:
+            raise Unsupported("indirect access tile with more than two indirect dimensions")
+        f = RowForm(bool(lookups), acc.view.dtype, per_tile(base, [walk[b[j]] for j in outer]),
+                    walk[b[rd]] if rd is not None else 0, rows=dims[rd] if rd is not None else 1, cols=run)
+        for i, (dt, ioff, iwalk, mult) in enumerate(lookups):
+            off, st = per_tile(ioff, [iwalk[b[j]] for j in outer]), iwalk[b[rd]] if rd is not None else 0
+            if i == 0:
+                f.idx_dtype, f.idx_off, f.idx_stride, f.idx_mult = dt, off, st, mult
+            else:
+                f.idx2_dtype, f.idx2_off, f.idx2_stride, f.idx2_mult = dt, off, st, mult
+        forms.append(f)
+    return forms, n_outer
+
+
 class RowsStatement(Statement):
     """rows_program (direct destination) or ordered scatter_rows (indirect destination)."""
 
@@ -219,11 +310,18 @@ class RowsStatement(Statement):
         sel, cores = _points(store)
         n_tiles = len(sel)
         accs = [n.attrs["access"] for n in pb.inputs] + [store.target]
-        forms = [row_form(a, store.axes, sel) for a in accs]
-        out = forms[-1]
-        for f in forms[:-1]:
-            if (f.rows, f.cols) != (out.rows, out.cols):
+        try:
+            forms = [row_form(a, store.axes, sel) for a in accs]
+            if any((f.rows, f.cols) != (forms[-1].rows, forms[-1].cols) for f in forms[:-1]):
                 raise Unsupported("row statement operands with different tile shapes")
+        except Unsupported:
+            # tiles of more than [rows, columns], or two index subscripts: one split for all operands
+            forms, n_outer = joint_forms(accs, store.axes, sel)
+            sel, cores = np.repeat(sel, n_outer), np.repeat(cores, n_outer)
+            n_tiles *= n_outer
+        out = forms[-1]
+        if out.idx2_off is not None:
+            raise Unsupported("indirect store through two index subscripts")
         if not self.ordered and out.cols >= 512 and n_tiles * out.rows < 65536:
             # few, very long rows (a block gather of whole expert matrices or KV pages): the kernel gives a
             # warp 32 rows to move one after the other, so each row is cut into short column segments that
@@ -236,6 +334,8 @@ class RowsStatement(Statement):
                     f.base = (f.base[:, None] + shift[None, :]).reshape(-1)
                     if f.idx_off is not None:
                         f.idx_off = np.repeat(f.idx_off, nseg)
+                    if f.idx2_off is not None:
+                        f.idx2_off = np.repeat(f.idx2_off, nseg)
                     f.cols = seg
                 sel, cores = np.repeat(sel, nseg), np.repeat(cores, nseg)
                 n_tiles *= nseg
@@ -276,6 +376,19 @@ class RowsStatement(Statement):
                 self.device_arrays.append(p)
                 op.dev_idx_off = p
                 vec = vec and f.idx_mult % 4 == 0
+                if f.idx2_off is not None:
+                    if n_tiles:
+                        ia = arena.check_range(int(f.idx2_off.min()),
+                                               int(f.idx2_off.max()) + (f.rows - 1) * f.idx2_stride + 1,
+                                               f.idx2_dtype, "Read from")
+                        self.fps.append(Footprint(np.array([ia.byte_lo]), np.array([ia.byte_hi]),
+                                                  np.array([-1]), np.array([-1]), False, stmt_id))
+                    op.indirect = 2
+                    op.idx2_dtype, op.idx2_stride, op.idx2_mult = R.DTYPE_CODE[f.idx2_dtype], f.idx2_stride, f.idx2_mult
+                    p = dev.upload(f.idx2_off)
+                    self.device_arrays.append(p)
+                    op.dev_idx2_off = p
+                    vec = vec and f.idx2_mult % 4 == 0
             else:
                 if n_tiles:
                     arena.check_range(int(f.base.min()), int(f.base.max()) + (f.rows - 1) * f.pos_stride + f.cols,

@@ -62,7 +62,9 @@ class RowOperand(C.Structure):
     _fields_ = [("indirect", C.c_int32), ("dtype", C.c_int32), ("idx_dtype", C.c_int32),
                 ("alias_dst", C.c_int32), ("dev_base", C.c_void_p), ("dev_idx_off", C.c_void_p),
                 ("idx_stride", C.c_int64), ("idx_mult", C.c_int64), ("pos_stride", C.c_int64),
-                ("lo", C.c_int64), ("hi", C.c_int64)]
+                ("lo", C.c_int64), ("hi", C.c_int64), ("dev_idx2_off", C.c_void_p),
+                ("idx2_stride", C.c_int64), ("idx2_mult", C.c_int64), ("idx2_dtype", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 class RowsArgs(C.Structure):

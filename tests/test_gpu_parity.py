@@ -554,11 +554,14 @@ def test_memory_seeded_at_fixed_addresses(build_lib):
 
 
 @pytest.mark.parametrize("shape,sel,kind", [((64, 96, 128), (5,), "rows_program"), ((32, 4, 64, 64), (3,), "rows_program"),
-                                            ((16, 40, 8), (9,), "rows_program"), ((40, 24, 64), (3, 5), "generic")])
+                                            ((16, 40, 8), (9,), "rows_program"), ((40, 24, 64), (3, 5), "rows_program"),
+                                            ((12, 10, 6, 32), (4, 3), "rows_program"), ((6, 5, 2048), (3, 2), "rows_program"),
+                                            ((6, 5, 7), (4, 3), "rows_program"), ((8, 6, 4, 16), (3, 2, 2), "generic")])
 def test_block_gathers_match_numpy(shape, sel, kind, build_lib):
     """The block gathers of the reference's indirect-load benchmark at small sizes: leading dims looked up
-    through index vectors, the rest taken whole.  One index: the fused row kernel (trailing dims folded into
-    columns, long rows cut into segments); two: the step-by-step path."""
+    through index vectors, the rest taken whole.  One or two indices: the fused row kernel (trailing dims
+    folded into columns, long rows cut into segments, the first of two lookups fixed per tile); three: the
+    step-by-step path."""
     rng = np.random.default_rng(21)
     rshape = tuple(sel) + tuple(shape[len(sel):])
     kw = {"src_ptr": rng.standard_normal(shape).astype(np.float16)}
