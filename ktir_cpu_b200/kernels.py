@@ -1112,3 +1112,58 @@ def gather_elements(n_rows: int = 32, n_cols: int = 16, n_src: int = 64) -> str:
     s += (f"    %vals = ktdp.load %g : {at} -> {t}\n"
           f"    ktdp.store %vals, %o_tile : {t}, {at}\n    return\n  }}\n}}\n")
     return s
+
+
+def update_in_place(n_rows: int = 64, cols: int = 64, tile_rows: int = 8, cores: int = 2, loop: bool = True,
+                    reuse_new: bool = False) -> str:
+    """x = 2 * x in place, old = the x from before: each tile is loaded ONCE, its double stored back
+    over it, and the loaded tile stored to ``old`` afterwards — so ``old`` holds the values from
+    before the first store although its own store comes second.  ``loop``: the tiles of a core in an
+    ``scf.for`` (both stores inside it), else one tile per core.  ``reuse_new``: ``old`` instead gets
+    ``loaded tile + tile loaded again after the first store`` (= 3 * x), which ties the second store
+    to memory both before and after the first."""
+    per_core = n_rows // cores
+    assert per_core * cores == n_rows and per_core % tile_rows == 0 and (loop or per_core == tile_rows)
+    t, at = f"tensor<{tile_rows}x{cols}xf16>", f"!ktdp.access_tile<{tile_rows}x{cols}xindex>"
+    s = (f"module {{\n  func.func @update_in_place(%x_ptr: index, %old_ptr: index) attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %pid = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %per_core = arith.constant {per_core} : index\n    %tile_rows = arith.constant {tile_rows} : index\n"
+         f"    %begin = arith.muli %pid, %per_core : index\n    %end = arith.addi %begin, %per_core : index\n")
+    s += view("x", "x_ptr", [n_rows, cols], "f16") + view("old", "old_ptr", [n_rows, cols], "f16")
+    ind = "      " if loop else "    "
+    row = "%r" if loop else "%begin"
+    if loop:
+        s += "    scf.for %r = %begin to %end step %tile_rows {\n"
+    s += tile("xt", "x", [row, "%c0"], [tile_rows, cols], [n_rows, cols], "f16", ind)
+    s += tile("ot", "old", [row, "%c0"], [tile_rows, cols], [n_rows, cols], "f16", ind)
+    s += (f"{ind}%a = ktdp.load %xt : {at} -> {t}\n{ind}%b = arith.addf %a, %a : {t}\n"
+          f"{ind}ktdp.store %b, %xt : {t}, {at}\n")
+    if reuse_new:
+        s += f"{ind}%n = ktdp.load %xt : {at} -> {t}\n{ind}%s = arith.addf %a, %n : {t}\n{ind}ktdp.store %s, %ot : {t}, {at}\n"
+    else:
+        s += f"{ind}ktdp.store %a, %ot : {t}, {at}\n"
+    if loop:
+        s += "      scf.yield\n    }\n"
+    return s + "    return\n  }\n}\n"
+
+
+def shifted_reuse(n_rows: int = 64, cols: int = 64, tile_rows: int = 8) -> str:
+    """One core, one ``scf.for`` over row tiles: tile ``i`` of ``b`` gets ``2 * a[i]``, then tile ``i``
+    of ``c`` gets tile ``i + 1`` of ``b`` — which the loop has not written yet, so ``c`` holds what
+    ``b`` held on entry (the last tile reads row tile 0 again, already doubled)."""
+    t, at = f"tensor<{tile_rows}x{cols}xf16>", f"!ktdp.access_tile<{tile_rows}x{cols}xindex>"
+    s = (f"module {{\n  func.func @shifted_reuse(%a_ptr: index, %b_ptr: index, %c_ptr: index) attributes {{grid = [1, 1]}} {{\n"
+         f"    %c0 = arith.constant 0 : index\n    %n = arith.constant {n_rows} : index\n"
+         f"    %tile_rows = arith.constant {tile_rows} : index\n")
+    for nm in "abc":
+        s += view(nm, f"{nm}_ptr", [n_rows, cols], "f16")
+    s += ("    scf.for %r = %c0 to %n step %tile_rows {\n"
+          "      %r1 = arith.addi %r, %tile_rows : index\n      %nx = arith.remui %r1, %n : index\n")
+    s += tile("at", "a", ["%r", "%c0"], [tile_rows, cols], [n_rows, cols], "f16", "      ")
+    s += tile("bt", "b", ["%r", "%c0"], [tile_rows, cols], [n_rows, cols], "f16", "      ")
+    s += tile("bn", "b", ["%nx", "%c0"], [tile_rows, cols], [n_rows, cols], "f16", "      ")
+    s += tile("ct", "c", ["%r", "%c0"], [tile_rows, cols], [n_rows, cols], "f16", "      ")
+    s += (f"      %x = ktdp.load %at : {at} -> {t}\n      %y = arith.addf %x, %x : {t}\n"
+          f"      ktdp.store %y, %bt : {t}, {at}\n      %z = ktdp.load %bn : {at} -> {t}\n"
+          f"      ktdp.store %z, %ct : {t}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s

@@ -725,6 +725,8 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
     """``row_shard = (rank, world)``: ordered scatters apply only the destination rows this rank owns.
     ``fused=False`` skips the fused kernels and runs every direct store step by step (the op-by-op
     form of the reference, ktir_cpu/interpreter.py:196-281) — a cross-check for the fused paths."""
+    from .order import program_order
+    stores = [stores[k] for k in program_order(stores, arena)]
     plan = Plan()
     for st in stores:
         sid = len(plan.statements)

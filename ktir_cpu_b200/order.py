@@ -1,0 +1,222 @@
+"""Program order of loads and stores on one core.
+
+The reference runs a core's operations one after another (ktir_cpu/interpreter.py:196-281,
+ktir_cpu/grid.py:595-613): a ``ktdp.load`` sees memory as it is at the load's position, whatever the
+tile is used for later.  The device plan runs one statement per ``ktdp.store`` — all points of the
+first store, then all points of the second, each statement reading its inputs when it runs.  The two
+orders give the same memory unless, on one core,
+
+* a tile is loaded BEFORE an earlier statement's store to the same bytes and used by a later
+  statement (the plan would read the new bytes, the reference the old ones), or
+* two statements inside the same ``scf.for`` touch the same bytes in different iterations and the
+  earlier statement's access belongs to the LATER iteration (the reference interleaves the
+  iterations, the plan does not).
+
+``program_order`` finds both on the traced stores.  The first is cured by launching the later statement
+first when nothing else ties the two (``x = load X; store f(x) -> X; store x -> Y`` runs as
+``store x -> Y; store f(x) -> X``); what no order of whole statements cures raises ``Unsupported``.
+Overlaps between different cores are the business of ``lower.check_hazards``.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import numpy as np
+
+from .dtypes import bytes_per_elem
+from .trace import Access, IndirectAccess, Node, Store, TableAccess, Unsupported, iv_full
+
+
+class _Runs:
+    """Byte intervals of one access at the active points of an iteration space, with the core and
+    the flat point index of each."""
+
+    def __init__(self, lo, hi, point, axes):
+        self.lo, self.hi, self.point, self.axes = lo, hi, point, tuple(axes)
+        inner = int(np.prod(self.axes[1:], dtype=np.int64)) if len(self.axes) > 1 else 1
+        self.core = point // max(inner, 1)
+
+    def key(self, common: int) -> np.ndarray:
+        """Trip indices of the first ``common`` loop axes, flattened (0 when there are none)."""
+        if not common or len(self.axes) < 1 + common:
+            return np.zeros(len(self.point), np.int64)
+        coords = np.unravel_index(self.point, self.axes)
+        return np.ravel_multi_index(coords[1:1 + common], self.axes[1:1 + common]).astype(np.int64)
+
+
+def _alloc_span(arena, view) -> Tuple[int, int]:
+    base = int(np.asarray(view.base).reshape(-1)[0]) * bytes_per_elem(view.dtype)
+    a = arena.find(base)
+    if a is None:
+        return 0, max((x.byte_hi for x in arena.allocs), default=1)
+    return a.byte_lo, a.byte_hi
+
+
+def _runs(acc, axes, active, arena) -> List[_Runs]:
+    n = int(np.prod(axes, dtype=np.int64))
+    point = np.arange(n, dtype=np.int64)
+    if active is not None and tuple(active.shape) == tuple(axes):
+        point = point[active.reshape(-1)]
+    if isinstance(acc, Access):
+        bpe = bytes_per_elem(acc.view.dtype)
+        off = iv_full(acc.off, tuple(axes)).reshape(-1)[point].astype(np.int64)
+        if acc.coords is not None:
+            rel = acc.coords.astype(np.int64) @ np.asarray(acc.view.strides, np.int64)
+            lo_rel, hi_rel = (int(rel.min()), int(rel.max())) if rel.size else (0, 0)
+        else:
+            steps = [(s - 1) * st for s, st in zip(acc.shape, acc.strides)]
+            lo_rel, hi_rel = sum(min(x, 0) for x in steps), sum(max(x, 0) for x in steps)
+        return [_Runs((off + lo_rel) * bpe, (off + hi_rel + 1) * bpe, point, axes)]
+    if isinstance(acc, TableAccess):
+        bpe = bytes_per_elem(acc.dtype)
+        tab = np.asarray(acc.addr).reshape(-1, acc.addr.shape[-1]) if acc.addr.ndim > 1 else np.asarray(acc.addr).reshape(1, -1)
+        if tab.shape[0] == n:
+            tab = tab[point]
+        else:                                          # one table for every point
+            tab = np.broadcast_to(tab[:1], (len(point), tab.shape[1]))
+        big = np.iinfo(np.int64).max
+        lo = np.where(tab >= 0, tab, big).min(axis=1) if tab.shape[1] else np.zeros(len(point), np.int64)
+        hi = tab.max(axis=1) if tab.shape[1] else np.full(len(point), -1)
+        keep = hi >= 0
+        return [_Runs(lo[keep] * bpe, (hi[keep] + 1) * bpe, point[keep], axes)]
+    if isinstance(acc, IndirectAccess):
+        out = []
+        for view in [acc.view] + list(acc.index_views.values()):
+            lo, hi = _alloc_span(arena, view)
+            out.append(_Runs(np.full(len(point), lo, np.int64), np.full(len(point), hi, np.int64), point, axes))
+        return out
+    return []
+
+
+def _loads(value: Node) -> List[Node]:
+    seen, out, stack = set(), [], [value]
+    while stack:
+        n = stack.pop()
+        if id(n) in seen:
+            continue
+        seen.add(id(n))
+        if n.kind in ("load", "iload", "tload"):
+            out.append(n)
+        stack.extend(a for a in n.args if isinstance(a, Node))
+        for v in n.attrs.values():                      # loop bodies keep their yields in attrs
+            if isinstance(v, Node):
+                stack.append(v)
+            elif isinstance(v, (list, tuple)):
+                stack.extend(x for x in v if isinstance(x, Node))
+    return out
+
+
+def _later_than(a: _Runs, ka: np.ndarray, b: _Runs, kb: np.ndarray, span: int, strict: bool) -> bool:
+    """True if some run of ``a`` overlaps a run of ``b`` on the same core with ``ka > kb``
+    (``strict``) or ``ka >= kb`` (not ``strict``)."""
+    if not len(a.lo) or not len(b.lo):
+        return False
+    alo, ahi = a.lo + a.core * span, a.hi + a.core * span
+    blo, bhi = b.lo + b.core * span, b.hi + b.core * span
+    if alo.min() >= bhi.max() or blo.min() >= ahi.max():
+        return False
+    order = np.argsort(alo, kind="stable")
+    alo, ahi, ka = alo[order], np.maximum.accumulate(ahi[order]), ka[order]
+    first = np.searchsorted(ahi, blo, side="right")      # runs before `first` end at or before b starts
+    last = np.searchsorted(alo, bhi, side="left")        # runs from `last` on start at or after b ends
+    has = last > first
+    if not has.any():
+        return False
+    # max of ka over [first, last) by a sparse table
+    levels = [ka]
+    w = 1
+    while 2 * w <= len(ka):
+        prev = levels[-1]
+        levels.append(np.maximum(prev[:len(prev) - w], prev[w:]))
+        w *= 2
+    f, l = first[has], last[has]
+    lg = np.floor(np.log2(np.maximum(l - f, 1))).astype(np.int64)
+    best = np.empty(len(f), np.int64)
+    for g in np.unique(lg):
+        m = lg == g
+        t = levels[int(g)]
+        best[m] = np.maximum(t[f[m]], t[l[m] - (1 << int(g))])
+    return bool((best > kb[has]).any() if strict else (best >= kb[has]).any())
+
+
+def program_order(stores: List[Store], arena) -> List[int]:
+    """The order to launch the stores' statements in (indices into ``stores``): program order unless a
+    statement has to move in front of an earlier one whose store would otherwise clobber a tile it
+    loaded first.  Raises ``Unsupported`` when no order of whole statements reproduces what a core of
+    the reference sees (see the module docstring)."""
+    if len(stores) < 2:
+        return list(range(len(stores)))
+    span = max((a.byte_hi for a in arena.allocs), default=0) + 1
+    writes = [_runs(st.target, st.axes, st.active, arena) for st in stores]
+    index_reads: List[List[_Runs]] = []
+    for st, w in zip(stores, writes):
+        # an indirect store reads its index tensors when it runs; only the parent view is written
+        index_reads.append(w[1:] if isinstance(st.target, IndirectAccess) else [])
+        if isinstance(st.target, IndirectAccess):
+            del w[1:]
+    reads: List[List[Tuple[_Runs, int, int]]] = []       # per store: (runs, stores traced before the load, loop depth of the load)
+    for j, st in enumerate(stores):
+        rs = []
+        for n in _loads(st.value):
+            own = tuple(n.attrs.get("axes", st.axes))
+            axes, active = (st.axes, st.active) if len(own) <= len(st.axes) else (own, None)
+            before = int(n.attrs.get("stores_before", j))
+            rs.extend((r, before, len(own) - 1) for r in _runs(n.attrs["access"], axes, active, arena))
+        rs.extend((r, j, len(st.axes) - 1) for r in index_reads[j])
+        reads.append(rs)
+    inverted = Unsupported("two statements inside one scf.for touch the same memory in different iterations, the "
+                           "earlier statement in the later iteration: the statements cannot run one after the other")
+    after = {j: set() for j in range(len(stores))}        # after[j]: statements that must run before j
+    for j in range(1, len(stores)):
+        B = stores[j]
+        for i in range(j):
+            A = stores[i]
+            common = 0
+            for x, y in zip(A.loop_path, B.loop_path):
+                if x != y:
+                    break
+                common += 1
+            fwd = bwd = False                              # A before B needed / B before A needed
+            for wa in writes[i]:
+                for rb, before, depth in reads[j]:
+                    # B's load against A's store.  Run after A, B sees every byte A wrote; the reference shows it
+                    # those written before the load: in an earlier iteration of the loops both sit in, or in
+                    # the same one if the load comes after A's store.
+                    c = min(common, depth)
+                    ka, kb = wa.key(c), rb.key(c)
+                    if _later_than(wa, ka, rb, kb, span, strict=True):
+                        raise inverted
+                    if before <= i:
+                        bwd = bwd or _later_than(wa, ka, rb, kb, span, strict=False)     # same iteration: stale
+                        fwd = fwd or (c > 0 and _later_than(rb, kb, wa, ka, span, strict=True))
+                    else:
+                        fwd = fwd or _later_than(rb, kb, wa, ka, span, strict=False)
+                for wb in writes[j]:
+                    ka, kb = wa.key(common), wb.key(common)
+                    if common and _later_than(wa, ka, wb, kb, span, strict=True):
+                        raise inverted
+                    fwd = fwd or _later_than(wb, kb, wa, ka, span, strict=False)       # B's bytes land last
+            for ra, _, depth in reads[i]:
+                c = min(common, depth)
+                for wb in writes[j]:
+                    ka, kb = ra.key(c), wb.key(c)
+                    if c and _later_than(ra, ka, wb, kb, span, strict=True):
+                        raise inverted
+                    fwd = fwd or _later_than(wb, kb, ra, ka, span, strict=False)       # A reads before B writes
+            if fwd and bwd:
+                raise Unsupported("a tile is loaded before an earlier store to the same memory and used after it, "
+                                  "by a statement that also depends on that store: the statements cannot run one "
+                                  "after the other")
+            if bwd:
+                after[i].add(j)
+            elif fwd:
+                after[j].add(i)
+    order, done = [], set()
+    while len(order) < len(stores):
+        ready = [k for k in range(len(stores)) if k not in done and after[k] <= done]
+        if not ready:
+            raise Unsupported("tiles loaded before earlier stores to the same memory and used after them tie the "
+                              "statements into a cycle: they cannot run one after the other")
+        order.append(ready[0])
+        done.add(ready[0])
+    return order

@@ -277,14 +277,14 @@ def _load(tr, op, scope):
         if at.order is not None and not at.order.is_permutation():
             raise ValueError("indirect_load: variables_space_order must permute its input "
                              f"dimensions; got non-permutation map: {at.order.source}")
-        return Node("iload", rshape, at.view.dtype, (), {"access": at, "axes": tuple(tr.axes)})
+        return Node("iload", rshape, at.view.dtype, (), {"access": at, "axes": tuple(tr.axes), "stores_before": len(tr.stores)})
     if isinstance(at, TableAccess):
         return Node("tload", rshape if int(np.prod(rshape)) == int(np.prod(at.shape)) else tuple(at.shape), at.dtype, (),
-                    {"access": at, "axes": tuple(tr.axes)})
+                    {"access": at, "axes": tuple(tr.axes), "stores_before": len(tr.stores)})
     if not isinstance(at, Access):
         raise Unsupported("ktdp.load from a value that is not an access tile")
     shape = tuple(at.shape) if at.coords is None else rshape
-    return Node("load", shape, at.view.dtype, (), {"access": at, "axes": tuple(tr.axes)})
+    return Node("load", shape, at.view.dtype, (), {"access": at, "axes": tuple(tr.axes), "stores_before": len(tr.stores)})
 
 
 @rule("ktdp.store")

@@ -180,6 +180,12 @@ def cases(ref_root=None):
         K.gather_rows_transposed(32, 16, 64, 8, 2), "gather_rows_transposed",
         dict(table_ptr=gt.standard_normal((32, 16)).astype(np.float16), idx_ptr=gt.integers(0, 32, 64).astype(np.int32),
              out_ptr=np.zeros((16, 64), np.float16)))
+    # a tile loaded once, overwritten in place, and stored elsewhere afterwards: the second store holds the old values
+    ui = np.random.default_rng(18)
+    out["update_in_place_64x64"] = (K.update_in_place(64, 64, 8, 2, True), "update_in_place",
+                                    dict(x_ptr=ui.standard_normal((64, 64)).astype(np.float16), old_ptr=np.zeros((64, 64), np.float16)))
+    out["update_in_place_16x64_flat"] = (K.update_in_place(16, 64, 8, 2, False), "update_in_place",
+                                         dict(x_ptr=ui.standard_normal((16, 64)).astype(np.float16), old_ptr=np.zeros((16, 64), np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

@@ -9,6 +9,7 @@ from ktir_cpu_b200.dtypes import to_ktir_dtype
 from ktir_cpu_b200.interpreter import Session, arena_layout
 from ktir_cpu_b200.lower import Allocation, ArenaMap, _points
 from ktir_cpu_b200.lower_generic import build_generic
+from ktir_cpu_b200.order import program_order
 from ktir_cpu_b200.parser import KTIRParser
 from ktir_cpu_b200.runtime import PlanOnlyDevice
 from ktir_cpu_b200.trace import Tracer
@@ -29,7 +30,8 @@ def run_generic(src, fn, kw):
     kinds = set()
     tracer = Tracer(func, scalars, ptrs)
     tracer.arena = amap
-    for st in tracer.run():
+    stores = tracer.run()
+    for st in [stores[k] for k in program_order(stores, amap)]:
         sel, _ = _points(st)
         prog = build_generic(st, amap, sel)[0]
         kinds.update(op.kind for op in prog.ops)
@@ -45,7 +47,7 @@ EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elemen
          "ring_allreduce_16x16_add_f16", "ring_allreduce_16x4_add_f16", "shared_slot_store_12x5",
          "vector_add_short_4000", "sharded_scale_64x64_shift0", "sharded_scale_64x64_shift3", "sharded_center_8x256",
          "paged_gather_4x64", "region_reduce_16x37", "generic_contraction_4x8x13",
-         "gather_rows_transposed_64x16")
+         "gather_rows_transposed_64x16", "update_in_place_64x64", "update_in_place_16x64_flat")
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 

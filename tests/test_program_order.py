@@ -1,0 +1,61 @@
+"""Order of a core's loads and stores (host logic, no GPU): a load sees memory as it is at the load's
+position in the program (ktir_cpu/interpreter.py:196-281), so a statement whose tile was loaded before
+an earlier store to the same bytes has to run first — or the plan is refused."""
+import numpy as np
+import pytest
+
+from ktir_cpu_b200 import kernels as K
+from ktir_cpu_b200.interpreter import Session
+from ktir_cpu_b200.parser import KTIRParser
+from ktir_cpu_b200.runtime import PlanOnlyDevice
+from ktir_cpu_b200.trace import Unsupported
+from oracle.numpy_interp import OracleInterpreter
+from test_generic_lowering import run_generic
+
+F16 = np.dtype(np.float16)
+
+
+def _plan(src, fn, tensors):
+    return Session(PlanOnlyDevice(), KTIRParser().parse_module(src).get_function(fn), tensors, {}, arena_ptr=0)
+
+
+def _written_first(sess):
+    """Name of the tensor the first statement of the plan writes."""
+    fp = next(f for f in sess.plan.statements[0].footprints() if f.write)
+    return sess.arena_map.find(int(fp.starts[0])).name
+
+
+@pytest.mark.parametrize("loop,n_rows", [(True, 64), (False, 16)])
+def test_store_of_an_earlier_load_moves_in_front_of_the_store_that_overwrites_it(loop, n_rows):
+    src = K.update_in_place(n_rows, 64, 8, 2, loop)
+    sess = _plan(src, "update_in_place", [("x_ptr", (n_rows, 64), F16), ("old_ptr", (n_rows, 64), F16)])
+    assert len(sess.plan.statements) == 2 and _written_first(sess) == "old_ptr"
+    rng = np.random.default_rng(3)
+    kw = dict(x_ptr=rng.standard_normal((n_rows, 64)).astype(np.float16), old_ptr=np.zeros((n_rows, 64), np.float16))
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("update_in_place", **{k: v.copy() for k, v in kw.items()})
+    np.testing.assert_array_equal(want["old_ptr"], kw["x_ptr"])
+    got, _ = run_generic(src, "update_in_place", kw)
+    for k in want:
+        np.testing.assert_array_equal(got[k], want[k])
+
+
+def test_program_order_is_kept_when_nothing_is_loaded_early():
+    """Two stores fed by the same load, nothing overwritten: max row first, then the sum row, as written."""
+    sess = _plan(K.region_reduce_rows(16, 37, 4), "region_reduce",
+                 [("x_ptr", (16, 37), F16), ("mx_ptr", (16,), F16), ("sa_ptr", (16,), F16)])
+    first = [sess.arena_map.find(int(next(f for f in s.footprints() if f.write).starts[0])).name
+             for s in sess.plan.statements]
+    assert first == ["mx_ptr", "sa_ptr"]
+
+
+def test_a_store_that_needs_memory_from_before_and_after_an_earlier_store_is_refused():
+    src = K.update_in_place(64, 64, 8, 2, True, reuse_new=True)
+    with pytest.raises(Unsupported, match="loaded before an earlier store"):
+        _plan(src, "update_in_place", [("x_ptr", (64, 64), F16), ("old_ptr", (64, 64), F16)])
+
+
+def test_a_load_of_the_next_iterations_store_is_refused():
+    with pytest.raises(Unsupported, match="different iterations"):
+        _plan(K.shifted_reuse(), "shifted_reuse", [(k, (64, 64), F16) for k in ("a_ptr", "b_ptr", "c_ptr")])
