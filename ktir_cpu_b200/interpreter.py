@@ -22,9 +22,9 @@ import numpy as np
 from . import runtime as R
 from .dtypes import bytes_per_elem, to_ktir_dtype
 from .ir import IRModule
-from .lower import Allocation, ArenaMap, Plan, lower
+from .lower import Allocation, ArenaMap, Plan, lower, lower_core_groups
 from .parser import KTIRParser, KTIRParserBase
-from .trace import Tracer
+from .trace import CoreOrderHazard, Tracer
 
 STICK = 128
 ARENA_BASE = 0x10000
@@ -136,7 +136,18 @@ class Session:
                     part = Tracer(func, scalars, ptrs, core_range=core_slice(tracer.ncores, *shard))
                     part.arena = self.arena_map
                     stores = part.run()
-            self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard, fused=fused)
+            try:
+                self.plan: Plan = lower(dev, stores, self.arena_map, row_shard=row_shard, fused=fused)
+            except CoreOrderHazard:
+                if shard is not None and shard[1] > 1:
+                    raise
+                # some core touches bytes another core writes: groups of cores, one after the other
+
+                def trace_cores(lo, hi):
+                    part = Tracer(func, scalars, ptrs, core_range=(lo, hi))
+                    part.arena = self.arena_map
+                    return part.run()
+                self.plan = lower_core_groups(dev, trace_cores, tracer.ncores, self.arena_map, fused=fused)
         except Exception:
             if self.own_arena:
                 dev.free(self.arena)

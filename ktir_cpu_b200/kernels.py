@@ -1167,3 +1167,20 @@ def shifted_reuse(n_rows: int = 64, cols: int = 64, tile_rows: int = 8) -> str:
           f"      ktdp.store %y, %bt : {t}, {at}\n      %z = ktdp.load %bn : {at} -> {t}\n"
           f"      ktdp.store %z, %ct : {t}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n")
     return s
+
+
+def core_chain(n_cores: int = 8, cols: int = 64, dtype: str = "f16") -> str:
+    """x[c + 1] += x[c] on core c: every core reads the row the core before it has just written, so
+    the core-after-core order of the reference turns the rows into running sums (row r ends as
+    x[0] + ... + x[r], rounded to the tile dtype at every step)."""
+    t, at = f"tensor<1x{cols}x{dtype}>", f"!ktdp.access_tile<1x{cols}xindex>"
+    rows = n_cores + 1
+    s = (f"module {{\n  func.func @core_chain(%x_ptr: index) attributes {{grid = [{n_cores}, 1]}} {{\n"
+         f"    %c = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n    %n = arith.addi %c, %c1 : index\n")
+    s += view("x", "x_ptr", [rows, cols], dtype)
+    s += tile("prev", "x", ["%c", "%c0"], [1, cols], [rows, cols], dtype)
+    s += tile("mine", "x", ["%n", "%c0"], [1, cols], [rows, cols], dtype)
+    s += (f"    %a = ktdp.load %prev : {at} -> {t}\n    %b = ktdp.load %mine : {at} -> {t}\n"
+          f"    %s = arith.addf %a, %b : {t}\n    ktdp.store %s, %mine : {t}, {at}\n    return\n  }}\n}}\n")
+    return s

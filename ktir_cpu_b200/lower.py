@@ -18,7 +18,7 @@ import numpy as np
 
 from . import runtime as R
 from .dtypes import bytes_per_elem
-from .trace import Access, IndirectAccess, Node, Store, Unsupported, iv_full
+from .trace import Access, CoreOrderHazard, IndirectAccess, Node, Store, Unsupported, iv_full
 
 F_DT = ("f16", "f32")
 
@@ -621,7 +621,7 @@ def check_hazards(fps: List[Footprint]):
         trouble[gid[bad]] = True
         trouble[g2[1:][clash]] = True
         if (trouble & ~fixable).any():
-            raise Unsupported("memory written by one core/iteration is accessed by another: "
+            raise CoreOrderHazard("memory written by one core/iteration is accessed by another: "
                               "sequential core order matters and has no device path yet")
         for g in np.flatnonzero(trouble):
             members = np.unique(point[gid == g])
@@ -633,7 +633,7 @@ def check_hazards(fps: List[Footprint]):
     cw = np.concatenate([[0], np.cumsum(g_write)])
     writes_after = cw[k] - cw[np.minimum(idx + 1, ng)]
     if ((k > idx + 1) & (g_write | (writes_after > 0))).any():
-        raise Unsupported("overlapping tile stores/loads across cores or iterations: "
+        raise CoreOrderHazard("overlapping tile stores/loads across cores or iterations: "
                           "sequential core order matters and has no device path yet")
     return ordered
 
@@ -665,6 +665,7 @@ class Plan:
         self.statements: List[Statement] = []
         self.written: set = set()
         self.fully_overwritten: set = set()
+        self.core_groups: Optional[List[Tuple[int, int]]] = None     # set when the cores run group after group
 
     def launch(self, dev: R.Device, arena_ptr: int):
         for s in self.statements:
@@ -697,6 +698,42 @@ class Plan:
             for p in getattr(s, "device_arrays", []):
                 dev.free(p)
         self.statements = []
+
+
+def lower_core_groups(dev: R.Device, trace_cores, n_cores: int, arena: ArenaMap, fused: bool = True) -> Plan:
+    """Plan for a grid whose cores cannot all run at once (``CoreOrderHazard``): the cores are cut into
+    consecutive groups that pass the hazard check on their own, and the groups' plans run one after the
+    other — inside a group nothing clashes, between groups the launch order is the reference's core
+    order (ktir_cpu/grid.py:595-613), so the memory a later core sees and the bytes that survive are
+    the reference's.  ``trace_cores(lo, hi)`` returns the traced stores of cores [lo, hi).  A single
+    core that still clashes with itself (iterations of a loop) propagates its error."""
+    groups: List[Tuple[int, int]] = []
+    probe = R.PlanOnlyDevice()
+    lo, last = 0, n_cores
+    while lo < n_cores:
+        # the whole grid is known to clash; after that, try twice the size that last worked
+        size = min(n_cores - lo, 2 * last) if lo else max(1, n_cores // 2)
+        while True:
+            try:
+                lower(probe, trace_cores(lo, lo + size), arena, fused=fused)
+                break
+            except CoreOrderHazard:
+                if size == 1:
+                    raise
+                size = max(1, size // 2)
+        groups.append((lo, lo + size))
+        lo, last = lo + size, size
+    plan = Plan()
+    try:
+        for lo, hi in groups:
+            part = lower(dev, trace_cores(lo, hi), arena, fused=fused)
+            plan.statements.extend(part.statements)
+            plan.written |= part.written
+    except Exception:
+        plan.release(dev)
+        raise
+    plan.core_groups = groups
+    return plan
 
 
 def _fused_statement(dev, st: Store, arena: ArenaMap, sid: int, row_shard):
@@ -745,7 +782,7 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
     for sid, groups in check_hazards(fps).items():
         stmt = plan.statements[sid]
         if not hasattr(stmt, "order_points"):
-            raise Unsupported(f"several cores store to the same bytes in a {stmt.kind} statement: "
+            raise CoreOrderHazard(f"several cores store to the same bytes in a {stmt.kind} statement: "
                               "sequential core order matters and has no device path yet")
         stmt.order_points(launch_rounds(groups))
     read_names, write_runs = set(), {}

@@ -27,6 +27,11 @@ class Unsupported(NotImplementedError):
     """Raised when a kernel uses something this backend has no device path for."""
 
 
+class CoreOrderHazard(Unsupported):
+    """The cores (or loop iterations) of a grid cannot all run at once: one touches bytes another
+    writes, so the result depends on the reference's core-after-core order (ktir_cpu/grid.py:595-613)."""
+
+
 # ---------------------------------------------------------------------------
 # Integer values over the iteration space
 # ---------------------------------------------------------------------------

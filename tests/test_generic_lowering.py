@@ -15,8 +15,9 @@ from ktir_cpu_b200.runtime import PlanOnlyDevice
 from ktir_cpu_b200.trace import Tracer
 
 
-def run_generic(src, fn, kw):
-    """Every store of the kernel through build_generic + the emulator, in program order."""
+def run_generic(src, fn, kw, core_groups=None):
+    """Every store of the kernel through build_generic + the emulator, in launch order.  ``core_groups``
+    = [(lo, hi), ...] runs the cores group after group, as a plan does whose cores cannot all run at once."""
     func = KTIRParser().parse_module(src).get_function(fn)
     tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items() if isinstance(v, np.ndarray)]
     scalars = {k: v for k, v in kw.items() if not isinstance(v, np.ndarray)}
@@ -28,10 +29,13 @@ def run_generic(src, fn, kw):
         allocs.append(Allocation(name, off, off + nb, to_ktir_dtype(dt)))
     amap = ArenaMap(allocs)
     kinds = set()
-    tracer = Tracer(func, scalars, ptrs)
-    tracer.arena = amap
-    stores = tracer.run()
-    for st in [stores[k] for k in program_order(stores, amap)]:
+    stores = []
+    for rng in core_groups or [None]:
+        tracer = Tracer(func, scalars, ptrs, core_range=rng)
+        tracer.arena = amap
+        part = tracer.run()
+        stores += [part[k] for k in program_order(part, amap)]
+    for st in stores:
         sel, _ = _points(st)
         prog = build_generic(st, amap, sel)[0]
         kinds.update(op.kind for op in prog.ops)
@@ -48,16 +52,17 @@ EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elemen
          "vector_add_short_4000", "sharded_scale_64x64_shift0", "sharded_scale_64x64_shift3", "sharded_center_8x256",
          "paged_gather_4x64", "region_reduce_16x37", "generic_contraction_4x8x13",
          "gather_rows_transposed_64x16", "update_in_place_64x64", "update_in_place_16x64_flat")
+SEQUENTIAL = {"core_chain_16x64": [(c, c + 1) for c in range(16)]}
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 
 
-@pytest.mark.parametrize("name", EXACT + CLOSE)
+@pytest.mark.parametrize("name", EXACT + CLOSE + tuple(SEQUENTIAL))
 def test_generic_steps_reproduce_the_reference(name):
     src, fn, kw, want = load_golden(name)
-    got, kinds = run_generic(src, fn, kw)
+    got, kinds = run_generic(src, fn, kw, core_groups=SEQUENTIAL.get(name))
     for k, w in want.items():
-        if name in EXACT and "erf" not in k:
+        if (name in EXACT or name in SEQUENTIAL) and "erf" not in k:
             np.testing.assert_array_equal(got[k], w)
             np.testing.assert_array_equal(np.signbit(got[k]) | np.isnan(w), np.signbit(w) | np.isnan(w))
         else:

@@ -26,7 +26,7 @@ def _run_both(src, fn, kwargs):
 
 
 def _exact(name):
-    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place"))
+    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain"))
 
 
 SUPPORTED = golden_names()
@@ -577,3 +577,31 @@ def test_block_gathers_match_numpy(shape, sel, kind, build_lib):
     want = kw["src_ptr"][np.ix_(*[kw[f"idx{i}_ptr"] for i in range(len(sel))])]
     np.testing.assert_array_equal(got["out_ptr"], want)
     np.testing.assert_array_equal(got["src_ptr"], kw["src_ptr"])
+
+
+def test_cores_run_in_order_where_they_touch_each_others_memory(build_lib):
+    """Running sums down the rows (core c adds row c into row c + 1) and blocks shifted with wrap-around:
+    both results exist only in the reference's core-after-core order (ktir_cpu/grid.py:595-613).  Called
+    three times, so that the recorded CUDA graph of the group-after-group plan is replayed as well."""
+    from test_sharded import SHIFT
+    rng = np.random.default_rng(77)
+    gpu = KTIRInterpreter()
+    gpu.load(K_.core_chain(32, 256))
+    for _ in range(3):
+        x = rng.standard_normal((33, 256)).astype(np.float16)
+        want = x.copy()
+        for c in range(32):
+            want[c + 1] = want[c + 1] + want[c]
+        got = gpu.execute_function("core_chain", x_ptr=x)
+        np.testing.assert_array_equal(got["x_ptr"], want)
+    (sess,) = gpu._sessions.values()
+    assert sess.plan.core_groups == [(c, c + 1) for c in range(32)]
+    gpu.close()
+    gpu = KTIRInterpreter()
+    gpu.load(SHIFT)
+    x = rng.standard_normal(256).astype(np.float16)
+    want = x.copy()
+    for c in range(4):
+        want[c * 64:(c + 1) * 64] = want[((c + 1) % 4) * 64:((c + 1) % 4 + 1) * 64]
+    np.testing.assert_array_equal(gpu.execute_function("shift", x_ptr=x)["x_ptr"], want)
+    gpu.close()

@@ -59,3 +59,39 @@ def test_a_store_that_needs_memory_from_before_and_after_an_earlier_store_is_ref
 def test_a_load_of_the_next_iterations_store_is_refused():
     with pytest.raises(Unsupported, match="different iterations"):
         _plan(K.shifted_reuse(), "shifted_reuse", [(k, (64, 64), F16) for k in ("a_ptr", "b_ptr", "c_ptr")])
+
+
+def _core_groups(src, fn, tensors):
+    return _plan(src, fn, tensors).plan.core_groups
+
+
+@pytest.mark.parametrize("n_cores", [1, 5, 8])
+def test_cores_that_read_each_others_rows_run_one_after_the_other(n_cores):
+    """x[c + 1] += x[c] on core c: running sums only come out in the reference's core order."""
+    src = K.core_chain(n_cores, 64)
+    groups = _core_groups(src, "core_chain", [("x_ptr", (n_cores + 1, 64), F16)])
+    assert groups == ([(c, c + 1) for c in range(n_cores)] if n_cores > 1 else None)
+    x = np.random.default_rng(9).standard_normal((n_cores + 1, 64)).astype(np.float16)
+    want = x.copy()
+    for c in range(n_cores):
+        want[c + 1] = want[c + 1] + want[c]
+    ora = OracleInterpreter()
+    ora.load(src)
+    np.testing.assert_array_equal(ora.execute_function("core_chain", x_ptr=x.copy())["x_ptr"], want)
+    got, _ = run_generic(src, "core_chain", dict(x_ptr=x.copy()), core_groups=groups)
+    np.testing.assert_array_equal(got["x_ptr"], want)
+
+
+def test_core_groups_are_as_large_as_the_clashes_allow():
+    """Blocks shifted down by one with wrap-around: cores 0..2 read old blocks, core 3 reads what core 0 wrote."""
+    from test_sharded import SHIFT
+    x = np.arange(256, dtype=np.float16)
+    groups = _core_groups(SHIFT, "shift", [("x_ptr", (256,), F16)])
+    got, _ = run_generic(SHIFT, "shift", dict(x_ptr=x.copy()), core_groups=groups)
+    want = x.copy()
+    for c in range(4):
+        want[c * 64:(c + 1) * 64] = want[((c + 1) % 4) * 64:((c + 1) % 4 + 1) * 64]
+    np.testing.assert_array_equal(got["x_ptr"], want)
+    ora = OracleInterpreter()
+    ora.load(SHIFT)
+    np.testing.assert_array_equal(ora.execute_function("shift", x_ptr=x.copy())["x_ptr"], want)

@@ -156,14 +156,14 @@ SHIFT = """module {
 """
 
 
-def test_cross_rank_read_after_write_is_rejected_like_on_one_gpu():
-    """Core c reads the block core c+1 writes: the sequential core order matters.  Inside one rank's
-    slice nothing clashes (with one core per rank there is no second core at all), so the whole grid
-    has to be checked."""
+def test_cross_rank_read_after_write_is_rejected():
+    """Core c reads the block core c+1 writes: the sequential core order matters.  One GPU runs the
+    cores one group after the other; across ranks there is no such order, and inside one rank's slice
+    nothing clashes (with one core per rank there is no second core at all), so the whole grid has to
+    be checked."""
     from ktir_cpu_b200.trace import Unsupported
     t = [("x_ptr", (256,), np.dtype(np.float16))]
-    with pytest.raises(Unsupported, match="sequential core order"):
-        _plan(SHIFT, "shift", t, 0, 1)
+    assert _plan(SHIFT, "shift", t, 0, 1).plan.core_groups == [(0, 1), (1, 2), (2, 3), (3, 4)]
     for rank in range(4):
         with pytest.raises(Unsupported, match="sequential core order"):
             _plan(SHIFT, "shift", t, rank, 4)
