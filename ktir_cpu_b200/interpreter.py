@@ -143,9 +143,9 @@ class Session:
                     raise
                 # some core touches bytes another core writes: groups of cores, one after the other
 
-                def trace_cores(lo, hi):
+                def trace_cores(lo, hi, unroll):
                     part = Tracer(func, scalars, ptrs, core_range=(lo, hi))
-                    part.arena = self.arena_map
+                    part.arena, part.unroll_loops = self.arena_map, unroll
                     return part.run()
                 self.plan = lower_core_groups(dev, trace_cores, tracer.ncores, self.arena_map, fused=fused)
         except Exception:

@@ -1184,3 +1184,23 @@ def core_chain(n_cores: int = 8, cols: int = 64, dtype: str = "f16") -> str:
     s += (f"    %a = ktdp.load %prev : {at} -> {t}\n    %b = ktdp.load %mine : {at} -> {t}\n"
           f"    %s = arith.addf %a, %b : {t}\n    ktdp.store %s, %mine : {t}, {at}\n    return\n  }}\n}}\n")
     return s
+
+
+def accumulate_rows(n_cores: int = 4, per_core: int = 6, cols: int = 64, dtype: str = "f16") -> str:
+    """acc[c] += x[c * per_core + i] for i = 0 .. per_core - 1, the running row re-loaded from memory
+    and stored back in every iteration of an ``scf.for`` — each iteration reads what the one before it
+    wrote (rounded to the tile dtype), so the iterations only make sense one after the other."""
+    t, at = f"tensor<1x{cols}x{dtype}>", f"!ktdp.access_tile<1x{cols}xindex>"
+    rows = n_cores * per_core
+    s = (f"module {{\n  func.func @accumulate_rows(%x_ptr: index, %acc_ptr: index) attributes {{grid = [{n_cores}, 1]}} {{\n"
+         f"    %c = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %c1 = arith.constant 1 : index\n    %per_core = arith.constant {per_core} : index\n"
+         f"    %begin = arith.muli %c, %per_core : index\n    %end = arith.addi %begin, %per_core : index\n")
+    s += view("x", "x_ptr", [rows, cols], dtype) + view("acc", "acc_ptr", [n_cores, cols], dtype)
+    s += tile("at", "acc", ["%c", "%c0"], [1, cols], [n_cores, cols], dtype)
+    s += "    scf.for %r = %begin to %end step %c1 {\n"
+    s += tile("xt", "x", ["%r", "%c0"], [1, cols], [rows, cols], dtype, "      ")
+    s += (f"      %a = ktdp.load %at : {at} -> {t}\n      %b = ktdp.load %xt : {at} -> {t}\n"
+          f"      %s = arith.addf %a, %b : {t}\n      ktdp.store %s, %at : {t}, {at}\n      scf.yield\n    }}\n"
+          f"    return\n  }}\n}}\n")
+    return s

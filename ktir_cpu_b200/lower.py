@@ -666,6 +666,7 @@ class Plan:
         self.written: set = set()
         self.fully_overwritten: set = set()
         self.core_groups: Optional[List[Tuple[int, int]]] = None     # set when the cores run group after group
+        self.unrolled_groups: List[Tuple[int, int]] = []             # ... and the groups whose loops run iteration by iteration
 
     def launch(self, dev: R.Device, arena_ptr: int):
         for s in self.statements:
@@ -705,34 +706,44 @@ def lower_core_groups(dev: R.Device, trace_cores, n_cores: int, arena: ArenaMap,
     consecutive groups that pass the hazard check on their own, and the groups' plans run one after the
     other — inside a group nothing clashes, between groups the launch order is the reference's core
     order (ktir_cpu/grid.py:595-613), so the memory a later core sees and the bytes that survive are
-    the reference's.  ``trace_cores(lo, hi)`` returns the traced stores of cores [lo, hi).  A single
-    core that still clashes with itself (iterations of a loop) propagates its error."""
-    groups: List[Tuple[int, int]] = []
+    the reference's.  ``trace_cores(lo, hi, unroll)`` returns the traced stores of cores [lo, hi).  A
+    group that clashes because iterations of an ``scf.for`` read or overwrite each other's bytes is
+    traced with its loops unrolled instead: every iteration's store becomes a statement of its own and
+    they run in program order."""
+    groups: List[Tuple[int, int, bool]] = []
     probe = R.PlanOnlyDevice()
     lo, last = 0, n_cores
     while lo < n_cores:
         # the whole grid is known to clash; after that, try twice the size that last worked
-        size = min(n_cores - lo, 2 * last) if lo else max(1, n_cores // 2)
+        size = min(n_cores - lo, 2 * last) if lo else n_cores
         while True:
+            # as they are; else with the loops unrolled (iterations that clash, cores that do not); else fewer cores
+            unroll = False
             try:
-                lower(probe, trace_cores(lo, lo + size), arena, fused=fused)
+                lower(probe, trace_cores(lo, lo + size, False), arena, fused=fused)
                 break
-            except CoreOrderHazard:
-                if size == 1:
-                    raise
-                size = max(1, size // 2)
-        groups.append((lo, lo + size))
+            except CoreOrderHazard as plain:
+                try:
+                    lower(probe, trace_cores(lo, lo + size, True), arena, fused=fused)
+                    unroll = True
+                    break
+                except Unsupported as unrolled:
+                    if size == 1:
+                        raise (unrolled if isinstance(unrolled, CoreOrderHazard) else plain)
+            size = max(1, size // 2)
+        groups.append((lo, lo + size, unroll))
         lo, last = lo + size, size
     plan = Plan()
     try:
-        for lo, hi in groups:
-            part = lower(dev, trace_cores(lo, hi), arena, fused=fused)
+        for lo, hi, unroll in groups:
+            part = lower(dev, trace_cores(lo, hi, unroll), arena, fused=fused)
             plan.statements.extend(part.statements)
             plan.written |= part.written
     except Exception:
         plan.release(dev)
         raise
-    plan.core_groups = groups
+    plan.core_groups = [(lo, hi) for lo, hi, _ in groups]
+    plan.unrolled_groups = [(lo, hi) for lo, hi, unroll in groups if unroll]
     return plan
 
 

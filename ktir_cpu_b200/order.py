@@ -24,7 +24,7 @@ from typing import List, Optional, Tuple
 import numpy as np
 
 from .dtypes import bytes_per_elem
-from .trace import Access, IndirectAccess, Node, Store, TableAccess, Unsupported, iv_full
+from .trace import Access, CoreOrderHazard, IndirectAccess, Node, Store, TableAccess, Unsupported, iv_full
 
 
 class _Runs:
@@ -164,8 +164,9 @@ def program_order(stores: List[Store], arena) -> List[int]:
             rs.extend((r, before, len(own) - 1) for r in _runs(n.attrs["access"], axes, active, arena))
         rs.extend((r, j, len(st.axes) - 1) for r in index_reads[j])
         reads.append(rs)
-    inverted = Unsupported("two statements inside one scf.for touch the same memory in different iterations, the "
-                           "earlier statement in the later iteration: the statements cannot run one after the other")
+    # (cured by tracing the loop iteration by iteration: ``lower.lower_core_groups``)
+    inverted = CoreOrderHazard("two statements inside one scf.for touch the same memory in different iterations, the "
+                               "earlier statement in the later iteration: the statements cannot run one after the other")
     after = {j: set() for j in range(len(stores))}        # after[j]: statements that must run before j
     for j in range(1, len(stores)):
         B = stores[j]

@@ -185,6 +185,7 @@ class Tracer:
         self.axes: List[int] = [self.ncores]
         self.active: Optional[np.ndarray] = None
         self.stores: List[Store] = []
+        self.unroll_loops = False       # trace every scf.for iteration by iteration (its stores become statements of their own)
         self.loop_path: List[int] = []
         self._loop_counter = 0
         self.latency = None            # a trace_latency.LatencyRecorder when the latency model is on

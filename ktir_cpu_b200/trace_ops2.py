@@ -439,7 +439,7 @@ def _for(tr: Tracer, op: Op, scope):
     iv_name, iter_names = reg.arg_names[0], reg.arg_names[1:]
     inits = [tr.get(scope, n) for n in op.operands[3:]]
 
-    if not iter_names:
+    if not iter_names and not tr.unroll_loops:
         if T == 0:
             return None
         depth = len(tr.axes)
@@ -464,12 +464,13 @@ def _for(tr: Tracer, op: Op, scope):
     tmin = int(trips_full.min()) if trips_full.size else 0
     live = trips_full if tr.active is None else trips_full[tr.active]
     if live.size and int(live.min()) != T:
-        raise Unsupported("scf.for with iter_args and a trip count that differs between cores")
+        raise Unsupported("scf.for traced iteration by iteration (iter_args, or iterations that touch each other's "
+                          "memory) and a trip count that differs between cores")
     tile_carried = any(is_node(v) for v in inits)
     if tile_carried and _has_op(reg.ops, ("linalg.matmul", "linalg.batch_matmul")) and T >= 1:
         return _symbolic_loop(tr, op, scope, lb, step, T, inits)
     if T > MAX_UNROLL:
-        raise Unsupported(f"scf.for with iter_args and {T} iterations")
+        raise Unsupported(f"scf.for traced iteration by iteration with {T} iterations")
     vals = list(inits)
     _lx_bind_carried(tr, iter_names, [Node("held", v.shape, v.dtype) if is_node(v) else v for v in vals])
     for k in range(T):

@@ -188,6 +188,9 @@ def cases(ref_root=None):
                                          dict(x_ptr=ui.standard_normal((16, 64)).astype(np.float16), old_ptr=np.zeros((16, 64), np.float16)))
     # every core reads the row the core before it wrote: running sums in core order
     out["core_chain_16x64"] = (K.core_chain(16, 64), "core_chain", dict(x_ptr=ui.standard_normal((17, 64)).astype(np.float16)))
+    # every iteration of a loop reads the row the iteration before it stored
+    out["accumulate_rows_4x6"] = (K.accumulate_rows(4, 6, 64), "accumulate_rows",
+                                  dict(x_ptr=ui.standard_normal((24, 64)).astype(np.float16), acc_ptr=ui.standard_normal((4, 64)).astype(np.float16)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

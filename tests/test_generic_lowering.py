@@ -15,9 +15,10 @@ from ktir_cpu_b200.runtime import PlanOnlyDevice
 from ktir_cpu_b200.trace import Tracer
 
 
-def run_generic(src, fn, kw, core_groups=None):
+def run_generic(src, fn, kw, core_groups=None, unrolled=()):
     """Every store of the kernel through build_generic + the emulator, in launch order.  ``core_groups``
-    = [(lo, hi), ...] runs the cores group after group, as a plan does whose cores cannot all run at once."""
+    = [(lo, hi), ...] runs the cores group after group, as a plan does whose cores cannot all run at once;
+    the groups listed in ``unrolled`` are traced with their loops unrolled."""
     func = KTIRParser().parse_module(src).get_function(fn)
     tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items() if isinstance(v, np.ndarray)]
     scalars = {k: v for k, v in kw.items() if not isinstance(v, np.ndarray)}
@@ -32,7 +33,7 @@ def run_generic(src, fn, kw, core_groups=None):
     stores = []
     for rng in core_groups or [None]:
         tracer = Tracer(func, scalars, ptrs, core_range=rng)
-        tracer.arena = amap
+        tracer.arena, tracer.unroll_loops = amap, rng in tuple(unrolled)
         part = tracer.run()
         stores += [part[k] for k in program_order(part, amap)]
     for st in stores:
@@ -52,7 +53,7 @@ EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elemen
          "vector_add_short_4000", "sharded_scale_64x64_shift0", "sharded_scale_64x64_shift3", "sharded_center_8x256",
          "paged_gather_4x64", "region_reduce_16x37", "generic_contraction_4x8x13",
          "gather_rows_transposed_64x16", "update_in_place_64x64", "update_in_place_16x64_flat")
-SEQUENTIAL = {"core_chain_16x64": [(c, c + 1) for c in range(16)]}
+SEQUENTIAL = {"core_chain_16x64": ([(c, c + 1) for c in range(16)], ()), "accumulate_rows_4x6": ([(0, 4)], [(0, 4)])}
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")
 
@@ -60,7 +61,8 @@ CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "soft
 @pytest.mark.parametrize("name", EXACT + CLOSE + tuple(SEQUENTIAL))
 def test_generic_steps_reproduce_the_reference(name):
     src, fn, kw, want = load_golden(name)
-    got, kinds = run_generic(src, fn, kw, core_groups=SEQUENTIAL.get(name))
+    groups, unrolled = SEQUENTIAL.get(name, (None, ()))
+    got, kinds = run_generic(src, fn, kw, core_groups=groups, unrolled=unrolled)
     for k, w in want.items():
         if (name in EXACT or name in SEQUENTIAL) and "erf" not in k:
             np.testing.assert_array_equal(got[k], w)

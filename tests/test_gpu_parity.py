@@ -26,7 +26,7 @@ def _run_both(src, fn, kwargs):
 
 
 def _exact(name):
-    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain"))
+    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain", "accumulate_rows"))
 
 
 SUPPORTED = golden_names()
@@ -604,4 +604,16 @@ def test_cores_run_in_order_where_they_touch_each_others_memory(build_lib):
     for c in range(4):
         want[c * 64:(c + 1) * 64] = want[((c + 1) % 4) * 64:((c + 1) % 4 + 1) * 64]
     np.testing.assert_array_equal(gpu.execute_function("shift", x_ptr=x)["x_ptr"], want)
+    gpu.close()
+    # a running row re-loaded and stored back in every loop iteration: one statement per iteration
+    gpu = KTIRInterpreter()
+    gpu.load(K_.accumulate_rows(8, 40, 128))
+    for _ in range(3):
+        x, acc = rng.standard_normal((320, 128)).astype(np.float16), rng.standard_normal((8, 128)).astype(np.float16)
+        want = acc.copy()
+        for i in range(40):
+            want = want + x[i::40]
+        np.testing.assert_array_equal(gpu.execute_function("accumulate_rows", x_ptr=x, acc_ptr=acc)["acc_ptr"], want)
+    (sess,) = gpu._sessions.values()
+    assert sess.plan.unrolled_groups == [(0, 8)] and len(sess.plan.statements) == 40
     gpu.close()

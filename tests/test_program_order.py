@@ -56,9 +56,22 @@ def test_a_store_that_needs_memory_from_before_and_after_an_earlier_store_is_ref
         _plan(src, "update_in_place", [("x_ptr", (64, 64), F16), ("old_ptr", (64, 64), F16)])
 
 
-def test_a_load_of_the_next_iterations_store_is_refused():
-    with pytest.raises(Unsupported, match="different iterations"):
-        _plan(K.shifted_reuse(), "shifted_reuse", [(k, (64, 64), F16) for k in ("a_ptr", "b_ptr", "c_ptr")])
+def test_a_load_of_the_next_iterations_store_unrolls_the_loop():
+    """b[i] = 2 a[i]; c[i] = b[i + 1] inside one loop: as two whole statements the second would see the
+    new b everywhere, so the loop runs iteration by iteration (2 statements x 8 iterations)."""
+    src = K.shifted_reuse()
+    sess = _plan(src, "shifted_reuse", [(k, (64, 64), F16) for k in ("a_ptr", "b_ptr", "c_ptr")])
+    assert sess.plan.unrolled_groups == [(0, 1)] and len(sess.plan.statements) == 16
+    rng = np.random.default_rng(6)
+    kw = {k: rng.standard_normal((64, 64)).astype(np.float16) for k in ("a_ptr", "b_ptr", "c_ptr")}
+    want_c = np.roll(kw["b_ptr"], -8, axis=0)
+    want_c[-8:] = 2 * kw["a_ptr"][:8]
+    got, _ = run_generic(src, "shifted_reuse", kw, core_groups=sess.plan.core_groups, unrolled=sess.plan.unrolled_groups)
+    np.testing.assert_array_equal(got["c_ptr"], want_c)
+    np.testing.assert_array_equal(got["b_ptr"], 2 * kw["a_ptr"])
+    ora = OracleInterpreter()
+    ora.load(src)
+    np.testing.assert_array_equal(ora.execute_function("shifted_reuse", **kw)["c_ptr"], want_c)
 
 
 def _core_groups(src, fn, tensors):
@@ -95,3 +108,28 @@ def test_core_groups_are_as_large_as_the_clashes_allow():
     ora = OracleInterpreter()
     ora.load(SHIFT)
     np.testing.assert_array_equal(ora.execute_function("shift", x_ptr=x.copy())["x_ptr"], want)
+
+
+@pytest.mark.parametrize("n_cores,per_core", [(4, 6), (1, 3), (3, 1)])
+def test_loop_iterations_that_read_what_the_last_one_wrote_run_one_by_one(n_cores, per_core):
+    """acc[c] += x[i] with the running row re-loaded every iteration: the loop is unrolled into one
+    statement per iteration (all cores at once — they do not touch each other's rows)."""
+    src = K.accumulate_rows(n_cores, per_core, 64)
+    rows = n_cores * per_core
+    sess = _plan(src, "accumulate_rows", [("x_ptr", (rows, 64), F16), ("acc_ptr", (n_cores, 64), F16)])
+    if per_core > 1:
+        assert sess.plan.core_groups == [(0, n_cores)] and sess.plan.unrolled_groups == [(0, n_cores)]
+        assert len(sess.plan.statements) == per_core
+    else:
+        assert sess.plan.core_groups is None
+    rng = np.random.default_rng(4)
+    kw = dict(x_ptr=rng.standard_normal((rows, 64)).astype(np.float16), acc_ptr=rng.standard_normal((n_cores, 64)).astype(np.float16))
+    want = kw["acc_ptr"].copy()
+    for c in range(n_cores):
+        for i in range(per_core):
+            want[c] = want[c] + kw["x_ptr"][c * per_core + i]
+    ora = OracleInterpreter()
+    ora.load(src)
+    np.testing.assert_array_equal(ora.execute_function("accumulate_rows", **{k: v.copy() for k, v in kw.items()})["acc_ptr"], want)
+    got, _ = run_generic(src, "accumulate_rows", kw, core_groups=sess.plan.core_groups, unrolled=sess.plan.unrolled_groups)
+    np.testing.assert_array_equal(got["acc_ptr"], want)
