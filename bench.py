@@ -663,9 +663,40 @@ def report(w, interp, kw_host, steps, warm, dist, clocks_for=None, shard=None, w
         out["roofline"]["frac_sustained"] = ach / peak
         out["roofline"]["sustained"] = {"achieved": ach, "ms_per_launch": sms,
                                         "how": "8 back-to-back launches over 8 distinct arenas, one event pair, no L2 flush"}
+        if algo // 2 <= (2 << 30):
+            cms = time_copy_sustained(dev, algo // 2)
+            cach = algo / (cms * 1e-3) / scale
+            out["roofline"]["sustained"]["device_copy_same_bytes"] = {
+                "achieved": cach, "ms_per_copy": cms, "kernel_over_copy": ach / cach,
+                "how": "cudaMemcpyAsync device to device moving the same bytes (half read, half written), timed the same way"}
     if cpu and dist.rank == 0:
         out["cpu_baseline"] = cpu_baseline(w)
     return out
+
+
+def time_copy_sustained(dev, nbytes, sets=8, reps=3):
+    """Milliseconds per plain device-to-device copy of ``nbytes`` (read ``nbytes``, write ``nbytes``), measured like
+    ``time_sustained``: ``sets`` copies over distinct buffers back to back inside one event pair.  What the
+    memory system gives a kernel-free stream of this size — the measured peak is quoted on far larger buffers."""
+    bufs = [dev.alloc(2 * nbytes + 256) for _ in range(sets)]
+    try:
+        for b in bufs:
+            dev.check(dev.lib.ktb_memset(dev.h, b, 1, 2 * nbytes))
+        dev.sync()
+        best = None
+        for _ in range(reps + 1):
+            dev.flush_l2()
+            dev.record(2)
+            for b in bufs:
+                dev.check(dev.lib.ktb_d2d(dev.h, b + nbytes, b, nbytes))
+            dev.record(3)
+            dev.sync()
+            ms = dev.elapsed_ms(2, 3) / sets
+            best = ms if best is None else min(best, ms)
+        return best
+    finally:
+        for b in bufs:
+            dev.free(b)
 
 
 def host_link_probe(dev, dist, mib=64, reps=8):

@@ -130,6 +130,24 @@ def test_softmax_full_size_properties(build_lib):
     assert (np.argmax(y, 1) == np.argmax(x, 1)).mean() > 0.99
 
 
+@pytest.mark.parametrize("rows,cols,cores,r", [(2405, 1024, 5, 13), (2400, 2048, 4, 8), (2372, 4096, 4, 1)])
+def test_softmax_bulk_copy_ring_sizes(rows, cols, cores, r, build_lib):
+    """Enough rows of 2 .. 8 KB for the kernel that stages rows through shared memory by bulk copies:
+    row counts that do not fill the last group of eight, row tiles that straddle the groups."""
+    rng = np.random.default_rng(rows)
+    x = (rng.standard_normal((rows, cols)) * 3).astype(np.float16)
+    x[7] = 0                      # a constant row: every element 1 / cols
+    x[11, 5] = np.float16(60000)  # one huge value: that element takes everything
+    gpu = KTIRInterpreter()
+    gpu.load(K.softmax_rows(rows, cols, cores, r, True))
+    y = gpu.execute_function("softmax_kernel", output_ptr=np.full_like(x, 9), input_ptr=x)["output_ptr"]
+    gpu.close()
+    xf = x.astype(np.float32)
+    e = np.exp(xf - xf.max(1, keepdims=True))
+    np.testing.assert_allclose(y.astype(np.float32), e / e.sum(1, keepdims=True), rtol=2e-3, atol=2e-6)
+    assert y[11, 5] == 1 and (np.delete(y[11], 5) == 0).all()
+
+
 def _dup_indices(rng, n_rows, n_idx, tile_rows, dup):
     idx = rng.integers(0, n_rows, n_idx)
     for t in range(n_idx // tile_rows):
