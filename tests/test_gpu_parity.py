@@ -131,9 +131,9 @@ def test_softmax_full_size_properties(build_lib):
 
 
 @pytest.mark.parametrize("rows,cols,cores,r", [(2405, 1024, 5, 13), (2400, 2048, 4, 8), (2372, 4096, 4, 1)])
-def test_softmax_bulk_copy_ring_sizes(rows, cols, cores, r, build_lib):
-    """Enough rows of 2 .. 8 KB for the kernel that stages rows through shared memory by bulk copies:
-    row counts that do not fill the last group of eight, row tiles that straddle the groups."""
+def test_softmax_many_ragged_rows(rows, cols, cores, r, build_lib):
+    """Thousands of rows of 2 .. 8 KB with row counts that are no multiple of the rows a CTA takes per
+    iteration and row tiles that straddle them; a constant row and a row with one huge value."""
     rng = np.random.default_rng(rows)
     x = (rng.standard_normal((rows, cols)) * 3).astype(np.float16)
     x[7] = 0                      # a constant row: every element 1 / cols
