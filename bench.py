@@ -115,7 +115,7 @@ class Softmax(Workload):
 
 
 class VectorAdd(Workload):
-    name, func, kernel = "vector_add", "add_kernel", "ktb_ew_stream_kernel"
+    name, func, kernel = "vector_add", "add_kernel", "ktb_ew_f16_kernel"
     N, BLOCK, CORES = 1 << 26, 131072, 32
     units_per_step = N
     algo_per_step = 3 * N * 2

@@ -10,17 +10,18 @@
 
 // SPECIAL >= 0: the program is the single op SPECIAL applied to inputs (0, 1);
 // SPECIAL < 0: general register program.
-template <int V, int SPECIAL>
+template <int V, int SPECIAL, typename IDX>
 __global__ void __launch_bounds__(256) ktb_ew_stream_kernel(const ktb_ew_args args, uint32_t chunks_per_row,
                                                             uint32_t chunks_per_item, uint64_t total_chunks) {
-    const uint64_t chunk = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (chunk >= total_chunks) return;
-    const uint64_t item = chunk / chunks_per_item;
-    const uint32_t rem = (uint32_t)(chunk - item * chunks_per_item);
+    const uint64_t chunk64 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (chunk64 >= total_chunks) return;
+    const IDX chunk = (IDX)chunk64;
+    const IDX item = chunk / (IDX)chunks_per_item;
+    const uint32_t rem = (uint32_t)(chunk - item * (IDX)chunks_per_item);
     const uint32_t row = rem / chunks_per_row;
     const uint32_t col = (rem - row * chunks_per_row) * V;
     const int n_in = args.program.n_in;
-    const int64_t* offs = args.dev_item_offsets + item * (n_in + 1);
+    const int64_t* offs = args.dev_item_offsets + (int64_t)item * (n_in + 1);
 
     float out[V];
     if (SPECIAL >= 0) {
@@ -47,12 +48,80 @@ __global__ void __launch_bounds__(256) ktb_ew_stream_kernel(const ktb_ew_args ar
     ktb_store_vec<V>(args.arena, offs[n_in] + (int64_t)row * args.row_stride[n_in] + col, args.dtype[n_in], out);
 }
 
+// All operands f16, one op: every thread takes U chunks of 8 elements, a block 256 * U consecutive chunks
+// (thread t the chunks t, t + 256, ...: each warp access stays one contiguous 512-byte run), and issues the
+// 16-byte loads of all its chunks before it touches any of them.  Chunk indices are 32-bit when they fit: the
+// two divisions that find a chunk's item, row and column cost a multiple of the add itself in 64 bits.
+// Vector add of 2^26 elements: 71.7 us with the general kernel, 63.5 with U = 1, 59.4 with U = 2, 63.5 with
+// U = 4, 73.7 with U = 8 (fewer resident threads).
+#ifndef KTB_EW_U
+#define KTB_EW_U 2
+#endif
+template <int U, int OP, typename IDX>
+__global__ void __launch_bounds__(256) ktb_ew_f16_kernel(const ktb_ew_args args, uint32_t chunks_per_row,
+                                                         uint32_t chunks_per_item, uint64_t total_chunks) {
+    const uint64_t first = (uint64_t)blockIdx.x * (256u * U) + threadIdx.x;
+    const bool two = args.program.n_in > 1;
+    const int n_in = args.program.n_in;
+    const __half* arena = reinterpret_cast<const __half*>(args.arena);
+    uint4 ra[U], rb[U];
+    int64_t dst[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const uint64_t chunk = first + (uint64_t)u * 256u;
+        dst[u] = -1;
+        if (chunk < total_chunks) {
+            const IDX c = (IDX)chunk;
+            const IDX item = c / (IDX)chunks_per_item;
+            const uint32_t rem = (uint32_t)(c - item * (IDX)chunks_per_item);
+            const uint32_t row = rem / chunks_per_row;
+            const uint32_t col = (rem - row * chunks_per_row) * 8;
+            const int64_t* offs = args.dev_item_offsets + (int64_t)item * (n_in + 1);
+            ra[u] = __ldcs(reinterpret_cast<const uint4*>(arena + offs[0] + (int64_t)row * args.row_stride[0] + col));
+            if (two) rb[u] = __ldcs(reinterpret_cast<const uint4*>(arena + offs[1] + (int64_t)row * args.row_stride[1] + col));
+            dst[u] = offs[n_in] + (int64_t)row * args.row_stride[n_in] + col;
+        }
+    }
+    const bool r16 = (args.program.ops[0].opcode & KTB_VM_ROUND16) != 0;
+    const float imm = args.program.ops[0].imm;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        if (dst[u] < 0) continue;
+        const __half2* ha = reinterpret_cast<const __half2*>(&ra[u]);
+        const __half2* hb = reinterpret_cast<const __half2*>(&rb[u]);
+        uint4 o;
+        __half2* ho = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 a = __half22float2(ha[i]);
+            const float2 b = two ? __half22float2(hb[i]) : make_float2(0.f, 0.f);
+            float x = ktb_vm_apply(OP, a.x, b.x, 0.f, imm), y = ktb_vm_apply(OP, a.y, b.y, 0.f, imm);
+            if (r16) {
+                x = ktb_round16(x);
+                y = ktb_round16(y);
+            }
+            ho[i] = __floats2half2_rn(x, y);
+        }
+        __stcs(reinterpret_cast<uint4*>(const_cast<__half*>(arena) + dst[u]), o);
+    }
+}
+
 template <int V>
 static void launch_ew(ktb_ctx* ctx, const ktb_ew_args& a, int special, uint32_t cpr, uint32_t cpi, uint64_t total) {
     const unsigned blocks = (unsigned)((total + 255) / 256);
+    bool f16 = V == 8 && special >= 0;
+    for (int i = 0; i <= a.program.n_in; ++i) f16 = f16 && a.dtype[i] == KTB_F16;
+    const unsigned fblocks = (unsigned)((total + 256 * KTB_EW_U - 1) / (256 * KTB_EW_U));
 #define KTB_EW_CASE(OP)                                                                                   \
     case OP:                                                                                              \
-        ktb_ew_stream_kernel<V, OP><<<blocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total);                 \
+        if (f16 && total < (1ull << 32))                                                                  \
+            ktb_ew_f16_kernel<KTB_EW_U, OP, uint32_t><<<fblocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total); \
+        else if (f16)                                                                                     \
+            ktb_ew_f16_kernel<KTB_EW_U, OP, uint64_t><<<fblocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total); \
+        else if (total < (1ull << 32))                                                                    \
+            ktb_ew_stream_kernel<V, OP, uint32_t><<<blocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total);   \
+        else                                                                                              \
+            ktb_ew_stream_kernel<V, OP, uint64_t><<<blocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total);   \
         break;
     switch (special) {
         KTB_EW_CASE(KTB_VM_MOV)
@@ -63,7 +132,8 @@ static void launch_ew(ktb_ctx* ctx, const ktb_ew_args& a, int special, uint32_t 
         KTB_EW_CASE(KTB_VM_MAX)
         KTB_EW_CASE(KTB_VM_MIN)
         default:
-            ktb_ew_stream_kernel<V, -1><<<blocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total);
+            if (total < (1ull << 32)) ktb_ew_stream_kernel<V, -1, uint32_t><<<blocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total);
+            else ktb_ew_stream_kernel<V, -1, uint64_t><<<blocks, 256, 0, ctx->stream>>>(a, cpr, cpi, total);
     }
 #undef KTB_EW_CASE
 }
