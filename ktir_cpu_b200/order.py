@@ -35,13 +35,46 @@ class _Runs:
         self.lo, self.hi, self.point, self.axes = lo, hi, point, tuple(axes)
         inner = int(np.prod(self.axes[1:], dtype=np.int64)) if len(self.axes) > 1 else 1
         self.core = point // max(inner, 1)
+        self.lo_min = int(lo.min()) if len(lo) else 0
+        self.hi_max = int(hi.max()) if len(hi) else 0
+        self._keys, self._shifted, self._tables = {}, None, {}
 
     def key(self, common: int) -> np.ndarray:
         """Trip indices of the first ``common`` loop axes, flattened (0 when there are none)."""
-        if not common or len(self.axes) < 1 + common:
-            return np.zeros(len(self.point), np.int64)
-        coords = np.unravel_index(self.point, self.axes)
-        return np.ravel_multi_index(coords[1:1 + common], self.axes[1:1 + common]).astype(np.int64)
+        k = self._keys.get(common)
+        if k is None:
+            if not common or len(self.axes) < 1 + common:
+                k = np.zeros(len(self.point), np.int64)
+            else:
+                coords = np.unravel_index(self.point, self.axes)
+                k = np.ravel_multi_index(coords[1:1 + common], self.axes[1:1 + common]).astype(np.int64)
+            self._keys[common] = k
+        return k
+
+    def shifted(self, span: int):
+        """(lo, hi) with every core moved into an address range of its own: runs of different cores never meet."""
+        if self._shifted is None:
+            off = self.core * span
+            self._shifted = (self.lo + off, self.hi + off)
+        return self._shifted
+
+    def table(self, common: int, span: int):
+        """Runs sorted by start, ends made monotone (a superset of the true overlaps), and a sparse table
+        for the maximum key over a range of them."""
+        t = self._tables.get(common)
+        if t is None:
+            lo, hi = self.shifted(span)
+            order = np.argsort(lo, kind="stable")
+            ka = self.key(common)[order]
+            levels = [ka]
+            w = 1
+            while 2 * w <= len(ka):
+                prev = levels[-1]
+                levels.append(np.maximum(prev[:len(prev) - w], prev[w:]))
+                w *= 2
+            t = (lo[order], np.maximum.accumulate(hi[order]), levels)
+            self._tables[common] = t
+        return t
 
 
 def _alloc_span(arena, view) -> Tuple[int, int]:
@@ -106,29 +139,18 @@ def _loads(value: Node) -> List[Node]:
     return out
 
 
-def _later_than(a: _Runs, ka: np.ndarray, b: _Runs, kb: np.ndarray, span: int, strict: bool) -> bool:
-    """True if some run of ``a`` overlaps a run of ``b`` on the same core with ``ka > kb``
-    (``strict``) or ``ka >= kb`` (not ``strict``)."""
-    if not len(a.lo) or not len(b.lo):
+def _later_than(a: _Runs, b: _Runs, common: int, span: int, strict: bool) -> bool:
+    """True if some run of ``a`` overlaps a run of ``b`` on the same core with a trip key (over the
+    first ``common`` loops) greater than b's (``strict``) or at least b's (not ``strict``)."""
+    if not len(a.lo) or not len(b.lo) or a.lo_min >= b.hi_max or b.lo_min >= a.hi_max:
         return False
-    alo, ahi = a.lo + a.core * span, a.hi + a.core * span
-    blo, bhi = b.lo + b.core * span, b.hi + b.core * span
-    if alo.min() >= bhi.max() or blo.min() >= ahi.max():
-        return False
-    order = np.argsort(alo, kind="stable")
-    alo, ahi, ka = alo[order], np.maximum.accumulate(ahi[order]), ka[order]
+    alo, ahi, levels = a.table(common, span)
+    blo, bhi = b.shifted(span)
     first = np.searchsorted(ahi, blo, side="right")      # runs before `first` end at or before b starts
     last = np.searchsorted(alo, bhi, side="left")        # runs from `last` on start at or after b ends
     has = last > first
     if not has.any():
         return False
-    # max of ka over [first, last) by a sparse table
-    levels = [ka]
-    w = 1
-    while 2 * w <= len(ka):
-        prev = levels[-1]
-        levels.append(np.maximum(prev[:len(prev) - w], prev[w:]))
-        w *= 2
     f, l = first[has], last[has]
     lg = np.floor(np.log2(np.maximum(l - f, 1))).astype(np.int64)
     best = np.empty(len(f), np.int64)
@@ -136,7 +158,8 @@ def _later_than(a: _Runs, ka: np.ndarray, b: _Runs, kb: np.ndarray, span: int, s
         m = lg == g
         t = levels[int(g)]
         best[m] = np.maximum(t[f[m]], t[l[m] - (1 << int(g))])
-    return bool((best > kb[has]).any() if strict else (best >= kb[has]).any())
+    kb = b.key(common)[has]
+    return bool((best > kb).any() if strict else (best >= kb).any())
 
 
 def program_order(stores: List[Store], arena) -> List[int]:
@@ -155,60 +178,88 @@ def program_order(stores: List[Store], arena) -> List[int]:
         if isinstance(st.target, IndirectAccess):
             del w[1:]
     reads: List[List[Tuple[_Runs, int, int]]] = []       # per store: (runs, stores traced before the load, loop depth of the load)
+    seen = {}                                            # a tile loaded once and stored several times: one set of runs
     for j, st in enumerate(stores):
         rs = []
-        for n in _loads(st.value):
-            own = tuple(n.attrs.get("axes", st.axes))
-            axes, active = (st.axes, st.active) if len(own) <= len(st.axes) else (own, None)
-            before = int(n.attrs.get("stores_before", j))
-            rs.extend((r, before, len(own) - 1) for r in _runs(n.attrs["access"], axes, active, arena))
+        for node in _loads(st.value):
+            own = tuple(node.attrs.get("axes", st.axes))
+            axes, active = (tuple(st.axes), st.active) if len(own) <= len(st.axes) else (own, None)
+            before = int(node.attrs.get("stores_before", j))
+            k = (id(node), axes, None if active is None else active.tobytes())
+            if k not in seen:
+                seen[k] = _runs(node.attrs["access"], axes, active, arena)
+            rs.extend((r, before, len(own) - 1) for r in seen[k])
         rs.extend((r, j, len(st.axes) - 1) for r in index_reads[j])
         reads.append(rs)
     # (cured by tracing the loop iteration by iteration: ``lower.lower_core_groups``)
     inverted = CoreOrderHazard("two statements inside one scf.for touch the same memory in different iterations, the "
                                "earlier statement in the later iteration: the statements cannot run one after the other")
-    after = {j: set() for j in range(len(stores))}        # after[j]: statements that must run before j
-    for j in range(1, len(stores)):
-        B = stores[j]
+    count = len(stores)
+    commons = {}
+    for j in range(1, count):
         for i in range(j):
-            A = stores[i]
-            common = 0
-            for x, y in zip(A.loop_path, B.loop_path):
+            c = 0
+            for x, y in zip(stores[i].loop_path, stores[j].loop_path):
                 if x != y:
                     break
-                common += 1
-            fwd = bwd = False                              # A before B needed / B before A needed
+                c += 1
+            commons[i, j] = c
+    # What can force a statement in front of an earlier one, or rule every order out: a tile loaded before an
+    # earlier store to its bytes, and accesses of two statements of one loop that meet in the wrong iterations.
+    bwd = set()
+    for j in range(1, count):
+        for i in range(j):
+            common = commons[i, j]
+            stale = False
             for wa in writes[i]:
                 for rb, before, depth in reads[j]:
                     # B's load against A's store.  Run after A, B sees every byte A wrote; the reference shows it
                     # those written before the load: in an earlier iteration of the loops both sit in, or in
                     # the same one if the load comes after A's store.
                     c = min(common, depth)
-                    ka, kb = wa.key(c), rb.key(c)
-                    if _later_than(wa, ka, rb, kb, span, strict=True):
+                    if c and _later_than(wa, rb, c, span, strict=True):
                         raise inverted
+                    if before <= i and not stale:
+                        stale = _later_than(wa, rb, c, span, strict=False)     # same iteration: B must read first
+                if common:
+                    for wb in writes[j]:
+                        if _later_than(wa, wb, common, span, strict=True):
+                            raise inverted
+            for ra, _, depth in reads[i]:
+                c = min(common, depth)
+                if c:
+                    for wb in writes[j]:
+                        if _later_than(ra, wb, c, span, strict=True):
+                            raise inverted
+            if stale:
+                bwd.add((i, j))
+    if not bwd:
+        return list(range(count))                         # program order works as it is
+
+    # Some statement has to move: find what else ties the pairs together (any other overlap keeps program order)
+    after = {j: set() for j in range(count)}              # after[j]: statements that must run before j
+    for j in range(1, count):
+        for i in range(j):
+            common = commons[i, j]
+            fwd = False
+            for wa in writes[i]:
+                for rb, before, depth in reads[j]:
+                    c = min(common, depth)
                     if before <= i:
-                        bwd = bwd or _later_than(wa, ka, rb, kb, span, strict=False)     # same iteration: stale
-                        fwd = fwd or (c > 0 and _later_than(rb, kb, wa, ka, span, strict=True))
+                        fwd = fwd or (c > 0 and _later_than(rb, wa, c, span, strict=True))   # bytes of earlier iterations
                     else:
-                        fwd = fwd or _later_than(rb, kb, wa, ka, span, strict=False)
+                        fwd = fwd or _later_than(rb, wa, c, span, strict=False)
                 for wb in writes[j]:
-                    ka, kb = wa.key(common), wb.key(common)
-                    if common and _later_than(wa, ka, wb, kb, span, strict=True):
-                        raise inverted
-                    fwd = fwd or _later_than(wb, kb, wa, ka, span, strict=False)       # B's bytes land last
+                    fwd = fwd or _later_than(wb, wa, common, span, strict=False)          # B's bytes land last
             for ra, _, depth in reads[i]:
                 c = min(common, depth)
                 for wb in writes[j]:
-                    ka, kb = ra.key(c), wb.key(c)
-                    if c and _later_than(ra, ka, wb, kb, span, strict=True):
-                        raise inverted
-                    fwd = fwd or _later_than(wb, kb, ra, ka, span, strict=False)       # A reads before B writes
-            if fwd and bwd:
+                    fwd = fwd or _later_than(wb, ra, c, span, strict=False)               # A reads before B writes
+            if fwd and (i, j) in bwd:
                 raise Unsupported("a tile is loaded before an earlier store to the same memory and used after it, "
                                   "by a statement that also depends on that store: the statements cannot run one "
                                   "after the other")
-            if bwd:
+            if (i, j) in bwd:
                 after[i].add(j)
             elif fwd:
                 after[j].add(i)
