@@ -135,7 +135,8 @@ __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3) ktb_row_softmax_kernel(c
     for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
         const bool live = it * groups + group < total_rows;
         const int64_t row = live ? it * groups + group : 0;
-        const int64_t item = row / a.rows_per_item;
+        // (32-bit: the launcher refuses more than 2^31 rows; a 64-bit division costs as much as a fifth of the row's arithmetic)
+        const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
         const int64_t r = row - item * a.rows_per_item;
         const int64_t in_off = a.dev_item_offsets[item * 2] + r * a.in_row_stride;
         const int64_t out_off = a.dev_item_offsets[item * 2 + 1] + r * a.out_row_stride;
@@ -290,7 +291,8 @@ ktb_row_softmax_fast_kernel(const ktb_softmax_args a, int T, int64_t total_rows)
     for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
         const bool live = it * groups + group < total_rows;
         const int64_t row = live ? it * groups + group : 0;
-        const int64_t item = row / a.rows_per_item;
+        // (32-bit: the launcher refuses more than 2^31 rows; a 64-bit division costs as much as a fifth of the row's arithmetic)
+        const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
         const int64_t r = row - item * a.rows_per_item;
         const int64_t in_off = a.dev_item_offsets[item * 2] + r * a.in_row_stride;
         const int64_t out_off = a.dev_item_offsets[item * 2 + 1] + r * a.out_row_stride;
@@ -433,6 +435,7 @@ extern "C" int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args
     if (T > 256) T = 256;             // ... unless the row is wider than 16384 elements
     const int NV = vecs / T;
     const int64_t total_rows = a.n_items * (int64_t)a.rows_per_item;
+    if (total_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_softmax", "more than 2^31 rows");
     switch (NV) {
         case 1: launch_softmax<1>(ctx, a, T, total_rows); break;
         case 2: launch_softmax<2>(ctx, a, T, total_rows); break;
