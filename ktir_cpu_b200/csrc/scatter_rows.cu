@@ -271,8 +271,19 @@ __global__ void __launch_bounds__(128) ktb_scatter_prepare_kernel(const __grid_c
             if (addr >= 0) {
                 const int64_t rel = addr - a.dst_row0;
                 // rows that do not start on a row boundary of the destination cannot be ordered by id
-                addr = (rel >= 0 && rel % a.out.idx_mult == 0 && rel / a.out.idx_mult < a.dst_rows)
-                           ? rel / a.out.idx_mult : -1;
+                // (32-bit division when the operands fit: a 64-bit one costs more than the rest of the entry)
+                int64_t q = -1, rem = 1;
+                if (rel >= 0) {
+                    if (((uint64_t)rel | (uint64_t)a.out.idx_mult) >> 32) {
+                        q = rel / a.out.idx_mult;
+                        rem = rel - q * a.out.idx_mult;
+                    } else {
+                        const uint32_t q32 = (uint32_t)rel / (uint32_t)a.out.idx_mult;
+                        q = q32;
+                        rem = (uint32_t)rel - q32 * (uint32_t)a.out.idx_mult;
+                    }
+                }
+                addr = (rem == 0 && q < a.dst_rows) ? q : -1;
             }
             s_addr[pos] = addr;
         }
