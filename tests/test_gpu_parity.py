@@ -635,3 +635,45 @@ def test_cores_run_in_order_where_they_touch_each_others_memory(build_lib):
     (sess,) = gpu._sessions.values()
     assert sess.plan.unrolled_groups == [(0, 8)] and len(sess.plan.statements) == 40
     gpu.close()
+
+
+def _tile_binop(op, rows, cols, tr, tc, cores):
+    """out[tile] = x[tile] (op) y[tile] over [tr, tc] tiles of a [rows, cols] tensor: tiles narrower than the
+    tensor, so an item has several rows with a stride; tile (i, j) belongs to core (i * ncol + j) % cores."""
+    nrow, ncol = rows // tr, cols // tc
+    per_core = nrow * ncol // cores
+    assert nrow * tr == rows and ncol * tc == cols and per_core * cores == nrow * ncol
+    t, at = f"tensor<{tr}x{tc}xf16>", f"!ktdp.access_tile<{tr}x{tc}xindex>"
+    s = (f"module {{\n  func.func @tile_binop(%x_ptr: index, %y_ptr: index, %out_ptr: index) attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %c = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n    %c1 = arith.constant 1 : index\n"
+         f"    %per = arith.constant {per_core} : index\n    %ncol = arith.constant {ncol} : index\n"
+         f"    %tr = arith.constant {tr} : index\n    %tc = arith.constant {tc} : index\n"
+         f"    %b = arith.muli %c, %per : index\n    %e = arith.addi %b, %per : index\n")
+    for nm in ("x", "y", "out"):
+        s += K_.view(nm, f"{nm}_ptr", [rows, cols], "f16")
+    s += ("    scf.for %k = %b to %e step %c1 {\n      %i = arith.divui %k, %ncol : index\n      %j = arith.remui %k, %ncol : index\n"
+          "      %r = arith.muli %i, %tr : index\n      %q = arith.muli %j, %tc : index\n")
+    for nm in ("x", "y", "out"):
+        s += K_.tile(f"{nm}t", nm, ["%r", "%q"], [tr, tc], [rows, cols], "f16", "      ")
+    s += (f"      %a = ktdp.load %xt : {at} -> {t}\n      %bb = ktdp.load %yt : {at} -> {t}\n"
+          f"      %v = {op} %a, %bb : {t}\n      ktdp.store %v, %outt : {t}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s
+
+
+@pytest.mark.parametrize("op,fn", [("arith.addf", np.add), ("arith.mulf", np.multiply), ("arith.subf", np.subtract),
+                                   ("arith.maximumf", np.maximum)])
+@pytest.mark.parametrize("rows,cols,tr,tc,cores", [(96, 320, 8, 64, 4), (60, 1000, 4, 200, 5), (33, 24, 3, 8, 11),
+                                                   (40, 36, 5, 12, 3)])
+def test_elementwise_on_strided_tiles_bit_exact(op, fn, rows, cols, tr, tc, cores, build_lib):
+    """One f16 op on tiles narrower than the tensor (several strided rows per item), chunk counts that are no
+    multiple of what a block takes, widths of 8-element vectors and widths that fall back to scalars."""
+    rng = np.random.default_rng(rows * cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float16)
+    y = rng.standard_normal((rows, cols)).astype(np.float16)
+    gpu = KTIRInterpreter()
+    gpu.load(_tile_binop(op, rows, cols, tr, tc, cores))
+    got = gpu.execute_function("tile_binop", x_ptr=x, y_ptr=y, out_ptr=np.full_like(x, 7))["out_ptr"]
+    kinds = [s.kind for sess in gpu._sessions.values() for s in sess.plan.statements]
+    gpu.close()
+    assert kinds == ["ew_stream"]
+    np.testing.assert_array_equal(got.view(np.uint16), fn(x, y).astype(np.float16).view(np.uint16))
