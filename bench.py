@@ -149,7 +149,7 @@ class VectorAdd(Workload):
 
 
 class GatherScatter(Workload):
-    name, func, kernel = "gather_scatter", "gather_scale_scatter", "ktb_scatter_apply_axpy128_kernel"
+    name, func, kernel = "gather_scatter", "gather_scale_scatter", "ktb_scatter_apply_axpy128h_kernel"
     ROWS, COLS, NIDX, TILE, CORES = 65536, 128, 262144, 64, 64
     units_per_step = NIDX * COLS
     algo_per_step = NIDX * (4 + 3 * COLS * 2)

@@ -597,6 +597,97 @@ __global__ void __launch_bounds__(256, 6) ktb_scatter_apply_axpy128_kernel(const
     }
 }
 
+// The same with TWO destination rows per warp, one per half-warp (a lane holds 8 elements), for buckets of at
+// most 16 entries: the rank and selection steps — shuffles, votes, address checks, the bulk of the
+// instructions of a row in the one-row kernel, which is issue-bound — serve both rows at once.  Order
+// and rounding are those of the kernel above.
+template <int ACC>
+#ifndef KTB_H_OCC
+#define KTB_H_OCC 4
+#endif
+__global__ void __launch_bounds__(256, KTB_H_OCC) ktb_scatter_apply_axpy128h_kernel(const __grid_constant__ ktb_rows_args a,
+                                                                           const sc_scratch sc, ktb_status* st) {
+    constexpr int K = 1 - ACC;                      // the gathered operand
+    const int lane = threadIdx.x & 31, hl = lane & 15, half = lane >> 4;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const __half* arena = reinterpret_cast<const __half*>(a.arena);
+    __half* arena_w = reinterpret_cast<__half*>(a.arena);
+    const __half2 c2 = __float2half2_rn(a.program.ops[0].imm);      // the scale is an f16 value (checked on the host)
+    const int64_t in_lo = a.in[K].lo, in_hi = a.in[K].hi - 128;
+    const int64_t* baddr = sc.bucket_addr + (int64_t)K * sc.slots;
+    const int bl = hl < sc.cap ? hl : 0;
+    int64_t row = warp * 2 + half;
+    bool have = row < a.dst_rows;
+    int cnt_n = have ? sc.count[row] : 0;
+    int32_t e_n = have ? sc.bucket_e[row * sc.cap + bl] : 0;
+    int64_t ad_n = have ? baddr[row * sc.cap + bl] : 0;
+    for (; __any_sync(0xffffffffu, have); row += n_warps * 2) {
+        have = row < a.dst_rows;
+        int cnt = have ? cnt_n : 0;
+        if (cnt > sc.cap) cnt = 0;                   // long chains are left to the general kernel
+        const int32_t e = hl < cnt ? e_n : 0x7fffffff;
+        const int64_t my_ad = ad_n;
+        const int64_t nrow = row + n_warps * 2;
+        if (nrow < a.dst_rows) {
+            cnt_n = sc.count[nrow];
+            e_n = sc.bucket_e[nrow * sc.cap + bl];
+            ad_n = baddr[nrow * sc.cap + bl];
+        }
+        const int other = __shfl_xor_sync(0xffffffffu, cnt, 16);
+        const int cmax = cnt > other ? cnt : other;  // the two halves walk their chains in step
+        if (cmax == 0) continue;
+        int rank = 0;
+        for (int j = 0; j < cmax; ++j) rank += __shfl_sync(0xffffffffu, e, j, 16) < e ? 1 : 0;
+        __half* drow = arena_w + a.dst_row0 + (have ? row : 0) * a.out.idx_mult + hl * 8;
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (cnt > 0) raw = *reinterpret_cast<const uint4*>(drow);
+        __half2* cur = reinterpret_cast<__half2*>(&raw);
+        for (int j0 = 0; j0 < cmax; j0 += 4) {
+            uint4 x[4];
+            bool use[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                x[g] = make_uint4(0u, 0u, 0u, 0u);
+                use[g] = false;
+                if (j0 + g < cmax) {                 // uniform
+                    const unsigned m = __ballot_sync(0xffffffffu, hl < cnt && rank == j0 + g);
+                    const unsigned mine = (m >> (half * 16)) & 0xffffu;       // the entry of my half, if it has one left
+                    const int64_t ad = sc_shfl64(my_ad, mine ? __ffs(mine) - 1 + half * 16 : lane);
+                    use[g] = mine != 0 && ad >= 0;   // an unresolved (negative) index was reported by prepare
+                    if (mine == 0) {
+                    } else if (ad >= in_lo && ad <= in_hi) {
+                        if ((ad & 7) == 0) {
+                            x[g] = __ldg(reinterpret_cast<const uint4*>(arena + ad + hl * 8));
+                        } else {                     // gathered rows start on multiples of 4 elements only
+                            const uint2 p0 = __ldg(reinterpret_cast<const uint2*>(arena + ad + hl * 8));
+                            const uint2 p1 = __ldg(reinterpret_cast<const uint2*>(arena + ad + hl * 8 + 4));
+                            x[g] = make_uint4(p0.x, p0.y, p1.x, p1.y);
+                        }
+                    } else if (ad >= 0 && ad + 128 > in_lo && ad < in_hi + 128) {
+                        // a row that straddles the end of its allocation: elements outside read as 0
+                        __half h[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int64_t el = ad + hl * 8 + i;
+                            h[i] = (el >= in_lo && el < in_hi + 128) ? arena[el] : __float2half(0.f);
+                        }
+                        x[g] = *reinterpret_cast<const uint4*>(h);
+                    }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                if (!use[g]) continue;
+                const __half2* xv = reinterpret_cast<const __half2*>(&x[g]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) cur[i] = __hadd2_rn(cur[i], __hmul2_rn(xv[i], c2));
+            }
+        }
+        if (cnt > 0) *reinterpret_cast<uint4*>(drow) = raw;
+    }
+}
+
 static bool sc_axpy128_ok(const ktb_rows_args& a, int acc) {
     if (a.n_in != 2 || !a.in[acc].alias_dst || a.in[1 - acc].alias_dst || !a.vector_ok || a.cols != 128) return false;
     if (a.in[0].dtype != KTB_F16 || a.in[1].dtype != KTB_F16 || a.out.dtype != KTB_F16) return false;
@@ -707,7 +798,18 @@ int ktb_scatter_rows_impl(ktb_ctx* ctx, const ktb_rows_args& a_in, int32_t* scra
     if ((prog == SC_PROG_AXPY0 || prog == SC_PROG_AXPY1) && sc_axpy128_ok(a, prog == SC_PROG_AXPY0 ? 0 : 1)) {
         int64_t fb = (R + 7) / 8;
         if (fb > (int64_t)ctx->sm_count * 6) fb = (int64_t)ctx->sm_count * 6;      // resident CTAs; rows are strided over them
-        if (prog == SC_PROG_AXPY0) ktb_scatter_apply_axpy128_kernel<0><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
+        const bool halves = sc.cap <= 16 && (a.dst_row0 % 8) == 0 && (a.out.idx_mult % 8) == 0;
+#ifdef KTB_SCATTER_NO_HALVES
+        const bool two_rows = false;
+#else
+        const bool two_rows = halves;
+#endif
+        if (two_rows) {
+            fb = (R + 15) / 16;
+            if (fb > (int64_t)ctx->sm_count * KTB_H_OCC) fb = (int64_t)ctx->sm_count * KTB_H_OCC;
+            if (prog == SC_PROG_AXPY0) ktb_scatter_apply_axpy128h_kernel<0><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
+            else ktb_scatter_apply_axpy128h_kernel<1><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
+        } else if (prog == SC_PROG_AXPY0) ktb_scatter_apply_axpy128_kernel<0><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
         else ktb_scatter_apply_axpy128_kernel<1><<<(unsigned)fb, 256, 0, ctx->stream>>>(a, sc, ctx->dev_status);
         KTB_CHECK_LAUNCH(ctx, "ktb_scatter_apply_axpy128_kernel");
         only_long = 1;
