@@ -638,6 +638,22 @@ def check_hazards(fps: List[Footprint]):
     return ordered
 
 
+def _reads_overlap_writes(fps: List[Footprint]) -> bool:
+    """True if some byte run a statement reads overlaps a run it writes without being that very run
+    (an in-place update of the same run is what the fused kernels are built for)."""
+    reads = [f for f in fps if not f.write and len(f.starts)]
+    writes = [f for f in fps if f.write and len(f.starts)]
+    if not reads or not writes:
+        return False
+    rs, re_ = np.concatenate([f.starts for f in reads]), np.concatenate([f.ends for f in reads])
+    ws, we = np.concatenate([f.starts for f in writes]), np.concatenate([f.ends for f in writes])
+    if len(rs) * len(ws) > (1 << 22):
+        return bool(rs.min() < we.max() and ws.min() < re_.max())       # too many runs to compare: go by the hulls
+    over = (rs[:, None] < we[None, :]) & (ws[None, :] < re_[:, None])
+    same = (rs[:, None] == ws[None, :]) & (re_[:, None] == we[None, :])
+    return bool((over & ~same).any())
+
+
 def launch_rounds(groups: List[np.ndarray]) -> Dict[int, int]:
     """Round of every point that shares a stored run with another point: points are taken in
     sequential (core-major) order and each goes one round after the latest earlier point it
@@ -789,13 +805,27 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
             from .lower_generic import generic_statement
             stmt = generic_statement(dev, st, arena, sid)
         plan.statements.append(stmt)
-    fps = [f for s in plan.statements for f in s.footprints()]
-    for sid, groups in check_hazards(fps).items():
-        stmt = plan.statements[sid]
-        if not hasattr(stmt, "order_points"):
-            raise CoreOrderHazard(f"several cores store to the same bytes in a {stmt.kind} statement: "
-                              "sequential core order matters and has no device path yet")
-        stmt.order_points(launch_rounds(groups))
+    pts = [_points(st) for st in stores]
+    if stores and row_shard is None and all(len(p[0]) <= 1 for p in pts) and \
+            len({int(p[1][0]) for p in pts if len(p[0])}) <= 1:
+        # One core, every store executed once: the statements run in program order as they are, nothing is
+        # concurrent.  What is left is a statement whose own inputs overlap its output (an index tensor that
+        # shares bytes with the destination, say): the step-by-step form reads everything before it writes,
+        # as the reference's load and store ops do; a fused kernel does not promise that.
+        for sid, (stmt, st) in enumerate(zip(plan.statements, stores)):
+            if stmt.kind != "generic" and _reads_overlap_writes(stmt.footprints()):
+                from .lower_generic import generic_statement
+                for ptr in getattr(stmt, "device_arrays", []):
+                    dev.free(ptr)
+                plan.statements[sid] = generic_statement(dev, st, arena, sid)
+    else:
+        fps = [f for s in plan.statements for f in s.footprints()]
+        for sid, groups in check_hazards(fps).items():
+            stmt = plan.statements[sid]
+            if not hasattr(stmt, "order_points"):
+                raise CoreOrderHazard(f"several cores store to the same bytes in a {stmt.kind} statement: "
+                                      "sequential core order matters and has no device path yet")
+            stmt.order_points(launch_rounds(groups))
     read_names, write_runs = set(), {}
     for s in plan.statements:
         for f in s.footprints():

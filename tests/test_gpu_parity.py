@@ -677,3 +677,38 @@ def test_elementwise_on_strided_tiles_bit_exact(op, fn, rows, cols, tr, tc, core
     gpu.close()
     assert kinds == ["ew_stream"]
     np.testing.assert_array_equal(got.view(np.uint16), fn(x, y).astype(np.float16).view(np.uint16))
+
+
+def _aliased_gather_source():
+    """out[i, j] = src[idx[i, j], j] at fixed addresses, the destination laid over the second half of the
+    index tensor's bytes (src: bytes 0..1024, idx: 1024..1536, out: 1280..1536)."""
+    return K_.gather_elements(8, 16, 32).replace("(%src_ptr: index, %idx_ptr: index, %out_ptr: index)", "()").replace(
+        "    %c0 = arith.constant 0 : index\n",
+        "    %c0 = arith.constant 0 : index\n    %src_ptr = arith.constant 0 : index\n"
+        "    %idx_ptr = arith.constant 256 : index\n    %out_ptr = arith.constant 640 : index\n")
+
+
+def test_a_tile_whose_index_tensor_shares_bytes_with_its_destination(build_lib):
+    """One core, one load, one store: the load reads every index before the store overwrites half of them
+    (ktir_cpu/ops/memory_ops.py:867-964), so the kernel runs in the step-by-step form, which reads
+    before it writes, and the indices that are not overwritten survive."""
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((32, 16)).astype(np.float16)
+    idx = rng.integers(0, 32, (8, 16)).astype(np.int32)
+    gpu = KTIRInterpreter()
+    gpu.load(_aliased_gather_source())
+    orig = gpu._prepare_execution
+
+    def prepare_and_seed(grid_shape):
+        orig(grid_shape)
+        gpu.memory.hbm.write(0, x.reshape(-1))
+        gpu.memory.hbm.write(8, idx.reshape(-1))                 # stick 8 = byte 1024
+    gpu._prepare_execution = prepare_and_seed
+    gpu.execute_function("gather_elements")
+    kinds = [s.kind for sess in gpu._sessions.values() for s in sess.plan.statements]
+    got = gpu.memory.hbm.read(10, 128, "f16").reshape(8, 16)     # stick 10 = byte 1280
+    kept = gpu.memory.hbm.read(8, 64, "i32")
+    gpu.close()
+    assert kinds == ["generic"]
+    np.testing.assert_array_equal(got, x[idx, np.arange(16)[None, :]])
+    np.testing.assert_array_equal(kept, idx.reshape(-1)[:64])

@@ -133,3 +133,12 @@ def test_loop_iterations_that_read_what_the_last_one_wrote_run_one_by_one(n_core
     np.testing.assert_array_equal(ora.execute_function("accumulate_rows", **{k: v.copy() for k, v in kw.items()})["acc_ptr"], want)
     got, _ = run_generic(src, "accumulate_rows", kw, core_groups=sess.plan.core_groups, unrolled=sess.plan.unrolled_groups)
     np.testing.assert_array_equal(got["acc_ptr"], want)
+
+
+def test_a_single_core_kernel_whose_index_tensor_overlaps_its_destination_plans_step_by_step():
+    """Nothing runs concurrently on one core with one load and one store; the statement only has to read
+    all its inputs before it writes — the step-by-step form does, a fused gather does not promise it."""
+    from test_gpu_parity import _aliased_gather_source
+    func = KTIRParser().parse_module(_aliased_gather_source()).get_function("gather_elements")
+    sess = Session(PlanOnlyDevice(), func, [], {}, arena_ptr=0, seeded=[(0, 1024, "f16"), (1024, 512, "i32")])
+    assert [s.kind for s in sess.plan.statements] == ["generic"]
