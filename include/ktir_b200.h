@@ -204,6 +204,50 @@ typedef struct {
 } ktb_softmax_args;
 int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args);
 
+/* ---- fused row programs: elementwise ops and row reductions in one pass over HBM ----------
+ * A statement whose value mixes elementwise ops with reductions along the last tile dimension — layer
+ * norm, RMS norm, softmax variants the softmax kernel does not take — runs as up to KTB_RP_MAX_RED
+ * reduction phases and one output phase per row.  Phase p evaluates a register program on every
+ * 8-element vector of the row (inputs: the operand tiles, then the row scalars known so far) and
+ * folds the results with `op` in the pairing order of the reference's linalg.reduce
+ * (ktir_cpu/dialects/linalg_ops.py:86-246); row scalars (mean, 1/sqrt(var + eps), ...) are register
+ * programs over the reduction results, evaluated once per row; the output phase stores its
+ * program's result.  A row is read from HBM once: later phases find it in L1/L2.  Replaces the op
+ * sequence linalg.reduce -> arith/math ops on the reduced tile -> broadcast -> elementwise ops
+ * (ktir_cpu/dialects/linalg_ops.py:136-246, 349-465; ktir_cpu/dialects/arith_ops.py:49-308) with the
+ * same rounding points.  cols: power of two in [8, 16384]; offsets and strides multiples of 8. */
+#define KTB_RP_MAX_RED 3
+#define KTB_RP_MAX_SCAL 4
+enum { KTB_RP_ADD = 0, KTB_RP_MAX = 1, KTB_RP_MAXNUM = 2 };
+typedef struct {
+    ktb_vm_program prog;      /* vector program; registers 0..n_in-1 = operand tiles, n_in..n_in+n_scal-1 = row scalars */
+    int32_t op;               /* KTB_RP_* */
+    int32_t round16;          /* 1: the fold rounds to f16 after every combine (an f16 tile is reduced) */
+    int32_t load_mask;        /* bit k: the program reads operand k */
+    int32_t reserved;
+} ktb_rp_phase;
+typedef struct {
+    ktb_vm_program prog;      /* one value per row; registers 0..n_red-1 = the reduction results */
+    int32_t ready_after;      /* index of the last reduction it reads, -1 for none; entries sorted by it */
+    int32_t reserved;
+} ktb_rp_scalar;
+typedef struct {
+    void* arena;
+    const int64_t* dev_item_offsets;   /* [n_items][n_in + 1]: operand tiles, then the output */
+    int64_t n_items;
+    int32_t rows_per_item, cols;
+    int32_t n_in, n_red, n_scal;
+    int32_t out_per_row;      /* 1: the statement stores ONE value per row (a row mean, say): `out.prog` is a program over the
+                                 reduction results like a row scalar, and row_stride[n_in] is the element distance between the
+                                 values of consecutive rows of an item */
+    int64_t row_stride[KTB_VM_MAX_IN + 1];   /* elements; inputs then output */
+    int32_t dtype[KTB_VM_MAX_IN + 1];        /* KTB_F16 / KTB_F32 */
+    ktb_rp_phase red[KTB_RP_MAX_RED];
+    ktb_rp_scalar scal[KTB_RP_MAX_SCAL];
+    ktb_rp_phase out;                        /* op unused */
+} ktb_rowprog_args;
+int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args);
+
 /* ---- row gather / ordered row scatter ---------------------------------------------
  * A statement moves E = n_tiles * tile_rows rows ("entries") of `cols` elements per
  * operand; entry (t, pos) of an operand lives at element offset

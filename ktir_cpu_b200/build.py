@@ -23,6 +23,7 @@ COMMON = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-I", INCLUDE
 PER_FILE = {
     "ew_stream.cu": ["--fmad=false"],
     "row_softmax.cu": ["--fmad=false"],
+    "row_program.cu": ["--fmad=false"],
     "scatter_rows.cu": ["--fmad=false"],
     "generic_ops.cu": ["--fmad=false"],
 }

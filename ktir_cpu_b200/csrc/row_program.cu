@@ -1,0 +1,176 @@
+// Fused row programs: elementwise ops and reductions along a row in one launch.
+//
+// A row of `cols` elements belongs to a group of T threads (T = cols / 64, between 1 and 256; thread t
+// owns the 16-byte vectors j * T + t, j < NV), a CTA of 256 threads carries 256 / T rows.  Per row
+// the kernel runs the reduction phases of the statement one after the other — evaluate the phase's
+// register program on every vector (operand tiles re-read through L1, row scalars broadcast into
+// registers), fold the values in the halving order of the reference's linalg.reduce — then the
+// scalar programs that have become computable, and finally the output program, whose result is
+// stored.  Replaces the per-op dispatch of a normalisation kernel: linalg.reduce
+// (ktir_cpu/dialects/linalg_ops.py:136-246), the arith / math ops on the reduced tile, the broadcast
+// back (linalg_ops.py:349-465) and the elementwise ops around them, with the same rounding points
+// (f16 tiles round after every op, f32 tiles do not).
+#include "row_fold.cuh"
+#include "vm.cuh"
+
+template <int NV>
+static __device__ __forceinline__ float rp_fold(const float (&x)[NV][8], const ktb_rp_phase& ph, int T, int t, int group,
+                                                float* xchg, float* bcast) {
+    if (ph.op == KTB_RP_ADD)
+        return ph.round16 ? row_fold<NV, 1, false, true>(x, T, t, group, xchg, bcast)
+                          : row_fold<NV, 1, false, false>(x, T, t, group, xchg, bcast);
+    return ph.op == KTB_RP_MAXNUM ? row_fold<NV, 0, true, false>(x, T, t, group, xchg, bcast)
+                                  : row_fold<NV, 0, false, false>(x, T, t, group, xchg, bcast);
+}
+
+static __device__ __forceinline__ void rp_load8(const void* arena, int64_t off, int dtype, float (&x)[8]) {
+    if (dtype == KTB_F16) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(arena) + off);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(h[i]);
+            x[2 * i] = f.x;
+            x[2 * i + 1] = f.y;
+        }
+    } else {
+        const float* p = reinterpret_cast<const float*>(arena) + off;
+        const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3)
+ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_t total_rows) {
+    __shared__ float xchg[256 * 8];
+    __shared__ float bcast[8];
+    const int groups = 256 / T;
+    const int group = threadIdx.x / T;
+    const int t = threadIdx.x - group * T;
+    // the trip count is the same for every thread of the CTA (the folds use group barriers and full-warp
+    // shuffles); a group past the last row recomputes row 0 and skips the store
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
+        const bool live = it * groups + group < total_rows;
+        const int64_t row = live ? it * groups + group : 0;
+        const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;      // (the launcher refuses 2^31 rows and more)
+        const int64_t r = row - item * a.rows_per_item;
+        int64_t off[KTB_VM_MAX_IN + 1];
+#pragma unroll
+        for (int k = 0; k <= KTB_VM_MAX_IN; ++k)
+            off[k] = k <= a.n_in ? a.dev_item_offsets[item * (a.n_in + 1) + k] + r * a.row_stride[k] : 0;
+
+        float red[KTB_RP_MAX_RED] = {0.f, 0.f, 0.f};
+        float scal[KTB_RP_MAX_SCAL] = {0.f, 0.f, 0.f, 0.f};
+        int scal_done = 0;
+        for (int p = 0; p <= a.n_red; ++p) {
+            if (p == a.n_red && a.out_per_row) {
+                // one value per row: a program over the reduction results, stored by the group's first thread
+                float sregs[KTB_VM_REGS][1], o[1];
+#pragma unroll
+                for (int q = 0; q < KTB_VM_REGS; ++q) sregs[q][0] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
+                ktb_vm_run<1>(a.out.prog, sregs, o);
+                if (live && t == 0) {
+                    if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[off[a.n_in]] = __float2half_rn(o[0]);
+                    else reinterpret_cast<float*>(a.arena)[off[a.n_in]] = o[0];
+                }
+                break;
+            }
+            // row scalars that only need the reductions done so far
+            for (; scal_done < a.n_scal && a.scal[scal_done].ready_after < p; ++scal_done) {
+                float sregs[KTB_VM_REGS][1], o[1];
+#pragma unroll
+                for (int q = 0; q < KTB_VM_REGS; ++q) sregs[q][0] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
+                ktb_vm_run<1>(a.scal[scal_done].prog, sregs, o);
+                scal[scal_done] = o[0];
+            }
+            const ktb_rp_phase& ph = p < a.n_red ? a.red[p] : a.out;
+            float x[NV][8];
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                float regs[KTB_VM_REGS][8];
+                const int64_t col = ((int64_t)j * T + t) * 8;
+#pragma unroll
+                for (int k = 0; k < KTB_VM_MAX_IN; ++k)
+                    if (k < a.n_in && ((ph.load_mask >> k) & 1)) rp_load8(a.arena, off[k] + col, a.dtype[k], regs[k]);
+#pragma unroll
+                for (int s = 0; s < KTB_RP_MAX_SCAL; ++s)
+                    if (s < a.n_scal && a.n_in + s < KTB_VM_REGS) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) regs[a.n_in + s][v] = scal[s];
+                    }
+                ktb_vm_run<8>(ph.prog, regs, x[j]);
+            }
+            if (p < a.n_red) {
+                red[p] = rp_fold<NV>(x, ph, T, t, group, xchg, bcast);
+            } else if (live) {
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    ktb_store_vec<8>(a.arena, off[a.n_in] + ((int64_t)j * T + t) * 8, a.dtype[a.n_in], x[j]);
+            }
+        }
+    }
+}
+
+static int rp_check_program(ktb_ctx* ctx, const ktb_vm_program& p, int n_in) {
+    if (p.n_in != n_in || p.n_ops < 0 || p.n_ops > KTB_VM_MAX_OPS || p.result_reg < 0 || p.result_reg >= KTB_VM_REGS)
+        return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad program header");
+    for (int i = 0; i < p.n_ops; ++i) {
+        const ktb_vm_op& o = p.ops[i];
+        if ((o.opcode & 0xff) >= KTB_VM_NOPS || o.dst < 0 || o.dst >= KTB_VM_REGS || o.a < 0 || o.a >= KTB_VM_REGS ||
+            o.b < 0 || o.b >= KTB_VM_REGS || o.c < 0 || o.c >= KTB_VM_REGS)
+            return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad program op");
+    }
+    return KTB_OK;
+}
+
+extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args) {
+    if (!ctx || !args) return KTB_E_ARG;
+    const ktb_rowprog_args& a = *args;
+    if (a.n_items <= 0 || a.rows_per_item <= 0) return KTB_OK;
+    if (a.n_in < 1 || a.n_in > KTB_VM_MAX_IN || a.n_red < 0 || a.n_red > KTB_RP_MAX_RED || a.n_scal < 0 ||
+        a.n_scal > KTB_RP_MAX_SCAL || a.n_in + a.n_scal > KTB_VM_REGS)
+        return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad operand / phase counts");
+    if (a.cols < 8 || a.cols > 16384 || (a.cols & (a.cols - 1)) != 0)
+        return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "cols must be a power of two in [8, 16384]");
+    for (int k = 0; k <= a.n_in; ++k) {
+        if (a.dtype[k] != KTB_F16 && a.dtype[k] != KTB_F32)
+            return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "operand dtype must be f16 or f32");
+        if (a.row_stride[k] % 8 && !(k == a.n_in && a.out_per_row))
+            return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "row strides must be multiples of 8 elements");
+    }
+    int rc;
+    for (int p = 0; p < a.n_red; ++p) {
+        if ((rc = rp_check_program(ctx, a.red[p].prog, a.n_in + a.n_scal))) return rc;
+        if (a.red[p].op != KTB_RP_ADD && a.red[p].op != KTB_RP_MAX && a.red[p].op != KTB_RP_MAXNUM)
+            return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "reduction must be add or max");
+    }
+    if ((rc = rp_check_program(ctx, a.out.prog, a.out_per_row ? a.n_red : a.n_in + a.n_scal))) return rc;
+    for (int s = 0; s < a.n_scal; ++s) {
+        if ((rc = rp_check_program(ctx, a.scal[s].prog, a.n_red))) return rc;
+        if (a.scal[s].ready_after < -1 || a.scal[s].ready_after >= a.n_red || (s && a.scal[s].ready_after < a.scal[s - 1].ready_after))
+            return ktb_fail(ctx, KTB_E_ARG, "row_program", "row scalars must be sorted by the last reduction they read");
+    }
+    const int vecs = a.cols / 8;
+    int T = vecs / 8;
+    if (T < 1) T = 1;
+    if (T > 256) T = 256;
+    const int NV = vecs / T;
+    const int64_t total_rows = a.n_items * (int64_t)a.rows_per_item;
+    if (total_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "more than 2^31 rows");
+    const int groups = 256 / T;
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    int64_t blocks = (int64_t)ctx->sm_count * 8;
+    if (blocks > n_iter) blocks = n_iter;
+    switch (NV) {
+        case 1: ktb_row_program_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
+        case 2: ktb_row_program_kernel<2><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
+        case 4: ktb_row_program_kernel<4><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
+        case 8: ktb_row_program_kernel<8><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
+        default: return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "unsupported row width");
+    }
+    KTB_CHECK_LAUNCH(ctx, "ktb_row_program_kernel");
+    return KTB_OK;
+}

@@ -1204,3 +1204,47 @@ def accumulate_rows(n_cores: int = 4, per_core: int = 6, cols: int = 64, dtype: 
           f"      %s = arith.addf %a, %b : {t}\n      ktdp.store %s, %at : {t}, {at}\n      scf.yield\n    }}\n"
           f"    return\n  }}\n}}\n")
     return s
+
+
+def rmsnorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows: int = 4, eps: float = 1e-6) -> str:
+    """y = x / sqrt(mean(x^2) + eps) per row, ``tile_rows`` rows per iteration, f32 statistics; also writes
+    the per-row 1 / sqrt(mean(x^2) + eps) — one reduction, one per-row value broadcast back, a stored
+    tile with one value per row."""
+    R = n_rows // cores
+    assert R * cores == n_rows and R % tile_rows == 0
+    t16, t32, tv = f"tensor<{tile_rows}x{n_cols}xf16>", f"tensor<{tile_rows}x{n_cols}xf32>", f"tensor<{tile_rows}xf32>"
+    at, atv = f"!ktdp.access_tile<{tile_rows}x{n_cols}xindex>", f"!ktdp.access_tile<{tile_rows}xindex>"
+    s = (f"module {{\n  func.func @rmsnorm_kernel(%x_ptr: index, %y_ptr: index, %rstd_ptr: index) "
+         f"attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n    %step = arith.constant {tile_rows} : index\n"
+         f"    %rows = arith.constant {R} : index\n"
+         f"    %row0 = arith.muli %core_id, %rows : index\n"
+         f"    %row_end = arith.addi %row0, %rows : index\n"
+         f"    %zero = arith.constant 0.0 : f32\n"
+         f"    %inv_n = arith.constant {1.0 / n_cols} : f32\n"
+         f"    %eps = arith.constant {eps} : f32\n")
+    s += view("x_view", "x_ptr", [n_rows, n_cols], "f16") + view("y_view", "y_ptr", [n_rows, n_cols], "f16")
+    s += view("rstd_view", "rstd_ptr", [n_rows], "f32")
+    s += "    scf.for %row = %row0 to %row_end step %step {\n"
+    s += tile("x_tile", "x_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += (f"      %x16 = ktdp.load %x_tile : {at} -> {t16}\n"
+          f"      %x = arith.extf %x16 : {t16} to {t32}\n"
+          f"      %sq = arith.mulf %x, %x : {t32}\n"
+          f"      %acc = tensor.splat %zero : {tv}\n"
+          f"      %ssq = linalg.reduce {{ arith.addf }} ins(%sq : {t32}) outs(%acc : {tv}) dimensions = [1]\n"
+          f"      %inv_n_t = tensor.splat %inv_n : {tv}\n"
+          f"      %ms = arith.mulf %ssq, %inv_n_t : {tv}\n"
+          f"      %eps_t = tensor.splat %eps : {tv}\n"
+          f"      %ms_eps = arith.addf %ms, %eps_t : {tv}\n"
+          f"      %rstd = math.rsqrt %ms_eps : {tv}\n"
+          f"      %bshape = tensor.empty() : {t32}\n"
+          f"      %rstd_b = linalg.broadcast ins(%rstd : {tv}) outs(%bshape : {t32}) dimensions = [1]\n"
+          f"      %y = arith.mulf %x, %rstd_b : {t32}\n"
+          f"      %y16 = arith.truncf %y : {t32} to {t16}\n")
+    s += tile("y_tile", "y_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += tile("r_tile", "rstd_view", ["%row"], [tile_rows], [n_rows], "f32", "      ")
+    s += (f"      ktdp.store %y16, %y_tile : {t16}, {at}\n"
+          f"      ktdp.store %rstd, %r_tile : {tv}, {atv}\n"
+          f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
+    return s

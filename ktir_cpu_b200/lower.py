@@ -777,6 +777,9 @@ def _fused_statement(dev, st: Store, arena: ArenaMap, sid: int, row_shard):
         from .lower_attn import try_lower_attention
         stmt = try_lower_attention(dev, st, arena, sid)
     if stmt is None:
+        from .lower_rowprog import try_lower_row_program
+        stmt = try_lower_row_program(dev, st, arena, sid)
+    if stmt is None:
         from .lower_scatter import RowsStatement, has_indirect_load
         if has_indirect_load(st.value):
             stmt = RowsStatement(dev, st, arena, sid)

@@ -1,0 +1,367 @@
+"""Lowering of statements that mix elementwise ops with reductions along the rows of a tile.
+
+Layer norm, RMS norm and the softmax forms the dedicated kernel does not take have the same shape of
+tile program: ``linalg.reduce`` over the last dimension (ktir_cpu/dialects/linalg_ops.py:136-246), a few
+ops on the reduced ``[rows]`` tile (scale by 1/n, add eps, rsqrt ...), a broadcast back to the full tile
+(linalg_ops.py:349-465) and elementwise ops around all of it.  ``RowProgramStatement`` turns such a DAG
+into the phases of ``ktb_launch_row_program``:
+
+* every ``reduce`` node becomes a reduction phase — a register program for the reduced expression,
+  evaluated per 8-element vector of a row, and the fold;
+* every broadcast of a per-row value becomes a *row scalar* — a register program over the reduction
+  results, evaluated once per row — and enters the later programs as one more input register;
+* the stored expression becomes the output phase.
+
+Rounding follows the tile dtypes as in the elementwise lowering (an op on an f16 tile rounds to f16).
+Anything that does not fit — other reductions, tiles whose rows are not a power of two long, more
+operands, scalars or registers than the kernel has — raises ``Unsupported`` and the statement runs
+step by step.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Tuple
+
+import numpy as np
+
+from . import runtime as R
+from .dtypes import bytes_per_elem
+from .lower import (F_DT, ArenaMap, Footprint, Statement, _VM_BIN, _VM_UN, _access_offsets, _copy_args,
+                    _order_item_table, _points, strip_views, tile_geom)
+from .trace import Access, Node, Store, Unsupported
+
+_RED_OPS = {"arith.addf": "add", "arith.maximumf": "max", "arith.maxnumf": "maxnum", "arith.maxf": "max"}
+
+
+def _prod(shape) -> int:
+    return int(np.prod(shape)) if len(shape) else 1
+
+
+def has_row_reduce(n: Node, seen=None) -> bool:
+    seen = seen if seen is not None else set()
+    if id(n) in seen:
+        return False
+    seen.add(id(n))
+    return n.kind == "reduce" or any(isinstance(a, Node) and has_row_reduce(a, seen) for a in n.args)
+
+
+def _canon(n: Node) -> Node:
+    """The node whose register a node shares: reshapes, casts to f32 (f16 values are exact in the f32
+    registers) and full-shape broadcasts of constants add no op."""
+    while True:
+        n = strip_views(n)
+        if n.kind == "cast" and n.dtype == "f32" and n.args[0].dtype in F_DT:
+            n = n.args[0]
+        elif n.kind == "bcast" and strip_views(n.args[0]).kind == "const":
+            n = n.args[0]
+        else:
+            return n
+
+
+class _Compiler:
+    """Register program of one expression.  ``leaves`` maps node ids to input registers; temporaries are
+    handed back as soon as their last user has been emitted, so long chains fit the eight registers."""
+
+    def __init__(self, leaves: Dict[int, int], n_in: int, elems: int):
+        self.leaves, self.n_in, self.elems = leaves, n_in, elems
+        self.ops: List[Tuple[int, int, int, int, int, float]] = []
+        self.reg_of: Dict[int, int] = {}
+        self.uses: Dict[int, int] = {}
+        self.free = list(range(R.VM_REGS - 1, n_in - 1, -1))
+        self.used_inputs = set()
+
+    def _count(self, n: Node):
+        n = _canon(n)
+        self.uses[id(n)] = self.uses.get(id(n), 0) + 1
+        if self.uses[id(n)] > 1 or id(n) in self.leaves:
+            return
+        for a in n.args:
+            self._count(a)
+
+    def _alloc(self) -> int:
+        if not self.free:
+            raise Unsupported("row program needs more than 8 live registers")
+        return self.free.pop()
+
+    def _release(self, n: Node):
+        n = _canon(n)
+        self.uses[id(n)] -= 1
+        r = self.reg_of.get(id(n))
+        if self.uses[id(n)] == 0 and r is not None and r >= self.n_in:
+            self.free.append(r)
+
+    def _emit(self, code: str, dst: int, a=0, b=0, c=0, imm=0.0, r16=False):
+        if len(self.ops) >= R.VM_MAX_OPS:
+            raise Unsupported("row program phase longer than 12 ops")
+        self.ops.append((R.VM[code] | (R.VM_ROUND16 if r16 else 0), dst, a, b, c, float(imm)))
+
+    def _visit(self, n: Node) -> int:
+        n = _canon(n)
+        if id(n) in self.leaves:
+            self.used_inputs.add(self.leaves[id(n)])
+            return self.leaves[id(n)]
+        if id(n) in self.reg_of:
+            return self.reg_of[id(n)]
+        r16 = n.dtype == "f16"
+        if n.kind == "const":
+            if n.attrs.get("list") is not None:
+                raise Unsupported("dense list constant in a row program")
+            v = n.attrs["value"]
+            v = float(np.float16(v)) if n.dtype == "f16" else float(np.float32(v))
+            r = self._alloc()
+            self._emit("CONST", r, imm=v)
+        elif n.kind == "cast":
+            if n.args[0].dtype not in F_DT or n.dtype not in F_DT:
+                raise Unsupported(f"cast {n.args[0].dtype}->{n.dtype} in a row program")
+            src = self._visit(n.args[0])
+            self._release(n.args[0])
+            r = self._alloc()
+            self._emit("MOV", r, src, r16=True)
+        elif n.kind == "ew":
+            op = n.attrs["op"]
+            if n.dtype not in F_DT:
+                raise Unsupported(f"{op} producing {n.dtype} in a row program")
+            for a in n.args:
+                ca = _canon(a)
+                if ca.kind != "const" and id(ca) not in self.leaves and _prod(ca.shape) != self.elems:
+                    raise Unsupported("operand of another shape in a row program")
+            regs = [self._visit(a) for a in n.args]
+            for a in n.args:
+                self._release(a)
+            r = self._alloc()
+            if op in _VM_BIN:
+                self._emit(_VM_BIN[op], r, regs[0], regs[1], r16=r16)
+            elif op in _VM_UN:
+                self._emit(_VM_UN[op], r, regs[0], r16=r16)
+            elif op == "math.fma":
+                self._emit("FMA", r, regs[0], regs[1], regs[2], r16=r16)
+            else:
+                raise Unsupported(f"{op} in a row program")
+        else:
+            raise Unsupported(f"{n.kind} node in a row program")
+        self.reg_of[id(n)] = r
+        return r
+
+    def compile(self, root: Node) -> R.VmProgram:
+        self._count(root)
+        res = self._visit(root)
+        p = R.VmProgram()
+        p.n_in, p.n_ops, p.result_reg = self.n_in, len(self.ops), res
+        for i, op in enumerate(self.ops):
+            p.ops[i] = R.VmOp(*op)
+        return p
+
+
+def _first_reduce(n: Node, seen=None):
+    seen = seen if seen is not None else set()
+    if id(n) in seen:
+        return None
+    seen.add(id(n))
+    if n.kind == "reduce":
+        return n
+    for a in n.args:
+        if isinstance(a, Node):
+            r = _first_reduce(a, seen)
+            if r is not None:
+                return r
+    return None
+
+
+class RowProgramStatement(Statement):
+    kind = "row_program"
+
+    def __init__(self, dev: R.Device, store: Store, arena: ArenaMap, stmt_id: int):
+        tgt = store.target
+        if not isinstance(tgt, Access) or tgt.coords is not None:
+            raise Unsupported("row program needs a plain rectangular destination tile")
+        # the tile that is reduced gives the row length; the stored tile is either of that shape or holds
+        # one value per row
+        first = _first_reduce(store.value)
+        src_shape = tuple(strip_views(first.args[0]).shape)
+        if not src_shape:
+            raise Unsupported("reduction of a scalar")
+        cols, full = int(src_shape[-1]), _prod(src_shape)
+        if cols < 8 or cols > 16384 or cols & (cols - 1):
+            raise Unsupported(f"row program over rows of {cols} elements (power of two in [8, 16384] only)")
+        rows_total = full // cols
+        per_row = _prod(tgt.shape) == rows_total and rows_total != full
+        if not per_row and _prod(tgt.shape) != full:
+            raise Unsupported("stored tile is neither the reduced tile's shape nor one value per row")
+
+        # --- the DAG: operand tiles, reductions (in dependency order), broadcast row values -------------
+        loads: List[Node] = []
+        reduces: List[Node] = []
+        scalars: List[Node] = []            # bcast nodes whose argument is a per-row value
+        seen = set()
+
+        def is_row_value(n: Node) -> bool:
+            return _prod(strip_views(n).shape) == rows_total and rows_total != full
+
+        def walk(n: Node):
+            n = strip_views(n)
+            if id(n) in seen:
+                return
+            seen.add(id(n))
+            if n.kind == "load":
+                if n.dtype not in F_DT:
+                    raise Unsupported(f"{n.dtype} tile in a row program")
+                if _prod(n.shape) != full:
+                    raise Unsupported("operand tile of another shape in a row program")
+                loads.append(n)
+                return
+            if n.kind == "reduce":
+                dims = n.attrs.get("dims")
+                src = strip_views(n.args[0])
+                if _prod(src.shape) != full or dims is None or tuple(dims) != (len(src.shape) - 1,) or \
+                        src.shape[-1] != cols:
+                    raise Unsupported("reduction that is not along the rows of the reduced tile")
+                if n.attrs["op"] not in _RED_OPS:
+                    raise Unsupported(f"row reduction with {n.attrs['op']}")
+                walk(n.args[0])
+                reduces.append(n)            # post-order: what it depends on is already listed
+                return
+            if n.kind == "bcast" and strip_views(n.args[0]).kind != "const":
+                if _prod(n.shape) != full or not is_row_value(n.args[0]) or \
+                        list(n.attrs.get("dims", [])) != [len(n.shape) - 1]:
+                    raise Unsupported("broadcast that is not a per-row value along the columns")
+                walk(n.args[0])
+                scalars.append(n)
+                return
+            if n.kind in ("const", "cast", "ew", "bcast"):
+                for a in n.args:
+                    walk(a)
+                return
+            raise Unsupported(f"{n.kind} node in a row program")
+
+        walk(store.value)
+        if len(reduces) > R.RP_MAX_RED or len(scalars) > R.RP_MAX_SCAL or len(loads) > R.VM_MAX_IN or not loads:
+            raise Unsupported("row program with more reductions, row values or operand tiles than the kernel takes")
+        n_in, n_red = len(loads), len(reduces)
+        if n_in + len(scalars) >= R.VM_REGS:
+            raise Unsupported("row program with too many inputs")
+        red_index = {id(r): k for k, r in enumerate(reduces)}
+
+        # --- row scalars: programs over the reduction results ------------------------------------------
+        def last_reduce(n: Node, memo) -> int:
+            n = strip_views(n)
+            if id(n) not in memo:
+                memo[id(n)] = red_index[id(n)] if id(n) in red_index else \
+                    max([last_reduce(a, memo) for a in n.args if isinstance(a, Node)] + [-1])
+            return memo[id(n)]
+
+        def scalar_program(root: Node) -> R.VmProgram:
+            return _Compiler(dict(red_index), n_red, rows_total).compile(root)
+
+        scal_progs = sorted(((last_reduce(s.args[0], {}), k, scalar_program(s.args[0]), s) for k, s in enumerate(scalars)),
+                            key=lambda x: x[:2])
+        scal_slot = {id(s): n_in + k for k, (_, _, _, s) in enumerate(scal_progs)}
+
+        # --- vector programs ----------------------------------------------------------------------------
+        leaves = {id(n): k for k, n in enumerate(loads)}
+        leaves.update(scal_slot)
+
+        def vector_program(root: Node):
+            comp = _Compiler(leaves, n_in + len(scalars), full)
+            prog = comp.compile(root)
+            return prog, sum(1 << r for r in comp.used_inputs if r < n_in)
+
+        self.args = a = R.RowProgArgs()
+        a.n_in, a.n_red, a.n_scal, a.out_per_row = n_in, n_red, len(scal_progs), int(per_row)
+        for k, r in enumerate(reduces):
+            ph = a.red[k]
+            ph.prog, ph.load_mask = vector_program(r.args[0])
+            ph.op = R.RP_OPS[_RED_OPS[r.attrs["op"]]]
+            ph.round16 = 1 if r.dtype == "f16" else 0
+        for k, (ready, _, prog, _) in enumerate(scal_progs):
+            a.scal[k].prog, a.scal[k].ready_after = prog, ready
+        if per_row:
+            a.out.prog, a.out.load_mask = scalar_program(store.value), 0
+        else:
+            a.out.prog, a.out.load_mask = vector_program(store.value)
+
+        # --- geometry: one table row per item, operand tiles then the destination -------------------------
+        in_accs: List[Access] = [n.attrs["access"] for n in loads]
+        expand = len(tile_geom(in_accs[0], False).lead) != 1
+        geoms = [tile_geom(acc, expand) for acc in in_accs]
+        g0 = geoms[0]
+        if g0.cols != cols or any((g.rows, g.cols, len(g.lead)) != (g0.rows, g0.cols, len(g0.lead)) for g in geoms):
+            raise Unsupported("operand tiles with another row structure in a row program")
+        sel, cores = _points(store)
+        n_lead = len(g0.lead)
+        if per_row:
+            # the stored tile has one element per row of an operand tile; its elements sit `stride` apart
+            big = [d for d, n_ in enumerate(tgt.shape) if n_ > 1]
+            if len(big) > 1 or n_lead != 1 or (big and tgt.shape[big[0]] != g0.rows):
+                raise Unsupported("per-row result tile of more than one dimension")
+            out_stride = int(tgt.strides[big[0]]) if big else 1
+        else:
+            go = tile_geom(tgt, expand)
+            if (go.rows, go.cols, len(go.lead)) != (g0.rows, g0.cols, n_lead):
+                raise Unsupported("stored tile with another row structure than the operands")
+            geoms.append(go)
+        operands = in_accs + [tgt]
+        table = np.empty((len(sel) * n_lead, len(operands)), np.int64)
+        self.fps: List[Footprint] = []
+        for k, acc in enumerate(operands):
+            is_out = k == len(operands) - 1
+            bpe = bytes_per_elem(acc.view.dtype)
+            a.dtype[k] = R.DTYPE_CODE[acc.view.dtype]
+            if is_out and per_row:
+                offs = _access_offsets(acc, store, sel).reshape(-1)
+                table[:, k] = offs
+                if len(offs):
+                    arena.check_range(int(offs.min()), int(offs.max()) + (g0.rows - 1) * out_stride + 1,
+                                      acc.view.dtype, "Scatter to")
+                rstart = (offs[:, None] + np.arange(g0.rows, dtype=np.int64)[None, :] * out_stride).reshape(-1) * bpe
+                self.fps.append(Footprint(rstart, rstart + bpe, np.repeat(sel, g0.rows), np.repeat(cores, g0.rows),
+                                          True, stmt_id))
+                a.row_stride[k] = out_stride
+                continue
+            g = geoms[k]
+            offs = (_access_offsets(acc, store, sel)[:, None] + g.lead[None, :]).reshape(-1)
+            table[:, k] = offs
+            if len(offs):
+                arena.check_range(int(offs.min()), int(offs.max()) + (g.rows - 1) * g.row_stride + g.cols,
+                                  acc.view.dtype, "Scatter to" if is_out else "Read from")
+            rstart = (offs[:, None] + np.arange(g.rows, dtype=np.int64)[None, :] * g.row_stride).reshape(-1) * bpe
+            self.fps.append(Footprint(rstart, rstart + g.cols * bpe, np.repeat(sel, n_lead * g.rows),
+                                      np.repeat(cores, n_lead * g.rows), is_out, stmt_id))
+            a.row_stride[k] = max(g.row_stride, 8) if g.rows == 1 else g.row_stride
+            if (offs % 8).any() or (g.rows > 1 and g.row_stride % 8):
+                raise Unsupported("row program needs 16-byte aligned rows")
+        a.n_items, a.rows_per_item, a.cols = table.shape[0], g0.rows, cols
+        self.table = table
+        self._sel, self._n_lead, self._dev, self.rounds = sel, n_lead, dev, None
+        self.dev_table = dev.upload(table)
+        a.dev_item_offsets = self.dev_table
+        self.device_arrays = [self.dev_table]
+        self._n_op = len(operands)
+        self._bytes = int(table.shape[0]) * g0.rows * (cols * sum(bytes_per_elem(x.view.dtype) for x in in_accs)
+                                                       + (1 if per_row else cols) * bytes_per_elem(tgt.view.dtype))
+
+    def launch(self, dev, arena_ptr):
+        self.args.arena = arena_ptr
+        if self.rounds:
+            for lo, hi in self.rounds:
+                sub = _copy_args(self.args)
+                sub.dev_item_offsets = self.dev_table + lo * self._n_op * 8
+                sub.n_items = hi - lo
+                dev.check(dev.lib.ktb_launch_row_program(dev.h, C.byref(sub)))
+            return
+        dev.check(dev.lib.ktb_launch_row_program(dev.h, C.byref(self.args)))
+
+    def order_points(self, rounds: Dict[int, int]):
+        _order_item_table(self, self._sel, self._n_lead, rounds, self._dev)
+
+    def footprints(self):
+        return self.fps
+
+    def bytes_moved(self):
+        return self._bytes
+
+
+def try_lower_row_program(dev, store: Store, arena: ArenaMap, stmt_id: int):
+    """The fused row kernel for a statement with row reductions, or None if it has none."""
+    if not isinstance(store.target, Access) or not has_row_reduce(store.value):
+        return None
+    return RowProgramStatement(dev, store, arena, stmt_id)

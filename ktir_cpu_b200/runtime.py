@@ -46,6 +46,27 @@ class EwArgs(C.Structure):
                 ("vector_ok", C.c_int32), ("program", VmProgram)]
 
 
+RP_MAX_RED, RP_MAX_SCAL = 3, 4
+RP_OPS = {"add": 0, "max": 1, "maxnum": 2}
+
+
+class RpPhase(C.Structure):
+    _fields_ = [("prog", VmProgram), ("op", C.c_int32), ("round16", C.c_int32), ("load_mask", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
+class RpScalar(C.Structure):
+    _fields_ = [("prog", VmProgram), ("ready_after", C.c_int32), ("reserved", C.c_int32)]
+
+
+class RowProgArgs(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("dev_item_offsets", C.c_void_p), ("n_items", C.c_int64),
+                ("rows_per_item", C.c_int32), ("cols", C.c_int32),
+                ("n_in", C.c_int32), ("n_red", C.c_int32), ("n_scal", C.c_int32), ("out_per_row", C.c_int32),
+                ("row_stride", C.c_int64 * (VM_MAX_IN + 1)), ("dtype", C.c_int32 * (VM_MAX_IN + 1)),
+                ("red", RpPhase * RP_MAX_RED), ("scal", RpScalar * RP_MAX_SCAL), ("out", RpPhase)]
+
+
 class SoftmaxArgs(C.Structure):
     _fields_ = [("arena", C.c_void_p), ("dev_item_offsets", C.c_void_p), ("n_items", C.c_int64),
                 ("rows_per_item", C.c_int32), ("cols", C.c_int32),
@@ -160,6 +181,7 @@ SYMBOLS = {
     "ktb_set_copy_threads": (C.c_int, [C.c_int]),
     "ktb_copy_threads": (C.c_int, []),
     "ktb_launch_ew_stream": (C.c_int, [C.c_void_p, C.POINTER(EwArgs)]),
+    "ktb_launch_row_program": (C.c_int, [C.c_void_p, C.POINTER(RowProgArgs)]),
     "ktb_launch_row_softmax": (C.c_int, [C.c_void_p, C.POINTER(SoftmaxArgs)]),
     "ktb_launch_rows_program": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),
     "ktb_launch_scatter_rows": (C.c_int, [C.c_void_p, C.POINTER(RowsArgs)]),

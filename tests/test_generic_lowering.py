@@ -131,7 +131,7 @@ def test_scratch_is_reused():
     src, fn, kw, _ = load_golden("layernorm_16x64")
     func = KTIRParser().parse_module(src).get_function(fn)
     tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items() if isinstance(v, np.ndarray)]
-    sess = Session(PlanOnlyDevice(), func, tensors, {}, arena_ptr=0)
+    sess = Session(PlanOnlyDevice(), func, tensors, {}, arena_ptr=0, fused=False)
     gen = [s for s in sess.plan.statements if s.kind == "generic"]
     assert gen, [s.kind for s in sess.plan.statements]
     for s in gen:

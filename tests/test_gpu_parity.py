@@ -712,3 +712,69 @@ def test_a_tile_whose_index_tensor_shares_bytes_with_its_destination(build_lib):
     assert kinds == ["generic"]
     np.testing.assert_array_equal(got, x[idx, np.arange(16)[None, :]])
     np.testing.assert_array_equal(kept, idx.reshape(-1)[:64])
+
+
+def _kinds(gpu):
+    return [s.kind for sess in gpu._sessions.values() for s in sess.plan.statements]
+
+
+@pytest.mark.parametrize("rows,cols,cores", [(64, 256, 4), (96, 1024, 8), (24, 4096, 4), (6, 16384, 2), (40, 8, 5), (33, 64, 3)])
+def test_layernorm_runs_as_fused_row_programs(rows, cols, cores, build_lib):
+    """Layer norm (two reductions, two per-row values broadcast back, per-column weight and bias) and its row
+    means (a tile with one value per row): both statements on the fused row kernel, compared with the oracle.
+    Sums are folded in the reference's halving order and every op rounds where the reference rounds, so the
+    results are the reference's bits."""
+    rng = np.random.default_rng(cols + rows)
+    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 3 + 1).astype(np.float16), w_ptr=rng.standard_normal(cols).astype(np.float16),
+              b_ptr=rng.standard_normal(cols).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
+              mean_ptr=np.zeros(rows, np.float32))
+    src = K_.layernorm_rows(rows, cols, cores)
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    got = gpu.execute_function("layernorm_kernel", **kw)
+    kinds = _kinds(gpu)
+    gpu.close()
+    assert kinds == ["row_program", "row_program"]
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("layernorm_kernel", **kw)
+    np.testing.assert_array_equal(got["mean_ptr"].view(np.uint32), want["mean_ptr"].view(np.uint32))
+    np.testing.assert_array_equal(got["y_ptr"].view(np.uint16), want["y_ptr"].view(np.uint16))
+
+
+@pytest.mark.parametrize("rows,cols,cores,tile_rows", [(64, 256, 4, 4), (128, 2048, 4, 8), (12, 512, 3, 2), (64, 32, 2, 16)])
+def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, build_lib):
+    rng = np.random.default_rng(rows * 7 + cols)
+    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
+              rstd_ptr=np.zeros(rows, np.float32))
+    src = K_.rmsnorm_rows(rows, cols, cores, tile_rows)
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    got = gpu.execute_function("rmsnorm_kernel", **kw)
+    kinds = _kinds(gpu)
+    gpu.close()
+    assert kinds == ["row_program", "row_program"]
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("rmsnorm_kernel", **kw)
+    np.testing.assert_array_equal(got["rstd_ptr"].view(np.uint32), want["rstd_ptr"].view(np.uint32))
+    np.testing.assert_array_equal(got["y_ptr"].view(np.uint16), want["y_ptr"].view(np.uint16))
+    np.testing.assert_array_equal(got["x_ptr"], kw["x_ptr"])
+
+
+def test_row_widths_the_row_kernel_does_not_take_run_step_by_step(build_lib):
+    """37 columns: no power of two, so the statement keeps the step-by-step form (and the reference's result)."""
+    rng = np.random.default_rng(3)
+    kw = dict(x_ptr=rng.standard_normal((16, 37)).astype(np.float16), w_ptr=rng.standard_normal(37).astype(np.float16),
+              b_ptr=rng.standard_normal(37).astype(np.float16), y_ptr=np.zeros((16, 37), np.float16), mean_ptr=np.zeros(16, np.float32))
+    src = K_.layernorm_rows(16, 37, 4)
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    got = gpu.execute_function("layernorm_kernel", **kw)
+    kinds = _kinds(gpu)
+    gpu.close()
+    assert kinds == ["generic", "generic"]
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("layernorm_kernel", **kw)
+    np.testing.assert_allclose(got["y_ptr"].astype(np.float32), want["y_ptr"].astype(np.float32), rtol=2e-3, atol=2e-3)
