@@ -41,11 +41,75 @@ static __device__ __forceinline__ void rp_load8(const void* arena, int64_t off, 
     }
 }
 
+// The interpreter's registers live in shared memory, [register][element][thread]: consecutive threads hit
+// consecutive banks, and 8 registers x 8 elements x 256 threads are 64 KB per CTA.  (As per-thread arrays
+// they were local memory, more of it per SM than L1 holds, and every op waited on L2.)
+#define RP_REG(q, v) (((q) * 8 + (v)) * 256)
+#define RP_REGS_BYTES (KTB_VM_REGS * 8 * 256 * sizeof(float))
+
+// The register program on one 8-element vector; the result stays in its register.  Not inlined on purpose:
+// the kernel calls it from every phase and vector, and a copy of the interpreter at each call site (some
+// dozens of KB of code) made the kernel wait for instructions more than for data.
+#define RP_CASE(CODE, EXPR)                                                  \
+    case CODE:                                                               \
+        _Pragma("unroll") for (int v = 0; v < 8; ++v) {                      \
+            const float a = A[v], b = B[v], c = Cc[v];                       \
+            (void)a; (void)b; (void)c;                                       \
+            R[v] = (EXPR);                                                   \
+        }                                                                    \
+        break;
+static __device__ __noinline__ void rp_vm8(const ktb_vm_program& prog, float* regs /* this thread's slice */) {
+    for (int i = 0; i < prog.n_ops; ++i) {
+        const ktb_vm_op op = prog.ops[i];
+        float A[8], B[8], Cc[8], R[8];
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+            A[v] = regs[RP_REG(op.a, v)];
+            B[v] = regs[RP_REG(op.b, v)];
+            Cc[v] = regs[RP_REG(op.c, v)];
+        }
+        const float imm = op.imm;
+        switch (op.opcode & 0xff) {
+            RP_CASE(KTB_VM_MOV, a)
+            RP_CASE(KTB_VM_CONST, imm)
+            RP_CASE(KTB_VM_ADD, a + b)
+            RP_CASE(KTB_VM_SUB, a - b)
+            RP_CASE(KTB_VM_MUL, a * b)
+            RP_CASE(KTB_VM_DIV, a / b)
+            RP_CASE(KTB_VM_SQRT, sqrtf(a))
+            default:
+#pragma unroll
+                for (int v = 0; v < 8; ++v) R[v] = ktb_vm_apply(op.opcode & 0xff, A[v], B[v], Cc[v], imm);
+        }
+        if (op.opcode & KTB_VM_ROUND16) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) R[v] = ktb_round16(R[v]);
+        }
+#pragma unroll
+        for (int v = 0; v < 8; ++v) regs[RP_REG(op.dst, v)] = R[v];
+    }
+}
+
+// ... and on one value per row (row scalars, per-row results); registers 0.. hold the reduction results.
+static __device__ __noinline__ float rp_vm1(const ktb_vm_program& prog, const float* red) {
+    float regs[KTB_VM_REGS];
+#pragma unroll
+    for (int q = 0; q < KTB_VM_REGS; ++q) regs[q] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
+    for (int i = 0; i < prog.n_ops; ++i) {
+        const ktb_vm_op op = prog.ops[i];
+        const float x = ktb_vm_apply(op.opcode & 0xff, regs[op.a], regs[op.b], regs[op.c], op.imm);
+        regs[op.dst] = (op.opcode & KTB_VM_ROUND16) ? ktb_round16(x) : x;
+    }
+    return regs[prog.result_reg];
+}
+
 template <int NV>
 __global__ void __launch_bounds__(256, NV >= 8 ? 2 : 3)
 ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_t total_rows) {
     __shared__ float xchg[256 * 8];
     __shared__ float bcast[8];
+    extern __shared__ float rp_reg_file[];
+    float* regs = rp_reg_file + threadIdx.x;
     const int groups = 256 / T;
     const int group = threadIdx.x / T;
     const int t = threadIdx.x - group * T;
@@ -68,40 +132,42 @@ ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_
         for (int p = 0; p <= a.n_red; ++p) {
             if (p == a.n_red && a.out_per_row) {
                 // one value per row: a program over the reduction results, stored by the group's first thread
-                float sregs[KTB_VM_REGS][1], o[1];
-#pragma unroll
-                for (int q = 0; q < KTB_VM_REGS; ++q) sregs[q][0] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
-                ktb_vm_run<1>(a.out.prog, sregs, o);
+                const float o = rp_vm1(a.out.prog, red);
                 if (live && t == 0) {
-                    if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[off[a.n_in]] = __float2half_rn(o[0]);
-                    else reinterpret_cast<float*>(a.arena)[off[a.n_in]] = o[0];
+                    if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[off[a.n_in]] = __float2half_rn(o);
+                    else reinterpret_cast<float*>(a.arena)[off[a.n_in]] = o;
                 }
                 break;
             }
             // row scalars that only need the reductions done so far
-            for (; scal_done < a.n_scal && a.scal[scal_done].ready_after < p; ++scal_done) {
-                float sregs[KTB_VM_REGS][1], o[1];
-#pragma unroll
-                for (int q = 0; q < KTB_VM_REGS; ++q) sregs[q][0] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
-                ktb_vm_run<1>(a.scal[scal_done].prog, sregs, o);
-                scal[scal_done] = o[0];
-            }
+            for (; scal_done < a.n_scal && a.scal[scal_done].ready_after < p; ++scal_done)
+                scal[scal_done] = rp_vm1(a.scal[scal_done].prog, red);
             const ktb_rp_phase& ph = p < a.n_red ? a.red[p] : a.out;
             float x[NV][8];
 #pragma unroll
+            for (int s = 0; s < KTB_RP_MAX_SCAL; ++s)
+                if (s < a.n_scal && a.n_in + s < KTB_VM_REGS) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) regs[RP_REG(a.n_in + s, v)] = scal[s];
+                }
+#pragma unroll
             for (int j = 0; j < NV; ++j) {
-                float regs[KTB_VM_REGS][8];
                 const int64_t col = ((int64_t)j * T + t) * 8;
+                if (ph.prog.n_ops == 0) {             // the phase reduces (or stores) an operand as it is
+                    rp_load8(a.arena, off[ph.prog.result_reg] + col, a.dtype[ph.prog.result_reg], x[j]);
+                    continue;
+                }
 #pragma unroll
                 for (int k = 0; k < KTB_VM_MAX_IN; ++k)
-                    if (k < a.n_in && ((ph.load_mask >> k) & 1)) rp_load8(a.arena, off[k] + col, a.dtype[k], regs[k]);
+                    if (k < a.n_in && ((ph.load_mask >> k) & 1)) {
+                        float in[8];
+                        rp_load8(a.arena, off[k] + col, a.dtype[k], in);
 #pragma unroll
-                for (int s = 0; s < KTB_RP_MAX_SCAL; ++s)
-                    if (s < a.n_scal && a.n_in + s < KTB_VM_REGS) {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v) regs[a.n_in + s][v] = scal[s];
+                        for (int v = 0; v < 8; ++v) regs[RP_REG(k, v)] = in[v];
                     }
-                ktb_vm_run<8>(ph.prog, regs, x[j]);
+                rp_vm8(ph.prog, regs);               // (x[] is not passed by address: it stays in registers)
+#pragma unroll
+                for (int v = 0; v < 8; ++v) x[j][v] = regs[RP_REG(ph.prog.result_reg, v)];
             }
             if (p < a.n_red) {
                 red[p] = rp_fold<NV>(x, ph, T, t, group, xchg, bcast);
@@ -153,6 +219,9 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
         if (a.scal[s].ready_after < -1 || a.scal[s].ready_after >= a.n_red || (s && a.scal[s].ready_after < a.scal[s - 1].ready_after))
             return ktb_fail(ctx, KTB_E_ARG, "row_program", "row scalars must be sorted by the last reduction they read");
     }
+    // eight vectors per thread where the row is long enough (the fold pairs the same elements whatever the
+    // split; fewer, longer threads per row need fewer exchanges between warps: layer norm 8192 x 1024 takes
+    // 133 us with 8 vectors per thread, 145 with 4, 162 with 2, 221 with 1)
     const int vecs = a.cols / 8;
     int T = vecs / 8;
     if (T < 1) T = 1;
@@ -164,11 +233,19 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
     const int64_t n_iter = (total_rows + groups - 1) / groups;
     int64_t blocks = (int64_t)ctx->sm_count * 8;
     if (blocks > n_iter) blocks = n_iter;
+    static bool ready = false;
+    if (!ready) {
+        cudaFuncSetAttribute(ktb_row_program_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RP_REGS_BYTES);
+        cudaFuncSetAttribute(ktb_row_program_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RP_REGS_BYTES);
+        cudaFuncSetAttribute(ktb_row_program_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RP_REGS_BYTES);
+        cudaFuncSetAttribute(ktb_row_program_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RP_REGS_BYTES);
+        ready = true;
+    }
     switch (NV) {
-        case 1: ktb_row_program_kernel<1><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
-        case 2: ktb_row_program_kernel<2><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
-        case 4: ktb_row_program_kernel<4><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
-        case 8: ktb_row_program_kernel<8><<<(unsigned)blocks, 256, 0, ctx->stream>>>(a, T, total_rows); break;
+        case 1: ktb_row_program_kernel<1><<<(unsigned)blocks, 256, RP_REGS_BYTES, ctx->stream>>>(a, T, total_rows); break;
+        case 2: ktb_row_program_kernel<2><<<(unsigned)blocks, 256, RP_REGS_BYTES, ctx->stream>>>(a, T, total_rows); break;
+        case 4: ktb_row_program_kernel<4><<<(unsigned)blocks, 256, RP_REGS_BYTES, ctx->stream>>>(a, T, total_rows); break;
+        case 8: ktb_row_program_kernel<8><<<(unsigned)blocks, 256, RP_REGS_BYTES, ctx->stream>>>(a, T, total_rows); break;
         default: return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "unsupported row width");
     }
     KTB_CHECK_LAUNCH(ctx, "ktb_row_program_kernel");
