@@ -97,7 +97,17 @@ static __device__ __noinline__ float rp_vm1(const ktb_vm_program& prog, const fl
     for (int q = 0; q < KTB_VM_REGS; ++q) regs[q] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
     for (int i = 0; i < prog.n_ops; ++i) {
         const ktb_vm_op op = prog.ops[i];
-        const float x = ktb_vm_apply(op.opcode & 0xff, regs[op.a], regs[op.b], regs[op.c], op.imm);
+        const float a = regs[op.a], b = regs[op.b];
+        float x;
+        switch (op.opcode & 0xff) {                      // the handful of ops row values are made of, then the rest
+            case KTB_VM_CONST: x = op.imm; break;
+            case KTB_VM_ADD: x = a + b; break;
+            case KTB_VM_SUB: x = a - b; break;
+            case KTB_VM_MUL: x = a * b; break;
+            case KTB_VM_DIV: x = a / b; break;
+            case KTB_VM_SQRT: x = sqrtf(a); break;
+            default: x = ktb_vm_apply(op.opcode & 0xff, a, b, regs[op.c], op.imm);
+        }
         regs[op.dst] = (op.opcode & KTB_VM_ROUND16) ? ktb_round16(x) : x;
     }
     return regs[prog.result_reg];
@@ -180,6 +190,215 @@ ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_
     }
 }
 
+// ---- normalisation skeletons without the interpreter --------------------------------------------------
+// The vector programs of layer norm and RMS norm are always the same few ops; only the per-row values
+// (how the mean and the scale come out of the sums) differ from kernel to kernel.  When the phases have
+// one of these shapes, all in f32,
+//     RMS:    red0 = sum(x * x);                          out = x * s [* w] [+ b]
+//     mean:   red0 = sum(x);                              (per-row result only)
+//     layer:  red0 = sum(x);  red1 = sum((x - m)^2);      out = (x - m) * s [* w] [+ b]
+// (m, s: row scalars, any programs; operands of the commutative ops in either order; an optional final
+// rounding to f16; or, instead of `out`, one value per row that is any program over the sums), the row is
+// kept in registers and the skeleton runs as straight code with the same ops in the same order — same
+// bits, a fraction of the time.  Row scalars and per-row results still go through rp_vm1.
+enum { RP_RMS = 0, RP_MEAN = 1, RP_LAYER = 2 };
+struct rp_norm {
+    int mode, has_w, has_b, out_round16;
+    int x, w, b;            // operand indices
+    int s_mean, s_scale;    // row scalar indices
+};
+
+static bool rp_is(const ktb_vm_op& o, int code) { return (o.opcode & 0xff) == code && !(o.opcode & KTB_VM_ROUND16); }
+
+// o = code(p, q) with {p, q} = {cur, other}: returns `other`, or -1
+static int rp_other(const ktb_vm_op& o, int code, int cur) {
+    if (!rp_is(o, code)) return -1;
+    if (o.a == cur) return o.b;
+    if (o.b == cur) return o.a;
+    return -1;
+}
+
+static bool rp_match_norm(const ktb_rowprog_args& a, rp_norm& m) {
+    if (a.n_red < 1 || a.n_red > 2) return false;
+    for (int p = 0; p < a.n_red; ++p)
+        if (a.red[p].op != KTB_RP_ADD || a.red[p].round16) return false;
+    const int n_in = a.n_in;
+    auto is_load = [&](int r) { return r >= 0 && r < n_in; };
+    auto is_scal = [&](int r) { return r >= n_in && r < n_in + a.n_scal; };
+    m = rp_norm{};
+    m.w = m.b = m.s_mean = m.s_scale = -1;
+    // the sums
+    const ktb_vm_program& r0 = a.red[0].prog;
+    if (r0.n_ops == 0 && is_load(r0.result_reg)) {
+        m.x = r0.result_reg;
+        m.mode = RP_MEAN;
+    } else if (r0.n_ops == 1 && rp_is(r0.ops[0], KTB_VM_MUL) && r0.ops[0].a == r0.ops[0].b && is_load(r0.ops[0].a) &&
+               r0.result_reg == r0.ops[0].dst) {
+        m.x = r0.ops[0].a;
+        m.mode = RP_RMS;
+    } else {
+        return false;
+    }
+    int mean_reg = -1;
+    if (a.n_red == 2) {
+        const ktb_vm_program& r1 = a.red[1].prog;
+        if (m.mode != RP_MEAN || r1.n_ops != 2 || !rp_is(r1.ops[0], KTB_VM_SUB) || r1.ops[0].a != m.x ||
+            !is_scal(r1.ops[0].b) || !rp_is(r1.ops[1], KTB_VM_MUL) || r1.ops[1].a != r1.ops[0].dst ||
+            r1.ops[1].b != r1.ops[0].dst || r1.result_reg != r1.ops[1].dst)
+            return false;
+        m.mode = RP_LAYER;
+        mean_reg = r1.ops[0].b;
+        m.s_mean = mean_reg - n_in;
+        if (a.scal[m.s_mean].ready_after > 0) return false;
+    }
+    if (a.out_per_row) return true;                      // any program over the sums
+    if (m.mode == RP_MEAN) return false;
+    // the stored expression
+    const ktb_vm_program& o = a.out.prog;
+    int i = 0, cur, sc;
+    if (m.mode == RP_RMS) {
+        if (o.n_ops < 1) return false;
+        sc = rp_other(o.ops[0], KTB_VM_MUL, m.x);
+        cur = o.ops[0].dst;
+        i = 1;
+    } else {
+        if (o.n_ops < 2 || !rp_is(o.ops[0], KTB_VM_SUB) || o.ops[0].a != m.x || o.ops[0].b != mean_reg) return false;
+        sc = rp_other(o.ops[1], KTB_VM_MUL, o.ops[0].dst);
+        cur = o.ops[1].dst;
+        i = 2;
+    }
+    if (!is_scal(sc) || sc == mean_reg) return false;
+    m.s_scale = sc - n_in;
+    if (i < o.n_ops) {                                   // [* w]
+        const int w = rp_other(o.ops[i], KTB_VM_MUL, cur);
+        if (is_load(w) && w != m.x) {
+            m.w = w;
+            m.has_w = 1;
+            cur = o.ops[i++].dst;
+        }
+    }
+    if (i < o.n_ops) {                                   // [+ b]
+        const int b = rp_other(o.ops[i], KTB_VM_ADD, cur);
+        if (is_load(b) && b != m.x && b != m.w) {
+            m.b = b;
+            m.has_b = 1;
+            cur = o.ops[i++].dst;
+        }
+    }
+    if (i < o.n_ops && (o.ops[i].opcode & 0xff) == KTB_VM_MOV && (o.ops[i].opcode & KTB_VM_ROUND16) && o.ops[i].a == cur) {
+        m.out_round16 = 1;
+        cur = o.ops[i++].dst;
+    }
+    return i == o.n_ops && o.result_reg == cur;
+}
+
+template <int NV, int MODE, bool PER_ROW>
+__global__ void __launch_bounds__(256, NV >= 8 ? 1 : 2)
+ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m, int T, int64_t total_rows) {
+    __shared__ float xchg[256 * 8];
+    __shared__ float bcast[8];
+    __shared__ float s_red[256][KTB_RP_MAX_RED];
+    __shared__ float s_scal[256][KTB_RP_MAX_SCAL];
+    const int groups = 256 / T;
+    const int group = threadIdx.x / T;
+    const int t = threadIdx.x - group * T;
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
+        const bool live = it * groups + group < total_rows;
+        const int64_t row = live ? it * groups + group : 0;
+        const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
+        const int64_t r = row - item * a.rows_per_item;
+        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1);
+        const int64_t x_off = offs[m.x] + r * a.row_stride[m.x];
+        const int64_t y_off = offs[a.n_in] + r * a.row_stride[a.n_in];
+        float x[NV][8];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) rp_load8(a.arena, x_off + ((int64_t)j * T + t) * 8, a.dtype[m.x], x[j]);
+
+        // Row values are computed "sideways": the first thread of every row group parks the row's sums, then
+        // thread g of the CTA runs the scalar programs of row g — all rows of the CTA in the lanes of one or
+        // a few warps instead of the same program once per warp of every row.
+        float mean = 0.f;
+        if (MODE != RP_RMS) {
+            const float r0 = row_fold<NV, 1, false, false>(x, T, t, group, xchg, bcast);
+            if (t == 0) s_red[group][0] = r0;
+            if (MODE == RP_LAYER) {
+                __syncthreads();
+                if (threadIdx.x < groups && a.scal[m.s_mean].ready_after < 1)
+                    s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x]);
+                __syncthreads();
+                mean = s_scal[group][m.s_mean];
+            }
+        }
+        if (MODE != RP_MEAN) {
+            float sq[NV][8];
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const float d = MODE == RP_LAYER ? x[j][v] - mean : x[j][v];
+                    sq[j][v] = d * d;
+                }
+            const float r1 = row_fold<NV, 1, false, false>(sq, T, t, group, xchg, bcast);
+            if (t == 0) s_red[group][MODE == RP_LAYER ? 1 : 0] = r1;
+        }
+        __syncthreads();
+        if (threadIdx.x < groups) {
+            const int64_t grow = it * groups + threadIdx.x;
+            if (PER_ROW) {
+                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x]);
+                if (grow < total_rows) {
+                    const int64_t gitem = (uint32_t)grow / (uint32_t)a.rows_per_item;
+                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1) + a.n_in] +
+                                       (grow - gitem * a.rows_per_item) * a.row_stride[a.n_in];
+                    if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[go] = __float2half_rn(o);
+                    else reinterpret_cast<float*>(a.arena)[go] = o;
+                }
+            } else {
+                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x]);
+            }
+        }
+        __syncthreads();                                 // (also keeps the next iteration's sums off this one's readers)
+        if (PER_ROW) continue;
+        float scal[KTB_RP_MAX_SCAL];
+#pragma unroll
+        for (int q = 0; q < KTB_RP_MAX_SCAL; ++q) scal[q] = s_scal[group][q];
+        const float scale = scal[m.s_scale];
+        if (!live) continue;
+        const int64_t w_off = m.has_w ? offs[m.w] + r * a.row_stride[m.w] : 0;
+        const int64_t b_off = m.has_b ? offs[m.b] + r * a.row_stride[m.b] : 0;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const int64_t col = ((int64_t)j * T + t) * 8;
+            float y[8], w[8], b[8];
+            if (m.has_w) rp_load8(a.arena, w_off + col, a.dtype[m.w], w);
+            if (m.has_b) rp_load8(a.arena, b_off + col, a.dtype[m.b], b);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                float q = MODE == RP_LAYER ? x[j][v] - mean : x[j][v];
+                q = q * scale;
+                if (m.has_w) q = q * w[v];
+                if (m.has_b) q = q + b[v];
+                y[v] = m.out_round16 ? ktb_round16(q) : q;
+            }
+            ktb_store_vec<8>(a.arena, y_off + col, a.dtype[a.n_in], y);
+        }
+    }
+}
+
+template <int NV>
+static void rp_launch_norm(ktb_ctx* ctx, const ktb_rowprog_args& a, const rp_norm& m, unsigned blocks, int T, int64_t total_rows) {
+#define RP_NORM(M, P) ktb_row_norm_kernel<NV, M, P><<<blocks, 256, 0, ctx->stream>>>(a, m, T, total_rows)
+    switch (m.mode * 2 + (a.out_per_row ? 1 : 0)) {
+        case RP_RMS * 2: RP_NORM(RP_RMS, false); break;
+        case RP_RMS * 2 + 1: RP_NORM(RP_RMS, true); break;
+        case RP_MEAN * 2 + 1: RP_NORM(RP_MEAN, true); break;
+        case RP_LAYER * 2: RP_NORM(RP_LAYER, false); break;
+        default: RP_NORM(RP_LAYER, true); break;
+    }
+#undef RP_NORM
+}
+
 static int rp_check_program(ktb_ctx* ctx, const ktb_vm_program& p, int n_in) {
     if (p.n_in != n_in || p.n_ops < 0 || p.n_ops > KTB_VM_MAX_OPS || p.result_reg < 0 || p.result_reg >= KTB_VM_REGS)
         return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad program header");
@@ -233,6 +452,27 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
     const int64_t n_iter = (total_rows + groups - 1) / groups;
     int64_t blocks = (int64_t)ctx->sm_count * 8;
     if (blocks > n_iter) blocks = n_iter;
+#ifndef KTB_RP_NO_NORM
+    rp_norm nm;
+    if (rp_match_norm(a, nm)) {
+        // four vectors per thread (the row and its squares sit in registers): two CTAs per SM
+        int Tn = vecs / 4;
+        if (Tn < 1) Tn = 1;
+        if (Tn > 256) Tn = 256;
+        const int NVn = vecs / Tn, gn = 256 / Tn;
+        const int64_t iters = (total_rows + gn - 1) / gn;
+        const unsigned bn = (unsigned)(iters < (int64_t)ctx->sm_count * 4 ? iters : (int64_t)ctx->sm_count * 4);
+        switch (NVn) {
+            case 1: rp_launch_norm<1>(ctx, a, nm, bn, Tn, total_rows); break;
+            case 2: rp_launch_norm<2>(ctx, a, nm, bn, Tn, total_rows); break;
+            case 4: rp_launch_norm<4>(ctx, a, nm, bn, Tn, total_rows); break;
+            case 8: rp_launch_norm<8>(ctx, a, nm, bn, Tn, total_rows); break;
+            default: return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "unsupported row width");
+        }
+        KTB_CHECK_LAUNCH(ctx, "ktb_row_norm_kernel");
+        return KTB_OK;
+    }
+#endif
     static bool ready = false;
     if (!ready) {
         cudaFuncSetAttribute(ktb_row_program_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RP_REGS_BYTES);
