@@ -1,0 +1,139 @@
+"""Row-program lowering (host logic, no GPU): the phases, row scalars and register programs that
+``lower_rowprog.RowProgramStatement`` hands to ``ktb_launch_row_program`` are replayed in NumPy — register
+programs op by op with f16 rounding where flagged, reductions folded x[i] (op) x[i + h] like the
+reference's linalg.reduce (ktir_cpu/dialects/linalg_ops.py:86-133) — and compared with the oracle."""
+import numpy as np
+import pytest
+
+from ktir_cpu_b200 import kernels as K
+from ktir_cpu_b200 import runtime as R
+from ktir_cpu_b200.interpreter import Session, arena_layout
+from ktir_cpu_b200.parser import KTIRParser
+from oracle.numpy_interp import OracleInterpreter
+from test_row_forms import RecordingDevice
+
+NAMES = {v: k for k, v in R.VM.items()}
+
+
+def run_program(prog, inputs):
+    """``inputs``: list of float32 arrays (one per input register); returns the result register."""
+    regs = list(inputs) + [None] * (R.VM_REGS - len(inputs))
+    for o in list(prog.ops)[:prog.n_ops]:
+        a, b = regs[o.a], regs[o.b]
+        name = NAMES[o.opcode & 0xff]
+        with np.errstate(all="ignore"):
+            x = {"MOV": lambda: a, "CONST": lambda: np.float32(o.imm), "ADD": lambda: a + b, "SUB": lambda: a - b,
+                 "MUL": lambda: a * b, "DIV": lambda: a / b, "SQRT": lambda: np.sqrt(a)}[name]()
+        x = np.asarray(x, np.float32)
+        regs[o.dst] = x.astype(np.float16).astype(np.float32) if o.opcode & R.VM_ROUND16 else x
+    return regs[prog.result_reg]
+
+
+def fold(x, op, r16):
+    """x: [rows, cols] float32, cols a power of two; pairs (i, i + h), h = cols / 2 ... 1."""
+    x = x.copy()
+    while x.shape[1] > 1:
+        h = x.shape[1] // 2
+        x = (x[:, :h] + x[:, h:]) if op == R.RP_OPS["add"] else np.maximum(x[:, :h], x[:, h:])
+        if r16:
+            x = x.astype(np.float16).astype(np.float32)
+    return x[:, 0]
+
+
+def replay(stmt, dev, arena):
+    a = stmt.args
+    table = dev.arrays[a.dev_item_offsets].reshape(a.n_items, a.n_in + 1)
+    npdt = {R.DTYPE_CODE["f16"]: np.float16, R.DTYPE_CODE["f32"]: np.float32}
+    R_, Ccols = a.rows_per_item, a.cols
+    r = np.arange(R_)[None, :, None]
+    c = np.arange(Ccols)[None, None, :]
+
+    def tile(k):
+        mem = arena.view(npdt[a.dtype[k]])
+        idx = table[:, k][:, None, None] + r * a.row_stride[k] + c
+        return mem[idx].astype(np.float32).reshape(-1, Ccols)                  # [rows, cols]
+
+    loads = [tile(k) for k in range(a.n_in)]
+    rows = loads[0].shape[0]
+    red, scal, done = [], [None] * a.n_scal, 0
+    for p in range(a.n_red + 1):
+        while done < a.n_scal and a.scal[done].ready_after < p:
+            scal[done] = run_program(a.scal[done].prog, red + [np.zeros(rows, np.float32)] * (a.n_red - len(red)))
+            done += 1
+        if p == a.n_red and a.out_per_row:
+            out = run_program(a.out.prog, red)
+            mem = arena.view(npdt[a.dtype[a.n_in]])
+            idx = (table[:, a.n_in][:, None] + np.arange(R_)[None, :] * a.row_stride[a.n_in]).reshape(-1)
+            mem[idx] = out.astype(mem.dtype)
+            return
+        ph = a.red[p] if p < a.n_red else a.out
+        ins = loads + [np.broadcast_to(s[:, None], (rows, Ccols)) if s is not None else None for s in scal]
+        val = np.broadcast_to(run_program(ph.prog, ins), (rows, Ccols)).astype(np.float32)
+        if p < a.n_red:
+            red.append(fold(val, ph.op, bool(ph.round16)))
+        else:
+            mem = arena.view(npdt[a.dtype[a.n_in]])
+            idx = (table[:, a.n_in][:, None, None] + r * a.row_stride[a.n_in] + c).reshape(-1, Ccols)
+            mem[idx] = val.astype(mem.dtype)
+
+
+def plan_and_replay(src, fn, kw):
+    func = KTIRParser().parse_module(src).get_function(fn)
+    tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items()]
+    dev = RecordingDevice()
+    sess = Session(dev, func, tensors, {}, arena_ptr=0)
+    layout, _ = arena_layout(tensors)
+    arena = np.zeros(max(o + n for o, n, _, _ in layout.values()) + 256, np.uint8)
+    for name, (off, nb, _, _) in layout.items():
+        arena[off:off + nb] = np.ascontiguousarray(kw[name]).view(np.uint8).reshape(-1)
+    for stmt in sess.plan.statements:
+        assert stmt.kind == "row_program"
+        replay(stmt, dev, arena)
+    return {name: arena[off:off + nb].view(dt).reshape(shape).copy() for name, (off, nb, shape, dt) in layout.items()}, sess
+
+
+@pytest.mark.parametrize("rows,cols,cores", [(16, 64, 4), (12, 1024, 3), (8, 8, 2)])
+def test_layernorm_phases_give_the_oracle_bits(rows, cols, cores):
+    rng = np.random.default_rng(rows + cols)
+    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2 + 1).astype(np.float16), w_ptr=rng.standard_normal(cols).astype(np.float16),
+              b_ptr=rng.standard_normal(cols).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
+              mean_ptr=np.zeros(rows, np.float32))
+    src = K.layernorm_rows(rows, cols, cores)
+    got, sess = plan_and_replay(src, "layernorm_kernel", kw)
+    y_stmt, m_stmt = sess.plan.statements
+    assert (y_stmt.args.n_red, y_stmt.args.n_scal, y_stmt.args.out_per_row) == (2, 2, 0)
+    assert (m_stmt.args.n_red, m_stmt.args.n_scal, m_stmt.args.out_per_row) == (1, 0, 1)
+    assert y_stmt.args.red[0].prog.n_ops == 0 and y_stmt.args.out.load_mask == 0b111      # sum of x as it is; x, w, b at the end
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("layernorm_kernel", **kw)
+    for k in ("y_ptr", "mean_ptr"):
+        np.testing.assert_array_equal(got[k].view(np.uint8), want[k].view(np.uint8), err_msg=k)
+
+
+@pytest.mark.parametrize("rows,cols,cores,tile_rows", [(16, 64, 2, 4), (8, 256, 1, 8)])
+def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows):
+    rng = np.random.default_rng(cols)
+    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
+              rstd_ptr=np.zeros(rows, np.float32))
+    src = K.rmsnorm_rows(rows, cols, cores, tile_rows)
+    got, sess = plan_and_replay(src, "rmsnorm_kernel", kw)
+    assert [s.args.rows_per_item for s in sess.plan.statements] == [tile_rows, tile_rows]
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("rmsnorm_kernel", **kw)
+    for k in ("y_ptr", "rstd_ptr"):
+        np.testing.assert_array_equal(got[k].view(np.uint8), want[k].view(np.uint8), err_msg=k)
+
+
+def test_registers_are_reused_and_misfits_are_refused():
+    from ktir_cpu_b200.runtime import PlanOnlyDevice
+    f16, f32 = np.dtype(np.float16), np.dtype(np.float32)
+    t = [("x_ptr", (16, 48), f16), ("w_ptr", (48,), f16), ("b_ptr", (48,), f16), ("y_ptr", (16, 48), f16), ("mean_ptr", (16,), f32)]
+    sess = Session(PlanOnlyDevice(), KTIRParser().parse_module(K.layernorm_rows(16, 48, 4)).get_function("layernorm_kernel"), t, {}, arena_ptr=0)
+    assert [s.kind for s in sess.plan.statements] == ["generic", "generic"]          # 48 columns: no power of two
+    t = [(n, (16, 64) if s == (16, 48) else (64,) if s == (48,) else s, d) for n, s, d in t]
+    sess = Session(PlanOnlyDevice(), KTIRParser().parse_module(K.layernorm_rows(16, 64, 4)).get_function("layernorm_kernel"), t, {}, arena_ptr=0)
+    out = sess.plan.statements[0].args.out.prog
+    regs = {o.dst for o in list(out.ops)[:out.n_ops]}
+    assert out.n_ops == 5 and len(regs) == 1                     # sub, mul, mul, add, round: one temporary, reused
