@@ -293,7 +293,7 @@ static bool rp_match_norm(const ktb_rowprog_args& a, rp_norm& m) {
 }
 
 template <int NV, int MODE, bool PER_ROW>
-__global__ void __launch_bounds__(256, NV >= 8 ? 1 : 2)
+__global__ void __launch_bounds__(256, NV >= 8 ? 1 : NV >= 4 ? 2 : NV >= 2 ? 3 : 4)
 ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m, int T, int64_t total_rows) {
     __shared__ float xchg[256 * 8];
     __shared__ float bcast[8];
@@ -456,7 +456,10 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
     rp_norm nm;
     if (rp_match_norm(a, nm)) {
         // four vectors per thread (the row and its squares sit in registers): two CTAs per SM
-        int Tn = vecs / 4;
+#ifndef KTB_RP_NORM_VPT
+#define KTB_RP_NORM_VPT 4
+#endif
+        int Tn = vecs / KTB_RP_NORM_VPT;
         if (Tn < 1) Tn = 1;
         if (Tn > 256) Tn = 256;
         const int NVn = vecs / Tn, gn = 256 / Tn;
