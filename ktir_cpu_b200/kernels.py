@@ -1248,3 +1248,41 @@ def rmsnorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows:
           f"      ktdp.store %rstd, %r_tile : {tv}, {atv}\n"
           f"      scf.yield\n    }}\n    return\n  }}\n}}\n")
     return s
+
+
+def log_softmax_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows: int = 2) -> str:
+    """y = x - max(x) - log(sum(exp(x - max(x)))) per row, f32 arithmetic on f16 data: two reductions
+    (maxnumf, addf), the second over an expression of the first, and an output that uses both."""
+    R = n_rows // cores
+    assert R * cores == n_rows and R % tile_rows == 0
+    t16, t32, tv = f"tensor<{tile_rows}x{n_cols}xf16>", f"tensor<{tile_rows}x{n_cols}xf32>", f"tensor<{tile_rows}xf32>"
+    at = f"!ktdp.access_tile<{tile_rows}x{n_cols}xindex>"
+    s = (f"module {{\n  func.func @log_softmax_kernel(%x_ptr: index, %y_ptr: index) attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n"
+         f"    %c0 = arith.constant 0 : index\n    %step = arith.constant {tile_rows} : index\n"
+         f"    %rows = arith.constant {R} : index\n"
+         f"    %row0 = arith.muli %core_id, %rows : index\n"
+         f"    %row_end = arith.addi %row0, %rows : index\n"
+         f"    %zero = arith.constant 0.0 : f32\n"
+         f"    %ninf_bits = arith.constant 0xFF800000 : i32\n"
+         f"    %ninf = arith.bitcast %ninf_bits : i32 to f32\n")
+    s += view("x_view", "x_ptr", [n_rows, n_cols], "f16") + view("y_view", "y_ptr", [n_rows, n_cols], "f16")
+    s += "    scf.for %row = %row0 to %row_end step %step {\n"
+    s += tile("x_tile", "x_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += (f"      %x16 = ktdp.load %x_tile : {at} -> {t16}\n"
+          f"      %x = arith.extf %x16 : {t16} to {t32}\n"
+          f"      %m0 = tensor.splat %ninf : {tv}\n"
+          f"      %mx = linalg.reduce {{ arith.maxnumf }} ins(%x : {t32}) outs(%m0 : {tv}) dimensions = [1]\n"
+          f"      %bshape = tensor.empty() : {t32}\n"
+          f"      %mx_b = linalg.broadcast ins(%mx : {tv}) outs(%bshape : {t32}) dimensions = [1]\n"
+          f"      %xc = arith.subf %x, %mx_b : {t32}\n"
+          f"      %e = math.exp %xc : {t32}\n"
+          f"      %s0 = tensor.splat %zero : {tv}\n"
+          f"      %sum = linalg.reduce {{ arith.addf }} ins(%e : {t32}) outs(%s0 : {tv}) dimensions = [1]\n"
+          f"      %lse = math.log %sum : {tv}\n"
+          f"      %lse_b = linalg.broadcast ins(%lse : {tv}) outs(%bshape : {t32}) dimensions = [1]\n"
+          f"      %y = arith.subf %xc, %lse_b : {t32}\n"
+          f"      %y16 = arith.truncf %y : {t32} to {t16}\n")
+    s += tile("y_tile", "y_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
+    s += f"      ktdp.store %y16, %y_tile : {t16}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n"
+    return s

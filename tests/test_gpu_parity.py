@@ -763,6 +763,26 @@ def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, build_lib):
     np.testing.assert_array_equal(got["x_ptr"], kw["x_ptr"])
 
 
+@pytest.mark.parametrize("rows,cols,cores,tile_rows", [(64, 256, 4, 2), (32, 4096, 4, 1), (48, 64, 3, 8)])
+def test_log_softmax_on_the_interpreting_row_kernel(rows, cols, cores, tile_rows, build_lib):
+    """Phases that are no normalisation skeleton (max with maxnumf, exp, log): the interpreting row kernel.
+    exp and log are the device's, so the comparison with the oracle carries the f16 tolerance."""
+    rng = np.random.default_rng(rows + cols)
+    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 3).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16))
+    src = K_.log_softmax_rows(rows, cols, cores, tile_rows)
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    got = gpu.execute_function("log_softmax_kernel", **kw)
+    kinds = _kinds(gpu)
+    gpu.close()
+    assert kinds == ["row_program"]
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("log_softmax_kernel", **kw)
+    np.testing.assert_allclose(got["y_ptr"].astype(np.float32), want["y_ptr"].astype(np.float32), rtol=2e-3, atol=2e-3)
+    np.testing.assert_allclose(np.exp(got["y_ptr"].astype(np.float64)).sum(1), 1.0, atol=2e-2)
+
+
 def test_row_widths_the_row_kernel_does_not_take_run_step_by_step(build_lib):
     """37 columns: no power of two, so the statement keeps the step-by-step form (and the reference's result)."""
     rng = np.random.default_rng(3)

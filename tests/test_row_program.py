@@ -23,7 +23,8 @@ def run_program(prog, inputs):
         name = NAMES[o.opcode & 0xff]
         with np.errstate(all="ignore"):
             x = {"MOV": lambda: a, "CONST": lambda: np.float32(o.imm), "ADD": lambda: a + b, "SUB": lambda: a - b,
-                 "MUL": lambda: a * b, "DIV": lambda: a / b, "SQRT": lambda: np.sqrt(a)}[name]()
+                 "MUL": lambda: a * b, "DIV": lambda: a / b, "SQRT": lambda: np.sqrt(a), "EXP": lambda: np.exp(a),
+                 "LOG": lambda: np.log(a), "MAXNUM": lambda: np.fmax(a, b)}[name]()
         x = np.asarray(x, np.float32)
         regs[o.dst] = x.astype(np.float16).astype(np.float32) if o.opcode & R.VM_ROUND16 else x
     return regs[prog.result_reg]
@@ -34,7 +35,8 @@ def fold(x, op, r16):
     x = x.copy()
     while x.shape[1] > 1:
         h = x.shape[1] // 2
-        x = (x[:, :h] + x[:, h:]) if op == R.RP_OPS["add"] else np.maximum(x[:, :h], x[:, h:])
+        x = (x[:, :h] + x[:, h:]) if op == R.RP_OPS["add"] else \
+            np.fmax(x[:, :h], x[:, h:]) if op == R.RP_OPS["maxnum"] else np.maximum(x[:, :h], x[:, h:])
         if r16:
             x = x.astype(np.float16).astype(np.float32)
     return x[:, 0]
@@ -124,6 +126,20 @@ def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows):
     want = ora.execute_function("rmsnorm_kernel", **kw)
     for k in ("y_ptr", "rstd_ptr"):
         np.testing.assert_array_equal(got[k].view(np.uint8), want[k].view(np.uint8), err_msg=k)
+
+
+def test_log_softmax_uses_two_kinds_of_reduction():
+    """max (maxnumf) and sum of an expression of the max, an output that uses both row values."""
+    rng = np.random.default_rng(8)
+    kw = dict(x_ptr=(rng.standard_normal((16, 128)) * 3).astype(np.float16), y_ptr=np.zeros((16, 128), np.float16))
+    src = K.log_softmax_rows(16, 128, 2, 4)
+    got, sess = plan_and_replay(src, "log_softmax_kernel", kw)
+    a = sess.plan.statements[0].args
+    assert [a.red[k].op for k in range(a.n_red)] == [R.RP_OPS["maxnum"], R.RP_OPS["add"]] and a.n_scal == 2
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("log_softmax_kernel", **kw)
+    np.testing.assert_array_equal(got["y_ptr"].view(np.uint16), want["y_ptr"].view(np.uint16))
 
 
 def test_registers_are_reused_and_misfits_are_refused():
