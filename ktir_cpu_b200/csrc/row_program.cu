@@ -293,7 +293,10 @@ static bool rp_match_norm(const ktb_rowprog_args& a, rp_norm& m) {
 }
 
 template <int NV, int MODE, bool PER_ROW>
-__global__ void __launch_bounds__(256, NV >= 8 ? 1 : NV >= 4 ? 2 : NV >= 2 ? 3 : 4)
+#ifndef KTB_RP_NORM_OCC
+#define KTB_RP_NORM_OCC 3
+#endif
+__global__ void __launch_bounds__(256, NV >= 8 ? 1 : NV >= 4 ? KTB_RP_NORM_OCC : NV >= 2 ? 3 : 4)
 ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m, int T, int64_t total_rows) {
     __shared__ float xchg[256 * 8];
     __shared__ float bcast[8];
