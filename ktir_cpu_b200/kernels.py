@@ -1206,15 +1206,18 @@ def accumulate_rows(n_cores: int = 4, per_core: int = 6, cols: int = 64, dtype: 
     return s
 
 
-def rmsnorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows: int = 4, eps: float = 1e-6) -> str:
+def rmsnorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows: int = 4, eps: float = 1e-6,
+                 weight: bool = False) -> str:
     """y = x / sqrt(mean(x^2) + eps) per row, ``tile_rows`` rows per iteration, f32 statistics; also writes
     the per-row 1 / sqrt(mean(x^2) + eps) — one reduction, one per-row value broadcast back, a stored
-    tile with one value per row."""
+    tile with one value per row.  ``weight``: y is also multiplied by a weight row ``w[n_cols]`` that is
+    loaded once and broadcast over the rows of every tile (``%w_ptr`` becomes the second argument)."""
     R = n_rows // cores
     assert R * cores == n_rows and R % tile_rows == 0
     t16, t32, tv = f"tensor<{tile_rows}x{n_cols}xf16>", f"tensor<{tile_rows}x{n_cols}xf32>", f"tensor<{tile_rows}xf32>"
     at, atv = f"!ktdp.access_tile<{tile_rows}x{n_cols}xindex>", f"!ktdp.access_tile<{tile_rows}xindex>"
-    s = (f"module {{\n  func.func @rmsnorm_kernel(%x_ptr: index, %y_ptr: index, %rstd_ptr: index) "
+    wv = f"tensor<{n_cols}xf16>", f"tensor<{n_cols}xf32>", f"!ktdp.access_tile<{n_cols}xindex>"
+    s = (f"module {{\n  func.func @rmsnorm_kernel(%x_ptr: index, {'%w_ptr: index, ' if weight else ''}%y_ptr: index, %rstd_ptr: index) "
          f"attributes {{grid = [{cores}, 1]}} {{\n"
          f"    %core_id = ktdp.get_compute_tile_id : index\n"
          f"    %c0 = arith.constant 0 : index\n    %step = arith.constant {tile_rows} : index\n"
@@ -1226,7 +1229,13 @@ def rmsnorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows:
          f"    %eps = arith.constant {eps} : f32\n")
     s += view("x_view", "x_ptr", [n_rows, n_cols], "f16") + view("y_view", "y_ptr", [n_rows, n_cols], "f16")
     s += view("rstd_view", "rstd_ptr", [n_rows], "f32")
+    if weight:
+        s += view("w_view", "w_ptr", [n_cols], "f16") + tile("w_tile", "w_view", ["%c0"], [n_cols], [n_cols], "f16")
     s += "    scf.for %row = %row0 to %row_end step %step {\n"
+    if weight:
+        s += (f"      %w16 = ktdp.load %w_tile : {wv[2]} -> {wv[0]}\n      %w1 = arith.extf %w16 : {wv[0]} to {wv[1]}\n"
+              f"      %wshape = tensor.empty() : {t32}\n"
+              f"      %w = linalg.broadcast ins(%w1 : {wv[1]}) outs(%wshape : {t32}) dimensions = [0]\n")
     s += tile("x_tile", "x_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
     s += (f"      %x16 = ktdp.load %x_tile : {at} -> {t16}\n"
           f"      %x = arith.extf %x16 : {t16} to {t32}\n"
@@ -1240,7 +1249,8 @@ def rmsnorm_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_rows:
           f"      %rstd = math.rsqrt %ms_eps : {tv}\n"
           f"      %bshape = tensor.empty() : {t32}\n"
           f"      %rstd_b = linalg.broadcast ins(%rstd : {tv}) outs(%bshape : {t32}) dimensions = [1]\n"
-          f"      %y = arith.mulf %x, %rstd_b : {t32}\n"
+          f"      %y{'n' if weight else ''} = arith.mulf %x, %rstd_b : {t32}\n"
+          + (f"      %y = arith.mulf %yn, %w : {t32}\n" if weight else "") +
           f"      %y16 = arith.truncf %y : {t32} to {t16}\n")
     s += tile("y_tile", "y_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
     s += tile("r_tile", "rstd_view", ["%row"], [tile_rows], [n_rows], "f32", "      ")

@@ -192,6 +192,7 @@ class RowProgramStatement(Statement):
         loads: List[Node] = []
         reduces: List[Node] = []
         scalars: List[Node] = []            # bcast nodes whose argument is a per-row value
+        shared_row = set()                  # ids of operand nodes that are one row broadcast over the tile's rows
         seen = set()
 
         def is_row_value(n: Node) -> bool:
@@ -219,6 +220,16 @@ class RowProgramStatement(Statement):
                     raise Unsupported(f"row reduction with {n.attrs['op']}")
                 walk(n.args[0])
                 reduces.append(n)            # post-order: what it depends on is already listed
+                return
+            if n.kind == "bcast" and _canon(n.args[0]).kind == "load" and _prod(n.shape) == full and \
+                    _prod(_canon(n.args[0]).shape) == cols and rows_total > 1 and \
+                    sorted(n.attrs.get("dims", [])) == list(range(len(n.shape) - 1)):
+                # one row of weights for all rows of the tile: an operand whose rows do not advance
+                src = _canon(n.args[0])
+                if src.dtype not in F_DT:
+                    raise Unsupported(f"{src.dtype} tile in a row program")
+                loads.append(n)
+                shared_row.add(id(n))
                 return
             if n.kind == "bcast" and strip_views(n.args[0]).kind != "const":
                 if _prod(n.shape) != full or not is_row_value(n.args[0]) or \
@@ -280,11 +291,20 @@ class RowProgramStatement(Statement):
             a.out.prog, a.out.load_mask = vector_program(store.value)
 
         # --- geometry: one table row per item, operand tiles then the destination -------------------------
-        in_accs: List[Access] = [n.attrs["access"] for n in loads]
-        expand = len(tile_geom(in_accs[0], False).lead) != 1
-        geoms = [tile_geom(acc, expand) for acc in in_accs]
-        g0 = geoms[0]
-        if g0.cols != cols or any((g.rows, g.cols, len(g.lead)) != (g0.rows, g0.cols, len(g0.lead)) for g in geoms):
+        shared = [id(n) in shared_row for n in loads]
+        in_accs: List[Access] = [(_canon(n.args[0]) if sh else n).attrs["access"] for n, sh in zip(loads, shared)]
+        full_accs = [acc for acc, sh in zip(in_accs, shared) if not sh]
+        if not full_accs:
+            raise Unsupported("row program without an operand tile of the reduced shape")
+        expand = len(tile_geom(full_accs[0], False).lead) != 1
+        geoms = [tile_geom(acc, False if sh else expand) for acc, sh in zip(in_accs, shared)]
+        g0 = geoms[shared.index(False)]
+        for g, sh in zip(geoms, shared):
+            if sh and (g.rows, g.cols, len(g.lead)) != (1, cols, 1):
+                raise Unsupported("shared operand row of another length")
+            if not sh and (g.rows, g.cols, len(g.lead)) != (g0.rows, g0.cols, len(g0.lead)):
+                raise Unsupported("operand tiles with another row structure in a row program")
+        if g0.cols != cols or (any(shared) and len(g0.lead) != 1):
             raise Unsupported("operand tiles with another row structure in a row program")
         sel, cores = _points(store)
         n_lead = len(g0.lead)
@@ -326,7 +346,10 @@ class RowProgramStatement(Statement):
             rstart = (offs[:, None] + np.arange(g.rows, dtype=np.int64)[None, :] * g.row_stride).reshape(-1) * bpe
             self.fps.append(Footprint(rstart, rstart + g.cols * bpe, np.repeat(sel, n_lead * g.rows),
                                       np.repeat(cores, n_lead * g.rows), is_out, stmt_id))
-            a.row_stride[k] = max(g.row_stride, 8) if g.rows == 1 else g.row_stride
+            if not is_out and shared[k]:
+                a.row_stride[k] = 0                  # every row of the tile reads the same row
+            else:
+                a.row_stride[k] = max(g.row_stride, 8) if g.rows == 1 else g.row_stride
             if (offs % 8).any() or (g.rows > 1 and g.row_stride % 8):
                 raise Unsupported("row program needs 16-byte aligned rows")
         a.n_items, a.rows_per_item, a.cols = table.shape[0], g0.rows, cols

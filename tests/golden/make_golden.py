@@ -191,6 +191,10 @@ def cases(ref_root=None):
     # every iteration of a loop reads the row the iteration before it stored
     out["accumulate_rows_4x6"] = (K.accumulate_rows(4, 6, 64), "accumulate_rows",
                                   dict(x_ptr=ui.standard_normal((24, 64)).astype(np.float16), acc_ptr=ui.standard_normal((4, 64)).astype(np.float16)))
+    # RMS norm on tiles of four rows with a weight row shared by the rows of a tile, per-row scales stored too
+    out["rmsnorm_weighted_32x128"] = (K.rmsnorm_rows(32, 128, 2, 4, weight=True), "rmsnorm_kernel",
+                                      dict(x_ptr=(ui.standard_normal((32, 128)) * 2).astype(np.float16), w_ptr=ui.standard_normal(128).astype(np.float16),
+                                           y_ptr=np.zeros((32, 128), np.float16), rstd_ptr=np.zeros(32, np.float32)))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

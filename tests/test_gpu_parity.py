@@ -26,7 +26,7 @@ def _run_both(src, fn, kwargs):
 
 
 def _exact(name):
-    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain", "accumulate_rows"))
+    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain", "accumulate_rows", "rmsnorm_weighted"))
 
 
 SUPPORTED = golden_names()
@@ -743,12 +743,16 @@ def test_layernorm_runs_as_fused_row_programs(rows, cols, cores, build_lib):
     np.testing.assert_array_equal(got["y_ptr"].view(np.uint16), want["y_ptr"].view(np.uint16))
 
 
+@pytest.mark.parametrize("weight", [False, True])
 @pytest.mark.parametrize("rows,cols,cores,tile_rows", [(64, 256, 4, 4), (128, 2048, 4, 8), (12, 512, 3, 2), (64, 32, 2, 16)])
-def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, build_lib):
+def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, weight, build_lib):
+    """RMS norm on tiles of several rows, with and without a weight row that all rows of a tile share."""
     rng = np.random.default_rng(rows * 7 + cols)
-    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
-              rstd_ptr=np.zeros(rows, np.float32))
-    src = K_.rmsnorm_rows(rows, cols, cores, tile_rows)
+    kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2).astype(np.float16))
+    if weight:
+        kw["w_ptr"] = rng.standard_normal(cols).astype(np.float16)
+    kw.update(y_ptr=np.zeros((rows, cols), np.float16), rstd_ptr=np.zeros(rows, np.float32))
+    src = K_.rmsnorm_rows(rows, cols, cores, tile_rows, weight=weight)
     gpu = KTIRInterpreter()
     gpu.load(src)
     got = gpu.execute_function("rmsnorm_kernel", **kw)

@@ -128,6 +128,21 @@ def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows):
         np.testing.assert_array_equal(got[k].view(np.uint8), want[k].view(np.uint8), err_msg=k)
 
 
+def test_a_weight_row_shared_by_the_rows_of_a_tile_is_an_operand_whose_rows_do_not_advance():
+    rng = np.random.default_rng(5)
+    kw = dict(x_ptr=(rng.standard_normal((32, 128)) * 2).astype(np.float16), w_ptr=rng.standard_normal(128).astype(np.float16),
+              y_ptr=np.zeros((32, 128), np.float16), rstd_ptr=np.zeros(32, np.float32))
+    src = K.rmsnorm_rows(32, 128, 2, 4, weight=True)
+    got, sess = plan_and_replay(src, "rmsnorm_kernel", kw)
+    a = sess.plan.statements[0].args
+    assert (a.n_in, a.rows_per_item, list(a.row_stride)[:3]) == (2, 4, [128, 0, 128])
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("rmsnorm_kernel", **kw)
+    for k in ("y_ptr", "rstd_ptr"):
+        np.testing.assert_array_equal(got[k].view(np.uint8), want[k].view(np.uint8), err_msg=k)
+
+
 def test_log_softmax_uses_two_kinds_of_reduction():
     """max (maxnumf) and sum of an expression of the max, an output that uses both row values."""
     rng = np.random.default_rng(8)
