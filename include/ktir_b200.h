@@ -224,7 +224,14 @@ typedef struct {
     int32_t op;               /* KTB_RP_* */
     int32_t round16;          /* 1: the fold rounds to f16 after every combine (an f16 tile is reduced) */
     int32_t load_mask;        /* bit k: the program reads operand k */
-    int32_t reserved;
+    int32_t blocked;          /* 1: a row is `n_blocks` column blocks of `cols` elements (operand k's blocks are
+                                 blk_stride[k] elements apart).  A reduction phase evaluates its program on every block
+                                 and adds the results up elementwise, block after block, starting from acc_init — the
+                                 accumulator tile a column-blocked kernel carries through its scf.for
+                                 (examples/triton-ktir/layernorm_fwd_ktir.mlir:58-75) — before the fold over the `cols`
+                                 sums; the output phase stores one block after the other */
+    int32_t acc_round16;      /* blocked reduction: the elementwise adds round to f16 */
+    float acc_init;           /* blocked reduction: initial value of the accumulator */
 } ktb_rp_phase;
 typedef struct {
     ktb_vm_program prog;      /* one value per row; registers 0..n_red-1 = the reduction results */
@@ -242,6 +249,9 @@ typedef struct {
                                  values of consecutive rows of an item */
     int64_t row_stride[KTB_VM_MAX_IN + 1];   /* elements; inputs then output */
     int32_t dtype[KTB_VM_MAX_IN + 1];        /* KTB_F16 / KTB_F32 */
+    int64_t blk_stride[KTB_VM_MAX_IN + 1];   /* elements between the column blocks of a row (blocked phases); inputs then output */
+    int32_t n_blocks;                        /* column blocks per row, 1 if no phase is blocked */
+    int32_t reserved;
     ktb_rp_phase red[KTB_RP_MAX_RED];
     ktb_rp_scalar scal[KTB_RP_MAX_SCAL];
     ktb_rp_phase out;                        /* op unused */

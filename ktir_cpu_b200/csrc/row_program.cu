@@ -153,39 +153,57 @@ ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_
             for (; scal_done < a.n_scal && a.scal[scal_done].ready_after < p; ++scal_done)
                 scal[scal_done] = rp_vm1(a.scal[scal_done].prog, red);
             const ktb_rp_phase& ph = p < a.n_red ? a.red[p] : a.out;
+            const int nb = ph.blocked ? a.n_blocks : 1;
+            const bool accumulate = ph.blocked && p < a.n_red;
             float x[NV][8];
+            if (accumulate) {
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) x[j][v] = ph.acc_init;
+            }
 #pragma unroll
             for (int s = 0; s < KTB_RP_MAX_SCAL; ++s)
                 if (s < a.n_scal && a.n_in + s < KTB_VM_REGS) {
 #pragma unroll
                     for (int v = 0; v < 8; ++v) regs[RP_REG(a.n_in + s, v)] = scal[s];
                 }
+            for (int jb = 0; jb < nb; ++jb) {
 #pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int64_t col = ((int64_t)j * T + t) * 8;
-                if (ph.prog.n_ops == 0) {             // the phase reduces (or stores) an operand as it is
-                    rp_load8(a.arena, off[ph.prog.result_reg] + col, a.dtype[ph.prog.result_reg], x[j]);
-                    continue;
-                }
+                for (int j = 0; j < NV; ++j) {
+                    const int64_t col = ((int64_t)j * T + t) * 8;
+                    float val[8];
+                    if (ph.prog.n_ops == 0) {         // the phase reduces (or stores) an operand as it is
+                        const int k = ph.prog.result_reg;
+                        rp_load8(a.arena, off[k] + jb * a.blk_stride[k] + col, a.dtype[k], val);
+                    } else {
 #pragma unroll
-                for (int k = 0; k < KTB_VM_MAX_IN; ++k)
-                    if (k < a.n_in && ((ph.load_mask >> k) & 1)) {
-                        float in[8];
-                        rp_load8(a.arena, off[k] + col, a.dtype[k], in);
+                        for (int k = 0; k < KTB_VM_MAX_IN; ++k)
+                            if (k < a.n_in && ((ph.load_mask >> k) & 1)) {
+                                float in[8];
+                                rp_load8(a.arena, off[k] + jb * a.blk_stride[k] + col, a.dtype[k], in);
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) regs[RP_REG(k, v)] = in[v];
+                                for (int v = 0; v < 8; ++v) regs[RP_REG(k, v)] = in[v];
+                            }
+                        rp_vm8(ph.prog, regs);       // (x[] is not passed by address: it stays in registers)
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) val[v] = regs[RP_REG(ph.prog.result_reg, v)];
                     }
-                rp_vm8(ph.prog, regs);               // (x[] is not passed by address: it stays in registers)
+                    if (accumulate) {
 #pragma unroll
-                for (int v = 0; v < 8; ++v) x[j][v] = regs[RP_REG(ph.prog.result_reg, v)];
-            }
-            if (p < a.n_red) {
-                red[p] = rp_fold<NV>(x, ph, T, t, group, xchg, bcast);
-            } else if (live) {
+                        for (int v = 0; v < 8; ++v) {
+                            const float sacc = x[j][v] + val[v];
+                            x[j][v] = ph.acc_round16 ? ktb_round16(sacc) : sacc;
+                        }
+                    } else if (p < a.n_red) {
 #pragma unroll
-                for (int j = 0; j < NV; ++j)
-                    ktb_store_vec<8>(a.arena, off[a.n_in] + ((int64_t)j * T + t) * 8, a.dtype[a.n_in], x[j]);
+                        for (int v = 0; v < 8; ++v) x[j][v] = val[v];
+                    } else if (live) {
+                        ktb_store_vec<8>(a.arena, off[a.n_in] + jb * a.blk_stride[a.n_in] + col, a.dtype[a.n_in], val);
+                    }
+                }
             }
+            if (p < a.n_red) red[p] = rp_fold<NV>(x, ph, T, t, group, xchg, bcast);
         }
     }
 }
@@ -423,6 +441,12 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
         return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad operand / phase counts");
     if (a.cols < 8 || a.cols > 16384 || (a.cols & (a.cols - 1)) != 0)
         return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "cols must be a power of two in [8, 16384]");
+    bool any_blocked = a.out.blocked != 0;
+    for (int p = 0; p < a.n_red; ++p) any_blocked = any_blocked || a.red[p].blocked;
+    if (a.n_blocks < 1 || a.n_blocks > 4096 || (!any_blocked && a.n_blocks != 1) || (a.out.blocked && a.out_per_row))
+        return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad column-block count");
+    for (int k = 0; any_blocked && k <= a.n_in; ++k)
+        if (a.blk_stride[k] % 8) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "block strides must be multiples of 8 elements");
     for (int k = 0; k <= a.n_in; ++k) {
         if (a.dtype[k] != KTB_F16 && a.dtype[k] != KTB_F32)
             return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "operand dtype must be f16 or f32");
@@ -448,6 +472,8 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
     int T = vecs / 8;
     if (T < 1) T = 1;
     if (T > 256) T = 256;
+    // ... but few rows (of many column blocks, say) must still give every SM a couple of CTAs: more threads per row
+    while (T < vecs && T < 256 && a.n_items * (int64_t)a.rows_per_item / (256 / T) < 2 * (int64_t)ctx->sm_count) T *= 2;
     const int NV = vecs / T;
     const int64_t total_rows = a.n_items * (int64_t)a.rows_per_item;
     if (total_rows >= (1ll << 31)) return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "more than 2^31 rows");
@@ -457,7 +483,7 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
     if (blocks > n_iter) blocks = n_iter;
 #ifndef KTB_RP_NO_NORM
     rp_norm nm;
-    if (rp_match_norm(a, nm)) {
+    if (!any_blocked && rp_match_norm(a, nm)) {
         // four vectors per thread (the row and its squares sit in registers): two CTAs per SM
 #ifndef KTB_RP_NORM_VPT
 #define KTB_RP_NORM_VPT 4

@@ -1296,3 +1296,58 @@ def log_softmax_rows(n_rows: int = 64, n_cols: int = 256, cores: int = 4, tile_r
     s += tile("y_tile", "y_view", ["%row", "%c0"], [tile_rows, n_cols], [n_rows, n_cols], "f16", "      ")
     s += f"      ktdp.store %y16, %y_tile : {t16}, {at}\n      scf.yield\n    }}\n    return\n  }}\n}}\n"
     return s
+
+
+def layernorm_blocked(n_rows: int = 64, n_cols: int = 1024, block: int = 256, cores: int = 4) -> str:
+    """Layer norm the way examples/triton-ktir/layernorm_fwd_ktir.mlir writes it (same name, arguments and op
+    sequence, sizes of one's choosing): f16 throughout; a row is walked in column blocks of ``block``
+    elements — the blocks are summed elementwise into a ``[1, block]`` accumulator carried through an
+    ``scf.for``, the accumulator is reduced, mean = sum / N; the same again for the squared deviations;
+    rstd = 1 / sqrt(var + eps); mean and rstd are stored per row; a third loop over the blocks writes
+    ``(x - mean) * rstd * w + b`` with per-element weights and biases of the input's shape.  Core ``c``
+    takes rows ``c, c + cores, ...``."""
+    assert n_cols % block == 0
+    tb, t1 = f"tensor<1x{block}xf16>", "tensor<1xf16>"
+    at, at1 = f"!ktdp.access_tile<1x{block}xindex>", "!ktdp.access_tile<1xindex>"
+    s = (f"module {{\n  func.func @_layer_norm_fwd_fused(%X: index, %Y: index, %W: index, %B: index, %Mean: index, "
+         f"%Rstd: index, %N: index, %eps: f16, %BLOCK_SIZE: index) attributes {{grid = [{cores}, 1]}} {{\n"
+         f"    %core_id = ktdp.get_compute_tile_id : index\n    %c0 = arith.constant 0 : index\n"
+         f"    %n_rows = arith.constant {n_rows} : index\n    %n_cores = arith.constant {cores} : index\n"
+         f"    %one = arith.constant 1.0 : f16\n")
+    for nm in ("X", "Y", "W", "B"):
+        s += view(f"{nm}_view", nm, [n_rows, n_cols], "f16")
+    s += view("Mean_view", "Mean", [n_rows], "f16") + view("Rstd_view", "Rstd", [n_rows], "f16")
+    s += ("    scf.for %row = %core_id to %n_rows step %n_cores : index {\n"
+          f"      %zero_block = arith.constant dense<0.0> : {tb}\n"
+          f"      %sum_block = scf.for %col = %c0 to %N step %BLOCK_SIZE iter_args(%sum_iter = %zero_block) -> {tb} {{\n")
+    s += tile("xa", "X_view", ["%row", "%col"], [1, block], [n_rows, n_cols], "f16", "        ")
+    s += (f"        %a = ktdp.load %xa : {at} -> {tb}\n        %sum_next = arith.addf %sum_iter, %a : {tb}\n"
+          f"        scf.yield %sum_next : {tb}\n      }}\n"
+          f"      %zero_scalar = arith.constant 0.0 : f16\n      %sum_init = tensor.splat %zero_scalar : {t1}\n"
+          f"      %reduce_sum = linalg.reduce {{ arith.addf }} ins(%sum_block : {tb}) outs(%sum_init : {t1}) dimensions = [1]\n"
+          f"      %N_i32 = arith.index_cast %N : index to i32\n      %N_f16 = arith.sitofp %N_i32 : i32 to f16\n"
+          f"      %N_tensor = tensor.splat %N_f16 : {t1}\n      %mean = arith.divf %reduce_sum, %N_tensor : {t1}\n"
+          f"      %mean_scalar = tensor.extract %mean[%c0] : {t1}\n      %mean_block = tensor.splat %mean_scalar : {tb}\n"
+          f"      %var_block = scf.for %col = %c0 to %N step %BLOCK_SIZE iter_args(%var_iter = %zero_block) -> {tb} {{\n")
+    s += tile("xb", "X_view", ["%row", "%col"], [1, block], [n_rows, n_cols], "f16", "        ")
+    s += (f"        %a = ktdp.load %xb : {at} -> {tb}\n        %x = arith.subf %a, %mean_block : {tb}\n"
+          f"        %x2 = arith.mulf %x, %x : {tb}\n        %var_next = arith.addf %var_iter, %x2 : {tb}\n"
+          f"        scf.yield %var_next : {tb}\n      }}\n"
+          f"      %var_init = tensor.splat %zero_scalar : {t1}\n"
+          f"      %reduce_var = linalg.reduce {{ arith.addf }} ins(%var_block : {tb}) outs(%var_init : {t1}) dimensions = [1]\n"
+          f"      %var = arith.divf %reduce_var, %N_tensor : {t1}\n      %eps_tensor = tensor.splat %eps : {t1}\n"
+          f"      %var_plus_eps = arith.addf %var, %eps_tensor : {t1}\n      %var_sqrt = math.sqrt %var_plus_eps : {t1}\n"
+          f"      %one_tensor = tensor.splat %one : {t1}\n      %rstd = arith.divf %one_tensor, %var_sqrt : {t1}\n"
+          f"      %rstd_scalar = tensor.extract %rstd[%c0] : {t1}\n      %rstd_block = tensor.splat %rstd_scalar : {tb}\n")
+    s += tile("ma", "Mean_view", ["%row"], [1], [n_rows], "f16", "      ")
+    s += tile("ra", "Rstd_view", ["%row"], [1], [n_rows], "f16", "      ")
+    s += (f"      ktdp.store %mean, %ma : {t1}, {at1}\n      ktdp.store %rstd, %ra : {t1}, {at1}\n"
+          "      scf.for %col = %c0 to %N step %BLOCK_SIZE {\n")
+    for nm, vw in (("wa", "W_view"), ("ba", "B_view"), ("xc", "X_view"), ("ya", "Y_view")):
+        s += tile(nm, vw, ["%row", "%col"], [1, block], [n_rows, n_cols], "f16", "        ")
+    s += (f"        %w = ktdp.load %wa : {at} -> {tb}\n        %b = ktdp.load %ba : {at} -> {tb}\n"
+          f"        %xx = ktdp.load %xc : {at} -> {tb}\n        %xm = arith.subf %xx, %mean_block : {tb}\n"
+          f"        %xh = arith.mulf %xm, %rstd_block : {tb}\n        %xw = arith.mulf %xh, %w : {tb}\n"
+          f"        %y = arith.addf %xw, %b : {tb}\n        ktdp.store %y, %ya : {tb}, {at}\n"
+          "        scf.yield\n      }\n      scf.yield\n    }\n    return\n  }\n}\n")
+    return s

@@ -54,6 +54,8 @@ def _canon(n: Node) -> Node:
             n = n.args[0]
         elif n.kind == "bcast" and strip_views(n.args[0]).kind == "const":
             n = n.args[0]
+        elif n.kind == "extract" and _prod(n.args[0].shape) == 1:
+            n = n.args[0]
         else:
             return n
 
@@ -167,6 +169,50 @@ def _first_reduce(n: Node, seen=None):
     return None
 
 
+def _signature(n: Node, loads: List[Node], fixed: Dict[int, int]):
+    """Structure of an expression with its loads numbered in the order they are met (``loads`` collects
+    them); nodes listed in ``fixed`` (row values) count as themselves."""
+    n = _canon(n)
+    if id(n) in fixed:
+        return ("S", id(n))
+    if n.kind == "load":
+        loads.append(n)
+        return ("L", len(loads) - 1, n.dtype)
+    if n.kind == "const":
+        return ("C", repr(n.attrs.get("value")), n.dtype, n.attrs.get("list") is not None)
+    if n.kind == "bcast":                                # of a row value: same node or no match
+        return ("B", id(n))
+    if n.kind in ("ew", "cast"):
+        return (n.kind, n.attrs.get("op"), n.dtype, tuple(_signature(a, loads, fixed) for a in n.args))
+    return ("?", id(n))
+
+
+def _block_chain(src: Node):
+    """``src = (((init + t_0) + t_1) + ... + t_{B-1})``, the accumulator a column-blocked kernel carries
+    through its loop over the blocks of a row: (init value, [t_0 ...], adds round to f16) or None."""
+    terms = []
+    n = _canon(src)
+    dtype = n.dtype
+    while n.kind == "ew" and n.attrs.get("op") == "arith.addf" and len(n.args) == 2 and n.dtype == dtype:
+        terms.append(n.args[1])
+        n = _canon(n.args[0])
+    if n.kind != "const" or n.attrs.get("list") is not None or len(terms) < 2:
+        return None
+    terms.reverse()
+    return float(n.attrs["value"]), terms, dtype == "f16"
+
+
+class _Operand:
+    """One operand tile of the statement: where it lives per item, how its rows and column blocks advance."""
+
+    def __init__(self, acc: Access, offs: np.ndarray, shared_row: bool, blk_stride: int):
+        self.acc, self.offs, self.shared_row, self.blk_stride = acc, offs, shared_row, blk_stride
+
+    def key(self):
+        return (self.acc.view.dtype, tuple(self.acc.shape), tuple(self.acc.strides), self.shared_row, self.blk_stride,
+                self.offs.tobytes())
+
+
 class RowProgramStatement(Statement):
     kind = "row_program"
 
@@ -188,11 +234,74 @@ class RowProgramStatement(Statement):
         if not per_row and _prod(tgt.shape) != full:
             raise Unsupported("stored tile is neither the reduced tile's shape nor one value per row")
 
+        # --- iteration points.  A statement inside a loop over the column blocks of a row (its last axis) whose
+        # reductions walk the same blocks is taken row by row: the block axis moves into the operands.
+        axes = tuple(store.axes)
+        sel_all, cores_all = _points(store)
+        chains = {}
+
+        def find_chains(n: Node, seen):
+            n = strip_views(n)
+            if id(n) in seen:
+                return
+            seen.add(id(n))
+            if n.kind == "reduce":
+                c = _block_chain(n.args[0])
+                if c is not None:
+                    chains[id(n)] = c
+            for a_ in n.args:
+                if isinstance(a_, Node):
+                    find_chains(a_, seen)
+
+        find_chains(store.value, set())
+        n_blocks = 1
+        if chains:
+            counts = {len(c[1]) for c in chains.values()}
+            if len(counts) != 1:
+                raise Unsupported("blocked reductions over different numbers of column blocks")
+            n_blocks = counts.pop()
+        absorb = bool(chains) and not per_row and len(axes) >= 2 and axes[-1] == n_blocks and \
+            (store.active is None or bool((store.active == store.active[..., :1]).all()))
+        if chains and not per_row and not absorb:
+            raise Unsupported("blocked reductions next to a stored tile that does not walk the same column blocks")
+        if absorb:
+            keep = (sel_all % n_blocks) == 0                # points with block index 0 stand for their row
+            sel, cores = sel_all[keep], cores_all[keep]
+        else:
+            sel, cores = sel_all, cores_all
+
+        def offsets_of(acc: Access, own_axes) -> Tuple[np.ndarray, int]:
+            """Element offset of the tile at every item, and the step between column blocks (0: none)."""
+            from .trace import iv_full
+            offs_full = np.asarray(iv_full(acc.off, axes)).reshape(-1).astype(np.int64)
+            offs = offs_full[sel]
+            if not absorb:
+                return offs, 0
+            cube = offs_full.reshape(-1, n_blocks)
+            step = cube[:, 1:] - cube[:, :-1]
+            if step.size and (step != step.flat[0]).any():
+                raise Unsupported("tile that does not advance evenly over the column blocks")
+            return offs, int(step.flat[0]) if step.size else 0
+
+        operands: List[_Operand] = []
+        op_index: Dict[tuple, int] = {}
+
+        def operand(acc: Access, shared: bool, blk_stride=None) -> int:
+            if acc.coords is not None:
+                raise Unsupported("coordinate-set tile in a row program")
+            offs, step = offsets_of(acc, None)
+            o = _Operand(acc, offs, shared, step if blk_stride is None else blk_stride)
+            k = op_index.get(o.key())
+            if k is None:
+                k = op_index[o.key()] = len(operands)
+                operands.append(o)
+            return k
+
         # --- the DAG: operand tiles, reductions (in dependency order), broadcast row values -------------
-        loads: List[Node] = []
+        leaves: Dict[int, int] = {}         # node id -> operand index (row values are added below)
         reduces: List[Node] = []
         scalars: List[Node] = []            # bcast nodes whose argument is a per-row value
-        shared_row = set()                  # ids of operand nodes that are one row broadcast over the tile's rows
+        blocked_terms: Dict[int, Node] = {} # reduce node id -> the term evaluated per block
         seen = set()
 
         def is_row_value(n: Node) -> bool:
@@ -208,7 +317,7 @@ class RowProgramStatement(Statement):
                     raise Unsupported(f"{n.dtype} tile in a row program")
                 if _prod(n.shape) != full:
                     raise Unsupported("operand tile of another shape in a row program")
-                loads.append(n)
+                leaves[id(n)] = operand(n.attrs["access"], False)
                 return
             if n.kind == "reduce":
                 dims = n.attrs.get("dims")
@@ -218,36 +327,78 @@ class RowProgramStatement(Statement):
                     raise Unsupported("reduction that is not along the rows of the reduced tile")
                 if n.attrs["op"] not in _RED_OPS:
                     raise Unsupported(f"row reduction with {n.attrs['op']}")
-                walk(n.args[0])
+                chain = chains.get(id(n))
+                if chain is None:
+                    walk(n.args[0])
+                else:
+                    # every term must be the first one with its loads moved on by a whole number of blocks
+                    _, terms, _ = chain
+                    fixed = {}
+                    first_loads: List[Node] = []
+                    for t_ in terms:                     # row values inside the terms come first
+                        collect_row_values(t_)
+                    sig0 = _signature(terms[0], first_loads, fixed)
+                    steps = [None] * len(first_loads)
+                    for j_, t_ in enumerate(terms[1:], 1):
+                        lj: List[Node] = []
+                        if _signature(t_, lj, fixed) != sig0 or len(lj) != len(first_loads):
+                            raise Unsupported("blocked reduction whose blocks are not computed alike")
+                        for q, (l0, l1) in enumerate(zip(first_loads, lj)):
+                            a0, a1 = l0.attrs["access"], l1.attrs["access"]
+                            if (a0.view.dtype, tuple(a0.shape), tuple(a0.strides)) != (a1.view.dtype, tuple(a1.shape), tuple(a1.strides)):
+                                raise Unsupported("blocked reduction over tiles of different layouts")
+                            o0, _ = offsets_of(a0, None)
+                            o1, _ = offsets_of(a1, None)
+                            d = o1 - o0
+                            if d.size and (d != d.flat[0]).any():
+                                raise Unsupported("blocked reduction whose blocks are not evenly spaced")
+                            step = int(d.flat[0]) if d.size else 0
+                            if step % j_ or (steps[q] is not None and steps[q] != step // j_):
+                                raise Unsupported("blocked reduction whose blocks are not evenly spaced")
+                            steps[q] = step // j_
+                    for l0, st_ in zip(first_loads, steps):
+                        if l0.dtype not in F_DT or _prod(l0.shape) != full:
+                            raise Unsupported("operand tile of another shape in a row program")
+                        leaves[id(l0)] = operand(l0.attrs["access"], False, blk_stride=st_ or 0)
+                    blocked_terms[id(n)] = terms[0]
                 reduces.append(n)            # post-order: what it depends on is already listed
                 return
-            if n.kind == "bcast" and _canon(n.args[0]).kind == "load" and _prod(n.shape) == full and \
-                    _prod(_canon(n.args[0]).shape) == cols and rows_total > 1 and \
-                    sorted(n.attrs.get("dims", [])) == list(range(len(n.shape) - 1)):
-                # one row of weights for all rows of the tile: an operand whose rows do not advance
-                src = _canon(n.args[0])
-                if src.dtype not in F_DT:
-                    raise Unsupported(f"{src.dtype} tile in a row program")
-                loads.append(n)
-                shared_row.add(id(n))
-                return
             if n.kind == "bcast" and strip_views(n.args[0]).kind != "const":
-                if _prod(n.shape) != full or not is_row_value(n.args[0]) or \
-                        list(n.attrs.get("dims", [])) != [len(n.shape) - 1]:
-                    raise Unsupported("broadcast that is not a per-row value along the columns")
-                walk(n.args[0])
-                scalars.append(n)
-                return
-            if n.kind in ("const", "cast", "ew", "bcast"):
-                for a in n.args:
-                    walk(a)
+                if is_row_value(n.args[0]) and _prod(n.shape) == full and \
+                        (rows_total == 1 or list(n.attrs.get("dims", [])) == [len(n.shape) - 1]):
+                    walk(n.args[0])
+                    scalars.append(n)
+                    return
+                src = _canon(n.args[0])
+                if src.kind == "load" and _prod(n.shape) == full and _prod(src.shape) == cols and rows_total > 1 and \
+                        sorted(n.attrs.get("dims", [])) == list(range(len(n.shape) - 1)):
+                    # one row of weights for all rows of the tile: an operand whose rows do not advance
+                    if src.dtype not in F_DT:
+                        raise Unsupported(f"{src.dtype} tile in a row program")
+                    leaves[id(n)] = operand(src.attrs["access"], True)
+                    return
+                raise Unsupported("broadcast that is neither a per-row value along the columns nor a shared row")
+            if n.kind in ("const", "cast", "ew", "bcast", "extract"):
+                for a_ in n.args:
+                    walk(a_)
                 return
             raise Unsupported(f"{n.kind} node in a row program")
 
+        def collect_row_values(n: Node):
+            """Row values used inside a blocked term are walked (their reductions come first) without
+            registering the term's own loads block by block."""
+            n = strip_views(n)
+            if n.kind == "bcast" and strip_views(n.args[0]).kind != "const" and is_row_value(n.args[0]):
+                walk(n)
+                return
+            for a_ in n.args:
+                if isinstance(a_, Node):
+                    collect_row_values(a_)
+
         walk(store.value)
-        if len(reduces) > R.RP_MAX_RED or len(scalars) > R.RP_MAX_SCAL or len(loads) > R.VM_MAX_IN or not loads:
+        if len(reduces) > R.RP_MAX_RED or len(scalars) > R.RP_MAX_SCAL or len(operands) > R.VM_MAX_IN or not operands:
             raise Unsupported("row program with more reductions, row values or operand tiles than the kernel takes")
-        n_in, n_red = len(loads), len(reduces)
+        n_in, n_red = len(operands), len(reduces)
         if n_in + len(scalars) >= R.VM_REGS:
             raise Unsupported("row program with too many inputs")
         red_index = {id(r): k for k, r in enumerate(reduces)}
@@ -257,100 +408,114 @@ class RowProgramStatement(Statement):
             n = strip_views(n)
             if id(n) not in memo:
                 memo[id(n)] = red_index[id(n)] if id(n) in red_index else \
-                    max([last_reduce(a, memo) for a in n.args if isinstance(a, Node)] + [-1])
+                    max([last_reduce(a_, memo) for a_ in n.args if isinstance(a_, Node)] + [-1])
             return memo[id(n)]
 
         def scalar_program(root: Node) -> R.VmProgram:
             return _Compiler(dict(red_index), n_red, rows_total).compile(root)
 
-        scal_progs = sorted(((last_reduce(s.args[0], {}), k, scalar_program(s.args[0]), s) for k, s in enumerate(scalars)),
+        scal_progs = sorted(((last_reduce(s_.args[0], {}), k, scalar_program(s_.args[0]), s_) for k, s_ in enumerate(scalars)),
                             key=lambda x: x[:2])
-        scal_slot = {id(s): n_in + k for k, (_, _, _, s) in enumerate(scal_progs)}
+        for k, (_, _, _, s_) in enumerate(scal_progs):
+            leaves[id(s_)] = n_in + k
 
         # --- vector programs ----------------------------------------------------------------------------
-        leaves = {id(n): k for k, n in enumerate(loads)}
-        leaves.update(scal_slot)
-
         def vector_program(root: Node):
             comp = _Compiler(leaves, n_in + len(scalars), full)
             prog = comp.compile(root)
             return prog, sum(1 << r for r in comp.used_inputs if r < n_in)
 
         self.args = a = R.RowProgArgs()
-        a.n_in, a.n_red, a.n_scal, a.out_per_row = n_in, n_red, len(scal_progs), int(per_row)
+        a.n_in, a.n_red, a.n_scal, a.out_per_row, a.n_blocks = n_in, n_red, len(scal_progs), int(per_row), n_blocks
         for k, r in enumerate(reduces):
             ph = a.red[k]
-            ph.prog, ph.load_mask = vector_program(r.args[0])
+            term = blocked_terms.get(id(r))
+            ph.prog, ph.load_mask = vector_program(term if term is not None else r.args[0])
             ph.op = R.RP_OPS[_RED_OPS[r.attrs["op"]]]
             ph.round16 = 1 if r.dtype == "f16" else 0
+            if term is not None:
+                init, _, r16 = chains[id(r)]
+                ph.blocked, ph.acc_round16, ph.acc_init = 1, int(r16), init
         for k, (ready, _, prog, _) in enumerate(scal_progs):
             a.scal[k].prog, a.scal[k].ready_after = prog, ready
         if per_row:
             a.out.prog, a.out.load_mask = scalar_program(store.value), 0
         else:
             a.out.prog, a.out.load_mask = vector_program(store.value)
+            a.out.blocked = int(absorb)
 
         # --- geometry: one table row per item, operand tiles then the destination -------------------------
-        shared = [id(n) in shared_row for n in loads]
-        in_accs: List[Access] = [(_canon(n.args[0]) if sh else n).attrs["access"] for n, sh in zip(loads, shared)]
-        full_accs = [acc for acc, sh in zip(in_accs, shared) if not sh]
-        if not full_accs:
+        full_ops = [o for o in operands if not o.shared_row]
+        if not full_ops:
             raise Unsupported("row program without an operand tile of the reduced shape")
-        expand = len(tile_geom(full_accs[0], False).lead) != 1
-        geoms = [tile_geom(acc, False if sh else expand) for acc, sh in zip(in_accs, shared)]
-        g0 = geoms[shared.index(False)]
-        for g, sh in zip(geoms, shared):
-            if sh and (g.rows, g.cols, len(g.lead)) != (1, cols, 1):
+        expand = len(tile_geom(full_ops[0].acc, False).lead) != 1
+        geoms = [tile_geom(o.acc, False if o.shared_row else expand) for o in operands]
+        g0 = geoms[[o.shared_row for o in operands].index(False)]
+        for g, o in zip(geoms, operands):
+            if o.shared_row and (g.rows, g.cols, len(g.lead)) != (1, cols, 1):
                 raise Unsupported("shared operand row of another length")
-            if not sh and (g.rows, g.cols, len(g.lead)) != (g0.rows, g0.cols, len(g0.lead)):
+            if not o.shared_row and (g.rows, g.cols, len(g.lead)) != (g0.rows, g0.cols, len(g0.lead)):
                 raise Unsupported("operand tiles with another row structure in a row program")
-        if g0.cols != cols or (any(shared) and len(g0.lead) != 1):
-            raise Unsupported("operand tiles with another row structure in a row program")
-        sel, cores = _points(store)
         n_lead = len(g0.lead)
+        if g0.cols != cols or ((any(o.shared_row for o in operands) or n_blocks > 1) and n_lead != 1):
+            raise Unsupported("operand tiles with another row structure in a row program")
+        out_step = 0
         if per_row:
             # the stored tile has one element per row of an operand tile; its elements sit `stride` apart
             big = [d for d, n_ in enumerate(tgt.shape) if n_ > 1]
             if len(big) > 1 or n_lead != 1 or (big and tgt.shape[big[0]] != g0.rows):
                 raise Unsupported("per-row result tile of more than one dimension")
             out_stride = int(tgt.strides[big[0]]) if big else 1
+            out_offs, _ = offsets_of(tgt, None)
         else:
             go = tile_geom(tgt, expand)
             if (go.rows, go.cols, len(go.lead)) != (g0.rows, g0.cols, n_lead):
                 raise Unsupported("stored tile with another row structure than the operands")
-            geoms.append(go)
-        operands = in_accs + [tgt]
-        table = np.empty((len(sel) * n_lead, len(operands)), np.int64)
+            out_offs, out_step = offsets_of(tgt, None)
+        table = np.empty((len(sel) * n_lead, n_in + 1), np.int64)
         self.fps: List[Footprint] = []
-        for k, acc in enumerate(operands):
-            is_out = k == len(operands) - 1
-            bpe = bytes_per_elem(acc.view.dtype)
-            a.dtype[k] = R.DTYPE_CODE[acc.view.dtype]
-            if is_out and per_row:
-                offs = _access_offsets(acc, store, sel).reshape(-1)
-                table[:, k] = offs
-                if len(offs):
-                    arena.check_range(int(offs.min()), int(offs.max()) + (g0.rows - 1) * out_stride + 1,
-                                      acc.view.dtype, "Scatter to")
-                rstart = (offs[:, None] + np.arange(g0.rows, dtype=np.int64)[None, :] * out_stride).reshape(-1) * bpe
-                self.fps.append(Footprint(rstart, rstart + bpe, np.repeat(sel, g0.rows), np.repeat(cores, g0.rows),
-                                          True, stmt_id))
-                a.row_stride[k] = out_stride
-                continue
-            g = geoms[k]
-            offs = (_access_offsets(acc, store, sel)[:, None] + g.lead[None, :]).reshape(-1)
+        blocks = np.arange(n_blocks, dtype=np.int64)
+
+        def footprint(offs, g, step, bpe, write):
+            rs = (offs[:, None, None] + np.arange(g.rows, dtype=np.int64)[None, :, None] * g.row_stride +
+                  blocks[None, None, :] * step).reshape(-1) * bpe
+            rep = n_lead * g.rows * n_blocks
+            self.fps.append(Footprint(rs, rs + g.cols * bpe, np.repeat(sel, rep), np.repeat(cores, rep), write, stmt_id))
+
+        for k, (o, g) in enumerate(zip(operands, geoms)):
+            bpe = bytes_per_elem(o.acc.view.dtype)
+            offs = (o.offs[:, None] + g.lead[None, :]).reshape(-1)
             table[:, k] = offs
+            a.dtype[k] = R.DTYPE_CODE[o.acc.view.dtype]
+            a.blk_stride[k] = o.blk_stride
             if len(offs):
-                arena.check_range(int(offs.min()), int(offs.max()) + (g.rows - 1) * g.row_stride + g.cols,
-                                  acc.view.dtype, "Scatter to" if is_out else "Read from")
-            rstart = (offs[:, None] + np.arange(g.rows, dtype=np.int64)[None, :] * g.row_stride).reshape(-1) * bpe
-            self.fps.append(Footprint(rstart, rstart + g.cols * bpe, np.repeat(sel, n_lead * g.rows),
-                                      np.repeat(cores, n_lead * g.rows), is_out, stmt_id))
-            if not is_out and shared[k]:
-                a.row_stride[k] = 0                  # every row of the tile reads the same row
-            else:
-                a.row_stride[k] = max(g.row_stride, 8) if g.rows == 1 else g.row_stride
-            if (offs % 8).any() or (g.rows > 1 and g.row_stride % 8):
+                arena.check_range(int(offs.min()), int(offs.max()) + (g.rows - 1) * g.row_stride +
+                                  (n_blocks - 1) * max(o.blk_stride, 0) + g.cols, o.acc.view.dtype, "Read from")
+            footprint(offs, g, o.blk_stride, bpe, False)
+            a.row_stride[k] = 0 if o.shared_row else (max(g.row_stride, 8) if g.rows == 1 else g.row_stride)
+            if (offs % 8).any() or (g.rows > 1 and g.row_stride % 8) or o.blk_stride % 8 or o.blk_stride < 0:
+                raise Unsupported("row program needs 16-byte aligned rows")
+        bpe = bytes_per_elem(tgt.view.dtype)
+        a.dtype[n_in] = R.DTYPE_CODE[tgt.view.dtype]
+        if per_row:
+            table[:, n_in] = out_offs
+            if len(out_offs):
+                arena.check_range(int(out_offs.min()), int(out_offs.max()) + (g0.rows - 1) * out_stride + 1,
+                                  tgt.view.dtype, "Scatter to")
+            rs = (out_offs[:, None] + np.arange(g0.rows, dtype=np.int64)[None, :] * out_stride).reshape(-1) * bpe
+            self.fps.append(Footprint(rs, rs + bpe, np.repeat(sel, g0.rows), np.repeat(cores, g0.rows), True, stmt_id))
+            a.row_stride[n_in] = out_stride
+        else:
+            offs = (out_offs[:, None] + go.lead[None, :]).reshape(-1)
+            table[:, n_in] = offs
+            a.blk_stride[n_in] = out_step
+            if len(offs):
+                arena.check_range(int(offs.min()), int(offs.max()) + (go.rows - 1) * go.row_stride +
+                                  (n_blocks - 1) * max(out_step, 0) + go.cols, tgt.view.dtype, "Scatter to")
+            footprint(offs, go, out_step if absorb else 0, bpe, True)
+            a.row_stride[n_in] = max(go.row_stride, 8) if go.rows == 1 else go.row_stride
+            if (offs % 8).any() or (go.rows > 1 and go.row_stride % 8) or out_step % 8 or out_step < 0 or \
+                    (absorb and out_step == 0):
                 raise Unsupported("row program needs 16-byte aligned rows")
         a.n_items, a.rows_per_item, a.cols = table.shape[0], g0.rows, cols
         self.table = table
@@ -358,9 +523,9 @@ class RowProgramStatement(Statement):
         self.dev_table = dev.upload(table)
         a.dev_item_offsets = self.dev_table
         self.device_arrays = [self.dev_table]
-        self._n_op = len(operands)
-        self._bytes = int(table.shape[0]) * g0.rows * (cols * sum(bytes_per_elem(x.view.dtype) for x in in_accs)
-                                                       + (1 if per_row else cols) * bytes_per_elem(tgt.view.dtype))
+        self._n_op = n_in + 1
+        self._bytes = int(table.shape[0]) * g0.rows * n_blocks * (
+            cols * sum(bytes_per_elem(o.acc.view.dtype) for o in operands) + (0 if per_row else cols) * bpe)
 
     def launch(self, dev, arena_ptr):
         self.args.arena = arena_ptr

@@ -52,7 +52,7 @@ RP_OPS = {"add": 0, "max": 1, "maxnum": 2}
 
 class RpPhase(C.Structure):
     _fields_ = [("prog", VmProgram), ("op", C.c_int32), ("round16", C.c_int32), ("load_mask", C.c_int32),
-                ("reserved", C.c_int32)]
+                ("blocked", C.c_int32), ("acc_round16", C.c_int32), ("acc_init", C.c_float)]
 
 
 class RpScalar(C.Structure):
@@ -64,6 +64,7 @@ class RowProgArgs(C.Structure):
                 ("rows_per_item", C.c_int32), ("cols", C.c_int32),
                 ("n_in", C.c_int32), ("n_red", C.c_int32), ("n_scal", C.c_int32), ("out_per_row", C.c_int32),
                 ("row_stride", C.c_int64 * (VM_MAX_IN + 1)), ("dtype", C.c_int32 * (VM_MAX_IN + 1)),
+                ("blk_stride", C.c_int64 * (VM_MAX_IN + 1)), ("n_blocks", C.c_int32), ("reserved", C.c_int32),
                 ("red", RpPhase * RP_MAX_RED), ("scal", RpScalar * RP_MAX_SCAL), ("out", RpPhase)]
 
 

@@ -803,3 +803,26 @@ def test_row_widths_the_row_kernel_does_not_take_run_step_by_step(build_lib):
     ora.load(src)
     want = ora.execute_function("layernorm_kernel", **kw)
     np.testing.assert_allclose(got["y_ptr"].astype(np.float32), want["y_ptr"].astype(np.float32), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows,cols,block,cores", [(8, 512, 256, 2), (37, 8192, 1024, 32), (12, 1024, 64, 5), (64, 256, 8, 4)])
+def test_column_blocked_layernorm_on_the_row_kernel(rows, cols, block, cores, build_lib):
+    """The reference's layer-norm example shape (f16, column blocks accumulated through loops, mean / rstd
+    per row, output block by block; rows that do not divide by the cores): three row programs, the
+    reference's bits."""
+    rng = np.random.default_rng(rows + cols + block)
+    kw = dict(X=rng.standard_normal((rows, cols)).astype(np.float16), Y=np.zeros((rows, cols), np.float16),
+              W=rng.standard_normal((rows, cols)).astype(np.float16), B=rng.standard_normal((rows, cols)).astype(np.float16),
+              Mean=np.zeros(rows, np.float16), Rstd=np.zeros(rows, np.float16), N=cols, eps=np.float16(1e-5), BLOCK_SIZE=block)
+    src = K_.layernorm_blocked(rows, cols, block, cores)
+    gpu = KTIRInterpreter()
+    gpu.load(src)
+    got = gpu.execute_function("_layer_norm_fwd_fused", **kw)
+    kinds = _kinds(gpu)
+    gpu.close()
+    assert kinds == ["row_program"] * 3
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("_layer_norm_fwd_fused", **kw)
+    for k in ("Mean", "Rstd", "Y"):
+        np.testing.assert_array_equal(got[k].view(np.uint16), want[k].view(np.uint16), err_msg=k)

@@ -50,13 +50,13 @@ def replay(stmt, dev, arena):
     r = np.arange(R_)[None, :, None]
     c = np.arange(Ccols)[None, None, :]
 
-    def tile(k):
-        mem = arena.view(npdt[a.dtype[k]])
-        idx = table[:, k][:, None, None] + r * a.row_stride[k] + c
-        return mem[idx].astype(np.float32).reshape(-1, Ccols)                  # [rows, cols]
+    def index(k, jb):
+        return (table[:, k][:, None, None] + r * a.row_stride[k] + jb * a.blk_stride[k] + c).reshape(-1, Ccols)
 
-    loads = [tile(k) for k in range(a.n_in)]
-    rows = loads[0].shape[0]
+    def tile(k, jb=0):
+        return arena.view(npdt[a.dtype[k]])[index(k, jb)].astype(np.float32)        # [rows, cols]
+
+    rows = a.n_items * R_
     red, scal, done = [], [None] * a.n_scal, 0
     for p in range(a.n_red + 1):
         while done < a.n_scal and a.scal[done].ready_after < p:
@@ -69,21 +69,31 @@ def replay(stmt, dev, arena):
             mem[idx] = out.astype(mem.dtype)
             return
         ph = a.red[p] if p < a.n_red else a.out
-        ins = loads + [np.broadcast_to(s[:, None], (rows, Ccols)) if s is not None else None for s in scal]
-        val = np.broadcast_to(run_program(ph.prog, ins), (rows, Ccols)).astype(np.float32)
+        acc = np.full((rows, Ccols), ph.acc_init, np.float32)
+        for jb in range(a.n_blocks if ph.blocked else 1):
+            ins = [tile(k, jb) for k in range(a.n_in)]
+            ins += [np.broadcast_to(s[:, None], (rows, Ccols)) if s is not None else None for s in scal]
+            val = np.broadcast_to(run_program(ph.prog, ins), (rows, Ccols)).astype(np.float32)
+            if p < a.n_red and ph.blocked:
+                acc = acc + val
+                if ph.acc_round16:
+                    acc = acc.astype(np.float16).astype(np.float32)
+            elif p < a.n_red:
+                acc = val
+            else:
+                mem = arena.view(npdt[a.dtype[a.n_in]])
+                mem[index(a.n_in, jb)] = val.astype(mem.dtype)
         if p < a.n_red:
-            red.append(fold(val, ph.op, bool(ph.round16)))
-        else:
-            mem = arena.view(npdt[a.dtype[a.n_in]])
-            idx = (table[:, a.n_in][:, None, None] + r * a.row_stride[a.n_in] + c).reshape(-1, Ccols)
-            mem[idx] = val.astype(mem.dtype)
+            red.append(fold(acc, ph.op, bool(ph.round16)))
 
 
 def plan_and_replay(src, fn, kw):
     func = KTIRParser().parse_module(src).get_function(fn)
+    scalars = {k: v for k, v in kw.items() if not isinstance(v, np.ndarray)}
+    kw = {k: v for k, v in kw.items() if isinstance(v, np.ndarray)}
     tensors = [(k, tuple(v.shape), v.dtype) for k, v in kw.items()]
     dev = RecordingDevice()
-    sess = Session(dev, func, tensors, {}, arena_ptr=0)
+    sess = Session(dev, func, tensors, scalars, arena_ptr=0)
     layout, _ = arena_layout(tensors)
     arena = np.zeros(max(o + n for o, n, _, _ in layout.values()) + 256, np.uint8)
     for name, (off, nb, _, _) in layout.items():
@@ -141,6 +151,31 @@ def test_a_weight_row_shared_by_the_rows_of_a_tile_is_an_operand_whose_rows_do_n
     want = ora.execute_function("rmsnorm_kernel", **kw)
     for k in ("y_ptr", "rstd_ptr"):
         np.testing.assert_array_equal(got[k].view(np.uint8), want[k].view(np.uint8), err_msg=k)
+
+
+@pytest.mark.parametrize("rows,cols,block,cores", [(8, 512, 256, 2), (6, 1024, 128, 3), (5, 64, 8, 5)])
+def test_column_blocked_layernorm_is_taken_row_by_row(rows, cols, block, cores):
+    """The layer norm of examples/triton-ktir/layernorm_fwd_ktir.mlir: f16 throughout, rows walked in column
+    blocks whose elementwise sums are carried through loops, mean and rstd stored per row, the output written
+    block by block in a third loop.  All three statements become row programs over rows of `cols / block`
+    blocks: blocked reduction phases (accumulate, then fold) and a blocked output phase."""
+    rng = np.random.default_rng(rows * cols)
+    kw = dict(X=rng.standard_normal((rows, cols)).astype(np.float16), Y=np.zeros((rows, cols), np.float16),
+              W=rng.standard_normal((rows, cols)).astype(np.float16), B=rng.standard_normal((rows, cols)).astype(np.float16),
+              Mean=np.zeros(rows, np.float16), Rstd=np.zeros(rows, np.float16), N=cols, eps=np.float16(1e-5), BLOCK_SIZE=block)
+    src = K.layernorm_blocked(rows, cols, block, cores)
+    got, sess = plan_and_replay(src, "_layer_norm_fwd_fused", kw)
+    mean_s, rstd_s, y_s = sess.plan.statements
+    nb = cols // block
+    assert [s.args.n_blocks for s in sess.plan.statements] == [nb] * 3
+    assert (y_s.args.n_in, y_s.args.n_red, y_s.args.n_scal, y_s.args.out.blocked, y_s.args.n_items) == (3, 2, 2, 1, rows)
+    assert list(y_s.args.blk_stride)[:4] == [block] * 4 and y_s.args.red[0].blocked and y_s.args.red[1].acc_round16
+    assert (mean_s.args.out_per_row, mean_s.args.n_red, rstd_s.args.n_red) == (1, 1, 2)
+    ora = OracleInterpreter()
+    ora.load(src)
+    want = ora.execute_function("_layer_norm_fwd_fused", **kw)
+    for k in ("Y", "Mean", "Rstd"):
+        np.testing.assert_array_equal(got[k].view(np.uint16), want[k].view(np.uint16), err_msg=k)
 
 
 def test_log_softmax_uses_two_kinds_of_reduction():
