@@ -195,6 +195,12 @@ def cases(ref_root=None):
     out["rmsnorm_weighted_32x128"] = (K.rmsnorm_rows(32, 128, 2, 4, weight=True), "rmsnorm_kernel",
                                       dict(x_ptr=(ui.standard_normal((32, 128)) * 2).astype(np.float16), w_ptr=ui.standard_normal(128).astype(np.float16),
                                            y_ptr=np.zeros((32, 128), np.float16), rstd_ptr=np.zeros(32, np.float32)))
+    # layer norm written like the reference's example: f16, rows walked in column blocks through scf.for loops
+    out["layernorm_blocked_8x512"] = (
+        K.layernorm_blocked(8, 512, 128, 3), "_layer_norm_fwd_fused",
+        dict(X=ui.standard_normal((8, 512)).astype(np.float16), Y=np.zeros((8, 512), np.float16),
+             W=ui.standard_normal((8, 512)).astype(np.float16), B=ui.standard_normal((8, 512)).astype(np.float16),
+             Mean=np.zeros(8, np.float16), Rstd=np.zeros(8, np.float16), N=512, eps=np.float16(1e-5), BLOCK_SIZE=128))
     out["gather_elements_8x16"] = (
         K.gather_elements(8, 16, 32), "gather_elements",
         dict(src_ptr=rng.standard_normal((32, 16)).astype(np.float16),

@@ -52,7 +52,8 @@ EXACT = ("vector_add_4096", "gather_elements_8x16", "matmul_f16acc_128", "elemen
          "ring_allreduce_16x16_add_f16", "ring_allreduce_16x4_add_f16", "shared_slot_store_12x5",
          "vector_add_short_4000", "sharded_scale_64x64_shift0", "sharded_scale_64x64_shift3", "sharded_center_8x256",
          "paged_gather_4x64", "region_reduce_16x37", "generic_contraction_4x8x13",
-         "gather_rows_transposed_64x16", "update_in_place_64x64", "update_in_place_16x64_flat", "rmsnorm_weighted_32x128")
+         "gather_rows_transposed_64x16", "update_in_place_64x64", "update_in_place_16x64_flat", "rmsnorm_weighted_32x128",
+         "layernorm_blocked_8x512")
 SEQUENTIAL = {"core_chain_16x64": ([(c, c + 1) for c in range(16)], ()), "accumulate_rows_4x6": ([(0, 4)], [(0, 4)])}
 CLOSE = ("layernorm_16x64", "naive_attention_32x16", "softmax_f32_64x256", "softmax_f16_64x256",
          "matmul_f32acc_128", "causal_attention_128x2")

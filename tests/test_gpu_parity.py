@@ -26,7 +26,7 @@ def _run_both(src, fn, kwargs):
 
 
 def _exact(name):
-    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain", "accumulate_rows", "rmsnorm_weighted"))
+    return name.startswith(("vector_add", "gather", "ring_allreduce", "shared_slot", "sharded_", "paged_gather", "region_reduce", "generic_contraction", "update_in_place", "core_chain", "accumulate_rows", "rmsnorm_weighted", "layernorm_blocked"))
 
 
 SUPPORTED = golden_names()
