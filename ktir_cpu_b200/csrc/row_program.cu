@@ -222,11 +222,17 @@ ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_
 enum { RP_RMS = 0, RP_MEAN = 1, RP_LAYER = 2 };
 struct rp_norm {
     int mode, has_w, has_b, out_round16;
+    int r16;                // every op (and every fold and accumulation) rounds to f16: an all-f16 kernel
+    int blocked;            // the phases walk column blocks
+    float acc_init;
     int x, w, b;            // operand indices
     int s_mean, s_scale;    // row scalar indices
 };
 
-static bool rp_is(const ktb_vm_op& o, int code) { return (o.opcode & 0xff) == code && !(o.opcode & KTB_VM_ROUND16); }
+static thread_local int rp_round16 = 0;   // rounding mode the matcher expects of every op (set at the top of a match)
+static bool rp_is(const ktb_vm_op& o, int code) {
+    return (o.opcode & 0xff) == code && ((o.opcode & KTB_VM_ROUND16) != 0) == (rp_round16 != 0);
+}
 
 // o = code(p, q) with {p, q} = {cur, other}: returns `other`, or -1
 static int rp_other(const ktb_vm_op& o, int code, int cur) {
@@ -238,13 +244,22 @@ static int rp_other(const ktb_vm_op& o, int code, int cur) {
 
 static bool rp_match_norm(const ktb_rowprog_args& a, rp_norm& m) {
     if (a.n_red < 1 || a.n_red > 2) return false;
-    for (int p = 0; p < a.n_red; ++p)
-        if (a.red[p].op != KTB_RP_ADD || a.red[p].round16) return false;
+    m = rp_norm{};
+    m.w = m.b = m.s_mean = m.s_scale = -1;
+    // one rounding mode and one way of walking the row for all phases
+    m.r16 = a.red[0].round16 != 0;
+    m.blocked = a.red[0].blocked != 0;
+    m.acc_init = a.red[0].acc_init;
+    for (int p = 0; p < a.n_red; ++p) {
+        const ktb_rp_phase& ph = a.red[p];
+        if (ph.op != KTB_RP_ADD || (ph.round16 != 0) != (m.r16 != 0) || (ph.blocked != 0) != (m.blocked != 0)) return false;
+        if (ph.blocked && ((ph.acc_round16 != 0) != (m.r16 != 0) || ph.acc_init != m.acc_init)) return false;
+    }
+    if (!a.out_per_row && (a.out.blocked != 0) != (m.blocked != 0)) return false;
+    rp_round16 = m.r16;
     const int n_in = a.n_in;
     auto is_load = [&](int r) { return r >= 0 && r < n_in; };
     auto is_scal = [&](int r) { return r >= n_in && r < n_in + a.n_scal; };
-    m = rp_norm{};
-    m.w = m.b = m.s_mean = m.s_scale = -1;
     // the sums
     const ktb_vm_program& r0 = a.red[0].prog;
     if (r0.n_ops == 0 && is_load(r0.result_reg)) {
@@ -303,7 +318,7 @@ static bool rp_match_norm(const ktb_rowprog_args& a, rp_norm& m) {
             cur = o.ops[i++].dst;
         }
     }
-    if (i < o.n_ops && (o.ops[i].opcode & 0xff) == KTB_VM_MOV && (o.ops[i].opcode & KTB_VM_ROUND16) && o.ops[i].a == cur) {
+    if (!m.r16 && i < o.n_ops && (o.ops[i].opcode & 0xff) == KTB_VM_MOV && (o.ops[i].opcode & KTB_VM_ROUND16) && o.ops[i].a == cur) {
         m.out_round16 = 1;
         cur = o.ops[i++].dst;
     }
@@ -407,6 +422,151 @@ ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m,
     }
 }
 
+// The same skeletons for rows given as NB column blocks and / or all-f16 arithmetic (the form of
+// examples/triton-ktir/layernorm_fwd_ktir.mlir): the whole row — NB blocks x NV vectors per thread — sits in
+// registers, the sums are accumulated block after block and folded, every op rounds to f16 where the tile
+// dtype is f16.  Mode, rounding and per-row output are run-time switches here (uniform branches).
+template <int NB, int NV>
+__global__ void __launch_bounds__(256, NB * NV >= 8 ? 2 : 3)
+ktb_row_norm_blocks_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m, int T, int64_t total_rows) {
+    __shared__ float xchg[256 * 8];
+    __shared__ float bcast[8];
+    __shared__ float s_red[256][KTB_RP_MAX_RED];
+    __shared__ float s_scal[256][KTB_RP_MAX_SCAL];
+    const int groups = 256 / T;
+    const int group = threadIdx.x / T;
+    const int t = threadIdx.x - group * T;
+    const bool r16 = m.r16 != 0;
+    auto rnd = [&](float v) { return r16 ? ktb_round16(v) : v; };
+    auto fold = [&](const float (&v)[NV][8]) {
+        return r16 ? row_fold<NV, 1, false, true>(v, T, t, group, xchg, bcast)
+                   : row_fold<NV, 1, false, false>(v, T, t, group, xchg, bcast);
+    };
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
+        const bool live = it * groups + group < total_rows;
+        const int64_t row = live ? it * groups + group : 0;
+        const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
+        const int64_t r = row - item * a.rows_per_item;
+        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1);
+        const int64_t x_off = offs[m.x] + r * a.row_stride[m.x];
+        const int64_t y_off = offs[a.n_in] + r * a.row_stride[a.n_in];
+        float x[NB][NV][8];
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb)
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+                rp_load8(a.arena, x_off + jb * a.blk_stride[m.x] + ((int64_t)j * T + t) * 8, a.dtype[m.x], x[jb][j]);
+
+        float mean = 0.f;
+        if (m.mode != RP_RMS) {
+            float acc[NV][8];
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float s_ = m.blocked ? rnd(m.acc_init + x[0][j][v]) : x[0][j][v];
+#pragma unroll
+                    for (int jb = 1; jb < NB; ++jb) s_ = rnd(s_ + x[jb][j][v]);
+                    acc[j][v] = s_;
+                }
+            const float r0 = fold(acc);
+            if (t == 0) s_red[group][0] = r0;
+            if (m.mode == RP_LAYER) {
+                __syncthreads();
+                if (threadIdx.x < groups) s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x]);
+                __syncthreads();
+                mean = s_scal[group][m.s_mean];
+            }
+        }
+        if (m.mode != RP_MEAN) {
+            float acc[NV][8];
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float s_ = 0.f;
+#pragma unroll
+                    for (int jb = 0; jb < NB; ++jb) {
+                        const float d = m.mode == RP_LAYER ? rnd(x[jb][j][v] - mean) : x[jb][j][v];
+                        const float q = rnd(d * d);
+                        s_ = jb == 0 ? (m.blocked ? rnd(m.acc_init + q) : q) : rnd(s_ + q);
+                    }
+                    acc[j][v] = s_;
+                }
+            const float r1 = fold(acc);
+            if (t == 0) s_red[group][m.mode == RP_LAYER ? 1 : 0] = r1;
+        }
+        __syncthreads();
+        if (threadIdx.x < groups) {
+            const int64_t grow = it * groups + threadIdx.x;
+            if (a.out_per_row) {
+                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x]);
+                if (grow < total_rows) {
+                    const int64_t gitem = (uint32_t)grow / (uint32_t)a.rows_per_item;
+                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1) + a.n_in] +
+                                       (grow - gitem * a.rows_per_item) * a.row_stride[a.n_in];
+                    if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[go] = __float2half_rn(o);
+                    else reinterpret_cast<float*>(a.arena)[go] = o;
+                }
+            } else {
+                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x]);
+            }
+        }
+        __syncthreads();
+        if (a.out_per_row) continue;
+        const float scale = s_scal[group][m.s_scale];
+        if (!live) continue;
+        const int64_t w_off = m.has_w ? offs[m.w] + r * a.row_stride[m.w] : 0;
+        const int64_t b_off = m.has_b ? offs[m.b] + r * a.row_stride[m.b] : 0;
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int64_t col = ((int64_t)j * T + t) * 8;
+                float y[8], w[8], b[8];
+                if (m.has_w) rp_load8(a.arena, w_off + jb * a.blk_stride[m.w] + col, a.dtype[m.w], w);
+                if (m.has_b) rp_load8(a.arena, b_off + jb * a.blk_stride[m.b] + col, a.dtype[m.b], b);
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float q = m.mode == RP_LAYER ? rnd(x[jb][j][v] - mean) : x[jb][j][v];
+                    q = rnd(q * scale);
+                    if (m.has_w) q = rnd(q * w[v]);
+                    if (m.has_b) q = rnd(q + b[v]);
+                    y[v] = m.out_round16 ? ktb_round16(q) : q;
+                }
+                ktb_store_vec<8>(a.arena, y_off + jb * a.blk_stride[a.n_in] + col, a.dtype[a.n_in], y);
+            }
+    }
+}
+
+template <int NB, int NV>
+static void rp_launch_norm_blocks(ktb_ctx* ctx, const ktb_rowprog_args& a, const rp_norm& m, int T, int64_t total_rows) {
+    const int groups = 256 / T;
+    const int64_t iters = (total_rows + groups - 1) / groups;
+    const unsigned blocks = (unsigned)(iters < (int64_t)ctx->sm_count * 4 ? iters : (int64_t)ctx->sm_count * 4);
+    ktb_row_norm_blocks_kernel<NB, NV><<<blocks, 256, 0, ctx->stream>>>(a, m, T, total_rows);
+}
+
+// NB blocks x NV vectors per thread, at most 8 together; false if the row does not fit that way
+static bool rp_try_norm_blocks(ktb_ctx* ctx, const ktb_rowprog_args& a, const rp_norm& m, int64_t total_rows) {
+    const int NB = m.blocked ? a.n_blocks : 1;
+    if (NB != 1 && NB != 2 && NB != 4 && NB != 8) return false;
+    const int vecs = a.cols / 8;
+    int NV = 8 / NB;                                     // as many vectors per thread as still fit ...
+    while (NV > 1 && (vecs / NV < 1 || total_rows / (256 / (vecs / NV > 256 ? 256 : vecs / NV)) < 2 * (int64_t)ctx->sm_count)) NV /= 2;
+    if (vecs / NV > 256) return false;                   // ... (fewer when there are few rows) and the row must fit a CTA
+    if (vecs % NV) return false;
+    const int T = vecs / NV;
+#define RP_NB(B, V) if (NB == B && NV == V) { rp_launch_norm_blocks<B, V>(ctx, a, m, T, total_rows); return true; }
+    RP_NB(1, 1) RP_NB(1, 2) RP_NB(1, 4) RP_NB(1, 8)
+    RP_NB(2, 1) RP_NB(2, 2) RP_NB(2, 4)
+    RP_NB(4, 1) RP_NB(4, 2)
+    RP_NB(8, 1)
+#undef RP_NB
+    return false;
+}
+
 template <int NV>
 static void rp_launch_norm(ktb_ctx* ctx, const ktb_rowprog_args& a, const rp_norm& m, unsigned blocks, int T, int64_t total_rows) {
 #define RP_NORM(M, P) ktb_row_norm_kernel<NV, M, P><<<blocks, 256, 0, ctx->stream>>>(a, m, T, total_rows)
@@ -483,7 +643,13 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
     if (blocks > n_iter) blocks = n_iter;
 #ifndef KTB_RP_NO_NORM
     rp_norm nm;
-    if (!any_blocked && rp_match_norm(a, nm)) {
+    const bool matched = rp_match_norm(a, nm);
+    if (matched && (nm.blocked || nm.r16)) {
+        if (rp_try_norm_blocks(ctx, a, nm, total_rows)) {
+            KTB_CHECK_LAUNCH(ctx, "ktb_row_norm_blocks_kernel");
+            return KTB_OK;
+        }
+    } else if (matched) {
         // four vectors per thread (the row and its squares sit in registers): two CTAs per SM
 #ifndef KTB_RP_NORM_VPT
 #define KTB_RP_NORM_VPT 4
