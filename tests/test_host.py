@@ -114,6 +114,13 @@ def test_library_exports_every_declared_symbol(build_lib):
     assert declared == set(R.SYMBOLS), "ctypes binding and header disagree"
 
 
+def test_launchers_answer_null_handles_without_touching_a_device(build_lib):
+    """Every launcher checks its two pointers before anything else: no context, no CUDA call."""
+    lib = R.lib()
+    for name in sorted(n for n in R.SYMBOLS if n.startswith("ktb_launch_") and n != "ktb_launch_count"):
+        assert getattr(lib, name)(None, None) == -2, name       # KTB_E_ARG
+
+
 @pytest.mark.parametrize("name", [n for n in golden_names() if n.startswith("paged_attention_ref")])
 def test_reference_generated_attention_text_plans_as_the_tensor_core_kernel(name):
     """Kernel text written by the reference's own generator (stored in the fixture): one fused
