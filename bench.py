@@ -284,7 +284,47 @@ class Attention(Workload):
                 4 * self.D * (S * (S + 1) // 2))
 
 
-WORKLOADS = {w.name: w for w in (Softmax(), VectorAdd(), GatherScatter(), Matmul(), Attention())}
+class LayerNorm(Workload):
+    """The reference's layer-norm example (examples/triton-ktir/layernorm_fwd_ktir.mlir: f16 throughout, rows
+    walked in column blocks, Mean and Rstd kept per row) at 4096 rows of its 8192 columns."""
+    name, func, kernel = "layernorm", "_layer_norm_fwd_fused", "ktb_row_norm_h_kernel"
+    ROWS, COLS, BLOCK, CORES = 4096, 8192, 1024, 32
+    units_per_step = ROWS * COLS
+    algo_per_step = 4 * ROWS * COLS * 2 + 2 * ROWS * 2          # X, W, B read, Y written; Mean and Rstd
+    describe = ("layer norm f16[4096,8192] in 8 column blocks of 1024 with per-element weight and bias tiles, Mean and "
+                "Rstd per row, 32 cores (row-scaled twin of the reference's 1151x8192 example)")
+    metric = "KTIR exec throughput (layer norm 4096x8192 f16, column-blocked)"
+    dtype = "f16"
+    cpu_ladder = ((128, 0.8), (512, 3.1), (2048, 12.6), (4096, 25.0))
+
+    def source(self):
+        from ktir_cpu_b200 import kernels as K
+        return K.layernorm_blocked(self.ROWS, self.COLS, self.BLOCK, self.CORES)
+
+    def _kw(self, rows, seed):
+        rng = np.random.default_rng(seed)
+        t = lambda: rng.standard_normal((rows, self.COLS), dtype=np.float32).astype(np.float16)     # noqa: E731
+        return dict(X=t(), Y=np.zeros((rows, self.COLS), np.float16), W=t(), B=t(), Mean=np.zeros(rows, np.float16),
+                    Rstd=np.zeros(rows, np.float16), N=self.COLS, eps=np.float16(1e-5), BLOCK_SIZE=self.BLOCK)
+
+    def inputs(self, rank=0):
+        return self._kw(self.ROWS, 6 + rank)
+
+    def check(self, kw, res):
+        pick = np.arange(0, self.ROWS, 131)
+        x = kw["X"][pick].astype(np.float64)
+        mean = x.mean(1, keepdims=True)
+        y = (x - mean) / np.sqrt(x.var(1, keepdims=True) + 1e-5) * kw["W"][pick].astype(np.float64) + kw["B"][pick].astype(np.float64)
+        return float(max(np.abs(res["Y"][pick].astype(np.float64) - y).max(),
+                         np.abs(res["Mean"][pick].astype(np.float64) - mean[:, 0]).max()))
+
+    def cpu_case(self, rows, seed=6):
+        from ktir_cpu_b200 import kernels as K
+        return (K.layernorm_blocked(rows, self.COLS, self.BLOCK, min(self.CORES, rows)), self.func, self._kw(rows, seed),
+                rows * self.COLS)
+
+
+WORKLOADS = {w.name: w for w in (Softmax(), VectorAdd(), GatherScatter(), Matmul(), Attention(), LayerNorm())}
 
 
 def measured_peak(bound):
@@ -936,7 +976,7 @@ def run_gpu(args, w):
     if not args.no_extras:
         extras = {}
         if dist.world == 1 and w.name == "softmax":
-            for name in ("vector_add", "gather_scatter", "matmul", "attention"):
+            for name in ("vector_add", "gather_scatter", "matmul", "attention", "layernorm"):
                 x = WORKLOADS[name]
                 it = KTIRInterpreter(device=dist.local)
                 it.load(x.source())

@@ -218,6 +218,7 @@ int ktb_launch_row_softmax(ktb_ctx* ctx, const ktb_softmax_args* args);
  * same rounding points.  cols: power of two in [8, 16384]; offsets and strides multiples of 8. */
 #define KTB_RP_MAX_RED 3
 #define KTB_RP_MAX_SCAL 4
+#define KTB_RP_MAX_SIDE 2
 enum { KTB_RP_ADD = 0, KTB_RP_MAX = 1, KTB_RP_MAXNUM = 2 };
 typedef struct {
     ktb_vm_program prog;      /* vector program; registers 0..n_in-1 = operand tiles, n_in..n_in+n_scal-1 = row scalars */
@@ -239,8 +240,14 @@ typedef struct {
     int32_t reserved;
 } ktb_rp_scalar;
 typedef struct {
+    ktb_vm_program prog;      /* one value per row; registers 0..n_red-1 = the reduction results */
+    int64_t row_stride;       /* elements between the values of consecutive rows of an item */
+    int32_t dtype;            /* KTB_F16 / KTB_F32 */
+    int32_t reserved;
+} ktb_rp_side;
+typedef struct {
     void* arena;
-    const int64_t* dev_item_offsets;   /* [n_items][n_in + 1]: operand tiles, then the output */
+    const int64_t* dev_item_offsets;   /* [n_items][n_in + 1 + n_side]: operand tiles, the output, the side results */
     int64_t n_items;
     int32_t rows_per_item, cols;
     int32_t n_in, n_red, n_scal;
@@ -251,10 +258,15 @@ typedef struct {
     int32_t dtype[KTB_VM_MAX_IN + 1];        /* KTB_F16 / KTB_F32 */
     int64_t blk_stride[KTB_VM_MAX_IN + 1];   /* elements between the column blocks of a row (blocked phases); inputs then output */
     int32_t n_blocks;                        /* column blocks per row, 1 if no phase is blocked */
-    int32_t reserved;
+    int32_t n_side;                          /* per-row results stored beside the output tile (the Mean and Rstd vectors a
+                                                layer norm keeps for its backward pass,
+                                                examples/triton-ktir/layernorm_fwd_ktir.mlir:127-128): programs over the
+                                                reduction results, evaluated once all reductions of the row are done; 0 when
+                                                out_per_row is set */
     ktb_rp_phase red[KTB_RP_MAX_RED];
     ktb_rp_scalar scal[KTB_RP_MAX_SCAL];
     ktb_rp_phase out;                        /* op unused */
+    ktb_rp_side side[KTB_RP_MAX_SIDE];
 } ktb_rowprog_args;
 int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args);
 

@@ -90,14 +90,16 @@ static __device__ __noinline__ void rp_vm8(const ktb_vm_program& prog, float* re
     }
 }
 
-// ... and on one value per row (row scalars, per-row results); registers 0.. hold the reduction results.
-static __device__ __noinline__ float rp_vm1(const ktb_vm_program& prog, const float* red) {
-    float regs[KTB_VM_REGS];
+// ... and on one value per row (row scalars, per-row results); registers 0.. hold the reduction results.  The
+// registers are the caller's words of shared memory, `stride` floats apart: as a per-thread array they were
+// local memory, which the streaming rows keep evicting from L1, and with every op waiting on L2 for its
+// operands one evaluation took several microseconds during which the whole CTA stood at a barrier.
+static __device__ __noinline__ float rp_vm1(const ktb_vm_program& prog, const float* red, float* regs, int stride) {
 #pragma unroll
-    for (int q = 0; q < KTB_VM_REGS; ++q) regs[q] = q < KTB_RP_MAX_RED ? red[q] : 0.f;
+    for (int q = 0; q < KTB_RP_MAX_RED; ++q) regs[q * stride] = red[q];
     for (int i = 0; i < prog.n_ops; ++i) {
         const ktb_vm_op op = prog.ops[i];
-        const float a = regs[op.a], b = regs[op.b];
+        const float a = regs[op.a * stride], b = regs[op.b * stride];
         float x;
         switch (op.opcode & 0xff) {                      // the handful of ops row values are made of, then the rest
             case KTB_VM_CONST: x = op.imm; break;
@@ -106,11 +108,26 @@ static __device__ __noinline__ float rp_vm1(const ktb_vm_program& prog, const fl
             case KTB_VM_MUL: x = a * b; break;
             case KTB_VM_DIV: x = a / b; break;
             case KTB_VM_SQRT: x = sqrtf(a); break;
-            default: x = ktb_vm_apply(op.opcode & 0xff, a, b, regs[op.c], op.imm);
+            default: x = ktb_vm_apply(op.opcode & 0xff, a, b, regs[op.c * stride], op.imm);
         }
-        regs[op.dst] = (op.opcode & KTB_VM_ROUND16) ? ktb_round16(x) : x;
+        regs[op.dst * stride] = (op.opcode & KTB_VM_ROUND16) ? ktb_round16(x) : x;
     }
-    return regs[prog.result_reg];
+    return regs[prog.result_reg * stride];
+}
+
+// Per-row results stored beside the output tile: programs over the finished reduction results of row `row`.
+// (`from_scal[s]` >= 0: the result is row scalar `scal[from_scal[s]]`, computed already.)
+static __device__ __forceinline__ void rp_store_sides(const ktb_rowprog_args& a, int64_t row, const float* red,
+                                                      float* vmr, int vm_stride, const float* scal = nullptr,
+                                                      const int* from_scal = nullptr) {
+    const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
+    const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1 + a.n_side) + a.n_in + 1;
+    for (int s = 0; s < a.n_side; ++s) {
+        const float o = from_scal && from_scal[s] >= 0 ? scal[from_scal[s]] : rp_vm1(a.side[s].prog, red, vmr, vm_stride);
+        const int64_t go = offs[s] + (row - item * a.rows_per_item) * a.side[s].row_stride;
+        if (a.side[s].dtype == KTB_F16) reinterpret_cast<__half*>(a.arena)[go] = __float2half_rn(o);
+        else reinterpret_cast<float*>(a.arena)[go] = o;
+    }
 }
 
 template <int NV>
@@ -134,7 +151,7 @@ ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_
         int64_t off[KTB_VM_MAX_IN + 1];
 #pragma unroll
         for (int k = 0; k <= KTB_VM_MAX_IN; ++k)
-            off[k] = k <= a.n_in ? a.dev_item_offsets[item * (a.n_in + 1) + k] + r * a.row_stride[k] : 0;
+            off[k] = k <= a.n_in ? a.dev_item_offsets[item * (a.n_in + 1 + a.n_side) + k] + r * a.row_stride[k] : 0;
 
         float red[KTB_RP_MAX_RED] = {0.f, 0.f, 0.f};
         float scal[KTB_RP_MAX_SCAL] = {0.f, 0.f, 0.f, 0.f};
@@ -142,16 +159,17 @@ ktb_row_program_kernel(const __grid_constant__ ktb_rowprog_args a, int T, int64_
         for (int p = 0; p <= a.n_red; ++p) {
             if (p == a.n_red && a.out_per_row) {
                 // one value per row: a program over the reduction results, stored by the group's first thread
-                const float o = rp_vm1(a.out.prog, red);
+                const float o = rp_vm1(a.out.prog, red, regs, 8 * 256);
                 if (live && t == 0) {
                     if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[off[a.n_in]] = __float2half_rn(o);
                     else reinterpret_cast<float*>(a.arena)[off[a.n_in]] = o;
                 }
                 break;
             }
+            if (p == a.n_red && a.n_side && live && t == 0) rp_store_sides(a, row, red, regs, 8 * 256);
             // row scalars that only need the reductions done so far
             for (; scal_done < a.n_scal && a.scal[scal_done].ready_after < p; ++scal_done)
-                scal[scal_done] = rp_vm1(a.scal[scal_done].prog, red);
+                scal[scal_done] = rp_vm1(a.scal[scal_done].prog, red, regs, 8 * 256);
             const ktb_rp_phase& ph = p < a.n_red ? a.red[p] : a.out;
             const int nb = ph.blocked ? a.n_blocks : 1;
             const bool accumulate = ph.blocked && p < a.n_red;
@@ -227,6 +245,7 @@ struct rp_norm {
     float acc_init;
     int x, w, b;            // operand indices
     int s_mean, s_scale;    // row scalar indices
+    int side_scal[KTB_RP_MAX_SIDE];   // per-row side result s is row scalar side_scal[s] (same program), or -1
 };
 
 static thread_local int rp_round16 = 0;   // rounding mode the matcher expects of every op (set at the top of a match)
@@ -242,7 +261,32 @@ static int rp_other(const ktb_vm_op& o, int code, int cur) {
     return -1;
 }
 
+static bool rp_same_program(const ktb_vm_program& p, const ktb_vm_program& q) {
+    if (p.n_in != q.n_in || p.n_ops != q.n_ops || p.result_reg != q.result_reg) return false;
+    for (int i = 0; i < p.n_ops; ++i) {
+        const ktb_vm_op &x = p.ops[i], &y = q.ops[i];
+        if (x.opcode != y.opcode || x.dst != y.dst || x.a != y.a || x.b != y.b || x.c != y.c ||
+            memcmp(&x.imm, &y.imm, sizeof(float)) != 0)
+            return false;
+    }
+    return true;
+}
+
+static bool rp_match_norm_phases(const ktb_rowprog_args& a, rp_norm& m);
 static bool rp_match_norm(const ktb_rowprog_args& a, rp_norm& m) {
+    if (!rp_match_norm_phases(a, m)) return false;
+    // a side result that is one of the two row scalars the skeleton computes anyway (the Mean and Rstd a layer
+    // norm stores are its mean and its scale) is stored from there
+    for (int s = 0; s < KTB_RP_MAX_SIDE; ++s) {
+        m.side_scal[s] = -1;
+        if (s >= a.n_side || a.out_per_row) continue;
+        if (m.s_mean >= 0 && rp_same_program(a.side[s].prog, a.scal[m.s_mean].prog)) m.side_scal[s] = m.s_mean;
+        else if (m.s_scale >= 0 && rp_same_program(a.side[s].prog, a.scal[m.s_scale].prog)) m.side_scal[s] = m.s_scale;
+    }
+    return true;
+}
+
+static bool rp_match_norm_phases(const ktb_rowprog_args& a, rp_norm& m) {
     if (a.n_red < 1 || a.n_red > 2) return false;
     m = rp_norm{};
     m.w = m.b = m.s_mean = m.s_scale = -1;
@@ -335,6 +379,7 @@ ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m,
     __shared__ float bcast[8];
     __shared__ float s_red[256][KTB_RP_MAX_RED];
     __shared__ float s_scal[256][KTB_RP_MAX_SCAL];
+    __shared__ float s_vm[KTB_VM_REGS * 256];            // registers of the row-value programs, [register][thread]
     const int groups = 256 / T;
     const int group = threadIdx.x / T;
     const int t = threadIdx.x - group * T;
@@ -344,7 +389,7 @@ ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m,
         const int64_t row = live ? it * groups + group : 0;
         const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
         const int64_t r = row - item * a.rows_per_item;
-        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1);
+        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1 + a.n_side);
         const int64_t x_off = offs[m.x] + r * a.row_stride[m.x];
         const int64_t y_off = offs[a.n_in] + r * a.row_stride[a.n_in];
         float x[NV][8];
@@ -360,8 +405,8 @@ ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m,
             if (t == 0) s_red[group][0] = r0;
             if (MODE == RP_LAYER) {
                 __syncthreads();
-                if (threadIdx.x < groups && a.scal[m.s_mean].ready_after < 1)
-                    s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x]);
+                if (threadIdx.x < groups)
+                    s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
                 __syncthreads();
                 mean = s_scal[group][m.s_mean];
             }
@@ -382,16 +427,17 @@ ktb_row_norm_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m,
         if (threadIdx.x < groups) {
             const int64_t grow = it * groups + threadIdx.x;
             if (PER_ROW) {
-                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x]);
+                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
                 if (grow < total_rows) {
                     const int64_t gitem = (uint32_t)grow / (uint32_t)a.rows_per_item;
-                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1) + a.n_in] +
+                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1 + a.n_side) + a.n_in] +
                                        (grow - gitem * a.rows_per_item) * a.row_stride[a.n_in];
                     if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[go] = __float2half_rn(o);
                     else reinterpret_cast<float*>(a.arena)[go] = o;
                 }
             } else {
-                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x]);
+                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
+                if (a.n_side && grow < total_rows) rp_store_sides(a, grow, s_red[threadIdx.x], s_vm + threadIdx.x, 256, s_scal[threadIdx.x], m.side_scal);
             }
         }
         __syncthreads();                                 // (also keeps the next iteration's sums off this one's readers)
@@ -433,6 +479,7 @@ ktb_row_norm_blocks_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_
     __shared__ float bcast[8];
     __shared__ float s_red[256][KTB_RP_MAX_RED];
     __shared__ float s_scal[256][KTB_RP_MAX_SCAL];
+    __shared__ float s_vm[KTB_VM_REGS * 256];            // registers of the row-value programs, [register][thread]
     const int groups = 256 / T;
     const int group = threadIdx.x / T;
     const int t = threadIdx.x - group * T;
@@ -448,7 +495,7 @@ ktb_row_norm_blocks_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_
         const int64_t row = live ? it * groups + group : 0;
         const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
         const int64_t r = row - item * a.rows_per_item;
-        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1);
+        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1 + a.n_side);
         const int64_t x_off = offs[m.x] + r * a.row_stride[m.x];
         const int64_t y_off = offs[a.n_in] + r * a.row_stride[a.n_in];
         float x[NB][NV][8];
@@ -474,7 +521,7 @@ ktb_row_norm_blocks_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_
             if (t == 0) s_red[group][0] = r0;
             if (m.mode == RP_LAYER) {
                 __syncthreads();
-                if (threadIdx.x < groups) s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x]);
+                if (threadIdx.x < groups) s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
                 __syncthreads();
                 mean = s_scal[group][m.s_mean];
             }
@@ -501,16 +548,17 @@ ktb_row_norm_blocks_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_
         if (threadIdx.x < groups) {
             const int64_t grow = it * groups + threadIdx.x;
             if (a.out_per_row) {
-                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x]);
+                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
                 if (grow < total_rows) {
                     const int64_t gitem = (uint32_t)grow / (uint32_t)a.rows_per_item;
-                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1) + a.n_in] +
+                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1 + a.n_side) + a.n_in] +
                                        (grow - gitem * a.rows_per_item) * a.row_stride[a.n_in];
                     if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[go] = __float2half_rn(o);
                     else reinterpret_cast<float*>(a.arena)[go] = o;
                 }
             } else {
-                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x]);
+                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
+                if (a.n_side && grow < total_rows) rp_store_sides(a, grow, s_red[threadIdx.x], s_vm + threadIdx.x, 256, s_scal[threadIdx.x], m.side_scal);
             }
         }
         __syncthreads();
@@ -540,12 +588,150 @@ ktb_row_norm_blocks_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_
     }
 }
 
+// ... and when everything is f16 — operand tiles, the stored tile, every op rounding to f16 — the arithmetic
+// runs on packed halves: an f16 add, subtract or multiply of f16 values is the f32 op rounded to f16 (the
+// double rounding cannot show: 24 >= 2 * 11 + 2 significand bits), so these are the bits of the kernel
+// above without its two conversions per op, which is what bounded it (layer norm f16[4096, 8192] in eight
+// column blocks: 176 us there).  The row sits in registers as it came from memory.
+#ifndef KTB_RP_H_OCC
+#define KTB_RP_H_OCC 4
+#endif
+template <int NB, int NV>
+__global__ void __launch_bounds__(256, KTB_RP_H_OCC)
+ktb_row_norm_h_kernel(const __grid_constant__ ktb_rowprog_args a, const rp_norm m, int T, int64_t total_rows) {
+    __shared__ float xchg[256 * 8];
+    __shared__ float bcast[8];
+    __shared__ float s_red[256][KTB_RP_MAX_RED];
+    __shared__ float s_scal[256][KTB_RP_MAX_SCAL];
+    __shared__ float s_vm[KTB_VM_REGS * 256];            // registers of the row-value programs, [register][thread]
+    const int groups = 256 / T;
+    const int group = threadIdx.x / T;
+    const int t = threadIdx.x - group * T;
+    const __half* arena = reinterpret_cast<const __half*>(a.arena);
+    const __half2 init = __float2half2_rn(m.acc_init);
+    auto load4 = [&](int64_t off, __half2 (&v)[4]) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(arena + off);
+        v[0] = *reinterpret_cast<const __half2*>(&raw.x);
+        v[1] = *reinterpret_cast<const __half2*>(&raw.y);
+        v[2] = *reinterpret_cast<const __half2*>(&raw.z);
+        v[3] = *reinterpret_cast<const __half2*>(&raw.w);
+    };
+    const int64_t n_iter = (total_rows + groups - 1) / groups;
+    for (int64_t it = blockIdx.x; it < n_iter; it += gridDim.x) {
+        const bool live = it * groups + group < total_rows;
+        const int64_t row = live ? it * groups + group : 0;
+        const int64_t item = (uint32_t)row / (uint32_t)a.rows_per_item;
+        const int64_t r = row - item * a.rows_per_item;
+        const int64_t* offs = a.dev_item_offsets + item * (a.n_in + 1 + a.n_side);
+        const int64_t x_off = offs[m.x] + r * a.row_stride[m.x];
+        const int64_t y_off = offs[a.n_in] + r * a.row_stride[a.n_in];
+        __half2 x[NB][NV][4];
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) load4(x_off + jb * a.blk_stride[m.x] + ((int64_t)j * T + t) * 8, x[jb][j]);
+
+        __half2 mean = __half2();
+        if (m.mode != RP_RMS) {
+            __half2 acc[NV][4];
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    __half2 s_ = m.blocked ? __hadd2_rn(init, x[0][j][q]) : x[0][j][q];
+#pragma unroll
+                    for (int jb = 1; jb < NB; ++jb) s_ = __hadd2_rn(s_, x[jb][j][q]);
+                    acc[j][q] = s_;
+                }
+            const float r0 = row_fold_h<NV>(acc, T, t, group, xchg, bcast);
+            if (t == 0) s_red[group][0] = r0;
+            if (m.mode == RP_LAYER) {
+                __syncthreads();
+                if (threadIdx.x < groups) s_scal[threadIdx.x][m.s_mean] = rp_vm1(a.scal[m.s_mean].prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
+                __syncthreads();
+                mean = __float2half2_rn(s_scal[group][m.s_mean]);
+            }
+        }
+        if (m.mode != RP_MEAN) {
+            __half2 acc[NV][4];
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    __half2 s_ = __half2();
+#pragma unroll
+                    for (int jb = 0; jb < NB; ++jb) {
+                        const __half2 d = m.mode == RP_LAYER ? __hsub2_rn(x[jb][j][q], mean) : x[jb][j][q];
+                        const __half2 sq = __hmul2_rn(d, d);
+                        s_ = jb == 0 ? (m.blocked ? __hadd2_rn(init, sq) : sq) : __hadd2_rn(s_, sq);
+                    }
+                    acc[j][q] = s_;
+                }
+            const float r1 = row_fold_h<NV>(acc, T, t, group, xchg, bcast);
+            if (t == 0) s_red[group][m.mode == RP_LAYER ? 1 : 0] = r1;
+        }
+        __syncthreads();
+        if (threadIdx.x < groups) {
+            const int64_t grow = it * groups + threadIdx.x;
+            if (a.out_per_row) {
+                const float o = rp_vm1(a.out.prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
+                if (grow < total_rows) {
+                    const int64_t gitem = (uint32_t)grow / (uint32_t)a.rows_per_item;
+                    const int64_t go = a.dev_item_offsets[gitem * (a.n_in + 1 + a.n_side) + a.n_in] +
+                                       (grow - gitem * a.rows_per_item) * a.row_stride[a.n_in];
+                    if (a.dtype[a.n_in] == KTB_F16) reinterpret_cast<__half*>(a.arena)[go] = __float2half_rn(o);
+                    else reinterpret_cast<float*>(a.arena)[go] = o;
+                }
+            } else {
+                s_scal[threadIdx.x][m.s_scale] = rp_vm1(a.scal[m.s_scale].prog, s_red[threadIdx.x], s_vm + threadIdx.x, 256);
+                if (a.n_side && grow < total_rows) rp_store_sides(a, grow, s_red[threadIdx.x], s_vm + threadIdx.x, 256, s_scal[threadIdx.x], m.side_scal);
+            }
+        }
+        __syncthreads();
+        if (a.out_per_row) continue;
+        const __half2 scale = __float2half2_rn(s_scal[group][m.s_scale]);
+        if (!live) continue;
+        const int64_t w_off = m.has_w ? offs[m.w] + r * a.row_stride[m.w] : 0;
+        const int64_t b_off = m.has_b ? offs[m.b] + r * a.row_stride[m.b] : 0;
+#pragma unroll
+        for (int jb = 0; jb < NB; ++jb)
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int64_t col = ((int64_t)j * T + t) * 8;
+                __half2 w[4], b[4];
+                uint4 y;
+                __half2* yh = reinterpret_cast<__half2*>(&y);
+                if (m.has_w) load4(w_off + jb * a.blk_stride[m.w] + col, w);
+                if (m.has_b) load4(b_off + jb * a.blk_stride[m.b] + col, b);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    __half2 v = m.mode == RP_LAYER ? __hsub2_rn(x[jb][j][q], mean) : x[jb][j][q];
+                    v = __hmul2_rn(v, scale);
+                    if (m.has_w) v = __hmul2_rn(v, w[q]);
+                    if (m.has_b) v = __hadd2_rn(v, b[q]);
+                    yh[q] = v;
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.arena) + y_off + jb * a.blk_stride[a.n_in] + col) = y;
+            }
+    }
+}
+
 template <int NB, int NV>
 static void rp_launch_norm_blocks(ktb_ctx* ctx, const ktb_rowprog_args& a, const rp_norm& m, int T, int64_t total_rows) {
     const int groups = 256 / T;
     const int64_t iters = (total_rows + groups - 1) / groups;
     const unsigned blocks = (unsigned)(iters < (int64_t)ctx->sm_count * 4 ? iters : (int64_t)ctx->sm_count * 4);
-    ktb_row_norm_blocks_kernel<NB, NV><<<blocks, 256, 0, ctx->stream>>>(a, m, T, total_rows);
+    // all f16, every op rounding to f16: packed-half arithmetic
+    bool halves = m.r16 && a.dtype[m.x] == KTB_F16 && (a.out_per_row || a.dtype[a.n_in] == KTB_F16) &&
+                  (!m.has_w || a.dtype[m.w] == KTB_F16) && (!m.has_b || a.dtype[m.b] == KTB_F16);
+#ifdef KTB_RP_NO_HALVES
+    halves = false;
+#endif
+    if (halves) {
+        ktb_row_norm_h_kernel<NB, NV><<<blocks, 256, 0, ctx->stream>>>(a, m, T, total_rows);
+    } else {
+        ktb_row_norm_blocks_kernel<NB, NV><<<blocks, 256, 0, ctx->stream>>>(a, m, T, total_rows);
+    }
 }
 
 // NB blocks x NV vectors per thread, at most 8 together; false if the row does not fit that way
@@ -613,7 +799,14 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
         if (a.row_stride[k] % 8 && !(k == a.n_in && a.out_per_row))
             return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "row strides must be multiples of 8 elements");
     }
+    if (a.n_side < 0 || a.n_side > KTB_RP_MAX_SIDE || (a.n_side && a.out_per_row))
+        return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad side result count");
     int rc;
+    for (int s = 0; s < a.n_side; ++s) {
+        if ((rc = rp_check_program(ctx, a.side[s].prog, a.n_red))) return rc;
+        if (a.side[s].dtype != KTB_F16 && a.side[s].dtype != KTB_F32)
+            return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "side result dtype must be f16 or f32");
+    }
     for (int p = 0; p < a.n_red; ++p) {
         if ((rc = rp_check_program(ctx, a.red[p].prog, a.n_in + a.n_scal))) return rc;
         if (a.red[p].op != KTB_RP_ADD && a.red[p].op != KTB_RP_MAX && a.red[p].op != KTB_RP_MAXNUM)

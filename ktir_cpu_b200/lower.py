@@ -788,6 +788,11 @@ def _fused_statement(dev, st: Store, arena: ArenaMap, sid: int, row_shard):
     return stmt
 
 
+# A statement that stores one value per row made of its neighbour's row reductions joins that neighbour's launch.
+# (Switch for tests that want the stand-alone per-row statements.)
+FUSE_ROW_RESULTS = True
+
+
 def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, fused: bool = True) -> Plan:
     """``row_shard = (rank, world)``: ordered scatters apply only the destination rows this rank owns.
     ``fused=False`` skips the fused kernels and runs every direct store step by step (the op-by-op
@@ -795,8 +800,18 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
     from .order import program_order
     stores = [stores[k] for k in program_order(stores, arena)]
     plan = Plan()
+    groups: List[List[Store]] = []          # the stores behind each statement (a row program may take in its neighbours)
+
+    def per_row_program(s) -> bool:
+        return s.kind == "row_program" and bool(s.args.out_per_row) and len(s.stores) == 1
+
     for st in stores:
         sid = len(plan.statements)
+        last = plan.statements[-1] if plan.statements else None
+        if FUSE_ROW_RESULTS and last is not None and last.kind == "row_program" and not last.args.out_per_row and \
+                last.try_absorb(st):
+            groups[-1].append(st)           # a per-row result of the statement before it: same launch
+            continue
         try:
             if not fused and not isinstance(st.target, IndirectAccess):
                 raise Unsupported("fused kernels disabled")
@@ -807,7 +822,16 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
                 raise
             from .lower_generic import generic_statement
             stmt = generic_statement(dev, st, arena, sid)
+        group = [st]
+        if FUSE_ROW_RESULTS and stmt.kind == "row_program" and not stmt.args.out_per_row:
+            # ... and per-row results stored just before it
+            while plan.statements and per_row_program(plan.statements[-1]) and stmt.try_absorb(groups[-1][0]):
+                for ptr in plan.statements.pop().device_arrays:
+                    dev.free(ptr)
+                group = groups.pop() + group
+            stmt.renumber(len(plan.statements))
         plan.statements.append(stmt)
+        groups.append(group)
     pts = [_points(st) for st in stores]
     if stores and row_shard is None and all(len(p[0]) <= 1 for p in pts) and \
             len({int(p[1][0]) for p in pts if len(p[0])}) <= 1:
@@ -815,12 +839,17 @@ def lower(dev: R.Device, stores: List[Store], arena: ArenaMap, row_shard=None, f
         # concurrent.  What is left is a statement whose own inputs overlap its output (an index tensor that
         # shares bytes with the destination, say): the step-by-step form reads everything before it writes,
         # as the reference's load and store ops do; a fused kernel does not promise that.
-        for sid, (stmt, st) in enumerate(zip(plan.statements, stores)):
+        redo = []
+        for stmt, group in zip(plan.statements, groups):
             if stmt.kind != "generic" and _reads_overlap_writes(stmt.footprints()):
                 from .lower_generic import generic_statement
                 for ptr in getattr(stmt, "device_arrays", []):
                     dev.free(ptr)
-                plan.statements[sid] = generic_statement(dev, st, arena, sid)
+                base = len(redo)
+                redo.extend([generic_statement(dev, st, arena, base + k) for k, st in enumerate(group)])
+            else:
+                redo.append(stmt)
+        plan.statements = redo
     else:
         fps = [f for s in plan.statements for f in s.footprints()]
         for sid, groups in check_hazards(fps).items():

@@ -520,12 +520,92 @@ class RowProgramStatement(Statement):
         a.n_items, a.rows_per_item, a.cols = table.shape[0], g0.rows, cols
         self.table = table
         self._sel, self._n_lead, self._dev, self.rounds = sel, n_lead, dev, None
+        self.stores = [store]
+        self._side_ctx = None if per_row or n_lead != 1 else dict(
+            red_index=red_index, n_red=n_red, rows_total=rows_total, axes=axes, cores=cores, rows=g0.rows,
+            div=n_blocks if absorb else 1, arena=arena, stmt_id=stmt_id)
         self.dev_table = dev.upload(table)
         a.dev_item_offsets = self.dev_table
         self.device_arrays = [self.dev_table]
         self._n_op = n_in + 1
         self._bytes = int(table.shape[0]) * g0.rows * n_blocks * (
             cols * sum(bytes_per_elem(o.acc.view.dtype) for o in operands) + (0 if per_row else cols) * bpe)
+
+    def try_absorb(self, side: Store) -> bool:
+        """Take over a neighbouring statement that stores one value per row made of this statement's own reduction
+        results (the Mean and Rstd vectors next to a layer norm's output,
+        examples/triton-ktir/layernorm_fwd_ktir.mlir:127-128): the kernel writes it from the sums it has anyway
+        instead of a second launch re-reading the rows.  False (and nothing changed) if it does not fit."""
+        c, a = self._side_ctx, self.args
+        tgt = side.target
+        if c is None or a.n_side >= R.RP_MAX_SIDE or not isinstance(tgt, Access) or tgt.coords is not None or \
+                tgt.view.dtype not in F_DT:
+            return False
+        rows_total, axes = c["rows_total"], c["axes"]
+        if _prod(tgt.shape) != rows_total:
+            return False
+        # the same iteration points: the side store sits at this statement's loop depth, or one level above the
+        # loop over column blocks this statement has absorbed
+        s_axes = tuple(side.axes)
+        if s_axes != (axes if c["div"] == 1 else axes[:-1]):
+            return False
+        s_sel, s_cores = _points(side)
+        if len(s_sel) != len(self._sel) or (s_sel != self._sel // c["div"]).any() or (s_cores != c["cores"]).any():
+            return False
+        # its value: a program over this statement's reduction results, nothing else
+        red_index = c["red_index"]
+
+        def only_known(n: Node, seen) -> bool:
+            n = strip_views(n)
+            if id(n) in seen or id(n) in red_index:
+                return True
+            seen.add(id(n))
+            if n.kind == "reduce" or n.kind == "load" or n.kind not in ("const", "cast", "ew", "bcast", "extract"):
+                return False
+            return all(only_known(x, seen) for x in n.args if isinstance(x, Node))
+
+        if not only_known(side.value, set()):
+            return False
+        try:
+            prog = _Compiler(dict(red_index), c["n_red"], rows_total).compile(side.value)
+        except Unsupported:
+            return False
+        big = [d for d, n_ in enumerate(tgt.shape) if n_ > 1]
+        if len(big) > 1 or (big and tgt.shape[big[0]] != c["rows"]):
+            return False
+        stride = int(tgt.strides[big[0]]) if big else 1
+        from .trace import iv_full
+        offs = np.asarray(iv_full(tgt.off, s_axes)).reshape(-1).astype(np.int64)[s_sel]
+        bpe = bytes_per_elem(tgt.view.dtype)
+        rs = (offs[:, None] + np.arange(c["rows"], dtype=np.int64)[None, :] * stride).reshape(-1) * bpe
+        # moving the store into this launch must not change what anything reads: its bytes are apart from
+        # everything the statement touches
+        for f in self.fps:
+            if len(f.starts) and len(rs) and _runs_overlap(rs, rs + bpe, f.starts, f.ends):
+                return False
+        if len(offs):
+            c["arena"].check_range(int(offs.min()), int(offs.max()) + (c["rows"] - 1) * stride + 1, tgt.view.dtype,
+                                   "Scatter to")
+        k = a.n_side
+        a.side[k].prog, a.side[k].row_stride, a.side[k].dtype = prog, stride, R.DTYPE_CODE[tgt.view.dtype]
+        a.n_side = k + 1
+        self.fps.append(Footprint(rs, rs + bpe, np.repeat(self._sel, c["rows"]), np.repeat(c["cores"], c["rows"]),
+                                  True, c["stmt_id"]))
+        self.table = np.ascontiguousarray(np.concatenate([self.table, offs[:, None]], axis=1))
+        self._dev.free(self.dev_table)
+        self.dev_table = self._dev.upload(self.table)
+        a.dev_item_offsets = self.dev_table
+        self.device_arrays = [self.dev_table]
+        self._n_op += 1
+        self._bytes += len(rs) * bpe
+        self.stores.append(side)
+        return True
+
+    def renumber(self, stmt_id: int):
+        for f in self.fps:
+            f.stmt = stmt_id
+        if self._side_ctx is not None:
+            self._side_ctx["stmt_id"] = stmt_id
 
     def launch(self, dev, arena_ptr):
         self.args.arena = arena_ptr
@@ -546,6 +626,17 @@ class RowProgramStatement(Statement):
 
     def bytes_moved(self):
         return self._bytes
+
+
+def _runs_overlap(s0, e0, s1, e1) -> bool:
+    """True if some run [s0, e0) meets some run [s1, e1)."""
+    if s0.min() >= e1.max() or s1.min() >= e0.max():
+        return False
+    order = np.argsort(s1, kind="stable")
+    s1, e1 = s1[order], np.maximum.accumulate(e1[order])
+    k = np.searchsorted(s1, e0, side="left") - 1          # last run of the second set that starts before each e0
+    ok = k >= 0
+    return bool((e1[k[ok]] > s0[ok]).any())
 
 
 def try_lower_row_program(dev, store: Store, arena: ArenaMap, stmt_id: int):

@@ -46,7 +46,7 @@ class EwArgs(C.Structure):
                 ("vector_ok", C.c_int32), ("program", VmProgram)]
 
 
-RP_MAX_RED, RP_MAX_SCAL = 3, 4
+RP_MAX_RED, RP_MAX_SCAL, RP_MAX_SIDE = 3, 4, 2
 RP_OPS = {"add": 0, "max": 1, "maxnum": 2}
 
 
@@ -59,13 +59,18 @@ class RpScalar(C.Structure):
     _fields_ = [("prog", VmProgram), ("ready_after", C.c_int32), ("reserved", C.c_int32)]
 
 
+class RpSide(C.Structure):
+    _fields_ = [("prog", VmProgram), ("row_stride", C.c_int64), ("dtype", C.c_int32), ("reserved", C.c_int32)]
+
+
 class RowProgArgs(C.Structure):
     _fields_ = [("arena", C.c_void_p), ("dev_item_offsets", C.c_void_p), ("n_items", C.c_int64),
                 ("rows_per_item", C.c_int32), ("cols", C.c_int32),
                 ("n_in", C.c_int32), ("n_red", C.c_int32), ("n_scal", C.c_int32), ("out_per_row", C.c_int32),
                 ("row_stride", C.c_int64 * (VM_MAX_IN + 1)), ("dtype", C.c_int32 * (VM_MAX_IN + 1)),
-                ("blk_stride", C.c_int64 * (VM_MAX_IN + 1)), ("n_blocks", C.c_int32), ("reserved", C.c_int32),
-                ("red", RpPhase * RP_MAX_RED), ("scal", RpScalar * RP_MAX_SCAL), ("out", RpPhase)]
+                ("blk_stride", C.c_int64 * (VM_MAX_IN + 1)), ("n_blocks", C.c_int32), ("n_side", C.c_int32),
+                ("red", RpPhase * RP_MAX_RED), ("scal", RpScalar * RP_MAX_SCAL), ("out", RpPhase),
+                ("side", RpSide * RP_MAX_SIDE)]
 
 
 class SoftmaxArgs(C.Structure):

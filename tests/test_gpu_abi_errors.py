@@ -153,6 +153,16 @@ def test_row_program_launcher_refuses_bad_phases(build_lib):
     a = _copy(stmt.args, sess.arena)
     a.row_stride[0] = cols + 4
     _refused(dev, launch, a, E_UNSUPPORTED, "row_program", "multiples of 8")
+    assert stmt.args.n_side == 1                     # the row means leave with this launch
+    a = _copy(stmt.args, sess.arena)
+    a.n_side = R.RP_MAX_SIDE + 1
+    _refused(dev, launch, a, E_ARG, "row_program", "side result")
+    a = _copy(stmt.args, sess.arena)
+    a.side[0].dtype = R.DTYPE_CODE["i32"]
+    _refused(dev, launch, a, E_UNSUPPORTED, "row_program", "side result dtype")
+    a = _copy(stmt.args, sess.arena)
+    a.side[0].prog.n_in = a.n_red + 1
+    _refused(dev, launch, a, E_ARG, "row_program", "program header")
     _still_matches(interp, src, "layernorm_kernel", kw, {"y_ptr": True, "mean_ptr": True})
     interp.close()
 

@@ -719,8 +719,17 @@ def _kinds(gpu):
     return [s.kind for sess in gpu._sessions.values() for s in sess.plan.statements]
 
 
+@pytest.fixture(params=[True, False], ids=["one_launch", "per_row_statements"])
+def fuse_row_results(request, monkeypatch):
+    """Per-row results (row means, 1/std) stored by the launch whose reductions they come from, or each by a
+    statement of its own."""
+    from ktir_cpu_b200 import lower as L
+    monkeypatch.setattr(L, "FUSE_ROW_RESULTS", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("rows,cols,cores", [(64, 256, 4), (96, 1024, 8), (24, 4096, 4), (6, 16384, 2), (40, 8, 5), (33, 64, 3)])
-def test_layernorm_runs_as_fused_row_programs(rows, cols, cores, build_lib):
+def test_layernorm_runs_as_fused_row_programs(rows, cols, cores, fuse_row_results, build_lib):
     """Layer norm (two reductions, two per-row values broadcast back, per-column weight and bias) and its row
     means (a tile with one value per row): both statements on the fused row kernel, compared with the oracle.
     Sums are folded in the reference's halving order and every op rounds where the reference rounds, so the
@@ -735,7 +744,7 @@ def test_layernorm_runs_as_fused_row_programs(rows, cols, cores, build_lib):
     got = gpu.execute_function("layernorm_kernel", **kw)
     kinds = _kinds(gpu)
     gpu.close()
-    assert kinds == ["row_program", "row_program"]
+    assert kinds == ["row_program"] * (1 if fuse_row_results else 2)
     ora = OracleInterpreter()
     ora.load(src)
     want = ora.execute_function("layernorm_kernel", **kw)
@@ -745,7 +754,7 @@ def test_layernorm_runs_as_fused_row_programs(rows, cols, cores, build_lib):
 
 @pytest.mark.parametrize("weight", [False, True])
 @pytest.mark.parametrize("rows,cols,cores,tile_rows", [(64, 256, 4, 4), (128, 2048, 4, 8), (12, 512, 3, 2), (64, 32, 2, 16)])
-def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, weight, build_lib):
+def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, weight, fuse_row_results, build_lib):
     """RMS norm on tiles of several rows, with and without a weight row that all rows of a tile share."""
     rng = np.random.default_rng(rows * 7 + cols)
     kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2).astype(np.float16))
@@ -758,7 +767,7 @@ def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, weight, bui
     got = gpu.execute_function("rmsnorm_kernel", **kw)
     kinds = _kinds(gpu)
     gpu.close()
-    assert kinds == ["row_program", "row_program"]
+    assert kinds == ["row_program"] * (1 if fuse_row_results else 2)
     ora = OracleInterpreter()
     ora.load(src)
     want = ora.execute_function("rmsnorm_kernel", **kw)
@@ -806,7 +815,7 @@ def test_row_widths_the_row_kernel_does_not_take_run_step_by_step(build_lib):
 
 
 @pytest.mark.parametrize("rows,cols,block,cores", [(8, 512, 256, 2), (37, 8192, 1024, 32), (12, 1024, 64, 5), (64, 256, 8, 4)])
-def test_column_blocked_layernorm_on_the_row_kernel(rows, cols, block, cores, build_lib):
+def test_column_blocked_layernorm_on_the_row_kernel(rows, cols, block, cores, fuse_row_results, build_lib):
     """The reference's layer-norm example shape (f16, column blocks accumulated through loops, mean / rstd
     per row, output block by block; rows that do not divide by the cores): three row programs, the
     reference's bits."""
@@ -820,7 +829,7 @@ def test_column_blocked_layernorm_on_the_row_kernel(rows, cols, block, cores, bu
     got = gpu.execute_function("_layer_norm_fwd_fused", **kw)
     kinds = _kinds(gpu)
     gpu.close()
-    assert kinds == ["row_program"] * 3
+    assert kinds == ["row_program"] * (1 if fuse_row_results else 3)
     ora = OracleInterpreter()
     ora.load(src)
     want = ora.execute_function("_layer_norm_fwd_fused", **kw)

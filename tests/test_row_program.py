@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 
 from ktir_cpu_b200 import kernels as K
+from ktir_cpu_b200 import lower as L
 from ktir_cpu_b200 import runtime as R
 from ktir_cpu_b200.interpreter import Session, arena_layout
 from ktir_cpu_b200.parser import KTIRParser
@@ -44,7 +45,7 @@ def fold(x, op, r16):
 
 def replay(stmt, dev, arena):
     a = stmt.args
-    table = dev.arrays[a.dev_item_offsets].reshape(a.n_items, a.n_in + 1)
+    table = dev.arrays[a.dev_item_offsets].reshape(a.n_items, a.n_in + 1 + a.n_side)
     npdt = {R.DTYPE_CODE["f16"]: np.float16, R.DTYPE_CODE["f32"]: np.float32}
     R_, Ccols = a.rows_per_item, a.cols
     r = np.arange(R_)[None, :, None]
@@ -68,6 +69,11 @@ def replay(stmt, dev, arena):
             idx = (table[:, a.n_in][:, None] + np.arange(R_)[None, :] * a.row_stride[a.n_in]).reshape(-1)
             mem[idx] = out.astype(mem.dtype)
             return
+        if p == a.n_red:
+            for s in range(a.n_side):               # per-row results stored beside the output tile
+                mem = arena.view(npdt[a.side[s].dtype])
+                idx = (table[:, a.n_in + 1 + s][:, None] + np.arange(R_)[None, :] * a.side[s].row_stride).reshape(-1)
+                mem[idx] = run_program(a.side[s].prog, red).astype(mem.dtype)
         ph = a.red[p] if p < a.n_red else a.out
         acc = np.full((rows, Ccols), ph.acc_init, np.float32)
         for jb in range(a.n_blocks if ph.blocked else 1):
@@ -104,17 +110,28 @@ def plan_and_replay(src, fn, kw):
     return {name: arena[off:off + nb].view(dt).reshape(shape).copy() for name, (off, nb, shape, dt) in layout.items()}, sess
 
 
+@pytest.fixture(params=[True, False], ids=["one_launch", "per_row_statements"])
+def fuse_row_results(request, monkeypatch):
+    """With and without per-row results joining the launch of the statement whose reductions they are."""
+    monkeypatch.setattr(L, "FUSE_ROW_RESULTS", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("rows,cols,cores", [(16, 64, 4), (12, 1024, 3), (8, 8, 2)])
-def test_layernorm_phases_give_the_oracle_bits(rows, cols, cores):
+def test_layernorm_phases_give_the_oracle_bits(rows, cols, cores, fuse_row_results):
     rng = np.random.default_rng(rows + cols)
     kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2 + 1).astype(np.float16), w_ptr=rng.standard_normal(cols).astype(np.float16),
               b_ptr=rng.standard_normal(cols).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
               mean_ptr=np.zeros(rows, np.float32))
     src = K.layernorm_rows(rows, cols, cores)
     got, sess = plan_and_replay(src, "layernorm_kernel", kw)
-    y_stmt, m_stmt = sess.plan.statements
+    if fuse_row_results:
+        y_stmt, = sess.plan.statements          # the row means leave with the launch that sums the rows anyway
+        assert (y_stmt.args.n_side, y_stmt.args.side[0].dtype, y_stmt.args.side[0].row_stride) == (1, R.DTYPE_CODE["f32"], 1)
+    else:
+        y_stmt, m_stmt = sess.plan.statements
+        assert (m_stmt.args.n_red, m_stmt.args.n_scal, m_stmt.args.out_per_row) == (1, 0, 1)
     assert (y_stmt.args.n_red, y_stmt.args.n_scal, y_stmt.args.out_per_row) == (2, 2, 0)
-    assert (m_stmt.args.n_red, m_stmt.args.n_scal, m_stmt.args.out_per_row) == (1, 0, 1)
     assert y_stmt.args.red[0].prog.n_ops == 0 and y_stmt.args.out.load_mask == 0b111      # sum of x as it is; x, w, b at the end
     ora = OracleInterpreter()
     ora.load(src)
@@ -124,13 +141,14 @@ def test_layernorm_phases_give_the_oracle_bits(rows, cols, cores):
 
 
 @pytest.mark.parametrize("rows,cols,cores,tile_rows", [(16, 64, 2, 4), (8, 256, 1, 8)])
-def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows):
+def test_rmsnorm_tiles_of_several_rows(rows, cols, cores, tile_rows, fuse_row_results):
     rng = np.random.default_rng(cols)
     kw = dict(x_ptr=(rng.standard_normal((rows, cols)) * 2).astype(np.float16), y_ptr=np.zeros((rows, cols), np.float16),
               rstd_ptr=np.zeros(rows, np.float32))
     src = K.rmsnorm_rows(rows, cols, cores, tile_rows)
     got, sess = plan_and_replay(src, "rmsnorm_kernel", kw)
-    assert [s.args.rows_per_item for s in sess.plan.statements] == [tile_rows, tile_rows]
+    assert [s.args.rows_per_item for s in sess.plan.statements] == [tile_rows] * (1 if fuse_row_results else 2)
+    assert sess.plan.statements[0].args.n_side == int(fuse_row_results)
     ora = OracleInterpreter()
     ora.load(src)
     want = ora.execute_function("rmsnorm_kernel", **kw)
@@ -154,7 +172,7 @@ def test_a_weight_row_shared_by_the_rows_of_a_tile_is_an_operand_whose_rows_do_n
 
 
 @pytest.mark.parametrize("rows,cols,block,cores", [(8, 512, 256, 2), (6, 1024, 128, 3), (5, 64, 8, 5)])
-def test_column_blocked_layernorm_is_taken_row_by_row(rows, cols, block, cores):
+def test_column_blocked_layernorm_is_taken_row_by_row(rows, cols, block, cores, fuse_row_results):
     """The layer norm of examples/triton-ktir/layernorm_fwd_ktir.mlir: f16 throughout, rows walked in column
     blocks whose elementwise sums are carried through loops, mean and rstd stored per row, the output written
     block by block in a third loop.  All three statements become row programs over rows of `cols / block`
@@ -165,12 +183,18 @@ def test_column_blocked_layernorm_is_taken_row_by_row(rows, cols, block, cores):
               Mean=np.zeros(rows, np.float16), Rstd=np.zeros(rows, np.float16), N=cols, eps=np.float16(1e-5), BLOCK_SIZE=block)
     src = K.layernorm_blocked(rows, cols, block, cores)
     got, sess = plan_and_replay(src, "_layer_norm_fwd_fused", kw)
-    mean_s, rstd_s, y_s = sess.plan.statements
     nb = cols // block
-    assert [s.args.n_blocks for s in sess.plan.statements] == [nb] * 3
+    if fuse_row_results:
+        # Mean and Rstd are stored outside the loop over column blocks that the output statement has absorbed:
+        # both leave with its launch, from the sums it folds anyway
+        y_s, = sess.plan.statements
+        assert (y_s.args.n_side, y_s.args.n_blocks, y_s.table.shape) == (2, nb, (rows, 6))
+    else:
+        mean_s, rstd_s, y_s = sess.plan.statements
+        assert [s.args.n_blocks for s in sess.plan.statements] == [nb] * 3
+        assert (mean_s.args.out_per_row, mean_s.args.n_red, rstd_s.args.n_red) == (1, 1, 2)
     assert (y_s.args.n_in, y_s.args.n_red, y_s.args.n_scal, y_s.args.out.blocked, y_s.args.n_items) == (3, 2, 2, 1, rows)
     assert list(y_s.args.blk_stride)[:4] == [block] * 4 and y_s.args.red[0].blocked and y_s.args.red[1].acc_round16
-    assert (mean_s.args.out_per_row, mean_s.args.n_red, rstd_s.args.n_red) == (1, 1, 2)
     ora = OracleInterpreter()
     ora.load(src)
     want = ora.execute_function("_layer_norm_fwd_fused", **kw)
