@@ -227,3 +227,21 @@ def test_registers_are_reused_and_misfits_are_refused():
     out = sess.plan.statements[0].args.out.prog
     regs = {o.dst for o in list(out.ops)[:out.n_ops]}
     assert out.n_ops == 5 and len(regs) == 1                     # sub, mul, mul, add, round: one temporary, reused
+
+
+def test_run_overlap_check_behind_the_absorption_of_per_row_results():
+    """A per-row result joins its neighbour's launch only if its bytes are apart from everything that launch
+    touches; the check takes sorted or unsorted runs, nested and touching ones."""
+    from ktir_cpu_b200.lower_rowprog import _runs_overlap
+    a = lambda *v: np.array(v, np.int64)                                     # noqa: E731
+    assert not _runs_overlap(a(0, 10), a(4, 14), a(4, 14), a(10, 20))        # touching ends do not meet
+    assert _runs_overlap(a(0, 10), a(4, 15), a(4, 14), a(10, 20))
+    assert _runs_overlap(a(100), a(101), a(300, 0), a(400, 1000))            # inside a long run listed second
+    assert not _runs_overlap(a(1000), a(1001), a(300, 0), a(400, 1000))
+    assert not _runs_overlap(a(5000, 6000), a(5002, 6002), a(0, 64), a(64, 128))   # apart altogether
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        s0 = rng.integers(0, 200, 5); e0 = s0 + rng.integers(1, 8, 5)
+        s1 = rng.integers(0, 200, 7); e1 = s1 + rng.integers(1, 30, 7)
+        want = bool(((s0[:, None] < e1[None, :]) & (s1[None, :] < e0[:, None])).any())
+        assert _runs_overlap(s0, e0, s1, e1) == want
