@@ -146,14 +146,17 @@ enum {
     KTB_VM_MAX, KTB_VM_MAXNUM, KTB_VM_MIN, KTB_VM_MINNUM, KTB_VM_NEG, KTB_VM_ABS,
     KTB_VM_EXP, KTB_VM_LOG, KTB_VM_LOG2, KTB_VM_SQRT, KTB_VM_RSQRT, KTB_VM_TANH,
     KTB_VM_SIN, KTB_VM_COS, KTB_VM_FMA, KTB_VM_NOPS,
-    KTB_VM_ROUND16 = 0x100
+    KTB_VM_ROUND16 = 0x100,
+    /* row-value programs of ktb_launch_row_program only (row scalars, per-row and side results): operand a / b of
+       the op is `imm` instead of a register, which saves the KTB_VM_CONST op in front of it */
+    KTB_VM_IMM_A = 0x200, KTB_VM_IMM_B = 0x400
 };
 #define KTB_VM_MAX_OPS 12
 #define KTB_VM_MAX_IN 4
 #define KTB_VM_REGS 8
 
 typedef struct {
-    int32_t opcode;      /* KTB_VM_* | optional KTB_VM_ROUND16 */
+    int32_t opcode;      /* KTB_VM_* | optional KTB_VM_ROUND16 | (row-value programs) KTB_VM_IMM_A / _B */
     int32_t dst, a, b, c;
     float imm;
 } ktb_vm_op;

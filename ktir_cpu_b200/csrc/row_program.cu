@@ -99,7 +99,8 @@ static __device__ __forceinline__ float rp_vm1_here(const ktb_vm_program& prog, 
     for (int q = 0; q < KTB_RP_MAX_RED; ++q) regs[q * stride] = red[q];
     for (int i = 0; i < prog.n_ops; ++i) {
         const ktb_vm_op op = prog.ops[i];
-        const float a = regs[op.a * stride], b = regs[op.b * stride];
+        const float a = (op.opcode & KTB_VM_IMM_A) ? op.imm : regs[op.a * stride];
+        const float b = (op.opcode & KTB_VM_IMM_B) ? op.imm : regs[op.b * stride];
         float x;
         switch (op.opcode & 0xff) {                      // the handful of ops row values are made of, then the rest
             case KTB_VM_CONST: x = op.imm; break;
@@ -773,7 +774,7 @@ static void rp_launch_norm(ktb_ctx* ctx, const ktb_rowprog_args& a, const rp_nor
 #undef RP_NORM
 }
 
-static int rp_check_program(ktb_ctx* ctx, const ktb_vm_program& p, int n_in) {
+static int rp_check_program(ktb_ctx* ctx, const ktb_vm_program& p, int n_in, bool row_value = false) {
     if (p.n_in != n_in || p.n_ops < 0 || p.n_ops > KTB_VM_MAX_OPS || p.result_reg < 0 || p.result_reg >= KTB_VM_REGS)
         return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad program header");
     for (int i = 0; i < p.n_ops; ++i) {
@@ -781,6 +782,8 @@ static int rp_check_program(ktb_ctx* ctx, const ktb_vm_program& p, int n_in) {
         if ((o.opcode & 0xff) >= KTB_VM_NOPS || o.dst < 0 || o.dst >= KTB_VM_REGS || o.a < 0 || o.a >= KTB_VM_REGS ||
             o.b < 0 || o.b >= KTB_VM_REGS || o.c < 0 || o.c >= KTB_VM_REGS)
             return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad program op");
+        if (!row_value && (o.opcode & (KTB_VM_IMM_A | KTB_VM_IMM_B)))
+            return ktb_fail(ctx, KTB_E_ARG, "row_program", "immediate operands are for row-value programs only");
     }
     return KTB_OK;
 }
@@ -810,7 +813,7 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
         return ktb_fail(ctx, KTB_E_ARG, "row_program", "bad side result count");
     int rc;
     for (int s = 0; s < a.n_side; ++s) {
-        if ((rc = rp_check_program(ctx, a.side[s].prog, a.n_red))) return rc;
+        if ((rc = rp_check_program(ctx, a.side[s].prog, a.n_red, true))) return rc;
         if (a.side[s].dtype != KTB_F16 && a.side[s].dtype != KTB_F32)
             return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "side result dtype must be f16 or f32");
     }
@@ -819,9 +822,9 @@ extern "C" int ktb_launch_row_program(ktb_ctx* ctx, const ktb_rowprog_args* args
         if (a.red[p].op != KTB_RP_ADD && a.red[p].op != KTB_RP_MAX && a.red[p].op != KTB_RP_MAXNUM)
             return ktb_fail(ctx, KTB_E_UNSUPPORTED, "row_program", "reduction must be add or max");
     }
-    if ((rc = rp_check_program(ctx, a.out.prog, a.out_per_row ? a.n_red : a.n_in + a.n_scal))) return rc;
+    if ((rc = rp_check_program(ctx, a.out.prog, a.out_per_row ? a.n_red : a.n_in + a.n_scal, a.out_per_row != 0))) return rc;
     for (int s = 0; s < a.n_scal; ++s) {
-        if ((rc = rp_check_program(ctx, a.scal[s].prog, a.n_red))) return rc;
+        if ((rc = rp_check_program(ctx, a.scal[s].prog, a.n_red, true))) return rc;
         if (a.scal[s].ready_after < -1 || a.scal[s].ready_after >= a.n_red || (s && a.scal[s].ready_after < a.scal[s - 1].ready_after))
             return ktb_fail(ctx, KTB_E_ARG, "row_program", "row scalars must be sorted by the last reduction they read");
     }

@@ -64,8 +64,10 @@ class _Compiler:
     """Register program of one expression.  ``leaves`` maps node ids to input registers; temporaries are
     handed back as soon as their last user has been emitted, so long chains fit the eight registers."""
 
-    def __init__(self, leaves: Dict[int, int], n_in: int, elems: int):
-        self.leaves, self.n_in, self.elems = leaves, n_in, elems
+    def __init__(self, leaves: Dict[int, int], n_in: int, elems: int, immediates: bool = False):
+        """``immediates``: a constant operand of a two-operand op rides in the op itself (row-value programs, whose
+        evaluator takes them; saves the CONST op in front)."""
+        self.leaves, self.n_in, self.elems, self.immediates = leaves, n_in, elems, immediates
         self.ops: List[Tuple[int, int, int, int, int, float]] = []
         self.reg_of: Dict[int, int] = {}
         self.uses: Dict[int, int] = {}
@@ -127,6 +129,25 @@ class _Compiler:
                 ca = _canon(a)
                 if ca.kind != "const" and id(ca) not in self.leaves and _prod(ca.shape) != self.elems:
                     raise Unsupported("operand of another shape in a row program")
+            imm_at = None
+            if self.immediates and op in _VM_BIN and len(n.args) == 2:
+                consts = [k for k, a in enumerate(n.args) if _canon(a).kind == "const" and _canon(a).attrs.get("list") is None]
+                if len(consts) == 1:
+                    imm_at = consts[0]
+            if imm_at is not None:
+                other = n.args[1 - imm_at]
+                ro = self._visit(other)
+                self._release(other)
+                self.uses[id(_canon(n.args[imm_at]))] -= 1
+                cn = _canon(n.args[imm_at])
+                v = float(np.float16(cn.attrs["value"])) if cn.dtype == "f16" else float(np.float32(cn.attrs["value"]))
+                r = self._alloc()
+                self.ops.append((R.VM[_VM_BIN[op]] | (R.VM_ROUND16 if r16 else 0) | (R.VM_IMM_A if imm_at == 0 else R.VM_IMM_B),
+                                 r, ro, ro, 0, v))
+                if len(self.ops) > R.VM_MAX_OPS:
+                    raise Unsupported("row program phase longer than 12 ops")
+                self.reg_of[id(n)] = r
+                return r
             regs = [self._visit(a) for a in n.args]
             for a in n.args:
                 self._release(a)
@@ -412,7 +433,7 @@ class RowProgramStatement(Statement):
             return memo[id(n)]
 
         def scalar_program(root: Node) -> R.VmProgram:
-            return _Compiler(dict(red_index), n_red, rows_total).compile(root)
+            return _Compiler(dict(red_index), n_red, rows_total, immediates=True).compile(root)
 
         scal_progs = sorted(((last_reduce(s_.args[0], {}), k, scalar_program(s_.args[0]), s_) for k, s_ in enumerate(scalars)),
                             key=lambda x: x[:2])
@@ -567,7 +588,7 @@ class RowProgramStatement(Statement):
         if not only_known(side.value, set()):
             return False
         try:
-            prog = _Compiler(dict(red_index), c["n_red"], rows_total).compile(side.value)
+            prog = _Compiler(dict(red_index), c["n_red"], rows_total, immediates=True).compile(side.value)
         except Unsupported:
             return False
         big = [d for d, n_ in enumerate(tgt.shape) if n_ > 1]

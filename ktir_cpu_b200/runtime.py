@@ -22,6 +22,7 @@ VM_OPS = ["MOV", "CONST", "ADD", "SUB", "MUL", "DIV", "MAX", "MAXNUM", "MIN", "M
           "EXP", "LOG", "LOG2", "SQRT", "RSQRT", "TANH", "SIN", "COS", "FMA"]
 VM = {n: i for i, n in enumerate(VM_OPS)}
 VM_ROUND16 = 0x100
+VM_IMM_A, VM_IMM_B = 0x200, 0x400          # row-value programs: operand a / b is the op's immediate
 
 
 class Status(C.Structure):

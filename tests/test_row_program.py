@@ -20,7 +20,8 @@ def run_program(prog, inputs):
     """``inputs``: list of float32 arrays (one per input register); returns the result register."""
     regs = list(inputs) + [None] * (R.VM_REGS - len(inputs))
     for o in list(prog.ops)[:prog.n_ops]:
-        a, b = regs[o.a], regs[o.b]
+        a = np.float32(o.imm) if o.opcode & R.VM_IMM_A else regs[o.a]
+        b = np.float32(o.imm) if o.opcode & R.VM_IMM_B else regs[o.b]
         name = NAMES[o.opcode & 0xff]
         with np.errstate(all="ignore"):
             x = {"MOV": lambda: a, "CONST": lambda: np.float32(o.imm), "ADD": lambda: a + b, "SUB": lambda: a - b,
