@@ -153,6 +153,9 @@ def test_row_program_launcher_refuses_bad_phases(build_lib):
     a = _copy(stmt.args, sess.arena)
     a.row_stride[0] = cols + 4
     _refused(dev, launch, a, E_UNSUPPORTED, "row_program", "multiples of 8")
+    a = _copy(stmt.args, sess.arena)
+    a.red[1].prog.ops[0].opcode |= R.VM_IMM_B        # immediates are for the row-value programs
+    _refused(dev, launch, a, E_ARG, "row_program", "immediate operands")
     assert stmt.args.n_side == 1                     # the row means leave with this launch
     a = _copy(stmt.args, sess.arena)
     a.n_side = R.RP_MAX_SIDE + 1
